@@ -1,0 +1,7 @@
+"""bam_b200 -- B200-native GPU storage hot path (page cache + parallel NVMe queues).
+
+Host-side mirror of the reference's C++ host objects (Controller, page_cache_t, range_t /
+array_t) over the C ABI of libbam_b200.so.  The CUDA library is mandatory.
+"""
+from ._lib import BamError, CacheStats, StatusOut, load  # noqa: F401
+from .host import Array, Controller, PageCache  # noqa: F401

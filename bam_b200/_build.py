@@ -1,0 +1,46 @@
+"""Build libbam_b200.so in-tree with nvcc for sm_100a (explicit command, no JIT cache)."""
+import os
+import shutil
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libbam_b200.so")
+SOURCES = ["bam_lib.cu"]
+
+
+def _newer_than(target, deps):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def _deps():
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+    inc = os.path.join(ROOT, "include")
+    for base, _, files in os.walk(inc):
+        deps += [os.path.join(base, f) for f in files]
+    return deps
+
+
+def nvcc_path():
+    return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+
+
+def build_library(force=False, verbose=False):
+    """Compile the CUDA library; returns the path of the .so."""
+    if not force and not _newer_than(LIB, _deps()):
+        return LIB
+    cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+           "-Xptxas", "-v", "-shared", "-Xcompiler", "-fPIC",
+           "-I" + os.path.join(ROOT, "include"), "-I" + CSRC, "-o", LIB]
+    cmd += [os.path.join(CSRC, s) for s in SOURCES]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        print(res.stdout)
+        print(res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed building libbam_b200.so")
+    return LIB

@@ -1,0 +1,86 @@
+"""ctypes binding of libbam_b200.so (the C ABI declared in include/bam_abi.h).
+
+The library is the product: if it is missing this module raises, there is no fallback.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libbam_b200.so")
+
+u32, u64, vp, ci = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int
+
+
+class CacheStats(C.Structure):
+    _fields_ = [("hits", u64), ("misses", u64), ("read_ios", u64)]
+
+
+class StatusOut(C.Structure):
+    _fields_ = [("code", u32), ("where", u32), ("detail", u64)]
+
+
+# name -> (restype, argtypes); mirrors include/bam_abi.h one to one
+SIGNATURES = {
+    "bam_version": (C.c_char_p, []),
+    "bam_strerror": (C.c_char_p, [ci]),
+    "bam_ctrl_create": (ci, [C.POINTER(vp), ci, u64, u32, u32, u32]),
+    "bam_ctrl_destroy": (ci, [vp]),
+    "bam_ctrl_store_host": (vp, [vp]),
+    "bam_ctrl_store_bytes": (u64, [vp]),
+    "bam_ctrl_fill_store": (ci, [vp, u64, u64, vp]),
+    "bam_ctrl_write_store": (ci, [vp, u64, vp, u64]),
+    "bam_ctrl_configure": (ci, [vp, u32, u32, u64]),
+    "bam_ctrl_set_max_grid": (ci, [vp, u32]),
+    "bam_ctrl_set_launch_timeout": (ci, [vp, u64]),
+    "bam_ctrl_inject_fault": (ci, [vp, u32, u64, u32]),
+    "bam_ctrl_status": (ci, [vp, C.POINTER(StatusOut), ci]),
+    "bam_ctrl_served": (ci, [vp, C.POINTER(u64), ci]),
+    "bam_ctrl_reset_queues": (ci, [vp]),
+    "bam_ctrl_device_controller": (vp, [vp]),
+    "bam_ctrl_emu_descriptor": (ci, [vp, vp, C.c_size_t]),
+    "bam_cache_create": (ci, [C.POINTER(vp), vp, u32, u64]),
+    "bam_cache_destroy": (ci, [vp]),
+    "bam_cache_stats": (ci, [vp, C.POINTER(CacheStats), ci]),
+    "bam_cache_invalidate": (ci, [vp]),
+    "bam_cache_audit": (ci, [vp, C.POINTER(u64)]),
+    "bam_cache_descriptor": (ci, [vp, vp, C.c_size_t]),
+    "bam_array_create": (ci, [C.POINTER(vp), vp, u64, u32, u64]),
+    "bam_array_destroy": (ci, [vp]),
+    "bam_array_device_ptr": (vp, [vp]),
+    "bam_launch_block_read": (ci, [vp, u64, vp, u64, vp, vp, vp]),
+    "bam_launch_array_read": (ci, [vp, u64, u64, vp, u64, vp, vp]),
+    "bam_launch_page_scan": (ci, [vp, u64, vp, u64, vp, vp]),
+    "bam_launch_geometry": (ci, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library and declare every entry point.  Raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            "libbam_b200.so is not built (run `python -c 'import __graft_entry__ as g; g.build()'`); "
+            "bam_b200 has no CPU fallback")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+class BamError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        msg = load().bam_strerror(code).decode()
+        super().__init__(f"{what}: {msg} (code {code})")
+
+
+def check(code, what):
+    if code != 0:
+        raise BamError(code, what)

@@ -1,0 +1,61 @@
+/*
+ * bam_internal.h -- host-side objects behind the opaque handles of bam_abi.h.
+ */
+#ifndef BAM_INTERNAL_H
+#define BAM_INTERNAL_H
+
+#include "bam/abi_types.h"
+#include "bam/array.cuh"
+
+#define BAM_THREADS 256               /* threads per block of every fused launch            */
+#define BAM_MIN_BLOCKS 3              /* resident blocks per SM the kernels are compiled for */
+#define BAM_DEFAULT_CTRL_BLOCKS 16    /* controller blocks unless configured otherwise       */
+#define BAM_DB_STRIDE_WORDS 8         /* doorbell stride: 32 bytes, one sector per register   */
+
+struct bam_ctrl {
+    int device = 0;
+    int num_sms = 0;
+    uint8_t* store_host = nullptr;
+    uint8_t* store_dev = nullptr;
+    uint64_t store_bytes = 0;
+    uint32_t lba_bytes = 0;
+    uint32_t n_qps = 0, qdepth = 0;
+    uint64_t spin_timeout_ns = 0;
+    uint64_t launch_timeout_ns = 0;
+    void* arena = nullptr;
+    size_t arena_bytes = 0;
+    nvm_cmd_t* d_sq_mem = nullptr;
+    nvm_cpl_t* d_cq_mem = nullptr;
+    uint32_t* d_tickets = nullptr;
+    uint32_t* d_marks = nullptr;
+    uint32_t* d_cids = nullptr;
+    uint32_t* d_doorbells = nullptr;
+    bam_emu_qp_t* d_emu_qps = nullptr;
+    QueuePair* d_qps = nullptr;
+    Controller* d_ctrl = nullptr;
+    bam_status_t* d_status = nullptr;
+    uint32_t* d_remaining = nullptr;
+    bam_fault_t* d_fault = nullptr;
+    uint64_t* d_served = nullptr;
+    bam_emu_d_t emu = {};
+    uint32_t max_grid = 0;            /* 0 = as many blocks as fit                            */
+    uint32_t last_grid = 0;
+};
+
+struct bam_cache {
+    bam_ctrl* ctrl = nullptr;
+    page_cache_d_t d;
+    uint64_t n_buckets = 0;
+    uint32_t n_ranges = 0;
+};
+
+struct bam_array {
+    bam_cache* pc = nullptr;
+    uint32_t elem_bytes = 0;
+    uint64_t n_elems = 0;
+    bam::range_d_t<uint64_t> h_range;   /* layout does not depend on the element type */
+    void* d_range = nullptr;
+    void* d_array = nullptr;
+};
+
+#endif

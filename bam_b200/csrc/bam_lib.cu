@@ -1,0 +1,758 @@
+/*
+ * bam_lib.cu -- host side of libbam_b200.so (the C ABI of include/bam_abi.h) and the fused
+ * kernels it launches.  sm_100a only; there is no CPU path.
+ *
+ * Launch model.  A workload kernel waits on completions that the emulated controller produces,
+ * so both must be running at the same time.  They are therefore ONE cooperative launch
+ * (co-residency of all blocks is guaranteed by cudaLaunchCooperativeKernel or the launch fails):
+ * blocks [0, n_ctrl_blocks) run bam::emu_controller_main, the remaining blocks are persistent
+ * workers that stride over the workload.  The controller blocks leave when the last worker
+ * block has finished.
+ */
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "bam_abi.h"
+#include "bam_synth.h"
+#include "bam/array.cuh"
+#include "bam/emu_ctrl.cuh"
+#include "bam_internal.h"
+
+using namespace bam;
+
+static thread_local cudaError_t g_last_cuda = cudaSuccess;
+#define CK(x)                                              \
+    do {                                                   \
+        cudaError_t e_ = (x);                              \
+        if (e_ != cudaSuccess) { g_last_cuda = e_; (void)cudaGetLastError(); return BAM_ECUDA; } \
+    } while (0)
+
+/* ====================================================================================== */
+/* small kernels: initialisation, store fill, audit                                       */
+/* ====================================================================================== */
+
+__global__ void k_init_cache(bam_slot_t* slots, uint32_t n_slots, uint32_t* table, uint64_t n_words)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthr = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = tid; i < n_slots; i += nthr) { slots[i].tag = BAM_TAG_NONE; slots[i].state = 0; slots[i].pad = 0; }
+    for (uint64_t i = tid; i < n_words; i += nthr) table[i] = (i % BAM_BUCKET_WORDS) ? BAM_ENTRY_EMPTY : 0u;
+}
+
+__global__ void k_fill_store(uint64_t* dst, uint64_t n_elems, uint64_t seed, uint64_t first_elem)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthr = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = tid * 2; i < n_elems; i += nthr * 2) {
+        ulonglong2 v;
+        v.x = bam_store_elem(seed, first_elem + i);
+        v.y = bam_store_elem(seed, first_elem + i + 1);
+        if (i + 1 < n_elems) *reinterpret_cast<ulonglong2*>(dst + i) = v;
+        else dst[i] = v.x;
+    }
+}
+
+/* Post-launch audit of the cache invariants; counts violations. */
+__global__ void k_audit(page_cache_d_t pc, uint64_t n_buckets, unsigned long long* violations)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthr = (uint64_t)gridDim.x * blockDim.x;
+    unsigned long long bad = 0;
+    for (uint64_t s = tid; s < pc.n_slots; s += nthr) {
+        const uint32_t st = pc.slots[s].state;
+        const uint64_t tag = pc.slots[s].tag;
+        if (st & BAM_CNT_MASK) bad++;                                  /* a pin was leaked          */
+        if (st & BAM_BUSY) bad++;                                      /* a fill/evict never ended  */
+        if ((st & BAM_VALID) && tag == BAM_TAG_NONE) bad++;
+        if (!(st & BAM_VALID) && tag != BAM_TAG_NONE) bad++;
+        if (st & BAM_VALID) {
+            const uint64_t h = pt_hash(tag);
+            if (pt_lookup(pc, tag, (uint32_t)h & pc.bucket_mask, (uint32_t)(h >> 56)) != (uint32_t)s) bad++;
+        }
+    }
+    for (uint64_t b = tid; b < n_buckets; b += nthr) {
+        const uint32_t* w = pc.table + b * BAM_BUCKET_WORDS;
+        if (w[0] & BAM_BUCKET_LOCK) bad++;
+        for (int i = 1; i < BAM_BUCKET_WORDS; i++) {
+            if (w[i] == BAM_ENTRY_EMPTY) continue;
+            const uint32_t s = w[i] & 0xffffffu;
+            if (s >= pc.n_slots) { bad++; continue; }
+            const uint64_t tag = pc.slots[s].tag;
+            if (tag == BAM_TAG_NONE || (uint32_t)(pt_hash(tag) >> 56) != (w[i] >> 24)) bad++;
+        }
+    }
+    if (bad) atomicAdd(violations, bad);
+}
+
+/* ====================================================================================== */
+/* fused launch                                                                            */
+/* ====================================================================================== */
+
+template <class Work>
+__global__ void __launch_bounds__(BAM_THREADS, BAM_MIN_BLOCKS)
+bam_fused(const __grid_constant__ bam_emu_d_t emu, const __grid_constant__ Work work)
+{
+    if (blockIdx.x < emu.n_ctrl_blocks) {
+        emu_controller_main(emu);
+        return;
+    }
+    work(blockIdx.x - emu.n_ctrl_blocks, gridDim.x - emu.n_ctrl_blocks);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        red_add_release(emu.consumers_remaining, 0xffffffffu);
+    }
+}
+
+template <class Work>
+static int launch_fused(bam_ctrl* c, const Work& w, cudaStream_t s)
+{
+    static thread_local int blocks_per_sm = 0;
+    if (blocks_per_sm == 0) {
+        int nb = 0;
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, bam_fused<Work>, BAM_THREADS, 0));
+        if (nb < 1) return BAM_EINVAL;
+        blocks_per_sm = nb;
+    }
+    uint32_t grid = (uint32_t)blocks_per_sm * (uint32_t)c->num_sms;
+    if (c->max_grid && grid > c->max_grid) grid = c->max_grid;
+    if (grid <= c->emu.n_ctrl_blocks) return BAM_EINVAL;
+    const uint32_t n_work = grid - c->emu.n_ctrl_blocks;
+    CK(cudaMemcpyAsync(c->emu.consumers_remaining, &n_work, sizeof n_work, cudaMemcpyHostToDevice, s));
+    bam_emu_d_t emu = c->emu;
+    void* args[] = { (void*)&emu, (void*)&w };
+    CK(cudaLaunchCooperativeKernel((const void*)bam_fused<Work>, dim3(grid), dim3(BAM_THREADS), args, 0, s));
+    c->last_grid = grid;
+    return BAM_OK;
+}
+
+template <class Work>
+static int fused_geometry(bam_ctrl* c, uint32_t* grid)
+{
+    int nb = 0;
+    CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, bam_fused<Work>, BAM_THREADS, 0));
+    *grid = (uint32_t)nb * (uint32_t)c->num_sms;
+    if (c->max_grid && *grid > c->max_grid) *grid = c->max_grid;
+    return BAM_OK;
+}
+
+/* wrapping 64-bit sum of one value per lane, added to *out by lane 0 */
+BAM_DEV void warp_sum_to(uint64_t v, uint64_t* out)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31u) == 0u && out) red_add_relaxed(out, v);
+}
+
+/* ---- block benchmark --------------------------------------------------------------------- */
+struct BlockReadWork {
+    page_cache_d_t pc;
+    uint64_t n_reqs;
+    const uint64_t* pages;
+    uint64_t req_seed;
+    uint64_t n_store_pages;
+    uint32_t* crc_out;
+    uint64_t* sum_out;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        __shared__ uint32_t crc_tab[256];
+        if (crc_out) {
+            for (uint32_t i = threadIdx.x; i < 256; i += blockDim.x) {
+                uint32_t c = i;
+                for (int k = 0; k < 8; k++) c = (c >> 1) ^ (0xEDB88320u & (0u - (c & 1u)));
+                crc_tab[i] = c;
+            }
+            __syncthreads();
+        }
+        const uint64_t gid = (uint64_t)vb * blockDim.x + threadIdx.x;
+        const uint64_t nthr = (uint64_t)nvb * blockDim.x;
+        const uint32_t slot = (uint32_t)gid;                 /* private slot, as pc_entry = tid in the reference */
+        Controller* c = pc.d_ctrl;
+        QueuePair* qp = c->d_qps + ((uint32_t)(gid >> 5) % c->n_qps);
+        const uint64_t bus = slot_bus_addr(pc, slot);
+        const uint64_t prp2 = pc.page_size > 4096 ? bus + 4096 : 0;
+        uint64_t sum = 0;
+        for (uint64_t r = gid; r < n_reqs; r += nthr) {
+            const uint64_t pg = pages ? pages[r] : bam_block_request_page(req_seed, r, n_store_pages);
+            const int rc = access_data_raw(qp, pg * pc.n_blocks_per_page, pc.n_blocks_per_page, bus, prp2, NVM_IO_READ);
+            if (rc != BAM_OK) break;
+            if (crc_out || sum_out) {
+                uint32_t crc = ~0u;
+                const uint8_t* p = reinterpret_cast<const uint8_t*>(bus);
+                for (uint32_t o = 0; o < pc.page_size; o += 16) {
+                    const uint4 v = ld_cg_v4(p + o);
+                    sum += (((uint64_t)v.y << 32) | v.x) + (((uint64_t)v.w << 32) | v.z);
+                    if (crc_out) {
+                        const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            uint32_t x = w[j];
+#pragma unroll
+                            for (int b = 0; b < 4; b++) { crc = (crc >> 8) ^ crc_tab[(crc ^ x) & 0xffu]; x >>= 8; }
+                        }
+                    }
+                }
+                if (crc_out) crc_out[r] = ~crc;
+            }
+        }
+        __syncwarp();
+        warp_sum_to(sum, sum_out);
+    }
+};
+
+/* ---- array benchmark --------------------------------------------------------------------- */
+struct ArrayReadWork {
+    range_d_t<uint64_t> r;
+    uint64_t n_lanes, reqs_per_lane;
+    const uint64_t* idx;
+    uint64_t access_seed;
+    uint64_t* sum_out;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint64_t gid = (uint64_t)vb * blockDim.x + threadIdx.x;
+        const uint64_t nthr = (uint64_t)nvb * blockDim.x;
+        const uint32_t queue = (uint32_t)(gid >> 5);
+        const uint64_t n_elems = r.count - r.index_start;
+        uint64_t sum = 0;
+        for (uint64_t lane = gid; lane < n_lanes; lane += nthr) {
+            bam_pcg32_t g;
+            bam_lane_stream(&g, access_seed, lane);
+            for (uint64_t k = 0; k < reqs_per_lane; k++) {
+                const uint64_t i = idx ? idx[lane * reqs_per_lane + k] : r.index_start + bam_uniform_index(&g, n_elems);
+                sum += range_read<uint64_t>(r, i, queue);
+            }
+        }
+        __syncwarp();
+        warp_sum_to(sum, sum_out);
+    }
+};
+
+/* ---- cache benchmark: a warp reads whole pages ----------------------------------------------- */
+struct PageScanWork {
+    range_d_t<uint64_t> r;
+    uint64_t n_pages;
+    const uint64_t* pages;
+    uint64_t first_page;
+    uint64_t* sum_out;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint32_t lane = threadIdx.x & 31u;
+        const uint32_t wpb = blockDim.x >> 5;
+        const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
+        const uint64_t nwarps = (uint64_t)nvb * wpb;
+        uint64_t sum = 0;
+        for (uint64_t p = warp; p < n_pages; p += nwarps) {
+            const uint64_t page = pages ? pages[p] : first_page + p;
+            uint32_t slot = BAM_SLOT_ERR;
+            if (lane == 0) slot = r.acquire_page(page, 1, false, (uint32_t)warp);
+            slot = __shfl_sync(0xffffffffu, slot, 0);
+            if (slot == BAM_SLOT_ERR) break;
+            const uint8_t* base = reinterpret_cast<const uint8_t*>(r.get_cache_page_addr(slot));
+            for (uint32_t o = lane * 16; o < r.cache.page_size; o += 32 * 16 * 4) {
+                uint4 v[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (o + j * 512 < r.cache.page_size) v[j] = *reinterpret_cast<const uint4*>(base + o + j * 512);
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (o + j * 512 < r.cache.page_size)
+                        sum += (((uint64_t)v[j].y << 32) | v[j].x) + (((uint64_t)v[j].w << 32) | v[j].z);
+            }
+            __syncwarp();
+            if (lane == 0) r.release_page(slot, 1);
+        }
+        __syncwarp();
+        warp_sum_to(sum, sum_out);
+    }
+};
+
+/* ====================================================================================== */
+/* C ABI                                                                                   */
+/* ====================================================================================== */
+
+extern "C" const char* bam_version(void) { return "bam_b200 0.1 (sm_100a)"; }
+
+extern "C" const char* bam_strerror(int code)
+{
+    switch (code) {
+    case BAM_OK: return "success";
+    case BAM_EIO: return "I/O error (NVMe completion status or earlier device-side failure)";
+    case BAM_ENOMEM: return "out of memory";
+    case BAM_EBUSY: return "resource busy";
+    case BAM_EINVAL: return "invalid argument";
+    case BAM_ENOSPC: return "page table full";
+    case BAM_ERANGE: return "index outside the array";
+    case BAM_ETIMEDOUT: return "a device-side wait exceeded its limit";
+    case BAM_ECUDA: return cudaGetErrorString(g_last_cuda);
+    default: return "unknown error";
+    }
+}
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+static uint32_t log2_u32(uint64_t x) { uint32_t l = 0; while ((1ull << l) < x) l++; return l; }
+
+/* Build the power-on image of every queue structure on the host and upload it. */
+static int upload_queue_image(bam_ctrl* c)
+{
+    std::vector<uint8_t> img(c->arena_bytes, 0);
+    uint8_t* dev = (uint8_t*)c->arena;
+    auto host_of = [&](void* devp) { return img.data() + ((uint8_t*)devp - dev); };
+    const uint32_t qs = c->qdepth;
+    for (uint32_t q = 0; q < c->n_qps; q++) {
+        QueuePair* qp = (QueuePair*)host_of(c->d_qps + q);
+        qp->pageSize = 4096;
+        qp->block_size = c->lba_bytes;
+        qp->block_size_log = log2_u32(c->lba_bytes);
+        qp->block_size_minus_1 = c->lba_bytes - 1;
+        qp->nvmNamespace = 1;
+        qp->qp_id = (uint16_t)(q + 1);
+        for (int is_cq = 0; is_cq < 2; is_cq++) {
+            nvm_queue_t* nq = is_cq ? &qp->cq : &qp->sq;
+            nq->qs = qs; nq->qs_minus_1 = qs - 1; nq->qs_log2 = log2_u32(qs);
+            nq->no = (uint16_t)(q + 1);
+            nq->es = is_cq ? sizeof(nvm_cpl_t) : sizeof(nvm_cmd_t);
+            nq->phase = 1; nq->local = 1;
+            nq->status = c->d_status;
+            nq->db = c->d_doorbells + (size_t)(2 * (q + 1) + is_cq) * BAM_DB_STRIDE_WORDS;
+            nq->vaddr = is_cq ? (void*)(c->d_cq_mem + (size_t)q * qs) : (void*)(c->d_sq_mem + (size_t)q * qs);
+            nq->ioaddr = (uint64_t)nq->vaddr;
+            nq->tickets = c->d_tickets + (size_t)q * qs;
+            nq->tail_mark = c->d_marks + (size_t)q * qs;
+            nq->cid = c->d_cids + (size_t)q * BAM_CID_SPACE;
+        }
+        uint32_t* tk = (uint32_t*)host_of(c->d_tickets + (size_t)q * qs);
+        for (uint32_t i = 0; i < qs; i++) tk[i] = i;            /* slot i is first used by ticket i */
+        bam_emu_qp_t* e = (bam_emu_qp_t*)host_of(c->d_emu_qps + q);
+        e->sq_mem = c->d_sq_mem + (size_t)q * qs;
+        e->cq_mem = c->d_cq_mem + (size_t)q * qs;
+        e->sq_db = c->d_doorbells + (size_t)(2 * (q + 1)) * BAM_DB_STRIDE_WORDS;
+        e->cq_db = c->d_doorbells + (size_t)(2 * (q + 1) + 1) * BAM_DB_STRIDE_WORDS;
+        e->qs = qs; e->qs_log2 = log2_u32(qs);
+        e->sqid = e->cqid = (uint16_t)(q + 1);
+    }
+    Controller* ctl = (Controller*)host_of(c->d_ctrl);
+    ctl->d_qps = c->d_qps; ctl->n_qps = c->n_qps; ctl->page_size = 4096;
+    ctl->blk_size = c->lba_bytes; ctl->blk_size_log = log2_u32(c->lba_bytes);
+    ctl->status = c->d_status;
+    bam_status_t* st = (bam_status_t*)host_of(c->d_status);
+    st->spin_timeout_ns = c->spin_timeout_ns;
+    st->launch_timeout_ns = c->launch_timeout_ns;
+    CK(cudaMemcpy(c->arena, img.data(), c->arena_bytes, cudaMemcpyHostToDevice));
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_create(bam_ctrl_t* out, int device, uint64_t store_bytes, uint32_t lba_bytes,
+                               uint32_t n_queues, uint32_t queue_depth)
+{
+    if (!out) return BAM_EINVAL;
+    *out = nullptr;
+    if (lba_bytes != 512 && lba_bytes != 4096) return BAM_EINVAL;
+    if (n_queues == 0 || n_queues > 1024) return BAM_EINVAL;
+    if (queue_depth < 2 || queue_depth > 1024 || (queue_depth & (queue_depth - 1))) return BAM_EINVAL;
+    if (store_bytes == 0 || store_bytes % 4096) return BAM_EINVAL;
+    CK(cudaSetDevice(device));
+    bam_ctrl* c = new (std::nothrow) bam_ctrl();
+    if (!c) return BAM_ENOMEM;
+    c->device = device;
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) { g_last_cuda = e; delete c; return BAM_ECUDA; }
+    c->num_sms = prop.multiProcessorCount;
+    c->store_bytes = store_bytes; c->lba_bytes = lba_bytes;
+    c->n_qps = n_queues; c->qdepth = queue_depth;
+    c->spin_timeout_ns = 20ull * 1000 * 1000 * 1000;
+    c->launch_timeout_ns = 300ull * 1000 * 1000 * 1000;
+
+    e = cudaHostAlloc((void**)&c->store_host, store_bytes, cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e != cudaSuccess) { g_last_cuda = e; (void)cudaGetLastError(); delete c; return BAM_ENOMEM; }
+    e = cudaHostGetDevicePointer((void**)&c->store_dev, c->store_host, 0);
+    if (e != cudaSuccess) { g_last_cuda = e; cudaFreeHost(c->store_host); delete c; return BAM_ECUDA; }
+
+    /* one device arena for every queue structure */
+    const size_t qs = queue_depth, nq = n_queues;
+    size_t off = 0;
+    auto take = [&](size_t bytes, size_t align) { off = align_up(off, align); size_t o = off; off += bytes; return o; };
+    const size_t o_sq = take(nq * qs * sizeof(nvm_cmd_t), 4096);
+    const size_t o_cq = take(nq * qs * sizeof(nvm_cpl_t), 4096);
+    const size_t o_tk = take(nq * qs * 4, 256);
+    const size_t o_mk = take(nq * qs * 4, 256);
+    const size_t o_cid = take(nq * (size_t)BAM_CID_SPACE * 4, 256);
+    const size_t o_db = take((2 * (nq + 1)) * BAM_DB_STRIDE_WORDS * 4, 256);
+    const size_t o_eqp = take(nq * sizeof(bam_emu_qp_t), 256);
+    const size_t o_qp = take(nq * sizeof(QueuePair), 256);
+    const size_t o_ctl = take(sizeof(Controller), 256);
+    const size_t o_st = take(sizeof(bam_status_t), 256);
+    const size_t o_rem = take(4, 256);
+    const size_t o_flt = take(sizeof(bam_fault_t), 256);
+    const size_t o_srv = take(8, 256);
+    c->arena_bytes = align_up(off, 4096);
+    e = cudaMalloc(&c->arena, c->arena_bytes);
+    if (e != cudaSuccess) { g_last_cuda = e; (void)cudaGetLastError(); cudaFreeHost(c->store_host); delete c; return BAM_ENOMEM; }
+    uint8_t* a = (uint8_t*)c->arena;
+    c->d_sq_mem = (nvm_cmd_t*)(a + o_sq); c->d_cq_mem = (nvm_cpl_t*)(a + o_cq);
+    c->d_tickets = (uint32_t*)(a + o_tk); c->d_marks = (uint32_t*)(a + o_mk); c->d_cids = (uint32_t*)(a + o_cid);
+    c->d_doorbells = (uint32_t*)(a + o_db); c->d_emu_qps = (bam_emu_qp_t*)(a + o_eqp);
+    c->d_qps = (QueuePair*)(a + o_qp); c->d_ctrl = (Controller*)(a + o_ctl);
+    c->d_status = (bam_status_t*)(a + o_st); c->d_remaining = (uint32_t*)(a + o_rem);
+    c->d_fault = (bam_fault_t*)(a + o_flt); c->d_served = (uint64_t*)(a + o_srv);
+
+    c->emu.qps = c->d_emu_qps; c->emu.n_qps = n_queues;
+    c->emu.n_ctrl_blocks = BAM_DEFAULT_CTRL_BLOCKS;
+    c->emu.store = c->store_dev; c->emu.store_bytes = store_bytes;
+    c->emu.lba_log2 = log2_u32(lba_bytes); c->emu.mps_log2 = 12;
+    c->emu.batch = 2; c->emu.copy_mode = 0;
+    c->emu.consumers_remaining = c->d_remaining; c->emu.status = c->d_status;
+    c->emu.fault = c->d_fault; c->emu.served = c->d_served;
+    int rc = upload_queue_image(c);
+    if (rc != BAM_OK) { cudaFree(c->arena); cudaFreeHost(c->store_host); delete c; return rc; }
+    *out = c;
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_destroy(bam_ctrl_t c)
+{
+    if (!c) return BAM_EINVAL;
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    cudaFree(c->arena);
+    cudaFreeHost(c->store_host);
+    delete c;
+    return BAM_OK;
+}
+
+extern "C" void* bam_ctrl_store_host(bam_ctrl_t c) { return c ? c->store_host : nullptr; }
+extern "C" uint64_t bam_ctrl_store_bytes(bam_ctrl_t c) { return c ? c->store_bytes : 0; }
+
+extern "C" int bam_ctrl_fill_store(bam_ctrl_t c, uint64_t seed, uint64_t first_elem, void* stream)
+{
+    if (!c) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    k_fill_store<<<c->num_sms * 8, 256, 0, (cudaStream_t)stream>>>((uint64_t*)c->store_dev, c->store_bytes / 8, seed, first_elem);
+    CK(cudaGetLastError());
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_write_store(bam_ctrl_t c, uint64_t byte_offset, const void* src, uint64_t bytes)
+{
+    if (!c || !src || byte_offset + bytes > c->store_bytes || byte_offset + bytes < byte_offset) return BAM_EINVAL;
+    memcpy(c->store_host + byte_offset, src, bytes);
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_set_launch_timeout(bam_ctrl_t c, uint64_t launch_timeout_ns)
+{
+    if (!c || launch_timeout_ns == 0) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    CK(cudaDeviceSynchronize());
+    c->launch_timeout_ns = launch_timeout_ns;
+    CK(cudaMemcpy(&c->d_status->launch_timeout_ns, &launch_timeout_ns, 8, cudaMemcpyHostToDevice));
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_configure(bam_ctrl_t c, uint32_t n_ctrl_blocks, uint32_t batch, uint64_t spin_timeout_ns)
+{
+    if (!c) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    if (n_ctrl_blocks) c->emu.n_ctrl_blocks = n_ctrl_blocks;
+    if (batch) { if (batch > 32) return BAM_EINVAL; c->emu.batch = batch; }
+    if (spin_timeout_ns) {
+        c->spin_timeout_ns = spin_timeout_ns;
+        CK(cudaDeviceSynchronize());
+        CK(cudaMemcpy(&c->d_status->spin_timeout_ns, &spin_timeout_ns, 8, cudaMemcpyHostToDevice));
+    }
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_set_max_grid(bam_ctrl_t c, uint32_t max_grid)
+{
+    if (!c) return BAM_EINVAL;
+    c->max_grid = max_grid;
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_inject_fault(bam_ctrl_t c, uint32_t mode, uint64_t nth, uint32_t status)
+{
+    if (!c || mode > BAM_FAULT_STATUS) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    CK(cudaDeviceSynchronize());
+    bam_fault_t f = { mode, status, nth, 0 };
+    CK(cudaMemcpy(c->d_fault, &f, sizeof f, cudaMemcpyHostToDevice));
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_status(bam_ctrl_t c, bam_status_out_t* out, int clear)
+{
+    if (!c || !out) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    CK(cudaDeviceSynchronize());
+    bam_status_t st;
+    CK(cudaMemcpy(&st, c->d_status, sizeof st, cudaMemcpyDeviceToHost));
+    out->code = st.code; out->where = st.where; out->detail = st.detail;
+    if (clear && st.code) {
+        st.code = 0; st.where = 0; st.detail = 0;
+        CK(cudaMemcpy(c->d_status, &st, sizeof st, cudaMemcpyHostToDevice));
+    }
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_served(bam_ctrl_t c, uint64_t* out, int reset)
+{
+    if (!c || !out) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    CK(cudaDeviceSynchronize());
+    CK(cudaMemcpy(out, c->d_served, 8, cudaMemcpyDeviceToHost));
+    if (reset) CK(cudaMemset(c->d_served, 0, 8));
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_reset_queues(bam_ctrl_t c)
+{
+    if (!c) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    CK(cudaDeviceSynchronize());
+    return upload_queue_image(c);
+}
+
+extern "C" void* bam_ctrl_device_controller(bam_ctrl_t c) { return c ? c->d_ctrl : nullptr; }
+
+extern "C" int bam_ctrl_emu_descriptor(bam_ctrl_t c, void* out, size_t out_bytes)
+{
+    if (!c || !out || out_bytes < sizeof(bam_emu_d_t)) return BAM_EINVAL;
+    memcpy(out, &c->emu, sizeof(bam_emu_d_t));
+    return BAM_OK;
+}
+
+/* ---- cache -------------------------------------------------------------------------------- */
+
+static int cache_reset_device(bam_cache* pc)
+{
+    k_init_cache<<<pc->ctrl->num_sms * 4, 256>>>(pc->d.slots, pc->d.n_slots, pc->d.table, pc->n_buckets * BAM_BUCKET_WORDS);
+    CK(cudaGetLastError());
+    CK(cudaMemset(pc->d.clock_hand, 0, 8));
+    CK(cudaMemset(pc->d.stats, 0, sizeof(bam_stat_stripe_t) * BAM_STAT_STRIPES));
+    CK(cudaDeviceSynchronize());
+    return BAM_OK;
+}
+
+extern "C" int bam_cache_create(bam_cache_t* out, bam_ctrl_t ctrl, uint32_t page_size, uint64_t n_pages)
+{
+    if (!out) return BAM_EINVAL;
+    *out = nullptr;
+    if (!ctrl || n_pages == 0 || n_pages >= 0xffffffull) return BAM_EINVAL;
+    if (page_size < 512 || (page_size & (page_size - 1)) || page_size < ctrl->lba_bytes || page_size > (1u << 20)) return BAM_EINVAL;
+    CK(cudaSetDevice(ctrl->device));
+    bam_cache* pc = new (std::nothrow) bam_cache();
+    if (!pc) return BAM_ENOMEM;
+    pc->ctrl = ctrl;
+    uint64_t want = (n_pages * 2 + 6) / 7;           /* load factor <= 0.5 over 7-entry buckets */
+    pc->n_buckets = 1; while (pc->n_buckets < want) pc->n_buckets <<= 1;
+    page_cache_d_t& d = pc->d;
+    memset(&d, 0, sizeof d);
+    d.page_size = page_size; d.page_size_minus_1 = page_size - 1; d.page_size_log = log2_u32(page_size);
+    d.n_slots = (uint32_t)n_pages;
+    d.bucket_mask = (uint32_t)(pc->n_buckets - 1);
+    d.n_blocks_per_page = page_size / ctrl->lba_bytes;
+    d.d_ctrl = ctrl->d_ctrl; d.status = ctrl->d_status;
+    d.n_ranges_bits = BAM_RANGE_BITS; d.n_ranges_mask = BAM_MAX_RANGES - 1;
+    const uint32_t chunks = page_size / 4096;
+    d.prp_list_stride = chunks > 2 ? chunks - 1 : 0;
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(p, bytes); };
+    alloc((void**)&d.base_addr, n_pages * (size_t)page_size);
+    alloc((void**)&d.slots, n_pages * sizeof(bam_slot_t));
+    alloc((void**)&d.table, pc->n_buckets * BAM_BUCKET_WORDS * 4);
+    alloc((void**)&d.clock_hand, 8);
+    alloc((void**)&d.stats, sizeof(bam_stat_stripe_t) * BAM_STAT_STRIPES);
+    alloc((void**)&d.range_page_starts, 8 * BAM_MAX_RANGES);
+    if (d.prp_list_stride) alloc((void**)&d.prp_lists, n_pages * d.prp_list_stride * 8);
+    if (e != cudaSuccess) {
+        g_last_cuda = e; (void)cudaGetLastError();
+        cudaFree(d.base_addr); cudaFree(d.slots); cudaFree(d.table); cudaFree(d.clock_hand);
+        cudaFree(d.stats); cudaFree(d.range_page_starts); cudaFree(d.prp_lists);
+        delete pc;
+        return BAM_ENOMEM;
+    }
+    if (d.prp_list_stride) {
+        std::vector<uint64_t> lists(n_pages * d.prp_list_stride);
+        for (uint64_t s = 0; s < n_pages; s++)
+            for (uint32_t k = 0; k < d.prp_list_stride; k++)
+                lists[s * d.prp_list_stride + k] = (uint64_t)(d.base_addr + s * page_size + (size_t)(k + 1) * 4096);
+        CK(cudaMemcpy(d.prp_lists, lists.data(), lists.size() * 8, cudaMemcpyHostToDevice));
+    }
+    CK(cudaMemset(d.range_page_starts, 0, 8 * BAM_MAX_RANGES));
+    int rc = cache_reset_device(pc);
+    if (rc != BAM_OK) return rc;
+    *out = pc;
+    return BAM_OK;
+}
+
+extern "C" int bam_cache_destroy(bam_cache_t pc)
+{
+    if (!pc) return BAM_EINVAL;
+    cudaSetDevice(pc->ctrl->device);
+    cudaDeviceSynchronize();
+    page_cache_d_t& d = pc->d;
+    cudaFree(d.base_addr); cudaFree(d.slots); cudaFree(d.table); cudaFree(d.clock_hand);
+    cudaFree(d.stats); cudaFree(d.range_page_starts); cudaFree(d.prp_lists);
+    delete pc;
+    return BAM_OK;
+}
+
+extern "C" int bam_cache_stats(bam_cache_t pc, bam_cache_stats_t* out, int reset)
+{
+    if (!pc || !out) return BAM_EINVAL;
+    CK(cudaSetDevice(pc->ctrl->device));
+    CK(cudaDeviceSynchronize());
+    bam_stat_stripe_t h[BAM_STAT_STRIPES];
+    CK(cudaMemcpy(h, pc->d.stats, sizeof h, cudaMemcpyDeviceToHost));
+    out->hits = out->misses = out->read_ios = 0;
+    for (int i = 0; i < BAM_STAT_STRIPES; i++) { out->hits += h[i].hits; out->misses += h[i].misses; out->read_ios += h[i].read_ios; }
+    if (reset) CK(cudaMemset(pc->d.stats, 0, sizeof h));
+    return BAM_OK;
+}
+
+extern "C" int bam_cache_invalidate(bam_cache_t pc)
+{
+    if (!pc) return BAM_EINVAL;
+    CK(cudaSetDevice(pc->ctrl->device));
+    CK(cudaDeviceSynchronize());
+    return cache_reset_device(pc);
+}
+
+extern "C" int bam_cache_audit(bam_cache_t pc, uint64_t* violations)
+{
+    if (!pc || !violations) return BAM_EINVAL;
+    CK(cudaSetDevice(pc->ctrl->device));
+    CK(cudaDeviceSynchronize());
+    unsigned long long* d_bad = nullptr;
+    CK(cudaMalloc(&d_bad, 8));
+    CK(cudaMemset(d_bad, 0, 8));
+    k_audit<<<pc->ctrl->num_sms * 4, 256>>>(pc->d, pc->n_buckets, d_bad);
+    cudaError_t e = cudaDeviceSynchronize();
+    unsigned long long bad = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&bad, d_bad, 8, cudaMemcpyDeviceToHost);
+    cudaFree(d_bad);
+    if (e != cudaSuccess) { g_last_cuda = e; return BAM_ECUDA; }
+    *violations = bad;
+    return BAM_OK;
+}
+
+extern "C" int bam_cache_descriptor(bam_cache_t pc, void* out, size_t out_bytes)
+{
+    if (!pc || !out || out_bytes < sizeof(page_cache_d_t)) return BAM_EINVAL;
+    memcpy(out, &pc->d, sizeof(page_cache_d_t));
+    return BAM_OK;
+}
+
+/* ---- arrays ----------------------------------------------------------------------------------- */
+
+extern "C" int bam_array_create(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
+                                uint64_t store_byte_offset)
+{
+    if (!out) return BAM_EINVAL;
+    *out = nullptr;
+    if (!pc || n_elems == 0 || (elem_bytes != 4 && elem_bytes != 8)) return BAM_EINVAL;
+    if (store_byte_offset % pc->d.page_size) return BAM_EINVAL;
+    if (store_byte_offset + n_elems * elem_bytes > pc->ctrl->store_bytes) return BAM_EINVAL;
+    if (pc->n_ranges >= BAM_MAX_RANGES) return BAM_ENOSPC;
+    CK(cudaSetDevice(pc->ctrl->device));
+    bam_array* a = new (std::nothrow) bam_array();
+    if (!a) return BAM_ENOMEM;
+    a->pc = pc; a->elem_bytes = elem_bytes; a->n_elems = n_elems;
+    range_d_t<uint64_t>& r = a->h_range;
+    r.index_start = 0; r.count = n_elems; r.range_id = pc->n_ranges;
+    r.page_start_offset = 0;
+    r.page_start = store_byte_offset / pc->d.page_size;
+    r.page_count = (n_elems * elem_bytes + pc->d.page_size - 1) / pc->d.page_size;
+    r.n_elems_per_page = pc->d.page_size / elem_bytes;
+    r.cache = pc->d;
+    struct { uint64_t n_elems, start_offset, n_ranges; void* d_ranges; } h_arr;
+    cudaError_t e = cudaMalloc(&a->d_range, sizeof r);
+    if (e == cudaSuccess) e = cudaMalloc(&a->d_array, sizeof h_arr);
+    if (e == cudaSuccess) e = cudaMemcpy(a->d_range, &r, sizeof r, cudaMemcpyHostToDevice);
+    h_arr.n_elems = n_elems; h_arr.start_offset = store_byte_offset; h_arr.n_ranges = 1; h_arr.d_ranges = a->d_range;
+    if (e == cudaSuccess) e = cudaMemcpy(a->d_array, &h_arr, sizeof h_arr, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(pc->d.range_page_starts + r.range_id, &r.page_start, 8, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { g_last_cuda = e; cudaFree(a->d_range); cudaFree(a->d_array); delete a; return BAM_ECUDA; }
+    pc->n_ranges++;
+    *out = a;
+    return BAM_OK;
+}
+
+extern "C" int bam_array_destroy(bam_array_t a)
+{
+    if (!a) return BAM_EINVAL;
+    cudaSetDevice(a->pc->ctrl->device);
+    cudaDeviceSynchronize();
+    cudaFree(a->d_range); cudaFree(a->d_array);
+    delete a;
+    return BAM_OK;
+}
+
+extern "C" void* bam_array_device_ptr(bam_array_t a) { return a ? a->d_array : nullptr; }
+
+/* ---- launchers --------------------------------------------------------------------------------- */
+
+extern "C" int bam_launch_block_read(bam_cache_t pc, uint64_t n_reqs, const uint64_t* pages_dev, uint64_t req_seed,
+                                     uint32_t* crc_out_dev, uint64_t* sum_out_dev, void* stream)
+{
+    if (!pc) return BAM_EINVAL;
+    bam_ctrl* c = pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    if (pc->d.page_size > 8192) return BAM_EINVAL;
+    uint32_t grid = 0;
+    int rc = fused_geometry<BlockReadWork>(c, &grid);
+    if (rc) return rc;
+    if (grid <= c->emu.n_ctrl_blocks) return BAM_EINVAL;
+    /* every worker thread owns one cache slot as its landing buffer */
+    if ((uint64_t)(grid - c->emu.n_ctrl_blocks) * BAM_THREADS > pc->d.n_slots) return BAM_ENOSPC;
+    BlockReadWork w;
+    w.pc = pc->d; w.n_reqs = n_reqs; w.pages = pages_dev; w.req_seed = req_seed;
+    w.n_store_pages = c->store_bytes / pc->d.page_size;
+    w.crc_out = crc_out_dev; w.sum_out = sum_out_dev;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t reqs_per_lane, const uint64_t* idx_dev,
+                                     uint64_t access_seed, uint64_t* sum_out_dev, void* stream)
+{
+    if (!a || a->elem_bytes != 8) return BAM_EINVAL;
+    bam_ctrl* c = a->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    ArrayReadWork w;
+    w.r = a->h_range; w.n_lanes = n_lanes; w.reqs_per_lane = reqs_per_lane; w.idx = idx_dev;
+    w.access_seed = access_seed; w.sum_out = sum_out_dev;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_page_scan(bam_array_t a, uint64_t n_pages, const uint64_t* pages_dev, uint64_t first_page,
+                                    uint64_t* sum_out_dev, void* stream)
+{
+    if (!a || a->elem_bytes != 8) return BAM_EINVAL;
+    bam_ctrl* c = a->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    PageScanWork w;
+    w.r = a->h_range; w.n_pages = n_pages; w.pages = pages_dev; w.first_page = first_page; w.sum_out = sum_out_dev;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_geometry(bam_ctrl_t c, uint32_t* grid, uint32_t* ctrl_blocks, uint32_t* threads)
+{
+    if (!c) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    uint32_t g = 0;
+    int rc = fused_geometry<ArrayReadWork>(c, &g);
+    if (rc) return rc;
+    if (grid) *grid = g;
+    if (ctrl_blocks) *ctrl_blocks = c->emu.n_ctrl_blocks;
+    if (threads) *threads = BAM_THREADS;
+    return BAM_OK;
+}

@@ -1,0 +1,174 @@
+"""Host objects mirroring the reference's C++ wrappers over the C ABI.
+
+  Controller  <- struct Controller, include/ctrl.h:39-199 (opens the SSD, creates queue pairs)
+  PageCache   <- struct page_cache_t, include/page_cache.h:631-875
+  Array       <- range_t<T> + array_t<T>, include/page_cache.h:978-1030, :1719-1772
+
+Device buffers are passed as integer device addresses (e.g. torch.Tensor.data_ptr()).
+"""
+import ctypes as C
+
+from . import _lib
+from ._lib import CacheStats, StatusOut, check
+
+WHERE = {0: "none", 1: "cid", 2: "sq_turn", 3: "sq_doorbell", 4: "cq_wait", 5: "page_busy",
+         6: "find_slot", 7: "bucket_lock", 8: "table_full", 9: "nvme_status", 10: "ctrl_cq_full",
+         11: "range", 12: "tma", 13: "launch"}
+
+FAULT_NONE, FAULT_DROP_CPL, FAULT_STATUS = 0, 1, 2
+
+
+def _ptr(x):
+    """Accept None, an int device address, or an object with data_ptr()."""
+    if x is None:
+        return None
+    if hasattr(x, "data_ptr"):
+        return C.c_void_p(x.data_ptr())
+    return C.c_void_p(int(x))
+
+
+class Controller:
+    """Emulated NVMe controller with a pinned host backing store and n I/O queue pairs.
+
+    Same constructor shape as the reference's Controller(path, nvmNamespace, cudaDevice,
+    queueDepth, numQueues); `path` is replaced by the size of the emulated namespace.
+    """
+
+    def __init__(self, store_bytes, cuda_device=0, queue_depth=1024, num_queues=128, lba_bytes=512,
+                 nvm_namespace=1):
+        self.lib = _lib.load()
+        self.h = C.c_void_p()
+        check(self.lib.bam_ctrl_create(C.byref(self.h), cuda_device, store_bytes, lba_bytes, num_queues,
+                                       queue_depth), "bam_ctrl_create")
+        self.store_bytes, self.device = store_bytes, cuda_device
+        self.n_qps, self.queue_depth, self.lba_bytes = num_queues, queue_depth, lba_bytes
+        self.ns = nvm_namespace
+
+    def close(self):
+        if self.h:
+            self.lib.bam_ctrl_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def store_numpy(self, dtype="uint64"):
+        """The backing store as a numpy array over the pinned host memory."""
+        import numpy as np
+        n = self.store_bytes // np.dtype(dtype).itemsize
+        buf = (C.c_uint8 * self.store_bytes).from_address(self.lib.bam_ctrl_store_host(self.h))
+        return np.frombuffer(buf, dtype=dtype, count=n)
+
+    def fill_store(self, seed, first_elem=0, stream=None):
+        check(self.lib.bam_ctrl_fill_store(self.h, seed, first_elem, _ptr(stream)), "bam_ctrl_fill_store")
+
+    def configure(self, ctrl_blocks=0, batch=0, spin_timeout_ns=0):
+        check(self.lib.bam_ctrl_configure(self.h, ctrl_blocks, batch, spin_timeout_ns), "bam_ctrl_configure")
+
+    def set_launch_timeout(self, ns):
+        check(self.lib.bam_ctrl_set_launch_timeout(self.h, ns), "bam_ctrl_set_launch_timeout")
+
+    def set_max_grid(self, max_grid):
+        check(self.lib.bam_ctrl_set_max_grid(self.h, max_grid), "bam_ctrl_set_max_grid")
+
+    def inject_fault(self, mode, nth=0, status=0):
+        check(self.lib.bam_ctrl_inject_fault(self.h, mode, nth, status), "bam_ctrl_inject_fault")
+
+    def status(self, clear=False):
+        """Synchronise and return (code, where, detail) of the device status block."""
+        st = StatusOut()
+        check(self.lib.bam_ctrl_status(self.h, C.byref(st), int(clear)), "bam_ctrl_status")
+        return st.code, WHERE.get(st.where, str(st.where)), st.detail
+
+    def check_status(self):
+        code, where, detail = self.status()
+        if code:
+            raise _lib.BamError(code, f"device status (at {where}, detail {detail})")
+
+    def served(self, reset=False):
+        v = C.c_uint64()
+        check(self.lib.bam_ctrl_served(self.h, C.byref(v), int(reset)), "bam_ctrl_served")
+        return v.value
+
+    def reset_queues(self):
+        check(self.lib.bam_ctrl_reset_queues(self.h), "bam_ctrl_reset_queues")
+
+    def geometry(self):
+        g, cb, t = C.c_uint32(), C.c_uint32(), C.c_uint32()
+        check(self.lib.bam_launch_geometry(self.h, C.byref(g), C.byref(cb), C.byref(t)), "bam_launch_geometry")
+        return g.value, cb.value, t.value
+
+
+class PageCache:
+    """page_cache_t(page_size, n_pages, gpu, ctrl, ...)."""
+
+    def __init__(self, ctrl, page_size=4096, n_pages=65536):
+        self.lib, self.ctrl = ctrl.lib, ctrl
+        self.h = C.c_void_p()
+        check(self.lib.bam_cache_create(C.byref(self.h), ctrl.h, page_size, n_pages), "bam_cache_create")
+        self.page_size, self.n_pages = page_size, n_pages
+
+    def close(self):
+        if self.h:
+            self.lib.bam_cache_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def stats(self, reset=False):
+        s = CacheStats()
+        check(self.lib.bam_cache_stats(self.h, C.byref(s), int(reset)), "bam_cache_stats")
+        return {"hits": s.hits, "misses": s.misses, "read_ios": s.read_ios, "accesses": s.hits + s.misses}
+
+    def invalidate(self):
+        check(self.lib.bam_cache_invalidate(self.h), "bam_cache_invalidate")
+
+    def audit(self):
+        v = C.c_uint64()
+        check(self.lib.bam_cache_audit(self.h, C.byref(v)), "bam_cache_audit")
+        return v.value
+
+    def block_read(self, n_reqs, pages=None, req_seed=0, crc_out=None, sum_out=None, stream=None):
+        check(self.lib.bam_launch_block_read(self.h, n_reqs, _ptr(pages), req_seed, _ptr(crc_out), _ptr(sum_out),
+                                             _ptr(stream)), "bam_launch_block_read")
+
+
+class Array:
+    """array_t<T>(n_elems, disk_start_offset, {range_t<T>(...)}) for a single range."""
+
+    def __init__(self, cache, n_elems, elem_bytes=8, store_byte_offset=0):
+        self.lib, self.cache = cache.lib, cache
+        self.h = C.c_void_p()
+        check(self.lib.bam_array_create(C.byref(self.h), cache.h, n_elems, elem_bytes, store_byte_offset),
+              "bam_array_create")
+        self.n_elems, self.elem_bytes = n_elems, elem_bytes
+
+    def close(self):
+        if self.h:
+            self.lib.bam_array_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def d_array_ptr(self):
+        return self.lib.bam_array_device_ptr(self.h)
+
+    def read(self, n_lanes, reqs_per_lane, sum_out, idx=None, access_seed=0, stream=None):
+        check(self.lib.bam_launch_array_read(self.h, n_lanes, reqs_per_lane, _ptr(idx), access_seed, _ptr(sum_out),
+                                             _ptr(stream)), "bam_launch_array_read")
+
+    def page_scan(self, n_pages, sum_out, pages=None, first_page=0, stream=None):
+        check(self.lib.bam_launch_page_scan(self.h, n_pages, _ptr(pages), first_page, _ptr(sum_out), _ptr(stream)),
+              "bam_launch_page_scan")

@@ -1,0 +1,198 @@
+/*
+ * bam/array.cuh -- the array abstraction kernels program against:
+ *   range_d_t<T>, array_d_t<T>  (include/page_cache.h:878-1224, :1229-1716 in the reference)
+ *   bam_ptr<T>                  (:415-485)  a per-thread cursor that keeps one page pinned
+ *   bafs_ptr<T>                 (include/bafs_ptr.h:17-132) a raw-pointer-like façade
+ *   bam::array<T>               the name the library's users know the device array by
+ *
+ * Element index -> (range, page, byte offset) is shift/mask arithmetic.  Lanes of a warp that
+ * touch the same page are coalesced with __match_any_sync: the lowest lane of each group pins
+ * the page once for the whole group (one fetch-add of the group size), the slot index is
+ * broadcast with __shfl_sync, every lane loads its element, and the leader unpins once.
+ * Groups are independent: no lane waits for another group between its pin and its unpin, so
+ * a warp never holds one page while waiting for another.
+ */
+#ifndef BAM_ARRAY_CUH
+#define BAM_ARRAY_CUH
+
+#include "cache.cuh"
+
+namespace bam {
+
+BAM_DEV uint32_t default_queue() { return (blockIdx.x * blockDim.x + threadIdx.x) >> 5; }
+
+template <typename T>
+struct range_d_t {
+    uint64_t index_start;        /* first element index covered by the range        */
+    uint64_t count;              /* one past the last element index (as the reference) */
+    uint64_t range_id;
+    uint64_t page_start_offset;  /* byte offset of element index_start in its first page */
+    uint64_t page_start;         /* first backing page of the range                 */
+    uint64_t page_count;
+    uint64_t n_elems_per_page;
+    page_cache_d_t cache;
+
+    BAM_DEV uint64_t get_page(size_t i) const { return ((i - index_start) * sizeof(T) + page_start_offset) >> cache.page_size_log; }
+    BAM_DEV uint64_t get_subindex(size_t i) const { return ((i - index_start) * sizeof(T) + page_start_offset) & cache.page_size_minus_1; }
+    BAM_DEV uint64_t get_global_address(size_t page) const { return (page << cache.n_ranges_bits) | range_id; }
+    BAM_DEV uint64_t get_backing_page(size_t page) const { return page_start + page; }
+    BAM_DEV uint64_t get_cache_page_addr(uint32_t slot) const { return (uint64_t)(cache.base_addr + (size_t)slot * cache.page_size); }
+
+    /* returns the cache slot (BAM_SLOT_ERR on failure); the page stays pinned `count` times */
+    BAM_DEV uint32_t acquire_page(size_t page, uint32_t cnt, bool write, uint32_t queue) const
+    {
+        return cache_acquire(cache, get_global_address(page), cnt, get_backing_page(page), queue, write);
+    }
+    BAM_DEV void release_page(uint32_t slot, uint32_t cnt = 1) const { cache_release(cache, slot, cnt); }
+};
+
+template <typename T>
+struct array_d_t {
+    uint64_t n_elems;
+    uint64_t start_offset;
+    uint64_t n_ranges;
+    range_d_t<T>* d_ranges;
+
+    BAM_DEV int64_t find_range(size_t i) const
+    {
+        for (int64_t k = 0; k < (int64_t)n_ranges; k++)
+            if (d_ranges[k].index_start <= i && d_ranges[k].count > i) return k;
+        return -1;
+    }
+
+    /* Coalesced pin.  All lanes of `mask` call this together.  Outputs the group mask, its
+     * leader and size, and the slot (BAM_SLOT_ERR on failure). */
+    BAM_DEV static void coalesce_page(const range_d_t<T>& r, uint32_t mask, uint64_t page, bool write,
+                                      uint32_t& eq_mask, uint32_t& leader, uint32_t& cnt, uint32_t& slot)
+    {
+        const uint64_t gaddr = r.get_global_address(page);
+        eq_mask = __match_any_sync(mask, gaddr);
+        leader = __ffs(eq_mask) - 1;
+        cnt = __popc(eq_mask);
+        const uint32_t dirty = __ballot_sync(eq_mask, write) != 0u;
+        slot = BAM_SLOT_ERR;
+        if (lane_id() == leader) slot = r.acquire_page(page, cnt, dirty, default_queue());
+        slot = __shfl_sync(eq_mask, slot, leader);
+    }
+
+    BAM_DEV T seq_read(size_t i) const
+    {
+        const uint32_t mask = __activemask();
+        const int64_t ri = find_range(i);
+        T v = T();
+        /* lanes that hit different ranges (or none) form separate groups before anyone leaves */
+        const uint32_t rmask = __match_any_sync(mask, (uint64_t)ri);
+        if (ri < 0) { status_fail(d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i); return v; }
+        const range_d_t<T>& r = d_ranges[ri];
+        uint32_t eq, leader, cnt, slot;
+        coalesce_page(r, rmask, r.get_page(i), false, eq, leader, cnt, slot);
+        if (slot != BAM_SLOT_ERR) v = *reinterpret_cast<const T*>(r.get_cache_page_addr(slot) + r.get_subindex(i));
+        __syncwarp(eq);
+        if (lane_id() == leader && slot != BAM_SLOT_ERR) r.release_page(slot, cnt);
+        return v;
+    }
+
+    BAM_DEV T operator[](size_t i) const { return seq_read(i); }
+};
+
+/* Same read as array_d_t<T>::seq_read for the common single-range array whose descriptor sits
+ * in kernel parameter space (no pointer chasing through global memory per access). */
+template <typename T>
+BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
+{
+    const uint32_t mask = __activemask();
+    const uint64_t page = r.get_page(i);
+    const uint32_t eq = __match_any_sync(mask, page);
+    const uint32_t leader = __ffs(eq) - 1;
+    const uint32_t cnt = __popc(eq);
+    uint32_t slot = BAM_SLOT_ERR;
+    if (lane_id() == leader) slot = r.acquire_page(page, cnt, false, queue);
+    slot = __shfl_sync(eq, slot, leader);
+    T v = T();
+    if (slot != BAM_SLOT_ERR) v = *reinterpret_cast<const T*>(r.get_cache_page_addr(slot) + r.get_subindex(i));
+    __syncwarp(eq);
+    if (lane_id() == leader && slot != BAM_SLOT_ERR) r.release_page(slot, cnt);
+    return v;
+}
+
+/* Per-thread cursor that keeps the page of its last access pinned, so a run of accesses to one
+ * page costs one pin/unpin (reference: bam_ptr, page_cache.h:415-485).  Reads never mark the
+ * page dirty (the reference's non-const operator[] does, :478-484, which causes spurious
+ * write-backs). */
+template <typename T>
+struct bam_ptr {
+    const array_d_t<T>* array = nullptr;
+    const range_d_t<T>* range = nullptr;
+    uint32_t slot = BAM_SLOT_ERR;
+    size_t start = 0, end = 0;
+    const T* addr = nullptr;
+
+    BAM_DEV explicit bam_ptr(const array_d_t<T>* a) : array(a) {}
+    BAM_DEV ~bam_ptr() { fini(); }
+
+    BAM_DEV void fini()
+    {
+        if (slot != BAM_SLOT_ERR) {
+            const uint32_t mask = __activemask();
+            const uint32_t eq = __match_any_sync(mask, ((uint64_t)(uintptr_t)range << 24) ^ slot);
+            if (lane_id() == (uint32_t)(__ffs(eq) - 1)) range->release_page(slot, __popc(eq));
+            slot = BAM_SLOT_ERR;
+            start = end = 0;
+        }
+    }
+
+    BAM_DEV const T* update_page(size_t i)
+    {
+        fini();
+        const uint32_t mask = __activemask();
+        const int64_t ri = array->find_range(i);
+        const uint32_t rmask = __match_any_sync(mask, (uint64_t)ri);
+        if (ri < 0) { status_fail(array->d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i); addr = nullptr; return nullptr; }
+        range = &array->d_ranges[ri];
+        const uint64_t page = range->get_page(i);
+        uint32_t eq, leader, cnt;
+        array_d_t<T>::coalesce_page(*range, rmask, page, false, eq, leader, cnt, slot);
+        if (slot == BAM_SLOT_ERR) { addr = nullptr; return nullptr; }
+        /* first element index that lives in this page, and one past the last */
+        const uint64_t page_byte0 = page << range->cache.page_size_log;
+        const uint64_t first_byte = page_byte0 > range->page_start_offset ? page_byte0 - range->page_start_offset : 0;
+        start = range->index_start + (first_byte + sizeof(T) - 1) / sizeof(T);
+        end = range->index_start + (page_byte0 + range->cache.page_size - range->page_start_offset) / sizeof(T);
+        addr = reinterpret_cast<const T*>(range->get_cache_page_addr(slot) + range->get_subindex(start));
+        return addr;
+    }
+
+    BAM_DEV T operator[](size_t i)
+    {
+        if (i < start || i >= end) {
+            if (update_page(i) == nullptr) return T();
+        }
+        return addr[i - start];
+    }
+};
+
+/* Raw-pointer-like view of an array (reference: include/bafs_ptr.h:17-132). */
+template <typename T>
+struct bafs_ptr {
+    const array_d_t<T>* d = nullptr;
+    uint64_t start_idx = 0;
+
+    __host__ __device__ bafs_ptr() {}
+    __host__ __device__ bafs_ptr(const array_d_t<T>* a, uint64_t s = 0) : d(a), start_idx(s) {}
+    BAM_DEV T operator*() const { return (*d)[start_idx]; }
+    BAM_DEV T operator[](uint64_t i) const { return (*d)[start_idx + i]; }
+    __host__ __device__ bafs_ptr operator+(uint64_t i) const { return bafs_ptr(d, start_idx + i); }
+    __host__ __device__ bafs_ptr operator-(uint64_t i) const { return bafs_ptr(d, start_idx - i); }
+    __host__ __device__ bafs_ptr& operator++() { ++start_idx; return *this; }
+    __host__ __device__ bafs_ptr operator++(int) { bafs_ptr c(*this); ++start_idx; return c; }
+    __host__ __device__ bafs_ptr& operator--() { --start_idx; return *this; }
+    __host__ __device__ bafs_ptr operator--(int) { bafs_ptr c(*this); --start_idx; return c; }
+    __host__ __device__ bool operator==(const bafs_ptr& o) const { return d == o.d && start_idx == o.start_idx; }
+    __host__ __device__ bool operator!=(const bafs_ptr& o) const { return !(*this == o); }
+};
+
+template <typename T>
+using array = array_d_t<T>;
+
+}  // namespace bam
+#endif

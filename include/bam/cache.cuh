@@ -1,0 +1,230 @@
+/*
+ * bam/cache.cuh -- the GPU-resident software page cache.
+ *
+ * Role of the reference's page_cache_d_t + range_d_t<T>::acquire_page + find_slot
+ * (include/page_cache.h:1122-1224, :1786-1927), redesigned:
+ *
+ *  - The page table is HASHED and sized by the cache, not by the backing store.  The
+ *    reference keeps one 32-byte state entry per page of the backing store
+ *    (page_cache.h:96-102), i.e. 512 MiB of table for a 64 GiB store.  Here a bucket is one
+ *    32-byte sector: a control word (insert lock + overflow count) and seven entries of
+ *    (8-bit fingerprint | 24-bit slot index).  A look-up is two 128-bit loads of the home
+ *    bucket plus one 8-byte tag check; buckets overflow into their successors (linear
+ *    probing at bucket granularity, bounded by BAM_MAX_PROBE).
+ *  - The 32-bit state word (VALID | BUSY | DIRTY | pin count: the encodings of
+ *    page_cache.h:57-62) belongs to the cache slot.  Readers pin with one fetch-add and then
+ *    validate the slot's tag; eviction claims a slot with a 32-bit CAS that only succeeds on
+ *    an unpinned, non-busy word, so a pinned page can never be recycled and a reader that
+ *    raced with a recycle sees a tag mismatch, undoes its pin and looks the page up again.
+ *  - Eviction is a clock sweep over the slots (the reference's page_ticket hand, :1802).
+ *
+ * Slot life cycle:   0 (free) --CAS--> BUSY (filling) --xor--> VALID (+pins)
+ *                    VALID,0 pins --CAS--> VALID|BUSY (evicting: tag cleared, entry removed)
+ *                    --and--> BUSY (filling for the new page) ...
+ */
+#ifndef BAM_CACHE_CUH
+#define BAM_CACHE_CUH
+
+#include "queue.cuh"
+
+namespace bam {
+
+BAM_DEV uint64_t pt_hash(uint64_t tag)
+{
+    uint64_t h = tag * 0x9E3779B97F4A7C15ull;
+    h ^= h >> 32;
+    h *= 0xD6E8FEB86659FD93ull;
+    h ^= h >> 29;
+    return h;
+}
+
+/* Find the slot holding `tag`, or BAM_SLOT_NONE.  Lock-free. */
+BAM_DEV uint32_t pt_lookup(const page_cache_d_t& pc, uint64_t tag, uint32_t home, uint32_t fp)
+{
+    uint32_t b = home;
+#pragma unroll 1
+    for (uint32_t probe = 0; probe < BAM_MAX_PROBE; probe++) {
+        const uint32_t* w = pc.table + (size_t)b * BAM_BUCKET_WORDS;
+        const uint4 lo = ld_cg_v4(w);
+        const uint4 hi = ld_cg_v4(w + 4);
+        const uint32_t e[8] = { lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w };
+#pragma unroll
+        for (int i = 1; i < 8; i++) {
+            if (e[i] != BAM_ENTRY_EMPTY && (e[i] >> 24) == fp) {
+                uint32_t s = e[i] & 0xffffffu;
+                if (ld_relaxed_gpu(&pc.slots[s].tag) == tag) return s;
+            }
+        }
+        if (probe == 0 && (e[0] & ~BAM_BUCKET_LOCK) == 0u) return BAM_SLOT_NONE;
+        b = (b + 1u) & pc.bucket_mask;
+    }
+    return BAM_SLOT_NONE;
+}
+
+#define BAM_PT_OK 0
+#define BAM_PT_EXISTS 1
+#define BAM_PT_FULL 2
+#define BAM_PT_TIMEOUT 3
+
+/* Insert tag -> slot.  Inserts of keys with the same home bucket are serialised by the
+ * bucket's lock bit and re-check for the key under the lock, so a page is never present twice. */
+BAM_DEV int pt_insert(const page_cache_d_t& pc, uint64_t tag, uint32_t slot, uint32_t home, uint32_t fp)
+{
+    uint32_t* ctl = pc.table + (size_t)home * BAM_BUCKET_WORDS;
+    spin_t sp;
+    while (atom_or_acquire(ctl, BAM_BUCKET_LOCK) & BAM_BUCKET_LOCK)
+        if (sp.expired(pc.status, BAM_AT_BUCKET_LOCK, home)) return BAM_PT_TIMEOUT;
+    int rc = BAM_PT_FULL;
+    if (pt_lookup(pc, tag, home, fp) != BAM_SLOT_NONE) {
+        rc = BAM_PT_EXISTS;
+    } else {
+        const uint32_t entry = (fp << 24) | slot;
+        uint32_t b = home;
+#pragma unroll 1
+        for (uint32_t probe = 0; probe < BAM_MAX_PROBE && rc == BAM_PT_FULL; probe++) {
+            uint32_t* w = pc.table + (size_t)b * BAM_BUCKET_WORDS;
+            if (probe == 1) atom_add_relaxed(ctl, 1u);     /* the key will live outside its home */
+            for (int i = 1; i < 8; i++) {
+                if (ld_relaxed_gpu(&w[i]) == BAM_ENTRY_EMPTY &&
+                    atom_cas_relaxed(&w[i], BAM_ENTRY_EMPTY, entry) == BAM_ENTRY_EMPTY) {
+                    rc = BAM_PT_OK;
+                    break;
+                }
+            }
+            b = (b + 1u) & pc.bucket_mask;
+        }
+        if (rc == BAM_PT_FULL && BAM_MAX_PROBE > 1) atom_add_relaxed(ctl, 0xffffffffu);   /* undo the overflow count */
+    }
+    atom_and_release(ctl, ~BAM_BUCKET_LOCK);
+    return rc;
+}
+
+/* Remove the entry that maps to `slot` (the caller has claimed the slot). */
+BAM_DEV void pt_remove(const page_cache_d_t& pc, uint64_t tag, uint32_t slot)
+{
+    const uint64_t h = pt_hash(tag);
+    const uint32_t home = (uint32_t)h & pc.bucket_mask;
+    const uint32_t entry = ((uint32_t)(h >> 56) << 24) | slot;
+    uint32_t b = home;
+#pragma unroll 1
+    for (uint32_t probe = 0; probe < BAM_MAX_PROBE; probe++) {
+        uint32_t* w = pc.table + (size_t)b * BAM_BUCKET_WORDS;
+        for (int i = 1; i < 8; i++) {
+            if (ld_relaxed_gpu(&w[i]) == entry) {
+                st_release_gpu(&w[i], BAM_ENTRY_EMPTY);
+                if (b != home) atom_add_relaxed(pc.table + (size_t)home * BAM_BUCKET_WORDS, 0xffffffffu);
+                return;
+            }
+        }
+        b = (b + 1u) & pc.bucket_mask;
+    }
+}
+
+BAM_DEV uint64_t slot_bus_addr(const page_cache_d_t& pc, uint32_t slot)
+{
+    return (uint64_t)(pc.base_addr + (size_t)slot * pc.page_size);
+}
+
+/* Clock sweep: returns a slot claimed for the caller (state BUSY, no tag, no table entry), or
+ * BAM_SLOT_ERR.  Counterpart of page_cache_d_t::find_slot (page_cache.h:1786-1927). */
+BAM_DEV uint32_t find_slot(const page_cache_d_t& pc)
+{
+    spin_t sp;
+#pragma unroll 1
+    for (uint32_t tries = 1;; tries++) {
+        const uint64_t t = atom_add_relaxed(pc.clock_hand, 1ull);
+        const uint32_t s = (uint32_t)(t % pc.n_slots);
+        bam_slot_t* sl = &pc.slots[s];
+        const uint32_t st = ld_relaxed_gpu(&sl->state);
+        if (st == 0u) {
+            if (atom_cas_acquire(&sl->state, 0u, BAM_BUSY) == 0u) return s;
+        } else if ((st & ~BAM_DIRTY) == BAM_VALID) {
+            if (atom_cas_acquire(&sl->state, st, st | BAM_BUSY) == st) {
+                const uint64_t old = ld_relaxed_gpu(&sl->tag);
+                st_relaxed_gpu(&sl->tag, BAM_TAG_NONE);
+                pt_remove(pc, old, s);
+                /* write-back of a DIRTY victim belongs here once the write path exists */
+                atom_and_release(&sl->state, ~(BAM_VALID | BAM_DIRTY));
+                return s;
+            }
+        }
+        if ((tries & 63u) == 0u && sp.expired(pc.status, BAM_AT_FIND_SLOT)) return BAM_SLOT_ERR;
+    }
+}
+
+BAM_DEV void count_hit(const page_cache_d_t& pc, uint32_t count) { red_add_relaxed(&pc.stats[get_smid() & (BAM_STAT_STRIPES - 1)].hits, (uint64_t)count); }
+BAM_DEV void count_miss(const page_cache_d_t& pc, uint32_t count)
+{
+    bam_stat_stripe_t* s = &pc.stats[get_smid() & (BAM_STAT_STRIPES - 1)];
+    red_add_relaxed(&s->misses, (uint64_t)count);
+    red_add_relaxed(&s->read_ios, 1ull);
+}
+
+/* Pin the page `tag` for `count` lanes and return its slot; on a miss allocate a slot and read
+ * backing page `backing_page` through queue pair `queue`.  Returns BAM_SLOT_ERR after an
+ * error has been recorded.  Counterpart of range_d_t<T>::acquire_page (page_cache.h:1122-1224). */
+BAM_DEV uint32_t cache_acquire(const page_cache_d_t& pc, uint64_t tag, uint32_t count,
+                               uint64_t backing_page, uint32_t queue, bool write)
+{
+    bam_status_t* st = pc.status;
+    const uint64_t h = pt_hash(tag);
+    const uint32_t home = (uint32_t)h & pc.bucket_mask;
+    const uint32_t fp = (uint32_t)(h >> 56);
+    spin_t sp;
+#pragma unroll 1
+    for (;;) {
+        const uint32_t s = pt_lookup(pc, tag, home, fp);
+        if (s != BAM_SLOT_NONE) {
+            bam_slot_t* sl = &pc.slots[s];
+            uint32_t old = atom_add_acquire(&sl->state, count);
+            for (;;) {
+                if (ld_relaxed_gpu(&sl->tag) != tag) break;                 /* recycled under us */
+                if ((old & (BAM_VALID | BAM_BUSY)) == BAM_VALID) {
+                    if (write && !(old & BAM_DIRTY)) atom_or_relaxed(&sl->state, BAM_DIRTY);
+                    count_hit(pc, count);
+                    return s;
+                }
+                if ((old & (BAM_VALID | BAM_BUSY)) == 0u) break;           /* slot was given back */
+                if (sp.expired(st, BAM_AT_PAGE_BUSY, tag)) { red_add_relaxed(&sl->state, 0u - count); return BAM_SLOT_ERR; }
+                old = ld_acquire_gpu(&sl->state);
+            }
+            red_add_relaxed(&sl->state, 0u - count);
+            if (sp.expired(st, BAM_AT_PAGE_BUSY, tag)) return BAM_SLOT_ERR;
+            continue;
+        }
+        /* miss: claim a slot, publish the mapping, fill the slot */
+        const uint32_t v = find_slot(pc);
+        if (v == BAM_SLOT_ERR) return BAM_SLOT_ERR;
+        bam_slot_t* sl = &pc.slots[v];
+        st_relaxed_gpu(&sl->tag, tag);
+        __threadfence();
+        const int r = pt_insert(pc, tag, v, home, fp);
+        if (r != BAM_PT_OK) {
+            st_relaxed_gpu(&sl->tag, BAM_TAG_NONE);
+            atom_and_release(&sl->state, ~BAM_BUSY);                        /* give the slot back */
+            if (r == BAM_PT_EXISTS) continue;                               /* someone else is filling it */
+            if (r == BAM_PT_FULL) status_fail(st, BAM_ENOSPC, BAM_AT_TABLE_FULL, tag);
+            return BAM_SLOT_ERR;
+        }
+        Controller* c = pc.d_ctrl;
+        QueuePair* qp = c->d_qps + (queue % c->n_qps);
+        const uint64_t bus = slot_bus_addr(pc, v);
+        const uint64_t mps = 4096;
+        uint64_t prp2 = 0;
+        if (pc.page_size > mps) prp2 = (pc.page_size <= 2 * mps) ? bus + mps : (uint64_t)(pc.prp_lists + (size_t)v * pc.prp_list_stride);
+        const int rc = access_data_raw(qp, backing_page * pc.n_blocks_per_page, pc.n_blocks_per_page, bus, prp2, NVM_IO_READ);
+        if (rc != BAM_OK) return BAM_SLOT_ERR;
+        count_miss(pc, count);
+        atom_add_relaxed(&sl->state, count + (write ? BAM_DIRTY : 0u));
+        atom_xor_release(&sl->state, BAM_VALID | BAM_BUSY);                 /* BUSY -> VALID */
+        return v;
+    }
+}
+
+BAM_DEV void cache_release(const page_cache_d_t& pc, uint32_t slot, uint32_t count)
+{
+    red_add_release(&pc.slots[slot].state, 0u - count);
+}
+
+}  // namespace bam
+#endif

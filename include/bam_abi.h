@@ -1,0 +1,138 @@
+/*
+ * bam_abi.h -- C ABI of libbam_b200.so.
+ *
+ * Plain pointers, sizes and opaque handles only.  Every function returns 0 or a BAM_E*
+ * code (bam/abi_types.h) and never throws.  Kernel launchers are asynchronous on the given
+ * stream (a cudaStream_t passed as void*; NULL = default stream); device-side failures
+ * (a wait that ran out, an NVMe error status) are reported by bam_ctrl_status(), which
+ * synchronises the device first.  There is no CPU fallback: without a CUDA device every
+ * create call fails with BAM_ECUDA.
+ *
+ * Each entry point names the reference interface it stands in for.
+ */
+#ifndef BAM_ABI_H
+#define BAM_ABI_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct bam_ctrl* bam_ctrl_t;     /* emulated NVMe controller + its queue pairs  */
+typedef struct bam_cache* bam_cache_t;   /* page cache                                  */
+typedef struct bam_array* bam_array_t;   /* array of fixed-size elements over the cache */
+
+typedef struct {
+    uint64_t hits, misses, read_ios;
+} bam_cache_stats_t;
+
+typedef struct {
+    uint32_t code, where;
+    uint64_t detail;
+} bam_status_out_t;
+
+const char* bam_version(void);
+const char* bam_strerror(int code);                              /* nvm_strerror, include/nvm_error.h:67 */
+
+/* ---- controller ------------------------------------------------------------------------
+ * Replaces Controller::Controller(path, ns, gpu, queueDepth, numQueues) (include/ctrl.h:148-199)
+ * and the QueuePair constructor (include/queue.h:89-221): instead of opening /dev/libnvm*,
+ * it creates the emulated controller on `device` with a pinned, device-mapped backing store of
+ * `store_bytes` (logical block size `lba_bytes`, 512 or 4096) and `n_queues` I/O queue pairs of
+ * `queue_depth` entries (a power of two, 2..65536... capped at 1024 like MAX_SQ_ENTRIES_64K,
+ * include/queue.h:55) in device memory. */
+int bam_ctrl_create(bam_ctrl_t* out, int device, uint64_t store_bytes, uint32_t lba_bytes,
+                    uint32_t n_queues, uint32_t queue_depth);
+int bam_ctrl_destroy(bam_ctrl_t c);
+/* Host pointer of the backing store ("the media"); the caller may fill it directly. */
+void* bam_ctrl_store_host(bam_ctrl_t c);
+uint64_t bam_ctrl_store_bytes(bam_ctrl_t c);
+/* Fill the store with element[i] = splitmix64(seed ^ (first_elem + i)) (bam_synth.h) from the
+ * GPU through the mapping.  Stands in for loading a dataset onto the SSD
+ * (benchmarks/readwrite/main.cu:283-316). */
+int bam_ctrl_fill_store(bam_ctrl_t c, uint64_t seed, uint64_t first_elem, void* stream);
+/* Copy caller data into the store at a byte offset (host memcpy). */
+int bam_ctrl_write_store(bam_ctrl_t c, uint64_t byte_offset, const void* src, uint64_t bytes);
+/* Controller warps: n_blocks blocks of the fused launches run the command processor;
+ * batch = commands a warp fetches per lock hold.  0 keeps the current value. */
+int bam_ctrl_configure(bam_ctrl_t c, uint32_t n_ctrl_blocks, uint32_t batch, uint64_t spin_timeout_ns);
+/* Upper limit for one fused launch (default 300 s): the controller blocks flag BAM_ETIMEDOUT and
+ * every wait in the launch drains. */
+int bam_ctrl_set_launch_timeout(bam_ctrl_t c, uint64_t launch_timeout_ns);
+/* Cap the grid of the fused launches (0 = as many blocks as are co-resident).  Small caches
+ * need it: each resident warp may pin up to 32 pages at once. */
+int bam_ctrl_set_max_grid(bam_ctrl_t c, uint32_t max_grid);
+/* Fault injection on the controller side (host-configured, never faults the GPU):
+ * mode BAM_FAULT_DROP_CPL swallows the completion of the nth command from now,
+ * BAM_FAULT_STATUS completes it with `status`. */
+int bam_ctrl_inject_fault(bam_ctrl_t c, uint32_t mode, uint64_t nth, uint32_t status);
+/* Synchronise the device and read the status block; clear = reset it afterwards. */
+int bam_ctrl_status(bam_ctrl_t c, bam_status_out_t* out, int clear);
+/* Commands served since creation (Controller::print_reset_stats, include/ctrl.h:86-92). */
+int bam_ctrl_served(bam_ctrl_t c, uint64_t* out, int reset);
+/* Re-initialise every queue pair to its power-on state (nvm_queue_clear, src/queue.cpp:12-42).
+ * Needed after an injected fault left commands unaccounted for. */
+int bam_ctrl_reset_queues(bam_ctrl_t c);
+/* Device pointers for callers that write their own kernels (include/bam/*.cuh). */
+void* bam_ctrl_device_controller(bam_ctrl_t c);   /* Controller*            */
+int bam_ctrl_emu_descriptor(bam_ctrl_t c, void* out, size_t out_bytes); /* bam_emu_d_t by value */
+
+/* ---- page cache --------------------------------------------------------------------------
+ * Replaces page_cache_t::page_cache_t(page_size, n_pages, gpu, ctrl, max_range, ctrls)
+ * (include/page_cache.h:697-875). */
+int bam_cache_create(bam_cache_t* out, bam_ctrl_t ctrl, uint32_t page_size, uint64_t n_pages);
+int bam_cache_destroy(bam_cache_t pc);
+/* range_d_t counters (page_cache.h:904-907, printed by array_t::print_reset_stats :1731-1752). */
+int bam_cache_stats(bam_cache_t pc, bam_cache_stats_t* out, int reset);
+/* Drop every cached page (all slots free, table empty). */
+int bam_cache_invalidate(bam_cache_t pc);
+/* Audit after a launch: no pins left, no BUSY bits, every VALID slot is found through the page
+ * table, every table entry points at a slot with a matching tag.  *violations = 0 when clean. */
+int bam_cache_audit(bam_cache_t pc, uint64_t* violations);
+int bam_cache_descriptor(bam_cache_t pc, void* out, size_t out_bytes);  /* page_cache_d_t by value */
+
+/* ---- arrays --------------------------------------------------------------------------------
+ * Replaces range_t<T>(index_start, count, page_start, page_count, page_start_offset, page_size,
+ * cache, gpu) + array_t<T>(n_elems, disk_start_offset, {range}) (page_cache.h:978-1030,
+ * :1754-1772) for a single-range array of `elem_bytes`-sized elements (4 or 8) that starts at
+ * byte `store_byte_offset` (page aligned) of the backing store. */
+int bam_array_create(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
+                     uint64_t store_byte_offset);
+int bam_array_destroy(bam_array_t a);
+void* bam_array_device_ptr(bam_array_t a);         /* array_d_t<T>* (array_t::d_array_ptr) */
+
+/* ---- kernel launchers -----------------------------------------------------------------------
+ * The reference exports no kernels (they live in benchmarks/...); these are the same
+ * workloads as launchable entry points.  Every launcher runs ONE fused cooperative kernel:
+ * the first blocks are the emulated controller's command processor, the rest the workload. */
+
+/* Block benchmark (benchmarks/block/main.cu:137-200): request r reads 4 KiB-aligned page
+ * pages[r] (or, if pages == NULL, bam_block_request_page(req_seed, r, n_store_pages)) of
+ * `page_bytes` straight into a private cache slot through read_data, bypassing the cache
+ * look-up.  crc_out (device, n_reqs u32, may be NULL) receives the CRC-32 of what arrived;
+ * sum_out (device u64, may be NULL) is incremented by the wrapping sum of all words read. */
+int bam_launch_block_read(bam_cache_t pc, uint64_t n_reqs, const uint64_t* pages_dev, uint64_t req_seed,
+                          uint32_t* crc_out_dev, uint64_t* sum_out_dev, void* stream);
+
+/* Array benchmark (benchmarks/array/main.cu:54-65): n_lanes reader lanes x reqs_per_lane
+ * element reads through array[]; indices from idx_dev[lane*reqs_per_lane + k], or if idx_dev ==
+ * NULL from PCG32 stream `lane` seeded with access_seed (bam_synth.h).  *sum_out_dev (device u64)
+ * is incremented by the wrapping sum of the values read. */
+int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t reqs_per_lane, const uint64_t* idx_dev,
+                          uint64_t access_seed, uint64_t* sum_out_dev, void* stream);
+
+/* Cache benchmark (benchmarks/cache/main.cu:44-114): each warp reads whole pages of the
+ * array (page list pages_dev[n_pages], or pages first_page .. first_page+n_pages-1 when NULL),
+ * all 32 lanes striding the page; wrapping sum of every element into *sum_out_dev. */
+int bam_launch_page_scan(bam_array_t a, uint64_t n_pages, const uint64_t* pages_dev, uint64_t first_page,
+                         uint64_t* sum_out_dev, void* stream);
+
+/* Grid the launchers use: total blocks, controller blocks among them, threads per block. */
+int bam_launch_geometry(bam_ctrl_t c, uint32_t* grid, uint32_t* ctrl_blocks, uint32_t* threads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BAM_ABI_H */

@@ -1,0 +1,200 @@
+"""ctypes wrapper of oracle/libbam_oracle.so (built from bam_oracle.c by oracle/Makefile).
+
+Test infrastructure only: the checker and the timed host-core baseline, never a fallback.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libbam_oracle.so")
+u32, u64, vp = C.c_uint32, C.c_uint64, C.c_void_p
+
+
+class RefResult(C.Structure):
+    _fields_ = [("checksum", u64), ("accesses", u64), ("hits", u64), ("misses", u64), ("read_ios", u64),
+                ("seconds", C.c_double), ("worker_threads", u32), ("ctrl_threads", u32)]
+
+
+def build(force=False):
+    src = os.path.join(HERE, "bam_oracle.c")
+    hdr = os.path.join(HERE, "..", "include", "bam_synth.h")
+    if (force or not os.path.exists(LIB_PATH)
+            or os.path.getmtime(LIB_PATH) < max(os.path.getmtime(src), os.path.getmtime(hdr))):
+        subprocess.run(["make", "-C", HERE, "-B", "libbam_oracle.so"], check=True, capture_output=True)
+    return LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(LIB_PATH)
+        L.orc_splitmix64.restype = u64
+        L.orc_splitmix64.argtypes = [u64]
+        L.orc_pcg32_stream.argtypes = [u64, u64, vp, u64]
+        L.orc_crc32.restype = u32
+        L.orc_crc32.argtypes = [vp, u64]
+        L.orc_permute.restype = u64
+        L.orc_permute.argtypes = [u64, u64, u64]
+        L.orc_fill_store.argtypes = [vp, u64, u64, u64]
+        L.orc_array_indices.argtypes = [u64, u64, u64, u64, u64, vp]
+        L.orc_array_checksum.restype = u64
+        L.orc_array_checksum.argtypes = [u64, u64, u64, u64, u64, u64]
+        L.orc_indexed_checksum.restype = u64
+        L.orc_indexed_checksum.argtypes = [u64, u64, vp, u64]
+        L.orc_page_crc.restype = u32
+        L.orc_page_crc.argtypes = [u64, u64, u32]
+        L.orc_block_requests.argtypes = [u64, u64, u64, u32, u64, u64, vp, vp]
+        L.orc_zipf_indices.argtypes = [vp, u64, u32, u64, u64, u64, u64, u64, vp]
+        L.orc_rmat_csr.restype = u64
+        L.orc_rmat_csr.argtypes = [u64, u32, u64, u32, u32, u32, vp, vp]
+        L.orc_max_degree_vertex.restype = u64
+        L.orc_max_degree_vertex.argtypes = [u64, vp]
+        L.orc_bfs.restype = u64
+        L.orc_bfs.argtypes = [u64, vp, vp, u64, vp]
+        L.orc_cc.restype = u64
+        L.orc_cc.argtypes = [u64, vp, vp, vp]
+        L.ref_array_read.restype = C.c_int
+        L.ref_array_read.argtypes = [vp, u64, u32, u64, u32, u32, u32, u32, u32, vp, u64, u64, u64, u64,
+                                     C.POINTER(RefResult)]
+        L.ref_block_read.restype = C.c_int
+        L.ref_block_read.argtypes = [vp, u64, u32, u32, u32, u32, u32, u32, u64, u64, vp, C.POINTER(RefResult)]
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(vp) if a is not None else None
+
+
+def splitmix64(x):
+    return lib().orc_splitmix64(x)
+
+
+def pcg32_stream(state, seq, n):
+    out = np.empty(n, dtype=np.uint32)
+    lib().orc_pcg32_stream(state, seq, _p(out), n)
+    return out
+
+
+def crc32(b):
+    buf = np.frombuffer(bytes(b), dtype=np.uint8)
+    return lib().orc_crc32(_p(buf), len(buf))
+
+
+def fill_store(seed, first_elem, n, out=None):
+    if out is None:
+        out = np.empty(n, dtype=np.uint64)
+    lib().orc_fill_store(_p(out), seed, first_elem, n)
+    return out
+
+
+def array_indices(access_seed, n_elems, lane_begin, lane_end, reqs_per_lane):
+    out = np.empty((lane_end - lane_begin) * reqs_per_lane, dtype=np.uint64)
+    lib().orc_array_indices(access_seed, n_elems, lane_begin, lane_end, reqs_per_lane, _p(out))
+    return out
+
+
+def array_checksum(store_seed, n_elems, access_seed, lane_begin, lane_end, reqs_per_lane):
+    return lib().orc_array_checksum(store_seed, n_elems, access_seed, lane_begin, lane_end, reqs_per_lane)
+
+
+def indexed_checksum(store_seed, first_elem, idx):
+    idx = np.ascontiguousarray(idx, dtype=np.uint64)
+    return lib().orc_indexed_checksum(store_seed, first_elem, _p(idx), len(idx))
+
+
+def page_crc(store_seed, page, page_bytes=4096):
+    return lib().orc_page_crc(store_seed, page, page_bytes)
+
+
+def block_requests(store_seed, req_seed, n_pages, page_bytes, r0, r1, want_crc=True):
+    pages = np.empty(r1 - r0, dtype=np.uint64)
+    crc = np.empty(r1 - r0, dtype=np.uint32) if want_crc else None
+    lib().orc_block_requests(store_seed, req_seed, n_pages, page_bytes, r0, r1, _p(pages), _p(crc))
+    return pages, crc
+
+
+def zipf_cdf(n_pages, s=0.99):
+    """64-bit fixed-point CDF of Zipf(s) over ranks 1..n_pages (rank r has weight r^-s).
+    Built in float64 with a sequential cumulative sum; the last entry is forced to 2^64-1."""
+    w = np.arange(1, n_pages + 1, dtype=np.float64) ** (-s)
+    c = np.cumsum(w)
+    c /= c[-1]
+    q = np.minimum(np.floor(c * 18446744073709551616.0), 18446744073709549568.0).astype(np.uint64)
+    q[-1] = np.uint64(0xFFFFFFFFFFFFFFFF)
+    return q
+
+
+def zipf_indices(cdf, n_pages, elems_per_page, perm_seed, access_seed, lane_begin, lane_end, reqs_per_lane):
+    out = np.empty((lane_end - lane_begin) * reqs_per_lane, dtype=np.uint64)
+    lib().orc_zipf_indices(_p(cdf), n_pages, elems_per_page, perm_seed, access_seed, lane_begin, lane_end,
+                           reqs_per_lane, _p(out))
+    return out
+
+
+def rmat_thresholds(a=0.57, b=0.19, c=0.19):
+    """Integer quadrant thresholds floor(p * 2^32) for the R-MAT generator."""
+    ta = int(a * 4294967296.0)
+    tab = int((a + b) * 4294967296.0)
+    tabc = int((a + b + c) * 4294967296.0)
+    return ta, tab, tabc
+
+
+def rmat_csr(seed, scale, edge_factor=16, thresholds=None):
+    ta, tab, tabc = thresholds or rmat_thresholds()
+    n = 1 << scale
+    offsets = np.empty(n + 1, dtype=np.uint64)
+    m = lib().orc_rmat_csr(seed, scale, edge_factor, ta, tab, tabc, _p(offsets), None)
+    cols = np.empty(m, dtype=np.uint64)
+    m2 = lib().orc_rmat_csr(seed, scale, edge_factor, ta, tab, tabc, _p(offsets), _p(cols))
+    assert m == m2
+    return offsets, cols
+
+
+def max_degree_vertex(offsets):
+    return lib().orc_max_degree_vertex(len(offsets) - 1, _p(offsets))
+
+
+def bfs(offsets, cols, src):
+    n = len(offsets) - 1
+    level = np.empty(n, dtype=np.uint32)
+    scanned = lib().orc_bfs(n, _p(offsets), _p(cols), src, _p(level))
+    return level, scanned
+
+
+def cc(offsets, cols):
+    n = len(offsets) - 1
+    label = np.empty(n, dtype=np.uint64)
+    comps = lib().orc_cc(n, _p(offsets), _p(cols), _p(label))
+    return label, comps
+
+
+def ref_array_read(store, page_size, n_slots, n_qps, qdepth, lba_bytes, workers, ctrl_threads,
+                   idx=None, access_seed=0, lane_begin=0, lane_end=0, reqs_per_lane=0):
+    """The reference's array read path restated on host threads; returns a RefResult."""
+    r = RefResult()
+    if idx is not None:
+        idx = np.ascontiguousarray(idx, dtype=np.uint64)
+    rc = lib().ref_array_read(_p(store), len(store), page_size, n_slots, n_qps, qdepth, lba_bytes, workers,
+                              ctrl_threads, _p(idx), access_seed, lane_begin, lane_end, reqs_per_lane, C.byref(r))
+    if rc:
+        raise RuntimeError(f"ref_array_read failed: {rc}")
+    return r
+
+
+def ref_block_read(store, page_size, n_qps, qdepth, lba_bytes, workers, ctrl_threads, req_seed, n_reqs,
+                   want_crc=True):
+    r = RefResult()
+    crc = np.zeros(n_reqs, dtype=np.uint32) if want_crc else None
+    rc = lib().ref_block_read(_p(store), store.nbytes, page_size, n_qps, qdepth, lba_bytes, workers, ctrl_threads,
+                              req_seed, n_reqs, _p(crc), C.byref(r))
+    if rc:
+        raise RuntimeError(f"ref_block_read failed: {rc}")
+    return r, crc
