@@ -4,4 +4,5 @@ Host-side mirror of the reference's C++ host objects (Controller, page_cache_t, 
 array_t) over the C ABI of libbam_b200.so.  The CUDA library is mandatory.
 """
 from ._lib import BamError, CacheStats, StatusOut, load  # noqa: F401
-from .host import Array, Controller, PageCache  # noqa: F401
+from .host import (Array, Controller, PageCache, gen_uniform_indices, gen_zipf_indices,  # noqa: F401
+                   direct_checksum, shard_pages, zipf_cdf)

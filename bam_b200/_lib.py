@@ -50,6 +50,9 @@ SIGNATURES = {
     "bam_launch_block_read": (ci, [vp, u64, vp, u64, vp, vp, vp]),
     "bam_launch_array_read": (ci, [vp, u64, u64, vp, u64, vp, vp]),
     "bam_launch_page_scan": (ci, [vp, u64, vp, u64, vp, vp]),
+    "bam_gen_uniform_indices": (ci, [vp, u64, u64, u64, u64, vp]),
+    "bam_gen_zipf_indices": (ci, [vp, u64, u64, u64, vp, u64, u32, u64, vp]),
+    "bam_direct_checksum": (ci, [vp, u64, u64, u64, vp, vp]),
     "bam_launch_geometry": (ci, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
 }
 

@@ -57,6 +57,44 @@ __global__ void k_fill_store(uint64_t* dst, uint64_t n_elems, uint64_t seed, uin
     }
 }
 
+/* Access streams of the synthetic workloads, materialised as index lists in device memory. */
+__global__ void k_gen_uniform(uint64_t* out, uint64_t n_lanes, uint64_t reqs_per_lane, uint64_t access_seed, uint64_t n_elems)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthr = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t lane = tid; lane < n_lanes; lane += nthr) {
+        bam_pcg32_t g;
+        bam_lane_stream(&g, access_seed, lane);
+        for (uint64_t k = 0; k < reqs_per_lane; k++) out[lane * reqs_per_lane + k] = bam_uniform_index(&g, n_elems);
+    }
+}
+
+__global__ void k_gen_zipf(uint64_t* out, uint64_t n_lanes, uint64_t reqs_per_lane, uint64_t access_seed,
+                           const uint64_t* cdf, uint64_t n_pages, uint32_t elems_per_page, uint64_t perm_seed)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthr = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t lane = tid; lane < n_lanes; lane += nthr) {
+        bam_pcg32_t g;
+        bam_lane_stream(&g, access_seed, lane);
+        for (uint64_t k = 0; k < reqs_per_lane; k++)
+            out[lane * reqs_per_lane + k] = bam_zipf_access(&g, cdf, n_pages, elems_per_page, perm_seed);
+    }
+}
+
+/* Wrapping sum of store element (first_elem + idx[i]) recomputed from its definition: the value a
+ * cached read of that index must return.  Used to verify full-size runs on the device. */
+__global__ void k_direct_checksum(const uint64_t* idx, uint64_t n, uint64_t seed, uint64_t first_elem, uint64_t* out)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthr = (uint64_t)gridDim.x * blockDim.x;
+    uint64_t sum = 0;
+    for (uint64_t i = tid; i < n; i += nthr) sum += bam_store_elem(seed, first_elem + idx[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31u) == 0u) atomicAdd((unsigned long long*)out, (unsigned long long)sum);
+}
+
 /* Post-launch audit of the cache invariants; counts violations. */
 __global__ void k_audit(page_cache_d_t pc, uint64_t n_buckets, unsigned long long* violations)
 {
@@ -742,6 +780,35 @@ extern "C" int bam_launch_page_scan(bam_array_t a, uint64_t n_pages, const uint6
     PageScanWork w;
     w.r = a->h_range; w.n_pages = n_pages; w.pages = pages_dev; w.first_page = first_page; w.sum_out = sum_out_dev;
     return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_gen_uniform_indices(uint64_t* out_dev, uint64_t n_lanes, uint64_t reqs_per_lane, uint64_t access_seed,
+                                       uint64_t n_elems, void* stream)
+{
+    if (!out_dev || n_elems == 0) return BAM_EINVAL;
+    k_gen_uniform<<<1184, 256, 0, (cudaStream_t)stream>>>(out_dev, n_lanes, reqs_per_lane, access_seed, n_elems);
+    CK(cudaGetLastError());
+    return BAM_OK;
+}
+
+extern "C" int bam_gen_zipf_indices(uint64_t* out_dev, uint64_t n_lanes, uint64_t reqs_per_lane, uint64_t access_seed,
+                                    const uint64_t* cdf_dev, uint64_t n_pages, uint32_t elems_per_page,
+                                    uint64_t perm_seed, void* stream)
+{
+    if (!out_dev || !cdf_dev || n_pages == 0 || elems_per_page == 0) return BAM_EINVAL;
+    k_gen_zipf<<<1184, 256, 0, (cudaStream_t)stream>>>(out_dev, n_lanes, reqs_per_lane, access_seed, cdf_dev, n_pages,
+                                                       elems_per_page, perm_seed);
+    CK(cudaGetLastError());
+    return BAM_OK;
+}
+
+extern "C" int bam_direct_checksum(const uint64_t* idx_dev, uint64_t n, uint64_t store_seed, uint64_t first_elem,
+                                   uint64_t* sum_out_dev, void* stream)
+{
+    if (!idx_dev || !sum_out_dev) return BAM_EINVAL;
+    k_direct_checksum<<<1184, 256, 0, (cudaStream_t)stream>>>(idx_dev, n, store_seed, first_elem, sum_out_dev);
+    CK(cudaGetLastError());
+    return BAM_OK;
 }
 
 extern "C" int bam_launch_geometry(bam_ctrl_t c, uint32_t* grid, uint32_t* ctrl_blocks, uint32_t* threads)

@@ -172,3 +172,45 @@ class Array:
     def page_scan(self, n_pages, sum_out, pages=None, first_page=0, stream=None):
         check(self.lib.bam_launch_page_scan(self.h, n_pages, _ptr(pages), first_page, _ptr(sum_out), _ptr(stream)),
               "bam_launch_page_scan")
+
+
+def gen_uniform_indices(out, n_lanes, reqs_per_lane, access_seed, n_elems, stream=None):
+    """Write the array random-read access stream (bam_synth.h) into a device u64 buffer."""
+    lib = _lib.load()
+    check(lib.bam_gen_uniform_indices(_ptr(out), n_lanes, reqs_per_lane, access_seed, n_elems, _ptr(stream)),
+          "bam_gen_uniform_indices")
+
+
+def gen_zipf_indices(out, n_lanes, reqs_per_lane, access_seed, cdf, n_pages, elems_per_page, perm_seed, stream=None):
+    """Write the skewed-scan access stream (Zipf page popularity) into a device u64 buffer."""
+    lib = _lib.load()
+    check(lib.bam_gen_zipf_indices(_ptr(out), n_lanes, reqs_per_lane, access_seed, _ptr(cdf), n_pages, elems_per_page,
+                                   perm_seed, _ptr(stream)), "bam_gen_zipf_indices")
+
+
+def zipf_cdf(n_pages, s=0.99):
+    """64-bit fixed-point CDF table of Zipf(s) over page ranks 1..n_pages (host, numpy uint64).
+
+    cdf[r] = floor(2^64 * P(rank <= r)); float64 weights, sequential cumulative sum, last entry
+    forced to 2^64-1.  Built once on the host: the device only compares integers."""
+    import numpy as np
+    w = np.arange(1, n_pages + 1, dtype=np.float64) ** (-s)
+    c = np.cumsum(w)
+    c /= c[-1]
+    q = np.minimum(np.floor(c * 18446744073709551616.0), 18446744073709549568.0).astype(np.uint64)
+    q[-1] = np.uint64(0xFFFFFFFFFFFFFFFF)
+    return q
+
+
+def shard_pages(n_pages, world_size, rank):
+    """Contiguous page-range sharding of a store: returns (first_page, n_local_pages) of `rank`."""
+    base, rem = divmod(n_pages, world_size)
+    first = rank * base + min(rank, rem)
+    return first, base + (1 if rank < rem else 0)
+
+
+def direct_checksum(idx, n, store_seed, first_elem, sum_out, stream=None):
+    """Device-side recomputation of the wrapping sum an index list must read (no cache, no queues)."""
+    lib = _lib.load()
+    check(lib.bam_direct_checksum(_ptr(idx), n, store_seed, first_elem, _ptr(sum_out), _ptr(stream)),
+          "bam_direct_checksum")

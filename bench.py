@@ -1,0 +1,391 @@
+#!/usr/bin/env python
+"""bench.py -- 4 KiB-page IOPS / GB/s through the GPU page cache (skewed array scan).
+
+Workload (the multi-GPU skewed array scan configuration): a 64 GiB backing store of
+splitmix64(seed ^ i) elements, sharded by contiguous 4 KiB-page range over the N ranks, one
+16 GiB page cache and 128 x 1024 NVMe queue pairs per GPU; every step each GPU performs
+2^26 element reads (2^20 reader lanes x 64) whose page popularity is Zipf(0.99) over its
+shard (seeded rank permutation) with a uniform offset in the page.  One step = one fused launch
+(emulated NVMe controller blocks + reader blocks).  Output per rank: the wrapping 64-bit sum,
+verified on the device against the store's definition and reduced over ranks.
+
+    python bench.py --gpus N --steps K --warmup W            the CUDA path
+    python bench.py --impl reference ...                     the CPU restatement on host cores
+
+One JSON line on rank 0.  `value` is whole-job 4 KiB page reads per second with the access lists
+resident in HBM; `e2e` repeats it with the lists copied from pinned host memory and the result
+read back inside the timed region.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+STORE_SEED, PERM_SEED, ACCESS_SEED = 0x5EED, 17, 23
+PAGE = 4096
+EPP = PAGE // 8
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="bam", choices=["bam", "reference"])
+    ap.add_argument("--store-gib", type=float, default=64.0, help="total backing store over all ranks")
+    ap.add_argument("--cache-gib", type=float, default=16.0, help="page cache per GPU")
+    ap.add_argument("--lanes", type=int, default=1 << 20)
+    ap.add_argument("--reqs", type=int, default=64)
+    ap.add_argument("--queues", type=int, default=128)
+    ap.add_argument("--depth", type=int, default=1024)
+    ap.add_argument("--ctrl-blocks", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--cpu-sample-lanes", type=int, default=1 << 12)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi during the timed region."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+                for n, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return None
+
+
+def fill_touched_pages(orc, store, first_elem, idx):
+    pages = np.unique(idx // np.uint64(EPP))
+    orc.fill_pages(store, STORE_SEED, first_elem, pages, EPP)
+    return len(pages)
+
+
+def cpu_reference_step(orc, n_local_pages, first_page, cache_pages, queues, depth, lanes, reqs, access_seed,
+                       workers, ctrl_threads, store, cdf):
+    """One bounded sample of the workload through the CPU restatement of the reference's queue
+    and cache protocol.  Returns (RefResult, seconds spent in the timed access loop)."""
+    idx = orc.zipf_indices(cdf, n_local_pages, EPP, PERM_SEED, access_seed, 0, lanes, reqs)
+    fill_touched_pages(orc, store, first_page * EPP, idx)
+    r = orc.ref_array_read(store, PAGE, cache_pages, queues, depth, 512, workers, ctrl_threads, idx=idx,
+                           lane_end=lanes, reqs_per_lane=reqs)
+    want = orc.indexed_checksum(STORE_SEED, first_page * EPP, idx)
+    if r.checksum != want:
+        raise RuntimeError("CPU restatement checksum mismatch")
+    return r
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's own algorithm for this path restated for host threads
+    (the reference cannot be built to run here: its host library needs /dev/libnvm* and its
+    device headers do not compile for a host).  Rank 0 alone runs it."""
+    if rank != 0:
+        return
+    from oracle import pyoracle as orc
+    cores = os.cpu_count() or 1
+    ctrl_threads = max(1, cores // 8)
+    workers = max(1, cores - ctrl_threads)
+    total_pages = int(args.store_gib * (1 << 30)) // PAGE
+    n_local = total_pages // world
+    cache_pages = int(args.cache_gib * (1 << 30)) // PAGE
+    cdf = orc.zipf_cdf(n_local)
+    store = np.empty(n_local * EPP, dtype=np.uint64)        # virtual; only touched pages are filled
+    lanes = args.cpu_sample_lanes
+    # shrink the in-memory cache of the sample to what the sample can touch
+    cache_slots = min(cache_pages, lanes * args.reqs)
+    times, ios, acc = [], 0, 0
+    for s in range(args.warmup + args.steps):
+        r = cpu_reference_step(orc, n_local, 0, cache_slots, min(args.queues, 128), args.depth, lanes, args.reqs,
+                               ACCESS_SEED + 1000 + s, workers, ctrl_threads, store, cdf)
+        if s >= args.warmup:
+            times.append(r.seconds); ios += r.read_ios; acc += r.accesses
+    t = sum(times)
+    value = ios / t
+    sample = (f"{lanes} lanes x {args.reqs} reads per step of the same Zipf(0.99) stream over one {n_local}-page shard, "
+              f"cold cache of {cache_slots} slots each step, {workers} reader threads + {ctrl_threads} controller threads")
+    line = {
+        "impl": "reference", "metric": "4KB-page IOPS via page cache", "value": value, "unit": "IOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / max(1, args.steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+        "config": workload_config(args, world),
+        "gb_per_s": value * PAGE / 1e9, "accesses_per_s": acc / t,
+        "cpu_baseline": {"value": value, "unit": "IOPS", "cores": workers + ctrl_threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "IOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, world):
+    return {"workload": "multi-GPU skewed array scan (Zipf 0.99 page popularity) through the page cache",
+            "store_gib_total": args.store_gib, "shards": world, "cache_gib_per_gpu": args.cache_gib,
+            "page_bytes": PAGE, "queues_per_gpu": args.queues, "queue_depth": args.depth,
+            "reads_per_gpu_per_step": args.lanes * args.reqs, "zipf_s": 0.99,
+            "l2": "inputs (cache + access lists) far larger than L2; no explicit flush"}
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import bam_b200
+    from bam_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    total_pages = int(args.store_gib * (1 << 30)) // PAGE
+    first_page, n_local = bam_b200.shard_pages(total_pages, world, rank)
+    cache_pages = min(int(args.cache_gib * (1 << 30)) // PAGE, (1 << 24) - 2)
+    lanes, reqs = args.lanes, args.reqs
+    n_acc = lanes * reqs
+
+    t0 = time.time()
+    ctrl = bam_b200.Controller(n_local * PAGE, local_rank, queue_depth=args.depth, num_queues=args.queues)
+    ctrl.configure(ctrl_blocks=args.ctrl_blocks, batch=args.batch)
+    ctrl.fill_store(STORE_SEED, first_elem=first_page * EPP)
+    cache = bam_b200.PageCache(ctrl, PAGE, cache_pages)
+    arr = bam_b200.Array(cache, n_local * EPP)
+    cdf = bam_b200.zipf_cdf(n_local)
+    d_cdf = torch.from_numpy(cdf.view(np.int64)).to(dev)
+    torch.cuda.synchronize()
+    setup_s = time.time() - t0
+
+    n_steps = args.warmup + args.steps
+    stream = torch.cuda.current_stream()
+    sptr = stream.cuda_stream
+    d_idx = [torch.empty(n_acc, dtype=torch.int64, device=dev) for _ in range(n_steps)]
+    for s in range(n_steps):
+        bam_b200.gen_zipf_indices(d_idx[s], lanes, reqs, ACCESS_SEED + 1000 * rank + s, d_cdf, n_local, EPP,
+                                  PERM_SEED + rank, stream=sptr)
+    sums = torch.zeros(n_steps, dtype=torch.int64, device=dev)
+    want = torch.zeros(n_steps, dtype=torch.int64, device=dev)
+    for s in range(n_steps):
+        bam_b200.direct_checksum(d_idx[s], n_acc, STORE_SEED, first_page * EPP, want[s:s + 1], stream=sptr)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run_step(s):
+        arr.read(lanes, reqs, sums[s:s + 1], idx=d_idx[s], stream=sptr)
+
+    # ---- device-resident timing: value -------------------------------------------------------
+    for s in range(args.warmup):
+        run_step(s)
+    ctrl.check_status()
+    cache.stats(reset=True)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for k in range(args.steps):
+        ev[k][0].record(stream)
+        run_step(args.warmup + k)
+        ev[k][1].record(stream)
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ctrl.check_status()
+    elapsed_ms = e0.elapsed_time(e1)
+    kernel_ms = [a.elapsed_time(b) for a, b in ev]
+    st = cache.stats(reset=True)
+    ok = bool((sums == want).all().item())
+    audit = cache.audit()
+
+    # ---- end to end: access lists start in pinned host memory, result read back ----------------
+    h_idx = torch.empty(n_acc, dtype=torch.int64).pin_memory()
+    h_idx.copy_(d_idx[args.warmup])
+    d_stage = torch.empty(n_acc, dtype=torch.int64, device=dev)
+    e2e_sum = torch.zeros(1, dtype=torch.int64, device=dev)
+    h_sum = torch.zeros(1, dtype=torch.int64).pin_memory()
+    cache.stats(reset=True)
+    barrier()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record(stream)
+    for k in range(args.steps):
+        d_stage.copy_(h_idx, non_blocking=True)
+        e2e_sum.zero_()
+        arr.read(lanes, reqs, e2e_sum, idx=d_stage, stream=sptr)
+        h_sum.copy_(e2e_sum, non_blocking=True)
+        stream.synchronize()
+    g1.record(stream)
+    barrier()
+    ctrl.check_status()
+    e2e_ms = g0.elapsed_time(g1)
+    st_e2e = cache.stats(reset=True)
+    ok = ok and (int(h_sum.item()) == int(want[args.warmup].item()))
+
+    # ---- host-link peak (pinned H2D copy) and warm hit-path pass (HBM roofline) ----------------
+    link_gbs, hit = None, None
+    if rank == 0:
+        pin = torch.empty(1 << 28, dtype=torch.uint8).pin_memory()
+        dbuf = torch.empty(1 << 28, dtype=torch.uint8, device=dev)
+        best = 0.0
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); dbuf.copy_(pin, non_blocking=True); b.record(stream); stream.synchronize()
+            best = max(best, (1 << 28) / (a.elapsed_time(b) * 1e-3) / 1e9)
+        link_gbs = best
+        del pin, dbuf
+        # warm pass: scan pages that are resident (scan the same list twice, time the second)
+        n_scan = min(cache_pages // 2, n_local)
+        scan_sum = torch.zeros(1, dtype=torch.int64, device=dev)
+        cache.invalidate()
+        arr.page_scan(n_scan, scan_sum, first_page=0, stream=sptr)
+        torch.cuda.synchronize()
+        cache.stats(reset=True)
+        times = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); arr.page_scan(n_scan, scan_sum, first_page=0, stream=sptr); b.record(stream)
+            stream.synchronize()
+            times.append(a.elapsed_time(b))
+        ctrl.check_status()
+        sst = cache.stats(reset=True)
+        hit = {"ms": float(np.mean(times[1:])), "pages": n_scan, "hits": sst["hits"], "misses": sst["misses"]}
+
+    # ---- reduce over ranks ---------------------------------------------------------------------------
+    tot = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    cnt = torch.tensor([st["read_ios"], st["hits"], st["misses"], st_e2e["read_ios"], int(ok), audit],
+                       dtype=torch.int64, device=dev)
+    red = sums[args.warmup:].clone()
+    if world > 1:
+        dist.all_reduce(tot, op=dist.ReduceOp.MAX)
+        dist.all_reduce(cnt, op=dist.ReduceOp.SUM)
+        dist.all_reduce(red, op=dist.ReduceOp.SUM)          # wrapping u64 sum == int64 sum bit for bit
+    elapsed_ms, e2e_ms = tot.tolist()
+    read_ios, hits, misses, e2e_ios, n_ok, audits = cnt.tolist()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        hbm_peak = peaks["hbm_gbs"] if peaks else 6650.0
+        t = elapsed_ms * 1e-3
+        value = read_ios / t
+        gbs = value * PAGE / 1e9
+        # per-launch figures of the dominant (only) kernel of the step, rank 0
+        launch_ms = float(np.mean(kernel_ms))
+        ach_link = (st["read_ios"] / args.steps) * PAGE / (launch_ms * 1e-3) / 1e9
+        line = {
+            "metric": "4KB-page IOPS via page cache", "value": value, "unit": "IOPS",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+            "config": workload_config(args, world),
+            "gb_per_s": gbs, "accesses_per_s": world * n_acc * args.steps / t,
+            "hit_rate": hits / max(1, hits + misses),
+            "checksum_reduced": [f"{int(x) & ((1 << 64) - 1):#018x}" for x in red.tolist()],
+            "verified": bool(n_ok == world and audits == 0),
+            "e2e": {"value": e2e_ios / (e2e_ms * 1e-3), "unit": "IOPS", "h2d_bytes_per_step": n_acc * 8,
+                    "d2h_bytes_per_step": 8},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "host_link", "achieved": ach_link, "peak": link_gbs, "unit": "GB/s",
+                         "frac": ach_link / link_gbs if link_gbs else None, "traffic": None,
+                         "kernel": "bam_fused<ArrayReadWork>",
+                         "note": "miss path: 4096 algorithmic bytes per page read cross the host link once; peak = "
+                                 "pinned-memory H2D copy measured in this run"},
+            "roofline_hit": {"bound": "hbm", "achieved": hit["pages"] * PAGE / (hit["ms"] * 1e-3) / 1e9,
+                             "peak": hbm_peak, "unit": "GB/s",
+                             "frac": hit["pages"] * PAGE / (hit["ms"] * 1e-3) / 1e9 / hbm_peak, "traffic": None,
+                             "kernel": "bam_fused<PageScanWork>", "hits": hit["hits"], "misses": hit["misses"],
+                             "note": "warm cache: whole resident pages read through the cache, 4096 algorithmic "
+                                     "bytes per page; peak = MEASURED_PEAKS.json hbm_gbs" if peaks else "of fallback"},
+            "clocks": clocks, "setup_s": setup_s,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            try:
+                from oracle import pyoracle as orc
+                cores = os.cpu_count() or 1
+                ctrl_threads = max(1, cores // 8)
+                workers = max(1, cores - ctrl_threads)
+                cl = args.cpu_sample_lanes
+                store = np.empty(n_local * EPP, dtype=np.uint64)
+                slots = min(cache_pages, cl * reqs)
+                t_cpu, ios_cpu = 0.0, 0
+                for s in range(3):
+                    r = cpu_reference_step(orc, n_local, first_page, slots, min(args.queues, 128), args.depth, cl, reqs,
+                                           ACCESS_SEED + 5000 + s, workers, ctrl_threads, store, cdf)
+                    t_cpu += r.seconds; ios_cpu += r.read_ios
+                line["cpu_baseline"] = {
+                    "value": ios_cpu / t_cpu, "unit": "IOPS", "cores": workers + ctrl_threads, "kind": "port",
+                    "sample": f"3 x ({cl} lanes x {reqs} reads) of the same Zipf stream, cold {slots}-slot cache, "
+                              f"{workers} reader + {ctrl_threads} controller threads"}
+            except Exception as e:  # the baseline is reported, never required
+                line["cpu_baseline"] = {"value": None, "unit": "IOPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+        print(json.dumps(line), flush=True)
+
+    arr.close(); cache.close(); ctrl.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -129,6 +129,25 @@ int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t reqs_per_lan
 int bam_launch_page_scan(bam_array_t a, uint64_t n_pages, const uint64_t* pages_dev, uint64_t first_page,
                          uint64_t* sum_out_dev, void* stream);
 
+/* ---- synthetic access streams ------------------------------------------------------------------
+ * The reference benchmarks build their access lists on the host with rand()
+ * (benchmarks/array/main.cu:150-162, benchmarks/pattern/main.cu:560-600); these write the seeded
+ * streams of bam_synth.h as u64 element indices, out[lane*reqs_per_lane + k], on the device. */
+int bam_gen_uniform_indices(uint64_t* out_dev, uint64_t n_lanes, uint64_t reqs_per_lane, uint64_t access_seed,
+                            uint64_t n_elems, void* stream);
+/* Zipf page popularity from a 64-bit fixed-point CDF table (device, n_pages entries), rank ->
+ * page through the seeded permutation, uniform element offset inside the page. */
+int bam_gen_zipf_indices(uint64_t* out_dev, uint64_t n_lanes, uint64_t reqs_per_lane, uint64_t access_seed,
+                         const uint64_t* cdf_dev, uint64_t n_pages, uint32_t elems_per_page, uint64_t perm_seed,
+                         void* stream);
+
+/* Wrapping sum of splitmix64(store_seed ^ (first_elem + idx[i])) over an index list, recomputed
+ * from the store's definition without touching cache or queues: the value every cached read of
+ * those indices must add up to (verification of full-size runs; no counterpart in the reference,
+ * whose array benchmark discards the values it reads, benchmarks/array/main.cu:49,61). */
+int bam_direct_checksum(const uint64_t* idx_dev, uint64_t n, uint64_t store_seed, uint64_t first_elem,
+                        uint64_t* sum_out_dev, void* stream);
+
 /* Grid the launchers use: total blocks, controller blocks among them, threads per block. */
 int bam_launch_geometry(bam_ctrl_t c, uint32_t* grid, uint32_t* ctrl_blocks, uint32_t* threads);
 

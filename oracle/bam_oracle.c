@@ -57,6 +57,17 @@ ORC_API void orc_fill_store(uint64_t* dst, uint64_t seed, uint64_t first_elem, u
     for (uint64_t i = 0; i < n; i++) dst[i] = bam_store_elem(seed, first_elem + i);
 }
 
+/* Fill only the listed pages of a store (the rest stays as allocated): lets a bounded sample of
+ * a large workload run without materialising the whole backing store. */
+ORC_API void orc_fill_pages(uint64_t* store, uint64_t seed, uint64_t first_elem, const uint64_t* pages,
+                            uint64_t n_pages, uint32_t elems_per_page)
+{
+    for (uint64_t k = 0; k < n_pages; k++) {
+        uint64_t base = pages[k] * elems_per_page;
+        for (uint32_t w = 0; w < elems_per_page; w++) store[base + w] = bam_store_elem(seed, first_elem + base + w);
+    }
+}
+
 /* Indices of lanes [lane_begin, lane_end) of the array random-read workload. */
 ORC_API void orc_array_indices(uint64_t access_seed, uint64_t n_elems, uint64_t lane_begin,
                                uint64_t lane_end, uint64_t reqs_per_lane, uint64_t* out)

@@ -43,6 +43,7 @@ def lib():
         L.orc_permute.restype = u64
         L.orc_permute.argtypes = [u64, u64, u64]
         L.orc_fill_store.argtypes = [vp, u64, u64, u64]
+        L.orc_fill_pages.argtypes = [vp, u64, u64, vp, u64, u32]
         L.orc_array_indices.argtypes = [u64, u64, u64, u64, u64, vp]
         L.orc_array_checksum.restype = u64
         L.orc_array_checksum.argtypes = [u64, u64, u64, u64, u64, u64]
@@ -93,6 +94,11 @@ def fill_store(seed, first_elem, n, out=None):
         out = np.empty(n, dtype=np.uint64)
     lib().orc_fill_store(_p(out), seed, first_elem, n)
     return out
+
+
+def fill_pages(store, seed, first_elem, pages, elems_per_page=512):
+    pages = np.ascontiguousarray(pages, dtype=np.uint64)
+    lib().orc_fill_pages(_p(store), seed, first_elem, _p(pages), len(pages), elems_per_page)
 
 
 def array_indices(access_seed, n_elems, lane_begin, lane_end, reqs_per_lane):

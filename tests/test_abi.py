@@ -1,0 +1,75 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the header declares,
+the ctypes table covers the header, arguments are validated, and without a GPU the product path
+fails loudly instead of falling back to anything."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    src = open(os.path.join(ROOT, "include", "bam_abi.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    names = re.findall(r"\b(bam_[a-z0-9_]+)\s*\(", src)
+    return sorted(set(names))
+
+
+def test_header_symbols_are_exported(bam):
+    from bam_b200 import _lib
+    lib = C.CDLL(_lib.LIB_PATH)
+    names = declared_functions()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/bam_abi.h but not exported"
+
+
+def test_ctypes_table_covers_header(bam):
+    from bam_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == declared_functions()
+
+
+def test_no_oracle_in_product():
+    """Nothing under bam_b200/ or include/ may reference the oracle."""
+    for base in ("bam_b200", "include"):
+        for d, _, files in os.walk(os.path.join(ROOT, base)):
+            for f in files:
+                if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
+                    assert "oracle" not in open(os.path.join(d, f), errors="ignore").read().lower(), f
+
+
+def test_argument_validation(bam):
+    lib = bam.load()
+    h = C.c_void_p()
+    EINVAL = 22
+    assert lib.bam_ctrl_create(None, 0, 1 << 20, 512, 1, 64) == EINVAL
+    assert lib.bam_ctrl_create(C.byref(h), 0, 1 << 20, 513, 1, 64) == EINVAL      # block size
+    assert lib.bam_ctrl_create(C.byref(h), 0, 1 << 20, 512, 0, 64) == EINVAL      # no queues
+    assert lib.bam_ctrl_create(C.byref(h), 0, 1 << 20, 512, 1, 48) == EINVAL      # depth not 2^k
+    assert lib.bam_ctrl_create(C.byref(h), 0, 1 << 20, 512, 1, 2048) == EINVAL    # depth > 1024
+    assert lib.bam_ctrl_create(C.byref(h), 0, 1000, 512, 1, 64) == EINVAL         # store not page multiple
+    assert lib.bam_cache_create(C.byref(h), None, 4096, 16) == EINVAL
+    assert lib.bam_array_create(C.byref(h), None, 16, 8, 0) == EINVAL
+    assert lib.bam_launch_array_read(None, 1, 1, None, 0, None, None) == EINVAL
+    assert lib.bam_launch_block_read(None, 1, None, 0, None, None, None) == EINVAL
+    assert lib.bam_ctrl_status(None, None, 0) == EINVAL
+    assert b"invalid" in lib.bam_strerror(EINVAL)
+
+
+def test_fails_loudly_without_gpu(bam):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(bam.BamError) as e:
+        bam.Controller(1 << 20, 0, queue_depth=64, num_queues=1)
+    assert e.value.code == 1000            # BAM_ECUDA: no fallback path exists
+
+
+def test_shard_pages(bam):
+    for n, w in [(10, 3), (1 << 24, 8), (7, 8), (16, 1)]:
+        spans = [bam.shard_pages(n, w, r) for r in range(w)]
+        assert spans[0][0] == 0 and sum(c for _, c in spans) == n
+        for (a, ca), (b, _) in zip(spans, spans[1:]):
+            assert a + ca == b

@@ -1,0 +1,53 @@
+"""world_size-2 gloo test (CPU) of the multi-GPU sharding logic: the store is sharded by page
+range, every rank scans only its shard, and the wrapping sum of the per-rank checksums equals
+the single-rank checksum of the whole store's access stream.  No data-path collective exists;
+the only exchange is the final reduction."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    from oracle import pyoracle as orc
+    import bam_b200
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    n_pages_total, lanes, reqs, seed = 1 << 10, 128, 8, 9
+    first_page, n_local = bam_b200.shard_pages(n_pages_total, world, rank)
+    cdf = bam_b200.zipf_cdf(n_local)
+    idx = orc.zipf_indices(cdf, n_local, 512, 17 + rank, 23 + rank, 0, lanes, reqs)     # indices inside the shard
+    local = orc.indexed_checksum(seed, first_page * 512, idx)
+    # int64 carries the u64 bit pattern; wrapping addition is the same in both
+    t = torch.tensor([np.uint64(local).astype(np.int64)], dtype=torch.int64)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    glob_idx = idx + np.uint64(first_page * 512)
+    q.put((rank, int(t.item()) & ((1 << 64) - 1), local, glob_idx))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_checksum_reduces_to_global():
+    world, port = 2, 29571
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    sys.path.insert(0, ROOT)
+    from oracle import pyoracle as orc
+    total = sum(r[2] for r in res) & ((1 << 64) - 1)
+    assert all(r[1] == total for r in res)                      # every rank holds the reduced sum
+    all_idx = np.concatenate([r[3] for r in sorted(res, key=lambda r: r[0])])
+    assert orc.indexed_checksum(9, 0, all_idx) == total         # equals the unsharded computation

@@ -1,0 +1,227 @@
+"""CPU tests of the oracle: pins it against published known-answer vectors and against
+independent re-computations (numpy, zlib, scipy), then against the committed golden fixtures.
+
+The reference has no golden vectors for this path, so these pins are what anchors parity."""
+import hashlib
+import json
+import os
+import zlib
+
+import numpy as np
+import pytest
+
+GOLDEN = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "golden.json")))
+M64 = (1 << 64) - 1
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def np_splitmix64(x):
+    """Independent numpy SplitMix64 output function (state already advanced by the caller? no:
+    adds the golden gamma first, like the generator)."""
+    x = (np.asarray(x, dtype=np.uint64) + np.uint64(0x9E3779B97F4A7C15))
+    z = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return z ^ (z >> np.uint64(31))
+
+
+def py_pcg32(initstate, initseq, n):
+    """Pure-Python PCG32 (XSH-RR), written from the published description."""
+    mult = 6364136223846793005
+    inc = ((initseq << 1) | 1) & M64
+    state = 0
+
+    def step():
+        nonlocal state
+        old = state
+        state = (old * mult + inc) & M64
+        xs = (((old >> 18) ^ old) >> 27) & 0xFFFFFFFF
+        rot = old >> 59
+        return ((xs >> rot) | (xs << ((-rot) & 31))) & 0xFFFFFFFF
+
+    step()
+    state = (state + initstate) & M64
+    step()
+    return [step() for _ in range(n)]
+
+
+def test_splitmix64_known_answers(orc):
+    # first outputs of SplitMix64 seeded with 1234567 (the generator's published test vector)
+    want = [6457827717110365317, 3203168211198807973, 9817491932198370423, 4593380528125082431, 16408922859458223821]
+    state = 1234567
+    for w in want:
+        assert orc.splitmix64(state) == w
+        state = (state + 0x9E3779B97F4A7C15) & M64
+
+
+def test_splitmix64_matches_numpy(orc):
+    seed = 0xC0FFEE
+    got = orc.fill_store(seed, 1000, 4096)
+    with np.errstate(over="ignore"):
+        want = np_splitmix64(np.uint64(seed) ^ np.arange(1000, 1000 + 4096, dtype=np.uint64))
+    assert (got == want).all()
+
+
+def test_pcg32_demo_vector(orc):
+    # pcg32-demo: seed (42, 54) -> first six outputs
+    want = [0xA15C02B7, 0x7B47F409, 0xBA1D3330, 0x83D2F293, 0xBFA4784B, 0xCBED606E]
+    assert orc.pcg32_stream(42, 54, 6).tolist() == want
+    assert py_pcg32(42, 54, 6) == want
+
+
+@pytest.mark.parametrize("state,seq", [(0, 0), (29, 511), (0xDEADBEEF, 1 << 40)])
+def test_pcg32_matches_python(orc, state, seq):
+    assert orc.pcg32_stream(state, seq, 32).tolist() == py_pcg32(state, seq, 32)
+
+
+def test_crc32_check_value_and_zlib(orc):
+    assert orc.crc32(b"123456789") == 0xCBF43926
+    rng = np.random.default_rng(1)
+    for n in (0, 1, 15, 16, 4096):
+        b = rng.integers(0, 256, n, dtype=np.uint8).tobytes()
+        assert orc.crc32(b) == zlib.crc32(b)
+
+
+def test_page_crc_matches_zlib(orc):
+    for seed, page, nbytes in [(11, 0, 4096), (11, 77, 4096), (5, 3, 512), (5, 3, 8192)]:
+        words = orc.fill_store(seed, page * (nbytes // 8), nbytes // 8)
+        assert orc.page_crc(seed, page, nbytes) == zlib.crc32(words.tobytes())
+
+
+def test_array_indices_and_checksum(orc):
+    n_elems, seed, aseed, lanes, reqs = 1 << 20, 7, 99, 300, 9
+    idx = orc.array_indices(aseed, n_elems, 0, lanes, reqs)
+    # independent: lane l draws (hi, lo) pairs from PCG32 stream l
+    for l in (0, 1, 299):
+        d = py_pcg32(aseed, l, 2 * reqs)
+        want = [(((d[2 * k] << 32) | d[2 * k + 1]) & (n_elems - 1)) for k in range(reqs)]
+        assert idx[l * reqs:(l + 1) * reqs].tolist() == want
+    store = orc.fill_store(seed, 0, n_elems)
+    want = int(store[idx].sum(dtype=np.uint64))
+    assert orc.array_checksum(seed, n_elems, aseed, 0, lanes, reqs) == want
+    assert orc.indexed_checksum(seed, 0, idx) == want
+    # non power of two: modulo rule
+    idx2 = orc.array_indices(aseed, 1000003, 5, 6, 4)
+    d = py_pcg32(aseed, 5, 8)
+    assert idx2.tolist() == [(((d[2 * k] << 32) | d[2 * k + 1]) % 1000003) for k in range(4)]
+
+
+def test_lane_split_is_additive(orc):
+    a = orc.array_checksum(3, 1 << 18, 4, 0, 100, 5)
+    b = orc.array_checksum(3, 1 << 18, 4, 100, 257, 5)
+    assert (a + b) & M64 == orc.array_checksum(3, 1 << 18, 4, 0, 257, 5)
+
+
+@pytest.mark.parametrize("n", [1, 2, 7, 64, 1000, 4096, 100003])
+def test_permutation_is_bijection(orc, n):
+    out = np.array([orc.lib().orc_permute(x, n, 17) for x in range(n)], dtype=np.uint64)
+    assert sorted(out.tolist()) == list(range(n))
+
+
+def test_zipf_cdf_and_ranks(orc):
+    n = 1 << 10
+    cdf = orc.zipf_cdf(n)
+    assert (np.diff(cdf.astype(np.float64)) >= 0).all() and cdf[-1] == np.uint64(M64)
+    idx = orc.zipf_indices(cdf, n, 512, 17, 23, 0, 256, 64)
+    pages = idx // 512
+    assert pages.max() < n and (idx % 512).max() < 512
+    # the most popular rank maps to permute(0); it must be the most frequent page
+    top = orc.lib().orc_permute(0, n, 17)
+    counts = np.bincount(pages.astype(np.int64), minlength=n)
+    assert counts.argmax() == top
+    # rank-1 probability ~ 1/H(n, 0.99)
+    p1 = 1.0 / (np.arange(1, n + 1, dtype=np.float64) ** -0.99).sum()
+    assert abs(counts[top] / len(idx) - p1) < 0.02
+
+
+def _scipy_graph(off, cols):
+    import scipy.sparse as sp
+    n = len(off) - 1
+    return sp.csr_matrix((np.ones(len(cols), dtype=np.int8), cols.astype(np.int64), off.astype(np.int64)), shape=(n, n))
+
+
+@pytest.mark.parametrize("scale,seed", [(8, 1), (10, 2)])
+def test_rmat_csr_properties_and_scipy(orc, scale, seed):
+    from scipy.sparse import csgraph
+    off, cols = orc.rmat_csr(seed, scale, 16)
+    n = 1 << scale
+    assert off[0] == 0 and off[-1] == len(cols) and (np.diff(off.astype(np.int64)) >= 0).all()
+    src_of = np.repeat(np.arange(n, dtype=np.uint64), np.diff(off.astype(np.int64)))
+    assert (src_of != cols).all()                                   # no self loops
+    key = (src_of << np.uint64(32)) | cols
+    assert (np.diff(key.astype(np.int64)) > 0).all()                # sorted, no duplicates
+    rev = np.sort((cols << np.uint64(32)) | src_of)
+    assert (rev == key).all()                                       # symmetric
+    # independent regeneration of the edge list from the published R-MAT recursion
+    ta, tab, tabc = orc.rmat_thresholds()
+    edges = set()
+    for e in range(0, 16 << scale, 997):                            # a sample of the generated edges
+        d = py_pcg32(seed, e, scale)
+        u = v = 0
+        for r in d:
+            u = (u << 1) | (1 if r >= tab else 0)
+            v = (v << 1) | (1 if (ta <= r < tab) or r >= tabc else 0)
+        if u != v:
+            edges.add((u, v))
+    for (u, v) in edges:
+        assert v in cols[off[u]:off[u + 1]] and u in cols[off[v]:off[v + 1]]
+    g = _scipy_graph(off, cols)
+    src = orc.max_degree_vertex(off)
+    deg = np.diff(off.astype(np.int64))
+    assert src == int(np.flatnonzero(deg == deg.max())[0])
+    lvl, scanned = orc.bfs(off, cols, src)
+    dist = csgraph.shortest_path(g, unweighted=True, indices=src)
+    want = np.where(np.isinf(dist), 0xFFFFFFFF, dist).astype(np.uint32)
+    assert (lvl == want).all()
+    assert scanned == int(deg[lvl != 0xFFFFFFFF].sum())
+    lab, comps = orc.cc(off, cols)
+    ncomp, sl = csgraph.connected_components(g, directed=False)
+    assert comps == ncomp
+    mins = np.full(ncomp, n, dtype=np.int64)
+    np.minimum.at(mins, sl, np.arange(n))
+    assert (lab == mins[sl].astype(np.uint64)).all()                # canonical min-vertex label
+
+
+def test_protocol_restatement_matches_result_oracle(orc):
+    """The host-thread restatement of the reference's queue + cache protocol returns the same
+    checksum as the pure result oracle, with evictions, queue wrap-around and a shared queue."""
+    n_elems, seed, aseed = 1 << 18, 7, 99
+    store = orc.fill_store(seed, 0, n_elems)
+    for (slots, nq, depth, workers, lanes, reqs) in [(64, 1, 4, 3, 256, 8), (128, 2, 8, 4, 512, 8), (1024, 3, 64, 6, 2048, 4)]:
+        r = orc.ref_array_read(store, 4096, slots, nq, depth, 512, workers, 2, access_seed=aseed,
+                               lane_begin=0, lane_end=lanes, reqs_per_lane=reqs)
+        assert r.checksum == orc.array_checksum(seed, n_elems, aseed, 0, lanes, reqs)
+        assert r.accesses == lanes * reqs and r.hits + r.misses == r.accesses and r.read_ios == r.misses
+        assert r.read_ios >= min(len(np.unique(orc.array_indices(aseed, n_elems, 0, lanes, reqs) // 512)), 1)
+
+
+def test_protocol_restatement_block_read(orc):
+    seed = 5
+    store = orc.fill_store(seed, 0, 1 << 16)                       # 128 pages
+    r, crc = orc.ref_block_read(store, 4096, 2, 4, 512, 3, 1, 78, 600)
+    pages, want = orc.block_requests(seed, 78, 128, 4096, 0, 600)
+    assert (crc == want).all() and r.read_ios == 600
+
+
+def test_golden_fixtures(orc):
+    for c in GOLDEN["array_checksum"]:
+        assert orc.array_checksum(c["store_seed"], c["n_elems"], c["access_seed"], 0, c["lanes"], c["reqs"]) == c["checksum"]
+    for c in GOLDEN["page_crc"]:
+        assert orc.page_crc(c["store_seed"], c["page"], c["page_bytes"]) == c["crc"]
+    b = GOLDEN["block_requests"]
+    pages, crcs = orc.block_requests(b["store_seed"], b["req_seed"], b["n_pages"], b["page_bytes"], 0, 256)
+    assert sha(pages) == b["pages_sha256"] and sha(crcs) == b["crc_sha256"]
+    z = GOLDEN["zipf"]
+    cdf = orc.zipf_cdf(z["n_pages"], z["s"])
+    assert sha(cdf) == z["cdf_sha256"]
+    idx = orc.zipf_indices(cdf, z["n_pages"], 512, z["perm_seed"], z["access_seed"], 0, z["lanes"], z["reqs"])
+    assert sha(idx) == z["idx_sha256"] and orc.indexed_checksum(9, 0, idx) == z["checksum"]
+    for gph in GOLDEN["graphs"]:
+        off, cols = orc.rmat_csr(gph["seed"], gph["scale"], gph["edge_factor"])
+        assert sha(off) == gph["offsets_sha256"] and sha(cols) == gph["cols_sha256"]
+        lvl, scanned = orc.bfs(off, cols, gph["source"])
+        lab, comps = orc.cc(off, cols)
+        assert sha(lvl) == gph["levels_sha256"] and sha(lab) == gph["labels_sha256"]
+        assert comps == gph["components"] and scanned == gph["edges_scanned"]
