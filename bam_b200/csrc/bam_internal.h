@@ -12,6 +12,11 @@
 #define BAM_DEFAULT_CTRL_BLOCKS 16    /* controller blocks unless configured otherwise       */
 #define BAM_DB_STRIDE_WORDS 8         /* doorbell stride: 32 bytes, one sector per register   */
 
+/* fixed scratch of bam_cache_audit_noalloc (bam_noalloc.cu) */
+#define BAM_AUDIT_NOALLOC_WORDS 1024
+#define BAM_AUDIT_NOALLOC_SLOTS_PER_BLOCK 8192
+#define BAM_AUDIT_NOALLOC_MAX_SLOTS ((uint64_t)(BAM_AUDIT_NOALLOC_WORDS - 1) * BAM_AUDIT_NOALLOC_SLOTS_PER_BLOCK)
+
 struct bam_ctrl {
     int device = 0;
     int num_sms = 0;

@@ -323,6 +323,7 @@ extern "C" const char* bam_strerror(int code)
     switch (code) {
     case BAM_OK: return "success";
     case BAM_EIO: return "I/O error (NVMe completion status or earlier device-side failure)";
+    case BAM_E2BIG: return "size exceeds the fixed limit of this entry point";
     case BAM_ENOMEM: return "out of memory";
     case BAM_EBUSY: return "resource busy";
     case BAM_EINVAL: return "invalid argument";

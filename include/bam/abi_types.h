@@ -26,6 +26,7 @@
  * include/nvm_error.h:37-59) -------------------------------------------------------- */
 #define BAM_OK 0
 #define BAM_EIO 5
+#define BAM_E2BIG 7          /* a size exceeds the fixed limit of the entry point */
 #define BAM_ENOMEM 12
 #define BAM_EBUSY 16
 #define BAM_EINVAL 22

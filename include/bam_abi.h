@@ -92,6 +92,19 @@ int bam_cache_invalidate(bam_cache_t pc);
  * table, every table entry points at a slot with a matching tag.  *violations = 0 when clean. */
 int bam_cache_audit(bam_cache_t pc, uint64_t* violations);
 int bam_cache_descriptor(bam_cache_t pc, void* out, size_t out_bytes);  /* page_cache_d_t by value */
+/* The same audit for callers that must not allocate or stall the device (no counterpart in the
+ * reference).  bam_cache_audit takes its counter from cudaMalloc/cudaFree and synchronises the
+ * device; a caller that audits while other streams run, whose device memory belongs to a single
+ * allocator, or that is on a path where allocation calls are not allowed, uses this instead:
+ * it enqueues a memset and one kernel on `stream` and returns at once.  The count is written to
+ * *violations_out_dev (device memory, overwritten) when the kernel has run.
+ * Scratch is a fixed 8 KiB array inside the library's device image (held on every GPU that loads
+ * the library until exit), so caches of more than 8,380,416 slots are refused with BAM_E2BIG.
+ * All calls share that array: calls that can overlap on the GPU (different streams, no ordering
+ * between them) race and give wrong counts; calls on one stream are safe.  The first call on each
+ * device also looks up the array's device address; make that first call outside any stream
+ * capture. */
+int bam_cache_audit_noalloc(bam_cache_t pc, uint64_t* violations_out_dev, void* stream);
 
 /* ---- arrays --------------------------------------------------------------------------------
  * Replaces range_t<T>(index_start, count, page_start, page_count, page_start_offset, page_size,
