@@ -6,7 +6,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libbam_b200.so")
+# BAM_B200_LIB selects another build of the same library (e.g. one compiled with -DBAM_PROFILE)
+LIB_PATH = os.environ.get("BAM_B200_LIB") or os.path.join(HERE, "libbam_b200.so")
 
 u32, u64, vp, ci = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int
 
@@ -30,10 +31,12 @@ SIGNATURES = {
     "bam_ctrl_fill_store": (ci, [vp, u64, u64, vp]),
     "bam_ctrl_write_store": (ci, [vp, u64, vp, u64]),
     "bam_ctrl_configure": (ci, [vp, u32, u32, u64]),
+    "bam_ctrl_set_scope": (ci, [vp, ci]),
     "bam_ctrl_set_max_grid": (ci, [vp, u32]),
     "bam_ctrl_set_launch_timeout": (ci, [vp, u64]),
     "bam_ctrl_inject_fault": (ci, [vp, u32, u64, u32]),
     "bam_ctrl_status": (ci, [vp, C.POINTER(StatusOut), ci]),
+    "bam_ctrl_profile": (ci, [vp, C.POINTER(u64), ci]),
     "bam_ctrl_served": (ci, [vp, C.POINTER(u64), ci]),
     "bam_ctrl_reset_queues": (ci, [vp]),
     "bam_ctrl_device_controller": (vp, [vp]),

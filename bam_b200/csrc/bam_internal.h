@@ -9,7 +9,7 @@
 
 #define BAM_THREADS 256               /* threads per block of every fused launch            */
 #define BAM_MIN_BLOCKS 3              /* resident blocks per SM the kernels are compiled for */
-#define BAM_DEFAULT_CTRL_BLOCKS 16    /* controller blocks unless configured otherwise       */
+#define BAM_DEFAULT_CTRL_BLOCKS 48    /* controller blocks unless configured otherwise       */
 #define BAM_DB_STRIDE_WORDS 8         /* doorbell stride: 32 bytes, one sector per register   */
 
 /* fixed scratch of bam_cache_audit_noalloc (bam_noalloc.cu) */
@@ -43,6 +43,7 @@ struct bam_ctrl {
     bam_fault_t* d_fault = nullptr;
     uint64_t* d_served = nullptr;
     bam_emu_d_t emu = {};
+    uint32_t sys_scope = 0;           /* scope of doorbell/completion synchronisation          */
     uint32_t max_grid = 0;            /* 0 = as many blocks as fit                            */
     uint32_t last_grid = 0;
 };

@@ -131,12 +131,17 @@ __global__ void k_audit(page_cache_d_t pc, uint64_t n_buckets, unsigned long lon
 /* fused launch                                                                            */
 /* ====================================================================================== */
 
+/* Dynamic shared memory of every block of a fused launch: the controller blocks use it as their
+ * bulk-copy stages; it has to be the same size for all blocks of one grid. */
+extern __shared__ __align__(128) uint8_t bam_dyn_smem[];
+#define BAM_FUSED_SMEM BAM_EMU_SMEM_BYTES
+
 template <class Work>
 __global__ void __launch_bounds__(BAM_THREADS, BAM_MIN_BLOCKS)
 bam_fused(const __grid_constant__ bam_emu_d_t emu, const __grid_constant__ Work work)
 {
     if (blockIdx.x < emu.n_ctrl_blocks) {
-        emu_controller_main(emu);
+        emu_controller_main(emu, bam_dyn_smem);
         return;
     }
     work(blockIdx.x - emu.n_ctrl_blocks, gridDim.x - emu.n_ctrl_blocks);
@@ -153,7 +158,8 @@ static int launch_fused(bam_ctrl* c, const Work& w, cudaStream_t s)
     static thread_local int blocks_per_sm = 0;
     if (blocks_per_sm == 0) {
         int nb = 0;
-        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, bam_fused<Work>, BAM_THREADS, 0));
+        CK(cudaFuncSetAttribute(bam_fused<Work>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BAM_FUSED_SMEM));
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, bam_fused<Work>, BAM_THREADS, BAM_FUSED_SMEM));
         if (nb < 1) return BAM_EINVAL;
         blocks_per_sm = nb;
     }
@@ -164,7 +170,7 @@ static int launch_fused(bam_ctrl* c, const Work& w, cudaStream_t s)
     CK(cudaMemcpyAsync(c->emu.consumers_remaining, &n_work, sizeof n_work, cudaMemcpyHostToDevice, s));
     bam_emu_d_t emu = c->emu;
     void* args[] = { (void*)&emu, (void*)&w };
-    CK(cudaLaunchCooperativeKernel((const void*)bam_fused<Work>, dim3(grid), dim3(BAM_THREADS), args, 0, s));
+    CK(cudaLaunchCooperativeKernel((const void*)bam_fused<Work>, dim3(grid), dim3(BAM_THREADS), args, BAM_FUSED_SMEM, s));
     c->last_grid = grid;
     return BAM_OK;
 }
@@ -173,7 +179,8 @@ template <class Work>
 static int fused_geometry(bam_ctrl* c, uint32_t* grid)
 {
     int nb = 0;
-    CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, bam_fused<Work>, BAM_THREADS, 0));
+    CK(cudaFuncSetAttribute(bam_fused<Work>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BAM_FUSED_SMEM));
+    CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, bam_fused<Work>, BAM_THREADS, BAM_FUSED_SMEM));
     *grid = (uint32_t)nb * (uint32_t)c->num_sms;
     if (c->max_grid && *grid > c->max_grid) *grid = c->max_grid;
     return BAM_OK;
@@ -216,11 +223,15 @@ struct BlockReadWork {
         const uint64_t bus = slot_bus_addr(pc, slot);
         const uint64_t prp2 = pc.page_size > 4096 ? bus + 4096 : 0;
         uint64_t sum = 0;
-        for (uint64_t r = gid; r < n_reqs; r += nthr) {
-            const uint64_t pg = pages ? pages[r] : bam_block_request_page(req_seed, r, n_store_pages);
-            const int rc = access_data_raw(qp, pg * pc.n_blocks_per_page, pc.n_blocks_per_page, bus, prp2, NVM_IO_READ);
-            if (rc != BAM_OK) break;
-            if (crc_out || sum_out) {
+        const uint64_t warp_first = gid & ~31ull;             /* requests are issued by whole warps */
+        for (uint64_t r0 = warp_first; r0 < n_reqs; r0 += nthr) {
+            const uint64_t r = r0 + (threadIdx.x & 31u);
+            const bool active = r < n_reqs;
+            uint64_t pg = 0;
+            if (active) pg = pages ? pages[r] : bam_block_request_page(req_seed, r, n_store_pages);
+            const int rc = warp_io(0xffffffffu, active, qp, pg * pc.n_blocks_per_page, pc.n_blocks_per_page, bus, prp2, NVM_IO_READ);
+            if (__any_sync(0xffffffffu, rc != BAM_OK)) break;
+            if (active && (crc_out || sum_out)) {
                 uint32_t crc = ~0u;
                 const uint8_t* p = reinterpret_cast<const uint8_t*>(bus);
                 for (uint32_t o = 0; o < pc.page_size; o += 16) {
@@ -238,6 +249,7 @@ struct BlockReadWork {
                 }
                 if (crc_out) crc_out[r] = ~crc;
             }
+            __syncwarp();
         }
         __syncwarp();
         warp_sum_to(sum, sum_out);
@@ -289,9 +301,16 @@ struct PageScanWork {
         uint64_t sum = 0;
         for (uint64_t p = warp; p < n_pages; p += nwarps) {
             const uint64_t page = pages ? pages[p] : first_page + p;
-            uint32_t slot = BAM_SLOT_ERR;
-            if (lane == 0) slot = r.acquire_page(page, 1, false, (uint32_t)warp);
-            slot = __shfl_sync(0xffffffffu, slot, 0);
+            uint32_t slot;
+            {
+                spin_t sp;
+                for (;;) {       /* nothing is held between attempts */
+                    slot = r.acquire_page_warp(0xffffffffu, lane == 0, page, 1, false, (uint32_t)warp);
+                    slot = __shfl_sync(0xffffffffu, slot, 0);
+                    if (slot != BAM_SLOT_RETRY) break;
+                    if (__any_sync(0xffffffffu, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) { slot = BAM_SLOT_ERR; break; }
+                }
+            }
             if (slot == BAM_SLOT_ERR) break;
             const uint8_t* base = reinterpret_cast<const uint8_t*>(r.get_cache_page_addr(slot));
             for (uint32_t o = lane * 16; o < r.cache.page_size; o += 32 * 16 * 4) {
@@ -358,7 +377,7 @@ static int upload_queue_image(bam_ctrl* c)
             nq->qs = qs; nq->qs_minus_1 = qs - 1; nq->qs_log2 = log2_u32(qs);
             nq->no = (uint16_t)(q + 1);
             nq->es = is_cq ? sizeof(nvm_cpl_t) : sizeof(nvm_cmd_t);
-            nq->phase = 1; nq->local = 1;
+            nq->phase = 1; nq->local = c->sys_scope ? 0 : 1;
             nq->status = c->d_status;
             nq->db = c->d_doorbells + (size_t)(2 * (q + 1) + is_cq) * BAM_DB_STRIDE_WORDS;
             nq->vaddr = is_cq ? (void*)(c->d_cq_mem + (size_t)q * qs) : (void*)(c->d_sq_mem + (size_t)q * qs);
@@ -447,7 +466,7 @@ extern "C" int bam_ctrl_create(bam_ctrl_t* out, int device, uint64_t store_bytes
     c->emu.n_ctrl_blocks = BAM_DEFAULT_CTRL_BLOCKS;
     c->emu.store = c->store_dev; c->emu.store_bytes = store_bytes;
     c->emu.lba_log2 = log2_u32(lba_bytes); c->emu.mps_log2 = 12;
-    c->emu.batch = 2; c->emu.copy_mode = 0;
+    c->emu.batch = BAM_EMU_LANES; c->emu.sys_scope = c->sys_scope;
     c->emu.consumers_remaining = c->d_remaining; c->emu.status = c->d_status;
     c->emu.fault = c->d_fault; c->emu.served = c->d_served;
     int rc = upload_queue_image(c);
@@ -510,6 +529,16 @@ extern "C" int bam_ctrl_configure(bam_ctrl_t c, uint32_t n_ctrl_blocks, uint32_t
     return BAM_OK;
 }
 
+extern "C" int bam_ctrl_set_scope(bam_ctrl_t c, int system_scope)
+{
+    if (!c) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    CK(cudaDeviceSynchronize());
+    c->sys_scope = system_scope ? 1u : 0u;
+    c->emu.sys_scope = c->sys_scope;
+    return upload_queue_image(c);
+}
+
 extern "C" int bam_ctrl_set_max_grid(bam_ctrl_t c, uint32_t max_grid)
 {
     if (!c) return BAM_EINVAL;
@@ -539,6 +568,16 @@ extern "C" int bam_ctrl_status(bam_ctrl_t c, bam_status_out_t* out, int clear)
         st.code = 0; st.where = 0; st.detail = 0;
         CK(cudaMemcpy(c->d_status, &st, sizeof st, cudaMemcpyHostToDevice));
     }
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_profile(bam_ctrl_t c, uint64_t* out32, int reset)
+{
+    if (!c || !out32) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    CK(cudaDeviceSynchronize());
+    CK(cudaMemcpy(out32, c->d_status->prof, sizeof(uint64_t) * 32, cudaMemcpyDeviceToHost));
+    if (reset) CK(cudaMemset(c->d_status->prof, 0, sizeof(uint64_t) * 32));
     return BAM_OK;
 }
 

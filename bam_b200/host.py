@@ -71,6 +71,9 @@ class Controller:
     def set_launch_timeout(self, ns):
         check(self.lib.bam_ctrl_set_launch_timeout(self.h, ns), "bam_ctrl_set_launch_timeout")
 
+    def set_scope(self, system_scope):
+        check(self.lib.bam_ctrl_set_scope(self.h, int(system_scope)), "bam_ctrl_set_scope")
+
     def set_max_grid(self, max_grid):
         check(self.lib.bam_ctrl_set_max_grid(self.h, max_grid), "bam_ctrl_set_max_grid")
 
@@ -92,6 +95,12 @@ class Controller:
         v = C.c_uint64()
         check(self.lib.bam_ctrl_served(self.h, C.byref(v), int(reset)), "bam_ctrl_served")
         return v.value
+
+    def profile(self, reset=True):
+        """The 32 profiling counters (zeros unless the library was built with -DBAM_PROFILE)."""
+        buf = (C.c_uint64 * 32)()
+        check(self.lib.bam_ctrl_profile(self.h, buf, int(reset)), "bam_ctrl_profile")
+        return list(buf)
 
     def reset_queues(self):
         check(self.lib.bam_ctrl_reset_queues(self.h), "bam_ctrl_reset_queues")

@@ -287,13 +287,13 @@ def main():
     # ---- host-link peak (pinned H2D copy) and warm hit-path pass (HBM roofline) ----------------
     link_gbs, hit = None, None
     if rank == 0:
-        pin = torch.empty(1 << 28, dtype=torch.uint8).pin_memory()
-        dbuf = torch.empty(1 << 28, dtype=torch.uint8, device=dev)
+        pin = torch.empty(1 << 30, dtype=torch.uint8).pin_memory()
+        dbuf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
         best = 0.0
         for _ in range(5):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream); dbuf.copy_(pin, non_blocking=True); b.record(stream); stream.synchronize()
-            best = max(best, (1 << 28) / (a.elapsed_time(b) * 1e-3) / 1e9)
+            best = max(best, (1 << 30) / (a.elapsed_time(b) * 1e-3) / 1e9)
         link_gbs = best
         del pin, dbuf
         # warm pass: scan pages that are resident (scan the same list twice, time the second)

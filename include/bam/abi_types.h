@@ -59,6 +59,7 @@ typedef struct {
     uint64_t detail;
     uint64_t spin_timeout_ns;   /* limit for any single device-side wait */
     uint64_t launch_timeout_ns; /* limit for one fused launch, enforced by the controller blocks */
+    uint64_t prof[32];          /* cycle/event counters, only updated by builds with -DBAM_PROFILE   */
 } bam_status_t;
 
 /* ---- NVMe queue entries -------------------------------------------------------------- */
@@ -91,7 +92,8 @@ typedef struct {
     uint32_t qs, qs_minus_1, qs_log2;
     uint16_t no;                          /* queue number (unique per SQ/CQ pair)              */
     uint16_t es;                          /* entry size in bytes                               */
-    int8_t phase, local;
+    int8_t phase;
+    int8_t local;                         /* 1: the controller runs on this GPU (device scope suffices) */
     uint32_t last;
     volatile uint32_t* db;                /* doorbell register of this queue                   */
     volatile void* vaddr;                 /* queue memory                                      */
@@ -152,7 +154,7 @@ typedef struct {
     uint32_t lba_log2;          /* logical block size                                            */
     uint32_t mps_log2;          /* controller memory page size (PRP granule)                     */
     uint32_t batch;             /* commands one warp fetches per lock hold                        */
-    uint32_t copy_mode;         /* 0 = register-staged 128-bit copies, 1 = bulk-async through smem */
+    uint32_t sys_scope;         /* 1: doorbells/completions use system scope, 0: device scope      */
     uint32_t* consumers_remaining;
     bam_status_t* status;
     bam_fault_t* fault;
@@ -171,6 +173,8 @@ typedef struct {
 #define BAM_TAG_NONE 0xffffffffffffffffull
 #define BAM_SLOT_NONE 0xffffffffu
 #define BAM_SLOT_ERR 0xfffffffeu
+#define BAM_SLOT_RETRY 0xfffffffdu   /* no slot could be claimed right now: release what you hold and ask again */
+#define BAM_SLOT_MAX 0xfffffffcu     /* largest value that is a real slot index */
 
 typedef struct BAM_ALIGNAS(16) {
     uint64_t tag;        /* (page index in range << range bits) | range id; BAM_TAG_NONE if unassigned */

@@ -43,6 +43,11 @@ struct range_d_t {
     {
         return cache_acquire(cache, get_global_address(page), cnt, get_backing_page(page), queue, write);
     }
+    /* warp-cooperative form: every lane of `mask` calls it, lanes with want == true pin `page` */
+    BAM_DEV uint32_t acquire_page_warp(uint32_t mask, bool want, size_t page, uint32_t cnt, bool write, uint32_t queue) const
+    {
+        return warp_cache_acquire(mask, want, cache, get_global_address(page), cnt, get_backing_page(page), queue, write);
+    }
     BAM_DEV void release_page(uint32_t slot, uint32_t cnt = 1) const { cache_release(cache, slot, cnt); }
 };
 
@@ -70,8 +75,14 @@ struct array_d_t {
         leader = __ffs(eq_mask) - 1;
         cnt = __popc(eq_mask);
         const uint32_t dirty = __ballot_sync(eq_mask, write) != 0u;
-        slot = BAM_SLOT_ERR;
-        if (lane_id() == leader) slot = r.acquire_page(page, cnt, dirty, default_queue());
+        spin_t sp;
+        bool pending = true;
+        for (;;) {      /* the caller keeps the page, so a lane that cannot get a slot simply asks again */
+            const uint32_t s = r.acquire_page_warp(mask, pending && lane_id() == leader, page, cnt, dirty, default_queue());
+            if (pending && s != BAM_SLOT_RETRY) { slot = s; pending = false; }
+            if (!__any_sync(mask, pending)) break;
+            if (__any_sync(mask, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) { if (pending) slot = BAM_SLOT_ERR; break; }
+        }
         slot = __shfl_sync(eq_mask, slot, leader);
     }
 
@@ -80,15 +91,31 @@ struct array_d_t {
         const uint32_t mask = __activemask();
         const int64_t ri = find_range(i);
         T v = T();
-        /* lanes that hit different ranges (or none) form separate groups before anyone leaves */
-        const uint32_t rmask = __match_any_sync(mask, (uint64_t)ri);
-        if (ri < 0) { status_fail(d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i); return v; }
-        const range_d_t<T>& r = d_ranges[ri];
-        uint32_t eq, leader, cnt, slot;
-        coalesce_page(r, rmask, r.get_page(i), false, eq, leader, cnt, slot);
-        if (slot != BAM_SLOT_ERR) v = *reinterpret_cast<const T*>(r.get_cache_page_addr(slot) + r.get_subindex(i));
-        __syncwarp(eq);
-        if (lane_id() == leader && slot != BAM_SLOT_ERR) r.release_page(slot, cnt);
+        /* every active lane takes part in the cooperative acquire; a lane outside every range
+         * asks for nothing (and flags the error), lanes of different ranges never share a group
+         * because the range id is part of the page's global address */
+        const bool valid = ri >= 0;
+        const range_d_t<T>& r = d_ranges[valid ? ri : 0];
+        const uint64_t page = valid ? r.get_page(i) : ~0ull;
+        const uint64_t key = valid ? r.get_global_address(page) : ~0ull;
+        const uint32_t eq = __match_any_sync(mask, key);
+        const uint32_t leader = __ffs(eq) - 1;
+        const uint32_t cnt = __popc(eq);
+        bool pending = valid;
+        spin_t sp;
+        for (;;) {
+            uint32_t slot = r.acquire_page_warp(mask, pending && lane_id() == leader, valid ? page : 0, cnt, false, default_queue());
+            slot = __shfl_sync(eq, slot, leader);
+            if (pending && slot != BAM_SLOT_RETRY) {
+                if (slot != BAM_SLOT_ERR) v = *reinterpret_cast<const T*>(r.get_cache_page_addr(slot) + r.get_subindex(i));
+                __syncwarp(eq);
+                if (lane_id() == leader && slot != BAM_SLOT_ERR) r.release_page(slot, cnt);
+                pending = false;
+            }
+            if (!__any_sync(mask, pending)) break;
+            if (__any_sync(mask, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) break;
+        }
+        if (!valid) status_fail(d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i);
         return v;
     }
 
@@ -105,13 +132,21 @@ BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
     const uint32_t eq = __match_any_sync(mask, page);
     const uint32_t leader = __ffs(eq) - 1;
     const uint32_t cnt = __popc(eq);
-    uint32_t slot = BAM_SLOT_ERR;
-    if (lane_id() == leader) slot = r.acquire_page(page, cnt, false, queue);
-    slot = __shfl_sync(eq, slot, leader);
     T v = T();
-    if (slot != BAM_SLOT_ERR) v = *reinterpret_cast<const T*>(r.get_cache_page_addr(slot) + r.get_subindex(i));
-    __syncwarp(eq);
-    if (lane_id() == leader && slot != BAM_SLOT_ERR) r.release_page(slot, cnt);
+    bool pending = true;
+    spin_t sp;
+    for (;;) {
+        uint32_t slot = r.acquire_page_warp(mask, pending && lane_id() == leader, page, cnt, false, queue);
+        slot = __shfl_sync(eq, slot, leader);
+        if (pending && slot != BAM_SLOT_RETRY) {
+            if (slot != BAM_SLOT_ERR) v = *reinterpret_cast<const T*>(r.get_cache_page_addr(slot) + r.get_subindex(i));
+            __syncwarp(eq);
+            if (lane_id() == leader && slot != BAM_SLOT_ERR) r.release_page(slot, cnt);
+            pending = false;
+        }
+        if (!__any_sync(mask, pending)) break;
+        if (__any_sync(mask, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) break;
+    }
     return v;
 }
 
@@ -146,12 +181,25 @@ struct bam_ptr {
         fini();
         const uint32_t mask = __activemask();
         const int64_t ri = array->find_range(i);
-        const uint32_t rmask = __match_any_sync(mask, (uint64_t)ri);
-        if (ri < 0) { status_fail(array->d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i); addr = nullptr; return nullptr; }
-        range = &array->d_ranges[ri];
-        const uint64_t page = range->get_page(i);
-        uint32_t eq, leader, cnt;
-        array_d_t<T>::coalesce_page(*range, rmask, page, false, eq, leader, cnt, slot);
+        const bool valid = ri >= 0;
+        range = &array->d_ranges[valid ? ri : 0];
+        const uint64_t page = valid ? range->get_page(i) : ~0ull;
+        const uint64_t key = valid ? range->get_global_address(page) : ~0ull;
+        const uint32_t eq = __match_any_sync(mask, key);
+        const uint32_t leader = __ffs(eq) - 1;
+        {
+            spin_t sp;
+            bool pending = valid;
+            slot = BAM_SLOT_ERR;
+            for (;;) {   /* the old page was released by fini(), so retrying holds nothing */
+                const uint32_t s = range->acquire_page_warp(mask, pending && lane_id() == leader, valid ? page : 0, __popc(eq), false, default_queue());
+                if (pending && s != BAM_SLOT_RETRY) { slot = s; pending = false; }
+                if (!__any_sync(mask, pending)) break;
+                if (__any_sync(mask, sp.expired(range->cache.status, BAM_AT_FIND_SLOT, page))) break;
+            }
+        }
+        slot = __shfl_sync(eq, slot, leader);
+        if (!valid) { status_fail(array->d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i); slot = BAM_SLOT_ERR; }
         if (slot == BAM_SLOT_ERR) { addr = nullptr; return nullptr; }
         /* first element index that lives in this page, and one past the last */
         const uint64_t page_byte0 = page << range->cache.page_size_log;

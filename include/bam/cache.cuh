@@ -126,12 +126,14 @@ BAM_DEV uint64_t slot_bus_addr(const page_cache_d_t& pc, uint32_t slot)
 }
 
 /* Clock sweep: returns a slot claimed for the caller (state BUSY, no tag, no table entry), or
- * BAM_SLOT_ERR.  Counterpart of page_cache_d_t::find_slot (page_cache.h:1786-1927). */
-BAM_DEV uint32_t find_slot(const page_cache_d_t& pc)
+ * BAM_SLOT_ERR; with max_tries it gives up after that many probes and returns BAM_SLOT_NONE.
+ * Counterpart of page_cache_d_t::find_slot (page_cache.h:1786-1927). */
+BAM_DEV uint32_t find_slot(const page_cache_d_t& pc, uint32_t max_tries = 0xffffffffu)
 {
     spin_t sp;
 #pragma unroll 1
     for (uint32_t tries = 1;; tries++) {
+        if (tries > max_tries) return BAM_SLOT_NONE;          /* caller asked for a bounded attempt */
         const uint64_t t = atom_add_relaxed(pc.clock_hand, 1ull);
         const uint32_t s = (uint32_t)(t % pc.n_slots);
         bam_slot_t* sl = &pc.slots[s];
@@ -219,6 +221,109 @@ BAM_DEV uint32_t cache_acquire(const page_cache_d_t& pc, uint64_t tag, uint32_t 
         atom_xor_release(&sl->state, BAM_VALID | BAM_BUSY);                 /* BUSY -> VALID */
         return v;
     }
+}
+
+/* Warp-cooperative form of cache_acquire: all lanes of `mask` call it together; lanes with
+ * want == true pin their page.  Look-ups and slot claims run per lane without sleeping; the page
+ * reads of all missing lanes are then submitted and awaited as one group (warp_io), and lanes
+ * that found their page being filled by another warp poll for it in a converged loop, so the
+ * warp backs off once for everybody instead of once per lane.  Returns the slot, BAM_SLOT_ERR on
+ * failure or when want == false, or BAM_SLOT_RETRY when no slot could be claimed in a bounded
+ * sweep: the caller must first release the pages its warp holds (they may be exactly what keeps
+ * the cache full) and then call again. */
+BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d_t& pc, uint64_t tag, uint32_t count,
+                                    uint64_t backing_page, uint32_t queue, bool write)
+{
+    enum { S_DONE = 0, S_LOOKUP = 1, S_WAIT = 2, S_IO = 3 };
+    const uint32_t kClaimTries = 64;                     /* clock-sweep probes before giving the turn back */
+    bam_status_t* st = pc.status;
+    const uint64_t h = pt_hash(tag);
+    const uint32_t home = (uint32_t)h & pc.bucket_mask;
+    const uint32_t fp = (uint32_t)(h >> 56);
+    Controller* c = pc.d_ctrl;
+    QueuePair* qp = c->d_qps + (queue % c->n_qps);
+    uint32_t state = want ? S_LOOKUP : S_DONE;
+    uint32_t slot = BAM_SLOT_ERR;
+    spin_t sp;
+#pragma unroll 1
+    for (;;) {
+        if (state == S_LOOKUP) {
+            const uint32_t s = pt_lookup(pc, tag, home, fp);
+            if (s != BAM_SLOT_NONE) {
+                bam_slot_t* sl = &pc.slots[s];
+                const uint32_t old = atom_add_acquire(&sl->state, count);
+                if (ld_relaxed_gpu(&sl->tag) != tag || (old & (BAM_VALID | BAM_BUSY)) == 0u) {
+                    red_add_relaxed(&sl->state, 0u - count);                   /* recycled or given back */
+                } else if ((old & (BAM_VALID | BAM_BUSY)) == BAM_VALID) {
+                    if (write && !(old & BAM_DIRTY)) atom_or_relaxed(&sl->state, BAM_DIRTY);
+                    count_hit(pc, count);
+                    slot = s; state = S_DONE;
+                } else {
+                    slot = s; state = S_WAIT;                                  /* someone is filling it  */
+                }
+            } else {
+                const uint32_t v = find_slot(pc, kClaimTries);
+                if (v == BAM_SLOT_ERR) { state = S_DONE; }
+                else if (v == BAM_SLOT_NONE) {
+                    /* everything the sweep saw is pinned or busy.  The warp-mates that did get a
+                     * slot must not wait for this lane while it waits for slots they hold pinned:
+                     * report RETRY, the caller releases its pages and asks again. */
+                    slot = BAM_SLOT_RETRY; state = S_DONE;
+                } else {
+                    bam_slot_t* sl = &pc.slots[v];
+                    st_relaxed_gpu(&sl->tag, tag);
+                    __threadfence();
+                    const int r = pt_insert(pc, tag, v, home, fp);
+                    if (r == BAM_PT_OK) { slot = v; state = S_IO; }
+                    else {
+                        st_relaxed_gpu(&sl->tag, BAM_TAG_NONE);
+                        atom_and_release(&sl->state, ~BAM_BUSY);                /* give the slot back     */
+                        if (r != BAM_PT_EXISTS) {
+                            if (r == BAM_PT_FULL) status_fail(st, BAM_ENOSPC, BAM_AT_TABLE_FULL, tag);
+                            state = S_DONE;
+                        }
+                    }
+                }
+            }
+        }
+        /* all page reads of this round go out as one group */
+        const bool io = state == S_IO;
+        if (__any_sync(mask, io)) {
+            const uint64_t bus = io ? slot_bus_addr(pc, slot) : 0;
+            uint64_t prp2 = 0;
+            if (io && pc.page_size > 4096)
+                prp2 = (pc.page_size <= 8192) ? bus + 4096 : (uint64_t)(pc.prp_lists + (size_t)slot * pc.prp_list_stride);
+            const int rc = warp_io(mask, io, qp, backing_page * pc.n_blocks_per_page, pc.n_blocks_per_page, bus, prp2, NVM_IO_READ);
+            if (io) {
+                if (rc == BAM_OK) {
+                    bam_slot_t* sl = &pc.slots[slot];
+                    count_miss(pc, count);
+                    atom_add_relaxed(&sl->state, count + (write ? BAM_DIRTY : 0u));
+                    atom_xor_release(&sl->state, BAM_VALID | BAM_BUSY);         /* BUSY -> VALID          */
+                } else slot = BAM_SLOT_ERR;
+                state = S_DONE;
+            }
+        }
+        if (state == S_WAIT) {
+            bam_slot_t* sl = &pc.slots[slot];
+            const uint32_t cur = ld_acquire_gpu(&sl->state);
+            if (ld_relaxed_gpu(&sl->tag) != tag || (cur & (BAM_VALID | BAM_BUSY)) == 0u) {
+                red_add_relaxed(&sl->state, 0u - count);
+                slot = BAM_SLOT_ERR; state = S_LOOKUP;
+            } else if ((cur & (BAM_VALID | BAM_BUSY)) == BAM_VALID) {
+                if (write && !(cur & BAM_DIRTY)) atom_or_relaxed(&sl->state, BAM_DIRTY);
+                count_hit(pc, count);
+                state = S_DONE;
+            }
+        }
+        if (!__any_sync(mask, state != S_DONE)) break;
+        if (__any_sync(mask, sp.expired(st, BAM_AT_PAGE_BUSY, tag))) {
+            if (state == S_WAIT) red_add_relaxed(&pc.slots[slot].state, 0u - count);
+            if (state != S_DONE) slot = BAM_SLOT_ERR;
+            break;
+        }
+    }
+    return slot;
 }
 
 BAM_DEV void cache_release(const page_cache_d_t& pc, uint32_t slot, uint32_t count)

@@ -10,13 +10,20 @@
  * overwrites completions the host has not released through the CQ head doorbell, and may
  * complete commands out of order.
  *
- * Here that controller is a set of warps: blocks [0, n_ctrl_blocks) of a fused launch
- * (bam/launch.cuh) run emu_controller_main() while the remaining blocks run the workload.
- * The backing store is pinned host memory mapped into the device address space, so every
- * page a command reads crosses the host link exactly once, as it would from an SSD.
- * Several warps may serve one queue: a per-queue lock serialises only the fetch of a small
- * batch of commands (and the hand-out of their completion slots); the data movement of
- * different batches overlaps.
+ * Here that controller is a set of threads: blocks [0, n_ctrl_blocks) of a fused launch run
+ * emu_controller_main() while the remaining blocks run the workload.  The backing store is
+ * pinned host memory mapped into the device address space, so every page a command reads
+ * crosses the host link exactly once, as it would from an SSD.
+ *
+ * Data movement uses the bulk-copy engine (TMA, cp.async.bulk) and costs no registers: a lane
+ * issues an asynchronous bulk load (media -> its 4 KiB shared-memory stage, completion counted on
+ * an mbarrier), then an asynchronous bulk store (stage -> PRP target), and after the store has
+ * completed releases the completion entry.  What limits a software controller is not the copy
+ * but the chain of dependent protocol steps per command (doorbell read, lock, SQ entry read,
+ * completion release at system scope), so those are overlapped SIMT-style: a processor is one
+ * warp, it reserves a BATCH of commands from one queue under that queue's fetch lock, and then
+ * BAM_EMU_LANES lanes each decode, transfer and complete their own command side by side.
+ * Several processors may serve one queue; the lock covers only the reservation.
  */
 #ifndef BAM_EMU_CTRL_CUH
 #define BAM_EMU_CTRL_CUH
@@ -30,176 +37,264 @@ namespace bam {
 #define BAM_SC_INVALID_FIELD 0x02u
 #define BAM_SC_LBA_OUT_OF_RANGE 0x80u
 
-/* Copy `bytes` (a multiple of 16, both pointers 16-byte aligned) with the whole warp.
- * Up to eight 128-bit loads per lane are in flight before the first store. */
-BAM_DEV void warp_copy_16(uint8_t* dst, const uint8_t* src, uint32_t bytes, uint32_t lane)
+#define BAM_EMU_STAGE_BYTES 4096
+#define BAM_EMU_LANES 4             /* lanes of a controller warp that process commands (one stage each) */
+#define BAM_EMU_WARPS 4             /* warps of a controller block that are command processors            */
+#define BAM_EMU_STAGES (BAM_EMU_LANES * BAM_EMU_WARPS)     /* 4 KiB stages per controller block           */
+/* dynamic shared memory a controller block needs: the stages and one mbarrier per stage */
+#define BAM_EMU_SMEM_BYTES (BAM_EMU_STAGES * BAM_EMU_STAGE_BYTES + 256)
+
+/* ---- bulk-copy / mbarrier primitives ------------------------------------------------------- */
+BAM_DEV uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+BAM_DEV void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+BAM_DEV void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
+BAM_DEV bool mbar_test(uint32_t bar, uint32_t parity)
 {
-    const uint32_t n16 = bytes >> 4;
-    for (uint32_t base = 0; base < n16; base += 256) {
-        uint4 v[8];
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            uint32_t i = base + k * 32 + lane;
-            if (i < n16) v[k] = ld_cg_v4(src + ((size_t)i << 4));
-        }
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            uint32_t i = base + k * 32 + lane;
-            if (i < n16) *reinterpret_cast<uint4*>(dst + ((size_t)i << 4)) = v[k];
-        }
-    }
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+BAM_DEV void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+BAM_DEV void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes)
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+BAM_DEV void bulk_store_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.global;" ::: "memory");
 }
 
-/* Execute one READ or WRITE with the whole warp.  Returns the NVMe status code. */
-BAM_DEV uint32_t emu_execute(const bam_emu_d_t& c, uint32_t dw0, uint64_t prp1, uint64_t prp2,
-                             uint64_t slba, uint32_t nlb, uint32_t lane)
+/* One fetched command, decoded. */
+struct emu_cmd_t {
+    uint64_t prp1, prp2, media_off;
+    uint32_t bytes;        /* transfer length                               */
+    uint32_t cq_virt;      /* completion slot handed out at fetch time      */
+    uint32_t q;            /* queue pair index                              */
+    uint32_t cid, sqhd, opc, status;
+};
+
+/* Post the completion of a command (release at system scope, after its payload). */
+BAM_DEV void emu_post_completion(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t status)
 {
-    const uint32_t opc = dw0 & 0x7fu;
-    if (opc != NVM_IO_READ && opc != NVM_IO_WRITE) return BAM_SC_INVALID_OPCODE;
-    const uint64_t bytes = (uint64_t)(nlb + 1u) << c.lba_log2;
-    const uint64_t off = slba << c.lba_log2;
-    if (off + bytes > c.store_bytes || off + bytes < off) return BAM_SC_LBA_OUT_OF_RANGE;
-    if (prp1 & 15u) return BAM_SC_INVALID_FIELD;
+    bam_emu_qp_t* s = &c.qps[m.q];
+    bool drop = false;
+    if (c.fault) {
+        const uint32_t mode = ld_relaxed_gpu(&c.fault->mode);
+        if (mode != BAM_FAULT_NONE) {
+            const uint64_t k = atom_add_relaxed(&c.fault->counter, 1ull);
+            if (k == c.fault->nth) {
+                if (mode == BAM_FAULT_DROP_CPL) drop = true;
+                else if (mode == BAM_FAULT_STATUS) status = c.fault->status;
+            }
+        }
+    }
+    if (!drop) {
+        const uint32_t mask = s->qs - 1u;
+        const uint32_t phase = (~(m.cq_virt >> s->qs_log2)) & 1u;
+        nvm_cpl_t* e = &s->cq_mem[m.cq_virt & mask];
+        *reinterpret_cast<volatile uint64_t*>(&e->dword[0]) = 0ull;
+        const uint64_t dw2 = m.sqhd | ((uint32_t)s->sqid << 16);
+        const uint64_t dw3 = m.cid | (phase << 16) | (status << 17);
+        st_release_scoped(reinterpret_cast<uint64_t*>(&e->dword[2]), dw2 | (dw3 << 32), c.sys_scope != 0);
+    }
+    red_add_relaxed(c.served, 1ull);
+}
+
+/* Lane 0 of a processor: look at queue pair q and, if commands are waiting, take the fetch lock
+ * and reserve up to `want` of them together with their completion slots.  Returns the number
+ * reserved (0: nothing taken, lock not held).  The doorbells are polled with relaxed loads; one
+ * acquire fence follows only when there is work. */
+BAM_DEV uint32_t emu_reserve(const bam_emu_d_t& c, uint32_t q, uint32_t want, uint32_t& fetch, uint32_t& cqbase)
+{
+    bam_emu_qp_t* s = &c.qps[q];
+    const uint32_t mask = s->qs - 1u;
+    if (ld_relaxed_sys(s->sq_db) == (ld_relaxed_gpu(&s->sq_fetch) & mask)) return 0;
+    if (atom_cas_acquire(&s->lock, 0u, 1u) != 0u) return 0;
+    fetch = ld_relaxed_gpu(&s->sq_fetch);
+    const uint32_t tail = ld_relaxed_sys(s->sq_db);
+    const uint32_t hdb = ld_relaxed_sys(s->cq_db);
+    uint32_t cq_head = ld_relaxed_gpu(&s->cq_head);
+    cqbase = ld_relaxed_gpu(&s->cq_tail);
+    const uint32_t avail = (tail - fetch) & mask;
+    cq_head += (hdb - cq_head) & mask;
+    const uint32_t space = mask - (cqbase - cq_head);          /* keep one completion slot open */
+    uint32_t n = avail < space ? avail : space;
+    if (n > want) n = want;
+    if (n == 0) { st_release_gpu(&s->lock, 0u); return 0; }
+    fence_acq_rel_scoped(c.sys_scope != 0);                    /* acquire the command bytes      */
+    st_relaxed_gpu(&s->cq_head, cq_head);
+    st_relaxed_gpu(&s->cq_tail, cqbase + n);
+    return n;
+}
+
+/* Read and decode SQ entry `fetch_i` of queue pair q. */
+BAM_DEV void emu_decode(const bam_emu_d_t& c, uint32_t q, uint32_t fetch_i, uint32_t cq_virt, uint32_t sqhd, emu_cmd_t& m)
+{
+    bam_emu_qp_t* s = &c.qps[q];
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(&s->sq_mem[fetch_i & (s->qs - 1u)]);
+    const uint4 a = ld_cg_v4(p), b = ld_cg_v4(p + 16), d = ld_cg_v4(p + 32), e = ld_cg_v4(p + 48);
+    m.opc = a.x & 0x7fu;
+    m.cid = a.x >> 16;
+    m.prp1 = ((uint64_t)b.w << 32) | b.z;
+    m.prp2 = ((uint64_t)d.y << 32) | d.x;
+    const uint64_t slba = ((uint64_t)d.w << 32) | d.z;
+    const uint64_t bytes = (uint64_t)((e.x & 0xffffu) + 1u) << c.lba_log2;
+    m.media_off = slba << c.lba_log2;
+    m.bytes = (uint32_t)bytes;
+    m.cq_virt = cq_virt;
+    m.q = q;
+    m.sqhd = sqhd;
+    m.status = BAM_SC_SUCCESS;
+    if (m.opc != NVM_IO_READ && m.opc != NVM_IO_WRITE) m.status = BAM_SC_INVALID_OPCODE;
+    else if (m.media_off + bytes > c.store_bytes || m.media_off + bytes < m.media_off) m.status = BAM_SC_LBA_OUT_OF_RANGE;
+    else if ((m.prp1 & 15u) || (bytes & 15u)) m.status = BAM_SC_INVALID_FIELD;
+}
+
+/* Move the data of one command through this lane's stage, segment by segment (a 4 KiB page is
+ * one segment).  Returns the NVMe status. */
+BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t stage_smem, uint32_t bar, uint32_t& parity)
+{
     const uint64_t mps = 1ull << c.mps_log2;
-    uint8_t* media = c.store + off;
-    /* first chunk: from PRP1 to the end of its memory page */
-    uint64_t first = mps - (prp1 & (mps - 1));
-    if (first > bytes) first = bytes;
-    uint64_t done = 0;
-    uint64_t seg_addr = prp1, seg_len = first;
-    uint32_t list_i = 0;
-    const bool use_list = (bytes - first) > mps;
-    while (done < bytes) {
-        uint8_t* mem = reinterpret_cast<uint8_t*>(seg_addr);
-        uint8_t* med = media + done;
-        warp_copy_16(opc == NVM_IO_READ ? mem : med, opc == NVM_IO_READ ? med : mem, (uint32_t)seg_len, lane);
-        done += seg_len;
-        if (done >= bytes) break;
-        if (!use_list) seg_addr = prp2;
-        else seg_addr = ld_relaxed_gpu(reinterpret_cast<const uint64_t*>(prp2) + list_i++);
-        if (seg_addr & (mps - 1)) return BAM_SC_INVALID_FIELD;
-        seg_len = bytes - done < mps ? bytes - done : mps;
+    uint64_t first = mps - (m.prp1 & (mps - 1));
+    if (first > m.bytes) first = m.bytes;
+    const bool use_list = (m.bytes - first) > mps;
+    uint32_t done = 0, list_i = 0;
+    while (done < m.bytes) {
+        uint64_t mem;
+        uint32_t len;
+        if (done == 0) { mem = m.prp1; len = (uint32_t)first; }
+        else {
+            mem = use_list ? ld_relaxed_gpu(reinterpret_cast<const uint64_t*>(m.prp2) + list_i++) : m.prp2;
+            if (mem & (mps - 1)) return BAM_SC_INVALID_FIELD;
+            len = m.bytes - done < mps ? m.bytes - done : (uint32_t)mps;
+        }
+        if (len > BAM_EMU_STAGE_BYTES) len = BAM_EMU_STAGE_BYTES;
+        uint8_t* media = c.store + m.media_off + done;
+        const void* src = (m.opc == NVM_IO_READ) ? (const void*)media : (const void*)mem;
+        void* dst = (m.opc == NVM_IO_READ) ? (void*)mem : (void*)media;
+        BAM_PROF_T0();
+        mbar_expect_tx(bar, len);
+        bulk_load(stage_smem, src, len, bar);
+        const uint64_t t0 = global_timer_ns();
+        uint32_t polls = 0;
+        while (!mbar_test(bar, parity)) {
+            if (((++polls) & 1023u) == 0u) {
+                const uint64_t waited = global_timer_ns() - t0;
+                if (waited > c.status->spin_timeout_ns) status_fail(c.status, BAM_ETIMEDOUT, BAM_AT_TMA, (uint64_t)dst);
+                if (waited > 2 * c.status->spin_timeout_ns) return 0xffffffffu;     /* the copy never landed */
+            }
+        }
+        parity ^= 1u;
+        BAM_PROF_LAP(c.status, 20);
+        bulk_store(dst, stage_smem, len);
+        bulk_store_wait_all();
+        BAM_PROF_LAP(c.status, 21);
+        done += len;
     }
     return BAM_SC_SUCCESS;
 }
 
-/* Try to fetch and execute one batch from queue pair q.  Returns true if any command ran. */
-BAM_DEV bool emu_serve_queue(const bam_emu_d_t& c, uint32_t q, uint32_t lane)
-{
-    bam_emu_qp_t* s = &c.qps[q];
-    const uint32_t mask = s->qs - 1u;
-    uint32_t n = 0, fetch = 0, cqbase = 0;
-    if (lane == 0) {
-        uint32_t tail = ld_acquire_sys(s->sq_db);
-        if (tail != (ld_relaxed_gpu(&s->sq_fetch) & mask) && atom_cas_acquire(&s->lock, 0u, 1u) == 0u) {
-            fetch = ld_relaxed_gpu(&s->sq_fetch);
-            tail = ld_acquire_sys(s->sq_db);
-            uint32_t avail = (tail - fetch) & mask;
-            uint32_t hdb = ld_acquire_sys(s->cq_db);
-            uint32_t cq_head = ld_relaxed_gpu(&s->cq_head);
-            cq_head += (hdb - cq_head) & mask;
-            st_relaxed_gpu(&s->cq_head, cq_head);
-            cqbase = ld_relaxed_gpu(&s->cq_tail);
-            uint32_t space = mask - (cqbase - cq_head);      /* keep one completion slot open */
-            n = avail < space ? avail : space;
-            if (n > c.batch) n = c.batch;
-            if (n) st_relaxed_gpu(&s->cq_tail, cqbase + n);
-            else st_release_gpu(&s->lock, 0u);
-        }
-    }
-    n = __shfl_sync(0xffffffffu, n, 0);
-    if (n == 0) return false;
-    fetch = __shfl_sync(0xffffffffu, fetch, 0);
-    cqbase = __shfl_sync(0xffffffffu, cqbase, 0);
-
-    /* lane i reads command i of the batch into registers, then the SQ slots are released */
-    uint32_t dw0 = 0, nlb = 0;
-    uint64_t prp1 = 0, prp2 = 0, slba = 0;
-    if (lane < n) {
-        const uint8_t* p = reinterpret_cast<const uint8_t*>(&s->sq_mem[(fetch + lane) & mask]);
-        uint4 a = ld_cg_v4(p), b = ld_cg_v4(p + 16), d = ld_cg_v4(p + 32), e = ld_cg_v4(p + 48);
-        dw0 = a.x;
-        prp1 = ((uint64_t)b.w << 32) | b.z;
-        prp2 = ((uint64_t)d.y << 32) | d.x;
-        slba = ((uint64_t)d.w << 32) | d.z;
-        nlb = e.x & 0xffffu;
-    }
-    __syncwarp();
-    if (lane == 0) {
-        st_relaxed_gpu(&s->sq_fetch, fetch + n);
-        st_release_gpu(&s->lock, 0u);
-    }
-    const uint32_t sqhd = (fetch + n) & mask;
-
-    /* fault injection is decided per command by lane 0 */
-    const uint32_t fault_mode = c.fault ? ld_relaxed_gpu(&c.fault->mode) : BAM_FAULT_NONE;
-
-    for (uint32_t i = 0; i < n; i++) {
-        uint32_t c_dw0 = __shfl_sync(0xffffffffu, dw0, i);
-        uint32_t c_nlb = __shfl_sync(0xffffffffu, nlb, i);
-        uint64_t c_prp1 = __shfl_sync(0xffffffffu, prp1, i);
-        uint64_t c_prp2 = __shfl_sync(0xffffffffu, prp2, i);
-        uint64_t c_slba = __shfl_sync(0xffffffffu, slba, i);
-        uint32_t status = emu_execute(c, c_dw0, c_prp1, c_prp2, c_slba, c_nlb, lane);
-        __threadfence();          /* every lane's payload stores are ordered before ...       */
-        __syncwarp();             /* ... lane 0's release of the completion entry              */
-        if (lane == 0) {
-            bool drop = false;
-            if (fault_mode != BAM_FAULT_NONE) {
-                uint64_t k = atom_add_relaxed(&c.fault->counter, 1ull);
-                if (k == c.fault->nth) {
-                    if (fault_mode == BAM_FAULT_DROP_CPL) drop = true;
-                    else if (fault_mode == BAM_FAULT_STATUS) status = c.fault->status;
-                }
-            }
-            if (!drop) {
-                uint32_t v = cqbase + i;
-                uint32_t phase = (~(v >> s->qs_log2)) & 1u;
-                nvm_cpl_t* e = &s->cq_mem[v & mask];
-                *reinterpret_cast<volatile uint64_t*>(&e->dword[0]) = 0ull;
-                uint64_t dw2 = sqhd | ((uint32_t)s->sqid << 16);
-                uint64_t dw3 = (c_dw0 >> 16) | (phase << 16) | (status << 17);
-                st_release_sys(reinterpret_cast<uint64_t*>(&e->dword[2]), dw2 | (dw3 << 32));
-            }
-            red_add_relaxed(c.served, 1ull);
-        }
-    }
-    return true;
-}
-
-/* Body of a controller block.  Runs until every workload block of the launch has finished
- * (consumers_remaining == 0) or an error has been flagged. */
-BAM_DEV void emu_controller_main(const bam_emu_d_t& c)
+/* Body of a controller block.  Warps [0, BAM_EMU_WARPS) are command processors; in each, lanes
+ * [0, BAM_EMU_LANES) own one 4 KiB stage and one mbarrier.  A processor reserves a batch of up to
+ * BAM_EMU_LANES commands from one queue under that queue's fetch lock, then every lane decodes,
+ * transfers and completes its own command, so the latencies of a batch overlap.  Runs until
+ * every workload block of the launch has finished (consumers_remaining == 0) or an error has been
+ * flagged.  `smem` is the block's dynamic shared memory (BAM_EMU_SMEM_BYTES, 128-byte aligned). */
+BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
 {
     const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t warps_per_block = blockDim.x >> 5;
-    const uint32_t warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-    const uint32_t n_warps = c.n_ctrl_blocks * warps_per_block;
-    const uint32_t rounds = (c.n_qps + n_warps - 1) / n_warps;
-    uint32_t idle_ns = 32;
+    const uint32_t wib = threadIdx.x >> 5;
+    if (wib >= BAM_EMU_WARPS || lane >= BAM_EMU_LANES) return;
+    const uint32_t wmask = (1u << BAM_EMU_LANES) - 1u;
+    const uint32_t me = blockIdx.x * BAM_EMU_WARPS + wib;
+    const uint32_t n_procs = c.n_ctrl_blocks * BAM_EMU_WARPS;
+    const uint32_t my_stage = wib * BAM_EMU_LANES + lane;
+    const uint32_t stage_smem = smem_u32(smem + (size_t)my_stage * BAM_EMU_STAGE_BYTES);
+    const uint32_t bar = smem_u32(smem + (size_t)BAM_EMU_STAGES * BAM_EMU_STAGE_BYTES + my_stage * 8);
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp(wmask);
+
     const uint64_t t_start = global_timer_ns();
+    const uint32_t rounds = (c.n_qps + n_procs - 1) / n_procs;
+    uint32_t want = c.batch < BAM_EMU_LANES ? c.batch : BAM_EMU_LANES;
+    if (want == 0) want = 1;
+    uint32_t parity = 0;
+    uint32_t q = me % c.n_qps;
+    uint32_t idle_ns = 32, idle_rounds = 0;
+
     for (;;) {
-        bool any = false;
-        uint32_t q = warp % c.n_qps;
-        for (uint32_t r = 0; r < rounds; r++) {
-            any |= emu_serve_queue(c, q, lane);
-            q += n_warps;
-            if (q >= c.n_qps) q -= c.n_qps;
-            if (q >= c.n_qps) q %= c.n_qps;
+        uint32_t n = 0, fetch = 0, cqbase = 0, bq = 0;
+#ifdef BAM_PROFILE
+        long long pt = clock64();
+#endif
+        if (lane == 0) {
+            for (uint32_t r = 0; r < rounds && n == 0; r++) {
+                n = emu_reserve(c, q, want, fetch, cqbase);
+                bq = q;
+                q += n_procs;
+                while (q >= c.n_qps) q -= c.n_qps;
+            }
         }
-        if (any) { idle_ns = 32; continue; }
+        n = __shfl_sync(wmask, n, 0);
+        if (n) {
+            fetch = __shfl_sync(wmask, fetch, 0);
+            cqbase = __shfl_sync(wmask, cqbase, 0);
+            bq = __shfl_sync(wmask, bq, 0);
+            __syncwarp(wmask);                                 /* lane 0's acquire fence covers the batch */
+            const uint32_t qmask = c.qps[bq].qs - 1u;
+            emu_cmd_t m;
+            if (lane < n) emu_decode(c, bq, fetch + lane, cqbase + lane, (fetch + n) & qmask, m);
+            __syncwarp(wmask);
+            if (lane == 0) {                                   /* the SQ entries are in registers now */
+                st_relaxed_gpu(&c.qps[bq].sq_fetch, fetch + n);
+                st_release_gpu(&c.qps[bq].lock, 0u);
+#ifdef BAM_PROFILE
+                { long long t = clock64(); BAM_PROF_ADD(c.status, 16, 1); BAM_PROF_ADD(c.status, 17, n); BAM_PROF_ADD(c.status, 18, t - pt); pt = t; }
+#endif
+            }
+            if (lane < n) {
+                uint32_t status = m.status;
+                if (status == BAM_SC_SUCCESS) status = emu_transfer(c, m, stage_smem, bar, parity);
+#ifdef BAM_PROFILE
+                long long t1 = clock64();
+#endif
+                if (status != 0xffffffffu) emu_post_completion(c, m, status);
+#ifdef BAM_PROFILE
+                BAM_PROF_ADD(c.status, 22, clock64() - t1);
+#endif
+            }
+            __syncwarp(wmask);
+#ifdef BAM_PROFILE
+            if (lane == 0) BAM_PROF_ADD(c.status, 19, clock64() - pt);
+#endif
+            idle_ns = 32; idle_rounds = 0;
+            continue;
+        }
         uint32_t stop = 0;
         if (lane == 0) {
             stop = (ld_acquire_gpu(c.consumers_remaining) == 0u) || status_bad(c.status);
-            if (!stop && global_timer_ns() - t_start > c.status->launch_timeout_ns) {
+            if (!stop && ((++idle_rounds) & 63u) == 0u && global_timer_ns() - t_start > c.status->launch_timeout_ns) {
                 status_fail(c.status, BAM_ETIMEDOUT, BAM_AT_LAUNCH, 0);
                 stop = 1;
             }
         }
-        stop = __shfl_sync(0xffffffffu, stop, 0);
+        stop = __shfl_sync(wmask, stop, 0);
+#ifdef BAM_PROFILE
+        if (lane == 0) { BAM_PROF_ADD(c.status, 23, 1); BAM_PROF_ADD(c.status, 24, clock64() - pt); }
+#endif
         if (stop) break;
         __nanosleep(idle_ns);
-        if (idle_ns < 1024) idle_ns <<= 1;
+        if (idle_ns < 512) idle_ns <<= 1;
     }
 }
 

@@ -42,6 +42,15 @@ BAM_DEV void st_release_sys(uint64_t* p, uint64_t v) { asm volatile("st.release.
 BAM_DEV void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 BAM_DEV void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 
+/* Scope chosen at run time.  Doorbells and completion entries are the words the NVMe controller
+ * shares with the GPU threads.  When the controller is another agent of the system (a device on
+ * the bus, host threads) they need system scope.  When it is the emulated controller running in
+ * the same launch on the same GPU, device scope already contains every thread involved, and it is
+ * much cheaper: a system-scope fence has to wait behind the host-link traffic. */
+BAM_DEV void st_release_scoped(uint32_t* p, uint32_t v, bool sys) { if (sys) st_release_sys(p, v); else st_release_gpu(p, v); }
+BAM_DEV void st_release_scoped(uint64_t* p, uint64_t v, bool sys) { if (sys) st_release_sys(p, v); else st_release_gpu(p, v); }
+BAM_DEV void fence_acq_rel_scoped(bool sys) { if (sys) fence_acq_rel_sys(); else fence_acq_rel_gpu(); }
+
 /* ---- read-modify-write ------------------------------------------------------------------ */
 BAM_DEV uint32_t atom_add_relaxed(uint32_t* p, uint32_t v) { uint32_t o; asm volatile("atom.relaxed.gpu.add.u32 %0, [%1], %2;" : "=r"(o) : "l"(p), "r"(v) : "memory"); return o; }
 BAM_DEV uint32_t atom_add_acquire(uint32_t* p, uint32_t v) { uint32_t o; asm volatile("atom.acquire.gpu.add.u32 %0, [%1], %2;" : "=r"(o) : "l"(p), "r"(v) : "memory"); return o; }
@@ -66,6 +75,17 @@ BAM_DEV uint4 ld_cg_v4(const void* p) { uint4 v; asm volatile("ld.global.cg.v4.u
 BAM_DEV uint32_t lane_id() { uint32_t r; asm volatile("mov.u32 %0, %%laneid;" : "=r"(r)); return r; }
 BAM_DEV uint32_t get_smid() { uint32_t r; asm volatile("mov.u32 %0, %%smid;" : "=r"(r)); return r; }
 BAM_DEV uint64_t global_timer_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+
+/* ---- optional profiling counters (compiled out unless -DBAM_PROFILE) ---------------------------- */
+#ifdef BAM_PROFILE
+#define BAM_PROF_T0() const long long bam_prof_t0_ = clock64()
+#define BAM_PROF_ADD(st, idx, v) red_add_relaxed(&(st)->prof[idx], (uint64_t)(v))
+#define BAM_PROF_LAP(st, idx) red_add_relaxed(&(st)->prof[idx], (uint64_t)(clock64() - bam_prof_t0_))
+#else
+#define BAM_PROF_T0() do {} while (0)
+#define BAM_PROF_ADD(st, idx, v) do {} while (0)
+#define BAM_PROF_LAP(st, idx) do {} while (0)
+#endif
 
 /* ---- status + bounded wait ---------------------------------------------------------------- */
 BAM_DEV bool status_bad(const bam_status_t* st) { return ld_relaxed_gpu(&st->code) != 0; }

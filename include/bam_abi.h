@@ -61,6 +61,11 @@ int bam_ctrl_configure(bam_ctrl_t c, uint32_t n_ctrl_blocks, uint32_t batch, uin
 /* Upper limit for one fused launch (default 300 s): the controller blocks flag BAM_ETIMEDOUT and
  * every wait in the launch drains. */
 int bam_ctrl_set_launch_timeout(bam_ctrl_t c, uint64_t launch_timeout_ns);
+/* Scope of the acquire/release operations on doorbells and completion entries.  1 = system scope
+ * (what a controller outside this GPU needs), 0 = device scope (sufficient, and the default, for
+ * the emulated controller, which runs inside the same launch on the same GPU).  Re-initialises
+ * the queue pairs. */
+int bam_ctrl_set_scope(bam_ctrl_t c, int system_scope);
 /* Cap the grid of the fused launches (0 = as many blocks as are co-resident).  Small caches
  * need it: each resident warp may pin up to 32 pages at once. */
 int bam_ctrl_set_max_grid(bam_ctrl_t c, uint32_t max_grid);
@@ -72,6 +77,9 @@ int bam_ctrl_inject_fault(bam_ctrl_t c, uint32_t mode, uint64_t nth, uint32_t st
 int bam_ctrl_status(bam_ctrl_t c, bam_status_out_t* out, int clear);
 /* Commands served since creation (Controller::print_reset_stats, include/ctrl.h:86-92). */
 int bam_ctrl_served(bam_ctrl_t c, uint64_t* out, int reset);
+/* The 32 profiling counters of the status block (all zero unless the library was built with
+ * -DBAM_PROFILE): cycles and event counts of the protocol stages, for tuning. */
+int bam_ctrl_profile(bam_ctrl_t c, uint64_t* out32, int reset);
 /* Re-initialise every queue pair to its power-on state (nvm_queue_clear, src/queue.cpp:12-42).
  * Needed after an injected fault left commands unaccounted for. */
 int bam_ctrl_reset_queues(bam_ctrl_t c);
