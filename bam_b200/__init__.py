@@ -6,3 +6,4 @@ array_t) over the C ABI of libbam_b200.so.  The CUDA library is mandatory.
 from ._lib import BamError, CacheStats, StatusOut, load  # noqa: F401
 from .host import (Array, Controller, PageCache, gen_uniform_indices, gen_zipf_indices,  # noqa: F401
                    direct_checksum, shard_pages, zipf_cdf)
+from .graph import CsrGraph, build_rmat_csr, rmat_thresholds  # noqa: F401,E402

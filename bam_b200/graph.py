@@ -1,0 +1,102 @@
+"""Graph consumers: CSR graphs in the backing store, BFS and connected components through
+bam::array (host mirror of the drivers in the reference's benchmarks/bfs and benchmarks/cc).
+
+The CSR is built on the GPU from the seeded R-MAT generator of include/bam_synth.h (torch sort /
+unique are plumbing here, exactly like reading a .bel file would be); row offsets and column
+indices are then written to the controller's backing store, offsets first, each page aligned, and
+from then on are read only through the page cache."""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import check
+from .host import Array, Controller, PageCache, _ptr
+
+
+def rmat_thresholds(a=0.57, b=0.19, c=0.19):
+    """Integer quadrant thresholds floor(p * 2^32) of the R-MAT generator."""
+    return int(a * 4294967296.0), int((a + b) * 4294967296.0), int((a + b + c) * 4294967296.0)
+
+
+def build_rmat_csr(seed, scale, edge_factor=16, device="cuda", thresholds=None, chunk_edges=1 << 25):
+    """Undirected, de-duplicated, sorted CSR of the seeded R-MAT graph, on the device.
+
+    Returns (offsets[n+1], cols[m]) as int64 tensors (the u64 values fit: scale <= 31)."""
+    import torch
+    lib = _lib.load()
+    ta, tab, tabc = thresholds or rmat_thresholds()
+    n, m = 1 << scale, edge_factor << scale
+    parts = []
+    for e0 in range(0, m, chunk_edges):
+        e1 = min(m, e0 + chunk_edges)
+        k = torch.empty(2 * (e1 - e0), dtype=torch.int64, device=device)
+        check(lib.bam_gen_rmat_keys(_ptr(k), e0, e1, seed, scale, ta, tab, tabc, None), "bam_gen_rmat_keys")
+        k = torch.unique(k)                      # sorted, duplicates within the chunk removed
+        parts.append(k)
+    keys = torch.unique(torch.cat(parts)) if len(parts) > 1 else parts[0]
+    del parts
+    if keys.numel() and int(keys[0].item()) == -1:      # self loops were written as ~0
+        keys = keys[1:]
+    src = keys >> 32
+    cols = keys & 0xFFFFFFFF
+    counts = torch.bincount(src, minlength=n)
+    offsets = torch.zeros(n + 1, dtype=torch.int64, device=device)
+    torch.cumsum(counts, 0, out=offsets[1:])
+    return offsets, cols
+
+
+class CsrGraph:
+    """A CSR graph stored behind an emulated NVMe controller and read through a page cache."""
+
+    def __init__(self, offsets, cols, cache_pages, cuda_device=0, queue_depth=1024, num_queues=128, page_size=4096,
+                 ctrl_blocks=0):
+        import torch
+        self.n = offsets.numel() - 1
+        self.m = cols.numel()
+        pad = lambda b: (b + page_size - 1) // page_size * page_size  # noqa: E731
+        self.off_bytes = pad((self.n + 1) * 8)
+        self.col_bytes = pad(max(1, self.m) * 8)
+        self.ctrl = Controller(self.off_bytes + self.col_bytes, cuda_device, queue_depth=queue_depth,
+                               num_queues=num_queues)
+        if ctrl_blocks:
+            self.ctrl.configure(ctrl_blocks=ctrl_blocks)
+        lib = self.ctrl.lib
+        check(lib.bam_ctrl_write_store_from_device(self.ctrl.h, 0, _ptr(offsets), (self.n + 1) * 8, None), "write offsets")
+        if self.m:
+            check(lib.bam_ctrl_write_store_from_device(self.ctrl.h, self.off_bytes, _ptr(cols), self.m * 8, None), "write cols")
+        torch.cuda.synchronize()
+        self.cache = PageCache(self.ctrl, page_size, cache_pages)
+        self.offsets = Array(self.cache, self.n + 1, 8, 0)
+        self.cols = Array(self.cache, max(1, self.m), 8, self.off_bytes)
+        self.device = cuda_device
+
+    def close(self):
+        self.cols.close(); self.offsets.close(); self.cache.close(); self.ctrl.close()
+
+    def bfs(self, source):
+        """Level-synchronous BFS from `source`; returns (levels uint32 tensor as int32 bits, n_levels, edges_scanned)."""
+        import torch
+        label = torch.empty(self.n, dtype=torch.int32, device=f"cuda:{self.device}")
+        nl, sc = C.c_uint32(), C.c_uint64()
+        check(self.ctrl.lib.bam_bfs_run(self.offsets.h, self.cols.h, self.n, source, _ptr(label), C.byref(nl), C.byref(sc)),
+              "bam_bfs_run")
+        return label, nl.value, sc.value
+
+    def cc(self):
+        """Connected components by label propagation; returns (labels int64 tensor, sweeps, edges_scanned)."""
+        import torch
+        comp = torch.empty(self.n, dtype=torch.int64, device=f"cuda:{self.device}")
+        ns, sc = C.c_uint32(), C.c_uint64()
+        check(self.ctrl.lib.bam_cc_run(self.offsets.h, self.cols.h, self.n, _ptr(comp), C.byref(ns), C.byref(sc)),
+              "bam_cc_run")
+        return comp, ns.value, sc.value
+
+    def bfs_level(self, v_begin, v_end, level, label, changed, scanned=None, stream=None):
+        check(self.ctrl.lib.bam_launch_bfs_level(self.offsets.h, self.cols.h, v_begin, v_end, level, _ptr(label),
+                                                 _ptr(changed), _ptr(scanned), _ptr(stream)), "bam_launch_bfs_level")
+
+    def cc_sweep(self, v_begin, v_end, comp, curr_visit, next_visit, changed, scanned=None, stream=None):
+        check(self.ctrl.lib.bam_launch_cc_sweep(self.offsets.h, self.cols.h, v_begin, v_end, _ptr(comp), _ptr(curr_visit),
+                                                _ptr(next_visit), _ptr(changed), _ptr(scanned), _ptr(stream)),
+              "bam_launch_cc_sweep")

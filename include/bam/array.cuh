@@ -150,6 +150,24 @@ BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
     return v;
 }
 
+/* Pin one page for a whole warp-group: every lane of `mask` calls it; the lanes with want == true
+ * get the slot of `page` pinned `cnt` times (normally one leader asks on behalf of a group).
+ * Nothing is held while it retries, so it may be used even when the cache is nearly all pinned. */
+template <typename T>
+BAM_DEV uint32_t range_pin_page(const range_d_t<T>& r, uint32_t mask, bool want, uint64_t page, uint32_t cnt, uint32_t queue)
+{
+    uint32_t slot = BAM_SLOT_ERR;
+    bool pending = want;
+    spin_t sp;
+    for (;;) {
+        const uint32_t s = r.acquire_page_warp(mask, pending, page, cnt, false, queue);
+        if (pending && s != BAM_SLOT_RETRY) { slot = s; pending = false; }
+        if (!__any_sync(mask, pending)) break;
+        if (__any_sync(mask, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) break;
+    }
+    return slot;
+}
+
 /* Per-thread cursor that keeps the page of its last access pinned, so a run of accesses to one
  * page costs one pin/unpin (reference: bam_ptr, page_cache.h:415-485).  Reads never mark the
  * page dirty (the reference's non-const operator[] does, :478-484, which causes spurious

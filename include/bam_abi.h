@@ -150,6 +150,38 @@ int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t reqs_per_lan
 int bam_launch_page_scan(bam_array_t a, uint64_t n_pages, const uint64_t* pages_dev, uint64_t first_page,
                          uint64_t* sum_out_dev, void* stream);
 
+/* ---- graph consumers -------------------------------------------------------------------------
+ * CSR graph in the backing store: `offsets` (n_vertices + 1 u64 row offsets) and `cols` (u64
+ * column indices) are two arrays over the SAME cache; both are read only through the cache
+ * (the reference keeps the offsets in plain GPU memory, benchmarks/bfs/main.cu:1244-1259). */
+
+/* One BFS level over vertices [v_begin, v_end) (benchmarks/bfs/main.cu:658-689): every vertex with
+ * label == level relaxes its neighbours; unreached = 0xFFFFFFFF.  *changed_dev is set to 1 if any
+ * label was written, *scanned_dev (may be NULL) is incremented by the edges read. */
+int bam_launch_bfs_level(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint32_t level,
+                         uint32_t* label_dev, uint32_t* changed_dev, uint64_t* scanned_dev, void* stream);
+/* One label-propagation sweep over the vertices of [v_begin, v_end) flagged in curr_visit
+ * (benchmarks/cc/main.cu:123-144, :595-617): for every edge the larger component label takes
+ * the smaller (atomicMin), the written vertex is flagged in next_visit. */
+int bam_launch_cc_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end,
+                        uint64_t* comp_dev, const uint8_t* curr_visit_dev, uint8_t* next_visit_dev,
+                        uint32_t* changed_dev, uint64_t* scanned_dev, void* stream);
+/* Whole traversals on one GPU (the host loops of benchmarks/bfs/main.cu:1577-1736 and
+ * benchmarks/cc/main.cu:1418-1623).  label_dev: n_vertices u32 levels; comp_dev: n_vertices u64
+ * labels, at the fixed point the minimum vertex id of each component.  Synchronous. */
+int bam_bfs_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vertices, uint64_t source,
+                uint32_t* label_dev, uint32_t* n_levels_out, uint64_t* edges_scanned_out);
+int bam_cc_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vertices, uint64_t* comp_dev,
+               uint32_t* n_sweeps_out, uint64_t* edges_scanned_out);
+/* R-MAT edges [e_begin, e_end) of bam_synth.h as directed 64-bit keys (u<<32|v and v<<32|u per
+ * edge, ~0 for self loops) into keys_dev[2*(e_end-e_begin)]; sorting and de-duplicating the keys
+ * gives the CSR (stands in for benchmarks/bam_data_conversion.py + the dataset files). */
+int bam_gen_rmat_keys(uint64_t* keys_dev, uint64_t e_begin, uint64_t e_end, uint64_t seed, uint32_t scale,
+                      uint32_t ta, uint32_t tab, uint32_t tabc, void* stream);
+/* Copy device data into the backing store (loading a dataset onto the "SSD",
+ * benchmarks/readwrite/main.cu:283-316). */
+int bam_ctrl_write_store_from_device(bam_ctrl_t c, uint64_t byte_offset, const void* src_dev, uint64_t bytes, void* stream);
+
 /* ---- synthetic access streams ------------------------------------------------------------------
  * The reference benchmarks build their access lists on the host with rand()
  * (benchmarks/array/main.cu:150-162, benchmarks/pattern/main.cu:560-600); these write the seeded
