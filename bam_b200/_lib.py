@@ -45,6 +45,7 @@ SIGNATURES = {
     "bam_cache_destroy": (ci, [vp]),
     "bam_cache_stats": (ci, [vp, C.POINTER(CacheStats), ci]),
     "bam_cache_invalidate": (ci, [vp]),
+    "bam_cache_invalidate_async": (ci, [vp, vp]),
     "bam_cache_audit": (ci, [vp, C.POINTER(u64)]),
     "bam_cache_audit_noalloc": (ci, [vp, vp, vp]),
     "bam_cache_descriptor": (ci, [vp, vp, C.c_size_t]),

@@ -213,7 +213,11 @@ struct ArrayReadWork {
     }
 };
 
-/* ---- cache benchmark: a warp reads whole pages ----------------------------------------------- */
+/* ---- cache benchmark: a warp reads whole pages -----------------------------------------------
+ * Hit data is staged through shared memory: the warp pins 32 pages at once (one look-up and one
+ * pin per lane, side by side), then streams them through its two 4 KiB stages of the block's
+ * dynamic shared memory with bulk-async loads (two pages in flight per warp), sums each page from
+ * shared memory with 128-bit loads, and finally unpins all 32. */
 struct PageScanWork {
     range_d_t<uint64_t> r;
     uint64_t n_pages;
@@ -224,36 +228,68 @@ struct PageScanWork {
     __device__ void operator()(uint32_t vb, uint32_t nvb) const
     {
         const uint32_t lane = threadIdx.x & 31u;
+        const uint32_t wib = threadIdx.x >> 5;
         const uint32_t wpb = blockDim.x >> 5;
-        const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
+        const uint64_t warp = (uint64_t)vb * wpb + wib;
         const uint64_t nwarps = (uint64_t)nvb * wpb;
+        const uint32_t psz = (uint32_t)r.cache.page_size;
+        /* two stages per warp; pages larger than a stage are streamed in 4 KiB pieces */
+        const uint32_t stage0 = smem_u32(bam_dyn_smem + (size_t)(wib * 2) * BAM_EMU_STAGE_BYTES);
+        const uint32_t bar0 = smem_u32(bam_dyn_smem + (size_t)BAM_EMU_STAGES * BAM_EMU_STAGE_BYTES + (wib * 2) * 8);
+        if (lane == 0) { mbar_init(bar0, 1); mbar_init(bar0 + 8, 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        uint32_t parity = 0;                                   /* bit s = parity stage s completes next */
         uint64_t sum = 0;
-        for (uint64_t p = warp; p < n_pages; p += nwarps) {
-            const uint64_t page = pages ? pages[p] : first_page + p;
-            uint32_t slot;
-            {
-                spin_t sp;
-                for (;;) {       /* nothing is held between attempts */
-                    slot = r.acquire_page_warp(0xffffffffu, lane == 0, page, 1, false, (uint32_t)warp);
-                    slot = __shfl_sync(0xffffffffu, slot, 0);
-                    if (slot != BAM_SLOT_RETRY) break;
-                    if (__any_sync(0xffffffffu, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) { slot = BAM_SLOT_ERR; break; }
+        bool failed = false;
+        for (uint64_t p0 = warp * 32; p0 < n_pages && !failed; p0 += nwarps * 32) {
+            const uint64_t pi = p0 + lane;
+            const bool have = pi < n_pages;
+            const uint64_t page = have ? (pages ? pages[pi] : first_page + pi) : 0;
+            const uint32_t slot = range_pin_page(r, 0xffffffffu, have, page, 1, (uint32_t)warp);
+            const uint32_t ok = __ballot_sync(0xffffffffu, have && slot != BAM_SLOT_ERR);
+            if (__any_sync(0xffffffffu, have && slot == BAM_SLOT_ERR)) failed = true;
+            /* the pieces of all pinned pages, in order: piece q = (lane q / ppp, offset (q % ppp) * 4 KiB) */
+            const uint32_t ppp = (psz + BAM_EMU_STAGE_BYTES - 1) / BAM_EMU_STAGE_BYTES;
+            const uint32_t plen = psz < BAM_EMU_STAGE_BYTES ? psz : BAM_EMU_STAGE_BYTES;
+            const uint32_t n_lanes_ok = __popc(ok);
+            const uint32_t n_pieces = n_lanes_ok * ppp;
+            const uint64_t my_base = (ok >> lane) & 1u ? r.get_cache_page_addr(slot) : 0;
+            /* issue piece q into stage q & 1 */
+            auto issue = [&](uint32_t q) {
+                const uint32_t src_lane = __fns(ok, 0, (int)(q / ppp) + 1);
+                const uint64_t base = __shfl_sync(0xffffffffu, my_base, src_lane);
+                if (lane == 0) {
+                    const uint32_t st = q & 1u;
+                    mbar_expect_tx(bar0 + st * 8, plen);
+                    bulk_load(stage0 + st * BAM_EMU_STAGE_BYTES, reinterpret_cast<const void*>(base + (uint64_t)(q % ppp) * BAM_EMU_STAGE_BYTES), plen, bar0 + st * 8);
                 }
-            }
-            if (slot == BAM_SLOT_ERR) break;
-            const uint8_t* base = reinterpret_cast<const uint8_t*>(r.get_cache_page_addr(slot));
-            for (uint32_t o = lane * 16; o < r.cache.page_size; o += 32 * 16 * 4) {
-                uint4 v[4];
+            };
+            if (n_pieces > 0) issue(0);
+            if (n_pieces > 1) issue(1);
+            for (uint32_t q = 0; q < n_pieces; q++) {
+                const uint32_t st = q & 1u;
+                uint32_t polls = 0;
+                while (!mbar_test(bar0 + st * 8, (parity >> st) & 1u)) {
+                    if (((++polls) & 0xfffffu) == 0u) {            /* bounded: give up after ~1e8 polls */
+                        if (polls > (1u << 27)) status_fail(r.cache.status, BAM_ETIMEDOUT, BAM_AT_TMA, q);
+                        if (status_bad(r.cache.status)) { failed = true; break; }
+                    }
+                }
+                parity ^= 1u << st;
+                const uint8_t* sm = bam_dyn_smem + (size_t)(wib * 2 + st) * BAM_EMU_STAGE_BYTES;
 #pragma unroll
-                for (int j = 0; j < 4; j++)
-                    if (o + j * 512 < r.cache.page_size) v[j] = *reinterpret_cast<const uint4*>(base + o + j * 512);
-#pragma unroll
-                for (int j = 0; j < 4; j++)
-                    if (o + j * 512 < r.cache.page_size)
-                        sum += (((uint64_t)v[j].y << 32) | v[j].x) + (((uint64_t)v[j].w << 32) | v[j].z);
+                for (uint32_t o = lane * 16; o < BAM_EMU_STAGE_BYTES; o += 512) {
+                    if (o < plen) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(sm + o);
+                        sum += (((uint64_t)v.y << 32) | v.x) + (((uint64_t)v.w << 32) | v.z);
+                    }
+                }
+                __syncwarp();                                      /* everyone has read the stage       */
+                if (q + 2 < n_pieces) issue(q + 2);
             }
-            __syncwarp();
-            if (lane == 0) r.release_page(slot, 1);
+            if ((ok >> lane) & 1u) r.release_page(slot, 1);
         }
         __syncwarp();
         warp_sum_to(sum, sum_out);
@@ -632,6 +668,17 @@ extern "C" int bam_cache_invalidate(bam_cache_t pc)
     CK(cudaSetDevice(pc->ctrl->device));
     CK(cudaDeviceSynchronize());
     return cache_reset_device(pc);
+}
+
+extern "C" int bam_cache_invalidate_async(bam_cache_t pc, void* stream)
+{
+    if (!pc) return BAM_EINVAL;
+    CK(cudaSetDevice(pc->ctrl->device));
+    cudaStream_t s = (cudaStream_t)stream;
+    k_init_cache<<<pc->ctrl->num_sms * 4, 256, 0, s>>>(pc->d.slots, pc->d.n_slots, pc->d.table, pc->n_buckets * BAM_BUCKET_WORDS);
+    CK(cudaGetLastError());
+    CK(cudaMemsetAsync(pc->d.clock_hand, 0, 8, s));
+    return BAM_OK;
 }
 
 extern "C" int bam_cache_audit(bam_cache_t pc, uint64_t* violations)

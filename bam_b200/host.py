@@ -139,6 +139,9 @@ class PageCache:
     def invalidate(self):
         check(self.lib.bam_cache_invalidate(self.h), "bam_cache_invalidate")
 
+    def invalidate_async(self, stream=None):
+        check(self.lib.bam_cache_invalidate_async(self.h, _ptr(stream)), "bam_cache_invalidate_async")
+
     def audit(self):
         v = C.c_uint64()
         check(self.lib.bam_cache_audit(self.h, C.byref(v)), "bam_cache_audit")

@@ -96,6 +96,8 @@ int bam_cache_destroy(bam_cache_t pc);
 int bam_cache_stats(bam_cache_t pc, bam_cache_stats_t* out, int reset);
 /* Drop every cached page (all slots free, table empty). */
 int bam_cache_invalidate(bam_cache_t pc);
+/* The same, enqueued on `stream` without synchronising; the counters are left alone. */
+int bam_cache_invalidate_async(bam_cache_t pc, void* stream);
 /* Audit after a launch: no pins left, no BUSY bits, every VALID slot is found through the page
  * table, every table entry points at a slot with a matching tag.  *violations = 0 when clean. */
 int bam_cache_audit(bam_cache_t pc, uint64_t* violations);
