@@ -44,3 +44,22 @@ def build_library(force=False, verbose=False):
     if res.returncode != 0:
         raise RuntimeError("nvcc failed building libbam_b200.so")
     return LIB
+
+
+def build_cpp_bench(force=False):
+    """Compile tests/cpp/array_bench.cu (the reference's array benchmark written against the drop-in
+    C++ headers) and link it against the in-tree library."""
+    src = os.path.join(ROOT, "tests", "cpp", "array_bench.cu")
+    exe = os.path.join(ROOT, "tests", "cpp", "array_bench")
+    build_library()
+    if not force and not _newer_than(exe, _deps() + [src, LIB]):
+        return exe
+    cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+           "-I" + os.path.join(ROOT, "include"), "-o", exe, src, "-L" + HERE, "-lbam_b200",
+           "-Xlinker", "-rpath", "-Xlinker", HERE]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        print(res.stdout)
+        print(res.stderr)
+        raise RuntimeError("nvcc failed building tests/cpp/array_bench")
+    return exe

@@ -6,9 +6,8 @@
 
 #include "bam/abi_types.h"
 #include "bam/array.cuh"
+#include "bam/launch.cuh"
 
-#define BAM_THREADS 256               /* threads per block of every fused launch            */
-#define BAM_MIN_BLOCKS 3              /* resident blocks per SM the kernels are compiled for */
 #define BAM_DEFAULT_CTRL_BLOCKS 48    /* controller blocks unless configured otherwise       */
 #define BAM_DB_STRIDE_WORDS 8         /* doorbell stride: 32 bytes, one sector per register   */
 

@@ -109,7 +109,34 @@ typedef struct {
     nvm_queue_t cq;
 } QueuePair;
 
-/* Device-side view of one controller (what kernels need to pick a queue and count I/O). */
+/* One controller.  The leading members are what kernels use to pick a queue and count I/O (the
+ * copy in device memory, Controller::d_ctrl_ptr, holds only those); the trailing members belong
+ * to the host object.  In C++ the struct also carries the reference's constructor
+ * Controller(path, nvmNamespace, cudaDevice, queueDepth, numQueues) (include/ctrl.h:148 there),
+ * defined in this library's ctrl.h on top of the C ABI. */
+#ifdef __cplusplus
+struct bam_ctrl;
+struct Controller {
+    uint64_t access_counter;
+    uint64_t queue_counter;
+    QueuePair* d_qps;
+    uint32_t n_qps;
+    uint32_t page_size;
+    uint32_t blk_size, blk_size_log;
+    bam_status_t* status;
+    /* host side */
+    bam_ctrl* h;
+    void* d_ctrl_ptr;
+    uint32_t deviceId;
+    uint32_t reserved_;
+
+    Controller() = default;
+    inline Controller(const char* path, uint32_t nvmNamespace, uint32_t cudaDevice, uint64_t queueDepth,
+                      uint64_t numQueues, uint64_t store_bytes = 0);
+    inline void close();
+    inline void print_reset_stats();
+};
+#else
 typedef struct {
     uint64_t access_counter;
     uint64_t queue_counter;
@@ -118,7 +145,12 @@ typedef struct {
     uint32_t page_size;
     uint32_t blk_size, blk_size_log;
     bam_status_t* status;
+    void* h;
+    void* d_ctrl_ptr;
+    uint32_t deviceId;
+    uint32_t reserved_;
 } Controller;
+#endif
 
 /* ---- emulated NVMe controller (device-resident command processor) ----------------------- */
 typedef struct BAM_ALIGNAS(64) {

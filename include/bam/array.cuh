@@ -51,6 +51,25 @@ struct range_d_t {
     BAM_DEV void release_page(uint32_t slot, uint32_t cnt = 1) const { cache_release(cache, slot, cnt); }
 };
 
+/* Pin pages for a warp: every lane of `mask` calls it; each lane with want == true gets the slot
+ * of its `page` pinned `cnt` times (one leader may ask on behalf of a group).  The pages are kept
+ * by the caller afterwards, so the round is all-or-nothing: if any lane could not claim a slot,
+ * the lanes that did get theirs give them back before the warp backs off and tries again --
+ * otherwise warps would sit on partial sets of a nearly full cache and wait for each other. */
+template <typename T>
+BAM_DEV uint32_t range_pin_page(const range_d_t<T>& r, uint32_t mask, bool want, uint64_t page, uint32_t cnt,
+                                uint32_t queue, bool write = false)
+{
+    spin_t sp;
+    for (;;) {
+        const uint32_t slot = r.acquire_page_warp(mask, want, page, cnt, write, queue);
+        if (!__any_sync(mask, want && slot == BAM_SLOT_RETRY)) return slot;
+        if (want && slot <= BAM_SLOT_MAX) r.release_page(slot, cnt);
+        if (__any_sync(mask, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) return BAM_SLOT_ERR;
+        __nanosleep(((get_smid() * 37u + (threadIdx.x >> 5) * 101u) & 255u) * 8u);     /* de-synchronise the warps */
+    }
+}
+
 template <typename T>
 struct array_d_t {
     uint64_t n_elems;
@@ -75,14 +94,7 @@ struct array_d_t {
         leader = __ffs(eq_mask) - 1;
         cnt = __popc(eq_mask);
         const uint32_t dirty = __ballot_sync(eq_mask, write) != 0u;
-        spin_t sp;
-        bool pending = true;
-        for (;;) {      /* the caller keeps the page, so a lane that cannot get a slot simply asks again */
-            const uint32_t s = r.acquire_page_warp(mask, pending && lane_id() == leader, page, cnt, dirty, default_queue());
-            if (pending && s != BAM_SLOT_RETRY) { slot = s; pending = false; }
-            if (!__any_sync(mask, pending)) break;
-            if (__any_sync(mask, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) { if (pending) slot = BAM_SLOT_ERR; break; }
-        }
+        slot = range_pin_page(r, mask, lane_id() == leader, page, cnt, default_queue(), dirty);
         slot = __shfl_sync(eq_mask, slot, leader);
     }
 
@@ -150,24 +162,6 @@ BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
     return v;
 }
 
-/* Pin one page for a whole warp-group: every lane of `mask` calls it; the lanes with want == true
- * get the slot of `page` pinned `cnt` times (normally one leader asks on behalf of a group).
- * Nothing is held while it retries, so it may be used even when the cache is nearly all pinned. */
-template <typename T>
-BAM_DEV uint32_t range_pin_page(const range_d_t<T>& r, uint32_t mask, bool want, uint64_t page, uint32_t cnt, uint32_t queue)
-{
-    uint32_t slot = BAM_SLOT_ERR;
-    bool pending = want;
-    spin_t sp;
-    for (;;) {
-        const uint32_t s = r.acquire_page_warp(mask, pending, page, cnt, false, queue);
-        if (pending && s != BAM_SLOT_RETRY) { slot = s; pending = false; }
-        if (!__any_sync(mask, pending)) break;
-        if (__any_sync(mask, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) break;
-    }
-    return slot;
-}
-
 /* Per-thread cursor that keeps the page of its last access pinned, so a run of accesses to one
  * page costs one pin/unpin (reference: bam_ptr, page_cache.h:415-485).  Reads never mark the
  * page dirty (the reference's non-const operator[] does, :478-484, which causes spurious
@@ -205,17 +199,7 @@ struct bam_ptr {
         const uint64_t key = valid ? range->get_global_address(page) : ~0ull;
         const uint32_t eq = __match_any_sync(mask, key);
         const uint32_t leader = __ffs(eq) - 1;
-        {
-            spin_t sp;
-            bool pending = valid;
-            slot = BAM_SLOT_ERR;
-            for (;;) {   /* the old page was released by fini(), so retrying holds nothing */
-                const uint32_t s = range->acquire_page_warp(mask, pending && lane_id() == leader, valid ? page : 0, __popc(eq), false, default_queue());
-                if (pending && s != BAM_SLOT_RETRY) { slot = s; pending = false; }
-                if (!__any_sync(mask, pending)) break;
-                if (__any_sync(mask, sp.expired(range->cache.status, BAM_AT_FIND_SLOT, page))) break;
-            }
-        }
+        slot = range_pin_page(*range, mask, valid && lane_id() == leader, valid ? page : 0, __popc(eq), default_queue());
         slot = __shfl_sync(eq, slot, leader);
         if (!valid) { status_fail(array->d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i); slot = BAM_SLOT_ERR; }
         if (slot == BAM_SLOT_ERR) { addr = nullptr; return nullptr; }
