@@ -55,8 +55,9 @@ SIGNATURES = {
     "bam_launch_block_read": (ci, [vp, u64, vp, u64, vp, vp, vp]),
     "bam_launch_array_read": (ci, [vp, u64, u64, vp, u64, vp, vp]),
     "bam_launch_page_scan": (ci, [vp, u64, vp, u64, vp, vp]),
-    "bam_launch_bfs_level": (ci, [vp, vp, u64, u64, u32, vp, vp, vp, vp]),
-    "bam_launch_cc_sweep": (ci, [vp, vp, u64, u64, vp, vp, vp, vp, vp, vp]),
+    "bam_launch_bfs_level": (ci, [vp, vp, u64, u64, u64, u32, vp, vp, vp, vp, u64, vp]),
+    "bam_graph_scratch_bytes": (u64, [u64]),
+    "bam_launch_cc_sweep": (ci, [vp, vp, u64, u64, u64, vp, vp, vp, vp, vp, vp, u64, vp]),
     "bam_bfs_run": (ci, [vp, vp, u64, u64, vp, C.POINTER(u32), C.POINTER(u64)]),
     "bam_cc_run": (ci, [vp, vp, u64, vp, C.POINTER(u32), C.POINTER(u64)]),
     "bam_gen_rmat_keys": (ci, [vp, u64, u64, u64, u32, u32, u32, u32, vp]),

@@ -16,6 +16,8 @@
  */
 #include <cuda_runtime.h>
 
+#include <cstddef>
+
 #include "bam_abi.h"
 #include "bam_synth.h"
 #include "bam_fused.cuh"
@@ -23,6 +25,20 @@
 using namespace bam;
 
 #define BAM_BFS_INF 0xffffffffu
+
+/* ---- scratch of one level / sweep: heavy adjacency lists split into work items ------------------
+ * R-MAT degrees are heavily skewed; a hub's list of 10^5 edges walked by one warp page after page
+ * would serialise hundreds of page reads.  Lists longer than BAM_HEAVY_EDGES are cut into items of
+ * BAM_ITEM_EDGES edges that every warp consumes after its own vertices (no grid barrier: a warp
+ * draws a ticket and waits for that item to be published, or for all producers to be done). */
+#define BAM_HEAVY_EDGES 2048u
+#define BAM_ITEM_EDGES 1024u
+
+struct graph_item_t { uint64_t u; uint64_t begin; uint64_t end; };   /* end != 0 marks the item ready */
+struct graph_scratch_t {
+    uint32_t n_items, cursor, producers_done, capacity;
+    graph_item_t items[1];
+};
 
 /* Pin the page of `r` holding element index i for the whole warp (lane 0 asks). */
 BAM_DEV const uint64_t* warp_page_of(const range_d_t<uint64_t>& r, uint64_t i, uint32_t queue, uint32_t& slot)
@@ -34,24 +50,138 @@ BAM_DEV const uint64_t* warp_page_of(const range_d_t<uint64_t>& r, uint64_t i, u
     return reinterpret_cast<const uint64_t*>(r.get_cache_page_addr(slot));
 }
 
-/* offsets[v] and offsets[v+1] for the 32 vertices v0+lane of a chunk (active lanes only) */
-BAM_DEV void chunk_offsets(const range_d_t<uint64_t>& off, uint64_t v, bool act, uint32_t queue, uint64_t& s, uint64_t& e)
+/* The whole warp walks cols[begin, end) page by page and calls fn(neighbour) per edge. */
+template <class EdgeFn>
+BAM_DEV bool warp_walk_edges(const range_d_t<uint64_t>& col, uint64_t begin, uint64_t end, uint32_t queue, EdgeFn fn)
 {
-    s = e = 0;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t epp_log = col.cache.page_size_log - 3;
+    for (uint64_t i = begin; i < end;) {
+        uint64_t pend = ((i >> epp_log) + 1) << epp_log;               /* first index of the next page */
+        if (pend > end) pend = end;
+        uint32_t slot;
+        const uint64_t* base = warp_page_of(col, i, queue, slot);
+        if (!base) return false;
+        const uint64_t page_first = (i >> epp_log) << epp_log;
+        for (uint64_t j = i + lane; j < pend; j += 32) fn(base[j - page_first]);
+        __syncwarp();
+        if (lane == 0) col.release_page(slot, 1);
+        i = pend;
+    }
+    return true;
+}
+
+/* One chunk of 32 consecutive local vertices (lane <-> vertex v, act = vertex is in the frontier).
+ * Offsets come through the cache as one or two coalesced page reads.  The FIRST edge page of every
+ * active vertex is pinned in one cooperative call (lanes that share a page share a pin, and all
+ * missing pages are in flight together); lists that continue on further pages are walked page by
+ * page; heavy lists become work items.  fn(src_lane, neighbour) is called for every edge. */
+template <class EdgeFn>
+BAM_DEV bool chunk_visit(const range_d_t<uint64_t>& off, const range_d_t<uint64_t>& col, uint64_t v, uint64_t u_global,
+                         bool act, uint32_t queue, graph_scratch_t* scratch, uint64_t& edges, EdgeFn fn)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t epp_log = col.cache.page_size_log - 3;
+    uint64_t s = 0, e = 0;
     if (act) {
         s = range_read<uint64_t>(off, v, queue);
         e = range_read<uint64_t>(off, v + 1, queue);
     }
     __syncwarp();
+    const uint64_t deg = e - s;
+    edges += deg;
+    bool heavy = act && scratch && deg > BAM_HEAVY_EDGES;
+    if (heavy) {
+        const uint32_t n_it = (uint32_t)((deg + BAM_ITEM_EDGES - 1) / BAM_ITEM_EDGES);
+        const uint32_t base = atom_add_relaxed(&scratch->n_items, n_it);
+        /* publish what fits (the scratch is sized so that everything does); anything beyond the
+         * capacity is walked by this warp below, and tickets past the capacity are never waited on */
+        const uint32_t fit = base >= scratch->capacity ? 0u : (scratch->capacity - base < n_it ? scratch->capacity - base : n_it);
+        for (uint32_t k = 0; k < fit; k++) {
+            graph_item_t* it = &scratch->items[base + k];
+            const uint64_t b0 = s + (uint64_t)k * BAM_ITEM_EDGES;
+            it->u = u_global;
+            it->begin = b0;
+            __threadfence();
+            st_release_gpu(&it->end, b0 + BAM_ITEM_EDGES < e ? b0 + BAM_ITEM_EDGES : e);
+        }
+        if (fit < n_it) { s += (uint64_t)fit * BAM_ITEM_EDGES; heavy = false; }
+    }
+    const bool light = act && !heavy && e > s;
+    const uint32_t lm = __ballot_sync(0xffffffffu, light);
+    if (lm == 0) return true;
+    const uint64_t page0 = s >> epp_log;
+    const uint32_t eq = __match_any_sync(0xffffffffu, light ? page0 : (~0ull - lane));
+    const uint32_t leader = __ffs(eq) - 1;
+    uint32_t slot = range_pin_page(col, 0xffffffffu, light && lane == leader, page0, (uint32_t)__popc(eq), queue);
+    slot = __shfl_sync(0xffffffffu, slot, leader);
+    if (__any_sync(0xffffffffu, light && slot == BAM_SLOT_ERR)) return false;
+    bool ok = true;
+    uint32_t am = lm;
+    while (am) {
+        const int src = __ffs(am) - 1;
+        am &= am - 1;
+        const uint64_t vs = __shfl_sync(0xffffffffu, s, src);
+        const uint64_t ve = __shfl_sync(0xffffffffu, e, src);
+        const uint32_t sl = __shfl_sync(0xffffffffu, slot, src);
+        const uint64_t page_first = (vs >> epp_log) << epp_log;
+        uint64_t first_end = page_first + (1ull << epp_log);
+        if (first_end > ve) first_end = ve;
+        const uint64_t* base = reinterpret_cast<const uint64_t*>(col.get_cache_page_addr(sl));
+        for (uint64_t j = vs + lane; j < first_end; j += 32) fn(src, base[j - page_first]);
+        if (first_end < ve) ok = warp_walk_edges(col, first_end, ve, queue, [&](uint64_t nb) { fn(src, nb); }) && ok;
+        if (!ok) break;
+    }
+    __syncwarp();
+    if (light && lane == leader && slot != BAM_SLOT_ERR) col.release_page(slot, (uint32_t)__popc(eq));
+    return ok;
+}
+
+/* After its own chunks a warp helps with the heavy items.  fn(u_global, neighbour) per edge. */
+template <class EdgeFn>
+BAM_DEV void consume_heavy_items(const range_d_t<uint64_t>& col, graph_scratch_t* scratch, uint32_t n_warps_total,
+                                 uint32_t queue, EdgeFn fn)
+{
+    if (!scratch) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    if (lane == 0) { __threadfence(); red_add_release(&scratch->producers_done, 1u); }
+    __syncwarp();
+    for (;;) {
+        uint32_t idx = 0;
+        if (lane == 0) idx = atom_add_relaxed(&scratch->cursor, 1u);
+        idx = __shfl_sync(0xffffffffu, idx, 0);
+        if (idx >= scratch->capacity) return;
+        graph_item_t* it = &scratch->items[idx];
+        uint64_t end = 0;
+        spin_t sp;
+        for (;;) {                                         /* the item is published, or it will never be */
+            uint32_t done = 0;
+            if (lane == 0) {
+                end = ld_acquire_gpu(&it->end);
+                if (end == 0 && ld_acquire_gpu(&scratch->producers_done) == n_warps_total &&
+                    ld_acquire_gpu(&scratch->n_items) <= idx) done = 1;
+                if (end == 0 && !done) end = ld_acquire_gpu(&it->end);
+            }
+            end = __shfl_sync(0xffffffffu, end, 0);
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (end != 0) break;
+            if (done) return;
+            if (__any_sync(0xffffffffu, sp.expired(col.cache.status, BAM_AT_PAGE_BUSY, idx))) return;
+        }
+        const uint64_t u = it->u, begin = it->begin;
+        if (!warp_walk_edges(col, begin, end, queue, [&](uint64_t nb) { fn(u, nb); })) return;
+    }
 }
 
 struct BfsLevelWork {
     range_d_t<uint64_t> off, col;
     uint64_t v_begin, v_end;
+    uint64_t v_base;            /* global id of local vertex 0 (labels are indexed by global id) */
     uint32_t level;
     uint32_t* label;
     uint32_t* changed;
     uint64_t* scanned;
+    graph_scratch_t* scratch;
 
     __device__ void operator()(uint32_t vb, uint32_t nvb) const
     {
@@ -60,39 +190,20 @@ struct BfsLevelWork {
         const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
         const uint64_t nwarps = (uint64_t)nvb * wpb;
         const uint32_t queue = (uint32_t)warp;
-        const uint32_t epp_log = col.cache.page_size_log - 3;
         uint64_t edges = 0;
         bool ch = false;
+        uint32_t* lab = label;
+        const uint32_t next_level = level + 1;
+        auto relax = [&](uint64_t nb) {
+            if (lab[nb] == BAM_BFS_INF) { lab[nb] = next_level; ch = true; }
+        };
         for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
             const uint64_t v = c0 + lane;
-            const bool act = v < v_end && label[v] == level;
-            uint32_t am = __ballot_sync(0xffffffffu, act);
-            if (am == 0) continue;
-            uint64_t s, e;
-            chunk_offsets(off, v, act, queue, s, e);
-            edges += e - s;
-            while (am) {
-                const int src = __ffs(am) - 1;
-                am &= am - 1;
-                const uint64_t vs = __shfl_sync(0xffffffffu, s, src);
-                const uint64_t ve = __shfl_sync(0xffffffffu, e, src);
-                for (uint64_t i = vs; i < ve;) {
-                    uint64_t pend = ((i >> epp_log) + 1) << epp_log;       /* first index of the next page */
-                    if (pend > ve) pend = ve;
-                    uint32_t slot;
-                    const uint64_t* base = warp_page_of(col, i, queue, slot);
-                    if (!base) { i = ve; am = 0; break; }
-                    const uint64_t page_first = (i >> epp_log) << epp_log;
-                    for (uint64_t j = i + lane; j < pend; j += 32) {
-                        const uint64_t nb = base[j - page_first];
-                        if (label[nb] == BAM_BFS_INF) { label[nb] = level + 1; ch = true; }
-                    }
-                    __syncwarp();
-                    if (lane == 0) col.release_page(slot, 1);
-                    i = pend;
-                }
-            }
+            const bool act = v < v_end && label[v_base + v] == level;
+            if (__ballot_sync(0xffffffffu, act) == 0) continue;
+            if (!chunk_visit(off, col, v, v_base + v, act, queue, scratch, edges, [&](int, uint64_t nb) { relax(nb); })) break;
         }
+        consume_heavy_items(col, scratch, (uint32_t)nwarps, queue, [&](uint64_t, uint64_t nb) { relax(nb); });
         __syncwarp();
         if (__any_sync(0xffffffffu, ch) && lane == 0) *changed = 1u;
         warp_sum_to(edges, scanned);
@@ -102,11 +213,13 @@ struct BfsLevelWork {
 struct CcSweepWork {
     range_d_t<uint64_t> off, col;
     uint64_t v_begin, v_end;
+    uint64_t v_base;
     unsigned long long* comp;
     const uint8_t* curr_visit;
     uint8_t* next_visit;
     uint32_t* changed;
     uint64_t* scanned;
+    graph_scratch_t* scratch;
 
     __device__ void operator()(uint32_t vb, uint32_t nvb) const
     {
@@ -115,44 +228,25 @@ struct CcSweepWork {
         const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
         const uint64_t nwarps = (uint64_t)nvb * wpb;
         const uint32_t queue = (uint32_t)warp;
-        const uint32_t epp_log = col.cache.page_size_log - 3;
         uint64_t edges = 0;
         bool ch = false;
+        unsigned long long* cp = comp;
+        uint8_t* nv = next_visit;
+        /* the relaxation of cc_compute: the larger label takes the smaller one */
+        auto relax = [&](uint64_t u, uint64_t nb) {
+            const unsigned long long cu = *reinterpret_cast<volatile unsigned long long*>(&cp[u]);
+            const unsigned long long cn = *reinterpret_cast<volatile unsigned long long*>(&cp[nb]);
+            if (cu < cn) { atomicMin(&cp[nb], cu); nv[nb] = 1; ch = true; }
+            else if (cn < cu) { atomicMin(&cp[u], cn); nv[u] = 1; ch = true; }
+        };
         for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
             const uint64_t v = c0 + lane;
-            const bool act = v < v_end && curr_visit[v] != 0;
-            uint32_t am = __ballot_sync(0xffffffffu, act);
-            if (am == 0) continue;
-            uint64_t s, e;
-            chunk_offsets(off, v, act, queue, s, e);
-            edges += e - s;
-            while (am) {
-                const int src = __ffs(am) - 1;
-                am &= am - 1;
-                const uint64_t vs = __shfl_sync(0xffffffffu, s, src);
-                const uint64_t ve = __shfl_sync(0xffffffffu, e, src);
-                const uint64_t u = c0 + src;
-                for (uint64_t i = vs; i < ve;) {
-                    uint64_t pend = ((i >> epp_log) + 1) << epp_log;
-                    if (pend > ve) pend = ve;
-                    uint32_t slot;
-                    const uint64_t* base = warp_page_of(col, i, queue, slot);
-                    if (!base) { i = ve; am = 0; break; }
-                    const uint64_t page_first = (i >> epp_log) << epp_log;
-                    for (uint64_t j = i + lane; j < pend; j += 32) {
-                        const uint64_t nb = base[j - page_first];
-                        /* the relaxation of cc_compute: the larger label takes the smaller one */
-                        const unsigned long long cu = *reinterpret_cast<volatile unsigned long long*>(&comp[u]);
-                        const unsigned long long cn = *reinterpret_cast<volatile unsigned long long*>(&comp[nb]);
-                        if (cu < cn) { atomicMin(&comp[nb], cu); next_visit[nb] = 1; ch = true; }
-                        else if (cn < cu) { atomicMin(&comp[u], cn); next_visit[u] = 1; ch = true; }
-                    }
-                    __syncwarp();
-                    if (lane == 0) col.release_page(slot, 1);
-                    i = pend;
-                }
-            }
+            const bool act = v < v_end && curr_visit[v_base + v] != 0;
+            if (__ballot_sync(0xffffffffu, act) == 0) continue;
+            const uint64_t ubase = v_base + c0;
+            if (!chunk_visit(off, col, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb) { relax(ubase + src, nb); })) break;
         }
+        consume_heavy_items(col, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb) { relax(u, nb); });
         __syncwarp();
         if (__any_sync(0xffffffffu, ch) && lane == 0) *changed = 1u;
         warp_sum_to(edges, scanned);
@@ -185,6 +279,25 @@ __global__ void k_rmat_keys(uint64_t* keys, uint64_t e_begin, uint64_t e_end, ui
     }
 }
 
+/* Clear the level's scratch (header and item flags) on the stream and set its capacity. */
+static int prepare_scratch(void* scratch_dev, uint64_t scratch_bytes, cudaStream_t s, graph_scratch_t** out)
+{
+    *out = nullptr;
+    if (!scratch_dev) return BAM_OK;
+    if (scratch_bytes < sizeof(graph_scratch_t) + sizeof(graph_item_t)) return BAM_EINVAL;
+    const uint64_t cap = (scratch_bytes - offsetof(graph_scratch_t, items)) / sizeof(graph_item_t);
+    CK(cudaMemsetAsync(scratch_dev, 0, scratch_bytes, s));
+    const uint32_t cap32 = cap > 0x7fffffffu ? 0x7fffffffu : (uint32_t)cap;
+    CK(cudaMemcpyAsync((uint8_t*)scratch_dev + offsetof(graph_scratch_t, capacity), &cap32, 4, cudaMemcpyHostToDevice, s));
+    *out = static_cast<graph_scratch_t*>(scratch_dev);
+    return BAM_OK;
+}
+
+extern "C" uint64_t bam_graph_scratch_bytes(uint64_t n_edges)
+{
+    return offsetof(graph_scratch_t, items) + (n_edges / BAM_ITEM_EDGES + n_edges / BAM_HEAVY_EDGES + 1024) * sizeof(graph_item_t);
+}
+
 static int check_graph_args(bam_array_t offsets, bam_array_t cols)
 {
     if (!offsets || !cols) return BAM_EINVAL;
@@ -193,8 +306,9 @@ static int check_graph_args(bam_array_t offsets, bam_array_t cols)
     return BAM_OK;
 }
 
-extern "C" int bam_launch_bfs_level(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint32_t level,
-                                    uint32_t* label_dev, uint32_t* changed_dev, uint64_t* scanned_dev, void* stream)
+extern "C" int bam_launch_bfs_level(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint64_t v_base,
+                                    uint32_t level, uint32_t* label_dev, uint32_t* changed_dev, uint64_t* scanned_dev,
+                                    void* scratch_dev, uint64_t scratch_bytes, void* stream)
 {
     int rc = check_graph_args(offsets, cols);
     if (rc) return rc;
@@ -202,14 +316,18 @@ extern "C" int bam_launch_bfs_level(bam_array_t offsets, bam_array_t cols, uint6
     bam_ctrl* c = offsets->pc->ctrl;
     CK(cudaSetDevice(c->device));
     BfsLevelWork w;
-    w.off = offsets->h_range; w.col = cols->h_range; w.v_begin = v_begin; w.v_end = v_end; w.level = level;
+    w.off = offsets->h_range; w.col = cols->h_range; w.v_begin = v_begin; w.v_end = v_end; w.v_base = v_base; w.level = level;
     w.label = label_dev; w.changed = changed_dev; w.scanned = scanned_dev;
+    w.scratch = nullptr;
+    rc = prepare_scratch(scratch_dev, scratch_bytes, (cudaStream_t)stream, &w.scratch);
+    if (rc) return rc;
     return launch_fused(c, w, (cudaStream_t)stream);
 }
 
-extern "C" int bam_launch_cc_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end,
+extern "C" int bam_launch_cc_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint64_t v_base,
                                    uint64_t* comp_dev, const uint8_t* curr_visit_dev, uint8_t* next_visit_dev,
-                                   uint32_t* changed_dev, uint64_t* scanned_dev, void* stream)
+                                   uint32_t* changed_dev, uint64_t* scanned_dev, void* scratch_dev, uint64_t scratch_bytes,
+                                   void* stream)
 {
     int rc = check_graph_args(offsets, cols);
     if (rc) return rc;
@@ -217,9 +335,12 @@ extern "C" int bam_launch_cc_sweep(bam_array_t offsets, bam_array_t cols, uint64
     bam_ctrl* c = offsets->pc->ctrl;
     CK(cudaSetDevice(c->device));
     CcSweepWork w;
-    w.off = offsets->h_range; w.col = cols->h_range; w.v_begin = v_begin; w.v_end = v_end;
+    w.off = offsets->h_range; w.col = cols->h_range; w.v_begin = v_begin; w.v_end = v_end; w.v_base = v_base;
     w.comp = reinterpret_cast<unsigned long long*>(comp_dev); w.curr_visit = curr_visit_dev; w.next_visit = next_visit_dev;
     w.changed = changed_dev; w.scanned = scanned_dev;
+    w.scratch = nullptr;
+    rc = prepare_scratch(scratch_dev, scratch_bytes, (cudaStream_t)stream, &w.scratch);
+    if (rc) return rc;
     return launch_fused(c, w, (cudaStream_t)stream);
 }
 
@@ -239,12 +360,15 @@ extern "C" int bam_bfs_run(bam_array_t offsets, bam_array_t cols, uint64_t n_ver
     cudaError_t e = cudaMalloc(&d_scanned, 8);
     if (e != cudaSuccess) { cudaFree(d_changed); g_last_cuda = e; return BAM_ENOMEM; }
     cudaMemset(d_scanned, 0, 8);
+    void* d_scratch = nullptr;
+    const uint64_t scratch_bytes = bam_graph_scratch_bytes(cols->n_elems);
+    if (cudaMalloc(&d_scratch, scratch_bytes) != cudaSuccess) { (void)cudaGetLastError(); d_scratch = nullptr; }
     k_bfs_init<<<c->num_sms * 4, 256>>>(label_dev, n_vertices, source);
     uint32_t level = 0;
     rc = BAM_OK;
     for (;; level++) {
         cudaMemsetAsync(d_changed, 0, 4, 0);
-        rc = bam_launch_bfs_level(offsets, cols, 0, n_vertices, level, label_dev, d_changed, d_scanned, nullptr);
+        rc = bam_launch_bfs_level(offsets, cols, 0, n_vertices, 0, level, label_dev, d_changed, d_scanned, d_scratch, d_scratch ? scratch_bytes : 0, nullptr);
         if (rc) break;
         uint32_t changed = 0;
         e = cudaMemcpy(&changed, d_changed, 4, cudaMemcpyDeviceToHost);
@@ -256,7 +380,7 @@ extern "C" int bam_bfs_run(bam_array_t offsets, bam_array_t cols, uint64_t n_ver
     }
     if (n_levels_out) *n_levels_out = level + 1;              /* levels 0..level hold vertices */
     if (edges_scanned_out) cudaMemcpy(edges_scanned_out, d_scanned, 8, cudaMemcpyDeviceToHost);
-    cudaFree(d_changed); cudaFree(d_scanned);
+    cudaFree(d_changed); cudaFree(d_scanned); cudaFree(d_scratch);
     return rc;
 }
 
@@ -276,6 +400,9 @@ extern "C" int bam_cc_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vert
     if (e == cudaSuccess) e = cudaMalloc(&d_visit, 2 * n_vertices);
     if (e != cudaSuccess) { cudaFree(d_changed); cudaFree(d_scanned); cudaFree(d_visit); g_last_cuda = e; (void)cudaGetLastError(); return BAM_ENOMEM; }
     cudaMemset(d_scanned, 0, 8);
+    void* d_scratch = nullptr;
+    const uint64_t scratch_bytes = bam_graph_scratch_bytes(cols->n_elems);
+    if (cudaMalloc(&d_scratch, scratch_bytes) != cudaSuccess) { (void)cudaGetLastError(); d_scratch = nullptr; }
     uint8_t* curr = d_visit;
     uint8_t* next = d_visit + n_vertices;
     k_cc_init<<<c->num_sms * 4, 256>>>(reinterpret_cast<unsigned long long*>(comp_dev), curr, next, n_vertices);
@@ -283,7 +410,7 @@ extern "C" int bam_cc_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vert
     rc = BAM_OK;
     for (;;) {
         cudaMemsetAsync(d_changed, 0, 4, 0);
-        rc = bam_launch_cc_sweep(offsets, cols, 0, n_vertices, comp_dev, curr, next, d_changed, d_scanned, nullptr);
+        rc = bam_launch_cc_sweep(offsets, cols, 0, n_vertices, 0, comp_dev, curr, next, d_changed, d_scanned, d_scratch, d_scratch ? scratch_bytes : 0, nullptr);
         if (rc) break;
         sweeps++;
         uint32_t changed = 0;
@@ -298,7 +425,7 @@ extern "C" int bam_cc_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vert
     }
     if (n_sweeps_out) *n_sweeps_out = sweeps;
     if (edges_scanned_out) cudaMemcpy(edges_scanned_out, d_scanned, 8, cudaMemcpyDeviceToHost);
-    cudaFree(d_changed); cudaFree(d_scanned); cudaFree(d_visit);
+    cudaFree(d_changed); cudaFree(d_scanned); cudaFree(d_visit); cudaFree(d_scratch);
     return rc;
 }
 

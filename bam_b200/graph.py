@@ -70,6 +70,9 @@ class CsrGraph:
         self.offsets = Array(self.cache, self.n + 1, 8, 0)
         self.cols = Array(self.cache, max(1, self.m), 8, self.off_bytes)
         self.device = cuda_device
+        # per-level scratch for the work items of hub vertices
+        self.scratch_bytes = lib.bam_graph_scratch_bytes(max(1, self.m))
+        self.scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=f"cuda:{cuda_device}")
 
     def close(self):
         self.cols.close(); self.offsets.close(); self.cache.close(); self.ctrl.close()
@@ -92,11 +95,121 @@ class CsrGraph:
               "bam_cc_run")
         return comp, ns.value, sc.value
 
-    def bfs_level(self, v_begin, v_end, level, label, changed, scanned=None, stream=None):
-        check(self.ctrl.lib.bam_launch_bfs_level(self.offsets.h, self.cols.h, v_begin, v_end, level, _ptr(label),
-                                                 _ptr(changed), _ptr(scanned), _ptr(stream)), "bam_launch_bfs_level")
+    def bfs_level(self, v_begin, v_end, level, label, changed, scanned=None, v_base=0, stream=None):
+        check(self.ctrl.lib.bam_launch_bfs_level(self.offsets.h, self.cols.h, v_begin, v_end, v_base, level, _ptr(label),
+                                                 _ptr(changed), _ptr(scanned), _ptr(self.scratch), self.scratch_bytes,
+                                                 _ptr(stream)), "bam_launch_bfs_level")
 
-    def cc_sweep(self, v_begin, v_end, comp, curr_visit, next_visit, changed, scanned=None, stream=None):
-        check(self.ctrl.lib.bam_launch_cc_sweep(self.offsets.h, self.cols.h, v_begin, v_end, _ptr(comp), _ptr(curr_visit),
-                                                _ptr(next_visit), _ptr(changed), _ptr(scanned), _ptr(stream)),
-              "bam_launch_cc_sweep")
+    def cc_sweep(self, v_begin, v_end, comp, curr_visit, next_visit, changed, scanned=None, v_base=0, stream=None):
+        check(self.ctrl.lib.bam_launch_cc_sweep(self.offsets.h, self.cols.h, v_begin, v_end, v_base, _ptr(comp),
+                                                _ptr(curr_visit), _ptr(next_visit), _ptr(changed), _ptr(scanned),
+                                                _ptr(self.scratch), self.scratch_bytes, _ptr(stream)), "bam_launch_cc_sweep")
+
+
+# ---- multi-GPU traversals: vertex-range sharding, replicated labels, all-gather exchange -------------
+
+def shard_vertices(n, world_size, rank):
+    """Contiguous vertex range [v0, v1) of `rank`."""
+    base, rem = divmod(n, world_size)
+    v0 = rank * base + min(rank, rem)
+    return v0, v0 + base + (1 if rank < rem else 0)
+
+
+def _all_gather_ragged(t, group=None):
+    """All-gather 1-D tensors of different lengths (counts first, then padded payloads).
+    Returns the concatenation over ranks, in rank order."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    cnt = torch.tensor([t.numel()], dtype=torch.int64, device=t.device)
+    cnts = [torch.zeros_like(cnt) for _ in range(world)]
+    dist.all_gather(cnts, cnt, group=group)
+    cnts = [int(c.item()) for c in cnts]
+    mx = max(cnts)
+    if mx == 0:
+        return t[:0]
+    send = torch.zeros(mx, dtype=t.dtype, device=t.device)       # the compaction result goes into the send buffer
+    send[:t.numel()] = t
+    recv = [torch.empty(mx, dtype=t.dtype, device=t.device) for _ in range(world)]
+    dist.all_gather(recv, send, group=group)
+    return torch.cat([r[:c] for r, c in zip(recv, cnts)])
+
+
+def exchange_bfs_frontier(label, level, group=None):
+    """After a BFS level: share the vertices this rank labelled level+1 and apply everybody's.
+    `label` is the replicated int32 view of the u32 labels.  Returns the size of the new frontier
+    over all ranks (0 = the traversal is finished)."""
+    import torch
+    mine = torch.nonzero(label == level + 1).flatten()
+    everyone = _all_gather_ragged(mine, group)
+    if everyone.numel():
+        label[everyone] = level + 1              # first-writer rule is order independent: same value
+    return int(everyone.numel())
+
+
+def exchange_cc_changes(comp, prev, next_visit, group=None):
+    """After a CC sweep: share (vertex, label) of every label this rank lowered, apply everybody's with
+    min, and flag the changed vertices for their owners' next sweep.  Returns the number of changes."""
+    import torch
+    idx = torch.nonzero(comp != prev).flatten()
+    vals = comp[idx]
+    all_idx = _all_gather_ragged(idx, group)
+    all_vals = _all_gather_ragged(vals, group)
+    if all_idx.numel():
+        comp.scatter_reduce_(0, all_idx, all_vals, reduce="amin", include_self=True)
+        next_visit[all_idx] = 1
+    return int(all_idx.numel())
+
+
+class DistCsrGraph:
+    """One rank's shard (a contiguous vertex range and its adjacency lists) of a CSR graph; BFS and
+    CC run level by level with the frontier / the changed labels exchanged by all-gather."""
+
+    def __init__(self, offsets, cols, rank, world_size, cache_pages, cuda_device=0, group=None, **kw):
+        self.n = offsets.numel() - 1
+        self.rank, self.world, self.group = rank, world_size, group
+        self.v0, self.v1 = shard_vertices(self.n, world_size, rank)
+        e0, e1 = int(offsets[self.v0].item()), int(offsets[self.v1].item())
+        loc_off = (offsets[self.v0:self.v1 + 1] - e0).contiguous()
+        loc_cols = cols[e0:e1].contiguous()
+        self.local = CsrGraph(loc_off, loc_cols, cache_pages, cuda_device=cuda_device, **kw)
+        self.device = cuda_device
+
+    def close(self):
+        self.local.close()
+
+    def bfs(self, source):
+        import torch
+        dev = f"cuda:{self.device}"
+        label = torch.full((self.n,), -1, dtype=torch.int32, device=dev)      # 0xFFFFFFFF
+        label[source] = 0
+        changed = torch.zeros(1, dtype=torch.int32, device=dev)
+        scanned = torch.zeros(1, dtype=torch.int64, device=dev)
+        level = 0
+        while True:
+            self.local.bfs_level(0, self.v1 - self.v0, level, label, changed, scanned, v_base=self.v0)
+            self.local.ctrl.check_status()
+            if exchange_bfs_frontier(label, level, self.group) == 0:
+                break
+            level += 1
+        return label, level + 1, int(scanned.item())
+
+    def cc(self):
+        import torch
+        dev = f"cuda:{self.device}"
+        comp = torch.arange(self.n, dtype=torch.int64, device=dev)
+        curr = torch.ones(self.n, dtype=torch.uint8, device=dev)
+        nxt = torch.zeros(self.n, dtype=torch.uint8, device=dev)
+        changed = torch.zeros(1, dtype=torch.int32, device=dev)
+        scanned = torch.zeros(1, dtype=torch.int64, device=dev)
+        sweeps = 0
+        while True:
+            prev = comp.clone()
+            self.local.cc_sweep(0, self.v1 - self.v0, comp, curr, nxt, changed, scanned, v_base=self.v0)
+            self.local.ctrl.check_status()
+            sweeps += 1
+            if exchange_cc_changes(comp, prev, nxt, self.group) == 0:
+                break
+            curr.zero_()
+            curr, nxt = nxt, curr
+        return comp, sweeps, int(scanned.item())

@@ -205,56 +205,82 @@ def verify_cc(off, cols, lab):
         bool((lab[srcs] == lab[cols]).all())
 
 
-def run_graph(args):
+def run_graph(args, rank, world, local_rank):
     """BFS (R-MAT scale 24, 4 GiB cache) or CC (scale 26, 8 GiB cache) over a CSR graph whose offsets
-    and edges are read only through bam::array; one step = one whole traversal."""
+    and edges are read only through bam::array; one step = one whole traversal from a cold cache.
+    With N > 1 ranks the graph is sharded by vertex range (each rank's rows in its own backing
+    store, cache and queues), labels are replicated and the frontier / changed labels are exchanged
+    by NCCL all-gather after every level."""
     import torch
+    import torch.distributed as dist
     import bam_b200
-    torch.cuda.set_device(0)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
     bfs = args.workload == "bfs"
     scale = args.scale or (24 if bfs else 26)
     cache_gib = args.cache_gib if args.cache_gib != 16.0 else (4.0 if bfs else 8.0)
     t0 = time.time()
-    off, cols = bam_b200.build_rmat_csr(1, scale, 16)
+    off, cols = bam_b200.build_rmat_csr(1, scale, 16, device=dev)
     n, m = off.numel() - 1, cols.numel()
     src = int(torch.argmax(off[1:] - off[:-1]).item())          # highest degree, lowest id on ties
-    gr = bam_b200.CsrGraph(off, cols, cache_pages=int(cache_gib * (1 << 30)) // PAGE, queue_depth=args.depth,
-                           num_queues=args.queues, ctrl_blocks=args.ctrl_blocks)
+    kw = dict(cache_pages=int(cache_gib * (1 << 30)) // PAGE, cuda_device=local_rank, queue_depth=args.depth,
+              num_queues=args.queues, ctrl_blocks=args.ctrl_blocks)
+    gr = bam_b200.DistCsrGraph(off, cols, rank, world, **kw) if world > 1 else bam_b200.CsrGraph(off, cols, **kw)
+    loc = gr.local if world > 1 else gr
     setup_s = time.time() - t0
     times, scanned, iters, ios = [], 0, 0, []
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(local_rank)
     out = None
     for s in range(args.warmup + args.steps):
-        if s == args.warmup:
+        if s == args.warmup and rank == 0:
             sampler.start()
-        gr.cache.stats(reset=True)
+        loc.cache.invalidate()
+        loc.cache.stats(reset=True)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
         a.record()
         out, iters, scanned = gr.bfs(src) if bfs else gr.cc()
         b.record()
         torch.cuda.synchronize()
-        gr.ctrl.check_status()
+        loc.ctrl.check_status()
         if s >= args.warmup:
-            times.append(a.elapsed_time(b)); ios.append(gr.cache.stats()["read_ios"])
-    clocks = sampler.stop()
+            times.append(a.elapsed_time(b)); ios.append(loc.cache.stats()["read_ios"])
+    clocks = sampler.stop() if rank == 0 else None
     ok = verify_bfs(off, cols, out, src) if bfs else verify_cc(off, cols, out)
-    ok = ok and gr.cache.audit() == 0
-    t = sum(times) * 1e-3
-    line = {"metric": "BFS GTEPS through bam::array" if bfs else "CC GTEPS through bam::array",
-            "value": scanned * len(times) / t / 1e9, "unit": "GTEPS", "n_gpus": 1, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1e3 * t / len(times), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-            "config": {"workload": f"{'BFS' if bfs else 'CC'} over R-MAT scale {scale} edge factor 16 (a,b,c = .57,.19,.19), "
-                                   "undirected, de-duplicated; u64 offsets and edges read through the page cache",
-                       "vertices": n, "directed_edges": m, "cache_gib": cache_gib, "queues": args.queues,
-                       "queue_depth": args.depth, "source": src,
-                       "l2": "graph (GiB) far larger than L2; no explicit flush"},
-            ("levels" if bfs else "sweeps"): iters, "edges_scanned_per_step": scanned,
-            "read_ios_per_step": float(np.mean(ios)), "link_gb_per_s": float(np.mean(ios)) * PAGE / (t / len(times)) / 1e9,
-            "verified": ok, "gpu_launches": iters * args.steps, "clocks": clocks, "setup_s": setup_s}
-    print(json.dumps(line), flush=True)
+    ok = ok and loc.cache.audit() == 0
+    red = torch.tensor([sum(times), float(scanned), float(np.mean(ios)), float(ok)], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = red.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(red, op=dist.ReduceOp.SUM)
+        t_ms, scanned_all, ios_all, n_ok = float(mx[0]), float(red[1]), float(red[2]), float(red[3])
+    else:
+        t_ms, scanned_all, ios_all, n_ok = float(red[0]), float(red[1]), float(red[2]), float(red[3])
+    if rank == 0:
+        t = t_ms * 1e-3
+        line = {"metric": "BFS GTEPS through bam::array" if bfs else "CC GTEPS through bam::array",
+                "value": scanned_all * len(times) / t / 1e9, "unit": "GTEPS", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": 1e3 * t / len(times), "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+                "config": {"workload": f"{'BFS' if bfs else 'CC'} over R-MAT scale {scale} edge factor 16 (a,b,c = .57,.19,.19), "
+                                       "undirected, de-duplicated; u64 offsets and edges read through the page cache, "
+                                       "cold cache at the start of every traversal",
+                           "vertices": n, "directed_edges": m, "cache_gib_per_gpu": cache_gib, "queues": args.queues,
+                           "queue_depth": args.depth, "source": src, "sharding": "vertex range" if world > 1 else "none",
+                           "l2": "graph (GiB) far larger than L2; no explicit flush"},
+                ("levels" if bfs else "sweeps"): iters, "edges_scanned_per_step": scanned_all,
+                "read_ios_per_step": ios_all, "link_gb_per_s": ios_all * PAGE / (t / len(times)) / 1e9,
+                "verified": bool(n_ok == world), "gpu_launches": iters * args.steps, "clocks": clocks, "setup_s": setup_s}
+        print(json.dumps(line), flush=True)
     gr.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main():
@@ -266,8 +292,7 @@ def main():
         run_reference(args, rank, world)
         return
     if args.workload in ("bfs", "cc"):
-        if rank == 0:
-            run_graph(args)
+        run_graph(args, rank, world, local_rank)
         return
 
     import torch

@@ -157,17 +157,25 @@ int bam_launch_page_scan(bam_array_t a, uint64_t n_pages, const uint64_t* pages_
  * column indices) are two arrays over the SAME cache; both are read only through the cache
  * (the reference keeps the offsets in plain GPU memory, benchmarks/bfs/main.cu:1244-1259). */
 
-/* One BFS level over vertices [v_begin, v_end) (benchmarks/bfs/main.cu:658-689): every vertex with
- * label == level relaxes its neighbours; unreached = 0xFFFFFFFF.  *changed_dev is set to 1 if any
- * label was written, *scanned_dev (may be NULL) is incremented by the edges read. */
-int bam_launch_bfs_level(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint32_t level,
-                         uint32_t* label_dev, uint32_t* changed_dev, uint64_t* scanned_dev, void* stream);
+/* One BFS level over local vertices [v_begin, v_end) (benchmarks/bfs/main.cu:658-689): every vertex
+ * with label == level relaxes its neighbours; unreached = 0xFFFFFFFF.  *changed_dev is set to 1 if
+ * any label was written, *scanned_dev (may be NULL) is incremented by the edges read.  When the
+ * graph is sharded by vertex range, `offsets`/`cols` hold this shard's rows (local vertex v is
+ * global vertex v_base + v), column indices and the label array stay global. */
+int bam_launch_bfs_level(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint64_t v_base,
+                         uint32_t level, uint32_t* label_dev, uint32_t* changed_dev, uint64_t* scanned_dev,
+                         void* scratch_dev, uint64_t scratch_bytes, void* stream);
 /* One label-propagation sweep over the vertices of [v_begin, v_end) flagged in curr_visit
  * (benchmarks/cc/main.cu:123-144, :595-617): for every edge the larger component label takes
  * the smaller (atomicMin), the written vertex is flagged in next_visit. */
-int bam_launch_cc_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end,
+int bam_launch_cc_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint64_t v_base,
                         uint64_t* comp_dev, const uint8_t* curr_visit_dev, uint8_t* next_visit_dev,
-                        uint32_t* changed_dev, uint64_t* scanned_dev, void* stream);
+                        uint32_t* changed_dev, uint64_t* scanned_dev, void* scratch_dev, uint64_t scratch_bytes,
+                        void* stream);
+/* scratch_dev (may be NULL) is device memory of bam_graph_scratch_bytes(number of edges) bytes that
+ * the launch clears and uses to split adjacency lists of hub vertices into work items shared by
+ * all warps; without it every list is walked by one warp. */
+uint64_t bam_graph_scratch_bytes(uint64_t n_edges);
 /* Whole traversals on one GPU (the host loops of benchmarks/bfs/main.cu:1577-1736 and
  * benchmarks/cc/main.cu:1418-1623).  label_dev: n_vertices u32 levels; comp_dev: n_vertices u64
  * labels, at the fixed point the minimum vertex id of each component.  Synchronous. */
