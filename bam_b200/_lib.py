@@ -64,6 +64,8 @@ SIGNATURES = {
     "bam_ctrl_write_store_from_device": (ci, [vp, u64, vp, u64, vp]),
     "bam_gen_uniform_indices": (ci, [vp, u64, u64, u64, u64, vp]),
     "bam_gen_zipf_indices": (ci, [vp, u64, u64, u64, vp, u64, u32, u64, vp]),
+    "bam_gen_block_pages": (ci, [vp, u64, u64, u64, vp]),
+    "bam_direct_page_sums": (ci, [vp, u64, u64, u32, vp, vp]),
     "bam_direct_checksum": (ci, [vp, u64, u64, u64, vp, vp]),
     "bam_launch_geometry": (ci, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
 }

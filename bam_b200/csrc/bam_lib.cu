@@ -91,6 +91,31 @@ __global__ void k_direct_checksum(const uint64_t* idx, uint64_t n, uint64_t seed
     if ((threadIdx.x & 31u) == 0u) atomicAdd((unsigned long long*)out, (unsigned long long)sum);
 }
 
+/* Page of every request of the block random-read workload. */
+__global__ void k_gen_block_pages(uint64_t* out, uint64_t n_reqs, uint64_t req_seed, uint64_t n_pages)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthr = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t r = tid; r < n_reqs; r += nthr) out[r] = bam_block_request_page(req_seed, r, n_pages);
+}
+
+/* Wrapping sum of every word of every listed page, recomputed from the store's definition
+ * (one warp per page). */
+__global__ void k_page_sums(const uint64_t* pages, uint64_t n, uint64_t seed, uint32_t words_per_page, uint64_t* out)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+    uint64_t sum = 0;
+    for (uint64_t i = warp; i < n; i += nwarps) {
+        const uint64_t first = pages[i] * words_per_page;
+        for (uint32_t w = lane; w < words_per_page; w += 32) sum += bam_store_elem(seed, first + w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) atomicAdd((unsigned long long*)out, (unsigned long long)sum);
+}
+
 /* Post-launch audit of the cache invariants; counts violations. */
 __global__ void k_audit(page_cache_d_t pc, uint64_t n_buckets, unsigned long long* violations)
 {
@@ -814,6 +839,23 @@ extern "C" int bam_gen_zipf_indices(uint64_t* out_dev, uint64_t n_lanes, uint64_
     if (!out_dev || !cdf_dev || n_pages == 0 || elems_per_page == 0) return BAM_EINVAL;
     k_gen_zipf<<<1184, 256, 0, (cudaStream_t)stream>>>(out_dev, n_lanes, reqs_per_lane, access_seed, cdf_dev, n_pages,
                                                        elems_per_page, perm_seed);
+    CK(cudaGetLastError());
+    return BAM_OK;
+}
+
+extern "C" int bam_gen_block_pages(uint64_t* out_dev, uint64_t n_reqs, uint64_t req_seed, uint64_t n_pages, void* stream)
+{
+    if (!out_dev || n_pages == 0) return BAM_EINVAL;
+    k_gen_block_pages<<<1184, 256, 0, (cudaStream_t)stream>>>(out_dev, n_reqs, req_seed, n_pages);
+    CK(cudaGetLastError());
+    return BAM_OK;
+}
+
+extern "C" int bam_direct_page_sums(const uint64_t* pages_dev, uint64_t n, uint64_t store_seed, uint32_t words_per_page,
+                                    uint64_t* sum_out_dev, void* stream)
+{
+    if (!pages_dev || !sum_out_dev || words_per_page == 0) return BAM_EINVAL;
+    k_page_sums<<<1184, 256, 0, (cudaStream_t)stream>>>(pages_dev, n, store_seed, words_per_page, sum_out_dev);
     CK(cudaGetLastError());
     return BAM_OK;
 }

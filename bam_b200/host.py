@@ -230,3 +230,16 @@ def direct_checksum(idx, n, store_seed, first_elem, sum_out, stream=None):
     lib = _lib.load()
     check(lib.bam_direct_checksum(_ptr(idx), n, store_seed, first_elem, _ptr(sum_out), _ptr(stream)),
           "bam_direct_checksum")
+
+
+def gen_block_pages(out, n_reqs, req_seed, n_pages, stream=None):
+    """Write the page of every request of the block random-read workload into a device u64 buffer."""
+    lib = _lib.load()
+    check(lib.bam_gen_block_pages(_ptr(out), n_reqs, req_seed, n_pages, _ptr(stream)), "bam_gen_block_pages")
+
+
+def page_sums(pages, n, store_seed, words_per_page, sum_out, stream=None):
+    """Device-side recomputation of the wrapping sum of all words of the listed pages."""
+    lib = _lib.load()
+    check(lib.bam_direct_page_sums(_ptr(pages), n, store_seed, words_per_page, _ptr(sum_out), _ptr(stream)),
+          "bam_direct_page_sums")

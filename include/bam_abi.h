@@ -204,6 +204,12 @@ int bam_gen_zipf_indices(uint64_t* out_dev, uint64_t n_lanes, uint64_t reqs_per_
                          const uint64_t* cdf_dev, uint64_t n_pages, uint32_t elems_per_page, uint64_t perm_seed,
                          void* stream);
 
+/* Pages of the block random-read workload's requests (bam_block_request_page of bam_synth.h). */
+int bam_gen_block_pages(uint64_t* out_dev, uint64_t n_reqs, uint64_t req_seed, uint64_t n_pages, void* stream);
+/* Wrapping sum of every word of every listed page, recomputed from the store's definition: what
+ * bam_launch_block_read's sum_out must equal (verification of full-size runs). */
+int bam_direct_page_sums(const uint64_t* pages_dev, uint64_t n, uint64_t store_seed, uint32_t words_per_page,
+                         uint64_t* sum_out_dev, void* stream);
 /* Wrapping sum of splitmix64(store_seed ^ (first_elem + idx[i])) over an index list, recomputed
  * from the store's definition without touching cache or queues: the value every cached read of
  * those indices must add up to (verification of full-size runs; no counterpart in the reference,
