@@ -238,6 +238,56 @@ struct ArrayReadWork {
     }
 };
 
+/* ---- write path ----------------------------------------------------------------------------------
+ * Element writes and atomic adds through the cache (the vectoradd-style consumers of the
+ * reference, benchmarks/vectoradd/main.cu:103-118), and the write-back of every dirty page
+ * (page_cache.h:584-629 __flush there). */
+struct ArrayWriteWork {
+    array_d_t<uint64_t> arr;            /* by value: n_ranges = 1, d_ranges points at the device descriptor */
+    uint64_t n;
+    const uint64_t* idx;
+    uint64_t val_seed;
+    uint64_t addend;                    /* 0: a[i] = splitmix64(val_seed ^ i); else a[i] += addend (atomic) */
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint64_t gid = (uint64_t)vb * blockDim.x + threadIdx.x;
+        const uint64_t nthr = (uint64_t)nvb * blockDim.x;
+        for (uint64_t k = gid; k < n; k += nthr) {
+            const uint64_t i = idx[k];
+            if (addend) arr.AtomicAdd(i, addend);
+            else arr.seq_write(i, bam_splitmix64(val_seed ^ i));
+        }
+    }
+};
+
+struct FlushWork {
+    page_cache_d_t pc;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint32_t lane = threadIdx.x & 31u;
+        const uint32_t wpb = blockDim.x >> 5;
+        const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
+        const uint64_t nwarps = (uint64_t)nvb * wpb;
+        Controller* c = pc.d_ctrl;
+        QueuePair* qp = c->d_qps + ((uint32_t)warp % c->n_qps);
+        for (uint64_t s0 = warp * 32; s0 < pc.n_slots; s0 += nwarps * 32) {
+            const uint64_t s = s0 + lane;
+            uint32_t st = 0;
+            uint64_t tag = BAM_TAG_NONE;
+            if (s < pc.n_slots) { st = ld_acquire_gpu(&pc.slots[s].state); tag = ld_relaxed_gpu(&pc.slots[s].tag); }
+            const bool dirty = (st & (BAM_VALID | BAM_DIRTY)) == (BAM_VALID | BAM_DIRTY) && tag != BAM_TAG_NONE;
+            if (!__any_sync(0xffffffffu, dirty)) continue;
+            const int rc = warp_io(0xffffffffu, dirty, qp, dirty ? backing_page_of_tag(pc, tag) * pc.n_blocks_per_page : 0,
+                                   pc.n_blocks_per_page, dirty ? slot_bus_addr(pc, (uint32_t)s) : 0,
+                                   dirty ? slot_prp2(pc, (uint32_t)s) : 0, NVM_IO_WRITE);
+            if (dirty && rc == BAM_OK) atom_and_release(&pc.slots[s].state, ~BAM_DIRTY);
+            if (__any_sync(0xffffffffu, rc != BAM_OK)) break;
+        }
+    }
+};
+
 /* ---- cache benchmark: a warp reads whole pages -----------------------------------------------
  * Hit data is staged through shared memory: the warp pins 32 pages at once (one look-up and one
  * pin per lane, side by side), then streams them through its two 4 KiB stages of the block's
@@ -809,6 +859,29 @@ extern "C" int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t r
     ArrayReadWork w;
     w.r = a->h_range; w.n_lanes = n_lanes; w.reqs_per_lane = reqs_per_lane; w.idx = idx_dev;
     w.access_seed = access_seed; w.sum_out = sum_out_dev;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_array_write(bam_array_t a, uint64_t n, const uint64_t* idx_dev, uint64_t val_seed, uint64_t addend,
+                                      void* stream)
+{
+    if (!a || a->elem_bytes != 8 || !idx_dev) return BAM_EINVAL;
+    bam_ctrl* c = a->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    ArrayWriteWork w;
+    w.arr.n_elems = a->n_elems; w.arr.start_offset = 0; w.arr.n_ranges = 1;
+    w.arr.d_ranges = static_cast<range_d_t<uint64_t>*>(a->d_range);
+    w.n = n; w.idx = idx_dev; w.val_seed = val_seed; w.addend = addend;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_cache_flush(bam_cache_t pc, void* stream)
+{
+    if (!pc) return BAM_EINVAL;
+    bam_ctrl* c = pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    FlushWork w;
+    w.pc = pc->d;
     return launch_fused(c, w, (cudaStream_t)stream);
 }
 

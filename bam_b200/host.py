@@ -147,6 +147,10 @@ class PageCache:
         check(self.lib.bam_cache_audit(self.h, C.byref(v)), "bam_cache_audit")
         return v.value
 
+    def flush(self, stream=None):
+        """Write every dirty page back to the backing store (page_cache_t::flush_cache)."""
+        check(self.lib.bam_cache_flush(self.h, _ptr(stream)), "bam_cache_flush")
+
     def audit_noalloc(self, violations_out, stream=None):
         """Enqueue the allocation-free audit; the count lands in the device u64 `violations_out`."""
         check(self.lib.bam_cache_audit_noalloc(self.h, _ptr(violations_out), _ptr(stream)), "bam_cache_audit_noalloc")
@@ -184,6 +188,10 @@ class Array:
     def read(self, n_lanes, reqs_per_lane, sum_out, idx=None, access_seed=0, stream=None):
         check(self.lib.bam_launch_array_read(self.h, n_lanes, reqs_per_lane, _ptr(idx), access_seed, _ptr(sum_out),
                                              _ptr(stream)), "bam_launch_array_read")
+
+    def write(self, n, idx, val_seed=0, addend=0, stream=None):
+        """a[idx[k]] = splitmix64(val_seed ^ idx[k]) (addend == 0) or a[idx[k]] += addend, through the cache."""
+        check(self.lib.bam_launch_array_write(self.h, n, _ptr(idx), val_seed, addend, _ptr(stream)), "bam_launch_array_write")
 
     def page_scan(self, n_pages, sum_out, pages=None, first_page=0, stream=None):
         check(self.lib.bam_launch_page_scan(self.h, n_pages, _ptr(pages), first_page, _ptr(sum_out), _ptr(stream)),

@@ -132,6 +132,49 @@ struct array_d_t {
     }
 
     BAM_DEV T operator[](size_t i) const { return seq_read(i); }
+
+    /* Shared body of the element updates: pin the page for writing (it becomes DIRTY), apply
+     * `op` to the element in the cache, unpin.  Counterpart of seq_write / AtomicAdd
+     * (page_cache.h:1577-1609, :1647-1711 in the reference). */
+    template <class Op>
+    BAM_DEV void update(size_t i, Op op) const
+    {
+        const uint32_t mask = __activemask();
+        const int64_t ri = find_range(i);
+        const bool valid = ri >= 0;
+        const range_d_t<T>& r = d_ranges[valid ? ri : 0];
+        const uint64_t page = valid ? r.get_page(i) : ~0ull;
+        const uint64_t key = valid ? r.get_global_address(page) : ~0ull;
+        const uint32_t eq = __match_any_sync(mask, key);
+        const uint32_t leader = __ffs(eq) - 1;
+        const uint32_t cnt = __popc(eq);
+        bool pending = valid;
+        spin_t sp;
+        for (;;) {
+            uint32_t slot = r.acquire_page_warp(mask, pending && lane_id() == leader, valid ? page : 0, cnt, true, default_queue());
+            slot = __shfl_sync(eq, slot, leader);
+            if (pending && slot != BAM_SLOT_RETRY) {
+                if (slot != BAM_SLOT_ERR) op(reinterpret_cast<T*>(r.get_cache_page_addr(slot) + r.get_subindex(i)));
+                __threadfence();
+                __syncwarp(eq);
+                if (lane_id() == leader && slot != BAM_SLOT_ERR) r.release_page(slot, cnt);
+                pending = false;
+            }
+            if (!__any_sync(mask, pending)) break;
+            if (__any_sync(mask, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) break;
+        }
+        if (!valid) status_fail(d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i);
+    }
+
+    BAM_DEV void seq_write(size_t i, const T val) const { update(i, [val](T* p) { *p = val; }); }
+    BAM_DEV void operator()(size_t i, const T val) const { seq_write(i, val); }
+    BAM_DEV void AtomicAdd(size_t i, const T val) const
+    {
+        update(i, [val](T* p) {
+            if constexpr (sizeof(T) == 8) atom_add_relaxed(reinterpret_cast<uint64_t*>(p), (uint64_t)val);
+            else atomicAdd(p, val);
+        });
+    }
 };
 
 /* Same read as array_d_t<T>::seq_read for the common single-range array whose descriptor sits
@@ -231,6 +274,7 @@ struct bafs_ptr {
     __host__ __device__ bafs_ptr(const array_d_t<T>* a, uint64_t s = 0) : d(a), start_idx(s) {}
     BAM_DEV T operator*() const { return (*d)[start_idx]; }
     BAM_DEV T operator[](uint64_t i) const { return (*d)[start_idx + i]; }
+    BAM_DEV void operator()(uint64_t i, const T val) const { (*d)(start_idx + i, val); }
     __host__ __device__ bafs_ptr operator+(uint64_t i) const { return bafs_ptr(d, start_idx + i); }
     __host__ __device__ bafs_ptr operator-(uint64_t i) const { return bafs_ptr(d, start_idx - i); }
     __host__ __device__ bafs_ptr& operator++() { ++start_idx; return *this; }

@@ -128,9 +128,10 @@ BAM_DEV uint64_t slot_bus_addr(const page_cache_d_t& pc, uint32_t slot)
 /* Clock sweep: returns a slot claimed for the caller (state BUSY, no tag, no table entry), or
  * BAM_SLOT_ERR; with max_tries it gives up after that many probes and returns BAM_SLOT_NONE.
  * Counterpart of page_cache_d_t::find_slot (page_cache.h:1786-1927). */
-BAM_DEV uint32_t find_slot(const page_cache_d_t& pc, uint32_t max_tries = 0xffffffffu)
+BAM_DEV uint32_t find_slot(const page_cache_d_t& pc, uint32_t max_tries = 0xffffffffu, uint64_t* dirty_tag = nullptr)
 {
     spin_t sp;
+    if (dirty_tag) *dirty_tag = BAM_TAG_NONE;
 #pragma unroll 1
     for (uint32_t tries = 1;; tries++) {
         if (tries > max_tries) return BAM_SLOT_NONE;          /* caller asked for a bounded attempt */
@@ -141,17 +142,46 @@ BAM_DEV uint32_t find_slot(const page_cache_d_t& pc, uint32_t max_tries = 0xffff
         if (st == 0u) {
             if (atom_cas_acquire(&sl->state, 0u, BAM_BUSY) == 0u) return s;
         } else if ((st & ~BAM_DIRTY) == BAM_VALID) {
+            if ((st & BAM_DIRTY) && !dirty_tag) continue;     /* this caller cannot write back: leave it */
             if (atom_cas_acquire(&sl->state, st, st | BAM_BUSY) == st) {
+                if (st & BAM_DIRTY) {
+                    /* the victim must reach the backing store first.  Its tag and table entry stay,
+                     * so anyone who wants that page meanwhile finds the slot VALID|BUSY and waits
+                     * instead of reading a stale copy from the store; finish_evict() ends it. */
+                    *dirty_tag = ld_relaxed_gpu(&sl->tag);
+                    return s;
+                }
                 const uint64_t old = ld_relaxed_gpu(&sl->tag);
                 st_relaxed_gpu(&sl->tag, BAM_TAG_NONE);
                 pt_remove(pc, old, s);
-                /* write-back of a DIRTY victim belongs here once the write path exists */
                 atom_and_release(&sl->state, ~(BAM_VALID | BAM_DIRTY));
                 return s;
             }
         }
         if ((tries & 63u) == 0u && sp.expired(pc.status, BAM_AT_FIND_SLOT)) return BAM_SLOT_ERR;
     }
+}
+
+/* Second half of the eviction of a dirty victim, after its write-back has completed. */
+BAM_DEV void finish_evict(const page_cache_d_t& pc, uint32_t s, uint64_t old_tag)
+{
+    bam_slot_t* sl = &pc.slots[s];
+    st_relaxed_gpu(&sl->tag, BAM_TAG_NONE);
+    pt_remove(pc, old_tag, s);
+    atom_and_release(&sl->state, ~(BAM_VALID | BAM_DIRTY));
+}
+
+/* Backing page of a cached page, from its tag: (page in range << range bits) | range id. */
+BAM_DEV uint64_t backing_page_of_tag(const page_cache_d_t& pc, uint64_t tag)
+{
+    return ld_relaxed_gpu(&pc.range_page_starts[tag & pc.n_ranges_mask]) + (tag >> pc.n_ranges_bits);
+}
+
+BAM_DEV uint64_t slot_prp2(const page_cache_d_t& pc, uint32_t slot)
+{
+    if (pc.page_size <= 4096) return 0;
+    const uint64_t bus = (uint64_t)(pc.base_addr + (size_t)slot * pc.page_size);
+    return (pc.page_size <= 8192) ? bus + 4096 : (uint64_t)(pc.prp_lists + (size_t)slot * pc.prp_list_stride);
 }
 
 BAM_DEV void count_hit(const page_cache_d_t& pc, uint32_t count) { red_add_relaxed(&pc.stats[get_smid() & (BAM_STAT_STRIPES - 1)].hits, (uint64_t)count); }
@@ -234,7 +264,8 @@ BAM_DEV uint32_t cache_acquire(const page_cache_d_t& pc, uint64_t tag, uint32_t 
 BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d_t& pc, uint64_t tag, uint32_t count,
                                     uint64_t backing_page, uint32_t queue, bool write)
 {
-    enum { S_DONE = 0, S_LOOKUP = 1, S_WAIT = 2, S_IO = 3 };
+    enum { S_DONE = 0, S_LOOKUP = 1, S_WAIT = 2, S_IO = 3, S_WB = 4 };
+    uint64_t victim_tag = BAM_TAG_NONE;
     const uint32_t kClaimTries = 64;                     /* clock-sweep probes before giving the turn back */
     bam_status_t* st = pc.status;
     const uint64_t h = pt_hash(tag);
@@ -262,8 +293,9 @@ BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d
                     slot = s; state = S_WAIT;                                  /* someone is filling it  */
                 }
             } else {
-                const uint32_t v = find_slot(pc, kClaimTries);
+                const uint32_t v = find_slot(pc, kClaimTries, &victim_tag);
                 if (v == BAM_SLOT_ERR) { state = S_DONE; }
+                else if (v <= BAM_SLOT_MAX && victim_tag != BAM_TAG_NONE) { slot = v; state = S_WB; }
                 else if (v == BAM_SLOT_NONE) {
                     /* everything the sweep saw is pinned or busy.  The warp-mates that did get a
                      * slot must not wait for this lane while it waits for slots they hold pinned:
@@ -286,13 +318,35 @@ BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d
                 }
             }
         }
+        /* dirty victims are written back as one group; then their slots are free for the new pages */
+        if (__any_sync(mask, state == S_WB)) {
+            const bool wb = state == S_WB;
+            const int rc = warp_io(mask, wb, qp, wb ? backing_page_of_tag(pc, victim_tag) * pc.n_blocks_per_page : 0,
+                                   pc.n_blocks_per_page, wb ? slot_bus_addr(pc, slot) : 0, wb ? slot_prp2(pc, slot) : 0, NVM_IO_WRITE);
+            if (wb) {
+                if (rc == BAM_OK) {
+                    finish_evict(pc, slot, victim_tag);
+                    bam_slot_t* sl = &pc.slots[slot];
+                    st_relaxed_gpu(&sl->tag, tag);
+                    __threadfence();
+                    const int r = pt_insert(pc, tag, slot, home, fp);
+                    if (r == BAM_PT_OK) state = S_IO;
+                    else {
+                        st_relaxed_gpu(&sl->tag, BAM_TAG_NONE);
+                        atom_and_release(&sl->state, ~BAM_BUSY);
+                        slot = BAM_SLOT_ERR;
+                        if (r == BAM_PT_EXISTS) state = S_LOOKUP;
+                        else { if (r == BAM_PT_FULL) status_fail(st, BAM_ENOSPC, BAM_AT_TABLE_FULL, tag); state = S_DONE; }
+                    }
+                } else { slot = BAM_SLOT_ERR; state = S_DONE; }
+                victim_tag = BAM_TAG_NONE;
+            }
+        }
         /* all page reads of this round go out as one group */
         const bool io = state == S_IO;
         if (__any_sync(mask, io)) {
             const uint64_t bus = io ? slot_bus_addr(pc, slot) : 0;
-            uint64_t prp2 = 0;
-            if (io && pc.page_size > 4096)
-                prp2 = (pc.page_size <= 8192) ? bus + 4096 : (uint64_t)(pc.prp_lists + (size_t)slot * pc.prp_list_stride);
+            const uint64_t prp2 = io ? slot_prp2(pc, slot) : 0;
             const int rc = warp_io(mask, io, qp, backing_page * pc.n_blocks_per_page, pc.n_blocks_per_page, bus, prp2, NVM_IO_READ);
             if (io) {
                 if (rc == BAM_OK) {

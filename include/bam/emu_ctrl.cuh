@@ -181,6 +181,9 @@ BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t
         const void* src = (m.opc == NVM_IO_READ) ? (const void*)media : (const void*)mem;
         void* dst = (m.opc == NVM_IO_READ) ? (void*)mem : (void*)media;
         BAM_PROF_T0();
+        /* a WRITE's source is a cache page other threads wrote with ordinary stores: order them
+         * before the bulk engine's read */
+        asm volatile("fence.proxy.async.global;" ::: "memory");
         mbar_expect_tx(bar, len);
         bulk_load(stage_smem, src, len, bar);
         const uint64_t t0 = global_timer_ns();

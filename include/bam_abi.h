@@ -146,6 +146,16 @@ int bam_launch_block_read(bam_cache_t pc, uint64_t n_reqs, const uint64_t* pages
 int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t reqs_per_lane, const uint64_t* idx_dev,
                           uint64_t access_seed, uint64_t* sum_out_dev, void* stream);
 
+/* Element updates through the cache (array_d_t<T>::seq_write / operator() / AtomicAdd,
+ * page_cache.h:1577-1711; the write side of benchmarks/vectoradd/main.cu:103-118): for k < n,
+ * addend == 0: a[idx[k]] = splitmix64(val_seed ^ idx[k]); addend != 0: a[idx[k]] += addend
+ * (atomic, wrapping).  Pages become DIRTY; a dirty page that is evicted is written back first. */
+int bam_launch_array_write(bam_array_t a, uint64_t n, const uint64_t* idx_dev, uint64_t val_seed, uint64_t addend,
+                           void* stream);
+/* Write every dirty page back to the backing store (page_cache_t::flush_cache, page_cache.h:675-682,
+ * kernel __flush :584-629).  Call it when no other launch is using the cache. */
+int bam_cache_flush(bam_cache_t pc, void* stream);
+
 /* Cache benchmark (benchmarks/cache/main.cu:44-114): each warp reads whole pages of the
  * array (page list pages_dev[n_pages], or pages first_page .. first_page+n_pages-1 when NULL),
  * all 32 lanes striding the page; wrapping sum of every element into *sum_out_dev. */

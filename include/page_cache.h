@@ -49,7 +49,7 @@ struct page_cache_t {
     page_cache_t(const page_cache_t&) = delete;
     page_cache_t& operator=(const page_cache_t&) = delete;
 
-    void flush_cache() {}                     /* nothing is ever dirty on the read path */
+    void flush_cache() { bam_cache_flush(h, nullptr); cudaDeviceSynchronize(); }
     void print_reset_stats()
     {
         bam_cache_stats_t s;

@@ -1,0 +1,69 @@
+"""GPU tests of the write path: element writes and atomic adds through the cache, write-back of
+dirty pages on eviction, flush.  The expected backing store is computed with numpy."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+SEC = 1_000_000_000
+M64 = (1 << 64) - 1
+
+
+def np_splitmix64(x):
+    x = x + np.uint64(0x9E3779B97F4A7C15)
+    z = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return z ^ (z >> np.uint64(31))
+
+
+@pytest.mark.parametrize("slots", [4096, 96])          # everything fits / constant eviction of dirty pages
+def test_write_flush_store_matches_numpy(cuda, bam, orc, slots):
+    n_elems, seed, vseed = 1 << 18, 11, 77                # 512 pages
+    ctrl = bam.Controller(n_elems * 8, 0, queue_depth=64, num_queues=4)
+    ctrl.configure(spin_timeout_ns=5 * SEC)
+    if slots < 1000:
+        ctrl.configure(ctrl_blocks=2)
+        ctrl.set_max_grid(4)
+    ctrl.fill_store(seed)
+    cache = bam.PageCache(ctrl, 4096, slots)
+    arr = bam.Array(cache, n_elems)
+    rng = np.random.default_rng(5)
+    idx = rng.integers(0, n_elems, 20000, dtype=np.uint64)
+    idx[:64] = np.arange(64)                              # a run inside one page, coalesced by the warp
+    d_idx = cuda.from_numpy(idx.view(np.int64)).cuda()
+    arr.write(len(idx), d_idx, val_seed=vseed)
+    assert ctrl.status() == (0, "none", 0)
+    cache.flush()
+    assert ctrl.status() == (0, "none", 0) and cache.audit() == 0
+    want = orc.fill_store(seed, 0, n_elems)
+    with np.errstate(over="ignore"):
+        want[idx.astype(np.int64)] = np_splitmix64(np.uint64(vseed) ^ idx)
+    assert (ctrl.store_numpy() == want).all()
+    # reads through the cache see the written values too
+    out = cuda.zeros(1, dtype=cuda.int64, device="cuda")
+    arr.read(len(idx), 1, out, idx=d_idx)
+    assert ctrl.status() == (0, "none", 0)
+    assert (int(out.item()) & M64) == int(want[idx.astype(np.int64)].sum(dtype=np.uint64))
+    arr.close(); cache.close(); ctrl.close()
+
+
+def test_atomic_add_through_cache(cuda, bam, orc):
+    n_elems, seed = 1 << 16, 3
+    ctrl = bam.Controller(n_elems * 8, 0, queue_depth=16, num_queues=2)
+    ctrl.configure(ctrl_blocks=2, spin_timeout_ns=5 * SEC)
+    ctrl.set_max_grid(6)
+    ctrl.fill_store(seed)
+    cache = bam.PageCache(ctrl, 4096, 64)                 # 128 pages in 64 slots
+    arr = bam.Array(cache, n_elems)
+    rng = np.random.default_rng(9)
+    idx = rng.integers(0, n_elems, 30000, dtype=np.uint64)
+    idx[:5000] = 4242                                     # a hot element: 5000 adds land on it
+    d_idx = cuda.from_numpy(idx.view(np.int64)).cuda()
+    arr.write(len(idx), d_idx, addend=0x100000001)
+    assert ctrl.status() == (0, "none", 0)
+    cache.flush()
+    assert ctrl.status() == (0, "none", 0) and cache.audit() == 0
+    want = orc.fill_store(seed, 0, n_elems)
+    with np.errstate(over="ignore"):
+        np.add.at(want, idx.astype(np.int64), np.uint64(0x100000001))
+    assert (ctrl.store_numpy() == want).all()
+    arr.close(); cache.close(); ctrl.close()
