@@ -251,3 +251,33 @@ def page_sums(pages, n, store_seed, words_per_page, sum_out, stream=None):
     lib = _lib.load()
     check(lib.bam_direct_page_sums(_ptr(pages), n, store_seed, words_per_page, _ptr(sum_out), _ptr(stream)),
           "bam_direct_page_sums")
+
+
+def bind_to_gpu_numa(cuda_device):
+    """Pin the calling process to the CPUs that are local to `cuda_device` (its PCIe root's NUMA
+    node), so that the backing store it allocates next -- pinned host memory, placed by first touch --
+    sits next to the GPU that will read it.  Returns {"numa_node", "cpus"} or None if the topology
+    cannot be read (then nothing is changed)."""
+    import os
+    try:
+        import torch
+        p = torch.cuda.get_device_properties(cuda_device)
+        dom, bus, dev = getattr(p, "pci_domain_id", 0), p.pci_bus_id, p.pci_device_id
+        base = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0"
+        cpulist = open(os.path.join(base, "local_cpulist")).read().strip()
+        node = int(open(os.path.join(base, "numa_node")).read().strip())
+        cpus = set()
+        for part in cpulist.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                cpus.update(range(int(a), int(b) + 1))
+            elif part:
+                cpus.add(int(part))
+        allowed = os.sched_getaffinity(0)
+        cpus &= allowed
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return {"numa_node": node, "cpus": len(cpus)}
+    except Exception:
+        return None

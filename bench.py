@@ -221,6 +221,7 @@ def run_graph(args, rank, world, local_rank):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+    bam_b200.bind_to_gpu_numa(local_rank)
     bfs = args.workload == "bfs"
     scale = args.scale or (24 if bfs else 26)
     cache_gib = args.cache_gib if args.cache_gib != 16.0 else (4.0 if bfs else 8.0)
@@ -404,6 +405,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    numa = bam_b200.bind_to_gpu_numa(local_rank)          # the pinned shard is placed next to its GPU
     total_pages = int(args.store_gib * (1 << 30)) // PAGE
     first_page, n_local = bam_b200.shard_pages(total_pages, world, rank)
     cache_pages = min(int(args.cache_gib * (1 << 30)) // PAGE, (1 << 24) - 2)
@@ -566,7 +568,7 @@ def main():
                              "kernel": "bam_fused<PageScanWork>", "hits": hit["hits"], "misses": hit["misses"],
                              "note": "warm cache: whole resident pages read through the cache, 4096 algorithmic "
                                      "bytes per page; peak = MEASURED_PEAKS.json hbm_gbs" if peaks else "of fallback"},
-            "clocks": clocks, "setup_s": setup_s,
+            "clocks": clocks, "setup_s": setup_s, "numa_rank0": numa,
         }
         if not args.no_cpu_baseline and world == 1:
             try:
