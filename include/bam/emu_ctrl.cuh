@@ -40,6 +40,7 @@ namespace bam {
 #define BAM_EMU_STAGE_BYTES 4096
 #define BAM_EMU_LANES 4             /* lanes of a controller warp that process commands (one stage each) */
 #define BAM_EMU_WARPS 4             /* warps of a controller block that are command processors            */
+#define BAM_EMU_MAX_PROCS_PER_QUEUE 8u
 #define BAM_EMU_STAGES (BAM_EMU_LANES * BAM_EMU_WARPS)     /* 4 KiB stages per controller block           */
 /* dynamic shared memory a controller block needs: the stages and one mbarrier per stage */
 #define BAM_EMU_SMEM_BYTES (BAM_EMU_STAGES * BAM_EMU_STAGE_BYTES + 256)
@@ -228,6 +229,8 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
     __syncwarp(wmask);
 
     const uint64_t t_start = global_timer_ns();
+    /* with few queues, more than a handful of processors per queue only fight for its fetch lock */
+    const bool spare = me >= c.n_qps * BAM_EMU_MAX_PROCS_PER_QUEUE;
     const uint32_t rounds = (c.n_qps + n_procs - 1) / n_procs;
     uint32_t want = c.batch < BAM_EMU_LANES ? c.batch : BAM_EMU_LANES;
     if (want == 0) want = 1;
@@ -240,7 +243,7 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
 #ifdef BAM_PROFILE
         long long pt = clock64();
 #endif
-        if (lane == 0) {
+        if (lane == 0 && !spare) {
             for (uint32_t r = 0; r < rounds && n == 0; r++) {
                 n = emu_reserve(c, q, want, fetch, cqbase);
                 bq = q;
@@ -296,7 +299,7 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
         if (lane == 0) { BAM_PROF_ADD(c.status, 23, 1); BAM_PROF_ADD(c.status, 24, clock64() - pt); }
 #endif
         if (stop) break;
-        __nanosleep(idle_ns);
+        __nanosleep(spare ? 2000u : idle_ns);
         if (idle_ns < 512) idle_ns <<= 1;
     }
 }
