@@ -506,7 +506,7 @@ extern "C" int bam_ctrl_create(bam_ctrl_t* out, int device, uint64_t store_bytes
     c->emu.n_ctrl_blocks = BAM_DEFAULT_CTRL_BLOCKS;
     c->emu.store = c->store_dev; c->emu.store_bytes = store_bytes;
     c->emu.lba_log2 = log2_u32(lba_bytes); c->emu.mps_log2 = 12;
-    c->emu.batch = BAM_EMU_LANES; c->emu.sys_scope = c->sys_scope;
+    c->emu.batch = 32; c->emu.sys_scope = c->sys_scope;
     c->emu.consumers_remaining = c->d_remaining; c->emu.status = c->d_status;
     c->emu.fault = c->d_fault; c->emu.served = c->d_served;
     int rc = upload_queue_image(c);

@@ -207,32 +207,34 @@ BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t
 }
 
 /* Body of a controller block.  Warps [0, BAM_EMU_WARPS) are command processors; in each, lanes
- * [0, BAM_EMU_LANES) own one 4 KiB stage and one mbarrier.  A processor reserves a batch of up to
- * BAM_EMU_LANES commands from one queue under that queue's fetch lock, then every lane decodes,
- * transfers and completes its own command, so the latencies of a batch overlap.  Runs until
+ * [0, BAM_EMU_LANES) own one 4 KiB stage and one mbarrier.  A processor reserves a batch of up to 32
+ * commands from one queue under that queue's fetch lock, every lane decodes one of them side by
+ * side, the lock is released, and the stage-owning lanes transfer and complete the commands
+ * BAM_EMU_LANES at a time, so the latencies of a round overlap and the lock is held once per batch.  Runs until
  * every workload block of the launch has finished (consumers_remaining == 0) or an error has been
  * flagged.  `smem` is the block's dynamic shared memory (BAM_EMU_SMEM_BYTES, 128-byte aligned). */
 BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
 {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t wib = threadIdx.x >> 5;
-    if (wib >= BAM_EMU_WARPS || lane >= BAM_EMU_LANES) return;
-    const uint32_t wmask = (1u << BAM_EMU_LANES) - 1u;
+    if (wib >= BAM_EMU_WARPS) return;
+    const uint32_t full = 0xffffffffu;
+    const bool mover = lane < BAM_EMU_LANES;               /* lanes that own a stage and move data */
     const uint32_t me = blockIdx.x * BAM_EMU_WARPS + wib;
     const uint32_t n_procs = c.n_ctrl_blocks * BAM_EMU_WARPS;
-    const uint32_t my_stage = wib * BAM_EMU_LANES + lane;
+    const uint32_t my_stage = wib * BAM_EMU_LANES + (lane & (BAM_EMU_LANES - 1));
     const uint32_t stage_smem = smem_u32(smem + (size_t)my_stage * BAM_EMU_STAGE_BYTES);
     const uint32_t bar = smem_u32(smem + (size_t)BAM_EMU_STAGES * BAM_EMU_STAGE_BYTES + my_stage * 8);
-    mbar_init(bar, 1);
+    if (mover) mbar_init(bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncwarp(wmask);
+    __syncwarp(full);
 
     const uint64_t t_start = global_timer_ns();
     /* with few queues, more than a handful of processors per queue only fight for its fetch lock */
     const bool spare = me >= c.n_qps * BAM_EMU_MAX_PROCS_PER_QUEUE;
     const uint32_t rounds = (c.n_qps + n_procs - 1) / n_procs;
-    uint32_t want = c.batch < BAM_EMU_LANES ? c.batch : BAM_EMU_LANES;
+    uint32_t want = c.batch < 32u ? c.batch : 32u;
     if (want == 0) want = 1;
     uint32_t parity = 0;
     uint32_t q = me % c.n_qps;
@@ -251,35 +253,52 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
                 while (q >= c.n_qps) q -= c.n_qps;
             }
         }
-        n = __shfl_sync(wmask, n, 0);
+        n = __shfl_sync(full, n, 0);
         if (n) {
-            fetch = __shfl_sync(wmask, fetch, 0);
-            cqbase = __shfl_sync(wmask, cqbase, 0);
-            bq = __shfl_sync(wmask, bq, 0);
-            __syncwarp(wmask);                                 /* lane 0's acquire fence covers the batch */
+            fetch = __shfl_sync(full, fetch, 0);
+            cqbase = __shfl_sync(full, cqbase, 0);
+            bq = __shfl_sync(full, bq, 0);
+            __syncwarp(full);                                  /* lane 0's acquire fence covers the batch */
             const uint32_t qmask = c.qps[bq].qs - 1u;
+            /* every lane decodes one SQ entry of the batch; then the queue is handed back */
             emu_cmd_t m;
+            m.prp1 = m.prp2 = m.media_off = 0; m.bytes = m.cq_virt = m.cid = m.opc = 0; m.status = BAM_SC_SUCCESS;
             if (lane < n) emu_decode(c, bq, fetch + lane, cqbase + lane, (fetch + n) & qmask, m);
-            __syncwarp(wmask);
-            if (lane == 0) {                                   /* the SQ entries are in registers now */
+            __syncwarp(full);
+            if (lane == 0) {
                 st_relaxed_gpu(&c.qps[bq].sq_fetch, fetch + n);
                 st_release_gpu(&c.qps[bq].lock, 0u);
 #ifdef BAM_PROFILE
                 { long long t = clock64(); BAM_PROF_ADD(c.status, 16, 1); BAM_PROF_ADD(c.status, 17, n); BAM_PROF_ADD(c.status, 18, t - pt); pt = t; }
 #endif
             }
-            if (lane < n) {
-                uint32_t status = m.status;
-                if (status == BAM_SC_SUCCESS) status = emu_transfer(c, m, stage_smem, bar, parity);
+            /* the mover lanes work through the batch, BAM_EMU_LANES commands per round */
+            for (uint32_t r0 = 0; r0 < n; r0 += BAM_EMU_LANES) {
+                const uint32_t src = r0 + (lane & (BAM_EMU_LANES - 1));
+                emu_cmd_t w;
+                w.prp1 = __shfl_sync(full, m.prp1, src);
+                w.prp2 = __shfl_sync(full, m.prp2, src);
+                w.media_off = __shfl_sync(full, m.media_off, src);
+                w.bytes = __shfl_sync(full, m.bytes, src);
+                w.cq_virt = __shfl_sync(full, m.cq_virt, src);
+                w.cid = __shfl_sync(full, m.cid, src);
+                w.opc = __shfl_sync(full, m.opc, src);
+                w.status = __shfl_sync(full, m.status, src);
+                w.q = bq;
+                w.sqhd = (fetch + n) & qmask;
+                if (mover && src < n) {
+                    uint32_t status = w.status;
+                    if (status == BAM_SC_SUCCESS) status = emu_transfer(c, w, stage_smem, bar, parity);
 #ifdef BAM_PROFILE
-                long long t1 = clock64();
+                    long long t1 = clock64();
 #endif
-                if (status != 0xffffffffu) emu_post_completion(c, m, status);
+                    if (status != 0xffffffffu) emu_post_completion(c, w, status);
 #ifdef BAM_PROFILE
-                BAM_PROF_ADD(c.status, 22, clock64() - t1);
+                    BAM_PROF_ADD(c.status, 22, clock64() - t1);
 #endif
+                }
+                __syncwarp(full);
             }
-            __syncwarp(wmask);
 #ifdef BAM_PROFILE
             if (lane == 0) BAM_PROF_ADD(c.status, 19, clock64() - pt);
 #endif
@@ -294,7 +313,7 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
                 stop = 1;
             }
         }
-        stop = __shfl_sync(wmask, stop, 0);
+        stop = __shfl_sync(full, stop, 0);
 #ifdef BAM_PROFILE
         if (lane == 0) { BAM_PROF_ADD(c.status, 23, 1); BAM_PROF_ADD(c.status, 24, clock64() - pt); }
 #endif
