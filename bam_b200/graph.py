@@ -46,6 +46,35 @@ def build_rmat_csr(seed, scale, edge_factor=16, device="cuda", thresholds=None, 
     return offsets, cols
 
 
+def write_bel(path, values):
+    """Write a `.bel.*` file as the reference's converter does (benchmarks/bam_data_conversion.py:26-35):
+    a 16-byte header {count: u64, type size: u64} followed by the values as little-endian int64."""
+    a = np.ascontiguousarray(values, dtype="<i8")
+    with open(path, "wb") as f:
+        f.write(np.array([a.size, 8], dtype="<u8").tobytes())
+        f.write(a.tobytes())
+
+
+def read_bel(path):
+    """Read a `.bel.col` (row offsets) / `.bel.dst` (column indices) file: 16-byte header, then
+    int64 values (the layout benchmarks/bfs/main.cu:1244-1281 reads)."""
+    with open(path, "rb") as f:
+        hdr = np.frombuffer(f.read(16), dtype="<u8")
+        count = int(hdr[0])
+        data = np.frombuffer(f.read(count * 8), dtype="<i8")
+    if data.size != count:
+        raise ValueError(f"{path}: header announces {count} values, file holds {data.size}")
+    return data
+
+
+def load_bel_graph(prefix, device="cuda"):
+    """CSR (offsets, cols) tensors from `<prefix>.bel.col` and `<prefix>.bel.dst`."""
+    import torch
+    off = torch.from_numpy(read_bel(prefix + ".bel.col").copy()).to(device)
+    cols = torch.from_numpy(read_bel(prefix + ".bel.dst").copy()).to(device)
+    return off, cols
+
+
 class CsrGraph:
     """A CSR graph stored behind an emulated NVMe controller and read through a page cache."""
 

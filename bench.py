@@ -279,6 +279,24 @@ def run_graph(args, rank, world, local_rank):
                 ("levels" if bfs else "sweeps"): iters, "edges_scanned_per_step": scanned_all,
                 "read_ios_per_step": ios_all, "link_gb_per_s": ios_all * PAGE / (t / len(times)) / 1e9,
                 "verified": bool(n_ok == world), "gpu_launches": iters * args.steps, "clocks": clocks, "setup_s": setup_s}
+        if world == 1 and not args.no_cpu_baseline:
+            # the same traversal through the CPU restatement of the reference's cache and queues, on the
+            # very store the GPU run used (cold cache, all host cores)
+            try:
+                from oracle import pyoracle as orc
+                cores = os.cpu_count() or 1
+                ctrl_threads = max(1, cores // 8)
+                workers = max(1, cores - ctrl_threads)
+                store = loc.ctrl.store_numpy()
+                res, sc, it, r = orc.ref_graph_run(store, n, loc.off_bytes, 0 if bfs else 1, src, kw["cache_pages"],
+                                                   min(args.queues, 128), args.depth, workers, ctrl_threads)
+                same = bool((torch.from_numpy(res.view(np.int32 if bfs else np.int64)).to(out.device) == out).all().item())
+                line["cpu_baseline"] = {"value": sc / r.seconds / 1e9, "unit": "GTEPS", "cores": workers + ctrl_threads,
+                                        "kind": "port", "seconds": r.seconds, "read_ios": r.read_ios,
+                                        "matches_gpu_result": same,
+                                        "sample": "the whole traversal on the same backing store, cold cache of the same size"}
+            except Exception as e:
+                line["cpu_baseline"] = {"value": None, "unit": "GTEPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
         print(json.dumps(line), flush=True)
     gr.close()
     if world > 1:

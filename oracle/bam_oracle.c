@@ -854,3 +854,160 @@ ORC_API int ref_block_read(const uint64_t* store, uint64_t store_bytes, uint32_t
     free(pc.qps); free(pc.base_addr); free(ct); free(ca); free(wt); free(wa);
     return 0;
 }
+
+
+/* ---- graph traversals through the restated cache ---------------------------------------------
+ * The reference's BFS / CC kernels (benchmarks/bfs/main.cu:658-689, benchmarks/cc/main.cu:123-144,
+ * :595-617) on host threads: vertices are handed out in chunks, a thread walks a vertex's neighbour
+ * list through a cursor that keeps the current page pinned (bam_ptr, page_cache.h:415-485), labels
+ * live in plain memory.  Offsets are read through the cache too, as the GPU build does. */
+typedef struct { ref_cache_t* pc; uint64_t page; uint32_t slot; int valid; uint32_t queue; } ref_cursor_t;
+
+static uint64_t ref_cursor_read(ref_cursor_t* c, uint64_t elem)
+{
+    ref_cache_t* pc = c->pc;
+    const uint64_t byte = elem * 8, page = byte >> pc->page_size_log;
+    if (!c->valid || c->page != page) {
+        if (c->valid) ref_release_page(pc, c->page, 1);
+        c->slot = ref_acquire_page(pc, page, 1, c->queue);
+        c->page = page; c->valid = 1;
+    }
+    return *(const uint64_t*)(pc->base_addr + (uint64_t)c->slot * pc->page_size + (byte & (pc->page_size - 1)));
+}
+
+static void ref_cursor_done(ref_cursor_t* c) { if (c->valid) { ref_release_page(c->pc, c->page, 1); c->valid = 0; } }
+
+typedef struct {
+    ref_cache_t* pc;
+    uint64_t n, cols_elem0;
+    int mode;                       /* 0 = BFS, 1 = CC */
+    uint32_t* level;
+    uint64_t* comp;
+    uint8_t *curr, *next;
+    uint32_t cur_level;
+    uint64_t* chunk_cursor;
+    int* changed;
+    pthread_barrier_t* bar;
+    volatile int* finished;
+    uint32_t worker, n_workers;
+    uint64_t scanned;
+    uint32_t iters;
+} ref_graph_arg_t;
+
+static void* ref_graph_thread(void* p)
+{
+    ref_graph_arg_t* a = (ref_graph_arg_t*)p;
+    ref_cursor_t co = { a->pc, 0, 0, 0, a->worker % a->pc->n_qps }, ce = co;
+    const uint64_t CH = 256;
+    for (;;) {
+        for (;;) {
+            uint64_t v0 = __atomic_fetch_add(a->chunk_cursor, CH, __ATOMIC_RELAXED);
+            if (v0 >= a->n) break;
+            uint64_t v1 = v0 + CH < a->n ? v0 + CH : a->n;
+            for (uint64_t v = v0; v < v1; v++) {
+                if (a->mode == 0 ? ld_rlx(&a->level[v]) != a->cur_level : a->curr[v] == 0) continue;
+                uint64_t s = ref_cursor_read(&co, v), e = ref_cursor_read(&co, v + 1);
+                a->scanned += e - s;
+                for (uint64_t i = s; i < e; i++) {
+                    uint64_t w = ref_cursor_read(&ce, a->cols_elem0 + i);
+                    if (a->mode == 0) {
+                        if (ld_rlx(&a->level[w]) == 0xFFFFFFFFu) { st_rlx(&a->level[w], a->cur_level + 1); st_rlx(a->changed, 1); }
+                    } else {
+                        uint64_t cu = ld_rlx(&a->comp[v]), cw = ld_rlx(&a->comp[w]);
+                        if (cu == cw) continue;
+                        uint64_t* tgt = cu < cw ? &a->comp[w] : &a->comp[v];
+                        uint64_t val = cu < cw ? cu : cw, old = ld_rlx(tgt);
+                        while (old > val && !__atomic_compare_exchange_n(tgt, &old, val, 1, __ATOMIC_RELAXED, __ATOMIC_RELAXED)) {}
+                        a->next[cu < cw ? w : v] = 1;
+                        st_rlx(a->changed, 1);
+                    }
+                }
+            }
+        }
+        ref_cursor_done(&co); ref_cursor_done(&ce);
+        pthread_barrier_wait(a->bar);
+        if (a->worker == 0) {                                   /* the host loop between two launches */
+            a->iters++;
+            if (!*a->changed) *a->finished = 1;
+            else {
+                *a->changed = 0;
+                if (a->mode == 0) { a->cur_level++; }
+                else { memset(a->curr, 0, a->n); }
+            }
+            *a->chunk_cursor = 0;
+        }
+        pthread_barrier_wait(a->bar);
+        if (*a->finished) break;
+        if (a->worker != 0) { if (a->mode == 0) a->cur_level++; }
+        if (a->mode == 1) { uint8_t* t = a->curr; a->curr = a->next; a->next = t; }
+    }
+    return 0;
+}
+
+/* store = [offsets (n+1 u64, padded to a page) | cols]; mode 0 writes BFS levels (from `source`),
+ * mode 1 writes min-vertex labels.  Only the traversal is timed. */
+ORC_API int ref_graph_run(const uint64_t* store, uint64_t store_bytes, uint64_t n_vertices, uint64_t cols_byte_offset,
+                          int mode, uint64_t source, uint32_t page_size, uint64_t n_slots, uint32_t n_qps, uint32_t qdepth,
+                          uint32_t lba_bytes, uint32_t workers, uint32_t ctrl_threads, uint32_t* level_out,
+                          uint64_t* comp_out, uint64_t* scanned_out, uint32_t* iters_out, ref_result_t* out)
+{
+    if (!store || !out || workers == 0 || ctrl_threads == 0 || n_qps == 0 || (mode == 0 ? !level_out : !comp_out)) return 22;
+    ref_cache_t pc;
+    memset(&pc, 0, sizeof pc);
+    pc.page_size = page_size;
+    while ((1u << pc.page_size_log) < page_size) pc.page_size_log++;
+    pc.n_slots = n_slots;
+    pc.base_addr = (uint8_t*)aligned_alloc(4096, n_slots * (uint64_t)page_size);
+    pc.slots = (ref_cache_page_t*)calloc(n_slots, sizeof(ref_cache_page_t));
+    for (uint64_t s = 0; s < n_slots; s++) pc.slots[s].take_lock = REF_FREE;
+    pc.n_data_pages = (store_bytes + page_size - 1) / page_size;
+    pc.pages = (ref_data_page_t*)calloc(pc.n_data_pages, sizeof(ref_data_page_t));
+    pc.n_qps = n_qps;
+    pc.qps = (ref_qp_t*)aligned_alloc(64, sizeof(ref_qp_t) * n_qps);
+    pc.n_blocks_per_page = page_size / lba_bytes;
+    pc.ns_id = 1;
+    for (uint32_t q = 0; q < n_qps; q++) {
+        ref_qp_t* qp = &pc.qps[q];
+        memset(qp, 0, sizeof *qp);
+        ref_queue_init(&qp->sq, qdepth, sizeof(ref_cmd_t), &qp->sq_db, 1);
+        ref_queue_init(&qp->cq, qdepth, sizeof(ref_cpl_t), &qp->cq_db, 0);
+    }
+    volatile int stop = 0;
+    uint32_t n_ct = ctrl_threads < n_qps ? ctrl_threads : n_qps;
+    pthread_t* ct = (pthread_t*)calloc(n_ct, sizeof(pthread_t));
+    ref_ctrl_arg_t* ca = (ref_ctrl_arg_t*)calloc(n_ct, sizeof(ref_ctrl_arg_t));
+    for (uint32_t c = 0; c < n_ct; c++) {
+        ca[c] = (ref_ctrl_arg_t){ pc.qps, n_qps, c, n_ct, (const uint8_t*)store, store_bytes, lba_bytes, &stop, 0 };
+        pthread_create(&ct[c], 0, ref_ctrl_thread, &ca[c]);
+    }
+    uint8_t* visit = (uint8_t*)malloc(2 * n_vertices);
+    if (mode == 0) { for (uint64_t v = 0; v < n_vertices; v++) level_out[v] = 0xFFFFFFFFu; level_out[source] = 0; }
+    else { for (uint64_t v = 0; v < n_vertices; v++) comp_out[v] = v; memset(visit, 1, n_vertices); memset(visit + n_vertices, 0, n_vertices); }
+    pthread_barrier_t bar;
+    pthread_barrier_init(&bar, 0, workers);
+    uint64_t chunk_cursor = 0;
+    int changed = 0;
+    volatile int finished = 0;
+    pthread_t* wt = (pthread_t*)calloc(workers, sizeof(pthread_t));
+    ref_graph_arg_t* wa = (ref_graph_arg_t*)calloc(workers, sizeof(ref_graph_arg_t));
+    double t0 = now_s();
+    for (uint32_t w = 0; w < workers; w++) {
+        wa[w] = (ref_graph_arg_t){ &pc, n_vertices, cols_byte_offset / 8, mode, level_out, comp_out, visit, visit + n_vertices,
+                                   0, &chunk_cursor, &changed, &bar, &finished, w, workers, 0, 0 };
+        pthread_create(&wt[w], 0, ref_graph_thread, &wa[w]);
+    }
+    uint64_t scanned = 0;
+    for (uint32_t w = 0; w < workers; w++) { pthread_join(wt[w], 0); scanned += wa[w].scanned; }
+    double t1 = now_s();
+    __atomic_store_n(&stop, 1, __ATOMIC_RELEASE);
+    for (uint32_t c = 0; c < n_ct; c++) pthread_join(ct[c], 0);
+    if (scanned_out) *scanned_out = scanned;
+    if (iters_out) *iters_out = wa[0].iters;
+    memset(out, 0, sizeof *out);
+    out->accesses = pc.access_cnt; out->hits = pc.hit_cnt; out->misses = pc.miss_cnt; out->read_ios = pc.read_io_cnt;
+    out->seconds = t1 - t0; out->worker_threads = workers; out->ctrl_threads = n_ct;
+    pthread_barrier_destroy(&bar);
+    for (uint32_t q = 0; q < n_qps; q++) { ref_queue_free(&pc.qps[q].sq); ref_queue_free(&pc.qps[q].cq); }
+    free(pc.qps); free(pc.pages); free(pc.slots); free(pc.base_addr); free(ct); free(ca); free(wt); free(wa); free(visit);
+    return 0;
+}

@@ -66,6 +66,9 @@ def lib():
                                      C.POINTER(RefResult)]
         L.ref_block_read.restype = C.c_int
         L.ref_block_read.argtypes = [vp, u64, u32, u32, u32, u32, u32, u32, u64, u64, vp, C.POINTER(RefResult)]
+        L.ref_graph_run.restype = C.c_int
+        L.ref_graph_run.argtypes = [vp, u64, u64, u64, C.c_int, u64, u32, u64, u32, u32, u32, u32, u32, vp, vp,
+                                    C.POINTER(u64), C.POINTER(u32), C.POINTER(RefResult)]
         _lib = L
     return _lib
 
@@ -204,3 +207,29 @@ def ref_block_read(store, page_size, n_qps, qdepth, lba_bytes, workers, ctrl_thr
     if rc:
         raise RuntimeError(f"ref_block_read failed: {rc}")
     return r, crc
+
+
+def csr_store(offsets, cols, page_size=4096):
+    """The backing-store image of a CSR graph: offsets (padded to a page) followed by cols."""
+    pad = lambda b: (b + page_size - 1) // page_size * page_size  # noqa: E731
+    off_bytes = pad(len(offsets) * 8)
+    store = np.zeros((off_bytes + pad(max(1, len(cols)) * 8)) // 8, dtype=np.uint64)
+    store[:len(offsets)] = offsets
+    store[off_bytes // 8:off_bytes // 8 + len(cols)] = cols
+    return store, off_bytes
+
+
+def ref_graph_run(store, n_vertices, cols_byte_offset, mode, source, n_slots, n_qps, qdepth, workers, ctrl_threads,
+                  page_size=4096, lba_bytes=512):
+    """BFS (mode 0) or CC (mode 1) through the CPU restatement of the reference's cache and queues.
+    Returns (levels or labels, edges scanned, iterations, RefResult)."""
+    r = RefResult()
+    level = np.empty(n_vertices, dtype=np.uint32) if mode == 0 else None
+    comp = np.empty(n_vertices, dtype=np.uint64) if mode == 1 else None
+    scanned, iters = u64(), u32()
+    rc = lib().ref_graph_run(_p(store), store.nbytes, n_vertices, cols_byte_offset, mode, source, page_size, n_slots,
+                             n_qps, qdepth, lba_bytes, workers, ctrl_threads, _p(level), _p(comp), C.byref(scanned),
+                             C.byref(iters), C.byref(r))
+    if rc:
+        raise RuntimeError(f"ref_graph_run failed: {rc}")
+    return (level if mode == 0 else comp), scanned.value, iters.value, r

@@ -73,3 +73,20 @@ def test_shard_pages(bam):
         assert spans[0][0] == 0 and sum(c for _, c in spans) == n
         for (a, ca), (b, _) in zip(spans, spans[1:]):
             assert a + ca == b
+
+
+def test_bel_file_round_trip(bam, tmp_path):
+    """The reference's on-disk CSR format (.bel.col / .bel.dst: 16-byte header {count, 8} + int64)."""
+    import numpy as np
+    off = np.array([0, 2, 3, 3, 6], dtype=np.int64)
+    dst = np.array([1, 3, 0, 0, 1, 2], dtype=np.int64)
+    prefix = str(tmp_path / "g")
+    bam.write_bel(prefix + ".bel.col", off)
+    bam.write_bel(prefix + ".bel.dst", dst)
+    raw = open(prefix + ".bel.col", "rb").read()
+    assert len(raw) == 16 + 8 * len(off) and np.frombuffer(raw[:16], dtype="<u8").tolist() == [len(off), 8]
+    assert (bam.read_bel(prefix + ".bel.col") == off).all() and (bam.read_bel(prefix + ".bel.dst") == dst).all()
+    open(prefix + ".bad", "wb").write(raw[:-8])
+    import pytest
+    with pytest.raises(ValueError):
+        bam.read_bel(prefix + ".bad")

@@ -285,3 +285,36 @@ def test_config1_shape_reduced_lanes(cuda, bam, orc):
     finish(ctrl, cache)
     assert u64(out) == c["checksum"]
     arr.close(); cache.close(); ctrl.close()
+
+
+def test_system_scope_queues(cuda, bam, orc):
+    """Doorbells and completion entries synchronised at system scope (what a controller outside the
+    GPU needs) give the same results as the default device scope."""
+    n_elems, seed, aseed = 1 << 20, 11, 29
+    ctrl, cache, arr = make(bam, n_elems, 1024, 4, 64, seed=seed)
+    ctrl.set_scope(1)
+    out = cuda.zeros(1, dtype=cuda.int64, device="cuda")
+    arr.read(1 << 13, 8, out, access_seed=aseed)
+    finish(ctrl, cache)
+    assert u64(out) == orc.array_checksum(seed, n_elems, aseed, 0, 1 << 13, 8)
+    ctrl.set_scope(0)
+    out.zero_()
+    arr.read(1 << 13, 8, out, access_seed=aseed + 1)
+    finish(ctrl, cache)
+    assert u64(out) == orc.array_checksum(seed, n_elems, aseed + 1, 0, 1 << 13, 8)
+    arr.close(); cache.close(); ctrl.close()
+
+
+def test_bel_files_to_bfs(cuda, bam, orc, tmp_path):
+    """A graph loaded from the reference's .bel files gives the oracle's BFS levels."""
+    off, cols = orc.rmat_csr(4, 9, 8)
+    prefix = str(tmp_path / "rmat9")
+    bam.write_bel(prefix + ".bel.col", off.astype(np.int64))
+    bam.write_bel(prefix + ".bel.dst", cols.astype(np.int64))
+    d_off, d_cols = bam.load_bel_graph(prefix)
+    gr = bam.CsrGraph(d_off, d_cols, cache_pages=64, queue_depth=16, num_queues=2)
+    src = orc.max_degree_vertex(off)
+    lv, _, _ = gr.bfs(src)
+    want, _ = orc.bfs(off, cols, src)
+    assert (lv.cpu().numpy().view(np.uint32) == want).all() and gr.ctrl.status() == (0, "none", 0)
+    gr.close()

@@ -225,3 +225,18 @@ def test_golden_fixtures(orc):
         lab, comps = orc.cc(off, cols)
         assert sha(lvl) == gph["levels_sha256"] and sha(lab) == gph["labels_sha256"]
         assert comps == gph["components"] and scanned == gph["edges_scanned"]
+
+
+def test_protocol_restatement_graph_traversals(orc):
+    """BFS and CC through the host-thread restatement of cache + queues equal the result oracle."""
+    off, cols = orc.rmat_csr(2, 10, 16)
+    store, off_bytes = orc.csr_store(off, cols)
+    n = len(off) - 1
+    src = orc.max_degree_vertex(off)
+    want_lv, want_sc = orc.bfs(off, cols, src)
+    lv, scanned, iters, r = orc.ref_graph_run(store, n, off_bytes, 0, src, 16, 2, 8, 4, 1)      # 16 slots: evictions
+    assert (lv == want_lv).all() and scanned == want_sc and r.read_ios > 0
+    assert iters == int(want_lv[want_lv != 0xFFFFFFFF].max()) + 1
+    want_lab, _ = orc.cc(off, cols)
+    lab, _, sweeps, _ = orc.ref_graph_run(store, n, off_bytes, 1, 0, 64, 2, 8, 4, 1)
+    assert (lab == want_lab).all() and sweeps >= 1
