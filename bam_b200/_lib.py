@@ -53,6 +53,7 @@ SIGNATURES = {
     "bam_array_destroy": (ci, [vp]),
     "bam_array_device_ptr": (vp, [vp]),
     "bam_launch_block_read": (ci, [vp, u64, vp, u64, vp, vp, vp]),
+    "bam_launch_block_read_depth": (ci, [vp, u64, vp, u64, u32, vp, vp, vp]),
     "bam_launch_array_read": (ci, [vp, u64, u64, vp, u64, vp, vp]),
     "bam_launch_array_write": (ci, [vp, u64, vp, u64, u64, vp]),
     "bam_cache_flush": (ci, [vp, vp]),

@@ -148,7 +148,11 @@ __global__ void k_audit(page_cache_d_t pc, uint64_t n_buckets, unsigned long lon
     if (bad) atomicAdd(violations, bad);
 }
 
-/* ---- block benchmark --------------------------------------------------------------------- */
+/* ---- block benchmark ---------------------------------------------------------------------
+ * Every thread keeps io_depth requests in flight (io_depth = 1: the block benchmark,
+ * benchmarks/block/main.cu:137-200; io_depth > 1: the iodepth-block benchmark,
+ * benchmarks/iodepth-block/main.cu:97-147), each landing in a private cache slot. */
+#define BAM_MAX_IO_DEPTH 8
 struct BlockReadWork {
     page_cache_d_t pc;
     uint64_t n_reqs;
@@ -157,6 +161,7 @@ struct BlockReadWork {
     uint64_t n_store_pages;
     uint32_t* crc_out;
     uint64_t* sum_out;
+    uint32_t io_depth;
 
     __device__ void operator()(uint32_t vb, uint32_t nvb) const
     {
@@ -171,39 +176,55 @@ struct BlockReadWork {
         }
         const uint64_t gid = (uint64_t)vb * blockDim.x + threadIdx.x;
         const uint64_t nthr = (uint64_t)nvb * blockDim.x;
-        const uint32_t slot = (uint32_t)gid;                 /* private slot, as pc_entry = tid in the reference */
         Controller* c = pc.d_ctrl;
         QueuePair* qp = c->d_qps + ((uint32_t)(gid >> 5) % c->n_qps);
-        const uint64_t bus = slot_bus_addr(pc, slot);
-        const uint64_t prp2 = pc.page_size > 4096 ? bus + 4096 : 0;
         uint64_t sum = 0;
         const uint64_t warp_first = gid & ~31ull;             /* requests are issued by whole warps */
-        for (uint64_t r0 = warp_first; r0 < n_reqs; r0 += nthr) {
-            const uint64_t r = r0 + (threadIdx.x & 31u);
-            const bool active = r < n_reqs;
-            uint64_t pg = 0;
-            if (active) pg = pages ? pages[r] : bam_block_request_page(req_seed, r, n_store_pages);
-            const int rc = warp_io(0xffffffffu, active, qp, pg * pc.n_blocks_per_page, pc.n_blocks_per_page, bus, prp2, NVM_IO_READ);
-            if (__any_sync(0xffffffffu, rc != BAM_OK)) break;
-            if (active && (crc_out || sum_out)) {
-                uint32_t crc = ~0u;
-                const uint8_t* p = reinterpret_cast<const uint8_t*>(bus);
-                for (uint32_t o = 0; o < pc.page_size; o += 16) {
-                    const uint4 v = ld_cg_v4(p + o);
-                    sum += (((uint64_t)v.y << 32) | v.x) + (((uint64_t)v.w << 32) | v.z);
-                    if (crc_out) {
-                        const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+        const uint32_t depth = io_depth;
+        for (uint64_t r0 = warp_first; r0 < n_reqs; r0 += nthr * depth) {
+            uint32_t cid[BAM_MAX_IO_DEPTH];
+            uint64_t req[BAM_MAX_IO_DEPTH];
+            bool fail = false;
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            uint32_t x = w[j];
-#pragma unroll
-                            for (int b = 0; b < 4; b++) { crc = (crc >> 8) ^ crc_tab[(crc ^ x) & 0xffu]; x >>= 8; }
-                        }
-                    }
+            for (uint32_t d = 0; d < BAM_MAX_IO_DEPTH; d++) {
+                if (d < depth) {
+                    req[d] = r0 + (uint64_t)d * nthr + (threadIdx.x & 31u);
+                    const bool active = req[d] < n_reqs;
+                    uint64_t pg = 0;
+                    if (active) pg = pages ? pages[req[d]] : bam_block_request_page(req_seed, req[d], n_store_pages);
+                    const uint64_t bus = slot_bus_addr(pc, (uint32_t)(gid * depth + d));     /* private slot */
+                    cid[d] = warp_io_submit(0xffffffffu, active, qp, pg * pc.n_blocks_per_page, pc.n_blocks_per_page, bus,
+                                            pc.page_size > 4096 ? bus + 4096 : 0, NVM_IO_READ);
                 }
-                if (crc_out) crc_out[r] = ~crc;
             }
-            __syncwarp();
+#pragma unroll
+            for (uint32_t d = 0; d < BAM_MAX_IO_DEPTH; d++) {
+                if (d < depth) {
+                    const bool active = req[d] < n_reqs;
+                    const int rc = warp_io_wait(0xffffffffu, active, qp, cid[d]);
+                    if (__any_sync(0xffffffffu, rc != BAM_OK)) fail = true;
+                    if (active && rc == BAM_OK && (crc_out || sum_out)) {
+                        uint32_t crc = ~0u;
+                        const uint8_t* p = reinterpret_cast<const uint8_t*>(slot_bus_addr(pc, (uint32_t)(gid * depth + d)));
+                        for (uint32_t o = 0; o < pc.page_size; o += 16) {
+                            const uint4 v = ld_cg_v4(p + o);
+                            sum += (((uint64_t)v.y << 32) | v.x) + (((uint64_t)v.w << 32) | v.z);
+                            if (crc_out) {
+                                const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+                                for (int j = 0; j < 4; j++) {
+                                    uint32_t x = w[j];
+#pragma unroll
+                                    for (int bb = 0; bb < 4; bb++) { crc = (crc >> 8) ^ crc_tab[(crc ^ x) & 0xffu]; x >>= 8; }
+                                }
+                            }
+                        }
+                        if (crc_out) crc_out[req[d]] = ~crc;
+                    }
+                    __syncwarp();
+                }
+            }
+            if (fail) break;
         }
         __syncwarp();
         warp_sum_to(sum, sum_out);
@@ -830,24 +851,32 @@ extern "C" void* bam_array_device_ptr(bam_array_t a) { return a ? a->d_array : n
 
 /* ---- launchers --------------------------------------------------------------------------------- */
 
-extern "C" int bam_launch_block_read(bam_cache_t pc, uint64_t n_reqs, const uint64_t* pages_dev, uint64_t req_seed,
-                                     uint32_t* crc_out_dev, uint64_t* sum_out_dev, void* stream)
+extern "C" int bam_launch_block_read_depth(bam_cache_t pc, uint64_t n_reqs, const uint64_t* pages_dev, uint64_t req_seed,
+                                           uint32_t io_depth, uint32_t* crc_out_dev, uint64_t* sum_out_dev, void* stream)
 {
-    if (!pc) return BAM_EINVAL;
+    if (!pc || io_depth == 0 || io_depth > BAM_MAX_IO_DEPTH) return BAM_EINVAL;
     bam_ctrl* c = pc->ctrl;
     CK(cudaSetDevice(c->device));
     if (pc->d.page_size > 8192) return BAM_EINVAL;
+    /* a warp's outstanding commands must stay below half the queue depth */
+    if (32u * io_depth >= c->qdepth / 2 && io_depth > 1) return BAM_EINVAL;
     uint32_t grid = 0;
     int rc = fused_geometry<BlockReadWork>(c, &grid);
     if (rc) return rc;
     if (grid <= c->emu.n_ctrl_blocks) return BAM_EINVAL;
-    /* every worker thread owns one cache slot as its landing buffer */
-    if ((uint64_t)(grid - c->emu.n_ctrl_blocks) * BAM_THREADS > pc->d.n_slots) return BAM_ENOSPC;
+    /* every worker thread owns io_depth cache slots as its landing buffers */
+    if ((uint64_t)(grid - c->emu.n_ctrl_blocks) * BAM_THREADS * io_depth > pc->d.n_slots) return BAM_ENOSPC;
     BlockReadWork w;
     w.pc = pc->d; w.n_reqs = n_reqs; w.pages = pages_dev; w.req_seed = req_seed;
     w.n_store_pages = c->store_bytes / pc->d.page_size;
-    w.crc_out = crc_out_dev; w.sum_out = sum_out_dev;
+    w.crc_out = crc_out_dev; w.sum_out = sum_out_dev; w.io_depth = io_depth;
     return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_block_read(bam_cache_t pc, uint64_t n_reqs, const uint64_t* pages_dev, uint64_t req_seed,
+                                     uint32_t* crc_out_dev, uint64_t* sum_out_dev, void* stream)
+{
+    return bam_launch_block_read_depth(pc, n_reqs, pages_dev, req_seed, 1, crc_out_dev, sum_out_dev, stream);
 }
 
 extern "C" int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t reqs_per_lane, const uint64_t* idx_dev,

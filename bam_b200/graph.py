@@ -144,6 +144,20 @@ def shard_vertices(n, world_size, rank):
     return v0, v0 + base + (1 if rank < rem else 0)
 
 
+def shard_vertices_by_edges(offsets, world_size, rank):
+    """Contiguous vertex range [v0, v1) of `rank` such that every rank owns about the same number of
+    edges (R-MAT degrees are so skewed that equal vertex counts would give very unequal shards).
+    `offsets` is the CSR row-offset tensor; the cut points are the same on every rank."""
+    import torch
+    n = offsets.numel() - 1
+    m = int(offsets[-1].item())
+    targets = torch.tensor([m * r // world_size for r in range(world_size + 1)], dtype=offsets.dtype, device=offsets.device)
+    cuts = torch.searchsorted(offsets, targets, right=False).clamp_(0, n)
+    cuts[0], cuts[-1] = 0, n
+    cuts = torch.cummax(cuts, 0).values
+    return int(cuts[rank].item()), int(cuts[rank + 1].item())
+
+
 def _all_gather_ragged(t, group=None):
     """All-gather 1-D tensors of different lengths (counts first, then padded payloads).
     Returns the concatenation over ranks, in rank order."""
@@ -197,7 +211,7 @@ class DistCsrGraph:
     def __init__(self, offsets, cols, rank, world_size, cache_pages, cuda_device=0, group=None, **kw):
         self.n = offsets.numel() - 1
         self.rank, self.world, self.group = rank, world_size, group
-        self.v0, self.v1 = shard_vertices(self.n, world_size, rank)
+        self.v0, self.v1 = shard_vertices_by_edges(offsets, world_size, rank)
         e0, e1 = int(offsets[self.v0].item()), int(offsets[self.v1].item())
         loc_off = (offsets[self.v0:self.v1 + 1] - e0).contiguous()
         loc_cols = cols[e0:e1].contiguous()

@@ -155,9 +155,9 @@ class PageCache:
         """Enqueue the allocation-free audit; the count lands in the device u64 `violations_out`."""
         check(self.lib.bam_cache_audit_noalloc(self.h, _ptr(violations_out), _ptr(stream)), "bam_cache_audit_noalloc")
 
-    def block_read(self, n_reqs, pages=None, req_seed=0, crc_out=None, sum_out=None, stream=None):
-        check(self.lib.bam_launch_block_read(self.h, n_reqs, _ptr(pages), req_seed, _ptr(crc_out), _ptr(sum_out),
-                                             _ptr(stream)), "bam_launch_block_read")
+    def block_read(self, n_reqs, pages=None, req_seed=0, crc_out=None, sum_out=None, stream=None, io_depth=1):
+        check(self.lib.bam_launch_block_read_depth(self.h, n_reqs, _ptr(pages), req_seed, io_depth, _ptr(crc_out),
+                                                   _ptr(sum_out), _ptr(stream)), "bam_launch_block_read_depth")
 
 
 class Array:

@@ -275,6 +275,7 @@ BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d
     QueuePair* qp = c->d_qps + (queue % c->n_qps);
     uint32_t state = want ? S_LOOKUP : S_DONE;
     uint32_t slot = BAM_SLOT_ERR;
+    uint32_t my_hits = 0;                    /* hit counts are summed over the warp: one atomic, not 32 */
     spin_t sp;
 #pragma unroll 1
     for (;;) {
@@ -287,7 +288,7 @@ BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d
                     red_add_relaxed(&sl->state, 0u - count);                   /* recycled or given back */
                 } else if ((old & (BAM_VALID | BAM_BUSY)) == BAM_VALID) {
                     if (write && !(old & BAM_DIRTY)) atom_or_relaxed(&sl->state, BAM_DIRTY);
-                    count_hit(pc, count);
+                    my_hits += count;
                     slot = s; state = S_DONE;
                 } else {
                     slot = s; state = S_WAIT;                                  /* someone is filling it  */
@@ -366,7 +367,7 @@ BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d
                 slot = BAM_SLOT_ERR; state = S_LOOKUP;
             } else if ((cur & (BAM_VALID | BAM_BUSY)) == BAM_VALID) {
                 if (write && !(cur & BAM_DIRTY)) atom_or_relaxed(&sl->state, BAM_DIRTY);
-                count_hit(pc, count);
+                my_hits += count;
                 state = S_DONE;
             }
         }
@@ -377,6 +378,8 @@ BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d
             break;
         }
     }
+    const uint32_t warp_hits = __reduce_add_sync(mask, my_hits);
+    if (warp_hits && lane_id() == (uint32_t)(__ffs(mask) - 1)) count_hit(pc, warp_hits);
     return slot;
 }
 

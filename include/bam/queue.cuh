@@ -312,14 +312,14 @@ BAM_DEV uint32_t cq_reap_warp(uint32_t mask, uint32_t leader, QueuePair* qp)
     return total;
 }
 
-/* One group: the lanes of `g` (a subset of mask, at most qs/2 of them, all on queue pair qp)
- * submit one command each and wait for all completions.  Every lane of mask takes part in the
- * votes and helps sweeping and reaping.  Returns BAM_OK / BAM_E* (per lane; BAM_OK if not in g). */
-BAM_DEV int warp_io_group(uint32_t mask, uint32_t g, QueuePair* qp, uint64_t starting_lba, uint32_t n_blocks,
-                          uint64_t bus_addr, uint64_t bus_addr2, uint8_t opcode)
+/* Submit half of a group: the lanes of `g` (a subset of mask, all on queue pair qp) write one
+ * command each and get it published.  Every lane of mask takes part in the votes and helps
+ * sweeping.  Returns the command id of the lane's command (BAM_CID_ERR for lanes outside g, or when
+ * a wait ran out). */
+BAM_DEV uint32_t warp_submit_group(uint32_t mask, uint32_t g, QueuePair* qp, uint64_t starting_lba, uint32_t n_blocks,
+                                   uint64_t bus_addr, uint64_t bus_addr2, uint8_t opcode)
 {
     nvm_queue_t* sq = &qp->sq;
-    nvm_queue_t* cq = &qp->cq;
     bam_status_t* st = sq->status;
     const uint32_t lane = lane_id();
     const bool mine = (g >> lane) & 1u;
@@ -338,7 +338,7 @@ BAM_DEV int warp_io_group(uint32_t mask, uint32_t g, QueuePair* qp, uint64_t sta
     for (;;) {
         const bool ok = !mine || ld_acquire_gpu(&sq->tickets[pos]) == ticket;
         if (__all_sync(mask, ok)) break;
-        if (__any_sync(mask, sp.expired(st, BAM_AT_SQ_TURN, ticket))) return mine ? BAM_ETIMEDOUT : BAM_OK;
+        if (__any_sync(mask, sp.expired(st, BAM_AT_SQ_TURN, ticket))) return BAM_CID_ERR;
     }
 #ifdef BAM_PROFILE
     { long long n = clock64(); if (mine) { BAM_PROF_ADD(st, 0, 1); BAM_PROF_ADD(st, 1, n - pt); } pt = n; }
@@ -359,7 +359,7 @@ BAM_DEV int warp_io_group(uint32_t mask, uint32_t g, QueuePair* qp, uint64_t sta
                 else probe += 32u;
             }
             if (__all_sync(mask, !mine || cid != BAM_CID_ERR)) break;
-            if (__any_sync(mask, sp.expired(st, BAM_AT_CID))) return mine ? BAM_ETIMEDOUT : BAM_OK;
+            if (__any_sync(mask, sp.expired(st, BAM_AT_CID))) return BAM_CID_ERR;
         }
     }
 #ifdef BAM_PROFILE
@@ -385,14 +385,29 @@ BAM_DEV int warp_io_group(uint32_t mask, uint32_t g, QueuePair* qp, uint64_t sta
         }
         const bool cleared = !mine || ld_relaxed_gpu(&sq->tail_mark[pos]) == 0u;
         if (__all_sync(mask, cleared)) break;
-        if (__any_sync(mask, sp.expired(st, BAM_AT_SQ_DOORBELL, ticket))) return mine ? BAM_ETIMEDOUT : BAM_OK;
+        if (__any_sync(mask, sp.expired(st, BAM_AT_SQ_DOORBELL, ticket))) return BAM_CID_ERR;
     }
 #ifdef BAM_PROFILE
     { long long n = clock64(); if (mine) BAM_PROF_ADD(st, 3, n - pt); pt = n; }
 #endif
-    /* completions: each lane watches its mailbox; whoever gets head_lock reaps with the whole warp */
+    return mine ? cid : BAM_CID_ERR;
+}
+
+/* Wait half: the lanes of `g` wait for the completions of their commands `cid`; whoever gets
+ * head_lock reaps with the whole warp.  Returns BAM_OK / BAM_E* (per lane; BAM_OK if not in g). */
+BAM_DEV int warp_wait_group(uint32_t mask, uint32_t g, QueuePair* qp, uint32_t cid)
+{
+    nvm_queue_t* sq = &qp->sq;
+    nvm_queue_t* cq = &qp->cq;
+    bam_status_t* st = sq->status;
+    const uint32_t lane = lane_id();
+    const bool mine = ((g >> lane) & 1u) && cid != BAM_CID_ERR;
+    const uint32_t gl = __ffs(g) - 1;
+#ifdef BAM_PROFILE
+    long long pt = clock64();
+#endif
     uint32_t status = BAM_CPL_ERR;
-    sp.reset();
+    spin_t sp;
     for (;;) {
         if (mine && status == BAM_CPL_ERR) {
             const uint32_t v = ld_acquire_gpu(&sq->cid[cid]);
@@ -423,11 +438,39 @@ BAM_DEV int warp_io_group(uint32_t mask, uint32_t g, QueuePair* qp, uint64_t sta
 #ifdef BAM_PROFILE
     { long long n = clock64(); if (mine) BAM_PROF_ADD(st, 4, n - pt); pt = n; }
 #endif
-    if (!mine) return BAM_OK;
+    if (!mine) return ((g >> lane) & 1u) ? BAM_ETIMEDOUT : BAM_OK;      /* a lane of g without an id never submitted */
     if (status == BAM_CPL_ERR) return BAM_ETIMEDOUT;       /* the id stays claimed: its completion may still arrive */
     put_cid(sq, cid);
     if (status != 0u) { status_fail(st, BAM_EIO, BAM_AT_NVME_STATUS, status); return BAM_EIO; }
     return BAM_OK;
+}
+
+/* One group, blocking: submit, then wait. */
+BAM_DEV int warp_io_group(uint32_t mask, uint32_t g, QueuePair* qp, uint64_t starting_lba, uint32_t n_blocks,
+                          uint64_t bus_addr, uint64_t bus_addr2, uint8_t opcode)
+{
+    const uint32_t cid = warp_submit_group(mask, g, qp, starting_lba, n_blocks, bus_addr, bus_addr2, opcode);
+    return warp_wait_group(mask, g, qp, cid);
+}
+
+/* Asynchronous pair for callers that keep several requests per thread in flight (the reference's
+ * access_data_async / poll_async, page_cache.h:1930-1959): every lane of `mask` calls them
+ * together, all on the same queue pair.  Submit as many rounds as wanted, then wait for each round
+ * with the ids it returned.  The commands a warp has outstanding must stay below half the queue
+ * depth (32 x rounds < qs / 2), or a later round would wait for slots its own commands occupy. */
+BAM_DEV uint32_t warp_io_submit(uint32_t mask, bool active, QueuePair* qp, uint64_t starting_lba, uint32_t n_blocks,
+                                uint64_t bus_addr, uint64_t bus_addr2, uint8_t opcode)
+{
+    const uint32_t g = __ballot_sync(mask, active);
+    if (g == 0u || __any_sync(mask, status_bad(qp->sq.status))) return BAM_CID_ERR;
+    return warp_submit_group(mask, g, qp, starting_lba, n_blocks, bus_addr, bus_addr2, opcode);
+}
+
+BAM_DEV int warp_io_wait(uint32_t mask, bool active, QueuePair* qp, uint32_t cid)
+{
+    const uint32_t g = __ballot_sync(mask, active);
+    if (g == 0u) return BAM_OK;
+    return warp_wait_group(mask, g, qp, cid);
 }
 
 /* Blocking I/O for a warp: every lane of `mask` calls this together; lanes with active == true

@@ -139,6 +139,13 @@ void* bam_array_device_ptr(bam_array_t a);         /* array_d_t<T>* (array_t::d_
 int bam_launch_block_read(bam_cache_t pc, uint64_t n_reqs, const uint64_t* pages_dev, uint64_t req_seed,
                           uint32_t* crc_out_dev, uint64_t* sum_out_dev, void* stream);
 
+/* The same with io_depth (1..8) requests in flight per thread, each in its own cache slot: the
+ * iodepth-block benchmark (benchmarks/iodepth-block/main.cu:97-147, access_data_async x N then
+ * poll_async x N, page_cache.h:1930-1959).  Needs 32 * io_depth < queue_depth / 2 and
+ * worker threads * io_depth cache slots. */
+int bam_launch_block_read_depth(bam_cache_t pc, uint64_t n_reqs, const uint64_t* pages_dev, uint64_t req_seed,
+                                uint32_t io_depth, uint32_t* crc_out_dev, uint64_t* sum_out_dev, void* stream);
+
 /* Array benchmark (benchmarks/array/main.cu:54-65): n_lanes reader lanes x reqs_per_lane
  * element reads through array[]; indices from idx_dev[lane*reqs_per_lane + k], or if idx_dev ==
  * NULL from PCG32 stream `lane` seeded with access_seed (bam_synth.h).  *sum_out_dev (device u64)

@@ -318,3 +318,21 @@ def test_bel_files_to_bfs(cuda, bam, orc, tmp_path):
     want, _ = orc.bfs(off, cols, src)
     assert (lv.cpu().numpy().view(np.uint32) == want).all() and gr.ctrl.status() == (0, "none", 0)
     gr.close()
+
+
+@pytest.mark.parametrize("io_depth", [2, 4])
+def test_block_read_with_several_requests_in_flight_per_thread(cuda, bam, orc, io_depth):
+    """The iodepth-block shape: each thread submits io_depth reads, then waits for each."""
+    seed, n_store_pages = 11, 1 << 13
+    ctrl = bam.Controller(n_store_pages * 4096, 0, queue_depth=1024, num_queues=16)
+    ctrl.configure(spin_timeout_ns=5 * SEC)
+    ctrl.fill_store(seed)
+    g, cb, th = ctrl.geometry()
+    cache = bam.PageCache(ctrl, 4096, g * th * io_depth)
+    n_reqs = (1 << 15) + 77                                  # ragged tail
+    crc = cuda.zeros(n_reqs, dtype=cuda.int32, device="cuda")
+    cache.block_read(n_reqs, req_seed=77, crc_out=crc, io_depth=io_depth)
+    assert ctrl.status() == (0, "none", 0)
+    _, want = orc.block_requests(seed, 77, n_store_pages, 4096, 0, n_reqs)
+    assert (crc.cpu().numpy().view(np.uint32) == want).all() and ctrl.served() == n_reqs
+    cache.close(); ctrl.close()
