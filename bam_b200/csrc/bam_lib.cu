@@ -193,15 +193,19 @@ struct BlockReadWork {
                     uint64_t pg = 0;
                     if (active) pg = pages ? pages[req[d]] : bam_block_request_page(req_seed, req[d], n_store_pages);
                     const uint64_t bus = slot_bus_addr(pc, (uint32_t)(gid * depth + d));     /* private slot */
-                    cid[d] = warp_io_submit(0xffffffffu, active, qp, pg * pc.n_blocks_per_page, pc.n_blocks_per_page, bus,
-                                            pc.page_size > 4096 ? bus + 4096 : 0, NVM_IO_READ);
+                    /* one request per thread: the blocking form, which also copes with queues shallower
+                     * than a warp; several per thread: submit now, wait below */
+                    if (depth == 1) cid[d] = (uint32_t)warp_io(0xffffffffu, active, qp, pg * pc.n_blocks_per_page, pc.n_blocks_per_page,
+                                                               bus, pc.page_size > 4096 ? bus + 4096 : 0, NVM_IO_READ);
+                    else cid[d] = warp_io_submit(0xffffffffu, active, qp, pg * pc.n_blocks_per_page, pc.n_blocks_per_page, bus,
+                                                 pc.page_size > 4096 ? bus + 4096 : 0, NVM_IO_READ);
                 }
             }
 #pragma unroll
             for (uint32_t d = 0; d < BAM_MAX_IO_DEPTH; d++) {
                 if (d < depth) {
                     const bool active = req[d] < n_reqs;
-                    const int rc = warp_io_wait(0xffffffffu, active, qp, cid[d]);
+                    const int rc = depth == 1 ? (int)cid[d] : warp_io_wait(0xffffffffu, active, qp, cid[d]);
                     if (__any_sync(0xffffffffu, rc != BAM_OK)) fail = true;
                     if (active && rc == BAM_OK && (crc_out || sum_out)) {
                         uint32_t crc = ~0u;
