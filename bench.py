@@ -56,6 +56,8 @@ def parse():
     ap.add_argument("--scale", type=int, default=0, help="R-MAT scale for bfs (default 24) / cc (default 26)")
     ap.add_argument("--cpu-sample-lanes", type=int, default=1 << 12)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sys-scope", action="store_true",
+                    help="synchronise doorbells and completions at system scope (default: device scope, see DESIGN.md)")
     return ap.parse_args()
 
 
@@ -178,6 +180,7 @@ def workload_config(args, world):
             "store_gib_total": args.store_gib, "shards": world, "cache_gib_per_gpu": args.cache_gib,
             "page_bytes": PAGE, "queues_per_gpu": args.queues, "queue_depth": args.depth,
             "reads_per_gpu_per_step": args.lanes * args.reqs, "zipf_s": 0.99, "cache_at_step_start": "empty",
+            "queue_scope": "system" if args.sys_scope else "device",
             "l2": "inputs (cache + access lists) far larger than L2; no explicit flush"}
 
 
@@ -433,6 +436,8 @@ def main():
     t0 = time.time()
     ctrl = bam_b200.Controller(n_local * PAGE, local_rank, queue_depth=args.depth, num_queues=args.queues)
     ctrl.configure(ctrl_blocks=args.ctrl_blocks, batch=args.batch)
+    if args.sys_scope:
+        ctrl.set_scope(1)
     ctrl.fill_store(STORE_SEED, first_elem=first_page * EPP)
     cache = bam_b200.PageCache(ctrl, PAGE, cache_pages)
     arr = bam_b200.Array(cache, n_local * EPP)
