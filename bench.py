@@ -569,7 +569,24 @@ def main():
         rst = cache.stats(reset=True)
         hit_rand = {"ms": float(np.mean(times[1:])), "reads": n_rand, "misses": rst["misses"],
                     "ok": int(rsum.item()) == int(rwant.item())}
-        del d_ridx
+        # the reference's cache benchmark in `array[]` mode: the 32 lanes of a warp read 32 consecutive
+        # elements per step, so one pin serves a whole warp (benchmarks/cache/main.cu:60-78)
+        seq = (torch.arange(n_rand // 2048, device=dev, dtype=torch.int64).view(-1, 1, 1) * 2048
+               + torch.arange(64, device=dev, dtype=torch.int64).view(1, 1, 64) * 32
+               + torch.arange(32, device=dev, dtype=torch.int64).view(1, 32, 1)).reshape(-1) % (n_scan * EPP)
+        rwant.zero_()
+        bam_b200.direct_checksum(seq, n_rand, STORE_SEED, first_page * EPP, rwant, stream=sptr)
+        times = []
+        for _ in range(4):
+            rsum.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); arr.read(1 << 20, 64, rsum, idx=seq, stream=sptr); b.record(stream)
+            stream.synchronize()
+            times.append(a.elapsed_time(b))
+        ctrl.check_status()
+        cache.stats(reset=True)
+        hit_seq = {"ms": float(np.mean(times[1:])), "reads": n_rand, "ok": int(rsum.item()) == int(rwant.item())}
+        del d_ridx, seq
 
     # ---- reduce over ranks ---------------------------------------------------------------------------
     tot = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
@@ -622,6 +639,10 @@ def main():
                                  "misses": hit_rand["misses"], "verified": hit_rand["ok"],
                                  "note": "2^26 uniform 8-byte reads over resident pages through the cache (all hits): one "
                                          "32-byte sector of page data per read plus bucket, slot word and two atomics"},
+            "hit_sequential_reads": {"reads_per_s": hit_seq["reads"] / (hit_seq["ms"] * 1e-3),
+                                     "gb_per_s": hit_seq["reads"] * 8 / (hit_seq["ms"] * 1e-3) / 1e9, "verified": hit_seq["ok"],
+                                     "note": "warm cache, each warp reads 32 consecutive 8-byte elements per step through "
+                                             "array[] (the reference's cache benchmark, 169 GiB/s in its published log)"},
             "clocks": clocks, "setup_s": setup_s, "numa_rank0": numa,
         }
         if not args.no_cpu_baseline and world == 1:

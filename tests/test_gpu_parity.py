@@ -336,3 +336,36 @@ def test_block_read_with_several_requests_in_flight_per_thread(cuda, bam, orc, i
     _, want = orc.block_requests(seed, 77, n_store_pages, 4096, 0, n_reqs)
     assert (crc.cpu().numpy().view(np.uint32) == want).all() and ctrl.served() == n_reqs
     cache.close(); ctrl.close()
+
+
+def test_randomised_configurations(cuda, bam, orc):
+    """Seeded random geometry: store size, cache size (from a handful of slots to everything),
+    queue count and depth, lane count and reads per lane -- the checksum must always equal the
+    oracle's and the cache must audit clean."""
+    rng = np.random.default_rng(20261125)
+    out = cuda.zeros(1, dtype=cuda.int64, device="cuda")
+    for case in range(10):
+        n_pages = int(rng.integers(64, 4096))
+        n_elems = n_pages * 512 - int(rng.integers(0, 511))            # ragged last page
+        slots = int(rng.choice([n_pages // 8 + 40, n_pages // 2 + 40, n_pages + 64]))
+        nq = int(rng.choice([1, 2, 3, 8, 32]))
+        depth = int(rng.choice([4, 16, 64, 256, 1024]))
+        lanes = int(rng.integers(1, 20000))
+        reqs = int(rng.integers(1, 12))
+        seed, aseed = int(rng.integers(1, 1 << 30)), int(rng.integers(1, 1 << 30))
+        ctrl = bam.Controller(n_pages * 4096, 0, queue_depth=depth, num_queues=nq)
+        ctrl.configure(spin_timeout_ns=5 * SEC)
+        ctrl.set_launch_timeout(60 * SEC)
+        # a resident warp can hold 32 pages while it waits for more: keep warps x 32 below the slots
+        ctrl.configure(ctrl_blocks=2)
+        ctrl.set_max_grid(2 + max(1, min(400, slots // 32 // 8)))
+        ctrl.fill_store(seed)
+        cache = bam.PageCache(ctrl, 4096, slots)
+        arr = bam.Array(cache, n_elems)
+        out.zero_()
+        arr.read(lanes, reqs, out, access_seed=aseed)
+        what = f"case {case}: pages {n_pages} slots {slots} queues {nq}x{depth} lanes {lanes}x{reqs}"
+        assert ctrl.status() == (0, "none", 0), what
+        assert cache.audit() == 0, what
+        assert u64(out) == orc.array_checksum(seed, n_elems, aseed, 0, lanes, reqs), what
+        arr.close(); cache.close(); ctrl.close()
