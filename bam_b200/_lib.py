@@ -42,6 +42,7 @@ SIGNATURES = {
     "bam_ctrl_device_controller": (vp, [vp]),
     "bam_ctrl_emu_descriptor": (ci, [vp, vp, C.c_size_t]),
     "bam_cache_create": (ci, [C.POINTER(vp), vp, u32, u64]),
+    "bam_cache_create_multi": (ci, [C.POINTER(vp), C.POINTER(vp), u32, u32, u64]),
     "bam_cache_destroy": (ci, [vp]),
     "bam_cache_stats": (ci, [vp, C.POINTER(CacheStats), ci]),
     "bam_cache_invalidate": (ci, [vp]),
@@ -50,6 +51,7 @@ SIGNATURES = {
     "bam_cache_audit_noalloc": (ci, [vp, vp, vp]),
     "bam_cache_descriptor": (ci, [vp, vp, C.c_size_t]),
     "bam_array_create": (ci, [C.POINTER(vp), vp, u64, u32, u64]),
+    "bam_array_create_dist": (ci, [C.POINTER(vp), vp, u64, u32, u64, u32]),
     "bam_array_destroy": (ci, [vp]),
     "bam_array_device_ptr": (vp, [vp]),
     "bam_launch_block_read": (ci, [vp, u64, vp, u64, vp, vp, vp]),

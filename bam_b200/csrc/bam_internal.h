@@ -4,6 +4,8 @@
 #ifndef BAM_INTERNAL_H
 #define BAM_INTERNAL_H
 
+#include <vector>
+
 #include "bam/abi_types.h"
 #include "bam/array.cuh"
 #include "bam/launch.cuh"
@@ -45,10 +47,17 @@ struct bam_ctrl {
     uint32_t sys_scope = 0;           /* scope of doorbell/completion synchronisation          */
     uint32_t max_grid = 0;            /* 0 = as many blocks as fit                            */
     uint32_t last_grid = 0;
+    /* membership in a multi-controller cache (bam_cache_create_multi) */
+    struct bam_cache* group = nullptr;
+    bam_ctrl* lead = nullptr;         /* first controller of the group: owner of the shared status block */
+    uint32_t group_index = 0;
+    bam_emu_qp_t* own_emu_qps = nullptr;   /* the arena's array, while d_emu_qps points into the group's */
 };
 
 struct bam_cache {
-    bam_ctrl* ctrl = nullptr;
+    bam_ctrl* ctrl = nullptr;         /* the (first) backing controller: launches run with its descriptor */
+    std::vector<bam_ctrl*> members;   /* all backing controllers when there are several */
+    bam_emu_qp_t* d_group_qps = nullptr;   /* controller-side state of all members' queues, contiguous */
     page_cache_d_t d;
     uint64_t n_buckets = 0;
     uint32_t n_ranges = 0;

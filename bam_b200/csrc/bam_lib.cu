@@ -295,8 +295,6 @@ struct FlushWork {
         const uint32_t wpb = blockDim.x >> 5;
         const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
         const uint64_t nwarps = (uint64_t)nvb * wpb;
-        Controller* c = pc.d_ctrl;
-        QueuePair* qp = c->d_qps + ((uint32_t)warp % c->n_qps);
         for (uint64_t s0 = warp * 32; s0 < pc.n_slots; s0 += nwarps * 32) {
             const uint64_t s = s0 + lane;
             uint32_t st = 0;
@@ -304,9 +302,7 @@ struct FlushWork {
             if (s < pc.n_slots) { st = ld_acquire_gpu(&pc.slots[s].state); tag = ld_relaxed_gpu(&pc.slots[s].tag); }
             const bool dirty = (st & (BAM_VALID | BAM_DIRTY)) == (BAM_VALID | BAM_DIRTY) && tag != BAM_TAG_NONE;
             if (!__any_sync(0xffffffffu, dirty)) continue;
-            const int rc = warp_io(0xffffffffu, dirty, qp, dirty ? backing_page_of_tag(pc, tag) * pc.n_blocks_per_page : 0,
-                                   pc.n_blocks_per_page, dirty ? slot_bus_addr(pc, (uint32_t)s) : 0,
-                                   dirty ? slot_prp2(pc, (uint32_t)s) : 0, NVM_IO_WRITE);
+            const int rc = warp_write_back(0xffffffffu, dirty, pc, tag, (uint32_t)s);
             if (dirty && rc == BAM_OK) atom_and_release(&pc.slots[s].state, ~BAM_DIRTY);
             if (__any_sync(0xffffffffu, rc != BAM_OK)) break;
         }
@@ -422,10 +418,18 @@ extern "C" const char* bam_strerror(int code)
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 static uint32_t log2_u32(uint64_t x) { uint32_t l = 0; while ((1ull << l) < x) l++; return l; }
 
+/* The status block a controller's waits report into: its own, or its group's. */
+static bam_status_t* status_block(bam_ctrl* c) { return c->lead ? c->lead->d_status : c->d_status; }
+
 /* Build the power-on image of every queue structure on the host and upload it. */
 static int upload_queue_image(bam_ctrl* c)
 {
     std::vector<uint8_t> img(c->arena_bytes, 0);
+    std::vector<bam_emu_qp_t> emu_qps(c->n_qps);
+    memset(emu_qps.data(), 0, emu_qps.size() * sizeof(bam_emu_qp_t));
+    /* a controller that backs a multi-controller cache reports into the status block of the
+     * cache's first controller, so that every waiter of a launch sees the same error state */
+    bam_status_t* const d_status = status_block(c);
     uint8_t* dev = (uint8_t*)c->arena;
     auto host_of = [&](void* devp) { return img.data() + ((uint8_t*)devp - dev); };
     const uint32_t qs = c->qdepth;
@@ -443,7 +447,7 @@ static int upload_queue_image(bam_ctrl* c)
             nq->no = (uint16_t)(q + 1);
             nq->es = is_cq ? sizeof(nvm_cpl_t) : sizeof(nvm_cmd_t);
             nq->phase = 1; nq->local = c->sys_scope ? 0 : 1;
-            nq->status = c->d_status;
+            nq->status = d_status;
             nq->db = c->d_doorbells + (size_t)(2 * (q + 1) + is_cq) * BAM_DB_STRIDE_WORDS;
             nq->vaddr = is_cq ? (void*)(c->d_cq_mem + (size_t)q * qs) : (void*)(c->d_sq_mem + (size_t)q * qs);
             nq->ioaddr = (uint64_t)nq->vaddr;
@@ -453,22 +457,27 @@ static int upload_queue_image(bam_ctrl* c)
         }
         uint32_t* tk = (uint32_t*)host_of(c->d_tickets + (size_t)q * qs);
         for (uint32_t i = 0; i < qs; i++) tk[i] = i;            /* slot i is first used by ticket i */
-        bam_emu_qp_t* e = (bam_emu_qp_t*)host_of(c->d_emu_qps + q);
+        bam_emu_qp_t* e = &emu_qps[q];
         e->sq_mem = c->d_sq_mem + (size_t)q * qs;
         e->cq_mem = c->d_cq_mem + (size_t)q * qs;
         e->sq_db = c->d_doorbells + (size_t)(2 * (q + 1)) * BAM_DB_STRIDE_WORDS;
         e->cq_db = c->d_doorbells + (size_t)(2 * (q + 1) + 1) * BAM_DB_STRIDE_WORDS;
         e->qs = qs; e->qs_log2 = log2_u32(qs);
         e->sqid = e->cqid = (uint16_t)(q + 1);
+        e->ctrl_index = c->group_index;
+        e->store = c->store_dev; e->store_bytes = c->store_bytes;
+        e->fault = c->d_fault; e->served = c->d_served;
     }
     Controller* ctl = (Controller*)host_of(c->d_ctrl);
     ctl->d_qps = c->d_qps; ctl->n_qps = c->n_qps; ctl->page_size = 4096;
     ctl->blk_size = c->lba_bytes; ctl->blk_size_log = log2_u32(c->lba_bytes);
-    ctl->status = c->d_status;
+    ctl->status = d_status;
     bam_status_t* st = (bam_status_t*)host_of(c->d_status);
     st->spin_timeout_ns = c->spin_timeout_ns;
     st->launch_timeout_ns = c->launch_timeout_ns;
     CK(cudaMemcpy(c->arena, img.data(), c->arena_bytes, cudaMemcpyHostToDevice));
+    /* the controller-side queue state lives in the arena, or in the group's array once grouped */
+    CK(cudaMemcpy(c->d_emu_qps, emu_qps.data(), emu_qps.size() * sizeof(bam_emu_qp_t), cudaMemcpyHostToDevice));
     return BAM_OK;
 }
 
@@ -529,11 +538,9 @@ extern "C" int bam_ctrl_create(bam_ctrl_t* out, int device, uint64_t store_bytes
 
     c->emu.qps = c->d_emu_qps; c->emu.n_qps = n_queues;
     c->emu.n_ctrl_blocks = BAM_DEFAULT_CTRL_BLOCKS;
-    c->emu.store = c->store_dev; c->emu.store_bytes = store_bytes;
     c->emu.lba_log2 = log2_u32(lba_bytes); c->emu.mps_log2 = 12;
     c->emu.batch = 32; c->emu.sys_scope = c->sys_scope;
     c->emu.consumers_remaining = c->d_remaining; c->emu.status = c->d_status;
-    c->emu.fault = c->d_fault; c->emu.served = c->d_served;
     int rc = upload_queue_image(c);
     if (rc != BAM_OK) { cudaFree(c->arena); cudaFreeHost(c->store_host); delete c; return rc; }
     *out = c;
@@ -576,7 +583,7 @@ extern "C" int bam_ctrl_set_launch_timeout(bam_ctrl_t c, uint64_t launch_timeout
     CK(cudaSetDevice(c->device));
     CK(cudaDeviceSynchronize());
     c->launch_timeout_ns = launch_timeout_ns;
-    CK(cudaMemcpy(&c->d_status->launch_timeout_ns, &launch_timeout_ns, 8, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(&status_block(c)->launch_timeout_ns, &launch_timeout_ns, 8, cudaMemcpyHostToDevice));
     return BAM_OK;
 }
 
@@ -589,7 +596,7 @@ extern "C" int bam_ctrl_configure(bam_ctrl_t c, uint32_t n_ctrl_blocks, uint32_t
     if (spin_timeout_ns) {
         c->spin_timeout_ns = spin_timeout_ns;
         CK(cudaDeviceSynchronize());
-        CK(cudaMemcpy(&c->d_status->spin_timeout_ns, &spin_timeout_ns, 8, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(&status_block(c)->spin_timeout_ns, &spin_timeout_ns, 8, cudaMemcpyHostToDevice));
     }
     return BAM_OK;
 }
@@ -627,11 +634,11 @@ extern "C" int bam_ctrl_status(bam_ctrl_t c, bam_status_out_t* out, int clear)
     CK(cudaSetDevice(c->device));
     CK(cudaDeviceSynchronize());
     bam_status_t st;
-    CK(cudaMemcpy(&st, c->d_status, sizeof st, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(&st, status_block(c), sizeof st, cudaMemcpyDeviceToHost));
     out->code = st.code; out->where = st.where; out->detail = st.detail;
     if (clear && st.code) {
         st.code = 0; st.where = 0; st.detail = 0;
-        CK(cudaMemcpy(c->d_status, &st, sizeof st, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(status_block(c), &st, sizeof st, cudaMemcpyHostToDevice));
     }
     return BAM_OK;
 }
@@ -641,8 +648,8 @@ extern "C" int bam_ctrl_profile(bam_ctrl_t c, uint64_t* out32, int reset)
     if (!c || !out32) return BAM_EINVAL;
     CK(cudaSetDevice(c->device));
     CK(cudaDeviceSynchronize());
-    CK(cudaMemcpy(out32, c->d_status->prof, sizeof(uint64_t) * 32, cudaMemcpyDeviceToHost));
-    if (reset) CK(cudaMemset(c->d_status->prof, 0, sizeof(uint64_t) * 32));
+    CK(cudaMemcpy(out32, status_block(c)->prof, sizeof(uint64_t) * 32, cudaMemcpyDeviceToHost));
+    if (reset) CK(cudaMemset(status_block(c)->prof, 0, sizeof(uint64_t) * 32));
     return BAM_OK;
 }
 
@@ -685,12 +692,42 @@ static int cache_reset_device(bam_cache* pc)
     return BAM_OK;
 }
 
-extern "C" int bam_cache_create(bam_cache_t* out, bam_ctrl_t ctrl, uint32_t page_size, uint64_t n_pages)
+static void cache_free_device(bam_cache* pc)
+{
+    page_cache_d_t& d = pc->d;
+    cudaFree(d.base_addr); cudaFree(d.slots); cudaFree(d.table); cudaFree(d.clock_hand);
+    cudaFree(d.stats); cudaFree(d.range_page_starts); cudaFree(d.range_dists); cudaFree(d.prp_lists);
+    cudaFree(d.d_ctrls); cudaFree(pc->d_group_qps);
+}
+
+/* Undo the grouping of bam_cache_create_multi: every member gets its own controller-side queue
+ * state and status block back (queues are reset; nothing is in flight when a cache is destroyed). */
+static void cache_ungroup(bam_cache* pc)
+{
+    for (bam_ctrl* m : pc->members) {
+        if (m->group != pc) continue;
+        m->group = nullptr; m->lead = nullptr; m->group_index = 0;
+        m->d_emu_qps = m->own_emu_qps;
+        m->emu.qps = m->own_emu_qps; m->emu.n_qps = m->n_qps;
+        (void)upload_queue_image(m);
+    }
+}
+
+extern "C" int bam_cache_create_multi(bam_cache_t* out, const bam_ctrl_t* ctrls, uint32_t n_ctrls, uint32_t page_size,
+                                      uint64_t n_pages)
 {
     if (!out) return BAM_EINVAL;
     *out = nullptr;
-    if (!ctrl || n_pages == 0 || n_pages >= 0xffffffull) return BAM_EINVAL;
+    if (!ctrls || n_ctrls == 0 || n_ctrls > BAM_MAX_CTRLS || n_pages == 0 || n_pages >= 0xffffffull) return BAM_EINVAL;
+    bam_ctrl* ctrl = ctrls[0];
+    if (!ctrl) return BAM_EINVAL;
     if (page_size < 512 || (page_size & (page_size - 1)) || page_size < ctrl->lba_bytes || page_size > (1u << 20)) return BAM_EINVAL;
+    for (uint32_t k = 0; k < n_ctrls; k++) {
+        bam_ctrl* m = ctrls[k];
+        if (!m || m->device != ctrl->device || m->lba_bytes != ctrl->lba_bytes || m->sys_scope != ctrl->sys_scope) return BAM_EINVAL;
+        for (uint32_t j = 0; j < k; j++) if (ctrls[j] == m) return BAM_EINVAL;
+        if (n_ctrls > 1 && m->group) return BAM_EBUSY;      /* a controller backs one multi-controller cache at a time */
+    }
     CK(cudaSetDevice(ctrl->device));
     bam_cache* pc = new (std::nothrow) bam_cache();
     if (!pc) return BAM_ENOMEM;
@@ -703,10 +740,12 @@ extern "C" int bam_cache_create(bam_cache_t* out, bam_ctrl_t ctrl, uint32_t page
     d.n_slots = (uint32_t)n_pages;
     d.bucket_mask = (uint32_t)(pc->n_buckets - 1);
     d.n_blocks_per_page = page_size / ctrl->lba_bytes;
-    d.d_ctrl = ctrl->d_ctrl; d.status = ctrl->d_status;
+    d.d_ctrl = ctrl->d_ctrl; d.status = status_block(ctrl); d.n_ctrls = n_ctrls;
     d.n_ranges_bits = BAM_RANGE_BITS; d.n_ranges_mask = BAM_MAX_RANGES - 1;
     const uint32_t chunks = page_size / 4096;
     d.prp_list_stride = chunks > 2 ? chunks - 1 : 0;
+    uint32_t total_qps = 0;
+    for (uint32_t k = 0; k < n_ctrls; k++) total_qps += ctrls[k]->n_qps;
     cudaError_t e = cudaSuccess;
     auto alloc = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(p, bytes); };
     alloc((void**)&d.base_addr, n_pages * (size_t)page_size);
@@ -715,26 +754,58 @@ extern "C" int bam_cache_create(bam_cache_t* out, bam_ctrl_t ctrl, uint32_t page
     alloc((void**)&d.clock_hand, 8);
     alloc((void**)&d.stats, sizeof(bam_stat_stripe_t) * BAM_STAT_STRIPES);
     alloc((void**)&d.range_page_starts, 8 * BAM_MAX_RANGES);
+    alloc((void**)&d.range_dists, 4 * BAM_MAX_RANGES);
+    alloc((void**)&d.d_ctrls, sizeof(Controller*) * n_ctrls);
     if (d.prp_list_stride) alloc((void**)&d.prp_lists, n_pages * d.prp_list_stride * 8);
+    if (n_ctrls > 1) alloc((void**)&pc->d_group_qps, sizeof(bam_emu_qp_t) * total_qps);
     if (e != cudaSuccess) {
         g_last_cuda = e; (void)cudaGetLastError();
-        cudaFree(d.base_addr); cudaFree(d.slots); cudaFree(d.table); cudaFree(d.clock_hand);
-        cudaFree(d.stats); cudaFree(d.range_page_starts); cudaFree(d.prp_lists);
+        cache_free_device(pc);
         delete pc;
         return BAM_ENOMEM;
     }
+    auto fail = [&](int rc) { cache_ungroup(pc); cache_free_device(pc); delete pc; return rc; };
     if (d.prp_list_stride) {
         std::vector<uint64_t> lists(n_pages * d.prp_list_stride);
         for (uint64_t s = 0; s < n_pages; s++)
             for (uint32_t k = 0; k < d.prp_list_stride; k++)
                 lists[s * d.prp_list_stride + k] = (uint64_t)(d.base_addr + s * page_size + (size_t)(k + 1) * 4096);
-        CK(cudaMemcpy(d.prp_lists, lists.data(), lists.size() * 8, cudaMemcpyHostToDevice));
+        if (cudaMemcpy(d.prp_lists, lists.data(), lists.size() * 8, cudaMemcpyHostToDevice) != cudaSuccess) return fail(BAM_ECUDA);
     }
-    CK(cudaMemset(d.range_page_starts, 0, 8 * BAM_MAX_RANGES));
+    std::vector<Controller*> h_ctrls(n_ctrls);
+    for (uint32_t k = 0; k < n_ctrls; k++) h_ctrls[k] = ctrls[k]->d_ctrl;
+    if (cudaMemcpy(d.d_ctrls, h_ctrls.data(), sizeof(Controller*) * n_ctrls, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemset(d.range_page_starts, 0, 8 * BAM_MAX_RANGES) != cudaSuccess ||
+        cudaMemset(d.range_dists, 0, 4 * BAM_MAX_RANGES) != cudaSuccess)
+        return fail(BAM_ECUDA);
+    if (n_ctrls > 1) {
+        /* One launch serves every member: their controller-side queue state moves into one
+         * contiguous array, which the first controller's launch descriptor then covers, and all of
+         * them report into the first controller's status block. */
+        if (cudaDeviceSynchronize() != cudaSuccess) return fail(BAM_ECUDA);
+        uint32_t at = 0;
+        for (uint32_t k = 0; k < n_ctrls; k++) {
+            bam_ctrl* m = ctrls[k];
+            pc->members.push_back(m);
+            m->group = pc; m->lead = (k == 0) ? nullptr : ctrl; m->group_index = k;
+            m->own_emu_qps = m->emu.qps;
+            m->d_emu_qps = pc->d_group_qps + at;
+            m->emu.qps = m->d_emu_qps;
+            at += m->n_qps;
+            const int rc = upload_queue_image(m);
+            if (rc != BAM_OK) return fail(rc);
+        }
+        ctrl->emu.qps = pc->d_group_qps; ctrl->emu.n_qps = total_qps;
+    }
     int rc = cache_reset_device(pc);
-    if (rc != BAM_OK) return rc;
+    if (rc != BAM_OK) return fail(rc);
     *out = pc;
     return BAM_OK;
+}
+
+extern "C" int bam_cache_create(bam_cache_t* out, bam_ctrl_t ctrl, uint32_t page_size, uint64_t n_pages)
+{
+    return bam_cache_create_multi(out, &ctrl, 1, page_size, n_pages);
 }
 
 extern "C" int bam_cache_destroy(bam_cache_t pc)
@@ -742,9 +813,8 @@ extern "C" int bam_cache_destroy(bam_cache_t pc)
     if (!pc) return BAM_EINVAL;
     cudaSetDevice(pc->ctrl->device);
     cudaDeviceSynchronize();
-    page_cache_d_t& d = pc->d;
-    cudaFree(d.base_addr); cudaFree(d.slots); cudaFree(d.table); cudaFree(d.clock_hand);
-    cudaFree(d.stats); cudaFree(d.range_page_starts); cudaFree(d.prp_lists);
+    cache_ungroup(pc);
+    cache_free_device(pc);
     delete pc;
     return BAM_OK;
 }
@@ -808,14 +878,26 @@ extern "C" int bam_cache_descriptor(bam_cache_t pc, void* out, size_t out_bytes)
 
 /* ---- arrays ----------------------------------------------------------------------------------- */
 
-extern "C" int bam_array_create(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
-                                uint64_t store_byte_offset)
+extern "C" int bam_array_create_dist(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
+                                     uint64_t store_byte_offset, uint32_t dist)
 {
     if (!out) return BAM_EINVAL;
     *out = nullptr;
     if (!pc || n_elems == 0 || (elem_bytes != 4 && elem_bytes != 8)) return BAM_EINVAL;
+    if (dist != BAM_DIST_REPLICATE && dist != BAM_DIST_STRIPE) return BAM_EINVAL;
     if (store_byte_offset % pc->d.page_size) return BAM_EINVAL;
-    if (store_byte_offset + n_elems * elem_bytes > pc->ctrl->store_bytes) return BAM_EINVAL;
+    const uint64_t page_count = (n_elems * elem_bytes + pc->d.page_size - 1) / pc->d.page_size;
+    const uint32_t n_ctrls = pc->d.n_ctrls;
+    /* bytes of the range that each controller must hold, from store_byte_offset on */
+    const uint64_t per_ctrl = (dist == BAM_DIST_STRIPE && n_ctrls > 1)
+                                  ? (page_count + n_ctrls - 1) / n_ctrls * pc->d.page_size
+                                  : n_elems * elem_bytes;
+    if (pc->members.empty()) {
+        if (store_byte_offset + per_ctrl > pc->ctrl->store_bytes) return BAM_EINVAL;
+    } else {
+        for (bam_ctrl* m : pc->members)
+            if (store_byte_offset + per_ctrl > m->store_bytes) return BAM_EINVAL;
+    }
     if (pc->n_ranges >= BAM_MAX_RANGES) return BAM_ENOSPC;
     CK(cudaSetDevice(pc->ctrl->device));
     bam_array* a = new (std::nothrow) bam_array();
@@ -825,8 +907,9 @@ extern "C" int bam_array_create(bam_array_t* out, bam_cache_t pc, uint64_t n_ele
     r.index_start = 0; r.count = n_elems; r.range_id = pc->n_ranges;
     r.page_start_offset = 0;
     r.page_start = store_byte_offset / pc->d.page_size;
-    r.page_count = (n_elems * elem_bytes + pc->d.page_size - 1) / pc->d.page_size;
+    r.page_count = page_count;
     r.n_elems_per_page = pc->d.page_size / elem_bytes;
+    r.dist = dist; r.pad_ = 0;
     r.cache = pc->d;
     struct { uint64_t n_elems, start_offset, n_ranges; void* d_ranges; } h_arr;
     cudaError_t e = cudaMalloc(&a->d_range, sizeof r);
@@ -835,10 +918,17 @@ extern "C" int bam_array_create(bam_array_t* out, bam_cache_t pc, uint64_t n_ele
     h_arr.n_elems = n_elems; h_arr.start_offset = store_byte_offset; h_arr.n_ranges = 1; h_arr.d_ranges = a->d_range;
     if (e == cudaSuccess) e = cudaMemcpy(a->d_array, &h_arr, sizeof h_arr, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(pc->d.range_page_starts + r.range_id, &r.page_start, 8, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(pc->d.range_dists + r.range_id, &dist, 4, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) { g_last_cuda = e; cudaFree(a->d_range); cudaFree(a->d_array); delete a; return BAM_ECUDA; }
     pc->n_ranges++;
     *out = a;
     return BAM_OK;
+}
+
+extern "C" int bam_array_create(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
+                                uint64_t store_byte_offset)
+{
+    return bam_array_create_dist(out, pc, n_elems, elem_bytes, store_byte_offset, BAM_DIST_REPLICATE);
 }
 
 extern "C" int bam_array_destroy(bam_array_t a)

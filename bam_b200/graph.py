@@ -96,15 +96,32 @@ class CsrGraph:
             check(lib.bam_ctrl_write_store_from_device(self.ctrl.h, self.off_bytes, _ptr(cols), self.m * 8, None), "write cols")
         torch.cuda.synchronize()
         self.cache = PageCache(self.ctrl, page_size, cache_pages)
-        self.offsets = Array(self.cache, self.n + 1, 8, 0)
-        self.cols = Array(self.cache, max(1, self.m), 8, self.off_bytes)
+        self._owns = True
+        self._bind(cuda_device)
+
+    @classmethod
+    def over_cache(cls, cache, n_vertices, n_edges, off_bytes, dist=0, cuda_device=0):
+        """A graph whose store image (offsets padded to `off_bytes`, then the edges) is already on the
+        media behind `cache` -- one controller or several, laid out as `dist` says."""
+        g = cls.__new__(cls)
+        g.n, g.m, g.off_bytes = n_vertices, n_edges, off_bytes
+        g.ctrl, g.cache, g._owns = cache.ctrl, cache, False
+        g._bind(cuda_device, dist)
+        return g
+
+    def _bind(self, cuda_device, dist=0):
+        import torch
+        self.offsets = Array(self.cache, self.n + 1, 8, 0, dist)
+        self.cols = Array(self.cache, max(1, self.m), 8, self.off_bytes, dist)
         self.device = cuda_device
         # per-level scratch for the work items of hub vertices
-        self.scratch_bytes = lib.bam_graph_scratch_bytes(max(1, self.m))
+        self.scratch_bytes = self.ctrl.lib.bam_graph_scratch_bytes(max(1, self.m))
         self.scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=f"cuda:{cuda_device}")
 
     def close(self):
-        self.cols.close(); self.offsets.close(); self.cache.close(); self.ctrl.close()
+        self.cols.close(); self.offsets.close()
+        if self._owns:
+            self.cache.close(); self.ctrl.close()
 
     def bfs(self, source):
         """Level-synchronous BFS from `source`; returns (levels uint32 tensor as int32 bits, n_levels, edges_scanned)."""

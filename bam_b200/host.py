@@ -111,13 +111,32 @@ class Controller:
         return g.value, cb.value, t.value
 
 
+REPLICATE, STRIPE = 0, 1       # data_dist_t (include/page_cache.h:42 in the reference)
+
+
+def backing_location(page, n_ctrls, dist, page_start=0):
+    """(controller, backing page) of page `page` of a range: get_backing_ctrl_ / get_backing_page_
+    (include/page_cache.h:558-582 in the reference).  controller is None when any will do."""
+    if dist == STRIPE and n_ctrls > 1:
+        return page % n_ctrls, page_start + page // n_ctrls
+    return None, page_start + page
+
+
 class PageCache:
-    """page_cache_t(page_size, n_pages, gpu, ctrl, ...)."""
+    """page_cache_t(page_size, n_pages, gpu, ctrl, max_range, ctrls): `ctrl` is one Controller or
+    the list of controllers the cache sits in front of."""
 
     def __init__(self, ctrl, page_size=4096, n_pages=65536):
-        self.lib, self.ctrl = ctrl.lib, ctrl
+        ctrls = list(ctrl) if isinstance(ctrl, (list, tuple)) else [ctrl]
+        self.ctrls, self.ctrl = ctrls, ctrls[0]
+        self.lib = self.ctrl.lib
         self.h = C.c_void_p()
-        check(self.lib.bam_cache_create(C.byref(self.h), ctrl.h, page_size, n_pages), "bam_cache_create")
+        if len(ctrls) == 1:
+            check(self.lib.bam_cache_create(C.byref(self.h), self.ctrl.h, page_size, n_pages), "bam_cache_create")
+        else:
+            hs = (C.c_void_p * len(ctrls))(*[c.h for c in ctrls])
+            check(self.lib.bam_cache_create_multi(C.byref(self.h), hs, len(ctrls), page_size, n_pages),
+                  "bam_cache_create_multi")
         self.page_size, self.n_pages = page_size, n_pages
 
     def close(self):
@@ -163,12 +182,12 @@ class PageCache:
 class Array:
     """array_t<T>(n_elems, disk_start_offset, {range_t<T>(...)}) for a single range."""
 
-    def __init__(self, cache, n_elems, elem_bytes=8, store_byte_offset=0):
+    def __init__(self, cache, n_elems, elem_bytes=8, store_byte_offset=0, dist=REPLICATE):
         self.lib, self.cache = cache.lib, cache
         self.h = C.c_void_p()
-        check(self.lib.bam_array_create(C.byref(self.h), cache.h, n_elems, elem_bytes, store_byte_offset),
-              "bam_array_create")
-        self.n_elems, self.elem_bytes = n_elems, elem_bytes
+        check(self.lib.bam_array_create_dist(C.byref(self.h), cache.h, n_elems, elem_bytes, store_byte_offset, dist),
+              "bam_array_create_dist")
+        self.n_elems, self.elem_bytes, self.dist = n_elems, elem_bytes, dist
 
     def close(self):
         if self.h:

@@ -57,7 +57,7 @@ def parse():
     ap.add_argument("--cpu-sample-lanes", type=int, default=1 << 12)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sys-scope", action="store_true",
-                    help="synchronise doorbells and completions at system scope (default: device scope, see DESIGN.md)")
+                    help="synchronise doorbells and completions at system scope (default: device scope, enough when the controller runs on the same GPU)")
     return ap.parse_args()
 
 

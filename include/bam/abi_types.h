@@ -164,13 +164,20 @@ typedef struct BAM_ALIGNAS(64) {
     uint32_t* cq_db;
     uint32_t qs, qs_log2;
     uint16_t sqid, cqid;
-    uint32_t pad;
+    uint32_t ctrl_index;    /* which controller of a multi-controller launch owns this queue */
+    /* the media behind this queue: several controllers can be served by one launch, every queue
+     * carries its own controller's store, fault plan and statistics */
+    uint8_t* store;         /* backing store: device-visible mapping of pinned host memory   */
+    uint64_t store_bytes;
+    struct bam_fault_s* fault;
+    uint64_t* served;       /* commands completed, for statistics                            */
+    uint64_t pad[4];
 } bam_emu_qp_t;
 
 #define BAM_FAULT_NONE 0
 #define BAM_FAULT_DROP_CPL 1     /* swallow the completion of the nth command           */
 #define BAM_FAULT_STATUS 2       /* complete the nth command with `status`               */
-typedef struct {
+typedef struct bam_fault_s {
     uint32_t mode;
     uint32_t status;
     uint64_t nth;
@@ -181,16 +188,12 @@ typedef struct {
     bam_emu_qp_t* qps;
     uint32_t n_qps;
     uint32_t n_ctrl_blocks;     /* blocks [0, n_ctrl_blocks) of a fused launch run the controller */
-    uint8_t* store;             /* backing store: device-visible mapping of pinned host memory   */
-    uint64_t store_bytes;
     uint32_t lba_log2;          /* logical block size                                            */
     uint32_t mps_log2;          /* controller memory page size (PRP granule)                     */
     uint32_t batch;             /* commands one warp fetches per lock hold                        */
     uint32_t sys_scope;         /* 1: doorbells/completions use system scope, 0: device scope      */
     uint32_t* consumers_remaining;
     bam_status_t* status;
-    bam_fault_t* fault;
-    uint64_t* served;           /* commands completed, for statistics                            */
 } bam_emu_d_t;
 
 /* ---- page cache -------------------------------------------------------------------------
@@ -225,6 +228,15 @@ typedef struct BAM_ALIGNAS(16) {
 #define BAM_STAT_STRIPES 64
 typedef struct BAM_ALIGNAS(32) { uint64_t hits, misses, read_ios, pad; } bam_stat_stripe_t;
 
+/* How a range's pages are laid out over the controllers of a cache (data_dist_t of
+ * include/page_cache.h:42, :558-582 in the reference): REPLICATE = every controller holds the whole
+ * range, a read may go to any of them and a write-back goes to all; STRIPE = page p of the range
+ * lives on controller p % n at backing page page_start + p / n. */
+#define BAM_DIST_REPLICATE 0u
+#define BAM_DIST_STRIPE 1u
+#define BAM_ALL_CTRLS 0xffffffffu
+#define BAM_MAX_CTRLS 16
+
 #define BAM_MAX_RANGES 64
 #define BAM_RANGE_BITS 6
 
@@ -238,7 +250,11 @@ typedef struct {
     uint32_t bucket_mask;        /* n_buckets - 1 (power of two)                 */
     uint32_t n_blocks_per_page;  /* logical blocks per cache page                */
     uint64_t* clock_hand;        /* the sweep position (page_ticket in the reference) */
-    Controller* d_ctrl;          /* backing controller                           */
+    Controller* d_ctrl;          /* backing controller (the first one when there are several) */
+    Controller** d_ctrls;        /* [n_ctrls] all backing controllers             */
+    uint32_t n_ctrls;
+    uint32_t pad_;
+    uint32_t* range_dists;       /* [BAM_MAX_RANGES] BAM_DIST_* of each range      */
     bam_stat_stripe_t* stats;    /* [BAM_STAT_STRIPES]                           */
     bam_status_t* status;
     uint32_t n_ranges_bits, n_ranges_mask;

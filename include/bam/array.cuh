@@ -19,8 +19,6 @@
 
 namespace bam {
 
-BAM_DEV uint32_t default_queue() { return (blockIdx.x * blockDim.x + threadIdx.x) >> 5; }
-
 template <typename T>
 struct range_d_t {
     uint64_t index_start;        /* first element index covered by the range        */
@@ -30,23 +28,27 @@ struct range_d_t {
     uint64_t page_start;         /* first backing page of the range                 */
     uint64_t page_count;
     uint64_t n_elems_per_page;
+    uint32_t dist;               /* BAM_DIST_REPLICATE / BAM_DIST_STRIPE over the cache's controllers */
+    uint32_t pad_;
     page_cache_d_t cache;
 
     BAM_DEV uint64_t get_page(size_t i) const { return ((i - index_start) * sizeof(T) + page_start_offset) >> cache.page_size_log; }
     BAM_DEV uint64_t get_subindex(size_t i) const { return ((i - index_start) * sizeof(T) + page_start_offset) & cache.page_size_minus_1; }
     BAM_DEV uint64_t get_global_address(size_t page) const { return (page << cache.n_ranges_bits) | range_id; }
-    BAM_DEV uint64_t get_backing_page(size_t page) const { return page_start + page; }
+    BAM_DEV uint64_t get_backing_page(size_t page) const { return backing_page_of(page_start, page, cache.n_ctrls, dist); }
+    BAM_DEV uint32_t get_backing_ctrl(size_t page) const { return backing_ctrl_of(page, cache.n_ctrls, dist); }
     BAM_DEV uint64_t get_cache_page_addr(uint32_t slot) const { return (uint64_t)(cache.base_addr + (size_t)slot * cache.page_size); }
 
     /* returns the cache slot (BAM_SLOT_ERR on failure); the page stays pinned `count` times */
     BAM_DEV uint32_t acquire_page(size_t page, uint32_t cnt, bool write, uint32_t queue) const
     {
-        return cache_acquire(cache, get_global_address(page), cnt, get_backing_page(page), queue, write);
+        return cache_acquire(cache, get_global_address(page), cnt, get_backing_page(page), queue, write, get_backing_ctrl(page));
     }
     /* warp-cooperative form: every lane of `mask` calls it, lanes with want == true pin `page` */
     BAM_DEV uint32_t acquire_page_warp(uint32_t mask, bool want, size_t page, uint32_t cnt, bool write, uint32_t queue) const
     {
-        return warp_cache_acquire(mask, want, cache, get_global_address(page), cnt, get_backing_page(page), queue, write);
+        return warp_cache_acquire(mask, want, cache, get_global_address(page), cnt, get_backing_page(page), queue, write,
+                                  get_backing_ctrl(page));
     }
     BAM_DEV void release_page(uint32_t slot, uint32_t cnt = 1) const { cache_release(cache, slot, cnt); }
 };

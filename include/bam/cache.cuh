@@ -171,10 +171,41 @@ BAM_DEV void finish_evict(const page_cache_d_t& pc, uint32_t s, uint64_t old_tag
     atom_and_release(&sl->state, ~(BAM_VALID | BAM_DIRTY));
 }
 
-/* Backing page of a cached page, from its tag: (page in range << range bits) | range id. */
-BAM_DEV uint64_t backing_page_of_tag(const page_cache_d_t& pc, uint64_t tag)
+/* Where page `page` of a range lives when the cache is backed by n_ctrls controllers
+ * (get_backing_page_ / get_backing_ctrl_, page_cache.h:558-582): a replicated range is whole on
+ * every controller; a striped range deals its pages round-robin. */
+BAM_DEV uint64_t backing_page_of(uint64_t page_start, uint64_t page, uint32_t n_ctrls, uint32_t dist)
 {
-    return ld_relaxed_gpu(&pc.range_page_starts[tag & pc.n_ranges_mask]) + (tag >> pc.n_ranges_bits);
+    return page_start + ((dist == BAM_DIST_STRIPE && n_ctrls > 1) ? page / n_ctrls : page);
+}
+BAM_DEV uint32_t backing_ctrl_of(uint64_t page, uint32_t n_ctrls, uint32_t dist)
+{
+    return (dist == BAM_DIST_STRIPE && n_ctrls > 1) ? (uint32_t)(page % n_ctrls) : BAM_ALL_CTRLS;
+}
+
+/* Backing page (and controller) of a cached page, from its tag: (page in range << range bits) | range id. */
+BAM_DEV uint64_t backing_location_of_tag(const page_cache_d_t& pc, uint64_t tag, uint32_t& ctrl)
+{
+    const uint32_t rid = (uint32_t)(tag & pc.n_ranges_mask);
+    const uint64_t page = tag >> pc.n_ranges_bits;
+    const uint32_t dist = pc.n_ctrls > 1 ? ld_relaxed_gpu(&pc.range_dists[rid]) : BAM_DIST_REPLICATE;
+    ctrl = backing_ctrl_of(page, pc.n_ctrls, dist);
+    return backing_page_of(ld_relaxed_gpu(&pc.range_page_starts[rid]), page, pc.n_ctrls, dist);
+}
+
+/* The value callers spread their requests over queues with: the global warp index. */
+BAM_DEV uint32_t default_queue() { return (blockIdx.x * blockDim.x + threadIdx.x) >> 5; }
+
+/* The queue pair a request goes to.  `queue` is the caller's spreading value (its global warp
+ * index); `ctrl` is the controller that owns the page, or BAM_ALL_CTRLS when any will do (the
+ * reference draws from a global counter there, page_cache.h:1150-1152; here the warp index picks
+ * the controller and its remaining bits the queue, so all queues of all controllers are used). */
+BAM_DEV QueuePair* pick_queue(const page_cache_d_t& pc, uint32_t ctrl, uint32_t queue)
+{
+    if (pc.n_ctrls <= 1) { Controller* c = pc.d_ctrl; return c->d_qps + (queue % c->n_qps); }
+    if (ctrl == BAM_ALL_CTRLS) ctrl = queue % pc.n_ctrls;
+    Controller* c = pc.d_ctrls[ctrl];
+    return c->d_qps + ((queue / pc.n_ctrls) % c->n_qps);
 }
 
 BAM_DEV uint64_t slot_prp2(const page_cache_d_t& pc, uint32_t slot)
@@ -182,6 +213,27 @@ BAM_DEV uint64_t slot_prp2(const page_cache_d_t& pc, uint32_t slot)
     if (pc.page_size <= 4096) return 0;
     const uint64_t bus = (uint64_t)(pc.base_addr + (size_t)slot * pc.page_size);
     return (pc.page_size <= 8192) ? bus + 4096 : (uint64_t)(pc.prp_lists + (size_t)slot * pc.prp_list_stride);
+}
+
+/* Write cache slot `slot`, which holds the page `tag`, back to its backing store; all lanes of
+ * `mask` call it, lanes with wb == true have a page to write.  A replicated page goes to every
+ * controller (page_cache.h:1856-1862), a striped page to the one that owns it. */
+BAM_DEV int warp_write_back(uint32_t mask, bool wb, const page_cache_d_t& pc, uint64_t tag, uint32_t slot)
+{
+    const uint32_t queue = default_queue();
+    uint32_t ctrl = 0;
+    const uint64_t lba = wb ? backing_location_of_tag(pc, tag, ctrl) * pc.n_blocks_per_page : 0;
+    const uint64_t bus = wb ? slot_bus_addr(pc, slot) : 0;
+    const uint64_t prp2 = wb ? slot_prp2(pc, slot) : 0;
+    int rc = BAM_OK;
+#pragma unroll 1
+    for (uint32_t k = 0; k < pc.n_ctrls; k++) {
+        const bool go = wb && (ctrl == BAM_ALL_CTRLS || ctrl == k);
+        if (!__any_sync(mask, go)) continue;
+        const int r = warp_io(mask, go, pick_queue(pc, k, queue), lba, pc.n_blocks_per_page, bus, prp2, NVM_IO_WRITE);
+        if (go && r != BAM_OK) rc = r;
+    }
+    return rc;
 }
 
 BAM_DEV void count_hit(const page_cache_d_t& pc, uint32_t count) { red_add_relaxed(&pc.stats[get_smid() & (BAM_STAT_STRIPES - 1)].hits, (uint64_t)count); }
@@ -196,7 +248,7 @@ BAM_DEV void count_miss(const page_cache_d_t& pc, uint32_t count)
  * backing page `backing_page` through queue pair `queue`.  Returns BAM_SLOT_ERR after an
  * error has been recorded.  Counterpart of range_d_t<T>::acquire_page (page_cache.h:1122-1224). */
 BAM_DEV uint32_t cache_acquire(const page_cache_d_t& pc, uint64_t tag, uint32_t count,
-                               uint64_t backing_page, uint32_t queue, bool write)
+                               uint64_t backing_page, uint32_t queue, bool write, uint32_t ctrl = BAM_ALL_CTRLS)
 {
     bam_status_t* st = pc.status;
     const uint64_t h = pt_hash(tag);
@@ -238,8 +290,7 @@ BAM_DEV uint32_t cache_acquire(const page_cache_d_t& pc, uint64_t tag, uint32_t 
             if (r == BAM_PT_FULL) status_fail(st, BAM_ENOSPC, BAM_AT_TABLE_FULL, tag);
             return BAM_SLOT_ERR;
         }
-        Controller* c = pc.d_ctrl;
-        QueuePair* qp = c->d_qps + (queue % c->n_qps);
+        QueuePair* qp = pick_queue(pc, ctrl, queue);
         const uint64_t bus = slot_bus_addr(pc, v);
         const uint64_t mps = 4096;
         uint64_t prp2 = 0;
@@ -262,7 +313,7 @@ BAM_DEV uint32_t cache_acquire(const page_cache_d_t& pc, uint64_t tag, uint32_t 
  * sweep: the caller must first release the pages its warp holds (they may be exactly what keeps
  * the cache full) and then call again. */
 BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d_t& pc, uint64_t tag, uint32_t count,
-                                    uint64_t backing_page, uint32_t queue, bool write)
+                                    uint64_t backing_page, uint32_t queue, bool write, uint32_t ctrl = BAM_ALL_CTRLS)
 {
     enum { S_DONE = 0, S_LOOKUP = 1, S_WAIT = 2, S_IO = 3, S_WB = 4 };
     uint64_t victim_tag = BAM_TAG_NONE;
@@ -271,8 +322,7 @@ BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d
     const uint64_t h = pt_hash(tag);
     const uint32_t home = (uint32_t)h & pc.bucket_mask;
     const uint32_t fp = (uint32_t)(h >> 56);
-    Controller* c = pc.d_ctrl;
-    QueuePair* qp = c->d_qps + (queue % c->n_qps);
+    QueuePair* qp = pick_queue(pc, ctrl, queue);
     uint32_t state = want ? S_LOOKUP : S_DONE;
     uint32_t slot = BAM_SLOT_ERR;
     uint32_t my_hits = 0;                    /* hit counts are summed over the warp: one atomic, not 32 */
@@ -322,8 +372,7 @@ BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d
         /* dirty victims are written back as one group; then their slots are free for the new pages */
         if (__any_sync(mask, state == S_WB)) {
             const bool wb = state == S_WB;
-            const int rc = warp_io(mask, wb, qp, wb ? backing_page_of_tag(pc, victim_tag) * pc.n_blocks_per_page : 0,
-                                   pc.n_blocks_per_page, wb ? slot_bus_addr(pc, slot) : 0, wb ? slot_prp2(pc, slot) : 0, NVM_IO_WRITE);
+            const int rc = warp_write_back(mask, wb, pc, victim_tag, slot);
             if (wb) {
                 if (rc == BAM_OK) {
                     finish_evict(pc, slot, victim_tag);

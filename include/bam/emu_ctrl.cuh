@@ -87,13 +87,14 @@ BAM_DEV void emu_post_completion(const bam_emu_d_t& c, const emu_cmd_t& m, uint3
 {
     bam_emu_qp_t* s = &c.qps[m.q];
     bool drop = false;
-    if (c.fault) {
-        const uint32_t mode = ld_relaxed_gpu(&c.fault->mode);
+    bam_fault_t* fault = s->fault;
+    if (fault) {
+        const uint32_t mode = ld_relaxed_gpu(&fault->mode);
         if (mode != BAM_FAULT_NONE) {
-            const uint64_t k = atom_add_relaxed(&c.fault->counter, 1ull);
-            if (k == c.fault->nth) {
+            const uint64_t k = atom_add_relaxed(&fault->counter, 1ull);
+            if (k == fault->nth) {
                 if (mode == BAM_FAULT_DROP_CPL) drop = true;
-                else if (mode == BAM_FAULT_STATUS) status = c.fault->status;
+                else if (mode == BAM_FAULT_STATUS) status = fault->status;
             }
         }
     }
@@ -106,7 +107,7 @@ BAM_DEV void emu_post_completion(const bam_emu_d_t& c, const emu_cmd_t& m, uint3
         const uint64_t dw3 = m.cid | (phase << 16) | (status << 17);
         st_release_scoped(reinterpret_cast<uint64_t*>(&e->dword[2]), dw2 | (dw3 << 32), c.sys_scope != 0);
     }
-    red_add_relaxed(c.served, 1ull);
+    red_add_relaxed(s->served, 1ull);
 }
 
 /* Lane 0 of a processor: look at queue pair q and, if commands are waiting, take the fetch lock
@@ -155,7 +156,7 @@ BAM_DEV void emu_decode(const bam_emu_d_t& c, uint32_t q, uint32_t fetch_i, uint
     m.sqhd = sqhd;
     m.status = BAM_SC_SUCCESS;
     if (m.opc != NVM_IO_READ && m.opc != NVM_IO_WRITE) m.status = BAM_SC_INVALID_OPCODE;
-    else if (m.media_off + bytes > c.store_bytes || m.media_off + bytes < m.media_off) m.status = BAM_SC_LBA_OUT_OF_RANGE;
+    else if (m.media_off + bytes > s->store_bytes || m.media_off + bytes < m.media_off) m.status = BAM_SC_LBA_OUT_OF_RANGE;
     else if ((m.prp1 & 15u) || (bytes & 15u)) m.status = BAM_SC_INVALID_FIELD;
 }
 
@@ -164,6 +165,7 @@ BAM_DEV void emu_decode(const bam_emu_d_t& c, uint32_t q, uint32_t fetch_i, uint
 BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t stage_smem, uint32_t bar, uint32_t& parity)
 {
     const uint64_t mps = 1ull << c.mps_log2;
+    uint8_t* const store = c.qps[m.q].store;               /* the media of the controller that owns the queue */
     uint64_t first = mps - (m.prp1 & (mps - 1));
     if (first > m.bytes) first = m.bytes;
     const bool use_list = (m.bytes - first) > mps;
@@ -178,7 +180,7 @@ BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t
             len = m.bytes - done < mps ? m.bytes - done : (uint32_t)mps;
         }
         if (len > BAM_EMU_STAGE_BYTES) len = BAM_EMU_STAGE_BYTES;
-        uint8_t* media = c.store + m.media_off + done;
+        uint8_t* media = store + m.media_off + done;
         const void* src = (m.opc == NVM_IO_READ) ? (const void*)media : (const void*)mem;
         void* dst = (m.opc == NVM_IO_READ) ? (void*)mem : (void*)media;
         BAM_PROF_T0();

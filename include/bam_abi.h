@@ -91,6 +91,16 @@ int bam_ctrl_emu_descriptor(bam_ctrl_t c, void* out, size_t out_bytes); /* bam_e
  * Replaces page_cache_t::page_cache_t(page_size, n_pages, gpu, ctrl, max_range, ctrls)
  * (include/page_cache.h:697-875). */
 int bam_cache_create(bam_cache_t* out, bam_ctrl_t ctrl, uint32_t page_size, uint64_t n_pages);
+/* The same constructor with its `ctrls` vector of several controllers (page_cache.h:714-720: one
+ * cache in front of n SSDs).  All controllers must sit on the same GPU with the same block size.
+ * From here until bam_cache_destroy the controllers form a group: one fused launch serves the
+ * queues of all of them, they report into the first controller's status block (bam_ctrl_status of
+ * any member reads it) and bam_ctrl_configure of the FIRST controller sets the launch geometry.
+ * A controller can back one multi-controller cache at a time (BAM_EBUSY otherwise); destroy the
+ * cache before its controllers.  How a range's pages map to the controllers is chosen per array:
+ * bam_array_create_dist. */
+int bam_cache_create_multi(bam_cache_t* out, const bam_ctrl_t* ctrls, uint32_t n_ctrls, uint32_t page_size,
+                           uint64_t n_pages);
 int bam_cache_destroy(bam_cache_t pc);
 /* range_d_t counters (page_cache.h:904-907, printed by array_t::print_reset_stats :1731-1752). */
 int bam_cache_stats(bam_cache_t pc, bam_cache_stats_t* out, int reset);
@@ -123,6 +133,12 @@ int bam_cache_audit_noalloc(bam_cache_t pc, uint64_t* violations_out_dev, void* 
  * byte `store_byte_offset` (page aligned) of the backing store. */
 int bam_array_create(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
                      uint64_t store_byte_offset);
+/* The same with the range's data_dist_t (page_cache.h:42, :558-582, :978): BAM_DIST_REPLICATE (0,
+ * what bam_array_create uses: every controller holds the whole range at store_byte_offset, a page
+ * read goes to any one of them, a write-back to all) or BAM_DIST_STRIPE (1: page p of the range
+ * lives on controller p % n at backing page store_byte_offset / page_size + p / n). */
+int bam_array_create_dist(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
+                          uint64_t store_byte_offset, uint32_t dist);
 int bam_array_destroy(bam_array_t a);
 void* bam_array_device_ptr(bam_array_t a);         /* array_d_t<T>* (array_t::d_array_ptr) */
 

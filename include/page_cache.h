@@ -36,14 +36,22 @@ struct page_cache_t {
     uint64_t page_size = 0, n_pages = 0;
     Controller* ctrl = nullptr;
 
+    /* `ctrls` lists every controller behind the cache (page_cache.h:714-720 there); `c` is the first of
+     * them.  With an empty or one-element list the cache has the single backing controller `c`. */
     page_cache_t(const uint64_t ps, const uint64_t np, const uint32_t /*cudaDevice*/, const Controller& c,
-                 const uint64_t /*max_range*/, const std::vector<Controller*>& /*ctrls*/)
+                 const uint64_t /*max_range*/, const std::vector<Controller*>& ctrls)
     {
-        int rc = bam_cache_create(&h, c.h, (uint32_t)ps, np);
+        int rc;
+        if (ctrls.size() > 1) {
+            std::vector<bam_ctrl_t> hs;
+            for (Controller* k : ctrls) hs.push_back(k->h);
+            rc = bam_cache_create_multi(&h, hs.data(), (uint32_t)hs.size(), (uint32_t)ps, np);
+        } else
+            rc = bam_cache_create(&h, c.h, (uint32_t)ps, np);
         if (rc != 0) throw std::runtime_error(std::string("Failed to create page cache: ") + bam_strerror(rc));
         bam_cache_descriptor(h, &pdt, sizeof pdt);
         page_size = ps; n_pages = np;
-        ctrl = const_cast<Controller*>(&c);
+        ctrl = ctrls.size() > 1 ? ctrls[0] : const_cast<Controller*>(&c);
     }
     ~page_cache_t() { if (h) bam_cache_destroy(h); }
     page_cache_t(const page_cache_t&) = delete;
@@ -69,9 +77,11 @@ template <typename T>
 struct range_t {
     uint64_t index_start, count, page_start, page_count, page_start_offset, page_size;
     page_cache_t* cache;
+    data_dist_t dist;
     range_t(uint64_t is, uint64_t cnt, uint64_t ps, uint64_t pc, uint64_t pso, uint64_t p_size, page_cache_t* c,
-            uint32_t /*cudaDevice*/, data_dist_t /*dist*/ = REPLICATE)
-        : index_start(is), count(cnt), page_start(ps), page_count(pc), page_start_offset(pso), page_size(p_size), cache(c)
+            uint32_t /*cudaDevice*/, data_dist_t d = REPLICATE)
+        : index_start(is), count(cnt), page_start(ps), page_count(pc), page_start_offset(pso), page_size(p_size), cache(c),
+          dist(d)
     {
         if (pso != 0) throw std::runtime_error("range_t: page_start_offset must be 0");
     }
@@ -90,7 +100,8 @@ struct array_t {
         range_t<T>* r = ranges[0];
         cache = r->cache;
         (void)disk_start_offset;
-        int rc = bam_array_create(&h, cache->h, num_elems, (uint32_t)sizeof(T), r->page_start * r->page_size);
+        int rc = bam_array_create_dist(&h, cache->h, num_elems, (uint32_t)sizeof(T), r->page_start * r->page_size,
+                                       (uint32_t)r->dist);
         if (rc != 0) throw std::runtime_error(std::string("Failed to create array: ") + bam_strerror(rc));
         d_array_ptr = static_cast<array_d_t<T>*>(bam_array_device_ptr(h));
     }

@@ -105,6 +105,18 @@ ORC_API uint64_t orc_indexed_checksum(uint64_t store_seed, uint64_t first_elem,
     return sum;
 }
 
+/* Where page `page` of a range lives when the cache sits in front of n_ctrls controllers:
+ * get_backing_page_ and get_backing_ctrl_ (include/page_cache.h:558-582).  dist 0 = REPLICATE
+ * (every controller holds the whole range; *ctrl = 0xffffffff, "all"), 1 = STRIPE (pages dealt
+ * round-robin).  Returns the backing page on that controller. */
+ORC_API uint64_t orc_backing_location(uint64_t page_start, uint64_t page, uint64_t n_ctrls, uint32_t dist, uint32_t* ctrl)
+{
+    uint64_t backing = page_start;
+    if (dist == 1) { backing += page / n_ctrls; *ctrl = (uint32_t)(page % n_ctrls); }
+    else { backing += page; *ctrl = 0xffffffffu; }
+    return backing;
+}
+
 /* CRC-32 of one page of the store (page_bytes/8 little-endian u64 words). */
 ORC_API uint32_t orc_page_crc(uint64_t store_seed, uint64_t page, uint32_t page_bytes)
 {

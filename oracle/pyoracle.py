@@ -49,6 +49,8 @@ def lib():
         L.orc_array_checksum.argtypes = [u64, u64, u64, u64, u64, u64]
         L.orc_indexed_checksum.restype = u64
         L.orc_indexed_checksum.argtypes = [u64, u64, vp, u64]
+        L.orc_backing_location.restype = u64
+        L.orc_backing_location.argtypes = [u64, u64, u64, u32, C.POINTER(u32)]
         L.orc_page_crc.restype = u32
         L.orc_page_crc.argtypes = [u64, u64, u32]
         L.orc_block_requests.argtypes = [u64, u64, u64, u32, u64, u64, vp, vp]
@@ -117,6 +119,13 @@ def array_checksum(store_seed, n_elems, access_seed, lane_begin, lane_end, reqs_
 def indexed_checksum(store_seed, first_elem, idx):
     idx = np.ascontiguousarray(idx, dtype=np.uint64)
     return lib().orc_indexed_checksum(store_seed, first_elem, _p(idx), len(idx))
+
+
+def backing_location(page_start, page, n_ctrls, dist):
+    """(controller or None for "all", backing page) of a range's page behind n_ctrls controllers."""
+    ctrl = C.c_uint32()
+    backing = lib().orc_backing_location(page_start, page, n_ctrls, dist, C.byref(ctrl))
+    return (None if ctrl.value == 0xFFFFFFFF else ctrl.value), backing
 
 
 def page_crc(store_seed, page, page_bytes=4096):

@@ -240,3 +240,24 @@ def test_protocol_restatement_graph_traversals(orc):
     want_lab, _ = orc.cc(off, cols)
     lab, _, sweeps, _ = orc.ref_graph_run(store, n, off_bytes, 1, 0, 64, 2, 8, 4, 1)
     assert (lab == want_lab).all() and sweeps >= 1
+
+
+def test_backing_location_of_replicated_and_striped_ranges(orc):
+    """The page -> (controller, backing page) map of include/page_cache.h:558-582: the oracle's C
+    restatement, the host mirror and a direct statement of the rule agree."""
+    import bam_b200
+    rng = np.random.default_rng(3)
+    for n_ctrls in (1, 2, 3, 8):
+        for page in [0, 1, n_ctrls - 1, n_ctrls, 12345] + rng.integers(0, 1 << 40, 20).tolist():
+            for start in (0, 77):
+                assert orc.backing_location(start, page, n_ctrls, 0) == (None, start + page)
+                assert bam_b200.backing_location(page, n_ctrls, bam_b200.REPLICATE, start) == (None, start + page)
+                want = (page % n_ctrls, start + page // n_ctrls)
+                assert orc.backing_location(start, page, n_ctrls, 1) == want
+                if n_ctrls > 1:
+                    assert bam_b200.backing_location(page, n_ctrls, bam_b200.STRIPE, start) == want
+    # striping is a bijection between a range's pages and (controller, backing page) pairs
+    n_ctrls, n_pages = 3, 1000
+    seen = {orc.backing_location(5, p, n_ctrls, 1) for p in range(n_pages)}
+    assert len(seen) == n_pages and max(b for _, b in seen) == 5 + (n_pages - 1) // n_ctrls
+
