@@ -46,11 +46,11 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
-def build_cpp_bench(force=False):
-    """Compile tests/cpp/array_bench.cu (the reference's array benchmark written against the drop-in
-    C++ headers) and link it against the in-tree library."""
-    src = os.path.join(ROOT, "tests", "cpp", "array_bench.cu")
-    exe = os.path.join(ROOT, "tests", "cpp", "array_bench")
+def build_cpp_bench(force=False, name="array_bench"):
+    """Compile tests/cpp/<name>.cu (a benchmark of the reference written against the drop-in C++
+    headers) and link it against the in-tree library."""
+    src = os.path.join(ROOT, "tests", "cpp", name + ".cu")
+    exe = os.path.join(ROOT, "tests", "cpp", name)
     build_library()
     if not force and not _newer_than(exe, _deps() + [src, LIB]):
         return exe
@@ -61,5 +61,5 @@ def build_cpp_bench(force=False):
     if res.returncode != 0:
         print(res.stdout)
         print(res.stderr)
-        raise RuntimeError("nvcc failed building tests/cpp/array_bench")
+        raise RuntimeError("nvcc failed building tests/cpp/" + name)
     return exe

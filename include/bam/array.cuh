@@ -208,16 +208,26 @@ BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
 }
 
 /* Per-thread cursor that keeps the page of its last access pinned, so a run of accesses to one
- * page costs one pin/unpin (reference: bam_ptr, page_cache.h:415-485).  Reads never mark the
- * page dirty (the reference's non-const operator[] does, :478-484, which causes spurious
- * write-backs). */
+ * page costs one pin/unpin (reference: bam_ptr, page_cache.h:415-485).  p[i] reads the element,
+ * p[i] = v writes it (benchmarks/vectoradd/main.cu:103-118 uses both).  Only a real write marks
+ * the page dirty; the reference's non-const operator[] marks it on every access (:478-484), which
+ * causes spurious write-backs. */
 template <typename T>
 struct bam_ptr {
     const array_d_t<T>* array = nullptr;
     const range_d_t<T>* range = nullptr;
     uint32_t slot = BAM_SLOT_ERR;
+    bool dirty = false;
     size_t start = 0, end = 0;
-    const T* addr = nullptr;
+    T* addr = nullptr;
+
+    struct ref_t {
+        bam_ptr* p;
+        size_t i;
+        BAM_DEV operator T() const { return p->read(i); }
+        BAM_DEV ref_t& operator=(const T v) { p->write(i, v); return *this; }
+        BAM_DEV ref_t& operator=(const ref_t& o) { p->write(i, (T)o); return *this; }
+    };
 
     BAM_DEV explicit bam_ptr(const array_d_t<T>* a) : array(a) {}
     BAM_DEV ~bam_ptr() { fini(); }
@@ -230,10 +240,11 @@ struct bam_ptr {
             if (lane_id() == (uint32_t)(__ffs(eq) - 1)) range->release_page(slot, __popc(eq));
             slot = BAM_SLOT_ERR;
             start = end = 0;
+            dirty = false;
         }
     }
 
-    BAM_DEV const T* update_page(size_t i)
+    BAM_DEV T* update_page(size_t i)
     {
         fini();
         const uint32_t mask = __activemask();
@@ -253,17 +264,28 @@ struct bam_ptr {
         const uint64_t first_byte = page_byte0 > range->page_start_offset ? page_byte0 - range->page_start_offset : 0;
         start = range->index_start + (first_byte + sizeof(T) - 1) / sizeof(T);
         end = range->index_start + (page_byte0 + range->cache.page_size - range->page_start_offset) / sizeof(T);
-        addr = reinterpret_cast<const T*>(range->get_cache_page_addr(slot) + range->get_subindex(start));
+        addr = reinterpret_cast<T*>(range->get_cache_page_addr(slot) + range->get_subindex(start));
         return addr;
     }
 
-    BAM_DEV T operator[](size_t i)
+    BAM_DEV T read(size_t i)
     {
         if (i < start || i >= end) {
             if (update_page(i) == nullptr) return T();
         }
         return addr[i - start];
     }
+
+    BAM_DEV void write(size_t i, const T v)
+    {
+        if (i < start || i >= end) {
+            if (update_page(i) == nullptr) return;
+        }
+        if (!dirty) { atom_or_relaxed(&range->cache.slots[slot].state, BAM_DIRTY); dirty = true; }
+        addr[i - start] = v;
+    }
+
+    BAM_DEV ref_t operator[](size_t i) { return ref_t{ this, i }; }
 };
 
 /* Raw-pointer-like view of an array (reference: include/bafs_ptr.h:17-132). */

@@ -5,7 +5,7 @@
  *   range_t<T>(index_start, count, page_start, page_count, page_start_offset,
  *              page_size, cache, cudaDevice, dist)                              (:978-1030)
  *   array_t<T>(n_elems, disk_start_offset, ranges, cudaDevice)                  (:1719-1772)
- *   array_d_t<T>, range_d_t<T>, bam_ptr<T>, page_cache_d_t (device side)
+ *   array_d_t<T>, range_d_t<T>, bam_ptr<T>, tlb<T,n>, bam_ptr_tlb<T,n>, page_cache_d_t (device side)
  * The host classes are thin wrappers over the C ABI (bam_abi.h); the device side is
  * include/bam/*.cuh.  Arrays of one range are supported (every benchmark of the reference
  * builds exactly one range per array).  Compile with nvcc.
@@ -22,10 +22,13 @@
 #include "ctrl.h"
 #include "bam/array.cuh"
 #include "bam/launch.cuh"
+#include "bam/tlb.cuh"
 
 using bam::array_d_t;
 using bam::bafs_ptr;
 using bam::bam_ptr;
+using bam::bam_ptr_tlb;
+using bam::tlb;
 using bam::range_d_t;
 
 enum data_dist_t { REPLICATE = 0, STRIPE = 1 };

@@ -1,7 +1,8 @@
 /*
  * array_bench.cu -- the reference's nvm-array-bench (benchmarks/array/main.cu) written against this
  * library's drop-in headers: Controller, page_cache_t, range_t, array_t on the host,
- * array_d_t<T>::operator[] on the device.  Differences from the reference program: the access
+ * array_d_t<T>::operator[] on the device (--bam_ptr 1: bam_ptr cursors, --bam_ptr 2: bam_ptr_tlb
+ * cursors over a block-level tlb in shared memory).  Differences from the reference program: the access
  * pattern is the seeded PCG32 stream of bam_synth.h instead of rand(), the values read are summed
  * (the reference discards them), and the kernel is launched fused with the emulated controller.
  * Prints one JSON line.
@@ -52,6 +53,30 @@ struct BamPtrKernel {                 /* the same reads through a bam_ptr cursor
     }
 };
 
+struct TlbPtrKernel {                 /* the same reads through bam_ptr_tlb cursors over a block-level tlb */
+    array_d_t<uint64_t>* dr;
+    uint64_t n_threads;
+    const uint64_t* assignment;
+    uint64_t reqs_per_thread;
+    unsigned long long* sum;
+
+    __device__ void operator()(uint32_t worker_block, uint32_t n_worker_blocks) const
+    {
+        __shared__ tlb<uint64_t, 32> t;
+        t.init(dr);
+        unsigned long long v = 0;
+        {
+            bam_ptr_tlb<uint64_t, 32> ptr(dr, &t);
+            for (uint64_t tid = (uint64_t)worker_block * blockDim.x + threadIdx.x; tid < n_threads;
+                 tid += (uint64_t)n_worker_blocks * blockDim.x)
+                for (uint64_t i = 0; i < reqs_per_thread; i++) v += ptr[assignment[tid * reqs_per_thread + i]];
+            ptr.fini();
+        }
+        t.fini();
+        atomicAdd(sum, v);
+    }
+};
+
 static uint64_t arg_u64(int argc, char** argv, const char* name, uint64_t def)
 {
     for (int i = 1; i + 1 < argc; i++)
@@ -96,7 +121,8 @@ int main(int argc, char** argv)
 
         Event before;
         cudaError_t e;
-        if (use_ptr) e = bam::launch_fused(h_pc.emu(), BamPtrKernel{ a.d_array_ptr, threads, d_assign, reqs, d_sum });
+        if (use_ptr == 2) e = bam::launch_fused(h_pc.emu(), TlbPtrKernel{ a.d_array_ptr, threads, d_assign, reqs, d_sum });
+        else if (use_ptr) e = bam::launch_fused(h_pc.emu(), BamPtrKernel{ a.d_array_ptr, threads, d_assign, reqs, d_sum });
         else e = bam::launch_fused(h_pc.emu(), RandomAccessKernel{ a.d_array_ptr, threads, d_assign, reqs, d_sum });
         Event after;
         cuda_err_chk(e);

@@ -1,9 +1,12 @@
 """GPU test of the C++ drop-in layer: tests/cpp/array_bench.cu is the reference's array benchmark
 written with Controller / page_cache_t / range_t / array_t on the host and array_d_t<T>::operator[]
-and bam_ptr<T> in a user kernel.  Its checksum must equal the oracle's."""
+and bam_ptr<T> / bam_ptr_tlb<T> in a user kernel; its checksum must equal the oracle's.
+tests/cpp/vectoradd_bench.cu is the reference's vector add (C[i] = A[i] + B[i] through three cursors),
+checked on the host after a flush."""
 import json
 import subprocess
 
+import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
@@ -15,16 +18,33 @@ def run(exe, *args):
     return json.loads(out.stdout.strip().splitlines()[-1])
 
 
-@pytest.mark.parametrize("use_ptr", [0, 1])
+@pytest.mark.parametrize("use_ptr", [0, 1, 2])
 def test_cpp_array_bench_matches_oracle(cuda, bam, orc, use_ptr):
     from bam_b200 import _build
     exe = _build.build_cpp_bench()
     # a bam_ptr keeps one page pinned per thread, so (as with the reference) the cache needs more
     # slots than threads that hold a cursor; operator[] has no such requirement
     n_elems, threads, reqs, seed, aseed = 1 << 22, 1 << 13, 16, 11, 29
-    pages = 16384 if use_ptr else 2048
+    # (with a tlb also 32 per block)
+    pages = {0: 2048, 1: 16384, 2: 32768}[use_ptr]
     r = run(exe, "--num_elems", n_elems, "--pages", pages, "--threads", threads, "--reqs", reqs, "--seed", seed,
             "--access_seed", aseed, "--queue_depth", 64, "--num_queues", 8, "--bam_ptr", use_ptr)
     assert r["status"] == 0 and r["audit"] == 0
     assert r["checksum"] == orc.array_checksum(seed, n_elems, aseed, 0, threads, reqs)
     assert r["hits"] + r["misses"] == threads * reqs if not use_ptr else r["read_ios"] > 0
+
+
+@pytest.mark.parametrize("use_tlb", [0, 1])
+def test_cpp_vectoradd_writes_through_cursors(cuda, bam, orc, use_tlb):
+    from bam_b200 import _build
+    exe = _build.build_cpp_bench(name="vectoradd_bench")
+    n_elems, seed = (1 << 20) + 77, 7                       # ragged last page and last warp
+    r = run(exe, "--num_elems", n_elems, "--pages", 1 << 16, "--seed", seed, "--tlb", use_tlb)
+    assert r["status"] == 0 and r["flush_status"] == 0 and r["audit"] == 0
+    assert r["mismatches"] == 0
+    a = orc.fill_store(seed, 0, n_elems)
+    b = orc.fill_store(seed + 1, 0, n_elems)
+    with np.errstate(over="ignore"):
+        assert r["checksum"] == int((a + b).sum(dtype=np.uint64))
+    assert r["read_ios"] >= 2 * (n_elems * 8 // 4096)       # A and B came in through the controller
+
