@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include <cstddef>
+#include <cstring>
 
 #include "bam_abi.h"
 #include "bam_synth.h"
@@ -253,6 +254,277 @@ struct CcSweepWork {
     }
 };
 
+/* ---- weighted walks (SSSP): edge j of the column array carries weight wt[j] (u32 array) ----------
+ * A 4 KiB page of column indices holds 512 edges; their weights are 2 KiB, so they sit inside ONE
+ * page of the weight array (weight page = column page / 2 for equal page sizes).  The walkers pin
+ * the two pages together. */
+typedef range_d_t<uint32_t> wrange_t;
+
+BAM_DEV const range_d_t<uint64_t>& as_u64_range(const wrange_t& w) { return reinterpret_cast<const range_d_t<uint64_t>&>(w); }
+
+/* The whole warp walks cols[begin, end) page by page and calls fn(neighbour, weight) per edge. */
+template <class EdgeFn>
+BAM_DEV bool warp_walk_edges_w(const range_d_t<uint64_t>& col, const wrange_t& wt, uint64_t begin, uint64_t end, uint32_t queue,
+                               EdgeFn fn)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t epp_log = col.cache.page_size_log - 3;
+    const uint32_t wpp_log = wt.cache.page_size_log - 2;
+    for (uint64_t i = begin; i < end;) {
+        uint64_t pend = ((i >> epp_log) + 1) << epp_log;               /* first index of the next page */
+        if (pend > end) pend = end;
+        /* lane 0 asks for the column page, lane 1 for the weight page: one all-or-nothing round */
+        const range_d_t<uint64_t>& r = lane == 1 ? as_u64_range(wt) : col;
+        const uint64_t pg = lane == 1 ? (i >> wpp_log) : (i >> epp_log);
+        uint32_t slot = range_pin_page(r, 0xffffffffu, lane < 2, pg, 1, queue);
+        const uint32_t cs = __shfl_sync(0xffffffffu, slot, 0), ws = __shfl_sync(0xffffffffu, slot, 1);
+        if (cs == BAM_SLOT_ERR || ws == BAM_SLOT_ERR) {
+            if (lane < 2 && slot <= BAM_SLOT_MAX) r.release_page(slot, 1);
+            return false;
+        }
+        const uint64_t* cbase = reinterpret_cast<const uint64_t*>(col.get_cache_page_addr(cs));
+        const uint32_t* wbase = reinterpret_cast<const uint32_t*>(wt.get_cache_page_addr(ws));
+        const uint64_t cfirst = (i >> epp_log) << epp_log, wfirst = (i >> wpp_log) << wpp_log;
+        for (uint64_t j = i + lane; j < pend; j += 32) fn(cbase[j - cfirst], wbase[j - wfirst]);
+        __syncwarp();
+        if (lane < 2) r.release_page(slot, 1);
+        i = pend;
+    }
+    return true;
+}
+
+/* chunk_visit for a weighted graph: fn(src_lane, neighbour, weight) per edge. */
+template <class EdgeFn>
+BAM_DEV bool chunk_visit_w(const range_d_t<uint64_t>& off, const range_d_t<uint64_t>& col, const wrange_t& wt, uint64_t v,
+                           uint64_t u_global, bool act, uint32_t queue, graph_scratch_t* scratch, uint64_t& edges, EdgeFn fn)
+{
+    uint64_t s = 0, e = 0;
+    if (act) {
+        s = range_read<uint64_t>(off, v, queue);
+        e = range_read<uint64_t>(off, v + 1, queue);
+    }
+    __syncwarp();
+    const uint64_t deg = e - s;
+    edges += deg;
+    bool heavy = act && scratch && deg > BAM_HEAVY_EDGES;
+    if (heavy) {
+        const uint32_t n_it = (uint32_t)((deg + BAM_ITEM_EDGES - 1) / BAM_ITEM_EDGES);
+        const uint32_t base = atom_add_relaxed(&scratch->n_items, n_it);
+        const uint32_t fit = base >= scratch->capacity ? 0u : (scratch->capacity - base < n_it ? scratch->capacity - base : n_it);
+        for (uint32_t k = 0; k < fit; k++) {
+            graph_item_t* it = &scratch->items[base + k];
+            const uint64_t b0 = s + (uint64_t)k * BAM_ITEM_EDGES;
+            it->u = u_global;
+            it->begin = b0;
+            __threadfence();
+            st_release_gpu(&it->end, b0 + BAM_ITEM_EDGES < e ? b0 + BAM_ITEM_EDGES : e);
+        }
+        if (fit < n_it) { s += (uint64_t)fit * BAM_ITEM_EDGES; heavy = false; }
+    }
+    const bool light = act && !heavy && e > s;
+    uint32_t am = __ballot_sync(0xffffffffu, light);
+    bool ok = true;
+    /* one vertex after the other; every page pair is pinned by the whole warp in one round */
+    while (am && ok) {
+        const int src = __ffs(am) - 1;
+        am &= am - 1;
+        const uint64_t vs = __shfl_sync(0xffffffffu, s, src);
+        const uint64_t ve = __shfl_sync(0xffffffffu, e, src);
+        ok = warp_walk_edges_w(col, wt, vs, ve, queue, [&](uint64_t nb, uint32_t w) { fn(src, nb, w); });
+    }
+    __syncwarp();
+    return ok;
+}
+
+template <class EdgeFn>
+BAM_DEV void consume_heavy_items_w(const range_d_t<uint64_t>& col, const wrange_t& wt, graph_scratch_t* scratch,
+                                   uint32_t n_warps_total, uint32_t queue, EdgeFn fn)
+{
+    if (!scratch) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    if (lane == 0) { __threadfence(); red_add_release(&scratch->producers_done, 1u); }
+    __syncwarp();
+    for (;;) {
+        uint32_t idx = 0;
+        if (lane == 0) idx = atom_add_relaxed(&scratch->cursor, 1u);
+        idx = __shfl_sync(0xffffffffu, idx, 0);
+        if (idx >= scratch->capacity) return;
+        graph_item_t* it = &scratch->items[idx];
+        uint64_t end = 0;
+        spin_t sp;
+        for (;;) {
+            uint32_t done = 0;
+            if (lane == 0) {
+                end = ld_acquire_gpu(&it->end);
+                if (end == 0 && ld_acquire_gpu(&scratch->producers_done) == n_warps_total &&
+                    ld_acquire_gpu(&scratch->n_items) <= idx) done = 1;
+                if (end == 0 && !done) end = ld_acquire_gpu(&it->end);
+            }
+            end = __shfl_sync(0xffffffffu, end, 0);
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (end != 0) break;
+            if (done) return;
+            if (__any_sync(0xffffffffu, sp.expired(col.cache.status, BAM_AT_PAGE_BUSY, idx))) return;
+        }
+        const uint64_t u = it->u, begin = it->begin;
+        if (!warp_walk_edges_w(col, wt, begin, end, queue, [&](uint64_t nb, uint32_t w) { fn(u, nb, w); })) return;
+    }
+}
+
+/* One relaxation sweep of label-correcting single-source shortest paths (benchmarks/sssp/main.cu:
+ * 115-146, 174-202: kernel_*_pc): every vertex flagged in `label` offers cost + weight to its
+ * neighbours with atomicMin on new_cost and clears its flag.  The reference samples the vertex's
+ * cost once and leaves the loop when it changes; here the current value is read per edge, which
+ * offers the same or a better bound (every value new_cost ever holds is the length of a real path). */
+struct SsspSweepWork {
+    range_d_t<uint64_t> off, col;
+    wrange_t wt;
+    uint64_t v_begin, v_end;
+    uint8_t* label;
+    uint32_t* new_cost;
+    uint64_t* scanned;
+    graph_scratch_t* scratch;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint32_t lane = threadIdx.x & 31u;
+        const uint32_t wpb = blockDim.x >> 5;
+        const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
+        const uint64_t nwarps = (uint64_t)nvb * wpb;
+        const uint32_t queue = (uint32_t)warp;
+        uint64_t edges = 0;
+        uint32_t* nc = new_cost;
+        auto relax = [&](uint64_t u, uint64_t nb, uint32_t w) {
+            const uint32_t cand = *reinterpret_cast<volatile uint32_t*>(&nc[u]) + w;
+            if (*reinterpret_cast<volatile uint32_t*>(&nc[nb]) > cand) atomicMin(&nc[nb], cand);
+        };
+        for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
+            const uint64_t v = c0 + lane;
+            const bool act = v < v_end && label[v] != 0;
+            if (__ballot_sync(0xffffffffu, act) == 0) continue;
+            if (act) label[v] = 0;
+            if (!chunk_visit_w(off, col, wt, v, v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t w) { relax(c0 + src, nb, w); })) break;
+        }
+        consume_heavy_items_w(col, wt, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t w) { relax(u, nb, w); });
+        warp_sum_to(edges, scanned);
+    }
+};
+
+/* update of benchmarks/sssp/main.cu:282-292: a vertex whose tentative cost fell becomes active */
+__global__ void k_sssp_update(uint8_t* label, uint32_t* cost, const uint32_t* new_cost, uint64_t n, uint32_t* changed)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (uint64_t)gridDim.x * blockDim.x;
+    bool ch = false;
+    for (uint64_t i = tid; i < n; i += nthr)
+        if (new_cost[i] < cost[i]) { cost[i] = new_cost[i]; label[i] = 1; ch = true; }
+    if (ch) *changed = 1u;
+}
+
+__global__ void k_sssp_init(uint8_t* label, uint32_t* cost, uint32_t* new_cost, uint64_t n, uint64_t src)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = tid; i < n; i += nthr) {
+        const bool is = i == src;
+        label[i] = is ? 1 : 0;
+        cost[i] = new_cost[i] = is ? 0u : BAM_BFS_INF;
+    }
+}
+
+/* ---- PageRank (benchmarks/pagerank/main.cu:107-115 initialize, :137-160 / :252-274 kernel_*_pc,
+ * :412-421 update): push-based delta PageRank.  Every active vertex adds delta[v] to the residual
+ * of each neighbour; a vertex whose residual exceeds the tolerance folds it into its value and
+ * becomes active with delta = residual * alpha / degree.
+ * The reference computes in float with atomicAdd, so its result depends on the order the adds
+ * happen to land in.  Here every quantity is a 64-bit fixed-point number with BAM_PR_FRAC_BITS
+ * fraction bits and alpha is a ratio of integers: integer adds commute, so the result is
+ * bit-identical for every schedule, every grid size and a sequential CPU run. */
+struct PrSweepWork {
+    range_d_t<uint64_t> off, col;
+    uint64_t v_begin, v_end;
+    uint8_t* label;
+    const uint64_t* delta;
+    unsigned long long* residual;
+    uint64_t* scanned;
+    graph_scratch_t* scratch;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint32_t lane = threadIdx.x & 31u;
+        const uint32_t wpb = blockDim.x >> 5;
+        const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
+        const uint64_t nwarps = (uint64_t)nvb * wpb;
+        const uint32_t queue = (uint32_t)warp;
+        uint64_t edges = 0;
+        unsigned long long* res = residual;
+        const uint64_t* dl = delta;
+        auto push = [&](uint64_t u, uint64_t nb) { atomicAdd(&res[nb], (unsigned long long)dl[u]); };
+        for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
+            const uint64_t v = c0 + lane;
+            const bool act = v < v_end && label[v] != 0;
+            if (__ballot_sync(0xffffffffu, act) == 0) continue;
+            if (act) label[v] = 0;
+            if (!chunk_visit(off, col, v, v, act, queue, scratch, edges, [&](int src, uint64_t nb) { push(c0 + src, nb); })) break;
+        }
+        consume_heavy_items(col, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb) { push(u, nb); });
+        warp_sum_to(edges, scanned);
+    }
+};
+
+/* degree of every vertex, read once through the cache (the reference keeps the row offsets in
+ * plain GPU memory for its initialize / update kernels) */
+struct DegreeWork {
+    range_d_t<uint64_t> off;
+    uint64_t n;
+    uint32_t* deg;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint64_t nthr = (uint64_t)nvb * blockDim.x;
+        const uint32_t queue = (uint32_t)(((uint64_t)vb * blockDim.x + threadIdx.x) >> 5);
+        for (uint64_t c0 = (uint64_t)vb * blockDim.x + (threadIdx.x & ~31u); c0 < n; c0 += nthr) {
+            const uint64_t v = c0 + (threadIdx.x & 31u);
+            if (v < n) {
+                const uint64_t s = range_read<uint64_t>(off, v, queue);
+                const uint64_t e = range_read<uint64_t>(off, v + 1, queue);
+                deg[v] = (uint32_t)(e - s);
+            }
+            __syncwarp();
+        }
+    }
+};
+
+__global__ void k_pr_init(uint8_t* label, uint64_t* delta, uint64_t* residual, uint64_t* value, const uint32_t* deg, uint64_t n,
+                          uint64_t alpha_num, uint64_t alpha_den)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (uint64_t)gridDim.x * blockDim.x;
+    const uint64_t one = 1ull << BAM_PR_FRAC_BITS;
+    const uint64_t base = one - bam_mul_ratio(one, alpha_num, alpha_den);  /* 1 - alpha */
+    for (uint64_t i = tid; i < n; i += nthr) {
+        value[i] = base;
+        delta[i] = deg[i] ? bam_mul_ratio(base, alpha_num, alpha_den) / deg[i] : 0;
+        residual[i] = 0;
+        label[i] = 1;
+    }
+}
+
+__global__ void k_pr_update(uint8_t* label, uint64_t* delta, uint64_t* residual, uint64_t* value, const uint32_t* deg, uint64_t n,
+                            uint64_t tolerance, uint64_t alpha_num, uint64_t alpha_den, uint32_t* changed)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (uint64_t)gridDim.x * blockDim.x;
+    bool ch = false;
+    for (uint64_t i = tid; i < n; i += nthr) {
+        const uint64_t r = residual[i];
+        if (r > tolerance) {
+            value[i] += r;
+            delta[i] = deg[i] ? bam_mul_ratio(r, alpha_num, alpha_den) / deg[i] : 0;
+            residual[i] = 0;
+            label[i] = 1;
+            ch = true;
+        }
+    }
+    if (ch) *changed = 1u;
+}
+
 __global__ void k_bfs_init(uint32_t* label, uint64_t n, uint64_t src)
 {
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (uint64_t)gridDim.x * blockDim.x;
@@ -445,4 +717,152 @@ extern "C" int bam_ctrl_write_store_from_device(bam_ctrl_t c, uint64_t byte_offs
     CK(cudaSetDevice(c->device));
     CK(cudaMemcpyAsync(c->store_host + byte_offset, src_dev, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     return BAM_OK;
+}
+
+/* ---- SSSP and PageRank drivers ------------------------------------------------------------------ */
+
+extern "C" int bam_launch_sssp_sweep(bam_array_t offsets, bam_array_t cols, bam_array_t weights, uint64_t v_begin, uint64_t v_end,
+                                     uint8_t* label_dev, uint32_t* new_cost_dev, uint64_t* scanned_dev, void* scratch_dev,
+                                     uint64_t scratch_bytes, void* stream)
+{
+    int rc = check_graph_args(offsets, cols);
+    if (rc) return rc;
+    if (!weights || weights->elem_bytes != 4 || weights->pc != cols->pc || weights->n_elems < cols->n_elems) return BAM_EINVAL;
+    if (!label_dev || !new_cost_dev || v_end > offsets->n_elems - 1 || v_begin > v_end) return BAM_EINVAL;
+    bam_ctrl* c = offsets->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    SsspSweepWork w;
+    w.off = offsets->h_range; w.col = cols->h_range;
+    static_assert(sizeof(wrange_t) == sizeof(range_d_t<uint64_t>), "range descriptors share one layout");
+    memcpy(&w.wt, &weights->h_range, sizeof w.wt);
+    w.v_begin = v_begin; w.v_end = v_end; w.label = label_dev; w.new_cost = new_cost_dev; w.scanned = scanned_dev;
+    w.scratch = nullptr;
+    rc = prepare_scratch(scratch_dev, scratch_bytes, (cudaStream_t)stream, &w.scratch);
+    if (rc) return rc;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+/* The host loop of benchmarks/sssp/main.cu:640-720: sweep, update, repeat until nothing changed. */
+extern "C" int bam_sssp_run(bam_array_t offsets, bam_array_t cols, bam_array_t weights, uint64_t n_vertices, uint64_t source,
+                            uint32_t* cost_dev, uint32_t* n_iters_out, uint64_t* edges_scanned_out)
+{
+    int rc = check_graph_args(offsets, cols);
+    if (rc) return rc;
+    if (!weights || !cost_dev || source >= n_vertices || n_vertices + 1 > offsets->n_elems) return BAM_EINVAL;
+    bam_ctrl* c = offsets->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    uint8_t* d_buf = nullptr;          /* new_cost (4n) | label (n) | changed (4) | scanned (8), 16-byte aligned parts */
+    const uint64_t o_label = (4 * n_vertices + 15) / 16 * 16, o_changed = (o_label + n_vertices + 15) / 16 * 16, o_scanned = o_changed + 8;
+    cudaError_t e = cudaMalloc(&d_buf, o_scanned + 8);
+    if (e != cudaSuccess) { g_last_cuda = e; (void)cudaGetLastError(); return BAM_ENOMEM; }
+    uint32_t* d_new = reinterpret_cast<uint32_t*>(d_buf);
+    uint8_t* d_label = d_buf + o_label;
+    uint32_t* d_changed = reinterpret_cast<uint32_t*>(d_buf + o_changed);
+    uint64_t* d_scanned = reinterpret_cast<uint64_t*>(d_buf + o_scanned);
+    cudaMemset(d_scanned, 0, 8);
+    void* d_scratch = nullptr;
+    const uint64_t scratch_bytes = bam_graph_scratch_bytes(cols->n_elems);
+    if (cudaMalloc(&d_scratch, scratch_bytes) != cudaSuccess) { (void)cudaGetLastError(); d_scratch = nullptr; }
+    k_sssp_init<<<c->num_sms * 4, 256>>>(d_label, cost_dev, d_new, n_vertices, source);
+    uint32_t iters = 0;
+    rc = BAM_OK;
+    for (;;) {
+        rc = bam_launch_sssp_sweep(offsets, cols, weights, 0, n_vertices, d_label, d_new, d_scanned, d_scratch,
+                                   d_scratch ? scratch_bytes : 0, nullptr);
+        if (rc) break;
+        iters++;
+        cudaMemsetAsync(d_changed, 0, 4, 0);
+        k_sssp_update<<<c->num_sms * 4, 256>>>(d_label, cost_dev, d_new, n_vertices, d_changed);
+        uint32_t changed = 0;
+        e = cudaMemcpy(&changed, d_changed, 4, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) { g_last_cuda = e; rc = BAM_ECUDA; break; }
+        bam_status_t st;
+        cudaMemcpy(&st, c->d_status, sizeof st, cudaMemcpyDeviceToHost);
+        if (st.code) { rc = (int)st.code; break; }
+        if (!changed) break;
+    }
+    if (n_iters_out) *n_iters_out = iters;
+    if (edges_scanned_out) cudaMemcpy(edges_scanned_out, d_scanned, 8, cudaMemcpyDeviceToHost);
+    cudaFree(d_buf); cudaFree(d_scratch);
+    return rc;
+}
+
+extern "C" int bam_launch_pr_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint8_t* label_dev,
+                                   const uint64_t* delta_dev, uint64_t* residual_dev, uint64_t* scanned_dev, void* scratch_dev,
+                                   uint64_t scratch_bytes, void* stream)
+{
+    int rc = check_graph_args(offsets, cols);
+    if (rc) return rc;
+    if (!label_dev || !delta_dev || !residual_dev || v_end > offsets->n_elems - 1 || v_begin > v_end) return BAM_EINVAL;
+    bam_ctrl* c = offsets->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    PrSweepWork w;
+    w.off = offsets->h_range; w.col = cols->h_range; w.v_begin = v_begin; w.v_end = v_end;
+    w.label = label_dev; w.delta = delta_dev; w.residual = reinterpret_cast<unsigned long long*>(residual_dev); w.scanned = scanned_dev;
+    w.scratch = nullptr;
+    rc = prepare_scratch(scratch_dev, scratch_bytes, (cudaStream_t)stream, &w.scratch);
+    if (rc) return rc;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_degrees(bam_array_t offsets, uint64_t n_vertices, uint32_t* deg_dev, void* stream)
+{
+    if (!offsets || offsets->elem_bytes != 8 || !deg_dev || n_vertices + 1 > offsets->n_elems) return BAM_EINVAL;
+    bam_ctrl* c = offsets->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    DegreeWork w;
+    w.off = offsets->h_range; w.n = n_vertices; w.deg = deg_dev;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+/* The host loop of benchmarks/pagerank/main.cu:678-772: initialize, then sweep + update until no
+ * residual exceeds the tolerance or max_iters sweeps have run (the reference stops at 100). */
+extern "C" int bam_pagerank_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vertices, uint64_t alpha_num, uint64_t alpha_den,
+                                uint64_t tolerance_q, uint32_t max_iters, uint64_t* value_dev, uint32_t* n_iters_out,
+                                uint64_t* edges_scanned_out)
+{
+    int rc = check_graph_args(offsets, cols);
+    if (rc) return rc;
+    if (!value_dev || n_vertices + 1 > offsets->n_elems || alpha_den == 0 || alpha_num >= alpha_den || alpha_den > (1u << 20)) return BAM_EINVAL;
+    bam_ctrl* c = offsets->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    uint8_t* d_buf = nullptr;          /* delta (8n) | residual (8n) | deg (4n) | label (n) | changed | scanned */
+    const uint64_t o_res = 8 * n_vertices, o_deg = 16 * n_vertices, o_label = 20 * n_vertices;
+    const uint64_t o_changed = (o_label + n_vertices + 15) / 16 * 16, o_scanned = o_changed + 8;
+    cudaError_t e = cudaMalloc(&d_buf, o_scanned + 8);
+    if (e != cudaSuccess) { g_last_cuda = e; (void)cudaGetLastError(); return BAM_ENOMEM; }
+    uint64_t* d_delta = reinterpret_cast<uint64_t*>(d_buf);
+    uint64_t* d_res = reinterpret_cast<uint64_t*>(d_buf + o_res);
+    uint32_t* d_deg = reinterpret_cast<uint32_t*>(d_buf + o_deg);
+    uint8_t* d_label = d_buf + o_label;
+    uint32_t* d_changed = reinterpret_cast<uint32_t*>(d_buf + o_changed);
+    uint64_t* d_scanned = reinterpret_cast<uint64_t*>(d_buf + o_scanned);
+    cudaMemset(d_scanned, 0, 8);
+    void* d_scratch = nullptr;
+    const uint64_t scratch_bytes = bam_graph_scratch_bytes(cols->n_elems);
+    if (cudaMalloc(&d_scratch, scratch_bytes) != cudaSuccess) { (void)cudaGetLastError(); d_scratch = nullptr; }
+    uint32_t iters = 0;
+    rc = bam_launch_degrees(offsets, n_vertices, d_deg, nullptr);
+    if (rc == BAM_OK) {
+        k_pr_init<<<c->num_sms * 4, 256>>>(d_label, d_delta, d_res, value_dev, d_deg, n_vertices, alpha_num, alpha_den);
+        while (iters < max_iters) {
+            rc = bam_launch_pr_sweep(offsets, cols, 0, n_vertices, d_label, d_delta, d_res, d_scanned, d_scratch,
+                                     d_scratch ? scratch_bytes : 0, nullptr);
+            if (rc) break;
+            iters++;
+            cudaMemsetAsync(d_changed, 0, 4, 0);
+            k_pr_update<<<c->num_sms * 4, 256>>>(d_label, d_delta, d_res, value_dev, d_deg, n_vertices, tolerance_q, alpha_num, alpha_den, d_changed);
+            uint32_t changed = 0;
+            e = cudaMemcpy(&changed, d_changed, 4, cudaMemcpyDeviceToHost);
+            if (e != cudaSuccess) { g_last_cuda = e; rc = BAM_ECUDA; break; }
+            bam_status_t st;
+            cudaMemcpy(&st, c->d_status, sizeof st, cudaMemcpyDeviceToHost);
+            if (st.code) { rc = (int)st.code; break; }
+            if (!changed) break;
+        }
+    }
+    if (n_iters_out) *n_iters_out = iters;
+    if (edges_scanned_out) cudaMemcpy(edges_scanned_out, d_scanned, 8, cudaMemcpyDeviceToHost);
+    cudaFree(d_buf); cudaFree(d_scratch);
+    return rc;
 }

@@ -75,18 +75,24 @@ def load_bel_graph(prefix, device="cuda"):
     return off, cols
 
 
+PR_FRAC_BITS = 40     # fraction bits of the fixed-point PageRank values (BAM_PR_FRAC_BITS)
+
+
 class CsrGraph:
     """A CSR graph stored behind an emulated NVMe controller and read through a page cache."""
 
     def __init__(self, offsets, cols, cache_pages, cuda_device=0, queue_depth=1024, num_queues=128, page_size=4096,
-                 ctrl_blocks=0):
+                 ctrl_blocks=0, weights=None):
+        """`weights` (optional, int32 tensor, one per edge) is stored behind the column indices as a
+        third array of u32 elements (the .val file of the reference's weighted benchmarks)."""
         import torch
         self.n = offsets.numel() - 1
         self.m = cols.numel()
         pad = lambda b: (b + page_size - 1) // page_size * page_size  # noqa: E731
         self.off_bytes = pad((self.n + 1) * 8)
         self.col_bytes = pad(max(1, self.m) * 8)
-        self.ctrl = Controller(self.off_bytes + self.col_bytes, cuda_device, queue_depth=queue_depth,
+        self.wt_bytes = pad(max(1, self.m) * 4) if weights is not None else 0
+        self.ctrl = Controller(self.off_bytes + self.col_bytes + self.wt_bytes, cuda_device, queue_depth=queue_depth,
                                num_queues=num_queues)
         if ctrl_blocks:
             self.ctrl.configure(ctrl_blocks=ctrl_blocks)
@@ -94,34 +100,65 @@ class CsrGraph:
         check(lib.bam_ctrl_write_store_from_device(self.ctrl.h, 0, _ptr(offsets), (self.n + 1) * 8, None), "write offsets")
         if self.m:
             check(lib.bam_ctrl_write_store_from_device(self.ctrl.h, self.off_bytes, _ptr(cols), self.m * 8, None), "write cols")
+            if weights is not None:
+                assert weights.numel() == self.m and weights.element_size() == 4
+                check(lib.bam_ctrl_write_store_from_device(self.ctrl.h, self.off_bytes + self.col_bytes, _ptr(weights),
+                                                           self.m * 4, None), "write weights")
         torch.cuda.synchronize()
         self.cache = PageCache(self.ctrl, page_size, cache_pages)
         self._owns = True
-        self._bind(cuda_device)
+        self._bind(cuda_device, weighted=weights is not None)
 
     @classmethod
     def over_cache(cls, cache, n_vertices, n_edges, off_bytes, dist=0, cuda_device=0):
         """A graph whose store image (offsets padded to `off_bytes`, then the edges) is already on the
         media behind `cache` -- one controller or several, laid out as `dist` says."""
         g = cls.__new__(cls)
-        g.n, g.m, g.off_bytes = n_vertices, n_edges, off_bytes
+        g.n, g.m, g.off_bytes, g.col_bytes = n_vertices, n_edges, off_bytes, 0
         g.ctrl, g.cache, g._owns = cache.ctrl, cache, False
         g._bind(cuda_device, dist)
         return g
 
-    def _bind(self, cuda_device, dist=0):
+    def _bind(self, cuda_device, dist=0, weighted=False):
         import torch
         self.offsets = Array(self.cache, self.n + 1, 8, 0, dist)
         self.cols = Array(self.cache, max(1, self.m), 8, self.off_bytes, dist)
+        self.weights = Array(self.cache, max(1, self.m), 4, self.off_bytes + self.col_bytes, dist) if weighted else None
         self.device = cuda_device
         # per-level scratch for the work items of hub vertices
         self.scratch_bytes = self.ctrl.lib.bam_graph_scratch_bytes(max(1, self.m))
         self.scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=f"cuda:{cuda_device}")
 
     def close(self):
+        if self.weights is not None:
+            self.weights.close()
         self.cols.close(); self.offsets.close()
         if self._owns:
             self.cache.close(); self.ctrl.close()
+
+    def sssp(self, source):
+        """Single-source shortest paths over the edge weights; returns (u32 distances as an int32
+        tensor, 0xFFFFFFFF = unreachable; sweeps; edges_scanned)."""
+        import torch
+        if self.weights is None:
+            raise ValueError("the graph has no weights")
+        cost = torch.empty(self.n, dtype=torch.int32, device=f"cuda:{self.device}")
+        ni, sc = C.c_uint32(), C.c_uint64()
+        check(self.ctrl.lib.bam_sssp_run(self.offsets.h, self.cols.h, self.weights.h, self.n, source, _ptr(cost),
+                                         C.byref(ni), C.byref(sc)), "bam_sssp_run")
+        return cost, ni.value, sc.value
+
+    def pagerank(self, alpha=(85, 100), tolerance_q=None, max_iters=100):
+        """Delta PageRank in 64-bit fixed point (PR_FRAC_BITS fraction bits); returns (ranks as an int64
+        tensor of fixed-point values, sweeps, edges_scanned).  tolerance_q defaults to 0.001."""
+        import torch
+        if tolerance_q is None:
+            tolerance_q = (1 << PR_FRAC_BITS) // 1000
+        value = torch.empty(self.n, dtype=torch.int64, device=f"cuda:{self.device}")
+        ni, sc = C.c_uint32(), C.c_uint64()
+        check(self.ctrl.lib.bam_pagerank_run(self.offsets.h, self.cols.h, self.n, alpha[0], alpha[1], tolerance_q, max_iters,
+                                             _ptr(value), C.byref(ni), C.byref(sc)), "bam_pagerank_run")
+        return value, ni.value, sc.value
 
     def bfs(self, source):
         """Level-synchronous BFS from `source`; returns (levels uint32 tensor as int32 bits, n_levels, edges_scanned)."""

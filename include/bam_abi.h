@@ -216,6 +216,34 @@ int bam_bfs_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vertices, uint
                 uint32_t* label_dev, uint32_t* n_levels_out, uint64_t* edges_scanned_out);
 int bam_cc_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vertices, uint64_t* comp_dev,
                uint32_t* n_sweeps_out, uint64_t* edges_scanned_out);
+
+/* Single-source shortest paths over a weighted CSR graph (benchmarks/sssp/main.cu): `weights` is a
+ * third array over the same cache, u32 elements, weights[j] belongs to edge cols[j] (the .val file
+ * of the reference, :379-431).  One sweep (kernel_*_pc, :115-146): every vertex flagged in label_dev
+ * (u8 per vertex) offers cost + weight to its neighbours with atomicMin on new_cost_dev and clears
+ * its flag.  bam_sssp_run is the host loop (:640-720) with the update kernel (:282-292) between
+ * sweeps; cost_dev receives n_vertices u32 distances, 0xFFFFFFFF = unreachable.  Synchronous. */
+int bam_launch_sssp_sweep(bam_array_t offsets, bam_array_t cols, bam_array_t weights, uint64_t v_begin, uint64_t v_end,
+                          uint8_t* label_dev, uint32_t* new_cost_dev, uint64_t* scanned_dev, void* scratch_dev,
+                          uint64_t scratch_bytes, void* stream);
+int bam_sssp_run(bam_array_t offsets, bam_array_t cols, bam_array_t weights, uint64_t n_vertices, uint64_t source,
+                 uint32_t* cost_dev, uint32_t* n_iters_out, uint64_t* edges_scanned_out);
+
+/* Push-based delta PageRank (benchmarks/pagerank/main.cu:107-115, 137-160, 412-421, host loop
+ * :678-772).  All quantities are 64-bit fixed-point numbers with BAM_PR_FRAC_BITS (40) fraction
+ * bits and the damping factor is alpha_num / alpha_den (the reference: float, alpha 0.85,
+ * tolerance 0.001, at most 100 sweeps), which makes the result independent of the order in which
+ * the atomic adds land: bit-identical on every run.  One sweep: every vertex flagged in label_dev
+ * adds delta_dev[v] to residual_dev of each neighbour and clears its flag.  bam_launch_degrees
+ * writes the out-degree of every vertex (read once through the cache).  bam_pagerank_run is the
+ * whole loop; value_dev receives n_vertices fixed-point ranks.  Synchronous. */
+int bam_launch_pr_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint8_t* label_dev,
+                        const uint64_t* delta_dev, uint64_t* residual_dev, uint64_t* scanned_dev, void* scratch_dev,
+                        uint64_t scratch_bytes, void* stream);
+int bam_launch_degrees(bam_array_t offsets, uint64_t n_vertices, uint32_t* deg_dev, void* stream);
+int bam_pagerank_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vertices, uint64_t alpha_num, uint64_t alpha_den,
+                     uint64_t tolerance_q, uint32_t max_iters, uint64_t* value_dev, uint32_t* n_iters_out,
+                     uint64_t* edges_scanned_out);
 /* R-MAT edges [e_begin, e_end) of bam_synth.h as directed 64-bit keys (u<<32|v and v<<32|u per
  * edge, ~0 for self loops) into keys_dev[2*(e_end-e_begin)]; sorting and de-duplicating the keys
  * gives the CSR (stands in for benchmarks/bam_data_conversion.py + the dataset files). */

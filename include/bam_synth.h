@@ -198,4 +198,22 @@ BAM_HD void bam_rmat_edge(uint64_t seed, uint64_t e, uint32_t scale, bam_rmat_th
     *dst = v;
 }
 
+/* ---- edge weights and fixed-point arithmetic of the weighted / ranking traversals ---------------
+ * Weight of CSR edge j (its position in the column array): 1..64.  (The reference reads weights
+ * from a .val file beside the .bel files, benchmarks/sssp/main.cu:379-431.) */
+BAM_HD uint32_t bam_edge_weight(uint64_t seed, uint64_t j)
+{
+    return 1u + (uint32_t)(bam_splitmix64(seed ^ j) >> 58);
+}
+
+/* PageRank quantities are 64-bit fixed-point numbers with this many fraction bits; the damping
+ * factor is the ratio alpha_num / alpha_den. */
+#define BAM_PR_FRAC_BITS 40
+
+/* floor(x * num / den) without overflow for num < den. */
+BAM_HD uint64_t bam_mul_ratio(uint64_t x, uint64_t num, uint64_t den)
+{
+    return x / den * num + (x % den) * num / den;
+}
+
 #endif /* BAM_SYNTH_H */

@@ -260,6 +260,104 @@ ORC_API uint64_t orc_cc(uint64_t n, const uint64_t* offsets, const uint64_t* col
     return comps;
 }
 
+/* Weight of every CSR edge (include/bam_synth.h: bam_edge_weight). */
+ORC_API void orc_edge_weights(uint64_t seed, uint64_t n_edges, uint32_t* out)
+{
+    for (uint64_t j = 0; j < n_edges; j++) out[j] = bam_edge_weight(seed, j);
+}
+
+/* Single-source shortest paths: Dijkstra with a binary heap, so the oracle does not share the
+ * label-correcting relaxation (benchmarks/sssp/main.cu:115-146 + update :282-292) with the code
+ * under test; both end at the unique distances.  Unreachable = 0xFFFFFFFF (MYINFINITY there). */
+typedef struct { uint64_t d; uint64_t v; } heap_item_t;
+
+ORC_API void orc_sssp(uint64_t n, const uint64_t* offsets, const uint64_t* cols, const uint32_t* weights,
+                      uint64_t src, uint32_t* dist)
+{
+    uint64_t* d = (uint64_t*)malloc(n * sizeof(uint64_t));
+    for (uint64_t v = 0; v < n; v++) d[v] = ~0ull;
+    uint64_t cap = 1024, sz = 0;
+    heap_item_t* h = (heap_item_t*)malloc(cap * sizeof(heap_item_t));
+    d[src] = 0;
+    h[sz].d = 0; h[sz].v = src; sz++;
+    while (sz) {
+        heap_item_t top = h[0];
+        heap_item_t last = h[--sz];
+        uint64_t i = 0;                                     /* sift the last item down from the root */
+        for (;;) {
+            uint64_t c = 2 * i + 1;
+            if (c >= sz) break;
+            if (c + 1 < sz && h[c + 1].d < h[c].d) c++;
+            if (h[c].d >= last.d) break;
+            h[i] = h[c];
+            i = c;
+        }
+        if (sz) h[i] = last;
+        if (top.d != d[top.v]) continue;                    /* a stale entry */
+        for (uint64_t e = offsets[top.v]; e < offsets[top.v + 1]; e++) {
+            uint64_t nd = top.d + weights[e], w = cols[e];
+            if (nd < d[w]) {
+                d[w] = nd;
+                if (sz == cap) { cap *= 2; h = (heap_item_t*)realloc(h, cap * sizeof(heap_item_t)); }
+                uint64_t k = sz++;                          /* sift up */
+                while (k && h[(k - 1) / 2].d > nd) { h[k] = h[(k - 1) / 2]; k = (k - 1) / 2; }
+                h[k].d = nd; h[k].v = w;
+            }
+        }
+    }
+    for (uint64_t v = 0; v < n; v++) dist[v] = d[v] == ~0ull ? 0xFFFFFFFFu : (uint32_t)d[v];
+    free(h);
+    free(d);
+}
+
+/* Push-based delta PageRank (benchmarks/pagerank/main.cu:107-115 initialize, :117-135 kernel,
+ * :412-421 update, loop :678-772) in 64-bit fixed point with BAM_PR_FRAC_BITS fraction bits and
+ * alpha = alpha_num / alpha_den.  Integer additions commute, so this sequential restatement and
+ * any parallel schedule give identical bits.  Returns the number of sweeps. */
+ORC_API uint32_t orc_pagerank(uint64_t n, const uint64_t* offsets, const uint64_t* cols, uint64_t alpha_num,
+                              uint64_t alpha_den, uint64_t tolerance_q, uint32_t max_iters, uint64_t* value,
+                              uint64_t* edges_scanned)
+{
+    uint64_t* delta = (uint64_t*)malloc(n * sizeof(uint64_t));
+    uint64_t* residual = (uint64_t*)calloc(n, sizeof(uint64_t));
+    uint8_t* label = (uint8_t*)malloc(n);
+    const uint64_t one = 1ull << BAM_PR_FRAC_BITS;
+    const uint64_t base = one - bam_mul_ratio(one, alpha_num, alpha_den);
+    uint64_t scanned = 0;
+    for (uint64_t v = 0; v < n; v++) {
+        uint64_t deg = offsets[v + 1] - offsets[v];
+        value[v] = base;
+        delta[v] = deg ? bam_mul_ratio(base, alpha_num, alpha_den) / deg : 0;
+        label[v] = 1;
+    }
+    uint32_t iters = 0;
+    while (iters < max_iters) {
+        for (uint64_t v = 0; v < n; v++) {
+            if (!label[v]) continue;
+            label[v] = 0;
+            scanned += offsets[v + 1] - offsets[v];
+            for (uint64_t e = offsets[v]; e < offsets[v + 1]; e++) residual[cols[e]] += delta[v];
+        }
+        iters++;
+        int changed = 0;
+        for (uint64_t v = 0; v < n; v++) {
+            uint64_t r = residual[v];
+            if (r > tolerance_q) {
+                uint64_t deg = offsets[v + 1] - offsets[v];
+                value[v] += r;
+                delta[v] = deg ? bam_mul_ratio(r, alpha_num, alpha_den) / deg : 0;
+                residual[v] = 0;
+                label[v] = 1;
+                changed = 1;
+            }
+        }
+        if (!changed) break;
+    }
+    if (edges_scanned) *edges_scanned = scanned;
+    free(delta); free(residual); free(label);
+    return iters;
+}
+
 /* ===================================================================================== */
 /* Layer 2: protocol restatement on host threads                                         */
 /* ===================================================================================== */

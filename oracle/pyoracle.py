@@ -63,6 +63,10 @@ def lib():
         L.orc_bfs.argtypes = [u64, vp, vp, u64, vp]
         L.orc_cc.restype = u64
         L.orc_cc.argtypes = [u64, vp, vp, vp]
+        L.orc_edge_weights.argtypes = [u64, u64, vp]
+        L.orc_sssp.argtypes = [u64, vp, vp, vp, u64, vp]
+        L.orc_pagerank.restype = u32
+        L.orc_pagerank.argtypes = [u64, vp, vp, u64, u64, u64, u32, vp, C.POINTER(u64)]
         L.ref_array_read.restype = C.c_int
         L.ref_array_read.argtypes = [vp, u64, u32, u64, u32, u32, u32, u32, u32, vp, u64, u64, u64, u64,
                                      C.POINTER(RefResult)]
@@ -192,6 +196,36 @@ def cc(offsets, cols):
     label = np.empty(n, dtype=np.uint64)
     comps = lib().orc_cc(n, _p(offsets), _p(cols), _p(label))
     return label, comps
+
+
+PR_FRAC_BITS = 40
+
+
+def edge_weights(seed, n_edges):
+    out = np.empty(n_edges, dtype=np.uint32)
+    lib().orc_edge_weights(seed, n_edges, _p(out))
+    return out
+
+
+def sssp(offsets, cols, weights, src):
+    """Dijkstra distances (uint32, 0xFFFFFFFF = unreachable)."""
+    n = len(offsets) - 1
+    dist = np.empty(n, dtype=np.uint32)
+    weights = np.ascontiguousarray(weights, dtype=np.uint32)
+    lib().orc_sssp(n, _p(offsets), _p(cols), _p(weights), src, _p(dist))
+    return dist
+
+
+def pagerank(offsets, cols, alpha=(85, 100), tolerance_q=None, max_iters=100):
+    """Fixed-point delta PageRank; returns (values uint64 with PR_FRAC_BITS fraction bits, sweeps, edges scanned)."""
+    n = len(offsets) - 1
+    if tolerance_q is None:
+        tolerance_q = (1 << PR_FRAC_BITS) // 1000
+    value = np.empty(n, dtype=np.uint64)
+    scanned = u64()
+    iters = lib().orc_pagerank(n, _p(offsets), _p(cols), alpha[0], alpha[1], tolerance_q, max_iters, _p(value),
+                               C.byref(scanned))
+    return value, iters, scanned.value
 
 
 def ref_array_read(store, page_size, n_slots, n_qps, qdepth, lba_bytes, workers, ctrl_threads,

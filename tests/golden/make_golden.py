@@ -45,7 +45,13 @@ def main():
         src = orc.max_degree_vertex(off)
         lvl, scanned = orc.bfs(off, cols, src)
         lab, comps = orc.cc(off, cols)
-        graphs.append({"scale": scale, "seed": seed, "edge_factor": 16, "directed_edges": int(len(cols)),
+        wts = orc.edge_weights(seed + 100, len(cols))
+        dist = orc.sssp(off, cols, wts, src)
+        rank, pr_iters, pr_scanned = orc.pagerank(off, cols)
+        graphs.append({"weight_seed": seed + 100, "weights_sha256": sha(wts), "dist_sha256": sha(dist),
+                       "max_dist": int(dist[dist != 0xFFFFFFFF].max()),
+                       "rank_sha256": sha(rank), "pr_sweeps": int(pr_iters), "pr_edges_scanned": int(pr_scanned),
+                       "rank_sum_q40": int(rank.sum(dtype=np.uint64)),"scale": scale, "seed": seed, "edge_factor": 16, "directed_edges": int(len(cols)),
                        "offsets_sha256": sha(off), "cols_sha256": sha(cols), "source": int(src),
                        "levels_sha256": sha(lvl), "max_level": int(lvl[lvl != 0xFFFFFFFF].max()),
                        "reached": int((lvl != 0xFFFFFFFF).sum()), "edges_scanned": int(scanned),

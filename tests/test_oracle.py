@@ -225,6 +225,11 @@ def test_golden_fixtures(orc):
         lab, comps = orc.cc(off, cols)
         assert sha(lvl) == gph["levels_sha256"] and sha(lab) == gph["labels_sha256"]
         assert comps == gph["components"] and scanned == gph["edges_scanned"]
+        wts = orc.edge_weights(gph["weight_seed"], len(cols))
+        dist = orc.sssp(off, cols, wts, gph["source"])
+        assert sha(wts) == gph["weights_sha256"] and sha(dist) == gph["dist_sha256"]
+        rank, sweeps, pr_scanned = orc.pagerank(off, cols)
+        assert sha(rank) == gph["rank_sha256"] and sweeps == gph["pr_sweeps"] and pr_scanned == gph["pr_edges_scanned"]
 
 
 def test_protocol_restatement_graph_traversals(orc):
@@ -260,4 +265,42 @@ def test_backing_location_of_replicated_and_striped_ranges(orc):
     n_ctrls, n_pages = 3, 1000
     seen = {orc.backing_location(5, p, n_ctrls, 1) for p in range(n_pages)}
     assert len(seen) == n_pages and max(b for _, b in seen) == 5 + (n_pages - 1) // n_ctrls
+
+
+def test_sssp_oracle_matches_scipy(orc):
+    sp = pytest.importorskip("scipy.sparse")
+    from scipy.sparse.csgraph import dijkstra
+    off, cols = orc.rmat_csr(4, 10, 8)
+    n = len(off) - 1
+    wts = orc.edge_weights(9, len(cols))
+    assert wts.min() >= 1 and wts.max() <= 64 and len(np.unique(wts)) == 64
+    m = sp.csr_matrix((wts.astype(np.float64), cols.astype(np.int64), off.astype(np.int64)), shape=(n, n))
+    for src in (0, int(orc.max_degree_vertex(off))):
+        want = dijkstra(m, directed=True, indices=src)
+        got = orc.sssp(off, cols, wts, src)
+        reach = np.isfinite(want)
+        assert (got[~reach] == 0xFFFFFFFF).all() and (got[reach] == want[reach].astype(np.uint32)).all()
+
+
+def test_pagerank_oracle_against_linear_solve(orc):
+    """The fixed-point delta PageRank ends within its tolerance of the solution of
+    x = (1 - alpha) + alpha * sum_{u -> v} x_u / deg_u (no redistribution of dangling mass, as in
+    benchmarks/pagerank/main.cu), and its sweeps are order independent."""
+    off, cols = orc.rmat_csr(6, 9, 8)
+    n = len(off) - 1
+    deg = np.diff(off).astype(np.float64)
+    P = np.zeros((n, n))
+    src = np.repeat(np.arange(n), np.diff(off).astype(np.int64))
+    np.add.at(P, (cols.astype(np.int64), src), 1.0 / deg[src])
+    alpha = 0.85
+    x = np.linalg.solve(np.eye(n) - alpha * P, np.full(n, 1 - alpha))
+    rank, sweeps, scanned = orc.pagerank(off, cols)
+    v = rank.astype(np.float64) / float(1 << orc.PR_FRAC_BITS)
+    assert 1 < sweeps < 100 and scanned >= len(cols)
+    assert np.abs(v - x).sum() / x.sum() < 0.01
+    assert (np.abs(v - x) / x).max() < 0.02
+    # a tighter tolerance gets closer
+    rank2, sweeps2, _ = orc.pagerank(off, cols, tolerance_q=(1 << orc.PR_FRAC_BITS) // 1000000)
+    v2 = rank2.astype(np.float64) / float(1 << orc.PR_FRAC_BITS)
+    assert sweeps2 >= sweeps and np.abs(v2 - x).sum() / x.sum() < 1e-4
 
