@@ -49,7 +49,7 @@ def parse():
     ap.add_argument("--depth", type=int, default=1024)
     ap.add_argument("--ctrl-blocks", type=int, default=0)
     ap.add_argument("--batch", type=int, default=0)
-    ap.add_argument("--workload", default="zipf", choices=["zipf", "bfs", "cc", "block", "array"],
+    ap.add_argument("--workload", default="zipf", choices=["zipf", "bfs", "cc", "sssp", "pagerank", "block", "array"],
                     help="zipf = the headline skewed array scan; bfs / cc = graph traversals through bam::array; "
                          "block = raw 4 KiB random reads (queue count x depth sweep); array = uniform random reads, 1 queue pair")
     ap.add_argument("--reqs-log2", type=int, default=24, help="block: log2 of the requests per sweep point")
@@ -307,6 +307,133 @@ def run_graph(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def verify_sssp(off, cols, wts, dist, src):
+    """A certificate of shortest-path distances with positive weights, checked on the device:
+    dist[src] == 0; no edge out of a reached vertex can shorten its head (so heads of reached
+    vertices are reached); every reached vertex but the source has an edge that it is tight on."""
+    import torch
+    n = off.numel() - 1
+    inf = 0xFFFFFFFF
+    d = dist.to(torch.int64) & inf
+    srcs = torch.repeat_interleave(torch.arange(n, device=off.device), off[1:] - off[:-1])
+    du, dv, w = d[srcs], d[cols], wts.to(torch.int64)
+    reach = du != inf
+    ok = bool(d[src] == 0) and bool((dv[reach] <= du[reach] + w[reach]).all())
+    tight = torch.zeros(n, dtype=torch.bool, device=off.device)
+    tight[cols[reach & (dv == du + w)]] = True
+    need = (d != inf)
+    need[src] = False
+    return ok and bool(tight[need].all())
+
+
+def verify_pagerank(off, cols, value, sweeps, alpha=(85, 100), frac_bits=40, max_iters=100):
+    """The same fixed-point sweeps recomputed with plain tensor operations on a copy of the CSR in
+    GPU memory (integer adds commute, so the result must be identical bit for bit)."""
+    import torch
+    n = off.numel() - 1
+    dev = off.device
+    num, den = alpha
+    ratio = lambda x: x // den * num + (x % den) * num // den  # noqa: E731
+    one = 1 << frac_bits
+    tol = one // 1000
+    deg = off[1:] - off[:-1]
+    degc = deg.clamp(min=1)
+    srcs = torch.repeat_interleave(torch.arange(n, device=dev), deg)
+    base = one - (one // den * num + (one % den) * num // den)
+    val = torch.full((n,), base, dtype=torch.int64, device=dev)
+    delta = torch.where(deg > 0, torch.full((n,), ratio(base), dtype=torch.int64, device=dev) // degc, torch.zeros_like(val))
+    res = torch.zeros(n, dtype=torch.int64, device=dev)
+    label = torch.ones(n, dtype=torch.bool, device=dev)
+    it = 0
+    while it < max_iters:
+        res.index_add_(0, cols, torch.where(label[srcs], delta[srcs], torch.zeros((), dtype=torch.int64, device=dev)))
+        it += 1
+        label = res > tol
+        if not bool(label.any()):
+            break
+        val = torch.where(label, val + res, val)
+        delta = torch.where(label, torch.where(deg > 0, ratio(res) // degc, torch.zeros_like(res)), delta)
+        res = torch.where(label, torch.zeros_like(res), res)
+    return it == sweeps and bool((val == value).all())
+
+
+def run_rank(args):
+    """SSSP (label-correcting, u32 weights in a third array) or fixed-point PageRank over an R-MAT
+    graph read only through bam::array; one step = one whole run from a cold cache; 1 GPU."""
+    import torch
+    import bam_b200
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    sssp = args.workload == "sssp"
+    scale = args.scale or 24
+    cache_gib = args.cache_gib if args.cache_gib != 16.0 else 4.0
+    t0 = time.time()
+    off, cols = bam_b200.build_rmat_csr(1, scale, 16, device=dev)
+    n, m = off.numel() - 1, cols.numel()
+    src = int(torch.argmax(off[1:] - off[:-1]).item())
+    wts = None
+    if sssp:
+        # bam_edge_weight(seed, j) = 1 + (splitmix64(seed ^ j) >> 58), evaluated with tensor operations
+        x = (torch.arange(m, dtype=torch.int64, device=dev) ^ 101) + (-7046029254386353131)
+        z = (x ^ ((x >> 30) & ((1 << 34) - 1))) * (-4658895280553007687)
+        z = (z ^ ((z >> 27) & ((1 << 37) - 1))) * (-7723592293110705685)
+        z = z ^ ((z >> 31) & ((1 << 33) - 1))
+        wts = (((z >> 58) & 63) + 1).to(torch.int32)
+    gr = bam_b200.CsrGraph(off, cols, cache_pages=int(cache_gib * (1 << 30)) // PAGE, queue_depth=args.depth,
+                           num_queues=args.queues, ctrl_blocks=args.ctrl_blocks, weights=wts)
+    setup_s = time.time() - t0
+    times, ios, out, iters, scanned = [], [], None, 0, 0
+    sampler = ClockSampler(0)
+    for s in range(args.warmup + args.steps):
+        if s == args.warmup:
+            sampler.start()
+        gr.cache.invalidate()
+        gr.cache.stats(reset=True)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        out, iters, scanned = gr.sssp(src) if sssp else gr.pagerank()
+        b.record()
+        torch.cuda.synchronize()
+        gr.ctrl.check_status()
+        if s >= args.warmup:
+            times.append(a.elapsed_time(b)); ios.append(gr.cache.stats()["read_ios"])
+    clocks = sampler.stop()
+    ok = (verify_sssp(off, cols, wts, out, src) if sssp else verify_pagerank(off, cols, out, iters)) and gr.cache.audit() == 0
+    t = float(np.mean(times)) * 1e-3
+    line = {"metric": ("SSSP" if sssp else "PageRank") + " GTEPS through bam::array", "value": scanned / t / 1e9, "unit": "GTEPS",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u32" if sssp else "u64 fixed point (40 fraction bits)",
+            "data": "synthetic",
+            "config": {"workload": ("SSSP, u32 weights 1..64 in a third array" if sssp else "push-based delta PageRank, alpha 0.85, "
+                                    "tolerance 0.001, at most 100 sweeps") + f" over R-MAT scale {scale} edge factor 16, u64 offsets "
+                       "and edges read through the page cache, cold cache at the start of every run",
+                       "vertices": n, "directed_edges": m, "cache_gib_per_gpu": cache_gib, "queues": args.queues,
+                       "queue_depth": args.depth, "source": src, "l2": "graph (GiB) far larger than L2; no explicit flush"},
+            "sweeps": iters, "edges_scanned_per_step": scanned, "read_ios_per_step": float(np.mean(ios)),
+            "link_gb_per_s": float(np.mean(ios)) * PAGE / t / 1e9, "verified": bool(ok), "gpu_launches": (iters + (0 if sssp else 1)) * args.steps,
+            "clocks": clocks, "setup_s": setup_s}
+    if not args.no_cpu_baseline:
+        try:
+            from oracle import pyoracle as orc
+            cs = min(scale, 20)                                   # a bounded sample: the same generator at a smaller scale
+            o, c = orc.rmat_csr(1, cs, 16)
+            t1 = time.time()
+            if sssp:
+                orc.sssp(o, c, orc.edge_weights(101, len(c)), orc.max_degree_vertex(o))
+                sc = len(c)
+            else:
+                _, _, sc = orc.pagerank(o, c)
+            dt = time.time() - t1
+            line["cpu_baseline"] = {"value": sc / dt / 1e9, "unit": "GTEPS", "cores": 1, "kind": "port",
+                                    "sample": f"the result oracle ({'Dijkstra' if sssp else 'sequential sweeps'}) on the same generator "
+                                              f"at scale {cs}, graph in host memory"}
+        except Exception as e:
+            line["cpu_baseline"] = {"value": None, "unit": "GTEPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+    print(json.dumps(line), flush=True)
+    gr.close()
+
+
 def run_block(args):
     """Block-level random read throughput (the nvm-block-bench shape): 4 KiB reads at seeded random
     page-aligned offsets of a 16 GiB store, no cache reuse, swept over queue count x depth.  Every
@@ -407,6 +534,9 @@ def main():
         return
     if args.workload in ("bfs", "cc"):
         run_graph(args, rank, world, local_rank)
+        return
+    if args.workload in ("sssp", "pagerank"):
+        run_rank(args)
         return
     if args.workload in ("block", "array"):
         if rank == 0:
