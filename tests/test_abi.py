@@ -90,3 +90,18 @@ def test_bel_file_round_trip(bam, tmp_path):
     import pytest
     with pytest.raises(ValueError):
         bam.read_bel(prefix + ".bad")
+
+
+def test_reference_include_list_compiles(tmp_path):
+    """tests/cpp/include_compat.cu includes the headers a benchmark of the reference includes, under
+    the reference's names, and touches the types they must provide (compile only, no GPU)."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    src = os.path.join(ROOT, "tests", "cpp", "include_compat.cu")
+    res = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-I" + os.path.join(ROOT, "include"),
+                          "-c", src, "-o", str(tmp_path / "include_compat.o")], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+
