@@ -177,6 +177,98 @@ struct array_d_t {
             else atomicAdd(p, val);
         });
     }
+
+    /* A pinned view of the page that holds element i (reference: returned_cache_page_t and
+     * get_raw / release_raw, page_cache.h:1370-1438): addr points at the first element of the
+     * page, size is the number of elements in it, offset the position of element i.  Every lane
+     * that calls get_raw(i) calls release_raw(i) with the same i when it is done; lanes of a warp
+     * that ask for the same page share one pin.  addr == nullptr after a failure. */
+    struct raw_page_t { T* addr; uint32_t size; uint32_t offset; };
+
+    BAM_DEV raw_page_t get_raw(size_t i) const
+    {
+        raw_page_t ret = { nullptr, 0u, 0u };
+        const uint32_t mask = __activemask();
+        const int64_t ri = find_range(i);
+        const bool valid = ri >= 0;
+        const range_d_t<T>& r = d_ranges[valid ? ri : 0];
+        const uint64_t page = valid ? r.get_page(i) : ~0ull;
+        const uint32_t eq = __match_any_sync(mask, valid ? r.get_global_address(page) : ~0ull);
+        const uint32_t leader = __ffs(eq) - 1;
+        uint32_t slot = range_pin_page(r, mask, valid && lane_id() == leader, valid ? page : 0, __popc(eq), default_queue());
+        slot = __shfl_sync(eq, slot, leader);
+        if (!valid) { status_fail(d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i); return ret; }
+        if (slot > BAM_SLOT_MAX) return ret;
+        ret.addr = reinterpret_cast<T*>(r.get_cache_page_addr(slot));
+        ret.size = (uint32_t)(r.cache.page_size / sizeof(T));
+        ret.offset = (uint32_t)(r.get_subindex(i) / sizeof(T));
+        return ret;
+    }
+
+    /* The lanes that call this together must be the lanes that called get_raw together. */
+    BAM_DEV void release_raw(size_t i, const raw_page_t& view) const
+    {
+        const uint32_t mask = __activemask();
+        const bool held = view.addr != nullptr;
+        const uint32_t eq = __match_any_sync(mask, held ? (uint64_t)(uintptr_t)view.addr : ~0ull);
+        if (!held || lane_id() != (uint32_t)(__ffs(eq) - 1)) return;
+        const int64_t ri = find_range(i);
+        const range_d_t<T>& r = d_ranges[ri >= 0 ? ri : 0];
+        const uint32_t slot = (uint32_t)(((uint64_t)(uintptr_t)view.addr - (uint64_t)(uintptr_t)r.cache.base_addr) >> r.cache.page_size_log);
+        r.release_page(slot, __popc(eq));
+    }
+
+    /* Pin the page of element i and describe it (reference: array_d_t::acquire_page,
+     * page_cache.h:1473-1505, what bam_ptr is built on): returns the address of element `start`,
+     * the first element of the page; [start, end) are the element indices the page holds; `slot`
+     * is what release_page takes. */
+    BAM_DEV T* acquire_page(size_t i, uint32_t& slot, size_t& start, size_t& end) const
+    {
+        raw_page_t v = get_raw(i);
+        if (!v.addr) { slot = BAM_SLOT_ERR; start = end = 0; return nullptr; }
+        const range_d_t<T>& r = d_ranges[find_range(i)];
+        slot = (uint32_t)(((uint64_t)(uintptr_t)v.addr - (uint64_t)(uintptr_t)r.cache.base_addr) >> r.cache.page_size_log);
+        start = i - v.offset;
+        end = start + v.size;
+        return v.addr;
+    }
+    BAM_DEV void release_page(size_t i, uint32_t slot) const
+    {
+        const uint32_t mask = __activemask();
+        const bool held = slot <= BAM_SLOT_MAX;
+        const uint32_t eq = __match_any_sync(mask, held ? (uint64_t)slot : ~0ull);
+        if (held && lane_id() == (uint32_t)(__ffs(eq) - 1)) d_ranges[find_range(i)].release_page(slot, __popc(eq));
+    }
+
+    /* The whole warp copies `count` elements starting at element i into dest (global or shared
+     * memory); all 32 lanes call with the same arguments.  The reference's memcpy
+     * (page_cache.h:1256-1316) copies from one page; here the run may cross pages. */
+    BAM_DEV void memcpy(uint64_t i, uint64_t count, T* dest) const
+    {
+        const uint32_t lane = lane_id();
+        while (count) {
+            const int64_t ri = find_range(i);
+            if (ri < 0) { status_fail(d_ranges[0].cache.status, BAM_ERANGE, BAM_AT_RANGE, i); return; }
+            const range_d_t<T>& r = d_ranges[ri];
+            const uint64_t page = r.get_page(i);
+            const uint32_t off = (uint32_t)(r.get_subindex(i) / sizeof(T));
+            const uint32_t per_page = (uint32_t)(r.cache.page_size / sizeof(T));
+            const uint64_t n = count < per_page - off ? count : per_page - off;
+            uint32_t slot = range_pin_page(r, 0xffffffffu, lane == 0, page, 1, default_queue());
+            slot = __shfl_sync(0xffffffffu, slot, 0);
+            if (slot > BAM_SLOT_MAX) return;
+            const T* src = reinterpret_cast<const T*>(r.get_cache_page_addr(slot)) + off;
+            if ((((uintptr_t)src | (uintptr_t)dest) & 15u) == 0 && (n * sizeof(T)) % 16 == 0) {
+                const uint4* s4 = reinterpret_cast<const uint4*>(src);
+                uint4* d4 = reinterpret_cast<uint4*>(dest);
+                for (uint64_t k = lane; k < n * sizeof(T) / 16; k += 32) d4[k] = s4[k];
+            } else
+                for (uint64_t k = lane; k < n; k += 32) dest[k] = src[k];
+            __syncwarp();
+            if (lane == 0) r.release_page(slot, 1);
+            i += n; dest += n; count -= n;
+        }
+    }
 };
 
 /* Same read as array_d_t<T>::seq_read for the common single-range array whose descriptor sits
@@ -306,6 +398,8 @@ struct bafs_ptr {
     __host__ __device__ bafs_ptr& operator--() { --start_idx; return *this; }
     __host__ __device__ bafs_ptr operator--(int) { bafs_ptr c(*this); --start_idx; return c; }
     __host__ __device__ bool operator==(const bafs_ptr& o) const { return d == o.d && start_idx == o.start_idx; }
+    /* warp-wide copy of `count` elements from element src_idx on (bafs_ptr.h:121-123) */
+    BAM_DEV void memcpy_to_array_aligned(uint64_t src_idx, uint64_t count, T* dest) const { d->memcpy(start_idx + src_idx, count, dest); }
     __host__ __device__ bool operator!=(const bafs_ptr& o) const { return !(*this == o); }
 };
 

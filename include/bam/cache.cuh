@@ -236,6 +236,37 @@ BAM_DEV int warp_write_back(uint32_t mask, bool wb, const page_cache_d_t& pc, ui
     return rc;
 }
 
+/* Raw block I/O between the backing store and cache slot pc_entry, under the reference's names
+ * (read_data / write_data / access_data, page_cache.h:2009-2132): one thread, blocking; any number
+ * of threads may call concurrently and divergently.  Returns BAM_OK or an error code. */
+BAM_DEV int access_data(const page_cache_d_t* pc, QueuePair* qp, uint64_t starting_lba, uint64_t n_blocks,
+                        unsigned long long pc_entry, uint8_t opcode)
+{
+    return access_data_raw(qp, starting_lba, (uint32_t)n_blocks, slot_bus_addr(*pc, (uint32_t)pc_entry), slot_prp2(*pc, (uint32_t)pc_entry), opcode);
+}
+BAM_DEV int read_data(const page_cache_d_t* pc, QueuePair* qp, uint64_t starting_lba, uint64_t n_blocks, unsigned long long pc_entry)
+{
+    return access_data(pc, qp, starting_lba, n_blocks, pc_entry, NVM_IO_READ);
+}
+BAM_DEV int write_data(const page_cache_d_t* pc, QueuePair* qp, uint64_t starting_lba, uint64_t n_blocks, unsigned long long pc_entry)
+{
+    return access_data(pc, qp, starting_lba, n_blocks, pc_entry, NVM_IO_WRITE);
+}
+/* The asynchronous pair (access_data_async / poll_async, page_cache.h:1930-1959): submit now, wait
+ * later.  A thread must keep fewer commands outstanding than the queue is deep.  *cid identifies
+ * the command for poll_async; *sq_pos is the submission slot (informational). */
+BAM_DEV int access_data_async(const page_cache_d_t* pc, QueuePair* qp, uint64_t starting_lba, uint64_t n_blocks,
+                              unsigned long long pc_entry, uint8_t opcode, uint16_t* cid, uint16_t* sq_pos)
+{
+    uint32_t c = 0, pos = 0;
+    const int rc = access_data_submit(qp, starting_lba, (uint32_t)n_blocks, slot_bus_addr(*pc, (uint32_t)pc_entry),
+                                      slot_prp2(*pc, (uint32_t)pc_entry), opcode, &c, &pos);
+    *cid = (uint16_t)c;
+    *sq_pos = (uint16_t)pos;
+    return rc;
+}
+BAM_DEV int poll_async(QueuePair* qp, uint16_t cid, uint16_t /*sq_pos*/) { return access_data_complete(qp, cid); }
+
 BAM_DEV void count_hit(const page_cache_d_t& pc, uint32_t count) { red_add_relaxed(&pc.stats[get_smid() & (BAM_STAT_STRIPES - 1)].hits, (uint64_t)count); }
 BAM_DEV void count_miss(const page_cache_d_t& pc, uint32_t count)
 {

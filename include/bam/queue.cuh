@@ -503,12 +503,10 @@ BAM_DEV int warp_io(uint32_t mask, bool active, QueuePair* qp, uint64_t starting
     return rc;
 }
 
-/* One blocking I/O: build the command, submit, wait, retire.  Counterpart of read_data /
- * write_data / access_data (include/page_cache.h:2009-2132); `bus_addr` is PRP1 (the cache
- * slot), `bus_addr2` PRP2 when the transfer spans more than one controller page.
- * Returns 0, or a BAM_E* code after recording it in the status block. */
-BAM_DEV int access_data_raw(QueuePair* qp, uint64_t starting_lba, uint32_t n_blocks,
-                            uint64_t bus_addr, uint64_t bus_addr2, uint8_t opcode)
+/* Submit half of one thread's I/O: build the command, claim a slot and an id, publish.  On
+ * success *cid_out names the command for access_data_complete. */
+BAM_DEV int access_data_submit(QueuePair* qp, uint64_t starting_lba, uint32_t n_blocks, uint64_t bus_addr, uint64_t bus_addr2,
+                               uint8_t opcode, uint32_t* cid_out, uint32_t* pos_out)
 {
     bam_status_t* st = qp->sq.status;
     if (status_bad(st)) return BAM_EIO;
@@ -538,14 +536,33 @@ BAM_DEV int access_data_raw(QueuePair* qp, uint64_t starting_lba, uint32_t n_blo
 #ifdef BAM_PROFILE
     { long long n = clock64(); BAM_PROF_ADD(st, 3, n - pt); pt = n; }
 #endif
-    uint32_t status = cq_poll(qp, cid);
-#ifdef BAM_PROFILE
-    { long long n = clock64(); BAM_PROF_ADD(st, 4, n - pt); pt = n; }
-#endif
+    *cid_out = cid;
+    if (pos_out) *pos_out = pos;
+    return BAM_OK;
+}
+
+/* Wait half: wait for the completion of command `cid`, retire its id. */
+BAM_DEV int access_data_complete(QueuePair* qp, uint32_t cid)
+{
+    bam_status_t* st = qp->sq.status;
+    BAM_PROF_T0();
+    const uint32_t status = cq_poll(qp, cid);
+    BAM_PROF_LAP(st, 4);
     if (status == BAM_CPL_ERR) return BAM_ETIMEDOUT;   /* the id stays claimed: its completion may still arrive */
     put_cid(&qp->sq, cid);
     if (status != 0) { status_fail(st, BAM_EIO, BAM_AT_NVME_STATUS, status); return BAM_EIO; }
     return BAM_OK;
+}
+
+/* One blocking I/O: build the command, submit, wait, retire.  Counterpart of read_data /
+ * write_data / access_data (page_cache.h:2009-2132 in the reference). */
+BAM_DEV int access_data_raw(QueuePair* qp, uint64_t starting_lba, uint32_t n_blocks,
+                            uint64_t bus_addr, uint64_t bus_addr2, uint8_t opcode)
+{
+    uint32_t cid = 0;
+    const int rc = access_data_submit(qp, starting_lba, n_blocks, bus_addr, bus_addr2, opcode, &cid, nullptr);
+    if (rc != BAM_OK) return rc;
+    return access_data_complete(qp, cid);
 }
 
 }  // namespace bam

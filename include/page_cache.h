@@ -28,6 +28,11 @@ using bam::array_d_t;
 using bam::bafs_ptr;
 using bam::bam_ptr;
 using bam::bam_ptr_tlb;
+using bam::read_data;
+using bam::write_data;
+using bam::access_data;
+using bam::access_data_async;
+using bam::poll_async;
 using bam::tlb;
 using bam::range_d_t;
 

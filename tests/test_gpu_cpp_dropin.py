@@ -48,3 +48,13 @@ def test_cpp_vectoradd_writes_through_cursors(cuda, bam, orc, use_tlb):
         assert r["checksum"] == int((a + b).sum(dtype=np.uint64))
     assert r["read_ios"] >= 2 * (n_elems * 8 // 4096)       # A and B came in through the controller
 
+
+def test_cpp_device_api(cuda, bam):
+    """get_raw / release_raw, acquire_page / release_page, memcpy, bafs_ptr::memcpy_to_array_aligned,
+    read_data / write_data and the asynchronous pair, each checked on the host by the program."""
+    from bam_b200 import _build
+    exe = _build.build_cpp_bench(name="device_api_bench")
+    r = run(exe)
+    assert r == {"bad_get_raw": 0, "bad_acquire_page": 0, "bad_memcpy": 0, "bad_raw_io": 0, "bad_async": 0,
+                 "status": 0, "where": 0, "audit": 0}
+
