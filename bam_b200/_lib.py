@@ -29,6 +29,7 @@ SIGNATURES = {
     "bam_ctrl_store_host": (vp, [vp]),
     "bam_ctrl_store_bytes": (u64, [vp]),
     "bam_ctrl_fill_store": (ci, [vp, u64, u64, vp]),
+    "bam_ctrl_fill_store_striped": (ci, [vp, u64, u64, u32, u32, u32, vp]),
     "bam_ctrl_write_store": (ci, [vp, u64, vp, u64]),
     "bam_ctrl_configure": (ci, [vp, u32, u32, u64]),
     "bam_ctrl_set_scope": (ci, [vp, ci]),

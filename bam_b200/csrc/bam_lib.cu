@@ -54,6 +54,20 @@ __global__ void k_fill_store(uint64_t* dst, uint64_t n_elems, uint64_t seed, uin
 }
 
 /* Access streams of the synthetic workloads, materialised as index lists in device memory. */
+/* The share of a striped store that controller `stripe` of `n_stripes` holds: its page j is page
+ * j * n_stripes + stripe of the logical store. */
+__global__ void k_fill_store_striped(uint64_t* dst, uint64_t n_elems, uint64_t seed, uint64_t first_elem, uint32_t page_elems_log2,
+                                     uint32_t stripe, uint32_t n_stripes)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthr = (uint64_t)gridDim.x * blockDim.x;
+    const uint64_t mask = (1ull << page_elems_log2) - 1;
+    for (uint64_t i = tid; i < n_elems; i += nthr) {
+        const uint64_t logical = (((i >> page_elems_log2) * n_stripes + stripe) << page_elems_log2) | (i & mask);
+        dst[i] = bam_store_elem(seed, first_elem + logical);
+    }
+}
+
 __global__ void k_gen_uniform(uint64_t* out, uint64_t n_lanes, uint64_t reqs_per_lane, uint64_t access_seed, uint64_t n_elems)
 {
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -566,6 +580,17 @@ extern "C" int bam_ctrl_fill_store(bam_ctrl_t c, uint64_t seed, uint64_t first_e
     if (!c) return BAM_EINVAL;
     CK(cudaSetDevice(c->device));
     k_fill_store<<<c->num_sms * 8, 256, 0, (cudaStream_t)stream>>>((uint64_t*)c->store_dev, c->store_bytes / 8, seed, first_elem);
+    CK(cudaGetLastError());
+    return BAM_OK;
+}
+
+extern "C" int bam_ctrl_fill_store_striped(bam_ctrl_t c, uint64_t seed, uint64_t first_elem, uint32_t page_bytes, uint32_t stripe,
+                                           uint32_t n_stripes, void* stream)
+{
+    if (!c || n_stripes == 0 || stripe >= n_stripes || page_bytes < 8 || (page_bytes & (page_bytes - 1))) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    k_fill_store_striped<<<c->num_sms * 8, 256, 0, (cudaStream_t)stream>>>((uint64_t*)c->store_dev, c->store_bytes / 8, seed, first_elem,
+                                                                         log2_u32(page_bytes / 8), stripe, n_stripes);
     CK(cudaGetLastError());
     return BAM_OK;
 }

@@ -65,6 +65,11 @@ class Controller:
     def fill_store(self, seed, first_elem=0, stream=None):
         check(self.lib.bam_ctrl_fill_store(self.h, seed, first_elem, _ptr(stream)), "bam_ctrl_fill_store")
 
+    def fill_store_striped(self, seed, stripe, n_stripes, first_elem=0, page_bytes=4096, stream=None):
+        """Fill this controller's share of a striped store: its page j gets logical page j * n_stripes + stripe."""
+        check(self.lib.bam_ctrl_fill_store_striped(self.h, seed, first_elem, page_bytes, stripe, n_stripes, _ptr(stream)),
+              "bam_ctrl_fill_store_striped")
+
     def configure(self, ctrl_blocks=0, batch=0, spin_timeout_ns=0):
         check(self.lib.bam_ctrl_configure(self.h, ctrl_blocks, batch, spin_timeout_ns), "bam_ctrl_configure")
 

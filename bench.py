@@ -56,6 +56,9 @@ def parse():
     ap.add_argument("--scale", type=int, default=0, help="R-MAT scale for bfs (default 24) / cc (default 26)")
     ap.add_argument("--cpu-sample-lanes", type=int, default=1 << 12)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ctrls", type=int, default=1, help="zipf: controllers behind each GPU's cache")
+    ap.add_argument("--dist", default="stripe", choices=["stripe", "replicate"],
+                    help="zipf with --ctrls > 1: how the array's pages are laid out over the controllers")
     ap.add_argument("--sys-scope", action="store_true",
                     help="synchronise doorbells and completions at system scope (default: device scope, enough when the controller runs on the same GPU)")
     return ap.parse_args()
@@ -181,6 +184,7 @@ def workload_config(args, world):
             "page_bytes": PAGE, "queues_per_gpu": args.queues, "queue_depth": args.depth,
             "reads_per_gpu_per_step": args.lanes * args.reqs, "zipf_s": 0.99, "cache_at_step_start": "empty",
             "queue_scope": "system" if args.sys_scope else "device",
+            "controllers_per_gpu": max(1, args.ctrls), "distribution": args.dist if args.ctrls > 1 else "single controller",
             "l2": "inputs (cache + access lists) far larger than L2; no explicit flush"}
 
 
@@ -564,13 +568,24 @@ def main():
     n_acc = lanes * reqs
 
     t0 = time.time()
-    ctrl = bam_b200.Controller(n_local * PAGE, local_rank, queue_depth=args.depth, num_queues=args.queues)
-    ctrl.configure(ctrl_blocks=args.ctrl_blocks, batch=args.batch)
-    if args.sys_scope:
-        ctrl.set_scope(1)
-    ctrl.fill_store(STORE_SEED, first_elem=first_page * EPP)
-    cache = bam_b200.PageCache(ctrl, PAGE, cache_pages)
-    arr = bam_b200.Array(cache, n_local * EPP)
+    k_ctrls = max(1, args.ctrls)
+    stripe = k_ctrls > 1 and args.dist == "stripe"
+    if stripe:
+        n_local -= n_local % k_ctrls                           # whole stripes
+    per_ctrl_pages = n_local // k_ctrls if stripe else n_local
+    ctrls = [bam_b200.Controller(per_ctrl_pages * PAGE, local_rank, queue_depth=args.depth, num_queues=args.queues)
+             for _ in range(k_ctrls)]
+    ctrl = ctrls[0]                                            # the first controller sets the launch geometry
+    for k, c in enumerate(ctrls):
+        c.configure(ctrl_blocks=args.ctrl_blocks, batch=args.batch)
+        if args.sys_scope:
+            c.set_scope(1)
+        if stripe:
+            c.fill_store_striped(STORE_SEED, k, k_ctrls, first_elem=first_page * EPP, page_bytes=PAGE)
+        else:
+            c.fill_store(STORE_SEED, first_elem=first_page * EPP)
+    cache = bam_b200.PageCache(ctrls if k_ctrls > 1 else ctrl, PAGE, cache_pages)
+    arr = bam_b200.Array(cache, n_local * EPP, dist=bam_b200.STRIPE if stripe else bam_b200.REPLICATE)
     cdf = bam_b200.zipf_cdf(n_local)
     d_cdf = torch.from_numpy(cdf.view(np.int64)).to(dev)
     torch.cuda.synchronize()
@@ -797,7 +812,9 @@ def main():
                 line["cpu_baseline"] = {"value": None, "unit": "IOPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
         print(json.dumps(line), flush=True)
 
-    arr.close(); cache.close(); ctrl.close()
+    arr.close(); cache.close()
+    for c in ctrls:
+        c.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

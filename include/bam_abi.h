@@ -53,6 +53,10 @@ uint64_t bam_ctrl_store_bytes(bam_ctrl_t c);
  * GPU through the mapping.  Stands in for loading a dataset onto the SSD
  * (benchmarks/readwrite/main.cu:283-316). */
 int bam_ctrl_fill_store(bam_ctrl_t c, uint64_t seed, uint64_t first_elem, void* stream);
+/* The same for controller `stripe` of `n_stripes` behind a striped range (BAM_DIST_STRIPE): its
+ * page j receives the elements of logical page j * n_stripes + stripe. */
+int bam_ctrl_fill_store_striped(bam_ctrl_t c, uint64_t seed, uint64_t first_elem, uint32_t page_bytes, uint32_t stripe,
+                                uint32_t n_stripes, void* stream);
 /* Copy caller data into the store at a byte offset (host memcpy). */
 int bam_ctrl_write_store(bam_ctrl_t c, uint64_t byte_offset, const void* src, uint64_t bytes);
 /* Controller warps: n_blocks blocks of the fused launches run the command processor;
