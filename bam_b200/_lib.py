@@ -66,9 +66,9 @@ SIGNATURES = {
     "bam_launch_cc_sweep": (ci, [vp, vp, u64, u64, u64, vp, vp, vp, vp, vp, vp, u64, vp]),
     "bam_bfs_run": (ci, [vp, vp, u64, u64, vp, C.POINTER(u32), C.POINTER(u64)]),
     "bam_cc_run": (ci, [vp, vp, u64, vp, C.POINTER(u32), C.POINTER(u64)]),
-    "bam_launch_sssp_sweep": (ci, [vp, vp, vp, u64, u64, vp, vp, vp, vp, u64, vp]),
+    "bam_launch_sssp_sweep": (ci, [vp, vp, vp, u64, u64, u64, vp, vp, vp, vp, u64, vp]),
     "bam_sssp_run": (ci, [vp, vp, vp, u64, u64, vp, C.POINTER(u32), C.POINTER(u64)]),
-    "bam_launch_pr_sweep": (ci, [vp, vp, u64, u64, vp, vp, vp, vp, vp, u64, vp]),
+    "bam_launch_pr_sweep": (ci, [vp, vp, u64, u64, u64, vp, vp, vp, vp, vp, u64, vp]),
     "bam_launch_degrees": (ci, [vp, u64, vp, vp]),
     "bam_pagerank_run": (ci, [vp, vp, u64, u64, u64, u64, u32, vp, C.POINTER(u32), C.POINTER(u64)]),
     "bam_gen_rmat_keys": (ci, [vp, u64, u64, u64, u32, u32, u32, u32, vp]),

@@ -380,6 +380,7 @@ struct SsspSweepWork {
     range_d_t<uint64_t> off, col;
     wrange_t wt;
     uint64_t v_begin, v_end;
+    uint64_t v_base;            /* global id of local vertex 0 (label and new_cost are indexed by global id) */
     uint8_t* label;
     uint32_t* new_cost;
     uint64_t* scanned;
@@ -400,10 +401,11 @@ struct SsspSweepWork {
         };
         for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
             const uint64_t v = c0 + lane;
-            const bool act = v < v_end && label[v] != 0;
+            const bool act = v < v_end && label[v_base + v] != 0;
             if (__ballot_sync(0xffffffffu, act) == 0) continue;
-            if (act) label[v] = 0;
-            if (!chunk_visit_w(off, col, wt, v, v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t w) { relax(c0 + src, nb, w); })) break;
+            if (act) label[v_base + v] = 0;
+            const uint64_t ubase = v_base + c0;
+            if (!chunk_visit_w(off, col, wt, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t w) { relax(ubase + src, nb, w); })) break;
         }
         consume_heavy_items_w(col, wt, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t w) { relax(u, nb, w); });
         warp_sum_to(edges, scanned);
@@ -441,6 +443,7 @@ __global__ void k_sssp_init(uint8_t* label, uint32_t* cost, uint32_t* new_cost, 
 struct PrSweepWork {
     range_d_t<uint64_t> off, col;
     uint64_t v_begin, v_end;
+    uint64_t v_base;            /* global id of local vertex 0 (label, delta and residual are indexed by global id) */
     uint8_t* label;
     const uint64_t* delta;
     unsigned long long* residual;
@@ -460,10 +463,11 @@ struct PrSweepWork {
         auto push = [&](uint64_t u, uint64_t nb) { atomicAdd(&res[nb], (unsigned long long)dl[u]); };
         for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
             const uint64_t v = c0 + lane;
-            const bool act = v < v_end && label[v] != 0;
+            const bool act = v < v_end && label[v_base + v] != 0;
             if (__ballot_sync(0xffffffffu, act) == 0) continue;
-            if (act) label[v] = 0;
-            if (!chunk_visit(off, col, v, v, act, queue, scratch, edges, [&](int src, uint64_t nb) { push(c0 + src, nb); })) break;
+            if (act) label[v_base + v] = 0;
+            const uint64_t ubase = v_base + c0;
+            if (!chunk_visit(off, col, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb) { push(ubase + src, nb); })) break;
         }
         consume_heavy_items(col, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb) { push(u, nb); });
         warp_sum_to(edges, scanned);
@@ -722,7 +726,7 @@ extern "C" int bam_ctrl_write_store_from_device(bam_ctrl_t c, uint64_t byte_offs
 /* ---- SSSP and PageRank drivers ------------------------------------------------------------------ */
 
 extern "C" int bam_launch_sssp_sweep(bam_array_t offsets, bam_array_t cols, bam_array_t weights, uint64_t v_begin, uint64_t v_end,
-                                     uint8_t* label_dev, uint32_t* new_cost_dev, uint64_t* scanned_dev, void* scratch_dev,
+                                     uint64_t v_base, uint8_t* label_dev, uint32_t* new_cost_dev, uint64_t* scanned_dev, void* scratch_dev,
                                      uint64_t scratch_bytes, void* stream)
 {
     int rc = check_graph_args(offsets, cols);
@@ -735,7 +739,7 @@ extern "C" int bam_launch_sssp_sweep(bam_array_t offsets, bam_array_t cols, bam_
     w.off = offsets->h_range; w.col = cols->h_range;
     static_assert(sizeof(wrange_t) == sizeof(range_d_t<uint64_t>), "range descriptors share one layout");
     memcpy(&w.wt, &weights->h_range, sizeof w.wt);
-    w.v_begin = v_begin; w.v_end = v_end; w.label = label_dev; w.new_cost = new_cost_dev; w.scanned = scanned_dev;
+    w.v_begin = v_begin; w.v_end = v_end; w.v_base = v_base; w.label = label_dev; w.new_cost = new_cost_dev; w.scanned = scanned_dev;
     w.scratch = nullptr;
     rc = prepare_scratch(scratch_dev, scratch_bytes, (cudaStream_t)stream, &w.scratch);
     if (rc) return rc;
@@ -767,7 +771,7 @@ extern "C" int bam_sssp_run(bam_array_t offsets, bam_array_t cols, bam_array_t w
     uint32_t iters = 0;
     rc = BAM_OK;
     for (;;) {
-        rc = bam_launch_sssp_sweep(offsets, cols, weights, 0, n_vertices, d_label, d_new, d_scanned, d_scratch,
+        rc = bam_launch_sssp_sweep(offsets, cols, weights, 0, n_vertices, 0, d_label, d_new, d_scanned, d_scratch,
                                    d_scratch ? scratch_bytes : 0, nullptr);
         if (rc) break;
         iters++;
@@ -787,7 +791,8 @@ extern "C" int bam_sssp_run(bam_array_t offsets, bam_array_t cols, bam_array_t w
     return rc;
 }
 
-extern "C" int bam_launch_pr_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint8_t* label_dev,
+extern "C" int bam_launch_pr_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint64_t v_base,
+                                   uint8_t* label_dev,
                                    const uint64_t* delta_dev, uint64_t* residual_dev, uint64_t* scanned_dev, void* scratch_dev,
                                    uint64_t scratch_bytes, void* stream)
 {
@@ -797,7 +802,7 @@ extern "C" int bam_launch_pr_sweep(bam_array_t offsets, bam_array_t cols, uint64
     bam_ctrl* c = offsets->pc->ctrl;
     CK(cudaSetDevice(c->device));
     PrSweepWork w;
-    w.off = offsets->h_range; w.col = cols->h_range; w.v_begin = v_begin; w.v_end = v_end;
+    w.off = offsets->h_range; w.col = cols->h_range; w.v_begin = v_begin; w.v_end = v_end; w.v_base = v_base;
     w.label = label_dev; w.delta = delta_dev; w.residual = reinterpret_cast<unsigned long long*>(residual_dev); w.scanned = scanned_dev;
     w.scratch = nullptr;
     rc = prepare_scratch(scratch_dev, scratch_bytes, (cudaStream_t)stream, &w.scratch);
@@ -846,7 +851,7 @@ extern "C" int bam_pagerank_run(bam_array_t offsets, bam_array_t cols, uint64_t 
     if (rc == BAM_OK) {
         k_pr_init<<<c->num_sms * 4, 256>>>(d_label, d_delta, d_res, value_dev, d_deg, n_vertices, alpha_num, alpha_den);
         while (iters < max_iters) {
-            rc = bam_launch_pr_sweep(offsets, cols, 0, n_vertices, d_label, d_delta, d_res, d_scanned, d_scratch,
+            rc = bam_launch_pr_sweep(offsets, cols, 0, n_vertices, 0, d_label, d_delta, d_res, d_scanned, d_scratch,
                                      d_scratch ? scratch_bytes : 0, nullptr);
             if (rc) break;
             iters++;

@@ -188,6 +188,16 @@ class CsrGraph:
                                                 _ptr(curr_visit), _ptr(next_visit), _ptr(changed), _ptr(scanned),
                                                 _ptr(self.scratch), self.scratch_bytes, _ptr(stream)), "bam_launch_cc_sweep")
 
+    def sssp_sweep(self, v_begin, v_end, label, new_cost, scanned=None, v_base=0, stream=None):
+        check(self.ctrl.lib.bam_launch_sssp_sweep(self.offsets.h, self.cols.h, self.weights.h, v_begin, v_end, v_base,
+                                                  _ptr(label), _ptr(new_cost), _ptr(scanned), _ptr(self.scratch),
+                                                  self.scratch_bytes, _ptr(stream)), "bam_launch_sssp_sweep")
+
+    def pr_sweep(self, v_begin, v_end, label, delta, residual, scanned=None, v_base=0, stream=None):
+        check(self.ctrl.lib.bam_launch_pr_sweep(self.offsets.h, self.cols.h, v_begin, v_end, v_base, _ptr(label), _ptr(delta),
+                                                _ptr(residual), _ptr(scanned), _ptr(self.scratch), self.scratch_bytes,
+                                                _ptr(stream)), "bam_launch_pr_sweep")
+
 
 # ---- multi-GPU traversals: vertex-range sharding, replicated labels, all-gather exchange -------------
 
@@ -258,26 +268,113 @@ def exchange_cc_changes(comp, prev, next_visit, group=None):
     return int(all_idx.numel())
 
 
+def allreduce_min_u32(t, group=None):
+    """Element-wise minimum over ranks of a tensor that holds u32 values in int32 storage
+    (0xFFFFFFFF = unreachable must compare as the largest value): flipping the sign bit maps the
+    unsigned order onto the signed one.  In place; returns t."""
+    import torch.distributed as dist
+    t ^= -2147483648
+    dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+    t ^= -2147483648
+    return t
+
+
+def u32_less(a, b):
+    """a < b for u32 values held in int32 tensors."""
+    return (a ^ -2147483648) < (b ^ -2147483648)
+
+
 class DistCsrGraph:
     """One rank's shard (a contiguous vertex range and its adjacency lists) of a CSR graph; BFS and
     CC run level by level with the frontier / the changed labels exchanged by all-gather."""
 
-    def __init__(self, offsets, cols, rank, world_size, cache_pages, cuda_device=0, group=None, **kw):
+    def __init__(self, offsets, cols, rank, world_size, cache_pages, cuda_device=0, group=None, weights=None, **kw):
         self.n = offsets.numel() - 1
         self.rank, self.world, self.group = rank, world_size, group
         self.v0, self.v1 = shard_vertices_by_edges(offsets, world_size, rank)
         e0, e1 = int(offsets[self.v0].item()), int(offsets[self.v1].item())
         loc_off = (offsets[self.v0:self.v1 + 1] - e0).contiguous()
         loc_cols = cols[e0:e1].contiguous()
-        self.local = CsrGraph(loc_off, loc_cols, cache_pages, cuda_device=cuda_device, **kw)
+        loc_w = weights[e0:e1].contiguous() if weights is not None else None
+        self.local = CsrGraph(loc_off, loc_cols, cache_pages, cuda_device=cuda_device, weights=loc_w, **kw)
         self.device = cuda_device
+        self.degree = (offsets[1:] - offsets[:-1]).contiguous()       # replicated, like the labels
+
+    def sssp(self, source):
+        """Label-correcting SSSP: every rank relaxes the edges of its own vertices into its copy of
+        the tentative costs, the copies are combined with an element-wise minimum (all-reduce), and
+        the update step runs replicated.  Returns (u32 distances in an int32 tensor, sweeps, edges
+        this rank scanned)."""
+        import torch
+        dev = self.torch_device
+        cost = torch.full((self.n,), -1, dtype=torch.int32, device=dev)       # 0xFFFFFFFF
+        cost[source] = 0
+        new = cost.clone()
+        label = torch.zeros(self.n, dtype=torch.uint8, device=dev)
+        label[source] = 1
+        scanned = torch.zeros(1, dtype=torch.int64, device=dev)
+        sweeps = 0
+        while True:
+            self.local.sssp_sweep(0, self.v1 - self.v0, label, new, scanned, v_base=self.v0)
+            self.local.ctrl.check_status()
+            sweeps += 1
+            allreduce_min_u32(new, self.group)
+            better = u32_less(new, cost)
+            if not bool(better.any()):
+                break
+            cost = torch.where(better, new, cost)
+            label = better.to(torch.uint8)
+        return cost, sweeps, int(scanned.item())
+
+    def pagerank(self, alpha=(85, 100), tolerance_q=None, max_iters=100):
+        """Fixed-point delta PageRank: every rank pushes the deltas of its own active vertices into a
+        zeroed buffer, the buffers are summed over ranks (all-reduce) and added to the replicated
+        residuals; the update step runs replicated.  Integer sums: the result does not depend on the
+        number of ranks.  Returns (ranks as int64 fixed-point values, sweeps, edges this rank scanned)."""
+        import torch
+        import torch.distributed as dist
+        dev = self.torch_device
+        num, den = alpha
+        one = 1 << PR_FRAC_BITS
+        if tolerance_q is None:
+            tolerance_q = one // 1000
+        ratio = lambda x: x // den * num + (x % den) * num // den  # noqa: E731
+        deg = self.degree
+        degc = deg.clamp(min=1)
+        zero = torch.zeros(self.n, dtype=torch.int64, device=dev)
+        base = one - ratio(one)
+        value = torch.full((self.n,), base, dtype=torch.int64, device=dev)
+        delta = torch.where(deg > 0, torch.full_like(value, ratio(base)) // degc, zero)
+        residual = zero.clone()
+        label = torch.ones(self.n, dtype=torch.uint8, device=dev)
+        scanned = torch.zeros(1, dtype=torch.int64, device=dev)
+        sweeps = 0
+        while sweeps < max_iters:
+            push = torch.zeros(self.n, dtype=torch.int64, device=dev)
+            self.local.pr_sweep(0, self.v1 - self.v0, label, delta, push, scanned, v_base=self.v0)
+            self.local.ctrl.check_status()
+            sweeps += 1
+            dist.all_reduce(push, op=dist.ReduceOp.SUM, group=self.group)
+            residual += push
+            act = residual > tolerance_q
+            if not bool(act.any()):
+                break
+            value = torch.where(act, value + residual, value)
+            delta = torch.where(act, torch.where(deg > 0, ratio(residual) // degc, zero), delta)
+            residual = torch.where(act, zero, residual)
+            label = act.to(torch.uint8)
+        return value, sweeps, int(scanned.item())
+
+    @property
+    def torch_device(self):
+        return "cpu" if self.device is None else f"cuda:{self.device}"
 
     def close(self):
         self.local.close()
 
     def bfs(self, source):
         import torch
-        dev = f"cuda:{self.device}"
+        dev = self.torch_device
         label = torch.full((self.n,), -1, dtype=torch.int32, device=dev)      # 0xFFFFFFFF
         label[source] = 0
         changed = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -293,7 +390,7 @@ class DistCsrGraph:
 
     def cc(self):
         import torch
-        dev = f"cuda:{self.device}"
+        dev = self.torch_device
         comp = torch.arange(self.n, dtype=torch.int64, device=dev)
         curr = torch.ones(self.n, dtype=torch.uint8, device=dev)
         nxt = torch.zeros(self.n, dtype=torch.uint8, device=dev)

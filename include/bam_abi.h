@@ -225,10 +225,11 @@ int bam_cc_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vertices, uint6
  * third array over the same cache, u32 elements, weights[j] belongs to edge cols[j] (the .val file
  * of the reference, :379-431).  One sweep (kernel_*_pc, :115-146): every vertex flagged in label_dev
  * (u8 per vertex) offers cost + weight to its neighbours with atomicMin on new_cost_dev and clears
- * its flag.  bam_sssp_run is the host loop (:640-720) with the update kernel (:282-292) between
+ * its flag (with a graph sharded by vertex range, local vertex v is global vertex v_base + v; the
+ * label and cost arrays and the column indices stay global).  bam_sssp_run is the host loop (:640-720) with the update kernel (:282-292) between
  * sweeps; cost_dev receives n_vertices u32 distances, 0xFFFFFFFF = unreachable.  Synchronous. */
 int bam_launch_sssp_sweep(bam_array_t offsets, bam_array_t cols, bam_array_t weights, uint64_t v_begin, uint64_t v_end,
-                          uint8_t* label_dev, uint32_t* new_cost_dev, uint64_t* scanned_dev, void* scratch_dev,
+                          uint64_t v_base, uint8_t* label_dev, uint32_t* new_cost_dev, uint64_t* scanned_dev, void* scratch_dev,
                           uint64_t scratch_bytes, void* stream);
 int bam_sssp_run(bam_array_t offsets, bam_array_t cols, bam_array_t weights, uint64_t n_vertices, uint64_t source,
                  uint32_t* cost_dev, uint32_t* n_iters_out, uint64_t* edges_scanned_out);
@@ -241,7 +242,8 @@ int bam_sssp_run(bam_array_t offsets, bam_array_t cols, bam_array_t weights, uin
  * adds delta_dev[v] to residual_dev of each neighbour and clears its flag.  bam_launch_degrees
  * writes the out-degree of every vertex (read once through the cache).  bam_pagerank_run is the
  * whole loop; value_dev receives n_vertices fixed-point ranks.  Synchronous. */
-int bam_launch_pr_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint8_t* label_dev,
+int bam_launch_pr_sweep(bam_array_t offsets, bam_array_t cols, uint64_t v_begin, uint64_t v_end, uint64_t v_base,
+                        uint8_t* label_dev,
                         const uint64_t* delta_dev, uint64_t* residual_dev, uint64_t* scanned_dev, void* scratch_dev,
                         uint64_t scratch_bytes, void* stream);
 int bam_launch_degrees(bam_array_t offsets, uint64_t n_vertices, uint32_t* deg_dev, void* stream);

@@ -1,5 +1,6 @@
 """Multi-GPU tests (need at least two GPUs; skipped otherwise): sharded array scan with the NCCL
-reduction of the checksums, and BFS / CC sharded by vertex range with the all-gather exchange.
+reduction of the checksums, BFS / CC sharded by vertex range with the all-gather exchange, SSSP /
+PageRank with the all-reduce exchange.
 Results must be bit-identical to the single-rank oracle on every rank."""
 import os
 import sys
@@ -48,8 +49,18 @@ def _worker(rank, world, port, q):
     lv, n_levels, scanned = g.bfs(src)
     lab, sweeps, _ = g.cc()
     audit = g.local.cache.audit()
-    q.put((scan, lv.cpu().numpy().view(np.uint32), lab.cpu().numpy().view(np.uint64), n_levels, scanned, audit))
     g.close()
+    # --- sharded SSSP / PageRank (dense exchange: all-reduce min / sum) ---
+    from oracle import pyoracle as orc
+    wts = torch.from_numpy(orc.edge_weights(41, cols.numel()).view(np.int32)).to(dev)
+    gw = bam_b200.DistCsrGraph(off, cols, rank, world, cache_pages=1024, cuda_device=rank, queue_depth=64, num_queues=8,
+                               weights=wts)
+    dist_, s_sweeps, _ = gw.sssp(src)
+    rank_, pr_sweeps, _ = gw.pagerank()
+    audit += gw.local.cache.audit()
+    q.put((scan, lv.cpu().numpy().view(np.uint32), lab.cpu().numpy().view(np.uint64), n_levels, scanned, audit,
+           dist_.cpu().numpy().view(np.uint32), rank_.cpu().numpy().view(np.uint64), pr_sweeps))
+    gw.close()
     dist.barrier()
     dist.destroy_process_group()
 
@@ -78,6 +89,9 @@ def test_two_gpu_scan_bfs_cc():
     off, cols = orc.rmat_csr(3, 12, 16)
     want_lv, want_scanned = orc.bfs(off, cols, orc.max_degree_vertex(off))
     want_lab, _ = orc.cc(off, cols)
-    for _, lv, lab, n_levels, scanned, audit in res:
+    want_dist = orc.sssp(off, cols, orc.edge_weights(41, len(cols)), orc.max_degree_vertex(off))
+    want_rank, want_pr_sweeps, _ = orc.pagerank(off, cols)
+    for _, lv, lab, n_levels, scanned, audit, dist_, rank_, pr_sweeps in res:
         assert (lv == want_lv).all() and (lab == want_lab).all() and audit == 0
+        assert (dist_ == want_dist).all() and (rank_ == want_rank).all() and pr_sweeps == want_pr_sweeps
     assert sum(r[4] for r in res) == want_scanned

@@ -105,6 +105,17 @@ def test_striped_read_matches_oracle(cuda, bam, orc, n_ctrls, slots):
         c.close()
 
 
+def test_striped_fill_matches_scatter(cuda, bam, orc):
+    n_ctrls, n_pages, seed, first = 3, 96, 5, 512 * 7
+    ctrls = make_ctrls(bam, n_ctrls, n_pages // n_ctrls * 4096, queue_depth=16, num_queues=1)
+    for k, c in enumerate(ctrls):
+        c.fill_store_striped(seed, k, n_ctrls, first_elem=first)
+    cuda.cuda.synchronize()
+    assert (gather_striped(ctrls, n_pages) == orc.fill_store(seed, first, n_pages * 512)).all()
+    for c in ctrls:
+        c.close()
+
+
 @pytest.mark.parametrize("dist_name", ["stripe", "replicate"])
 def test_write_back_reaches_the_right_controllers(cuda, bam, orc, dist_name):
     n_ctrls, n_pages, seed, vseed = 3, 510, 31, 99

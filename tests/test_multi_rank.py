@@ -122,3 +122,89 @@ def test_distributed_bfs_cc_exchange_matches_oracle():
     for _, lv, lab, n_levels, sweeps in res:            # every replica ends bit-identical to the oracle
         assert (lv == want_lv).all() and (lab == want_lab).all()
         assert n_levels == int(want_lv[want_lv != 0xFFFFFFFF].max()) + 1 and sweeps >= 1
+
+
+class _HostShard:
+    """Stands in for the rank's CsrGraph: the sweeps of the CUDA kernels restated with numpy on the
+    rank's rows (local vertex v = global vertex v_base + v)."""
+
+    class _Ctrl:
+        def check_status(self):
+            pass
+
+    def __init__(self, off, cols, wts):
+        self.off, self.cols, self.wts, self.ctrl = off.astype(np.int64), cols.astype(np.int64), wts, self._Ctrl()
+
+    def sssp_sweep(self, v_begin, v_end, label, new_cost, scanned, v_base=0):
+        lab, nc = label.numpy(), new_cost.numpy().view(np.uint32)
+        for v in range(v_begin, v_end):
+            u = v_base + v
+            if lab[u]:
+                lab[u] = 0
+                e0, e1 = self.off[u], self.off[u + 1]
+                scanned += int(e1 - e0)
+                cand = nc[u] + self.wts[e0:e1]
+                np.minimum.at(nc, self.cols[e0:e1], cand)
+
+    def pr_sweep(self, v_begin, v_end, label, delta, residual, scanned, v_base=0):
+        lab, dl, res = label.numpy(), delta.numpy(), residual.numpy()
+        for v in range(v_begin, v_end):
+            u = v_base + v
+            if lab[u]:
+                lab[u] = 0
+                e0, e1 = self.off[u], self.off[u + 1]
+                scanned += int(e1 - e0)
+                np.add.at(res, self.cols[e0:e1], dl[u])
+
+
+def _rank_worker(rank, world, port, q):
+    """Distributed SSSP and PageRank: the product's host loops and exchanges (DistCsrGraph.sssp /
+    .pagerank) over gloo, with the per-sweep kernel played by numpy."""
+    sys.path.insert(0, ROOT)
+    from oracle import pyoracle as orc
+    import bam_b200
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    off, cols = orc.rmat_csr(2, 9, 16)
+    wts = orc.edge_weights(55, len(cols))
+    n = len(off) - 1
+    g = bam_b200.DistCsrGraph.__new__(bam_b200.DistCsrGraph)
+    g.n, g.rank, g.world, g.group, g.device = n, rank, world, None, None
+    t_off = torch.from_numpy(off.view(np.int64))
+    g.v0, g.v1 = bam_b200.shard_vertices_by_edges(t_off, world, rank)
+    g.degree = (t_off[1:] - t_off[:-1]).contiguous()
+    g.local = _HostShard(off, cols, wts)
+    src = int(orc.max_degree_vertex(off))
+    cost, sweeps, _ = g.sssp(src)
+    value, pr_sweeps, _ = g.pagerank()
+    # the unsigned minimum must treat 0xFFFFFFFF as the largest value
+    t = torch.tensor([-1, 5, -2147483648] if rank == 0 else [7, -1, 3], dtype=torch.int32)
+    bam_b200.allreduce_min_u32(t)
+    q.put((rank, cost.numpy().view(np.uint32).copy(), sweeps, value.numpy().view(np.uint64).copy(), pr_sweeps, t.tolist()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_distributed_sssp_pagerank_match_oracle():
+    world, port = 2, 29577
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    sys.path.insert(0, ROOT)
+    from oracle import pyoracle as orc
+    off, cols = orc.rmat_csr(2, 9, 16)
+    wts = orc.edge_weights(55, len(cols))
+    want = orc.sssp(off, cols, wts, int(orc.max_degree_vertex(off)))
+    want_rank, want_sweeps, _ = orc.pagerank(off, cols)
+    for _, cost, sweeps, value, pr_sweeps, t in res:
+        assert (cost == want).all() and sweeps >= 2
+        assert (value == want_rank).all() and pr_sweeps == want_sweeps
+        assert t == [7, 5, 3]
+
