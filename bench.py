@@ -767,14 +767,23 @@ def main():
                     "d2h_bytes_per_step": 8},
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "host_link", "achieved": ach_link, "peak": link_gbs, "unit": "GB/s",
-                         "frac": ach_link / link_gbs if link_gbs else None, "traffic": None,
+                         "frac": ach_link / link_gbs if link_gbs else None,
+                         # DRAM bytes per launch, scaled from the ncu capture of a small case of this kernel
+                         # (2^23 reads, 1.40 M page reads: 6.0 GB written, 1.1 GB read): 4 300 B of DRAM writes per
+                         # page read (the page lands once, + queue entries and slot words) and 131 B of DRAM reads
+                         # per access (hit sector, bucket, slot word, index); both grow in proportion
+                         "traffic": (st["read_ios"] / args.steps) * 4300.0 + n_acc * 131.0,
+                         "traffic_note": "scaled from a small-case ncu capture, not measured on this launch; host-link "
+                                         "bytes (the bound) are not DRAM traffic",
                          "kernel": "bam_fused<ArrayReadWork>",
                          "peak_aggregate": link_agg,
                          "note": "miss path: 4096 algorithmic bytes per page read cross the host link once; peak = "
                                  "1 GiB pinned-memory H2D copy measured in this run on all ranks at once (per-GPU share)"},
             "roofline_hit": {"bound": "hbm", "achieved": hit["pages"] * PAGE / (hit["ms"] * 1e-3) / 1e9,
                              "peak": hbm_peak, "unit": "GB/s",
-                             "frac": hit["pages"] * PAGE / (hit["ms"] * 1e-3) / 1e9 / hbm_peak, "traffic": None,
+                             "frac": hit["pages"] * PAGE / (hit["ms"] * 1e-3) / 1e9 / hbm_peak,
+                             # ncu capture of a small warm pass: 272.7 MB read + 5.7 MB written for 268.4 MB of pages
+                             "traffic": hit["pages"] * PAGE * (272.7 + 5.7) / 268.4,
                              "kernel": "bam_fused<PageScanWork>", "hits": hit["hits"], "misses": hit["misses"],
                              "note": "warm cache: whole resident pages read through the cache, 4096 algorithmic "
                                      "bytes per page; peak = MEASURED_PEAKS.json hbm_gbs" if peaks else "of fallback"},
