@@ -59,7 +59,12 @@ typedef struct {
     uint64_t detail;
     uint64_t spin_timeout_ns;   /* limit for any single device-side wait */
     uint64_t launch_timeout_ns; /* limit for one fused launch, enforced by the controller blocks */
-    uint64_t prof[32];          /* cycle/event counters, only updated by builds with -DBAM_PROFILE   */
+    /* cycle/event counters, only updated by builds with -DBAM_PROFILE.  Consumers: 0 commands, 1 SQ-turn
+     * cycles, 2 cid cycles, 3 publish cycles, 4 completion-wait cycles, 5 reaps, 6 reap cycles, 7 entries
+     * reaped; cache: 10 inserts that lost the race for a page, 11 slots claimed by evicting a valid page,
+     * 12 free slots claimed, 13 clock-sweep probes; controller: 16 batches, 17 commands, 18 fetch cycles,
+     * 20 bulk-load cycles, 21 bulk-store cycles, 22 completion cycles. */
+    uint64_t prof[32];
 } bam_status_t;
 
 /* ---- NVMe queue entries -------------------------------------------------------------- */

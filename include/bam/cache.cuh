@@ -140,7 +140,7 @@ BAM_DEV uint32_t find_slot(const page_cache_d_t& pc, uint32_t max_tries = 0xffff
         bam_slot_t* sl = &pc.slots[s];
         const uint32_t st = ld_relaxed_gpu(&sl->state);
         if (st == 0u) {
-            if (atom_cas_acquire(&sl->state, 0u, BAM_BUSY) == 0u) return s;
+            if (atom_cas_acquire(&sl->state, 0u, BAM_BUSY) == 0u) { BAM_PROF_ADD(pc.status, 12, 1); BAM_PROF_ADD(pc.status, 13, tries); return s; }
         } else if ((st & ~BAM_DIRTY) == BAM_VALID) {
             if ((st & BAM_DIRTY) && !dirty_tag) continue;     /* this caller cannot write back: leave it */
             if (atom_cas_acquire(&sl->state, st, st | BAM_BUSY) == st) {
@@ -155,6 +155,7 @@ BAM_DEV uint32_t find_slot(const page_cache_d_t& pc, uint32_t max_tries = 0xffff
                 st_relaxed_gpu(&sl->tag, BAM_TAG_NONE);
                 pt_remove(pc, old, s);
                 atom_and_release(&sl->state, ~(BAM_VALID | BAM_DIRTY));
+                BAM_PROF_ADD(pc.status, 11, 1); BAM_PROF_ADD(pc.status, 13, tries);
                 return s;
             }
         }
@@ -392,6 +393,7 @@ BAM_DEV uint32_t warp_cache_acquire(uint32_t mask, bool want, const page_cache_d
                     else {
                         st_relaxed_gpu(&sl->tag, BAM_TAG_NONE);
                         atom_and_release(&sl->state, ~BAM_BUSY);                /* give the slot back     */
+                        BAM_PROF_ADD(st, 10, 1);
                         if (r != BAM_PT_EXISTS) {
                             if (r == BAM_PT_FULL) status_fail(st, BAM_ENOSPC, BAM_AT_TABLE_FULL, tag);
                             state = S_DONE;
