@@ -300,6 +300,78 @@ struct ArrayWriteWork {
     }
 };
 
+/* ---- access patterns through bam_ptr cursors (benchmarks/pattern/main.cu) ------------------------
+ * The *_pc kernels of the reference's pattern benchmark: every thread owns a bam_ptr and sums the
+ * elements it visits.  SEQUENTIAL (:131-146): element i goes to thread i mod T.  SEQUENTIAL_WARP
+ * (:232-265): warp w reads n_pages_per_warp consecutive pages; warp ids are interleaved by `stride`
+ * as there.  RANDOM (:155-170): thread t reads a[assignment[i]] for i = t, t + T, ...  RANDOM_WARP:
+ * warp w reads the whole pages assignment[w * n_pages_per_warp + k]. */
+#define BAM_PATTERN_SEQUENTIAL 0u
+#define BAM_PATTERN_SEQUENTIAL_WARP 1u
+#define BAM_PATTERN_RANDOM 2u
+#define BAM_PATTERN_RANDOM_WARP 3u
+
+struct PatternWork {
+    array_d_t<uint64_t> arr;
+    uint32_t pattern;
+    uint64_t n_elems, n_warps, n_pages_per_warp, stride;
+    const uint64_t* assignment;
+    uint64_t* sum_out;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint32_t lane = threadIdx.x & 31u;
+        const uint64_t gid = (uint64_t)vb * blockDim.x + threadIdx.x;
+        const uint64_t nthr = (uint64_t)nvb * blockDim.x;
+        const uint64_t epp = arr.d_ranges[0].cache.page_size / sizeof(uint64_t);
+        uint64_t v = 0;
+        {
+            bam_ptr<uint64_t> ptr(&arr);
+            /* one loop for all patterns, so that the cursor's code exists once: (w, k, j) walk warp
+             * items, pages of an item and element rows of a page; the element patterns use w only */
+            const bool by_warp = pattern == BAM_PATTERN_SEQUENTIAL_WARP || pattern == BAM_PATTERN_RANDOM_WARP;
+            const uint64_t nep = by_warp ? (n_warps + stride - 1) / stride : 1;
+            const uint64_t w_end = by_warp ? n_warps : (n_elems + 31) / 32;
+            const uint64_t rows = by_warp ? epp / 32 : 1;
+            const uint64_t pages = by_warp ? n_pages_per_warp : 1;
+            for (uint64_t w = gid >> 5; w < w_end; w += nthr >> 5) {
+                const uint64_t warp_id = pattern == BAM_PATTERN_SEQUENTIAL_WARP ? (w / nep) + (w % nep) * stride : w;
+                if (warp_id >= w_end) continue;
+                for (uint64_t k = 0; k < pages; k++) {
+                    uint64_t first;                                  /* element index of lane 0 in row 0 */
+                    if (pattern == BAM_PATTERN_SEQUENTIAL_WARP) first = (warp_id * pages + k) * epp;
+                    else if (pattern == BAM_PATTERN_RANDOM_WARP) first = assignment[warp_id * pages + k] * epp;
+                    else first = warp_id * 32;
+                    /* row 0 moves the cursor to the page; the other rows of the page are then read four
+                     * at a time (four loads in flight per lane) */
+                    uint64_t i0 = first + lane;
+                    const bool ok0 = by_warp ? i0 < arr.n_elems : i0 < n_elems;
+                    if (ok0 && pattern == BAM_PATTERN_RANDOM) i0 = assignment[i0];
+                    if (ok0) v += ptr.read(i0);
+                    for (uint64_t r = 1; r < rows; r += 4) {
+                        size_t idx[4];
+                        uint64_t x[4];
+                        bool ok[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const uint64_t i = first + (r + u) * 32 + lane;
+                            ok[u] = r + u < rows && i < arr.n_elems;
+                            idx[u] = ok[u] ? i : i0;
+                        }
+                        if (ok0) {
+                            ptr.read_n<4>(idx, x);
+#pragma unroll
+                            for (int u = 0; u < 4; u++) v += ok[u] ? x[u] : 0;
+                        }
+                    }
+                }
+            }
+            ptr.fini();
+        }
+        warp_sum_to(v, sum_out);
+    }
+};
+
 struct FlushWork {
     page_cache_d_t pc;
 
@@ -1020,6 +1092,23 @@ extern "C" int bam_launch_array_write(bam_array_t a, uint64_t n, const uint64_t*
     w.arr.n_elems = a->n_elems; w.arr.start_offset = 0; w.arr.n_ranges = 1;
     w.arr.d_ranges = static_cast<range_d_t<uint64_t>*>(a->d_range);
     w.n = n; w.idx = idx_dev; w.val_seed = val_seed; w.addend = addend;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_pattern_read(bam_array_t a, uint32_t pattern, uint64_t n_elems, uint64_t n_warps, uint64_t n_pages_per_warp,
+                                       uint64_t stride, const uint64_t* assignment_dev, uint64_t* sum_out_dev, void* stream)
+{
+    if (!a || a->elem_bytes != 8 || pattern > BAM_PATTERN_RANDOM_WARP || n_elems > a->n_elems) return BAM_EINVAL;
+    const bool by_warp = pattern == BAM_PATTERN_SEQUENTIAL_WARP || pattern == BAM_PATTERN_RANDOM_WARP;
+    if (by_warp && (n_warps == 0 || n_pages_per_warp == 0 || stride == 0)) return BAM_EINVAL;
+    if ((pattern == BAM_PATTERN_RANDOM || pattern == BAM_PATTERN_RANDOM_WARP) && !assignment_dev) return BAM_EINVAL;
+    bam_ctrl* c = a->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    PatternWork w;
+    w.arr.n_elems = a->n_elems; w.arr.start_offset = 0; w.arr.n_ranges = 1;
+    w.arr.d_ranges = static_cast<range_d_t<uint64_t>*>(a->d_range);
+    w.pattern = pattern; w.n_elems = n_elems; w.n_warps = n_warps; w.n_pages_per_warp = n_pages_per_warp; w.stride = stride;
+    w.assignment = assignment_dev; w.sum_out = sum_out_dev;
     return launch_fused(c, w, (cudaStream_t)stream);
 }
 

@@ -732,6 +732,21 @@ def main():
         cache.stats(reset=True)
         hit_seq = {"ms": float(np.mean(times[1:])), "reads": n_rand, "ok": int(rsum.item()) == int(rwant.item())}
         del d_ridx, seq
+        # the reference's pattern benchmark, warm: every warp reads one resident 4 KiB page through a bam_ptr
+        # cursor (nvm-pattern-bench --impl_type=3, 10 passes); checked against the page scan's sum of the same pages
+        pwant, psum = torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int64, device=dev)
+        arr.page_scan(n_scan, pwant, first_page=0, stream=sptr)
+        times = []
+        for _ in range(11):
+            psum.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); arr.pattern_read(1, n_scan * EPP, psum, n_warps=n_scan, n_pages_per_warp=1, stream=sptr); b.record(stream)
+            stream.synchronize()
+            times.append(a.elapsed_time(b))
+        ctrl.check_status()
+        pst = cache.stats(reset=True)
+        hit_ptr = {"ms": float(np.mean(times[1:])), "elems": n_scan * EPP, "misses": pst["misses"],
+                   "ok": int(psum.item()) == int(pwant.item())}
 
     # ---- reduce over ranks ---------------------------------------------------------------------------
     tot = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
@@ -793,8 +808,16 @@ def main():
                                  "misses": hit_rand["misses"], "verified": hit_rand["ok"],
                                  "note": "2^26 uniform 8-byte reads over resident pages through the cache (all hits): one "
                                          "32-byte sector of page data per read plus bucket, slot word and two atomics"},
+            "hit_pattern_bam_ptr": {"elems_per_s": hit_ptr["elems"] / (hit_ptr["ms"] * 1e-3),
+                                    "gib_per_s": hit_ptr["elems"] * 8 / (hit_ptr["ms"] * 1e-3) / (1 << 30),
+                                    "pages": hit_ptr["elems"] // EPP, "misses": hit_ptr["misses"], "verified": hit_ptr["ok"],
+                                    "vs_published": hit_ptr["elems"] * 8 / (hit_ptr["ms"] * 1e-3) / (1 << 30) / 373.6,
+                                    "note": "warm cache, one warp per resident 4 KiB page through a bam_ptr cursor (the reference's "
+                                            "pattern benchmark, impl 3); published: 373.6 GiB/s average over its warm passes, on its "
+                                            "own GPU (asplosaoe/nvm_pattern_bench.log:26-62)"},
             "hit_sequential_reads": {"reads_per_s": hit_seq["reads"] / (hit_seq["ms"] * 1e-3),
                                      "gb_per_s": hit_seq["reads"] * 8 / (hit_seq["ms"] * 1e-3) / 1e9, "verified": hit_seq["ok"],
+                                     "vs_published": hit_seq["reads"] / (hit_seq["ms"] * 1e-3) / 2.272e10,
                                      "note": "warm cache, each warp reads 32 consecutive 8-byte elements per step through "
                                              "array[] (the reference's cache benchmark, 169 GiB/s in its published log)"},
             "clocks": clocks, "setup_s": setup_s, "numa_rank0": numa,

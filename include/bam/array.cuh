@@ -377,6 +377,25 @@ struct bam_ptr {
         addr[i - start] = v;
     }
 
+    /* N reads at once: when all N elements lie in the page the cursor holds, their loads are issued
+     * back to back (N loads in flight per thread instead of one); otherwise they are read one after
+     * the other as read() would.  The reference has no counterpart: its cursor serialises a load
+     * behind the use of the previous one. */
+    template <int N>
+    BAM_DEV void read_n(const size_t* idx, T* out)
+    {
+        bool here = true;
+#pragma unroll
+        for (int k = 0; k < N; k++) here = here && idx[k] >= start && idx[k] < end;
+        if (here) {
+#pragma unroll
+            for (int k = 0; k < N; k++) out[k] = addr[idx[k] - start];
+        } else {
+#pragma unroll 1
+            for (int k = 0; k < N; k++) out[k] = read(idx[k]);
+        }
+    }
+
     BAM_DEV ref_t operator[](size_t i) { return ref_t{ this, i }; }
 };
 

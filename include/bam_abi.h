@@ -179,6 +179,16 @@ int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t reqs_per_lan
  * (atomic, wrapping).  Pages become DIRTY; a dirty page that is evicted is written back first. */
 int bam_launch_array_write(bam_array_t a, uint64_t n, const uint64_t* idx_dev, uint64_t val_seed, uint64_t addend,
                            void* stream);
+
+/* Pattern benchmark (benchmarks/pattern/main.cu, the *_pc kernels): every thread sums the elements
+ * it visits through a bam_ptr cursor; *sum_out_dev (device u64) is incremented by the wrapping sum.
+ * pattern 0 SEQUENTIAL (:131-146): elements [0, n_elems) dealt round-robin to the threads;
+ * 1 SEQUENTIAL_WARP (:232-265): warp w of n_warps reads n_pages_per_warp consecutive pages, warp ids
+ * interleaved by `stride` (1 = in order); 2 RANDOM (:155-170): a[assignment_dev[i]] for i in
+ * [0, n_elems); 3 RANDOM_WARP: warp w reads the whole pages assignment_dev[w * n_pages_per_warp + k].
+ * A cursor keeps its page pinned: the cache needs more slots than worker threads. */
+int bam_launch_pattern_read(bam_array_t a, uint32_t pattern, uint64_t n_elems, uint64_t n_warps, uint64_t n_pages_per_warp,
+                            uint64_t stride, const uint64_t* assignment_dev, uint64_t* sum_out_dev, void* stream);
 /* Write every dirty page back to the backing store (page_cache_t::flush_cache, page_cache.h:675-682,
  * kernel __flush :584-629).  Call it when no other launch is using the cache. */
 int bam_cache_flush(bam_cache_t pc, void* stream);

@@ -369,3 +369,45 @@ def test_randomised_configurations(cuda, bam, orc):
         assert cache.audit() == 0, what
         assert u64(out) == orc.array_checksum(seed, n_elems, aseed, 0, lanes, reqs), what
         arr.close(); cache.close(); ctrl.close()
+
+
+@pytest.mark.parametrize("slots", [1 << 15, 1 << 17])       # fewer slots than pages (evictions) / everything fits
+def test_pattern_reads_through_cursors(cuda, bam, orc, slots):
+    """The pattern benchmark's bam_ptr kernels: sequential, sequential by warp (in order and
+    interleaved), random elements, random whole pages -- every sum against the oracle."""
+    n_pages, seed = 1 << 16, 31
+    n_elems = n_pages * 512 - 100                              # ragged last page
+    ctrl = bam.Controller(n_pages * 4096, 0, queue_depth=256, num_queues=32)
+    ctrl.configure(spin_timeout_ns=5 * SEC)
+    # a cursor keeps its page pinned: with the smaller cache run fewer threads than there are slots
+    if slots < (1 << 17):
+        ctrl.set_max_grid(48 + 64)
+    ctrl.fill_store(seed)
+    cache = bam.PageCache(ctrl, 4096, slots)
+    arr = bam.Array(cache, n_elems)
+    store = orc.fill_store(seed, 0, n_elems)
+    out = cuda.zeros(1, dtype=cuda.int64, device="cuda")
+
+    def total(a):
+        return int(a.sum(dtype=np.uint64))
+
+    def run(*args, **kw):
+        out.zero_()
+        arr.pattern_read(*args, out, **kw)
+        assert ctrl.status() == (0, "none", 0) and cache.audit() == 0
+        return int(out.item()) & M64
+
+    assert run(0, n_elems) == total(store)                                     # sequential, everything
+    assert run(0, 12345) == total(store[:12345])                               # sequential, a ragged prefix
+    assert run(1, n_elems, n_warps=n_pages, n_pages_per_warp=1) == total(store)
+    assert run(1, n_elems, n_warps=n_pages // 4, n_pages_per_warp=4, stride=8) == total(store)
+    rng = np.random.default_rng(2)
+    idx = rng.integers(0, n_elems, 1 << 18, dtype=np.uint64)
+    d_idx = cuda.from_numpy(idx.view(np.int64)).cuda()
+    assert run(2, len(idx), assignment=d_idx) == total(store[idx.astype(np.int64)])
+    pages = rng.integers(0, n_pages - 1, 3000, dtype=np.uint64)               # whole pages, with repeats
+    d_pages = cuda.from_numpy(pages.view(np.int64)).cuda()
+    want = total(store[: (n_pages - 1) * 512].reshape(-1, 512)[pages.astype(np.int64)])
+    assert run(3, n_elems, n_warps=1000, n_pages_per_warp=3, assignment=d_pages) == want
+    arr.close(); cache.close(); ctrl.close()
+
