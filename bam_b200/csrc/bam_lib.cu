@@ -549,6 +549,7 @@ static int upload_queue_image(bam_ctrl* c)
         e->sq_db = c->d_doorbells + (size_t)(2 * (q + 1)) * BAM_DB_STRIDE_WORDS;
         e->cq_db = c->d_doorbells + (size_t)(2 * (q + 1) + 1) * BAM_DB_STRIDE_WORDS;
         e->qs = qs; e->qs_log2 = log2_u32(qs);
+        e->cq_qs = qs; e->cq_qs_log2 = e->qs_log2;
         e->sqid = e->cqid = (uint16_t)(q + 1);
         e->ctrl_index = c->group_index;
         e->store = c->store_dev; e->store_bytes = c->store_bytes;

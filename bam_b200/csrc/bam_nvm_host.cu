@@ -1,0 +1,531 @@
+/*
+ * bam_nvm_host.cu -- the reference's host-side libnvm interface over the emulated controller
+ * (declarations and the meaning of every name: include/nvm_host_api.h).
+ *
+ * A handle owns: the register window (one page of pinned, mapped host memory holding the doorbell
+ * registers at their NVMe offsets), a table of host-driven queue pairs in the format the command
+ * processor consumes (bam_emu_qp_t, with queue memory and doorbells in mapped host memory), and the
+ * service kernel that runs the command processor for those queue pairs until it is told to stop.
+ * Everything the host shares with that kernel is synchronised at system scope.
+ */
+#include <cuda_runtime.h>
+
+#include <cerrno>
+#include <cstdlib>
+#include <cstring>
+#include <ctime>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "bam/emu_ctrl.cuh"
+#include "bam_internal.h"
+#include "nvm_host_api.h"
+
+#define NVM_HOST_MAX_QUEUES 64                 /* host-driven queue pairs per handle            */
+#define NVM_HOST_SERVICE_BLOCKS 2              /* command-processor blocks of the service kernel */
+
+namespace {
+
+struct host_ctrl;
+struct host_dma {                               /* container of an nvm_dma_t (the public part comes last) */
+    host_ctrl* owner = nullptr;
+    void* registered = nullptr;                 /* memory this mapping pinned with cudaHostRegister */
+    void* allocated = nullptr;                  /* memory this mapping allocated                   */
+    bool device = false;
+};
+
+struct host_ctrl {
+    nvm_ctrl_t pub;                             /* must stay the first member: handles are cast back */
+    bam_ctrl* emu = nullptr;
+    std::mutex lock;
+    uint8_t* regs_host = nullptr;               /* register window                                   */
+    uint8_t* regs_dev = nullptr;
+    uint32_t* stop_host = nullptr;              /* 1 while the service should run (inside the window) */
+    bam_emu_qp_t* d_qps = nullptr;              /* [NVM_HOST_MAX_QUEUES]                              */
+    bam_emu_qp_t h_qps[NVM_HOST_MAX_QUEUES];
+    bool have_cq[NVM_HOST_MAX_QUEUES + 1] = {};
+    bool have_sq[NVM_HOST_MAX_QUEUES + 1] = {};
+    nvm_cpl_t* cq_mem_dev[NVM_HOST_MAX_QUEUES + 1] = {};
+    uint32_t cq_qs[NVM_HOST_MAX_QUEUES + 1] = {};
+    uint32_t n_qps = 0;
+    bam_status_t* d_status = nullptr;
+    bam_fault_t* d_fault = nullptr;
+    uint64_t* d_served = nullptr;
+    cudaStream_t stream = nullptr;
+    bool running = false;
+    uint16_t granted_cqs = NVM_HOST_MAX_QUEUES, granted_sqs = NVM_HOST_MAX_QUEUES;
+};
+
+struct nvm_dma_box { host_dma priv; nvm_dma_t pub; };
+
+host_ctrl* of(const nvm_ctrl_t* c) { return reinterpret_cast<host_ctrl*>(const_cast<nvm_ctrl_t*>(c)); }
+
+__global__ void __launch_bounds__(BAM_THREADS, 1) k_nvm_host_service(const __grid_constant__ bam_emu_d_t emu)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    bam::emu_controller_main(emu, smem);
+}
+
+/* device-visible address of host memory that is already pinned, or 0 */
+uint64_t device_address_of_host(void* p)
+{
+    void* d = nullptr;
+    if (cudaHostGetDevicePointer(&d, p, 0) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    return (uint64_t)(uintptr_t)d;
+}
+
+int stop_service_locked(host_ctrl* h)
+{
+    if (!h->running) return 0;
+    __atomic_store_n(h->stop_host, 0u, __ATOMIC_RELEASE);
+    cudaError_t e = cudaStreamSynchronize(h->stream);
+    h->running = false;
+    /* keep where every queue stands (fetch position, completion tail) for the next start */
+    if (e == cudaSuccess && h->n_qps) e = cudaMemcpy(h->h_qps, h->d_qps, sizeof(bam_emu_qp_t) * h->n_qps, cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? 0 : EIO;
+}
+
+int start_service_locked(host_ctrl* h)
+{
+    if (h->running) return 0;
+    if (h->n_qps == 0) return 0;
+    if (cudaSetDevice(h->emu->device) != cudaSuccess) return EIO;
+    if (cudaMemcpy(h->d_qps, h->h_qps, sizeof(bam_emu_qp_t) * h->n_qps, cudaMemcpyHostToDevice) != cudaSuccess) return EIO;
+    bam_status_t st;
+    memset(&st, 0, sizeof st);
+    st.spin_timeout_ns = h->emu->spin_timeout_ns;
+    st.launch_timeout_ns = h->emu->launch_timeout_ns;
+    if (cudaMemcpy(h->d_status, &st, sizeof st, cudaMemcpyHostToDevice) != cudaSuccess) return EIO;
+    __atomic_store_n(h->stop_host, 1u, __ATOMIC_RELEASE);
+    bam_emu_d_t emu;
+    memset(&emu, 0, sizeof emu);
+    emu.qps = h->d_qps; emu.n_qps = h->n_qps;
+    emu.n_ctrl_blocks = NVM_HOST_SERVICE_BLOCKS;
+    emu.lba_log2 = h->emu->emu.lba_log2; emu.mps_log2 = 12;
+    emu.batch = 32; emu.sys_scope = 1;
+    emu.consumers_remaining = reinterpret_cast<uint32_t*>(h->regs_dev + (reinterpret_cast<uint8_t*>(h->stop_host) - h->regs_host));
+    emu.status = h->d_status;
+    if (cudaFuncSetAttribute(k_nvm_host_service, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BAM_EMU_SMEM_BYTES) != cudaSuccess) return EIO;
+    k_nvm_host_service<<<NVM_HOST_SERVICE_BLOCKS, BAM_THREADS, BAM_EMU_SMEM_BYTES, h->stream>>>(emu);
+    if (cudaGetLastError() != cudaSuccess) return EIO;
+    h->running = true;
+    return 0;
+}
+
+/* Pinning, allocating and freeing memory can make the CUDA runtime wait for the device to go idle,
+ * which a running service kernel never is: such calls are made with the service paused. */
+struct pause_guard {
+    host_ctrl* h;
+    bool was_running;
+    explicit pause_guard(host_ctrl* c) : h(c), was_running(false)
+    {
+        h->lock.lock();
+        cudaSetDevice(h->emu->device);
+        was_running = h->running;
+        if (was_running) stop_service_locked(h);
+    }
+    ~pause_guard()
+    {
+        if (was_running) start_service_locked(h);
+        h->lock.unlock();
+    }
+};
+
+/* rebuild the table the service kernel reads: one entry per complete (CQ, SQ) pair */
+void rebuild_table(host_ctrl* h)
+{
+    h->n_qps = 0;
+    for (uint16_t id = 1; id <= NVM_HOST_MAX_QUEUES; id++)
+        if (h->have_sq[id]) h->n_qps++;
+}
+
+}  // namespace
+
+extern "C" int nvm_ctrl_init(nvm_ctrl_t** ctrl, int)
+{
+    if (ctrl) *ctrl = nullptr;
+    return ENODEV;                     /* no kernel module, no raw SSD: use nvm_emu_ctrl_init */
+}
+
+extern "C" int nvm_emu_ctrl_init(nvm_ctrl_t** ctrl, bam_ctrl_t emu)
+{
+    if (!ctrl) return EINVAL;
+    *ctrl = nullptr;
+    if (!emu) return EINVAL;
+    if (cudaSetDevice(emu->device) != cudaSuccess) { (void)cudaGetLastError(); return ENODEV; }
+    host_ctrl* h = new (std::nothrow) host_ctrl();
+    if (!h) return ENOMEM;
+    h->emu = emu;
+    h->pub.page_size = 4096;
+    h->pub.dstrd = 0;
+    h->pub.timeout = 5000;
+    h->pub.max_qs = 1024;
+    h->pub.mm_size = 0x2000;
+    cudaError_t e = cudaHostAlloc((void**)&h->regs_host, h->pub.mm_size, cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e == cudaSuccess) e = cudaHostGetDevicePointer((void**)&h->regs_dev, h->regs_host, 0);
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_qps, sizeof(bam_emu_qp_t) * NVM_HOST_MAX_QUEUES);
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_status, sizeof(bam_status_t));
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_fault, sizeof(bam_fault_t));
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_served, 8);
+    if (e == cudaSuccess) e = cudaMemset(h->d_fault, 0, sizeof(bam_fault_t));
+    if (e == cudaSuccess) e = cudaMemset(h->d_served, 0, 8);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        cudaFreeHost(h->regs_host); cudaFree(h->d_qps); cudaFree(h->d_status); cudaFree(h->d_fault); cudaFree(h->d_served);
+        delete h;
+        return ENOMEM;
+    }
+    memset(h->regs_host, 0, h->pub.mm_size);
+    h->pub.mm_ptr = h->regs_host;
+    h->stop_host = reinterpret_cast<uint32_t*>(h->regs_host + 0x40);    /* a word of the window the NVMe layout leaves unused */
+    memset(h->h_qps, 0, sizeof h->h_qps);
+    *ctrl = &h->pub;
+    return 0;
+}
+
+extern "C" void nvm_ctrl_free(nvm_ctrl_t* ctrl)
+{
+    if (!ctrl) return;
+    host_ctrl* h = of(ctrl);
+    {
+        std::lock_guard<std::mutex> g(h->lock);
+        cudaSetDevice(h->emu->device);
+        stop_service_locked(h);
+    }
+    cudaStreamDestroy(h->stream);
+    cudaFreeHost(h->regs_host); cudaFree(h->d_qps); cudaFree(h->d_status); cudaFree(h->d_fault); cudaFree(h->d_served);
+    delete h;
+}
+
+extern "C" int nvm_emu_service_start(const nvm_ctrl_t* ctrl)
+{
+    if (!ctrl) return EINVAL;
+    host_ctrl* h = of(ctrl);
+    std::lock_guard<std::mutex> g(h->lock);
+    return start_service_locked(h);
+}
+
+extern "C" int nvm_emu_service_stop(const nvm_ctrl_t* ctrl)
+{
+    if (!ctrl) return EINVAL;
+    host_ctrl* h = of(ctrl);
+    std::lock_guard<std::mutex> g(h->lock);
+    cudaSetDevice(h->emu->device);
+    return stop_service_locked(h);
+}
+
+/* ---- DMA mappings ---------------------------------------------------------------------------------- */
+
+static int make_map(nvm_dma_t** map, void* vaddr, size_t page_size, size_t n_pages, uint64_t base, const uint64_t* ioaddrs,
+                    const host_dma& priv, bool local)
+{
+    nvm_dma_box* box = static_cast<nvm_dma_box*>(calloc(1, sizeof(nvm_dma_box) + n_pages * sizeof(uint64_t)));
+    if (!box) return ENOMEM;
+    new (&box->priv) host_dma(priv);
+    box->pub.vaddr = vaddr;
+    box->pub.local = local;
+    box->pub.contiguous = 1;
+    box->pub.page_size = page_size;
+    box->pub.n_ioaddrs = n_pages;
+    for (size_t i = 0; i < n_pages; i++) box->pub.ioaddrs[i] = ioaddrs ? ioaddrs[i] : base + i * page_size;
+    *map = &box->pub;
+    return 0;
+}
+
+extern "C" int nvm_dma_map(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* vaddr, size_t page_size, size_t n_pages, const uint64_t* ioaddrs)
+{
+    if (!map) return EINVAL;
+    *map = nullptr;
+    if (!ctrl || !ioaddrs || n_pages == 0 || page_size == 0) return EINVAL;
+    host_dma priv;
+    priv.owner = of(ctrl);
+    return make_map(map, vaddr, page_size, n_pages, 0, ioaddrs, priv, true);
+}
+
+extern "C" int nvm_dma_map_host(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* vaddr, size_t size)
+{
+    if (!map) return EINVAL;
+    *map = nullptr;
+    if (!ctrl || !vaddr || size == 0) return EINVAL;
+    const size_t ps = ctrl->page_size;
+    if (((uintptr_t)vaddr & (ps - 1)) != 0) return EINVAL;
+    pause_guard pause(of(ctrl));
+    host_dma priv;
+    priv.owner = of(ctrl);
+    uint64_t dev = device_address_of_host(vaddr);
+    if (dev == 0) {                                   /* not pinned yet: pin and map it */
+        cudaError_t e = cudaHostRegister(vaddr, size, cudaHostRegisterMapped | cudaHostRegisterPortable);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); return EFAULT; }
+        priv.registered = vaddr;
+        dev = device_address_of_host(vaddr);
+        if (dev == 0) { cudaHostUnregister(vaddr); return EFAULT; }
+    }
+    int rc = make_map(map, vaddr, ps, (size + ps - 1) / ps, dev, nullptr, priv, true);
+    if (rc && priv.registered) cudaHostUnregister(vaddr);
+    return rc;
+}
+
+extern "C" int nvm_dma_map_device(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* devptr, size_t size)
+{
+    if (!map) return EINVAL;
+    *map = nullptr;
+    if (!ctrl || !devptr || size == 0) return EINVAL;
+    const size_t ps = ctrl->page_size;
+    if (((uintptr_t)devptr & (ps - 1)) != 0) return EINVAL;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, devptr) != cudaSuccess || attr.type != cudaMemoryTypeDevice) { (void)cudaGetLastError(); return EINVAL; }
+    host_dma priv;
+    priv.owner = of(ctrl);
+    priv.device = true;
+    return make_map(map, devptr, ps, (size + ps - 1) / ps, (uint64_t)(uintptr_t)devptr, nullptr, priv, false);
+}
+
+extern "C" int nvm_dma_create(nvm_dma_t** map, const nvm_ctrl_t* ctrl, size_t size)
+{
+    if (!map) return EINVAL;
+    *map = nullptr;
+    if (!ctrl || size == 0) return EINVAL;
+    const size_t ps = ctrl->page_size;
+    size = (size + ps - 1) / ps * ps;
+    pause_guard pause(of(ctrl));
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, size, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) { (void)cudaGetLastError(); return ENOMEM; }
+    memset(p, 0, size);
+    host_dma priv;
+    priv.owner = of(ctrl);
+    priv.allocated = p;
+    const uint64_t dev = device_address_of_host(p);
+    int rc = dev ? make_map(map, p, ps, size / ps, dev, nullptr, priv, true) : EFAULT;
+    if (rc) cudaFreeHost(p);
+    return rc;
+}
+
+extern "C" void nvm_dma_unmap(nvm_dma_t* map)
+{
+    if (!map) return;
+    nvm_dma_box* box = reinterpret_cast<nvm_dma_box*>(reinterpret_cast<uint8_t*>(map) - offsetof(nvm_dma_box, pub));
+    if (box->priv.owner && (box->priv.registered || box->priv.allocated)) {
+        pause_guard pause(box->priv.owner);
+        if (box->priv.registered) cudaHostUnregister(box->priv.registered);
+        if (box->priv.allocated) cudaFreeHost(box->priv.allocated);
+    }
+    free(box);
+}
+
+/* ---- admin ---------------------------------------------------------------------------------------------- */
+
+struct nvm_admin_reference { host_ctrl* h; };
+
+extern "C" int nvm_aq_create(nvm_aq_ref* ref, const nvm_ctrl_t* ctrl, const nvm_dma_t*)
+{
+    if (!ref) return EINVAL;
+    *ref = nullptr;
+    if (!ctrl) return EINVAL;
+    nvm_admin_reference* r = new (std::nothrow) nvm_admin_reference();
+    if (!r) return ENOMEM;
+    r->h = of(ctrl);
+    *ref = r;
+    return 0;
+}
+
+extern "C" void nvm_aq_destroy(nvm_aq_ref ref) { delete ref; }
+
+extern "C" int nvm_admin_ctrl_info(nvm_aq_ref ref, struct nvm_ctrl_info* info, void*, uint64_t)
+{
+    if (!ref || !info) return EINVAL;
+    memset(info, 0, sizeof *info);
+    info->nvme_version = 0x00010400;                       /* 1.4 */
+    info->page_size = ref->h->pub.page_size;
+    info->db_stride = (size_t)4 << ref->h->pub.dstrd;
+    info->timeout = ref->h->pub.timeout;
+    info->contiguous = 1;
+    info->max_entries = (uint16_t)ref->h->pub.max_qs;
+    memcpy(info->serial_no, "BAMB200EMU0000000001", 20);
+    memset(info->model_no, ' ', sizeof info->model_no);
+    memcpy(info->model_no, "emulated NVMe controller (pinned host memory)", 45 < sizeof info->model_no ? 45 : sizeof info->model_no);
+    memcpy(info->firmware, "1.0     ", 8);
+    info->max_data_size = (size_t)1 << 20;                  /* the largest cache page the library accepts */
+    info->max_data_pages = info->max_data_size / info->page_size;
+    info->cq_entry_size = sizeof(nvm_cpl_t);
+    info->sq_entry_size = sizeof(nvm_cmd_t);
+    info->max_out_cmds = BAM_CID_SPACE;
+    info->max_n_ns = 1;
+    return 0;
+}
+
+extern "C" int nvm_admin_ns_info(nvm_aq_ref ref, struct nvm_ns_info* info, uint32_t ns_id, void*, uint64_t)
+{
+    if (!ref || !info) return EINVAL;
+    if (ns_id != 1) return EINVAL;
+    memset(info, 0, sizeof *info);
+    info->ns_id = 1;
+    info->lba_data_size = ref->h->emu->lba_bytes;
+    info->size = info->capacity = info->utilization = ref->h->emu->store_bytes / ref->h->emu->lba_bytes;
+    return 0;
+}
+
+extern "C" int nvm_admin_set_num_queues(nvm_aq_ref ref, uint16_t n_cqs, uint16_t n_sqs)
+{
+    if (!ref || n_cqs == 0 || n_sqs == 0) return EINVAL;
+    ref->h->granted_cqs = n_cqs < NVM_HOST_MAX_QUEUES ? n_cqs : NVM_HOST_MAX_QUEUES;
+    ref->h->granted_sqs = n_sqs < NVM_HOST_MAX_QUEUES ? n_sqs : NVM_HOST_MAX_QUEUES;
+    return 0;
+}
+
+extern "C" int nvm_admin_get_num_queues(nvm_aq_ref ref, uint16_t* n_cqs, uint16_t* n_sqs)
+{
+    if (!ref || !n_cqs || !n_sqs) return EINVAL;
+    *n_cqs = ref->h->granted_cqs;
+    *n_sqs = ref->h->granted_sqs;
+    return 0;
+}
+
+extern "C" int nvm_admin_request_num_queues(nvm_aq_ref ref, uint16_t* n_cqs, uint16_t* n_sqs)
+{
+    if (!ref || !n_cqs || !n_sqs) return EINVAL;
+    int rc = nvm_admin_set_num_queues(ref, *n_cqs, *n_sqs);
+    if (rc) return rc;
+    return nvm_admin_get_num_queues(ref, n_cqs, n_sqs);
+}
+
+static int queue_memory(const nvm_ctrl_t* ctrl, const nvm_dma_t* dma, size_t offset, size_t qs, size_t es, void** host, uint64_t* dev)
+{
+    if (!dma || !dma->vaddr || !dma->local || offset >= dma->n_ioaddrs) return EINVAL;
+    if (qs * es > (dma->n_ioaddrs - offset) * dma->page_size) return EINVAL;
+    (void)ctrl;
+    *host = static_cast<uint8_t*>(dma->vaddr) + offset * dma->page_size;
+    *dev = dma->ioaddrs[offset];
+    return 0;
+}
+
+extern "C" int nvm_admin_cq_create(nvm_aq_ref ref, nvm_queue_t* cq, uint16_t id, const nvm_dma_t* dma, size_t offset, size_t qs)
+{
+    if (!ref || !cq || id == 0 || id > NVM_HOST_MAX_QUEUES) return EINVAL;
+    host_ctrl* h = ref->h;
+    if (qs == 0) qs = h->pub.page_size / sizeof(nvm_cpl_t);
+    if (qs < 2 || qs > h->pub.max_qs || (qs & (qs - 1))) return EINVAL;      /* the command processor wants a power of two */
+    void* host; uint64_t dev;
+    int rc = queue_memory(&h->pub, dma, offset, qs, sizeof(nvm_cpl_t), &host, &dev);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> g(h->lock);
+    if (h->have_cq[id]) return EEXIST;
+    memset(host, 0, qs * sizeof(nvm_cpl_t));
+    rc = nvm_queue_clear(cq, &h->pub, true, id, (uint32_t)qs, true, host, dev);
+    if (rc) return rc;
+    h->have_cq[id] = true;
+    h->cq_mem_dev[id] = reinterpret_cast<nvm_cpl_t*>((uintptr_t)dev);
+    h->cq_qs[id] = (uint32_t)qs;
+    return 0;
+}
+
+extern "C" int nvm_admin_sq_create(nvm_aq_ref ref, nvm_queue_t* sq, const nvm_queue_t* cq, uint16_t id, const nvm_dma_t* dma, size_t offset,
+                                   size_t qs)
+{
+    if (!ref || !sq || !cq || id == 0 || id > NVM_HOST_MAX_QUEUES) return EINVAL;
+    host_ctrl* h = ref->h;
+    if (qs == 0) qs = h->pub.page_size / sizeof(nvm_cmd_t);
+    if (qs < 2 || qs > h->pub.max_qs || (qs & (qs - 1))) return EINVAL;
+    void* host; uint64_t dev;
+    int rc = queue_memory(&h->pub, dma, offset, qs, sizeof(nvm_cmd_t), &host, &dev);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> g(h->lock);
+    if (!h->have_cq[cq->no] || h->have_sq[id]) return h->have_sq[id] ? EEXIST : EINVAL;
+    cudaSetDevice(h->emu->device);
+    rc = stop_service_locked(h);
+    if (rc) return rc;
+    memset(host, 0, qs * sizeof(nvm_cmd_t));
+    rc = nvm_queue_clear(sq, &h->pub, false, id, (uint32_t)qs, true, host, dev);
+    if (rc) return rc;
+    uint32_t slot = 0;                                     /* position in the table = creation order */
+    for (uint16_t k = 1; k <= NVM_HOST_MAX_QUEUES; k++) if (h->have_sq[k]) slot++;
+    bam_emu_qp_t* e = &h->h_qps[slot];
+    memset(e, 0, sizeof *e);
+    e->sq_mem = reinterpret_cast<nvm_cmd_t*>((uintptr_t)dev);
+    e->cq_mem = h->cq_mem_dev[cq->no];
+    e->sq_db = reinterpret_cast<uint32_t*>(h->regs_dev + NVM_SQ_DBL_OFFSET(id, h->pub.dstrd));
+    e->cq_db = reinterpret_cast<uint32_t*>(h->regs_dev + NVM_CQ_DBL_OFFSET(cq->no, h->pub.dstrd));
+    e->qs = (uint32_t)qs;
+    e->qs_log2 = 0; while ((1u << e->qs_log2) < qs) e->qs_log2++;
+    e->cq_qs = h->cq_qs[cq->no];
+    e->cq_qs_log2 = 0; while ((1u << e->cq_qs_log2) < e->cq_qs) e->cq_qs_log2++;
+    e->sqid = id; e->cqid = cq->no;
+    e->store = h->emu->store_dev; e->store_bytes = h->emu->store_bytes;
+    e->fault = h->d_fault; e->served = h->d_served;
+    *reinterpret_cast<volatile uint32_t*>(h->regs_host + NVM_SQ_DBL_OFFSET(id, h->pub.dstrd)) = 0;
+    *reinterpret_cast<volatile uint32_t*>(h->regs_host + NVM_CQ_DBL_OFFSET(cq->no, h->pub.dstrd)) = 0;
+    h->have_sq[id] = true;
+    rebuild_table(h);
+    return start_service_locked(h);
+}
+
+extern "C" int nvm_admin_cq_delete(nvm_aq_ref ref, nvm_queue_t* cq)
+{
+    if (!ref || !cq || cq->no == 0 || cq->no > NVM_HOST_MAX_QUEUES) return EINVAL;
+    std::lock_guard<std::mutex> g(ref->h->lock);
+    ref->h->have_cq[cq->no] = false;
+    cq->db = nullptr;
+    return 0;
+}
+
+extern "C" int nvm_admin_sq_delete(nvm_aq_ref ref, nvm_queue_t* sq, const nvm_queue_t*)
+{
+    if (!ref || !sq || sq->no == 0 || sq->no > NVM_HOST_MAX_QUEUES) return EINVAL;
+    host_ctrl* h = ref->h;
+    std::lock_guard<std::mutex> g(h->lock);
+    if (!h->have_sq[sq->no]) return EINVAL;
+    cudaSetDevice(h->emu->device);
+    int rc = stop_service_locked(h);
+    /* close the gap in the table */
+    uint32_t slot = 0, n = 0;
+    for (uint16_t k = 1; k <= NVM_HOST_MAX_QUEUES; k++) { if (k == sq->no) slot = n; if (h->have_sq[k]) n++; }
+    for (uint32_t k = slot; k + 1 < n; k++) h->h_qps[k] = h->h_qps[k + 1];
+    h->have_sq[sq->no] = false;
+    sq->db = nullptr;
+    rebuild_table(h);
+    if (rc == 0) rc = start_service_locked(h);
+    return rc;
+}
+
+extern "C" int nvm_raw_rpc(nvm_aq_ref, nvm_cmd_t*, nvm_cpl_t*) { return ENOTSUP; }
+extern "C" int nvm_admin_get_log_page(nvm_aq_ref, uint32_t, void*, uint64_t, uint8_t, uint64_t) { return ENOTSUP; }
+
+/* ---- host-side queue descriptors -------------------------------------------------------------------------- */
+
+extern "C" int nvm_queue_clear(nvm_queue_t* q, const nvm_ctrl_t* ctrl, bool cq, uint16_t no, uint32_t qs, bool local, volatile void* vaddr,
+                               uint64_t ioaddr)
+{
+    if (!q || !ctrl || qs < 2 || qs > 0x10000 || qs > ctrl->max_qs) return EINVAL;
+    memset(q, 0, sizeof *q);
+    q->no = no;
+    q->qs = qs; q->qs_minus_1 = qs - 1;
+    while ((1u << q->qs_log2) < qs) q->qs_log2++;
+    q->es = cq ? sizeof(nvm_cpl_t) : sizeof(nvm_cmd_t);
+    q->phase = 1;
+    q->local = local ? 1 : 0;
+    uint8_t* regs = static_cast<uint8_t*>(const_cast<void*>(ctrl->mm_ptr));
+    q->db = reinterpret_cast<volatile uint32_t*>(regs + (cq ? NVM_CQ_DBL_OFFSET(no, ctrl->dstrd) : NVM_SQ_DBL_OFFSET(no, ctrl->dstrd)));
+    q->vaddr = vaddr;
+    q->ioaddr = ioaddr;
+    return 0;
+}
+
+extern "C" void nvm_queue_reset(nvm_queue_t* q)
+{
+    if (!q) return;
+    q->head = 0; q->tail = 0; q->last = 0; q->phase = 1;
+}
+
+extern "C" nvm_cpl_t* nvm_cq_dequeue_block(nvm_queue_t* cq, uint64_t timeout_ms)
+{
+    struct timespec t0, t;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (;;) {
+        nvm_cpl_t* cpl = nvm_cq_dequeue(cq);
+        if (cpl) return cpl;
+        clock_gettime(CLOCK_MONOTONIC, &t);
+        const uint64_t ms = (uint64_t)(t.tv_sec - t0.tv_sec) * 1000ull + (uint64_t)((t.tv_nsec - t0.tv_nsec) / 1000000);
+        if (ms >= timeout_ms) return nullptr;
+    }
+}

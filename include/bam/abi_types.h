@@ -176,7 +176,8 @@ typedef struct BAM_ALIGNAS(64) {
     uint64_t store_bytes;
     struct bam_fault_s* fault;
     uint64_t* served;       /* commands completed, for statistics                            */
-    uint64_t pad[4];
+    uint32_t cq_qs, cq_qs_log2;   /* depth of the completion queue (may differ from the SQ's)  */
+    uint64_t pad[3];
 } bam_emu_qp_t;
 
 #define BAM_FAULT_NONE 0

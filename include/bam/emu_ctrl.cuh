@@ -99,8 +99,8 @@ BAM_DEV void emu_post_completion(const bam_emu_d_t& c, const emu_cmd_t& m, uint3
         }
     }
     if (!drop) {
-        const uint32_t mask = s->qs - 1u;
-        const uint32_t phase = (~(m.cq_virt >> s->qs_log2)) & 1u;
+        const uint32_t mask = s->cq_qs - 1u;
+        const uint32_t phase = (~(m.cq_virt >> s->cq_qs_log2)) & 1u;
         nvm_cpl_t* e = &s->cq_mem[m.cq_virt & mask];
         *reinterpret_cast<volatile uint64_t*>(&e->dword[0]) = 0ull;
         const uint64_t dw2 = m.sqhd | ((uint32_t)s->sqid << 16);
@@ -126,8 +126,9 @@ BAM_DEV uint32_t emu_reserve(const bam_emu_d_t& c, uint32_t q, uint32_t want, ui
     uint32_t cq_head = ld_relaxed_gpu(&s->cq_head);
     cqbase = ld_relaxed_gpu(&s->cq_tail);
     const uint32_t avail = (tail - fetch) & mask;
-    cq_head += (hdb - cq_head) & mask;
-    const uint32_t space = mask - (cqbase - cq_head);          /* keep one completion slot open */
+    const uint32_t cmask = s->cq_qs - 1u;
+    cq_head += (hdb - cq_head) & cmask;
+    const uint32_t space = cmask - (cqbase - cq_head);         /* keep one completion slot open */
     uint32_t n = avail < space ? avail : space;
     if (n > want) n = want;
     if (n == 0) { st_release_gpu(&s->lock, 0u); return 0; }
@@ -309,7 +310,7 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
         }
         uint32_t stop = 0;
         if (lane == 0) {
-            stop = (ld_acquire_gpu(c.consumers_remaining) == 0u) || status_bad(c.status);
+            stop = ((c.sys_scope ? ld_acquire_sys(c.consumers_remaining) : ld_acquire_gpu(c.consumers_remaining)) == 0u) || status_bad(c.status);
             if (!stop && ((++idle_rounds) & 63u) == 0u && global_timer_ns() - t_start > c.status->launch_timeout_ns) {
                 status_fail(c.status, BAM_ETIMEDOUT, BAM_AT_LAUNCH, 0);
                 stop = 1;

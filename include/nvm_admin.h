@@ -1,10 +1,6 @@
-/* nvm_admin.h -- present so that programs written against the reference's include list compile.  The
- * reference's nvm_admin.h declares part of its host-side control plane (controller bring-up over a
- * kernel module, admin queue, DMA windows, host-side queue polling); the emulated controller of
- * this library is created and driven through bam_abi.h (bam_ctrl_create, bam_ctrl_reset_queues,
- * ...) and needs none of it. */
+/* nvm_admin.h -- nvm_admin_ctrl_info / ns_info / *_num_queues / cq_create / sq_create / *_delete (include/nvm_admin.h:18-117 there).
+ * Served by the emulated controller: declarations and semantics in nvm_host_api.h. */
 #ifndef BAM_COMPAT_NVM_ADMIN_H
 #define BAM_COMPAT_NVM_ADMIN_H
-#include "bam_abi.h"
-#include "nvm_types.h"
+#include "nvm_host_api.h"
 #endif

@@ -1,10 +1,6 @@
-/* nvm_ctrl.h -- present so that programs written against the reference's include list compile.  The
- * reference's nvm_ctrl.h declares part of its host-side control plane (controller bring-up over a
- * kernel module, admin queue, DMA windows, host-side queue polling); the emulated controller of
- * this library is created and driven through bam_abi.h (bam_ctrl_create, bam_ctrl_reset_queues,
- * ...) and needs none of it. */
+/* nvm_ctrl.h -- nvm_ctrl_t, nvm_ctrl_init, nvm_emu_ctrl_init, nvm_ctrl_free (include/nvm_ctrl.h:36-76 there).
+ * Served by the emulated controller: declarations and semantics in nvm_host_api.h. */
 #ifndef BAM_COMPAT_NVM_CTRL_H
 #define BAM_COMPAT_NVM_CTRL_H
-#include "bam_abi.h"
-#include "nvm_types.h"
+#include "nvm_host_api.h"
 #endif

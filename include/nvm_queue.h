@@ -1,10 +1,6 @@
-/* nvm_queue.h -- present so that programs written against the reference's include list compile.  The
- * reference's nvm_queue.h declares part of its host-side control plane (controller bring-up over a
- * kernel module, admin queue, DMA windows, host-side queue polling); the emulated controller of
- * this library is created and driven through bam_abi.h (bam_ctrl_create, bam_ctrl_reset_queues,
- * ...) and needs none of it. */
+/* nvm_queue.h -- nvm_queue_clear / nvm_queue_reset and the classic host-side queue functions nvm_sq_enqueue, nvm_sq_submit, nvm_cq_poll, nvm_cq_dequeue(_block), nvm_sq_update, nvm_cq_update (include/nvm_queue.h:30-286 there).
+ * Served by the emulated controller: declarations and semantics in nvm_host_api.h. */
 #ifndef BAM_COMPAT_NVM_QUEUE_H
 #define BAM_COMPAT_NVM_QUEUE_H
-#include "bam_abi.h"
-#include "nvm_types.h"
+#include "nvm_host_api.h"
 #endif

@@ -1,0 +1,143 @@
+/*
+ * host_io_bench.cu -- a host program in the style of the reference's libnvm examples
+ * (deprecated/examples/integrity/transfer.c:42-138): bring up a controller handle, query it through
+ * the admin functions, create one I/O queue pair in host memory, and move data with NVMe WRITE and
+ * READ commands that the HOST submits with the classic queue functions -- all served by the
+ * emulated controller.  Checks every byte and prints one JSON line.
+ */
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include <nvm_types.h>
+#include <nvm_ctrl.h>
+#include <nvm_dma.h>
+#include <nvm_aq.h>
+#include <nvm_admin.h>
+#include <nvm_queue.h>
+#include <nvm_cmd.h>
+#include <nvm_error.h>
+#include <nvm_util.h>
+#include "bam_synth.h"
+
+#define CHECK(x) do { int rc_ = (x); if (rc_) { fprintf(stderr, "%s failed: %s\n", #x, nvm_strerror(rc_)); return 1; } } while (0)
+
+int main()
+{
+    const uint64_t store_bytes = 64ull << 20, seed = 23;
+    bam_ctrl_t emu = nullptr;
+    CHECK(bam_ctrl_create(&emu, 0, store_bytes, 512, 1, 64));
+    bam_ctrl_set_launch_timeout(emu, 60ull * 1000 * 1000 * 1000);       /* the service kernel leaves after a minute at most */
+    uint64_t* media = (uint64_t*)bam_ctrl_store_host(emu);
+    for (uint64_t i = 0; i < store_bytes / 8; i++) media[i] = bam_store_elem(seed, i);
+
+    /* device memory is allocated before the queues exist: while the service kernel runs, calls that may wait
+     * for an idle device are best avoided */
+    const size_t n_pages = 96;
+    void* d_mem = nullptr;
+    if (cudaMalloc(&d_mem, n_pages * 4096) != cudaSuccess) return 1;
+
+    nvm_ctrl_t* ctrl = nullptr;
+    CHECK(nvm_emu_ctrl_init(&ctrl, emu));
+    nvm_aq_ref aq = nullptr;
+    nvm_dma_t* aq_mem = nullptr;
+    CHECK(nvm_dma_create(&aq_mem, ctrl, 2 * ctrl->page_size));
+    CHECK(nvm_aq_create(&aq, ctrl, aq_mem));
+    struct nvm_ctrl_info ci;
+    struct nvm_ns_info ni;
+    CHECK(nvm_admin_ctrl_info(aq, &ci, aq_mem->vaddr, aq_mem->ioaddrs[0]));
+    CHECK(nvm_admin_ns_info(aq, &ni, 1, aq_mem->vaddr, aq_mem->ioaddrs[0]));
+    uint16_t n_cqs = 4, n_sqs = 4;
+    CHECK(nvm_admin_request_num_queues(aq, &n_cqs, &n_sqs));
+
+    /* queue memory: page 0 = CQ (256 entries fit one page), page 1 = SQ (64 entries) */
+    nvm_dma_t* q_mem = nullptr;
+    CHECK(nvm_dma_create(&q_mem, ctrl, 2 * ctrl->page_size));
+    nvm_queue_t cq, sq;
+    CHECK(nvm_admin_cq_create(aq, &cq, 1, q_mem, 0, 0));
+    CHECK(nvm_admin_sq_create(aq, &sq, &cq, 1, q_mem, 1, 0));
+
+    /* data buffers: one the library allocates, one of the program's own (malloc'd, pinned by the mapping), one in GPU memory */
+    const size_t page = ctrl->page_size, blocks_per_page = page / ni.lba_data_size;
+    nvm_dma_t *buf = nullptr, *own = nullptr, *devbuf = nullptr;
+    CHECK(nvm_dma_create(&buf, ctrl, n_pages * page));
+    void* own_mem = nullptr;
+    if (posix_memalign(&own_mem, 4096, n_pages * page)) return 1;
+    CHECK(nvm_dma_map_host(&own, ctrl, own_mem, n_pages * page));
+    CHECK(nvm_dma_map_device(&devbuf, ctrl, d_mem, n_pages * page));
+
+    /* submit `n` one-page commands, at most qs - 1 in flight, and reap them; returns the number of failed completions */
+    auto transfer = [&](uint8_t opcode, const nvm_dma_t* dma, uint64_t first_media_page, size_t n) -> int {
+        size_t sent = 0, done = 0;
+        int bad = 0;
+        while (done < n) {
+            while (sent < n) {
+                nvm_cmd_t* cmd = nvm_sq_enqueue(&sq);
+                if (!cmd) break;                                         /* queue full: reap first */
+                memset(cmd, 0, sizeof *cmd);
+                nvm_cmd_header(cmd, (uint16_t)sent, opcode, ni.ns_id);
+                nvm_cmd_data_ptr(cmd, dma->ioaddrs[sent], 0);
+                nvm_cmd_rw_blks(cmd, (first_media_page + sent) * blocks_per_page, (uint16_t)blocks_per_page);
+                sent++;
+            }
+            nvm_sq_submit(&sq);
+            nvm_cpl_t* cpl = nvm_cq_dequeue_block(&cq, ctrl->timeout);
+            if (!cpl) return -1;                                         /* the controller did not answer */
+            if ((cpl->dword[3] >> 17) != 0) bad++;
+            nvm_sq_update(&sq);
+            nvm_cq_update(&cq);
+            done++;
+        }
+        return bad;
+    };
+
+    int bad_read = 0, bad_write = 0, bad_own = 0, bad_dev = 0, bad_status = 0;
+    /* READ pages [100, 196) of the media into the library's buffer */
+    int rc = transfer(NVM_IO_READ, buf, 100, n_pages);
+    if (rc < 0) { fprintf(stderr, "read timed out\n"); return 1; }
+    bad_status += rc;
+    bad_read = memcmp(buf->vaddr, media + 100 * page / 8, n_pages * page) != 0;
+    /* WRITE a pattern from the program's own pinned memory to pages [5000, 5096), READ it back into GPU memory */
+    uint64_t* pat = (uint64_t*)own_mem;
+    for (size_t i = 0; i < n_pages * page / 8; i++) pat[i] = bam_splitmix64(i ^ 0xabcdef);
+    rc = transfer(NVM_IO_WRITE, own, 5000, n_pages);
+    if (rc < 0) { fprintf(stderr, "write timed out\n"); return 1; }
+    bad_status += rc;
+    bad_write = memcmp(media + 5000 * page / 8, pat, n_pages * page) != 0;
+    rc = transfer(NVM_IO_READ, devbuf, 5000, n_pages);
+    if (rc < 0) { fprintf(stderr, "read to device timed out\n"); return 1; }
+    bad_status += rc;
+    std::vector<uint64_t> back(n_pages * page / 8);
+    cudaMemcpy(back.data(), d_mem, n_pages * page, cudaMemcpyDeviceToHost);
+    bad_dev = memcmp(back.data(), pat, n_pages * page) != 0;
+    /* and the media pages next to the written range are untouched */
+    bad_own = media[4999 * page / 8 + 7] != bam_store_elem(seed, 4999 * page / 8 + 7) || media[5096 * page / 8] != bam_store_elem(seed, 5096 * page / 8);
+    /* a request beyond the namespace completes with an error status instead of touching memory */
+    nvm_cmd_t* cmd = nvm_sq_enqueue(&sq);
+    memset(cmd, 0, sizeof *cmd);
+    nvm_cmd_header(cmd, 7, NVM_IO_READ, ni.ns_id);
+    nvm_cmd_data_ptr(cmd, buf->ioaddrs[0], 0);
+    nvm_cmd_rw_blks(cmd, ni.size, (uint16_t)blocks_per_page);
+    nvm_sq_submit(&sq);
+    nvm_cpl_t* cpl = nvm_cq_dequeue_block(&cq, ctrl->timeout);
+    const unsigned oob_status = cpl ? (cpl->dword[3] >> 17) : 0xffffu;
+    const unsigned oob_cid = cpl ? (cpl->dword[3] & 0xffffu) : 0xffffu;
+    if (cpl) { nvm_sq_update(&sq); nvm_cq_update(&cq); }
+
+    printf("{\"page_size\": %zu, \"max_entries\": %u, \"sq_entry\": %zu, \"cq_entry\": %zu, \"ns_blocks\": %zu, \"lba\": %zu, \"queues\": [%u, %u], "
+           "\"sq_depth\": %u, \"cq_depth\": %u, \"bad_read\": %d, \"bad_write\": %d, \"bad_neighbours\": %d, \"bad_device_read\": %d, "
+           "\"bad_status\": %d, \"oob_status\": %u, \"oob_cid\": %u}\n",
+           ci.page_size, (unsigned)ci.max_entries, ci.sq_entry_size, ci.cq_entry_size, ni.size, ni.lba_data_size, n_cqs, n_sqs, sq.qs, cq.qs,
+           bad_read, bad_write, bad_own, bad_dev, bad_status, oob_status, oob_cid);
+
+    CHECK(nvm_admin_sq_delete(aq, &sq, &cq));
+    CHECK(nvm_admin_cq_delete(aq, &cq));
+    nvm_dma_unmap(devbuf); nvm_dma_unmap(own); nvm_dma_unmap(buf); nvm_dma_unmap(q_mem); nvm_dma_unmap(aq_mem);
+    cudaFree(d_mem);
+    free(own_mem);
+    nvm_aq_destroy(aq);
+    nvm_ctrl_free(ctrl);
+    bam_ctrl_destroy(emu);
+    return 0;
+}

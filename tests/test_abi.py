@@ -26,6 +26,23 @@ def test_header_symbols_are_exported(bam):
         assert hasattr(lib, n), f"{n} declared in include/bam_abi.h but not exported"
 
 
+def test_host_libnvm_symbols_are_exported(bam):
+    """Every function include/nvm_host_api.h declares (and does not define inline) is exported."""
+    from bam_b200 import _lib
+    lib = C.CDLL(_lib.LIB_PATH)
+    src = open(os.path.join(ROOT, "include", "nvm_host_api.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    src = src[: src.index("static inline")]                 # the classic queue functions are header-only
+    names = sorted(set(re.findall(r"\b(nvm_[a-z0-9_]+)\s*\(", src)))
+    names += ["nvm_queue_clear", "nvm_queue_reset", "nvm_cq_dequeue_block"]
+    assert len(names) >= 25
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/nvm_host_api.h but not exported"
+    ctrl = C.c_void_p()
+    assert lib.nvm_ctrl_init(C.byref(ctrl), 3) == 19        # ENODEV: there is no kernel module behind a descriptor
+    assert lib.nvm_emu_ctrl_init(C.byref(ctrl), None) == 22
+
+
 def test_ctypes_table_covers_header(bam):
     from bam_b200 import _lib
     assert sorted(_lib.SIGNATURES) == declared_functions()

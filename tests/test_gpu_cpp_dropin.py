@@ -58,3 +58,17 @@ def test_cpp_device_api(cuda, bam):
     assert r == {"bad_get_raw": 0, "bad_acquire_page": 0, "bad_memcpy": 0, "bad_raw_io": 0, "bad_async": 0,
                  "status": 0, "where": 0, "audit": 0}
 
+
+def test_cpp_host_libnvm_io(cuda, bam):
+    """tests/cpp/host_io_bench.cu: a host program written against the reference's libnvm names
+    (nvm_ctrl / nvm_dma / nvm_aq / nvm_admin / nvm_queue) submits NVMe READ and WRITE commands from the
+    host through a queue pair in host memory; the emulated controller serves them."""
+    from bam_b200 import _build
+    exe = _build.build_cpp_bench(name="host_io_bench")
+    r = run(exe)
+    assert (r["page_size"], r["max_entries"], r["sq_entry"], r["cq_entry"], r["lba"]) == (4096, 1024, 64, 16, 512)
+    assert r["ns_blocks"] == (64 << 20) // 512 and r["queues"] == [4, 4]
+    assert (r["sq_depth"], r["cq_depth"]) == (64, 256)        # the page-sized defaults of sq_create / cq_create
+    assert r["bad_read"] == r["bad_write"] == r["bad_neighbours"] == r["bad_device_read"] == r["bad_status"] == 0
+    assert r["oob_status"] == 0x80 and r["oob_cid"] == 7      # LBA out of range, generic status code type
+
