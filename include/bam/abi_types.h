@@ -114,6 +114,36 @@ typedef struct {
     nvm_queue_t cq;
 } QueuePair;
 
+/* ---- host-side controller handle and identify data (include/nvm_types.h:19-28, :198-232 in the
+ * reference); the functions that fill them are declared in nvm_host_api.h -------------------------- */
+typedef struct {
+    size_t page_size;          /* memory page size used by the controller (MPS)        */
+    uint8_t dstrd;             /* doorbell stride, encoded: registers are 4 << dstrd bytes apart */
+    uint64_t timeout;          /* controller time-out in milliseconds                  */
+    uint32_t max_qs;           /* maximum queue entries supported                      */
+    size_t mm_size;            /* size of the register window                          */
+    volatile void* mm_ptr;     /* register window: pinned host memory, doorbells at 0x1000 + ... */
+} nvm_ctrl_t;
+
+struct nvm_admin_reference;
+typedef struct nvm_admin_reference* nvm_aq_ref;
+
+struct nvm_ctrl_info {
+    uint32_t nvme_version;
+    size_t page_size, db_stride;
+    uint64_t timeout;
+    int contiguous;
+    uint16_t max_entries;
+    uint8_t pci_vendor[4];
+    char serial_no[20], model_no[40], firmware[8];
+    size_t max_data_size, max_data_pages, cq_entry_size, sq_entry_size, max_out_cmds, max_n_ns;
+};
+struct nvm_ns_info {
+    uint32_t ns_id;
+    size_t size, capacity, utilization;      /* in logical blocks */
+    size_t lba_data_size, metadata_size;
+};
+
 /* One controller.  The leading members are what kernels use to pick a queue and count I/O (the
  * copy in device memory, Controller::d_ctrl_ptr, holds only those); the trailing members belong
  * to the host object.  In C++ the struct also carries the reference's constructor
@@ -134,6 +164,11 @@ struct Controller {
     void* d_ctrl_ptr;
     uint32_t deviceId;
     uint32_t reserved_;
+    nvm_ctrl_t* ctrl;                 /* libnvm handle over the same emulated controller */
+    nvm_aq_ref aq_ref;
+    struct nvm_ctrl_info info;
+    struct nvm_ns_info ns;
+    uint16_t n_sqs, n_cqs;
 
     Controller() = default;
     inline Controller(const char* path, uint32_t nvmNamespace, uint32_t cudaDevice, uint64_t queueDepth,
@@ -154,6 +189,11 @@ typedef struct {
     void* d_ctrl_ptr;
     uint32_t deviceId;
     uint32_t reserved_;
+    nvm_ctrl_t* ctrl;
+    nvm_aq_ref aq_ref;
+    struct nvm_ctrl_info info;
+    struct nvm_ns_info ns;
+    uint16_t n_sqs, n_cqs;
 } Controller;
 #endif
 

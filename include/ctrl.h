@@ -20,6 +20,7 @@
 
 #include "bam_abi.h"
 #include "bam/abi_types.h"
+#include "nvm_host_api.h"
 
 #define MAX_QUEUES 1024
 
@@ -54,10 +55,18 @@ inline Controller::Controller(const char* path, uint32_t nvmNamespace, uint32_t 
     blk_size = 512;
     blk_size_log = 9;
     deviceId = cudaDevice;
+    /* the libnvm view of the same controller, as the reference's constructor leaves it (ctrl.h:148-199 there) */
+    if (nvm_emu_ctrl_init(&ctrl, handle) == 0 && nvm_aq_create(&aq_ref, ctrl, nullptr) == 0) {
+        nvm_admin_ctrl_info(aq_ref, &info, nullptr, 0);
+        nvm_admin_ns_info(aq_ref, &ns, nvmNamespace ? nvmNamespace : 1, nullptr, 0);
+        n_sqs = n_cqs = (uint16_t)numQueues;
+    }
 }
 
 inline void Controller::close()
 {
+    if (aq_ref) { nvm_aq_destroy(aq_ref); aq_ref = nullptr; }
+    if (ctrl) { nvm_ctrl_free(ctrl); ctrl = nullptr; }
     if (h) { bam_ctrl_destroy(h); h = nullptr; }
 }
 

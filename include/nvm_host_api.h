@@ -34,16 +34,7 @@
 extern "C" {
 #endif
 
-/* ---- controller handle (nvm_types.h:19-28) ---------------------------------------------------- */
-typedef struct {
-    size_t page_size;          /* memory page size used by the controller (MPS)        */
-    uint8_t dstrd;             /* doorbell stride, encoded: registers are 4 << dstrd bytes apart */
-    uint64_t timeout;          /* controller time-out in milliseconds                  */
-    uint32_t max_qs;           /* maximum queue entries supported                      */
-    size_t mm_size;            /* size of the register window                          */
-    volatile void* mm_ptr;     /* register window: pinned host memory, doorbells at 0x1000 + ... */
-} nvm_ctrl_t;
-
+/* ---- controller handle: nvm_ctrl_t is defined in bam/abi_types.h (nvm_types.h:19-28 there) ------ */
 /* The reference opens /dev/libnvm* (a kernel module bound to a raw SSD); not available: ENODEV. */
 int nvm_ctrl_init(nvm_ctrl_t** ctrl, int fd);
 /* A handle over an emulated controller made by bam_ctrl_create (which stays owned by the caller). */
@@ -70,24 +61,7 @@ int nvm_dma_create(nvm_dma_t** map, const nvm_ctrl_t* ctrl, size_t size);       
 void nvm_dma_unmap(nvm_dma_t* map);
 
 /* ---- admin queue reference and identify data (nvm_aq.h, nvm_admin.h, nvm_types.h:198-232) ------- */
-struct nvm_admin_reference;
-typedef struct nvm_admin_reference* nvm_aq_ref;
-
-struct nvm_ctrl_info {
-    uint32_t nvme_version;
-    size_t page_size, db_stride;
-    uint64_t timeout;
-    int contiguous;
-    uint16_t max_entries;
-    uint8_t pci_vendor[4];
-    char serial_no[20], model_no[40], firmware[8];
-    size_t max_data_size, max_data_pages, cq_entry_size, sq_entry_size, max_out_cmds, max_n_ns;
-};
-struct nvm_ns_info {
-    uint32_t ns_id;
-    size_t size, capacity, utilization;      /* in logical blocks */
-    size_t lba_data_size, metadata_size;
-};
+/* struct nvm_ctrl_info and struct nvm_ns_info are defined in bam/abi_types.h */
 
 /* dma: memory for the admin queues (unused by the emulator, accepted for source compatibility) */
 int nvm_aq_create(nvm_aq_ref* ref, const nvm_ctrl_t* ctrl, const nvm_dma_t* dma);

@@ -47,6 +47,14 @@ int main()
 {
     BufferPtr b = createBuffer(64);
     (void)b;
+    /* the members benchmarks read from a Controller (ctrl.h:39-59 of the reference) */
+    Controller* c = nullptr;
+    static_assert(sizeof(c->ns.lba_data_size) == sizeof(size_t) && sizeof(c->info.max_entries) == 2, "identify data");
+    static_assert(sizeof(c->ctrl->page_size) == sizeof(size_t) && sizeof(c->n_qps) == 4 && sizeof(c->d_qps->block_size_log) == 4, "handle");
+    nvm_queue_t q;
+    nvm_queue_reset(&q);
+    (void)nvm_sq_enqueue;
+    (void)nvm_cq_dequeue;
     printf("%s\n", nvm_strerror(0));
     return 0;
 }
