@@ -1113,6 +1113,43 @@ extern "C" int bam_launch_pattern_read(bam_array_t a, uint32_t pattern, uint64_t
     return launch_fused(c, w, (cudaStream_t)stream);
 }
 
+/* ---- command encoding, exposed for checks against other encoders ------------------------------------ */
+
+__global__ void k_encode_rw(uint32_t cid, uint8_t opcode, uint32_t ns_id, uint64_t prp1, uint64_t prp2, uint64_t slba, uint32_t n_blks,
+                            uint4* out)
+{
+    uint4 c0, c1, c2, c3;
+    bam::nvm_cmd_rw_quarters(cid, opcode, ns_id, prp1, prp2, slba, n_blks, c0, c1, c2, c3);
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+extern "C" int bam_encode_rw_command(void* out64, uint16_t cid, uint8_t opcode, uint32_t ns_id, uint64_t prp1, uint64_t prp2,
+                                     uint64_t start_lba, uint16_t n_blks, int on_device)
+{
+    if (!out64 || n_blks == 0) return BAM_EINVAL;
+    if (!on_device) {
+        /* the builders a host program (or a kernel) calls one after the other */
+        nvm_cmd_t cmd;
+        memset(&cmd, 0, sizeof cmd);
+        bam::nvm_cmd_header(&cmd, cid, opcode, ns_id);
+        bam::nvm_cmd_data_ptr(&cmd, prp1, prp2);
+        bam::nvm_cmd_rw_blks(&cmd, start_lba, n_blks);
+        /* and the register form the submission paths use must agree with them */
+        uint4 q[4];
+        bam::nvm_cmd_rw_quarters(cid, opcode, ns_id, prp1, prp2, start_lba, n_blks, q[0], q[1], q[2], q[3]);
+        if (memcmp(q, &cmd, 64) != 0) return BAM_EIO;
+        memcpy(out64, &cmd, 64);
+        return BAM_OK;
+    }
+    uint4* d = nullptr;
+    CK(cudaMalloc(&d, 64));
+    k_encode_rw<<<1, 1>>>(cid, opcode, ns_id, prp1, prp2, start_lba, n_blks, d);
+    cudaError_t e = cudaMemcpy(out64, d, 64, cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) { g_last_cuda = e; return BAM_ECUDA; }
+    return BAM_OK;
+}
+
 extern "C" int bam_cache_flush(bam_cache_t pc, void* stream)
 {
     if (!pc) return BAM_EINVAL;

@@ -58,6 +58,18 @@ __host__ __device__ __forceinline__ void nvm_cmd_rw_blks(nvm_cmd_t* cmd, uint64_
     cmd->dword[12] = (cmd->dword[12] & 0xffff0000u) | ((uint32_t)(n_blks - 1) & 0xffffu);
 }
 
+/* The same read/write command as four 16-byte quarters kept in registers (what the submission paths
+ * store into the queue): DW0 = CID | opcode, DW1 = NSID, DW6-9 = PRP1 / PRP2, DW10-11 = SLBA,
+ * DW12 = NLB - 1; everything else zero. */
+__host__ __device__ __forceinline__ void nvm_cmd_rw_quarters(uint32_t cid, uint8_t opcode, uint32_t ns_id, uint64_t prp1, uint64_t prp2,
+                                                             uint64_t start_lba, uint32_t n_blks, uint4& c0, uint4& c1, uint4& c2, uint4& c3)
+{
+    c0 = make_uint4((cid << 16) | (opcode & 0x7fu), ns_id, 0u, 0u);
+    c1 = make_uint4(0u, 0u, (uint32_t)prp1, (uint32_t)(prp1 >> 32));
+    c2 = make_uint4((uint32_t)prp2, (uint32_t)(prp2 >> 32), (uint32_t)start_lba, (uint32_t)(start_lba >> 32));
+    c3 = make_uint4((n_blks - 1u) & 0xffffu, 0u, 0u, 0u);
+}
+
 #define BAM_CID_ERR 0xffffffffu
 #define BAM_POS_ERR 0xffffffffu
 #define BAM_CPL_ERR 0xffffffffu
@@ -367,10 +379,9 @@ BAM_DEV uint32_t warp_submit_group(uint32_t mask, uint32_t g, QueuePair* qp, uin
 #endif
     if (mine) {
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<nvm_cmd_t*>(const_cast<void*>(sq->vaddr)) + pos);
-        dst[0] = make_uint4((cid << 16) | (opcode & 0x7fu), qp->nvmNamespace, 0u, 0u);
-        dst[1] = make_uint4(0u, 0u, (uint32_t)bus_addr, (uint32_t)(bus_addr >> 32));
-        dst[2] = make_uint4((uint32_t)bus_addr2, (uint32_t)(bus_addr2 >> 32), (uint32_t)starting_lba, (uint32_t)(starting_lba >> 32));
-        dst[3] = make_uint4((n_blocks - 1u) & 0xffffu, 0u, 0u, 0u);
+        uint4 c0, c1, c2, c3;
+        nvm_cmd_rw_quarters(cid, opcode, qp->nvmNamespace, bus_addr, bus_addr2, starting_lba, n_blocks, c0, c1, c2, c3);
+        dst[0] = c0; dst[1] = c1; dst[2] = c2; dst[3] = c3;
         st_release_gpu(&sq->tail_mark[pos], 1u);
     }
     /* publish: whoever gets tail_lock sweeps with the whole warp */
@@ -528,10 +539,8 @@ BAM_DEV int access_data_submit(QueuePair* qp, uint64_t starting_lba, uint32_t n_
 #endif
     /* DW0 = CID | opcode, DW1 = NSID, DW6-9 = PRP1/PRP2, DW10-11 = SLBA, DW12 = NLB-1
      * (the fields nvm_cmd_header / nvm_cmd_data_ptr / nvm_cmd_rw_blks set), built in registers */
-    const uint4 c0 = make_uint4((cid << 16) | (opcode & 0x7fu), qp->nvmNamespace, 0u, 0u);
-    const uint4 c1 = make_uint4(0u, 0u, (uint32_t)bus_addr, (uint32_t)(bus_addr >> 32));
-    const uint4 c2 = make_uint4((uint32_t)bus_addr2, (uint32_t)(bus_addr2 >> 32), (uint32_t)starting_lba, (uint32_t)(starting_lba >> 32));
-    const uint4 c3 = make_uint4((n_blocks - 1u) & 0xffffu, 0u, 0u, 0u);
+    uint4 c0, c1, c2, c3;
+    nvm_cmd_rw_quarters(cid, opcode, qp->nvmNamespace, bus_addr, bus_addr2, starting_lba, n_blocks, c0, c1, c2, c3);
     if (sq_publish(&qp->sq, pos, ticket, c0, c1, c2, c3) == BAM_POS_ERR) return BAM_ETIMEDOUT;
 #ifdef BAM_PROFILE
     { long long n = clock64(); BAM_PROF_ADD(st, 3, n - pt); pt = n; }

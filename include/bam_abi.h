@@ -295,6 +295,11 @@ int bam_direct_checksum(const uint64_t* idx_dev, uint64_t n, uint64_t store_seed
                         uint64_t* sum_out_dev, void* stream);
 
 /* Grid the launchers use: total blocks, controller blocks among them, threads per block. */
+/* The 64-byte NVMe read/write command the library writes into a submission queue for these fields
+ * (nvm_cmd_header / nvm_cmd_data_ptr / nvm_cmd_rw_blks, include/nvm_cmd.h:54-88), for checks against
+ * other encoders; on_device != 0 runs the register-built form in a kernel. */
+int bam_encode_rw_command(void* out64, uint16_t cid, uint8_t opcode, uint32_t ns_id, uint64_t prp1, uint64_t prp2,
+                          uint64_t start_lba, uint16_t n_blks, int on_device);
 int bam_launch_geometry(bam_ctrl_t c, uint32_t* grid, uint32_t* ctrl_blocks, uint32_t* threads);
 
 #ifdef __cplusplus

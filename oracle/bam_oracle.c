@@ -8,13 +8,14 @@
  * vectors and no fixtures for this path, its device headers do not compile for a host, and
  * its host library needs /dev/libnvm* (kernel module + raw SSD).  The oracle is therefore a
  * restatement, pinned by (a) published known-answer vectors of the generators it shares with
- * the device code (SplitMix64, PCG32, CRC-32) and (b) independent numpy/zlib/scipy
- * re-computations in the test-suite.
+ * the device code (SplitMix64, PCG32, CRC-32), (b) independent numpy/zlib/scipy
+ * re-computations in the test-suite and (c), for the command encoding only, the reference's
+ * own builders compiled from its sources (ref_wire.cpp, Makefile target `ref`).
  *
  * Two layers:
  *   1. Result oracle (orc_*): pure functions of the seeded inputs -- wrapping 64-bit sums,
  *      page CRC-32s, R-MAT CSR construction, BFS levels, min-vertex CC labels.  Independent
- *      of any cache or queue behaviour; this is what bit-exactness is judged against.
+ *      of any cache or queue behaviour; this is what bit-exactness is checked against.
  *   2. Protocol restatement (ref_*): the reference's device algorithms re-expressed for host
  *      threads -- the parallel NVMe queue protocol (include/nvm_parallel_queue.h), the page
  *      cache state machine (include/page_cache.h:1122-1224 acquire_page, :1786-1927
@@ -588,19 +589,32 @@ typedef struct {
  * enqueue_second (:1961-2007), an extra one-block read that flushes PCIe write ordering for
  * GPUDirect data; the emulated controller publishes its completion after the payload with a
  * release store, so that extra I/O has no counterpart here. */
-static void ref_read_data(ref_cache_t* pc, ref_qp_t* qp, uint64_t start_lba, uint32_t n_blocks, uint64_t slot)
+/* The READ / WRITE command of include/nvm_cmd.h:54-88 (nvm_cmd_header, nvm_cmd_data_ptr,
+ * nvm_cmd_rw_blks) as read_data builds it (page_cache.h:2009-2032).  Exported so that tests can
+ * compare it with the reference's own builders and with the library's. */
+ORC_API void orc_encode_rw(uint16_t cid, uint8_t opcode, uint32_t ns_id, uint64_t prp1, uint64_t prp2, uint64_t start_lba,
+                           uint32_t n_blocks, void* out64)
 {
     ref_cmd_t cmd;
     memset(&cmd, 0, sizeof cmd);
-    uint16_t cid = ref_get_cid(&qp->sq);
-    cmd.dword[0] = ((uint32_t)cid << 16) | 0x02u;            /* NVM_IO_READ */
-    cmd.dword[1] = pc->ns_id;
-    uint64_t prp1 = (uint64_t)(uintptr_t)(pc->base_addr + slot * pc->page_size);
+    cmd.dword[0] = ((uint32_t)cid << 16) | (opcode & 0x7fu);
+    cmd.dword[1] = ns_id;
     cmd.dword[6] = (uint32_t)prp1;
     cmd.dword[7] = (uint32_t)(prp1 >> 32);
+    cmd.dword[8] = (uint32_t)prp2;
+    cmd.dword[9] = (uint32_t)(prp2 >> 32);
     cmd.dword[10] = (uint32_t)start_lba;
     cmd.dword[11] = (uint32_t)(start_lba >> 32);
     cmd.dword[12] = (n_blocks - 1) & 0xffffu;
+    memcpy(out64, &cmd, 64);
+}
+
+static void ref_read_data(ref_cache_t* pc, ref_qp_t* qp, uint64_t start_lba, uint32_t n_blocks, uint64_t slot)
+{
+    ref_cmd_t cmd;
+    uint16_t cid = ref_get_cid(&qp->sq);
+    uint64_t prp1 = (uint64_t)(uintptr_t)(pc->base_addr + slot * pc->page_size);
+    orc_encode_rw(cid, 0x02u /* NVM_IO_READ */, pc->ns_id, prp1, 0, start_lba, n_blocks, &cmd);
     ref_sq_enqueue(&qp->sq, &cmd);
     uint32_t virt_pos, head_seen;
     uint32_t cq_pos = ref_cq_poll(&qp->cq, cid, &virt_pos, &head_seen);

@@ -27,6 +27,63 @@ def build(force=False):
     return LIB_PATH
 
 
+REF_WIRE_PATH = os.path.join(HERE, "_ref", "libref_wire.so")
+REFERENCE_ROOT = "/root/reference"
+
+
+def build_ref_wire(force=False):
+    """Compile the reference's own wire-format code (oracle/ref_wire.cpp + the reference's sources where
+    they lie) into oracle/_ref/libref_wire.so.  Needs the reference project; returns None without it and
+    without a prebuilt library."""
+    if os.path.isdir(os.path.join(REFERENCE_ROOT, "include")):
+        srcs = [os.path.join(HERE, "ref_wire.cpp"), os.path.join(HERE, "ref_shim", "simt", "atomic")]
+        if force or not os.path.exists(REF_WIRE_PATH) or os.path.getmtime(REF_WIRE_PATH) < max(map(os.path.getmtime, srcs)):
+            subprocess.run(["make", "-C", HERE, "-B", "ref", "REFERENCE=" + REFERENCE_ROOT], check=True, capture_output=True)
+    return REF_WIRE_PATH if os.path.exists(REF_WIRE_PATH) else None
+
+
+_ref_wire = None
+
+
+def ref_wire():
+    """ctypes handle of the reference's wire-format code, or None when it cannot be had."""
+    global _ref_wire
+    if _ref_wire is None:
+        path = build_ref_wire()
+        if path is None:
+            return None
+        L = C.CDLL(path)
+        u16, u8 = C.c_uint16, C.c_uint8
+        L.refw_queue_new.restype = vp
+        L.refw_queue_new.argtypes = [vp, C.c_int, u16, u32, vp, u64]
+        L.refw_queue_free.argtypes = [vp]
+        L.refw_queue_doorbell_offset.restype = u64
+        L.refw_queue_doorbell_offset.argtypes = [vp]
+        L.refw_encode_rw.argtypes = [u16, u8, u32, u64, u64, u64, u16, vp]
+        L.refw_sq_put_rw.argtypes = [vp, u16, u8, u32, u64, u64, u64, u16]
+        L.refw_sq_submit.argtypes = [vp]
+        L.refw_cq_take.argtypes = [vp, vp, u64, C.POINTER(u16), C.POINTER(u16), C.POINTER(u16), C.POINTER(u8), C.POINTER(u8),
+                                   C.POINTER(C.c_int)]
+        L.refw_strerror.restype = C.c_char_p
+        L.refw_strerror.argtypes = [C.c_int]
+        L.refw_unpack_sct.argtypes = [C.c_int]
+        L.refw_unpack_sc.argtypes = [C.c_int]
+        L.refw_page_align.restype = u64
+        L.refw_page_align.argtypes = [u64, u64]
+        L.refw_page_to_block.restype = u64
+        L.refw_page_to_block.argtypes = [u64, u64, u64]
+        L.refw_sizeof_queue.restype = u32
+        _ref_wire = L
+    return _ref_wire
+
+
+def encode_rw(cid, opcode, ns_id, prp1, prp2, start_lba, n_blocks):
+    """The oracle's restatement of the read/write command encoding (64 bytes)."""
+    out = (C.c_uint8 * 64)()
+    lib().orc_encode_rw(cid, opcode, ns_id, prp1, prp2, start_lba, n_blocks, out)
+    return bytes(out)
+
+
 _lib = None
 
 
@@ -51,6 +108,7 @@ def lib():
         L.orc_indexed_checksum.argtypes = [u64, u64, vp, u64]
         L.orc_backing_location.restype = u64
         L.orc_backing_location.argtypes = [u64, u64, u64, u32, C.POINTER(u32)]
+        L.orc_encode_rw.argtypes = [C.c_uint16, C.c_uint8, u32, u64, u64, u64, u32, vp]
         L.orc_page_crc.restype = u32
         L.orc_page_crc.argtypes = [u64, u64, u32]
         L.orc_block_requests.argtypes = [u64, u64, u64, u32, u64, u64, vp, vp]

@@ -1,0 +1,134 @@
+"""GPU interoperability test with the REFERENCE's own host code: its classic queue functions
+(nvm_sq_enqueue, nvm_sq_submit, nvm_cq_dequeue_block, nvm_sq_update, nvm_cq_update), its queue set-up
+(nvm_queue_clear, doorbell offsets of src/regs.h) and its command builders -- compiled from the
+reference's sources into oracle/_ref/libref_wire.so -- submit NVMe READ / WRITE commands that the
+emulated controller of this library serves.  What moves must equal the media, byte for byte, and every
+completion must carry what the reference's accessors expect."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+u8, u16, u32, u64, vp = C.c_uint8, C.c_uint16, C.c_uint32, C.c_uint64, C.c_void_p
+PAGE = 4096
+
+
+class NvmCtrl(C.Structure):                       # nvm_ctrl_t (include/bam/abi_types.h)
+    _fields_ = [("page_size", C.c_size_t), ("dstrd", u8), ("timeout", u64), ("max_qs", u32), ("mm_size", C.c_size_t),
+                ("mm_ptr", vp)]
+
+
+class NvmDma(C.Structure):                        # nvm_dma_t without its trailing ioaddrs[]
+    _fields_ = [("vaddr", vp), ("local", C.c_int8), ("contiguous", C.c_int8), ("page_size", C.c_size_t),
+                ("n_ioaddrs", C.c_size_t)]
+
+
+def ioaddrs(dma_ptr, n):
+    return (u64 * n).from_address(dma_ptr.value + C.sizeof(NvmDma))
+
+
+def test_reference_host_queue_code_drives_the_emulated_controller(cuda, bam, orc):
+    ref = orc.ref_wire()
+    if ref is None:
+        pytest.skip("the reference's wire-format code is not built (needs the reference project)")
+    lib = bam.load()
+    for name, args in (("nvm_emu_ctrl_init", [C.POINTER(vp), vp]), ("nvm_aq_create", [C.POINTER(vp), vp, vp]),
+                       ("nvm_dma_create", [C.POINTER(vp), vp, C.c_size_t]), ("nvm_admin_cq_create", [vp, vp, u16, vp, C.c_size_t, C.c_size_t]),
+                       ("nvm_admin_sq_create", [vp, vp, vp, u16, vp, C.c_size_t, C.c_size_t]), ("nvm_admin_sq_delete", [vp, vp, vp]),
+                       ("nvm_admin_cq_delete", [vp, vp])):
+        getattr(lib, name).argtypes = args
+        getattr(lib, name).restype = C.c_int
+    for name in ("nvm_dma_unmap", "nvm_aq_destroy", "nvm_ctrl_free"):
+        getattr(lib, name).argtypes = [vp]
+        getattr(lib, name).restype = None
+
+    n_media_pages, seed = 4096, 77
+    emu = bam.Controller(n_media_pages * PAGE, 0, queue_depth=64, num_queues=1)
+    emu.set_launch_timeout(60 * 1_000_000_000)               # the service kernel leaves after a minute at most
+    media = emu.store_numpy()
+    media[:] = orc.fill_store(seed, 0, n_media_pages * 512)
+
+    nctrl, aq, qmem, buf = vp(), vp(), vp(), vp()
+    assert lib.nvm_emu_ctrl_init(C.byref(nctrl), emu.h) == 0
+    ctrl = NvmCtrl.from_address(nctrl.value)
+    assert (ctrl.page_size, ctrl.dstrd, ctrl.max_qs) == (4096, 0, 1024) and ctrl.mm_ptr
+    assert lib.nvm_aq_create(C.byref(aq), nctrl, None) == 0
+    assert lib.nvm_dma_create(C.byref(qmem), nctrl, 2 * PAGE) == 0
+    n_buf = 200
+    assert lib.nvm_dma_create(C.byref(buf), nctrl, n_buf * PAGE) == 0
+    qd, bd = NvmDma.from_address(qmem.value), NvmDma.from_address(buf.value)
+    q_io, b_io = ioaddrs(qmem, 2), ioaddrs(buf, n_buf)
+    # this library's side: register the queue memory with the command processor (starts the service)
+    my_cq = np.zeros(4096, dtype=np.uint8)
+    my_sq = np.zeros(4096, dtype=np.uint8)
+    assert lib.nvm_admin_cq_create(aq, my_cq.ctypes.data, 1, qmem, 0, 0) == 0
+    assert lib.nvm_admin_sq_create(aq, my_sq.ctypes.data, my_cq.ctypes.data, 1, qmem, 1, 0) == 0
+    # the reference's side: its own queue descriptors over the same memory and register window
+    rcq = ref.refw_queue_new(ctrl.mm_ptr, 1, 1, 256, qd.vaddr, q_io[0])
+    rsq = ref.refw_queue_new(ctrl.mm_ptr, 0, 1, 64, qd.vaddr + PAGE, q_io[1])
+    assert rcq and rsq
+    assert ref.refw_queue_doorbell_offset(rsq) == 0x1000 + 2 * 4 and ref.refw_queue_doorbell_offset(rcq) == 0x1000 + 3 * 4
+
+    cid, sqhd, sqid, sct, sc, packed = u16(), u16(), u16(), u8(), u8(), C.c_int()
+
+    def transfer(opcode, first_media_page, n):
+        sent = done = 0
+        seen = []
+        while done < n:
+            while sent < n and ref.refw_sq_put_rw(rsq, 1000 + sent, opcode, 1, b_io[sent], 0, (first_media_page + sent) * 8, 8) == 0:
+                sent += 1
+            ref.refw_sq_submit(rsq)
+            assert ref.refw_cq_take(rcq, rsq, 5000, C.byref(cid), C.byref(sqhd), C.byref(sqid), C.byref(sct), C.byref(sc),
+                                    C.byref(packed)) == 0, "the controller did not answer"
+            assert (sqid.value, sct.value, sc.value, packed.value) == (1, 0, 0, 0) and sqhd.value < 64
+            seen.append(cid.value)
+            done += 1
+        assert sorted(seen) == list(range(1000, 1000 + n))     # every command completed exactly once
+        assert sent == n
+
+    data = np.frombuffer((C.c_uint8 * (n_buf * PAGE)).from_address(bd.vaddr), dtype=np.uint64)
+    # READ 200 pages (several wraps of the 64-entry SQ) and compare with the media
+    transfer(2, 300, n_buf)
+    assert (data == media[300 * 512: (300 + n_buf) * 512]).all()
+    # WRITE them somewhere else, READ that back
+    data[:] = orc.fill_store(seed + 1, 0, n_buf * 512)
+    transfer(1, 2000, n_buf)
+    assert (media[2000 * 512: (2000 + n_buf) * 512] == orc.fill_store(seed + 1, 0, n_buf * 512)).all()
+    assert media[2000 * 512 - 1] == orc.fill_store(seed, 2000 * 512 - 1, 1)[0]            # neighbours untouched
+    data[:] = 0
+    transfer(2, 2000, n_buf)
+    assert (data == orc.fill_store(seed + 1, 0, n_buf * 512)).all()
+    # a read beyond the namespace: generic status "LBA out of range", which the reference packs as -0x80
+    assert ref.refw_sq_put_rw(rsq, 7, 2, 1, b_io[0], 0, n_media_pages * 8, 8) == 0
+    ref.refw_sq_submit(rsq)
+    assert ref.refw_cq_take(rcq, rsq, 5000, C.byref(cid), C.byref(sqhd), C.byref(sqid), C.byref(sct), C.byref(sc), C.byref(packed)) == 0
+    assert (cid.value, sct.value, sc.value, packed.value) == (7, 0, 0x80, -0x80)
+    assert b"range" in ref.refw_strerror(packed.value).lower()
+
+    ref.refw_queue_free(rsq); ref.refw_queue_free(rcq)
+    assert lib.nvm_admin_sq_delete(aq, my_sq.ctypes.data, my_cq.ctypes.data) == 0
+    assert lib.nvm_admin_cq_delete(aq, my_cq.ctypes.data) == 0
+    del data
+    lib.nvm_dma_unmap(buf); lib.nvm_dma_unmap(qmem)
+    lib.nvm_aq_destroy(aq)
+    lib.nvm_ctrl_free(nctrl)
+    emu.close()
+
+
+def test_device_command_encoding_equals_the_reference_builders(cuda, bam, orc):
+    """The register-built command of the device submission paths, run in a kernel, against the reference's
+    nvm_cmd_header / nvm_cmd_data_ptr / nvm_cmd_rw_blks."""
+    ref = orc.ref_wire()
+    if ref is None:
+        pytest.skip("the reference's wire-format code is not built (needs the reference project)")
+    lib = bam.load()
+    rng = np.random.default_rng(5)
+    for _ in range(40):
+        cidv, opc, ns = int(rng.integers(0, 1 << 16)), int(rng.choice([1, 2])), int(rng.integers(1, 1 << 32))
+        prp1, prp2, lba = (int(x) for x in rng.integers(0, 1 << 63, 3, dtype=np.uint64))
+        nb = int(rng.integers(1, 1 << 16))
+        want, got = (C.c_uint8 * 64)(), (C.c_uint8 * 64)()
+        ref.refw_encode_rw(cidv, opc, ns, prp1, prp2, lba, nb, want)
+        assert lib.bam_encode_rw_command(got, cidv, opc, ns, prp1, prp2, lba, nb, 1) == 0
+        assert bytes(got) == bytes(want)

@@ -7,6 +7,8 @@ import json
 import os
 import zlib
 
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -303,4 +305,32 @@ def test_pagerank_oracle_against_linear_solve(orc):
     rank2, sweeps2, _ = orc.pagerank(off, cols, tolerance_q=(1 << orc.PR_FRAC_BITS) // 1000000)
     v2 = rank2.astype(np.float64) / float(1 << orc.PR_FRAC_BITS)
     assert sweeps2 >= sweeps and np.abs(v2 - x).sum() / x.sum() < 1e-4
+
+
+def test_command_encoding_against_the_reference_builders(orc, bam):
+    """The reference's own nvm_cmd_header / nvm_cmd_data_ptr / nvm_cmd_rw_blks (compiled from its sources
+    into oracle/_ref/libref_wire.so), the oracle's restatement and the library's host-side builders give
+    the same 64 bytes; so do the reference's status packing and page arithmetic."""
+    ref = orc.ref_wire()
+    if ref is None:
+        pytest.skip("the reference's wire-format code is not built (needs the reference project)")
+    lib = bam.load()
+    rng = np.random.default_rng(11)
+    for _ in range(300):
+        cid = int(rng.integers(0, 1 << 16))
+        opc = int(rng.choice([1, 2]))
+        ns = int(rng.integers(1, 1 << 32))
+        prp1, prp2, lba = (int(x) for x in rng.integers(0, 1 << 63, 3, dtype=np.uint64))
+        nb = int(rng.integers(1, 1 << 16))
+        want = (C.c_uint8 * 64)()
+        ref.refw_encode_rw(cid, opc, ns, prp1, prp2, lba, nb, want)
+        assert orc.encode_rw(cid, opc, ns, prp1, prp2, lba, nb) == bytes(want)
+        got = (C.c_uint8 * 64)()
+        assert lib.bam_encode_rw_command(got, cid, opc, ns, prp1, prp2, lba, nb, 0) == 0
+        assert bytes(got) == bytes(want)
+    # -(SCT << 8 | SC) packing and the strings behind it
+    assert ref.refw_unpack_sct(-0x281) == 2 and ref.refw_unpack_sc(-0x281) == 0x81
+    assert b"LBA out of range" in ref.refw_strerror(-0x80) or b"range" in ref.refw_strerror(-0x80).lower()
+    assert ref.refw_page_align(4097, 4096) == 8192 and ref.refw_page_to_block(4096, 512, 3) == 24
+    assert ref.refw_sizeof_queue() > 0
 
