@@ -762,6 +762,83 @@ static void* ref_ctrl_thread(void* p)
     return 0;
 }
 
+/* The same controller over bare queue memory and doorbell registers (no descriptors of this file):
+ * what an NVMe controller sees of a queue pair.  Lets other producers of the wire protocol -- in the
+ * tests: the reference's own queue code compiled from its sources -- be served by this controller.
+ * READ and WRITE; SQ and CQ may differ in depth. */
+typedef struct {
+    const ref_cmd_t* sq_mem; ref_cpl_t* cq_mem;
+    volatile uint32_t* sq_db; volatile uint32_t* cq_db;
+    uint32_t sq_qs, cq_qs, cq_qs_log2; uint16_t sqid;
+    uint8_t* store; uint64_t store_bytes; uint32_t lba_bytes;
+    volatile int stop;
+    uint64_t served;
+    pthread_t thread;
+} orc_wire_ctrl_t;
+
+static void* orc_wire_ctrl_thread(void* p)
+{
+    orc_wire_ctrl_t* a = (orc_wire_ctrl_t*)p;
+    uint32_t sq_head = 0, cq_tail = 0, cq_head_virt = 0;
+    const uint32_t smask = a->sq_qs - 1, cmask = a->cq_qs - 1;
+    unsigned idle = 0;
+    while (!ld_acq(&a->stop)) {
+        uint32_t tail = ld_acq(a->sq_db);
+        int worked = 0;
+        while (sq_head != tail) {
+            uint32_t hdb = ld_acq(a->cq_db);
+            cq_head_virt += (hdb - (cq_head_virt & cmask)) & cmask;
+            if (cq_tail - cq_head_virt >= a->cq_qs - 1) break;            /* keep one completion slot open */
+            const ref_cmd_t* cmd = a->sq_mem + sq_head;
+            uint32_t cid = cmd->dword[0] >> 16, opc = cmd->dword[0] & 0x7fu;
+            uint64_t prp1 = ((uint64_t)cmd->dword[7] << 32) | cmd->dword[6];
+            uint64_t slba = ((uint64_t)cmd->dword[11] << 32) | cmd->dword[10];
+            uint64_t bytes = (uint64_t)((cmd->dword[12] & 0xffffu) + 1) * a->lba_bytes;
+            uint32_t status = 0;
+            if (opc != 0x01u && opc != 0x02u) status = 0x01;                               /* invalid opcode */
+            else if (slba * a->lba_bytes + bytes > a->store_bytes) status = 0x80;          /* LBA out of range */
+            else if (opc == 0x02u) memcpy((void*)(uintptr_t)prp1, a->store + slba * a->lba_bytes, bytes);
+            else memcpy(a->store + slba * a->lba_bytes, (const void*)(uintptr_t)prp1, bytes);
+            sq_head = (sq_head + 1) & smask;
+            ref_cpl_t* c = a->cq_mem + (cq_tail & cmask);
+            uint32_t phase = (~(cq_tail >> a->cq_qs_log2)) & 1u;
+            c->dword[0] = 0; c->dword[1] = 0;
+            st_rlx(&c->dword[2], sq_head | ((uint32_t)a->sqid << 16));
+            st_rel(&c->dword[3], cid | (phase << 16) | (status << 17));
+            cq_tail++;
+            a->served++;
+            worked = 1;
+        }
+        if (!worked) { if (++idle > 64) { sched_yield(); idle = 0; } else __builtin_ia32_pause(); }
+        else idle = 0;
+    }
+    return 0;
+}
+
+ORC_API void* orc_wire_ctrl_start(const void* sq_mem, void* cq_mem, void* sq_db, void* cq_db, uint32_t sq_qs, uint32_t cq_qs,
+                                  uint16_t sqid, void* store, uint64_t store_bytes, uint32_t lba_bytes)
+{
+    orc_wire_ctrl_t* a = (orc_wire_ctrl_t*)calloc(1, sizeof *a);
+    if (!a) return 0;
+    a->sq_mem = (const ref_cmd_t*)sq_mem; a->cq_mem = (ref_cpl_t*)cq_mem;
+    a->sq_db = (volatile uint32_t*)sq_db; a->cq_db = (volatile uint32_t*)cq_db;
+    a->sq_qs = sq_qs; a->cq_qs = cq_qs; a->sqid = sqid;
+    while ((1u << a->cq_qs_log2) < cq_qs) a->cq_qs_log2++;
+    a->store = (uint8_t*)store; a->store_bytes = store_bytes; a->lba_bytes = lba_bytes;
+    if (pthread_create(&a->thread, 0, orc_wire_ctrl_thread, a) != 0) { free(a); return 0; }
+    return a;
+}
+
+ORC_API uint64_t orc_wire_ctrl_stop(void* h)
+{
+    orc_wire_ctrl_t* a = (orc_wire_ctrl_t*)h;
+    __atomic_store_n(&a->stop, 1, __ATOMIC_RELEASE);
+    pthread_join(a->thread, 0);
+    uint64_t served = a->served;
+    free(a);
+    return served;
+}
+
 static void ref_queue_init(ref_queue_t* q, uint32_t qs, size_t entry_bytes, volatile uint32_t* db, int is_sq)
 {
     memset(q, 0, sizeof *q);

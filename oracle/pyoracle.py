@@ -28,6 +28,7 @@ def build(force=False):
 
 
 REF_WIRE_PATH = os.path.join(HERE, "_ref", "libref_wire.so")
+REF_PQ_PATH = os.path.join(HERE, "_ref", "libref_pq.so")
 REFERENCE_ROOT = "/root/reference"
 
 
@@ -36,8 +37,9 @@ def build_ref_wire(force=False):
     they lie) into oracle/_ref/libref_wire.so.  Needs the reference project; returns None without it and
     without a prebuilt library."""
     if os.path.isdir(os.path.join(REFERENCE_ROOT, "include")):
-        srcs = [os.path.join(HERE, "ref_wire.cpp"), os.path.join(HERE, "ref_shim", "simt", "atomic")]
-        if force or not os.path.exists(REF_WIRE_PATH) or os.path.getmtime(REF_WIRE_PATH) < max(map(os.path.getmtime, srcs)):
+        srcs = [os.path.join(HERE, "ref_wire.cpp"), os.path.join(HERE, "ref_pq.cpp"), os.path.join(HERE, "ref_shim", "simt", "atomic")]
+        built = [REF_WIRE_PATH, REF_PQ_PATH]
+        if force or not all(map(os.path.exists, built)) or min(map(os.path.getmtime, built)) < max(map(os.path.getmtime, srcs)):
             subprocess.run(["make", "-C", HERE, "-B", "ref", "REFERENCE=" + REFERENCE_ROOT], check=True, capture_output=True)
     return REF_WIRE_PATH if os.path.exists(REF_WIRE_PATH) else None
 
@@ -77,6 +79,27 @@ def ref_wire():
     return _ref_wire
 
 
+_ref_pq = None
+
+
+def ref_pq():
+    """ctypes handle of the reference's parallel queue protocol compiled for host threads, or None."""
+    global _ref_pq
+    if _ref_pq is None:
+        build_ref_wire()
+        if not os.path.exists(REF_PQ_PATH):
+            return None
+        L = C.CDLL(REF_PQ_PATH)
+        u16, u8 = C.c_uint16, C.c_uint8
+        L.refpq_pair_new.restype = vp
+        L.refpq_pair_new.argtypes = [vp, u16, u32, vp, u64, u32, vp, u64, u32]
+        L.refpq_pair_free.argtypes = [vp]
+        L.refpq_run.argtypes = [vp, u32, u8, vp, vp, u16, u64, u64]
+        L.refpq_state.argtypes = [vp] + [C.POINTER(u32)] * 5
+        _ref_pq = L
+    return _ref_pq
+
+
 def encode_rw(cid, opcode, ns_id, prp1, prp2, start_lba, n_blocks):
     """The oracle's restatement of the read/write command encoding (64 bytes)."""
     out = (C.c_uint8 * 64)()
@@ -108,6 +131,10 @@ def lib():
         L.orc_indexed_checksum.argtypes = [u64, u64, vp, u64]
         L.orc_backing_location.restype = u64
         L.orc_backing_location.argtypes = [u64, u64, u64, u32, C.POINTER(u32)]
+        L.orc_wire_ctrl_start.restype = vp
+        L.orc_wire_ctrl_start.argtypes = [vp, vp, vp, vp, u32, u32, C.c_uint16, vp, u64, u32]
+        L.orc_wire_ctrl_stop.restype = u64
+        L.orc_wire_ctrl_stop.argtypes = [vp]
         L.orc_encode_rw.argtypes = [C.c_uint16, C.c_uint8, u32, u64, u64, u64, u32, vp]
         L.orc_page_crc.restype = u32
         L.orc_page_crc.argtypes = [u64, u64, u32]

@@ -116,6 +116,76 @@ def test_reference_host_queue_code_drives_the_emulated_controller(cuda, bam, orc
     emu.close()
 
 
+def test_reference_parallel_queue_code_drives_the_emulated_controller(cuda, bam, orc):
+    """The protocol the reference's GPU threads run -- get_cid, sq_enqueue with ticketed slots and batched
+    doorbells, cq_poll by command id and phase, cq_dequeue with SQ-head propagation, put_cid
+    (include/nvm_parallel_queue.h, compiled for the host into oracle/_ref/libref_pq.so) -- executed by 16 host
+    threads sharing one queue pair, against the emulated controller on the GPU."""
+    pq = orc.ref_pq()
+    if pq is None:
+        pytest.skip("the reference's queue code is not built (needs the reference project)")
+    lib = bam.load()
+    for name, args in (("nvm_emu_ctrl_init", [C.POINTER(vp), vp]), ("nvm_aq_create", [C.POINTER(vp), vp, vp]),
+                       ("nvm_dma_create", [C.POINTER(vp), vp, C.c_size_t]), ("nvm_admin_cq_create", [vp, vp, u16, vp, C.c_size_t, C.c_size_t]),
+                       ("nvm_admin_sq_create", [vp, vp, vp, u16, vp, C.c_size_t, C.c_size_t]), ("nvm_admin_sq_delete", [vp, vp, vp]),
+                       ("nvm_admin_cq_delete", [vp, vp])):
+        getattr(lib, name).argtypes = args
+        getattr(lib, name).restype = C.c_int
+    for name in ("nvm_dma_unmap", "nvm_aq_destroy", "nvm_ctrl_free"):
+        getattr(lib, name).argtypes = [vp]
+        getattr(lib, name).restype = None
+    n_media_pages, seed, qs = 8192, 91, 64
+    emu = bam.Controller(n_media_pages * PAGE, 0, queue_depth=64, num_queues=1)
+    emu.set_launch_timeout(60 * 1_000_000_000)
+    media = emu.store_numpy()
+    media[:] = orc.fill_store(seed, 0, n_media_pages * 512)
+    nctrl, aq, qmem, buf = vp(), vp(), vp(), vp()
+    assert lib.nvm_emu_ctrl_init(C.byref(nctrl), emu.h) == 0
+    ctrl = NvmCtrl.from_address(nctrl.value)
+    assert lib.nvm_aq_create(C.byref(aq), nctrl, None) == 0
+    assert lib.nvm_dma_create(C.byref(qmem), nctrl, 2 * PAGE) == 0
+    n_req = 3000
+    assert lib.nvm_dma_create(C.byref(buf), nctrl, n_req * PAGE) == 0
+    qd, bd = NvmDma.from_address(qmem.value), NvmDma.from_address(buf.value)
+    q_io, b_io = ioaddrs(qmem, 2), ioaddrs(buf, n_req)
+    my_cq, my_sq = np.zeros(4096, dtype=np.uint8), np.zeros(4096, dtype=np.uint8)
+    assert lib.nvm_admin_cq_create(aq, my_cq.ctypes.data, 1, qmem, 0, qs) == 0
+    assert lib.nvm_admin_sq_create(aq, my_sq.ctypes.data, my_cq.ctypes.data, 1, qmem, 1, qs) == 0
+    pair = pq.refpq_pair_new(ctrl.mm_ptr, 1, qs, qd.vaddr + PAGE, q_io[1], qs, qd.vaddr, q_io[0], 1)
+    assert pair
+    rng = np.random.default_rng(3)
+    pages = rng.integers(0, n_media_pages, n_req, dtype=np.uint64)
+    lbas = np.ascontiguousarray(pages * np.uint64(8))
+    prps = np.ascontiguousarray(np.array(b_io[:n_req], dtype=np.uint64))
+    data = np.frombuffer((C.c_uint8 * (n_req * PAGE)).from_address(bd.vaddr), dtype=np.uint64).reshape(n_req, 512)
+    # 3000 random page reads by 16 threads through a 64-entry queue pair: dozens of wraps, batched doorbells
+    assert pq.refpq_run(pair, 16, 2, lbas.ctypes.data, prps.ctypes.data, 8, n_req, 30000) == 0, "the protocol stalled"
+    assert (data == media.reshape(-1, 512)[pages.astype(np.int64)]).all()
+    sq_head, sq_tail, cq_head, cq_tail, in_ticket = (u32() for _ in range(5))
+    pq.refpq_state(pair, *(C.byref(x) for x in (sq_head, sq_tail, cq_head, cq_tail, in_ticket)))
+    # the reference's own view afterwards: every ticket was published, every completion consumed, SQ head caught up
+    assert in_ticket.value == n_req and sq_tail.value == n_req and cq_head.value == n_req
+    assert sq_head.value == n_req
+    # writes: distinct target pages, then read them back through the same code
+    targets = rng.permutation(n_media_pages)[:n_req].astype(np.uint64)
+    data[:] = orc.fill_store(seed + 5, 0, n_req * 512).reshape(n_req, 512)
+    want = data.copy()
+    wl = np.ascontiguousarray(targets * np.uint64(8))
+    assert pq.refpq_run(pair, 16, 1, wl.ctypes.data, prps.ctypes.data, 8, n_req, 30000) == 0
+    assert (media.reshape(-1, 512)[targets.astype(np.int64)] == want).all()
+    data[:] = 0
+    assert pq.refpq_run(pair, 7, 2, wl.ctypes.data, prps.ctypes.data, 8, n_req, 30000) == 0
+    assert (data == want).all()
+    pq.refpq_pair_free(pair)
+    assert lib.nvm_admin_sq_delete(aq, my_sq.ctypes.data, my_cq.ctypes.data) == 0
+    assert lib.nvm_admin_cq_delete(aq, my_cq.ctypes.data) == 0
+    del data
+    lib.nvm_dma_unmap(buf); lib.nvm_dma_unmap(qmem)
+    lib.nvm_aq_destroy(aq)
+    lib.nvm_ctrl_free(nctrl)
+    emu.close()
+
+
 def test_device_command_encoding_equals_the_reference_builders(cuda, bam, orc):
     """The register-built command of the device submission paths, run in a kernel, against the reference's
     nvm_cmd_header / nvm_cmd_data_ptr / nvm_cmd_rw_blks."""

@@ -334,3 +334,40 @@ def test_command_encoding_against_the_reference_builders(orc, bam):
     assert ref.refw_page_align(4097, 4096) == 8192 and ref.refw_page_to_block(4096, 512, 3) == 24
     assert ref.refw_sizeof_queue() > 0
 
+
+def test_reference_parallel_queue_code_against_the_oracle_controller(orc):
+    """The reference's parallel queue protocol (get_cid, sq_enqueue, cq_poll, cq_dequeue, put_cid of
+    include/nvm_parallel_queue.h, compiled for host threads into oracle/_ref/libref_pq.so) runs against the
+    oracle's NVMe controller over bare queue memory: the controller the CPU baseline uses speaks the
+    protocol the reference's code expects."""
+    pq = orc.ref_pq()
+    if pq is None:
+        pytest.skip("the reference's queue code is not built (needs the reference project)")
+    L = orc.lib()
+    qs, n_pages, n_req, seed = 16, 512, 2000, 13
+    regs = np.zeros(0x2000, dtype=np.uint8)
+    qmem = np.zeros(3 * 4096, dtype=np.uint8)
+    base = (qmem.ctypes.data + 4095) // 4096 * 4096            # page 0: CQ, page 1: SQ
+    media = orc.fill_store(seed, 0, n_pages * 512)
+    bufs = np.zeros((n_req, 512), dtype=np.uint64)
+    ctrl = L.orc_wire_ctrl_start(base + 4096, base, regs.ctypes.data + 0x1000 + 8, regs.ctypes.data + 0x1000 + 12, qs, qs, 1,
+                                 media.ctypes.data, media.nbytes, 512)
+    assert ctrl
+    pair = pq.refpq_pair_new(regs.ctypes.data, 1, qs, base + 4096, base + 4096, qs, base, base, 1)
+    assert pair
+    rng = np.random.default_rng(1)
+    pages = rng.integers(0, n_pages, n_req, dtype=np.uint64)
+    lbas = np.ascontiguousarray(pages * np.uint64(8))
+    prps = np.ascontiguousarray(bufs.ctypes.data + np.arange(n_req, dtype=np.uint64) * np.uint64(4096))
+    try:
+        assert pq.refpq_run(pair, 6, 2, lbas.ctypes.data, prps.ctypes.data, 8, n_req, 60000) == 0, "the protocol stalled"
+        assert (bufs == media.reshape(-1, 512)[pages.astype(np.int64)]).all()
+        state = [C.c_uint32() for _ in range(5)]
+        pq.refpq_state(pair, *(C.byref(x) for x in state))
+        sq_head, sq_tail, cq_head, cq_tail, in_ticket = (x.value for x in state)
+        assert in_ticket == n_req and sq_tail == n_req and cq_head == n_req and sq_head == n_req
+    finally:
+        served = L.orc_wire_ctrl_stop(ctrl)
+    assert served == n_req
+    pq.refpq_pair_free(pair)
+
