@@ -60,6 +60,8 @@ SIGNATURES = {
     "bam_launch_array_read": (ci, [vp, u64, u64, vp, u64, vp, vp]),
     "bam_launch_array_write": (ci, [vp, u64, vp, u64, u64, vp]),
     "bam_launch_pattern_read": (ci, [vp, u32, u64, u64, u64, u64, vp, vp, vp]),
+    "bam_launch_bulk_io": (ci, [vp, u64, u64, u64, ci, vp]),
+    "bam_cache_copy": (ci, [vp, u64, vp, u64, ci, vp]),
     "bam_cache_flush": (ci, [vp, vp]),
     "bam_launch_page_scan": (ci, [vp, u64, vp, u64, vp, vp]),
     "bam_launch_bfs_level": (ci, [vp, vp, u64, u64, u64, u32, vp, vp, vp, vp, u64, vp]),

@@ -300,6 +300,32 @@ struct ArrayWriteWork {
     }
 };
 
+/* ---- bulk transfer between cache memory and the store (benchmarks/readwrite/main.cu:283-390) -------
+ * The reference's loader copies a chunk of a file into the cache's memory and lets a kernel issue one
+ * NVMe WRITE per cache page (sequential_access_kernel with WRITE, :93-130 there); reading back is the
+ * same with READ.  Request r moves cache slot first_slot + r <-> store page first_store_page + r. */
+struct BulkIoWork {
+    page_cache_d_t pc;
+    uint64_t n_pages, first_store_page, first_slot;
+    uint8_t opcode;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint32_t lane = threadIdx.x & 31u;
+        const uint64_t gid = (uint64_t)vb * blockDim.x + threadIdx.x;
+        const uint64_t nthr = (uint64_t)nvb * blockDim.x;
+        const uint32_t queue = (uint32_t)(gid >> 5);
+        for (uint64_t base = gid - lane; base < n_pages; base += nthr) {
+            const uint64_t r = base + lane;
+            const bool active = r < n_pages;
+            const uint32_t slot = (uint32_t)(first_slot + r);
+            const int rc = warp_io(0xffffffffu, active, pick_queue(pc, 0, queue), (first_store_page + r) * pc.n_blocks_per_page,
+                                   pc.n_blocks_per_page, active ? slot_bus_addr(pc, slot) : 0, active ? slot_prp2(pc, slot) : 0, opcode);
+            if (__any_sync(0xffffffffu, active && rc != BAM_OK)) break;
+        }
+    }
+};
+
 /* ---- access patterns through bam_ptr cursors (benchmarks/pattern/main.cu) ------------------------
  * The *_pc kernels of the reference's pattern benchmark: every thread owns a bam_ptr and sums the
  * elements it visits.  SEQUENTIAL (:131-146): element i goes to thread i mod T.  SEQUENTIAL_WARP
@@ -1094,6 +1120,30 @@ extern "C" int bam_launch_array_write(bam_array_t a, uint64_t n, const uint64_t*
     w.arr.d_ranges = static_cast<range_d_t<uint64_t>*>(a->d_range);
     w.n = n; w.idx = idx_dev; w.val_seed = val_seed; w.addend = addend;
     return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_bulk_io(bam_cache_t pc, uint64_t n_pages, uint64_t first_store_page, uint64_t first_slot, int write,
+                                  void* stream)
+{
+    if (!pc || n_pages == 0) return BAM_EINVAL;
+    bam_ctrl* c = pc->ctrl;
+    if (first_slot + n_pages > pc->d.n_slots) return BAM_EINVAL;
+    if ((first_store_page + n_pages) * pc->d.page_size > c->store_bytes) return BAM_EINVAL;
+    CK(cudaSetDevice(c->device));
+    BulkIoWork w;
+    w.pc = pc->d; w.n_pages = n_pages; w.first_store_page = first_store_page; w.first_slot = first_slot;
+    w.opcode = write ? NVM_IO_WRITE : NVM_IO_READ;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_cache_copy(bam_cache_t pc, uint64_t first_slot, void* host, uint64_t bytes, int to_cache, void* stream)
+{
+    if (!pc || !host || first_slot * pc->d.page_size + bytes > (uint64_t)pc->d.n_slots * pc->d.page_size) return BAM_EINVAL;
+    CK(cudaSetDevice(pc->ctrl->device));
+    uint8_t* dev = pc->d.base_addr + first_slot * pc->d.page_size;
+    if (to_cache) CK(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    else CK(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return BAM_OK;
 }
 
 extern "C" int bam_launch_pattern_read(bam_array_t a, uint32_t pattern, uint64_t n_elems, uint64_t n_warps, uint64_t n_pages_per_warp,

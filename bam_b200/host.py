@@ -7,6 +7,7 @@
 Device buffers are passed as integer device addresses (e.g. torch.Tensor.data_ptr()).
 """
 import ctypes as C
+import os
 
 from . import _lib
 from ._lib import CacheStats, StatusOut, check
@@ -178,6 +179,63 @@ class PageCache:
     def audit_noalloc(self, violations_out, stream=None):
         """Enqueue the allocation-free audit; the count lands in the device u64 `violations_out`."""
         check(self.lib.bam_cache_audit_noalloc(self.h, _ptr(violations_out), _ptr(stream)), "bam_cache_audit_noalloc")
+
+    def bulk_io(self, n_pages, first_store_page, first_slot=0, write=False, stream=None):
+        """One NVMe command per cache page between the cache's memory and the store."""
+        check(self.lib.bam_launch_bulk_io(self.h, n_pages, first_store_page, first_slot, int(write), _ptr(stream)),
+              "bam_launch_bulk_io")
+
+    def load_file(self, path, store_byte_offset=0, file_offset=0, n_bytes=None):
+        """Copy a file onto the store through the cache's memory and NVMe WRITE commands, a cache-full at a
+        time (the loader of benchmarks/readwrite/main.cu:283-316).  Returns the bytes written; the last
+        page is padded with zeros.  Leaves the cache invalidated."""
+        import numpy as np
+        import torch
+        ps = self.page_size
+        assert store_byte_offset % ps == 0
+        size = os.path.getsize(path) - file_offset if n_bytes is None else n_bytes
+        self.invalidate()
+        chunk_pages = self.n_pages
+        staging = torch.empty(chunk_pages * ps, dtype=torch.uint8).pin_memory()
+        done = 0
+        with open(path, "rb") as f:
+            f.seek(file_offset)
+            while done < size:
+                n = min(chunk_pages * ps, size - done)
+                buf = staging.numpy()
+                got = f.readinto(memoryview(buf)[:n])
+                assert got == n, "short read"
+                pages = (n + ps - 1) // ps
+                buf[n:pages * ps] = 0
+                check(self.lib.bam_cache_copy(self.h, 0, staging.data_ptr(), pages * ps, 1, None), "bam_cache_copy")
+                self.bulk_io(pages, (store_byte_offset + done) // ps, 0, write=True)
+                torch.cuda.synchronize()
+                self.ctrl.check_status()
+                done += n
+        self.invalidate()
+        return size
+
+    def dump_file(self, path, n_bytes, store_byte_offset=0):
+        """The way back: NVMe READ commands into the cache's memory, then out to a file."""
+        import torch
+        ps = self.page_size
+        assert store_byte_offset % ps == 0
+        self.invalidate()
+        chunk_pages = self.n_pages
+        staging = torch.empty(chunk_pages * ps, dtype=torch.uint8).pin_memory()
+        done = 0
+        with open(path, "wb") as f:
+            while done < n_bytes:
+                n = min(chunk_pages * ps, n_bytes - done)
+                pages = (n + ps - 1) // ps
+                self.bulk_io(pages, (store_byte_offset + done) // ps, 0, write=False)
+                check(self.lib.bam_cache_copy(self.h, 0, staging.data_ptr(), pages * ps, 0, None), "bam_cache_copy")
+                torch.cuda.synchronize()
+                self.ctrl.check_status()
+                f.write(memoryview(staging.numpy())[:n])
+                done += n
+        self.invalidate()
+        return n_bytes
 
     def block_read(self, n_reqs, pages=None, req_seed=0, crc_out=None, sum_out=None, stream=None, io_depth=1):
         check(self.lib.bam_launch_block_read_depth(self.h, n_reqs, _ptr(pages), req_seed, io_depth, _ptr(crc_out),

@@ -180,6 +180,15 @@ int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t reqs_per_lan
 int bam_launch_array_write(bam_array_t a, uint64_t n, const uint64_t* idx_dev, uint64_t val_seed, uint64_t addend,
                            void* stream);
 
+/* Bulk transfer between the cache's memory and the store, one NVMe command per cache page (the loader
+ * and the read-back of benchmarks/readwrite/main.cu:283-390): request r moves cache slot first_slot + r
+ * to (write != 0) or from store page first_store_page + r.  The cache's page table is not involved: use
+ * it on an invalidated cache.  bam_cache_copy moves bytes between host memory and the cache's memory
+ * (slot first_slot onwards) on `stream`, which is how a file gets there. */
+int bam_launch_bulk_io(bam_cache_t pc, uint64_t n_pages, uint64_t first_store_page, uint64_t first_slot, int write,
+                       void* stream);
+int bam_cache_copy(bam_cache_t pc, uint64_t first_slot, void* host, uint64_t bytes, int to_cache, void* stream);
+
 /* Pattern benchmark (benchmarks/pattern/main.cu, the *_pc kernels): every thread sums the elements
  * it visits through a bam_ptr cursor; *sum_out_dev (device u64) is incremented by the wrapping sum.
  * pattern 0 SEQUENTIAL (:131-146): elements [0, n_elems) dealt round-robin to the threads;

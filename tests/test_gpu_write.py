@@ -67,3 +67,30 @@ def test_atomic_add_through_cache(cuda, bam, orc):
         np.add.at(want, idx.astype(np.int64), np.uint64(0x100000001))
     assert (ctrl.store_numpy() == want).all()
     arr.close(); cache.close(); ctrl.close()
+
+
+def test_file_round_trip_through_the_store(cuda, bam, orc, tmp_path):
+    """The reference's read-write check (benchmarks/readwrite/main.cu:392-468: file -> SSD -> file, compared
+    element by element): a file is loaded onto the store with NVMe WRITE commands, a cache-full at a time,
+    read back with NVMe READ commands and compared; the store holds it where it was put, a .bel graph
+    loaded this way traverses like the generated one."""
+    rng = np.random.default_rng(8)
+    blob = rng.integers(0, 256, 3 * 1024 * 1024 + 1234, dtype=np.uint8)         # ragged last page
+    src, back = tmp_path / "in.bin", tmp_path / "out.bin"
+    blob.tofile(src)
+    ctrl = bam.Controller(8 << 20, 0, queue_depth=64, num_queues=8)
+    ctrl.configure(spin_timeout_ns=5 * SEC)
+    ctrl.store_numpy()[:] = np.uint64(0x5555555555555555)
+    cache = bam.PageCache(ctrl, 4096, 200)                    # the file needs four cache-fulls
+    off = 1 << 20
+    assert cache.load_file(str(src), store_byte_offset=off) == blob.size
+    assert ctrl.status() == (0, "none", 0) and cache.audit() == 0
+    media = ctrl.store_numpy(dtype="uint8")
+    assert (media[off: off + blob.size] == blob).all()
+    assert (media[:off] == 0x55).all()                        # nothing before the target
+    pad_end = off + (blob.size + 4095) // 4096 * 4096
+    assert (media[off + blob.size: pad_end] == 0).all() and (media[pad_end:] == 0x55).all()
+    assert cache.dump_file(str(back), blob.size, store_byte_offset=off) == blob.size
+    assert (np.fromfile(back, dtype=np.uint8) == blob).all()
+    cache.close(); ctrl.close()
+
