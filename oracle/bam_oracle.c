@@ -4,13 +4,14 @@
  * Nothing the library ships may call into this file: it is the checker (tests, smoke) and
  * the timed host-core baseline (bench), never a fallback for the CUDA path.
  *
- * PARITY UNPINNED BY THE REFERENCE: the reference repository has no test-suite, no golden
- * vectors and no fixtures for this path, its device headers do not compile for a host, and
- * its host library needs /dev/libnvm* (kernel module + raw SSD).  The oracle is therefore a
- * restatement, pinned by (a) published known-answer vectors of the generators it shares with
- * the device code (SplitMix64, PCG32, CRC-32), (b) independent numpy/zlib/scipy
- * re-computations in the test-suite and (c), for the command encoding only, the reference's
- * own builders compiled from its sources (ref_wire.cpp, Makefile target `ref`).
+ * HOW IT IS PINNED.  The reference repository has no test-suite, golden vectors or fixtures for this
+ * path.  The restatement below is pinned by (a) published known-answer vectors of the generators it
+ * shares with the device code (SplitMix64, PCG32, CRC-32), (b) independent numpy / zlib / scipy
+ * re-computations, and (c) the reference's OWN code for this path, compiled for the host from its
+ * sources where they lie (Makefile target `ref`, glue in ref_wire.cpp / ref_pq.cpp / ref_cache.cpp) and
+ * run beside it in the test-suite: command encoding byte for byte, its parallel queue code against the
+ * controller below, its cache + array read path against ref_array_read on the same access lists (same
+ * checksum, hits, misses and page reads).
  *
  * Two layers:
  *   1. Result oracle (orc_*): pure functions of the seeded inputs -- wrapping 64-bit sums,

@@ -29,6 +29,7 @@ def build(force=False):
 
 REF_WIRE_PATH = os.path.join(HERE, "_ref", "libref_wire.so")
 REF_PQ_PATH = os.path.join(HERE, "_ref", "libref_pq.so")
+REF_CACHE_PATH = os.path.join(HERE, "_ref", "libref_cache.so")
 REFERENCE_ROOT = "/root/reference"
 
 
@@ -37,8 +38,9 @@ def build_ref_wire(force=False):
     they lie) into oracle/_ref/libref_wire.so.  Needs the reference project; returns None without it and
     without a prebuilt library."""
     if os.path.isdir(os.path.join(REFERENCE_ROOT, "include")):
-        srcs = [os.path.join(HERE, "ref_wire.cpp"), os.path.join(HERE, "ref_pq.cpp"), os.path.join(HERE, "ref_shim", "simt", "atomic")]
-        built = [REF_WIRE_PATH, REF_PQ_PATH]
+        srcs = [os.path.join(HERE, f) for f in ("ref_wire.cpp", "ref_pq.cpp", "ref_cache.cpp", "Makefile")]
+        srcs.append(os.path.join(HERE, "ref_shim", "simt", "atomic"))
+        built = [REF_WIRE_PATH, REF_PQ_PATH, REF_CACHE_PATH]
         if force or not all(map(os.path.exists, built)) or min(map(os.path.getmtime, built)) < max(map(os.path.getmtime, srcs)):
             subprocess.run(["make", "-C", HERE, "-B", "ref", "REFERENCE=" + REFERENCE_ROOT], check=True, capture_output=True)
     return REF_WIRE_PATH if os.path.exists(REF_WIRE_PATH) else None
@@ -98,6 +100,70 @@ def ref_pq():
         L.refpq_state.argtypes = [vp] + [C.POINTER(u32)] * 5
         _ref_pq = L
     return _ref_pq
+
+
+class RefCacheStats(C.Structure):
+    _fields_ = [("checksum", u64), ("accesses", u64), ("misses", u64), ("hits", u64), ("read_ios", u64), ("extra_reads", u64)]
+
+
+_ref_cache = None
+
+
+def ref_cache():
+    """ctypes handle of the reference's page cache + array read path compiled for host threads, or None."""
+    global _ref_cache
+    if _ref_cache is None:
+        build_ref_wire()
+        if not os.path.exists(REF_CACHE_PATH):
+            return None
+        L = C.CDLL(REF_CACHE_PATH)
+        L.refc_new.restype = vp
+        L.refc_new.argtypes = [vp, u32, u32, C.POINTER(vp), C.POINTER(vp), u32, u64, u64, u32]
+        L.refc_free.argtypes = [vp]
+        L.refc_array_read.argtypes = [vp, vp, u64, u32, u64, C.POINTER(RefCacheStats)]
+        L.refc_page_state.restype = u32
+        L.refc_page_state.argtypes = [vp, u64]
+        L.refc_page_slot.restype = u32
+        L.refc_page_slot.argtypes = [vp, u64]
+        _ref_cache = L
+    return _ref_cache
+
+
+class RefCacheWorld:
+    """The reference's array read path (host build) over queue pairs served by the oracle's controller:
+    `store` (numpy uint64) is the namespace; reads go through a cache of n_slots pages."""
+
+    def __init__(self, store, n_slots, n_qps=2, qs=16, page_size=4096, lba_bytes=512):
+        self.L, self.O = ref_cache(), lib()
+        self.store = store
+        self.regs = np.zeros(0x2000, dtype=np.uint8)
+        self.qmem = np.zeros((2 * n_qps + 1) * 4096, dtype=np.uint8)
+        base = (self.qmem.ctypes.data + 4095) // 4096 * 4096
+        sq = (vp * n_qps)(*[base + (2 * q + 1) * 4096 for q in range(n_qps)])
+        cq = (vp * n_qps)(*[base + (2 * q) * 4096 for q in range(n_qps)])
+        assert qs * 64 <= 4096
+        self.ctrls = [self.O.orc_wire_ctrl_start(sq[q], cq[q], self.regs.ctypes.data + 0x1000 + 8 * (q + 1),
+                                                 self.regs.ctypes.data + 0x1000 + 8 * (q + 1) + 4, qs, qs, q + 1,
+                                                 store.ctypes.data, store.nbytes, lba_bytes) for q in range(n_qps)]
+        self.h = self.L.refc_new(self.regs.ctypes.data, n_qps, qs, sq, cq, page_size, n_slots, store.nbytes // page_size, lba_bytes)
+        assert self.h and all(self.ctrls)
+
+    def read(self, idx, n_threads=1, timeout_ms=60000):
+        idx = np.ascontiguousarray(idx, dtype=np.uint64)
+        st = RefCacheStats()
+        rc = self.L.refc_array_read(self.h, idx.ctypes.data, len(idx), n_threads, timeout_ms, C.byref(st))
+        if rc:
+            raise RuntimeError(f"the reference's read path stalled ({rc})")
+        return st
+
+    def page_state(self, page):
+        return self.L.refc_page_state(self.h, page), self.L.refc_page_slot(self.h, page)
+
+    def close(self):
+        served = [self.O.orc_wire_ctrl_stop(c) for c in self.ctrls]
+        self.L.refc_free(self.h)
+        self.ctrls, self.h = [], None
+        return served
 
 
 def encode_rw(cid, opcode, ns_id, prp1, prp2, start_lba, n_blocks):

@@ -371,3 +371,53 @@ def test_reference_parallel_queue_code_against_the_oracle_controller(orc):
     assert served == n_req
     pq.refpq_pair_free(pair)
 
+
+@pytest.mark.parametrize("n_slots,n_qps,qs", [(8, 1, 4), (32, 2, 16), (300, 2, 64)])
+def test_restated_cache_against_the_reference_cache_code(orc, n_slots, n_qps, qs):
+    """The reference's own array read path -- array_d_t::seq_read, coalesce_page, acquire_page, find_slot,
+    read_data, over its parallel queues (include/page_cache.h and nvm_parallel_queue.h compiled for host
+    threads into oracle/_ref/libref_cache.so) -- and the restatement in bam_oracle.c read the same access
+    list through a cache with constant eviction: same checksum, and -- one thread, so the clock sweep is
+    deterministic -- the same hits, misses and page reads."""
+    if orc.ref_cache() is None:
+        pytest.skip("the reference's cache code is not built (needs the reference project)")
+    n_pages, seed = 256, 5
+    store = orc.fill_store(seed, 0, n_pages * 512)
+    rng = np.random.default_rng(n_slots)
+    # a skewed list: a hot set that fits, a cold tail that evicts
+    hot = rng.integers(0, 6 * 512, 3000, dtype=np.uint64)
+    cold = rng.integers(0, n_pages * 512, 3000, dtype=np.uint64)
+    idx = np.where(rng.random(3000) < 0.5, hot, cold).astype(np.uint64)
+    world = orc.RefCacheWorld(store, n_slots=n_slots, n_qps=n_qps, qs=qs)
+    try:
+        ref = world.read(idx, n_threads=1)
+    finally:
+        served = world.close()
+    port = orc.ref_array_read(store, 4096, n_slots, n_qps, qs, 512, 1, 1, idx=idx, lane_begin=0, lane_end=len(idx), reqs_per_lane=1)
+    want = orc.indexed_checksum(seed, 0, idx)
+    assert ref.checksum == want == port.checksum
+    assert (ref.accesses, ref.hits, ref.misses, ref.read_ios) == (port.accesses, port.hits, port.misses, port.read_ios)
+    assert ref.accesses == len(idx) and ref.hits + ref.misses == len(idx) and ref.read_ios == ref.misses
+    assert 0 < ref.hits < len(idx)
+    # the reference follows every page read with a second one-block read (enqueue_second, page_cache.h:1961-2007),
+    # which neither the restatement nor the library issue: its controller served both
+    assert ref.extra_reads == ref.misses and sum(served) == ref.read_ios + ref.extra_reads
+
+
+def test_reference_cache_code_with_concurrent_threads(orc):
+    """Six host threads share the reference's cache and queue pairs (races on pages, slots and queue slots
+    are real): the sum of everything read still equals the result oracle, and the counters add up."""
+    if orc.ref_cache() is None:
+        pytest.skip("the reference's cache code is not built (needs the reference project)")
+    n_pages, seed = 512, 9
+    store = orc.fill_store(seed, 0, n_pages * 512)
+    idx = np.random.default_rng(4).integers(0, n_pages * 512, 20000, dtype=np.uint64)
+    world = orc.RefCacheWorld(store, n_slots=64, n_qps=3, qs=16)
+    try:
+        ref = world.read(idx, n_threads=6)
+    finally:
+        served = world.close()
+    assert ref.checksum == orc.indexed_checksum(seed, 0, idx)
+    assert ref.accesses == len(idx) and ref.hits + ref.misses == len(idx) and ref.read_ios == ref.misses
+    assert all(s > 0 for s in served)                       # thread number mod 3 picks the queue pair, as smid does
+
