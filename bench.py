@@ -137,6 +137,31 @@ def cpu_reference_step(orc, n_local_pages, first_page, cache_pages, queues, dept
     return r
 
 
+def cpu_reference_code_step(orc, n_local_pages, first_page, cache_slots, n_qps, depth, lanes, reqs, access_seed, workers, store, cdf):
+    """The same bounded sample through the REFERENCE'S OWN cache and queue code (include/page_cache.h and
+    include/nvm_parallel_queue.h compiled for host threads, oracle/_ref/libref_cache.so), each queue pair served
+    by one controller thread of the oracle.  Returns (stats, seconds)."""
+    idx = orc.zipf_indices(cdf, n_local_pages, EPP, PERM_SEED, access_seed, 0, lanes, reqs)
+    fill_touched_pages(orc, store, first_page * EPP, idx)
+    world = orc.RefCacheWorld(store, n_slots=cache_slots, n_qps=n_qps, qs=min(depth, 64))
+    try:
+        t0 = time.time()
+        st = world.read(idx, n_threads=workers, timeout_ms=600000)
+        dt = time.time() - t0
+    finally:
+        world.close()
+    if st.checksum != orc.indexed_checksum(STORE_SEED, first_page * EPP, idx):
+        raise RuntimeError("reference code checksum mismatch")
+    return st, dt
+
+
+def reference_code_available(orc):
+    try:
+        return orc.ref_cache() is not None
+    except Exception:
+        return False
+
+
 def run_reference(args, rank, world):
     """--impl reference: the reference's own algorithm for this path restated for host threads
     (the reference cannot be built to run here: its host library needs /dev/libnvm* and its
@@ -156,22 +181,33 @@ def run_reference(args, rank, world):
     # shrink the in-memory cache of the sample to what the sample can touch
     cache_slots = min(cache_pages, lanes * args.reqs)
     times, ios, acc = [], 0, 0
+    use_ref_code = reference_code_available(orc)
     for s in range(args.warmup + args.steps):
-        r = cpu_reference_step(orc, n_local, 0, cache_slots, min(args.queues, 128), args.depth, lanes, args.reqs,
-                               ACCESS_SEED + 1000 + s, workers, ctrl_threads, store, cdf)
-        if s >= args.warmup:
-            times.append(r.seconds); ios += r.read_ios; acc += r.accesses
+        if use_ref_code:
+            st, dt = cpu_reference_code_step(orc, n_local, 0, cache_slots, ctrl_threads, args.depth, lanes, args.reqs,
+                                             ACCESS_SEED + 1000 + s, workers, store, cdf)
+            if s >= args.warmup:
+                times.append(dt); ios += st.read_ios; acc += st.accesses
+        else:
+            r = cpu_reference_step(orc, n_local, 0, cache_slots, min(args.queues, 128), args.depth, lanes, args.reqs,
+                                   ACCESS_SEED + 1000 + s, workers, ctrl_threads, store, cdf)
+            if s >= args.warmup:
+                times.append(r.seconds); ios += r.read_ios; acc += r.accesses
     t = sum(times)
     value = ios / t
     sample = (f"{lanes} lanes x {args.reqs} reads per step of the same Zipf(0.99) stream over one {n_local}-page shard, "
-              f"cold cache of {cache_slots} slots each step, {workers} reader threads + {ctrl_threads} controller threads")
+              f"cold cache of {cache_slots} slots each step, {workers} reader threads + {ctrl_threads} controller threads; "
+              + ("the reference's own page cache and queue code compiled for host threads (oracle/_ref), "
+                 f"{ctrl_threads} queue pairs of depth {min(args.depth, 64)}" if use_ref_code
+                 else "CPU restatement of the reference's protocol"))
     line = {
         "impl": "reference", "metric": "4KB-page IOPS via page cache", "value": value, "unit": "IOPS",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / max(1, args.steps),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
         "config": workload_config(args, world),
         "gb_per_s": value * PAGE / 1e9, "accesses_per_s": acc / t,
-        "cpu_baseline": {"value": value, "unit": "IOPS", "cores": workers + ctrl_threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "IOPS", "cores": workers + ctrl_threads, "kind": "reference" if use_ref_code else "port",
+                         "sample": sample},
         "e2e": {"value": value, "unit": "IOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -832,14 +868,23 @@ def main():
                 store = np.empty(n_local * EPP, dtype=np.uint64)
                 slots = min(cache_pages, cl * reqs)
                 t_cpu, ios_cpu = 0.0, 0
+                use_ref_code = reference_code_available(orc)
                 for s in range(3):
-                    r = cpu_reference_step(orc, n_local, first_page, slots, min(args.queues, 128), args.depth, cl, reqs,
-                                           ACCESS_SEED + 5000 + s, workers, ctrl_threads, store, cdf)
-                    t_cpu += r.seconds; ios_cpu += r.read_ios
+                    if use_ref_code:
+                        stc, dt = cpu_reference_code_step(orc, n_local, first_page, slots, ctrl_threads, args.depth, cl, reqs,
+                                                          ACCESS_SEED + 5000 + s, workers, store, cdf)
+                        t_cpu += dt; ios_cpu += stc.read_ios
+                    else:
+                        r = cpu_reference_step(orc, n_local, first_page, slots, min(args.queues, 128), args.depth, cl, reqs,
+                                               ACCESS_SEED + 5000 + s, workers, ctrl_threads, store, cdf)
+                        t_cpu += r.seconds; ios_cpu += r.read_ios
                 line["cpu_baseline"] = {
-                    "value": ios_cpu / t_cpu, "unit": "IOPS", "cores": workers + ctrl_threads, "kind": "port",
+                    "value": ios_cpu / t_cpu, "unit": "IOPS", "cores": workers + ctrl_threads,
+                    "kind": "reference" if use_ref_code else "port",
                     "sample": f"3 x ({cl} lanes x {reqs} reads) of the same Zipf stream, cold {slots}-slot cache, "
-                              f"{workers} reader + {ctrl_threads} controller threads"}
+                              f"{workers} reader + {ctrl_threads} controller threads"
+                              + ("; the reference's own page cache and queue code compiled for host threads (oracle/_ref)"
+                                 if use_ref_code else "; CPU restatement of the reference's protocol")}
             except Exception as e:  # the baseline is reported, never required
                 line["cpu_baseline"] = {"value": None, "unit": "IOPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
         print(json.dumps(line), flush=True)
