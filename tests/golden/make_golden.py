@@ -2,7 +2,8 @@
 
 The reference repository has no golden vectors for this path (no test-suite at all), and
 neither its host library nor its kernels can run without /dev/libnvm* and a raw SSD, so these
-fixtures come from the oracle, which is itself pinned by published known-answer vectors
+fixtures come from the oracle, which is itself pinned by published known-answer vectors, by
+independent numpy / scipy re-computations and by the reference's own code compiled for the host
 (see tests/test_oracle.py).  Run from the repository root:  python tests/golden/make_golden.py
 """
 import hashlib
