@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 
 #include <cerrno>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <ctime>
@@ -24,6 +25,7 @@
 
 #define NVM_HOST_MAX_QUEUES 64                 /* host-driven queue pairs per handle            */
 #define NVM_HOST_SERVICE_BLOCKS 2              /* command-processor blocks of the service kernel */
+#define NVM_HOST_MAX_WINDOWS 256               /* DMA mappings whose memory commands may name      */
 
 namespace {
 
@@ -39,6 +41,7 @@ struct host_ctrl {
     nvm_ctrl_t pub;                             /* must stay the first member: handles are cast back */
     bam_ctrl* emu = nullptr;
     std::mutex lock;
+    uint8_t* regs_raw = nullptr;                /* the allocation the register window lies in        */
     uint8_t* regs_host = nullptr;               /* register window                                   */
     uint8_t* regs_dev = nullptr;
     uint32_t* stop_host = nullptr;              /* 1 while the service should run (inside the window) */
@@ -55,6 +58,9 @@ struct host_ctrl {
     cudaStream_t stream = nullptr;
     bool running = false;
     uint16_t granted_cqs = NVM_HOST_MAX_QUEUES, granted_sqs = NVM_HOST_MAX_QUEUES;
+    bam_dma_window_t windows[NVM_HOST_MAX_WINDOWS];
+    uint32_t n_windows = 0;
+    bam_dma_window_t* d_windows = nullptr;
 };
 
 struct nvm_dma_box { host_dma priv; nvm_dma_t pub; };
@@ -106,6 +112,28 @@ int start_service_locked(host_ctrl* h)
     emu.batch = 32; emu.sys_scope = 1;
     emu.consumers_remaining = reinterpret_cast<uint32_t*>(h->regs_dev + (reinterpret_cast<uint8_t*>(h->stop_host) - h->regs_host));
     emu.status = h->d_status;
+    /* the data pointers of host-submitted commands are checked against the memory mapped for DMA */
+    if (cudaMemcpy(h->d_windows, h->windows, sizeof(bam_dma_window_t) * NVM_HOST_MAX_WINDOWS, cudaMemcpyHostToDevice) != cudaSuccess) return EIO;
+    emu.windows = h->d_windows; emu.n_windows = h->n_windows;
+    if (getenv("BAM_NVM_DEBUG")) {
+        auto show = [](const char* what, const void* p) {
+            cudaPointerAttributes a;
+            cudaError_t e = cudaPointerGetAttributes(&a, p);
+            fprintf(stderr, "[nvm] %-22s %p  type %d (err %d) dev %p host %p\n", what, p, e == cudaSuccess ? (int)a.type : -1, (int)e,
+                    e == cudaSuccess ? a.devicePointer : nullptr, e == cudaSuccess ? a.hostPointer : nullptr);
+            (void)cudaGetLastError();
+        };
+        show("qps table", emu.qps); show("status", emu.status); show("stop flag", emu.consumers_remaining); show("windows", emu.windows);
+        for (uint32_t q = 0; q < h->n_qps; q++) {
+            const bam_emu_qp_t& e = h->h_qps[q];
+            show("sq_mem", e.sq_mem); show("cq_mem", e.cq_mem); show("sq_db", e.sq_db); show("cq_db", e.cq_db);
+            show("store", e.store); show("fault", e.fault); show("served", e.served);
+            fprintf(stderr, "[nvm] qp %u: qs %u cq_qs %u sqid %u cqid %u store_bytes %llu fetch %u cq_tail %u\n", q, e.qs, e.cq_qs, e.sqid, e.cqid,
+                    (unsigned long long)e.store_bytes, e.sq_fetch, e.cq_tail);
+        }
+        for (uint32_t k = 0; k < h->n_windows; k++)
+            fprintf(stderr, "[nvm] window %u: %p + %llu\n", k, (void*)(uintptr_t)h->windows[k].base, (unsigned long long)h->windows[k].bytes);
+    }
     if (cudaFuncSetAttribute(k_nvm_host_service, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BAM_EMU_SMEM_BYTES) != cudaSuccess) return EIO;
     k_nvm_host_service<<<NVM_HOST_SERVICE_BLOCKS, BAM_THREADS, BAM_EMU_SMEM_BYTES, h->stream>>>(emu);
     if (cudaGetLastError() != cudaSuccess) return EIO;
@@ -162,18 +190,22 @@ extern "C" int nvm_emu_ctrl_init(nvm_ctrl_t** ctrl, bam_ctrl_t emu)
     h->pub.timeout = 5000;
     h->pub.max_qs = 1024;
     h->pub.mm_size = 0x2000;
-    cudaError_t e = cudaHostAlloc((void**)&h->regs_host, h->pub.mm_size, cudaHostAllocMapped | cudaHostAllocPortable);
-    if (e == cudaSuccess) e = cudaHostGetDevicePointer((void**)&h->regs_dev, h->regs_host, 0);
+    cudaError_t e = cudaHostAlloc((void**)&h->regs_raw, h->pub.mm_size + 4096, cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e == cudaSuccess) {
+        h->regs_host = reinterpret_cast<uint8_t*>(((uintptr_t)h->regs_raw + 4095) / 4096 * 4096);     /* a register window starts on a page */
+        e = cudaHostGetDevicePointer((void**)&h->regs_dev, h->regs_host, 0);
+    }
     if (e == cudaSuccess) e = cudaMalloc(&h->d_qps, sizeof(bam_emu_qp_t) * NVM_HOST_MAX_QUEUES);
     if (e == cudaSuccess) e = cudaMalloc(&h->d_status, sizeof(bam_status_t));
     if (e == cudaSuccess) e = cudaMalloc(&h->d_fault, sizeof(bam_fault_t));
     if (e == cudaSuccess) e = cudaMalloc(&h->d_served, 8);
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_windows, sizeof(bam_dma_window_t) * NVM_HOST_MAX_WINDOWS);
     if (e == cudaSuccess) e = cudaMemset(h->d_fault, 0, sizeof(bam_fault_t));
     if (e == cudaSuccess) e = cudaMemset(h->d_served, 0, 8);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
-        cudaFreeHost(h->regs_host); cudaFree(h->d_qps); cudaFree(h->d_status); cudaFree(h->d_fault); cudaFree(h->d_served);
+        cudaFreeHost(h->regs_raw); cudaFree(h->d_qps); cudaFree(h->d_status); cudaFree(h->d_fault); cudaFree(h->d_served); cudaFree(h->d_windows);
         delete h;
         return ENOMEM;
     }
@@ -195,7 +227,7 @@ extern "C" void nvm_ctrl_free(nvm_ctrl_t* ctrl)
         stop_service_locked(h);
     }
     cudaStreamDestroy(h->stream);
-    cudaFreeHost(h->regs_host); cudaFree(h->d_qps); cudaFree(h->d_status); cudaFree(h->d_fault); cudaFree(h->d_served);
+    cudaFreeHost(h->regs_raw); cudaFree(h->d_qps); cudaFree(h->d_status); cudaFree(h->d_fault); cudaFree(h->d_served); cudaFree(h->d_windows);
     delete h;
 }
 
@@ -216,6 +248,35 @@ extern "C" int nvm_emu_service_stop(const nvm_ctrl_t* ctrl)
     return stop_service_locked(h);
 }
 
+extern "C" int nvm_emu_service_status(const nvm_ctrl_t* ctrl, uint32_t* running, uint32_t* code, uint32_t* where, uint64_t* served)
+{
+    if (!ctrl) return EINVAL;
+    host_ctrl* h = of(ctrl);
+    std::lock_guard<std::mutex> g(h->lock);
+    if (cudaSetDevice(h->emu->device) != cudaSuccess) return EIO;
+    /* has the kernel left on its own (time limit, recorded error) or failed? */
+    if (h->running) {
+        const cudaError_t q = cudaStreamQuery(h->stream);
+        if (q == cudaSuccess) h->running = false;
+        else if (q != cudaErrorNotReady) { (void)cudaGetLastError(); h->running = false; if (running) *running = 0; return 1000 + (int)q; }
+    }
+    if (running) *running = h->running ? 1u : 0u;
+    /* the service kernel may be running: read on a stream of our own, not on the legacy default stream */
+    bam_status_t st;
+    uint64_t n = 0;
+    cudaStream_t s = nullptr;
+    cudaError_t e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&st, h->d_status, sizeof st, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&n, h->d_served, 8, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (s) cudaStreamDestroy(s);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return 1000 + (int)e; }
+    if (code) *code = st.code;
+    if (where) *where = st.where;
+    if (served) *served = n;
+    return 0;
+}
+
 /* ---- DMA mappings ---------------------------------------------------------------------------------- */
 
 static int make_map(nvm_dma_t** map, void* vaddr, size_t page_size, size_t n_pages, uint64_t base, const uint64_t* ioaddrs,
@@ -230,6 +291,17 @@ static int make_map(nvm_dma_t** map, void* vaddr, size_t page_size, size_t n_pag
     box->pub.page_size = page_size;
     box->pub.n_ioaddrs = n_pages;
     for (size_t i = 0; i < n_pages; i++) box->pub.ioaddrs[i] = ioaddrs ? ioaddrs[i] : base + i * page_size;
+    /* commands may name this memory from now on (a mapping given as a list of pages counts page by page) */
+    host_ctrl* h = priv.owner;
+    if (h) {
+        const size_t n_w = ioaddrs ? n_pages : 1;
+        if (h->n_windows + n_w > NVM_HOST_MAX_WINDOWS) { free(box); return ENOSPC; }
+        for (size_t i = 0; i < n_w; i++) {
+            h->windows[h->n_windows].base = ioaddrs ? ioaddrs[i] : base;
+            h->windows[h->n_windows].bytes = ioaddrs ? page_size : n_pages * page_size;
+            h->n_windows++;
+        }
+    }
     *map = &box->pub;
     return 0;
 }
@@ -239,6 +311,7 @@ extern "C" int nvm_dma_map(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* vaddr,
     if (!map) return EINVAL;
     *map = nullptr;
     if (!ctrl || !ioaddrs || n_pages == 0 || page_size == 0) return EINVAL;
+    pause_guard pause(of(ctrl));                       /* the service picks the new windows up when it resumes */
     host_dma priv;
     priv.owner = of(ctrl);
     return make_map(map, vaddr, page_size, n_pages, 0, ioaddrs, priv, true);
@@ -276,6 +349,7 @@ extern "C" int nvm_dma_map_device(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void*
     if (((uintptr_t)devptr & (ps - 1)) != 0) return EINVAL;
     cudaPointerAttributes attr;
     if (cudaPointerGetAttributes(&attr, devptr) != cudaSuccess || attr.type != cudaMemoryTypeDevice) { (void)cudaGetLastError(); return EINVAL; }
+    pause_guard pause(of(ctrl));
     host_dma priv;
     priv.owner = of(ctrl);
     priv.device = true;
@@ -290,15 +364,18 @@ extern "C" int nvm_dma_create(nvm_dma_t** map, const nvm_ctrl_t* ctrl, size_t si
     const size_t ps = ctrl->page_size;
     size = (size + ps - 1) / ps * ps;
     pause_guard pause(of(ctrl));
-    void* p = nullptr;
-    if (cudaHostAlloc(&p, size, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) { (void)cudaGetLastError(); return ENOMEM; }
+    /* pinned allocations come with the allocator's own alignment (512 bytes for small ones), DMA memory is
+     * page-granular: allocate one page more and start at the first page boundary */
+    void* raw = nullptr;
+    if (cudaHostAlloc(&raw, size + ps, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) { (void)cudaGetLastError(); return ENOMEM; }
+    void* p = reinterpret_cast<void*>(((uintptr_t)raw + ps - 1) / ps * ps);
     memset(p, 0, size);
     host_dma priv;
     priv.owner = of(ctrl);
-    priv.allocated = p;
+    priv.allocated = raw;
     const uint64_t dev = device_address_of_host(p);
-    int rc = dev ? make_map(map, p, ps, size / ps, dev, nullptr, priv, true) : EFAULT;
-    if (rc) cudaFreeHost(p);
+    int rc = (dev && (dev & (ps - 1)) == 0) ? make_map(map, p, ps, size / ps, dev, nullptr, priv, true) : EFAULT;
+    if (rc) cudaFreeHost(raw);
     return rc;
 }
 
@@ -306,6 +383,14 @@ extern "C" void nvm_dma_unmap(nvm_dma_t* map)
 {
     if (!map) return;
     nvm_dma_box* box = reinterpret_cast<nvm_dma_box*>(reinterpret_cast<uint8_t*>(map) - offsetof(nvm_dma_box, pub));
+    if (box->priv.owner) {                               /* the memory may no longer be named by commands */
+        pause_guard pause(box->priv.owner);
+        host_ctrl* h = box->priv.owner;
+        for (size_t i = 0; i < map->n_ioaddrs; i++)
+            for (uint32_t k = 0; k < h->n_windows;) {
+                if (h->windows[k].base == map->ioaddrs[i]) { h->windows[k] = h->windows[--h->n_windows]; } else k++;
+            }
+    }
     if (box->priv.owner && (box->priv.registered || box->priv.allocated)) {
         pause_guard pause(box->priv.owner);
         if (box->priv.registered) cudaHostUnregister(box->priv.registered);

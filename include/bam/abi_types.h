@@ -240,7 +240,15 @@ typedef struct {
     uint32_t sys_scope;         /* 1: doorbells/completions use system scope, 0: device scope      */
     uint32_t* consumers_remaining;
     bam_status_t* status;
+    /* Memory that commands may name as their data pointers, for submitters the controller does not trust
+     * (host programs): a PRP outside every window completes with a data transfer error instead of being
+     * touched.  NULL = no check (the library's own kernels build their PRPs from cache slots). */
+    const struct bam_dma_window_s* windows;
+    uint32_t n_windows;
+    uint32_t pad_;
 } bam_emu_d_t;
+
+typedef struct bam_dma_window_s { uint64_t base, bytes; } bam_dma_window_t;
 
 /* ---- page cache -------------------------------------------------------------------------
  * Slot state word (32 bits, updated with CAS / fetch-ops):

@@ -35,6 +35,7 @@ namespace bam {
 #define BAM_SC_SUCCESS 0x00u
 #define BAM_SC_INVALID_OPCODE 0x01u
 #define BAM_SC_INVALID_FIELD 0x02u
+#define BAM_SC_DATA_XFER_ERROR 0x04u
 #define BAM_SC_LBA_OUT_OF_RANGE 0x80u
 
 #define BAM_EMU_STAGE_BYTES 4096
@@ -181,6 +182,12 @@ BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t
             len = m.bytes - done < mps ? m.bytes - done : (uint32_t)mps;
         }
         if (len > BAM_EMU_STAGE_BYTES) len = BAM_EMU_STAGE_BYTES;
+        if (c.windows) {                                   /* an untrusted submitter: is [mem, mem + len) memory it may name? */
+            bool ok = false;
+            for (uint32_t k = 0; k < c.n_windows && !ok; k++)
+                ok = mem >= c.windows[k].base && mem + len <= c.windows[k].base + c.windows[k].bytes && mem + len >= mem;
+            if (!ok) return BAM_SC_DATA_XFER_ERROR;
+        }
         uint8_t* media = store + m.media_off + done;
         const void* src = (m.opc == NVM_IO_READ) ? (const void*)media : (const void*)mem;
         void* dst = (m.opc == NVM_IO_READ) ? (void*)mem : (void*)media;

@@ -43,6 +43,10 @@ void nvm_ctrl_free(nvm_ctrl_t* ctrl);
 /* Start / stop the command processor that serves the host-driven queue pairs (see above). */
 int nvm_emu_service_start(const nvm_ctrl_t* ctrl);
 int nvm_emu_service_stop(const nvm_ctrl_t* ctrl);
+/* Whether the service kernel is (believed to be) running, the error state it recorded (BAM_E* code and
+ * BAM_AT_* place, 0 = none) and the number of commands it has completed.  Returns 0, or 1000 + the CUDA
+ * error when the kernel or the query failed. */
+int nvm_emu_service_status(const nvm_ctrl_t* ctrl, uint32_t* running, uint32_t* code, uint32_t* where, uint64_t* served);
 
 /* ---- DMA mappings (nvm_types.h:52-66, nvm_dma.h) ------------------------------------------------ */
 typedef struct {

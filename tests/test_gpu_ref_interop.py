@@ -72,6 +72,13 @@ def test_reference_host_queue_code_drives_the_emulated_controller(cuda, bam, orc
 
     cid, sqhd, sqid, sct, sc, packed = u16(), u16(), u16(), u8(), u8(), C.c_int()
 
+    def service_state():
+        run, code, where, served = u32(), u32(), u32(), u64()
+        lib.nvm_emu_service_status.argtypes = [vp] + [vp] * 4
+        rc = lib.nvm_emu_service_status(nctrl, C.byref(run), C.byref(code), C.byref(where), C.byref(served))
+        sq_db = u32.from_address(ctrl.mm_ptr + 0x1008).value
+        return f"service: rc {rc} running {run.value} code {code.value} where {where.value} served {served.value}, SQ doorbell {sq_db}"
+
     def transfer(opcode, first_media_page, n):
         sent = done = 0
         seen = []
@@ -80,7 +87,7 @@ def test_reference_host_queue_code_drives_the_emulated_controller(cuda, bam, orc
                 sent += 1
             ref.refw_sq_submit(rsq)
             assert ref.refw_cq_take(rcq, rsq, 5000, C.byref(cid), C.byref(sqhd), C.byref(sqid), C.byref(sct), C.byref(sc),
-                                    C.byref(packed)) == 0, "the controller did not answer"
+                                    C.byref(packed)) == 0, "the controller did not answer; " + service_state()
             assert (sqid.value, sct.value, sc.value, packed.value) == (1, 0, 0, 0) and sqhd.value < 64
             seen.append(cid.value)
             done += 1
@@ -105,6 +112,16 @@ def test_reference_host_queue_code_drives_the_emulated_controller(cuda, bam, orc
     assert ref.refw_cq_take(rcq, rsq, 5000, C.byref(cid), C.byref(sqhd), C.byref(sqid), C.byref(sct), C.byref(sc), C.byref(packed)) == 0
     assert (cid.value, sct.value, sc.value, packed.value) == (7, 0, 0x80, -0x80)
     assert b"range" in ref.refw_strerror(packed.value).lower()
+    # a data pointer outside every DMA mapping is refused (data transfer error), not followed
+    assert ref.refw_sq_put_rw(rsq, 8, 2, 1, 0x10000, 0, 0, 8) == 0
+    ref.refw_sq_submit(rsq)
+    assert ref.refw_cq_take(rcq, rsq, 5000, C.byref(cid), C.byref(sqhd), C.byref(sqid), C.byref(sct), C.byref(sc), C.byref(packed)) == 0
+    assert (cid.value, sct.value, sc.value) == (8, 0, 0x04)
+    # so is a page-crossing transfer whose second pointer is missing
+    assert ref.refw_sq_put_rw(rsq, 9, 2, 1, b_io[0] + 512, 0, 0, 8) == 0
+    ref.refw_sq_submit(rsq)
+    assert ref.refw_cq_take(rcq, rsq, 5000, C.byref(cid), C.byref(sqhd), C.byref(sqid), C.byref(sct), C.byref(sc), C.byref(packed)) == 0
+    assert (cid.value, sc.value) == (9, 0x04)
 
     ref.refw_queue_free(rsq); ref.refw_queue_free(rcq)
     assert lib.nvm_admin_sq_delete(aq, my_sq.ctypes.data, my_cq.ctypes.data) == 0
