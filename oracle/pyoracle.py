@@ -119,6 +119,8 @@ def ref_cache():
         L = C.CDLL(REF_CACHE_PATH)
         L.refc_new.restype = vp
         L.refc_new.argtypes = [vp, u32, u32, C.POINTER(vp), C.POINTER(vp), u32, u64, u64, u32]
+        L.refc_new2.restype = vp
+        L.refc_new2.argtypes = [vp, u32, u32, C.POINTER(vp), C.POINTER(vp), u32, u64, u64, u32, vp, u64]
         L.refc_free.argtypes = [vp]
         L.refc_array_read.argtypes = [vp, vp, u64, u32, u64, C.POINTER(RefCacheStats)]
         L.refc_page_state.restype = u32

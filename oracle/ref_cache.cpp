@@ -96,8 +96,19 @@ static void* zalloc(refc_world* w, size_t bytes, size_t align = 64)
 /* n_qps queue pairs of depth qs over caller memory (sq_mem[q], cq_mem[q]; doorbells in the register window
  * mm_ptr), a cache of n_slots pages of page_size bytes, one range of u64 elements over n_store_pages pages
  * of the namespace starting at page 0. */
+REFC_API void* refc_new2(void* mm_ptr, uint32_t n_qps, uint32_t qs, void* const* sq_mem, void* const* cq_mem, uint32_t page_size,
+                         uint64_t n_slots, uint64_t n_store_pages, uint32_t lba_bytes, void* cache_mem, uint64_t cache_bus_addr);
+
 REFC_API void* refc_new(void* mm_ptr, uint32_t n_qps, uint32_t qs, void* const* sq_mem, void* const* cq_mem, uint32_t page_size,
                         uint64_t n_slots, uint64_t n_store_pages, uint32_t lba_bytes)
+{
+    return refc_new2(mm_ptr, n_qps, qs, sq_mem, cq_mem, page_size, n_slots, n_store_pages, lba_bytes, nullptr, 0);
+}
+
+/* The same with the cache's memory supplied by the caller (cache_mem: n_slots pages; cache_bus_addr: the
+ * address a controller uses for it), for controllers that cannot reach ordinary host memory. */
+REFC_API void* refc_new2(void* mm_ptr, uint32_t n_qps, uint32_t qs, void* const* sq_mem, void* const* cq_mem, uint32_t page_size,
+                         uint64_t n_slots, uint64_t n_store_pages, uint32_t lba_bytes, void* cache_mem, uint64_t cache_bus_addr)
 {
     refc_world* w = static_cast<refc_world*>(calloc(1, sizeof(refc_world)));
     w->owned = static_cast<void**>(calloc(64 + 5 * n_qps, sizeof(void*)));
@@ -155,9 +166,10 @@ REFC_API void* refc_new(void* mm_ptr, uint32_t n_qps, uint32_t qs, void* const* 
     pc.q_tail = static_cast<a64*>(zalloc(w, sizeof(a64)));
     pc.q_lock = static_cast<a64*>(zalloc(w, sizeof(a64)));
     pc.extra_reads = static_cast<a64*>(zalloc(w, sizeof(a64)));
-    pc.base_addr = static_cast<uint8_t*>(zalloc(w, n_slots * (size_t)page_size, 4096));
+    pc.base_addr = cache_mem ? static_cast<uint8_t*>(cache_mem) : static_cast<uint8_t*>(zalloc(w, n_slots * (size_t)page_size, 4096));
+    const uint64_t bus0 = cache_mem ? cache_bus_addr : (uint64_t)(uintptr_t)pc.base_addr;          /* bus address == address here */
     pc.prp1 = static_cast<uint64_t*>(zalloc(w, n_slots * sizeof(uint64_t)));
-    for (uint64_t i = 0; i < n_slots; i++) pc.prp1[i] = (uint64_t)(uintptr_t)(pc.base_addr + i * page_size);   /* bus address == address */
+    for (uint64_t i = 0; i < n_slots; i++) pc.prp1[i] = bus0 + i * page_size;
     pc.prps = false;
     /* one range over the whole namespace: range_t's constructor and page_cache_t::add_range (:978-1030, :685-695) */
     range_d_t<uint64_t>* r = static_cast<range_d_t<uint64_t>*>(zalloc(w, sizeof(range_d_t<uint64_t>)));

@@ -203,6 +203,59 @@ def test_reference_parallel_queue_code_drives_the_emulated_controller(cuda, bam,
     emu.close()
 
 
+def test_reference_array_read_path_end_to_end_on_the_emulated_controller(cuda, bam, orc):
+    """The reference's whole read path -- array_d_t::seq_read, its page cache (acquire_page, find_slot with
+    evictions), read_data with enqueue_second, its parallel queues -- compiled for host threads
+    (oracle/_ref/libref_cache.so), with its cache memory and queue pairs in DMA-mapped host memory, served by
+    the emulated controller on the GPU: 8 threads, a cache a fraction of the data, the result oracle's sum."""
+    rc_lib = orc.ref_cache()
+    if rc_lib is None:
+        pytest.skip("the reference's cache code is not built (needs the reference project)")
+    lib = bam.load()
+    for name, args in (("nvm_emu_ctrl_init", [C.POINTER(vp), vp]), ("nvm_aq_create", [C.POINTER(vp), vp, vp]),
+                       ("nvm_dma_create", [C.POINTER(vp), vp, C.c_size_t]), ("nvm_admin_cq_create", [vp, vp, u16, vp, C.c_size_t, C.c_size_t]),
+                       ("nvm_admin_sq_create", [vp, vp, vp, u16, vp, C.c_size_t, C.c_size_t]), ("nvm_admin_sq_delete", [vp, vp, vp]),
+                       ("nvm_admin_cq_delete", [vp, vp])):
+        getattr(lib, name).argtypes = args
+        getattr(lib, name).restype = C.c_int
+    for name in ("nvm_dma_unmap", "nvm_aq_destroy", "nvm_ctrl_free"):
+        getattr(lib, name).argtypes = [vp]
+        getattr(lib, name).restype = None
+    n_media_pages, seed, n_qps, qs, n_slots = 2048, 57, 3, 16, 96
+    emu = bam.Controller(n_media_pages * PAGE, 0, queue_depth=64, num_queues=1)
+    emu.set_launch_timeout(60 * 1_000_000_000)
+    emu.store_numpy()[:] = orc.fill_store(seed, 0, n_media_pages * 512)
+    nctrl, aq, qmem, cmem = vp(), vp(), vp(), vp()
+    assert lib.nvm_emu_ctrl_init(C.byref(nctrl), emu.h) == 0
+    ctrl = NvmCtrl.from_address(nctrl.value)
+    assert lib.nvm_aq_create(C.byref(aq), nctrl, None) == 0
+    assert lib.nvm_dma_create(C.byref(qmem), nctrl, 2 * n_qps * PAGE) == 0
+    assert lib.nvm_dma_create(C.byref(cmem), nctrl, n_slots * PAGE) == 0          # the reference's cache lives in DMA memory
+    qd, cd = NvmDma.from_address(qmem.value), NvmDma.from_address(cmem.value)
+    q_io, c_io = ioaddrs(qmem, 2 * n_qps), ioaddrs(cmem, n_slots)
+    mine = [(np.zeros(4096, dtype=np.uint8), np.zeros(4096, dtype=np.uint8)) for _ in range(n_qps)]
+    for q, (my_cq, my_sq) in enumerate(mine):                                     # page 2q: CQ q+1, page 2q+1: SQ q+1
+        assert lib.nvm_admin_cq_create(aq, my_cq.ctypes.data, q + 1, qmem, 2 * q, qs) == 0
+        assert lib.nvm_admin_sq_create(aq, my_sq.ctypes.data, my_cq.ctypes.data, q + 1, qmem, 2 * q + 1, qs) == 0
+    sq = (vp * n_qps)(*[qd.vaddr + (2 * q + 1) * PAGE for q in range(n_qps)])
+    cq = (vp * n_qps)(*[qd.vaddr + (2 * q) * PAGE for q in range(n_qps)])
+    world = rc_lib.refc_new2(ctrl.mm_ptr, n_qps, qs, sq, cq, PAGE, n_slots, n_media_pages, 512, cd.vaddr, c_io[0])
+    assert world
+    idx = np.random.default_rng(6).integers(0, n_media_pages * 512, 12000, dtype=np.uint64)
+    st = orc.RefCacheStats()
+    assert rc_lib.refc_array_read(world, idx.ctypes.data, len(idx), 8, 60000, C.byref(st)) == 0, "the read path stalled"
+    assert st.checksum == orc.indexed_checksum(seed, 0, idx)
+    assert st.accesses == len(idx) and st.hits + st.misses == len(idx) and st.read_ios == st.misses and st.misses > n_slots
+    rc_lib.refc_free(world)
+    for my_cq, my_sq in mine:
+        assert lib.nvm_admin_sq_delete(aq, my_sq.ctypes.data, my_cq.ctypes.data) == 0
+        assert lib.nvm_admin_cq_delete(aq, my_cq.ctypes.data) == 0
+    lib.nvm_dma_unmap(cmem); lib.nvm_dma_unmap(qmem)
+    lib.nvm_aq_destroy(aq)
+    lib.nvm_ctrl_free(nctrl)
+    emu.close()
+
+
 def test_device_command_encoding_equals_the_reference_builders(cuda, bam, orc):
     """The register-built command of the device submission paths, run in a kernel, against the reference's
     nvm_cmd_header / nvm_cmd_data_ptr / nvm_cmd_rw_blks."""
