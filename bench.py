@@ -645,6 +645,32 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def measure_link(reps):
+        """Pinned-memory H2D copy rate of this rank while every rank copies: (per-GPU mean, aggregate) in GB/s."""
+        pin = torch.empty(1 << 30, dtype=torch.uint8).pin_memory()
+        dbuf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+        best = 0.0
+        for _ in range(reps):
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); dbuf.copy_(pin, non_blocking=True); b.record(stream); stream.synchronize()
+            best = max(best, (1 << 30) / (a.elapsed_time(b) * 1e-3) / 1e9)
+        del pin, dbuf
+        link = torch.tensor([best], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(link, op=dist.ReduceOp.SUM)
+        return float(link.item()) / world, float(link.item())
+
+    # Pages the controller keeps in flight (16 per controller block) are sized to the bandwidth-delay product of
+    # the link this rank really gets: GPUs that share a PCIe uplink see about half the bandwidth and twice the
+    # latency under load, and flooding the shared switch with a full-rate window of 4 KiB reads costs throughput
+    # (8 GPUs of one box: 48 blocks 45.2 M IOPS, 24 blocks 48.4 M).  48 blocks at 55 GB/s, in proportion below.
+    ctrl_blocks = args.ctrl_blocks
+    if ctrl_blocks == 0:
+        link_before, _ = measure_link(2)
+        ctrl_blocks = max(16, min(48, int(48.0 * link_before / 55.0 / 8.0 + 0.5) * 8))
+        ctrl.configure(ctrl_blocks=ctrl_blocks)
+
     def run_step(s):
         cache.invalidate_async(stream=sptr)
         arr.read(lanes, reqs, sums[s:s + 1], idx=d_idx[s], stream=sptr)
@@ -702,19 +728,7 @@ def main():
     # ---- host-link peak (pinned H2D copy) and warm hit-path pass (HBM roofline) ----------------
     # every rank copies at the same time: GPUs of one box share PCIe uplinks, so the per-GPU ceiling
     # under load is what the miss path of an N-rank run can be compared with
-    pin = torch.empty(1 << 30, dtype=torch.uint8).pin_memory()
-    dbuf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
-    best = 0.0
-    for _ in range(5):
-        barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(stream); dbuf.copy_(pin, non_blocking=True); b.record(stream); stream.synchronize()
-        best = max(best, (1 << 30) / (a.elapsed_time(b) * 1e-3) / 1e9)
-    del pin, dbuf
-    link = torch.tensor([best], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(link, op=dist.ReduceOp.SUM)
-    link_agg = float(link.item())
+    _, link_agg = measure_link(5)
     link_gbs, hit = link_agg / world, None
     if rank == 0:
         # warm pass: scan pages that are resident (scan the same list twice, time the second)
@@ -858,6 +872,9 @@ def main():
                                              "array[] (the reference's cache benchmark, 169 GiB/s in its published log)"},
             "clocks": clocks, "setup_s": setup_s, "numa_rank0": numa,
         }
+        line["config"]["controller_blocks"] = ctrl_blocks
+        line["config"]["controller_blocks_rule"] = ("given on the command line" if args.ctrl_blocks else
+                                                    "48 x (pinned-copy GB/s measured on all ranks at once) / 55, in steps of 8")
         if not args.no_cpu_baseline and world == 1:
             try:
                 from oracle import pyoracle as orc
