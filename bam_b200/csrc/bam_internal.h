@@ -58,6 +58,7 @@ struct bam_cache {
     bam_ctrl* ctrl = nullptr;         /* the (first) backing controller: launches run with its descriptor */
     std::vector<bam_ctrl*> members;   /* all backing controllers when there are several */
     bam_emu_qp_t* d_group_qps = nullptr;   /* controller-side state of all members' queues, contiguous */
+    void* prp_lists_raw = nullptr;    /* the allocation d.prp_lists (page-aligned) lies in */
     page_cache_d_t d;
     uint64_t n_buckets = 0;
     uint32_t n_ranges = 0;

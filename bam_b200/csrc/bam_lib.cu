@@ -820,7 +820,7 @@ static void cache_free_device(bam_cache* pc)
 {
     page_cache_d_t& d = pc->d;
     cudaFree(d.base_addr); cudaFree(d.slots); cudaFree(d.table); cudaFree(d.clock_hand);
-    cudaFree(d.stats); cudaFree(d.range_page_starts); cudaFree(d.range_dists); cudaFree(d.prp_lists);
+    cudaFree(d.stats); cudaFree(d.range_page_starts); cudaFree(d.range_dists); cudaFree(pc->prp_lists_raw);
     cudaFree(d.d_ctrls); cudaFree(pc->d_group_qps);
 }
 
@@ -867,7 +867,12 @@ extern "C" int bam_cache_create_multi(bam_cache_t* out, const bam_ctrl_t* ctrls,
     d.d_ctrl = ctrl->d_ctrl; d.status = status_block(ctrl); d.n_ctrls = n_ctrls;
     d.n_ranges_bits = BAM_RANGE_BITS; d.n_ranges_mask = BAM_MAX_RANGES - 1;
     const uint32_t chunks = page_size / 4096;
-    d.prp_list_stride = chunks > 2 ? chunks - 1 : 0;
+    /* a slot's PRP list has chunks - 1 entries.  Lists are laid out at a power-of-two stride from a
+     * page-aligned base, so none crosses a memory page: the last 8 bytes of a list page mean "link to
+     * the next list page" to an NVMe controller whenever entries still follow */
+    const uint32_t list_entries = chunks > 2 ? chunks - 1 : 0;
+    d.prp_list_stride = 0;
+    if (list_entries) for (d.prp_list_stride = 1; d.prp_list_stride < list_entries;) d.prp_list_stride <<= 1;
     uint32_t total_qps = 0;
     for (uint32_t k = 0; k < n_ctrls; k++) total_qps += ctrls[k]->n_qps;
     cudaError_t e = cudaSuccess;
@@ -880,7 +885,10 @@ extern "C" int bam_cache_create_multi(bam_cache_t* out, const bam_ctrl_t* ctrls,
     alloc((void**)&d.range_page_starts, 8 * BAM_MAX_RANGES);
     alloc((void**)&d.range_dists, 4 * BAM_MAX_RANGES);
     alloc((void**)&d.d_ctrls, sizeof(Controller*) * n_ctrls);
-    if (d.prp_list_stride) alloc((void**)&d.prp_lists, n_pages * d.prp_list_stride * 8);
+    if (d.prp_list_stride) {
+        alloc(&pc->prp_lists_raw, n_pages * d.prp_list_stride * 8 + 4096);
+        d.prp_lists = reinterpret_cast<uint64_t*>(((uintptr_t)pc->prp_lists_raw + 4095) / 4096 * 4096);
+    }
     if (n_ctrls > 1) alloc((void**)&pc->d_group_qps, sizeof(bam_emu_qp_t) * total_qps);
     if (e != cudaSuccess) {
         g_last_cuda = e; (void)cudaGetLastError();
@@ -892,7 +900,7 @@ extern "C" int bam_cache_create_multi(bam_cache_t* out, const bam_ctrl_t* ctrls,
     if (d.prp_list_stride) {
         std::vector<uint64_t> lists(n_pages * d.prp_list_stride);
         for (uint64_t s = 0; s < n_pages; s++)
-            for (uint32_t k = 0; k < d.prp_list_stride; k++)
+            for (uint32_t k = 0; k < list_entries; k++)
                 lists[s * d.prp_list_stride + k] = (uint64_t)(d.base_addr + s * page_size + (size_t)(k + 1) * 4096);
         if (cudaMemcpy(d.prp_lists, lists.data(), lists.size() * 8, cudaMemcpyHostToDevice) != cudaSuccess) return fail(BAM_ECUDA);
     }

@@ -30,17 +30,23 @@
 namespace {
 
 struct host_ctrl;
+struct dma_backing {                            /* what a mapping pinned or allocated; shared with its remaps */
+    int refs = 1;
+    void* registered = nullptr;                 /* memory pinned with cudaHostRegister              */
+    void* allocated = nullptr;                  /* memory allocated with cudaHostAlloc              */
+};
 struct host_dma {                               /* container of an nvm_dma_t (the public part comes last) */
     host_ctrl* owner = nullptr;
-    void* registered = nullptr;                 /* memory this mapping pinned with cudaHostRegister */
-    void* allocated = nullptr;                  /* memory this mapping allocated                   */
+    dma_backing* backing = nullptr;             /* nullptr: the caller's memory, nothing to release  */
     bool device = false;
+    bool page_windows = false;                  /* one DMA window per page (a list of addresses) instead of one for the region */
 };
 
 struct host_ctrl {
     nvm_ctrl_t pub;                             /* must stay the first member: handles are cast back */
     bam_ctrl* emu = nullptr;
     std::mutex lock;
+    int refs = 1;                               /* handles given out for this controller (guarded by g_handles_lock) */
     uint8_t* regs_raw = nullptr;                /* the allocation the register window lies in        */
     uint8_t* regs_host = nullptr;               /* register window                                   */
     uint8_t* regs_dev = nullptr;
@@ -66,6 +72,9 @@ struct host_ctrl {
 struct nvm_dma_box { host_dma priv; nvm_dma_t pub; };
 
 host_ctrl* of(const nvm_ctrl_t* c) { return reinterpret_cast<host_ctrl*>(const_cast<nvm_ctrl_t*>(c)); }
+
+std::mutex g_handles_lock;                      /* live handles, so that a register window can be recognised */
+std::vector<host_ctrl*> g_handles;
 
 __global__ void __launch_bounds__(BAM_THREADS, 1) k_nvm_host_service(const __grid_constant__ bam_emu_d_t emu)
 {
@@ -160,6 +169,23 @@ struct pause_guard {
     }
 };
 
+/* The read-only registers a program may look at, at their NVMe offsets: CAP (0x00: MQES 15:0, CQR 16,
+ * TO 31:24 in 500 ms units, DSTRD 35:32, CSS 37 = NVM command set, MPSMIN 51:48, MPSMAX 55:52),
+ * VS (0x08) = 1.3, CC (0x14: EN 0, MPS 10:7, IOSQES 19:16 = 6, IOCQES 23:20 = 4), CSTS (0x1c: RDY 0),
+ * AQA / ASQ / ACQ (0x24 / 0x28 / 0x30). */
+void write_registers(host_ctrl* h, uint64_t asq, uint64_t acq)
+{
+    const uint64_t cap = (uint64_t)(h->pub.max_qs - 1) | (1ull << 16) | ((h->pub.timeout / 500) << 24) | ((uint64_t)h->pub.dstrd << 32) |
+                         (1ull << 37);
+    *reinterpret_cast<volatile uint64_t*>(h->regs_host + 0x00) = cap;
+    *reinterpret_cast<volatile uint32_t*>(h->regs_host + 0x08) = 0x00010300u;
+    *reinterpret_cast<volatile uint32_t*>(h->regs_host + 0x14) = 1u | (6u << 16) | (4u << 20);
+    *reinterpret_cast<volatile uint32_t*>(h->regs_host + 0x1c) = 1u;
+    *reinterpret_cast<volatile uint32_t*>(h->regs_host + 0x24) = ((uint32_t)(h->pub.page_size / 16 - 1) << 16) | (uint32_t)(h->pub.page_size / 64 - 1);
+    *reinterpret_cast<volatile uint64_t*>(h->regs_host + 0x28) = asq;
+    *reinterpret_cast<volatile uint64_t*>(h->regs_host + 0x30) = acq;
+}
+
 /* rebuild the table the service kernel reads: one entry per complete (CQ, SQ) pair */
 void rebuild_table(host_ctrl* h)
 {
@@ -213,14 +239,66 @@ extern "C" int nvm_emu_ctrl_init(nvm_ctrl_t** ctrl, bam_ctrl_t emu)
     h->pub.mm_ptr = h->regs_host;
     h->stop_host = reinterpret_cast<uint32_t*>(h->regs_host + 0x40);    /* a word of the window the NVMe layout leaves unused */
     memset(h->h_qps, 0, sizeof h->h_qps);
+    write_registers(h, 0, 0);
+    {
+        std::lock_guard<std::mutex> g(g_handles_lock);
+        g_handles.push_back(h);
+    }
     *ctrl = &h->pub;
     return 0;
+}
+
+/* The reference reads the controller's capabilities from a memory-mapped PCI BAR; here the only
+ * register windows that exist are those of emulated controllers, which this call recognises by
+ * address and hands out again (nvm_ctrl_free counts the handles). */
+extern "C" int nvm_raw_ctrl_init(nvm_ctrl_t** ctrl, volatile void* mm_ptr, size_t mm_size)
+{
+    if (!ctrl) return EINVAL;
+    *ctrl = nullptr;
+    if (!mm_ptr || mm_size < NVM_CTRL_MEM_MINSIZE) return EINVAL;
+    std::lock_guard<std::mutex> g(g_handles_lock);
+    for (host_ctrl* h : g_handles)
+        if (h->pub.mm_ptr == mm_ptr) {
+            /* what the reference derives from CAP: page size from MPSMIN, stride from DSTRD, time-out from TO, entries from MQES */
+            const uint64_t cap = *reinterpret_cast<volatile uint64_t*>(h->regs_host);
+            if (h->pub.page_size != ((size_t)1 << (12 + ((cap >> 48) & 0xf))) || h->pub.dstrd != ((cap >> 32) & 0xf) ||
+                h->pub.timeout != ((cap >> 24) & 0xff) * 500 || h->pub.max_qs != (cap & 0xffff) + 1)
+                return EIO;
+            h->refs++;
+            *ctrl = &h->pub;
+            return 0;
+        }
+    return ENODEV;
+}
+
+/* Controller reset with new admin queue addresses (controller pages): every I/O queue pair is
+ * deleted, the doorbells are cleared and the admin queue registers take the addresses. */
+extern "C" int nvm_raw_ctrl_reset(const nvm_ctrl_t* ctrl, uint64_t acq_ioaddr, uint64_t asq_ioaddr)
+{
+    if (!ctrl) return EINVAL;
+    host_ctrl* h = of(ctrl);
+    if ((acq_ioaddr | asq_ioaddr) & (ctrl->page_size - 1)) return EINVAL;
+    std::lock_guard<std::mutex> g(h->lock);
+    cudaSetDevice(h->emu->device);
+    const int rc = stop_service_locked(h);
+    for (uint16_t id = 0; id <= NVM_HOST_MAX_QUEUES; id++) h->have_cq[id] = h->have_sq[id] = false;
+    h->n_qps = 0;
+    memset(h->h_qps, 0, sizeof h->h_qps);
+    memset(h->regs_host, 0, h->pub.mm_size);
+    write_registers(h, asq_ioaddr, acq_ioaddr);
+    return rc;
 }
 
 extern "C" void nvm_ctrl_free(nvm_ctrl_t* ctrl)
 {
     if (!ctrl) return;
     host_ctrl* h = of(ctrl);
+    {
+        std::lock_guard<std::mutex> g(g_handles_lock);
+        if (--h->refs > 0) return;                         /* nvm_raw_ctrl_init handed the controller out more than once */
+        for (size_t i = 0; i < g_handles.size(); i++)
+            if (g_handles[i] == h) { g_handles[i] = g_handles.back(); g_handles.pop_back(); break; }
+    }
     {
         std::lock_guard<std::mutex> g(h->lock);
         cudaSetDevice(h->emu->device);
@@ -285,6 +363,7 @@ static int make_map(nvm_dma_t** map, void* vaddr, size_t page_size, size_t n_pag
     nvm_dma_box* box = static_cast<nvm_dma_box*>(calloc(1, sizeof(nvm_dma_box) + n_pages * sizeof(uint64_t)));
     if (!box) return ENOMEM;
     new (&box->priv) host_dma(priv);
+    box->priv.page_windows = ioaddrs != nullptr;
     box->pub.vaddr = vaddr;
     box->pub.local = local;
     box->pub.contiguous = 1;
@@ -306,6 +385,11 @@ static int make_map(nvm_dma_t** map, void* vaddr, size_t page_size, size_t n_pag
     return 0;
 }
 
+static nvm_dma_box* box_of(const nvm_dma_t* map)
+{
+    return reinterpret_cast<nvm_dma_box*>(reinterpret_cast<uint8_t*>(const_cast<nvm_dma_t*>(map)) - offsetof(nvm_dma_box, pub));
+}
+
 extern "C" int nvm_dma_map(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* vaddr, size_t page_size, size_t n_pages, const uint64_t* ioaddrs)
 {
     if (!map) return EINVAL;
@@ -315,6 +399,23 @@ extern "C" int nvm_dma_map(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* vaddr,
     host_dma priv;
     priv.owner = of(ctrl);
     return make_map(map, vaddr, page_size, n_pages, 0, ioaddrs, priv, true);
+}
+
+/* A second descriptor of the same memory.  What the first one pinned or allocated stays until the
+ * last of them is unmapped. */
+extern "C" int nvm_dma_remap(nvm_dma_t** new_map, const nvm_dma_t* other_map)
+{
+    if (!new_map) return EINVAL;
+    *new_map = nullptr;
+    if (!other_map) return EINVAL;
+    nvm_dma_box* other = box_of(other_map);
+    if (!other->priv.owner) return EINVAL;
+    pause_guard pause(other->priv.owner);
+    host_dma priv = other->priv;
+    const int rc = make_map(new_map, other_map->vaddr, other_map->page_size, other_map->n_ioaddrs, other_map->ioaddrs[0],
+                            other->priv.page_windows ? other_map->ioaddrs : nullptr, priv, other_map->local != 0);
+    if (rc == 0 && priv.backing) priv.backing->refs++;
+    return rc;
 }
 
 extern "C" int nvm_dma_map_host(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* vaddr, size_t size)
@@ -331,12 +432,13 @@ extern "C" int nvm_dma_map_host(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* v
     if (dev == 0) {                                   /* not pinned yet: pin and map it */
         cudaError_t e = cudaHostRegister(vaddr, size, cudaHostRegisterMapped | cudaHostRegisterPortable);
         if (e != cudaSuccess) { (void)cudaGetLastError(); return EFAULT; }
-        priv.registered = vaddr;
         dev = device_address_of_host(vaddr);
-        if (dev == 0) { cudaHostUnregister(vaddr); return EFAULT; }
+        priv.backing = dev ? new (std::nothrow) dma_backing() : nullptr;
+        if (!priv.backing) { cudaHostUnregister(vaddr); return dev ? ENOMEM : EFAULT; }
+        priv.backing->registered = vaddr;
     }
     int rc = make_map(map, vaddr, ps, (size + ps - 1) / ps, dev, nullptr, priv, true);
-    if (rc && priv.registered) cudaHostUnregister(vaddr);
+    if (rc && priv.backing) { cudaHostUnregister(vaddr); delete priv.backing; }
     return rc;
 }
 
@@ -372,31 +474,102 @@ extern "C" int nvm_dma_create(nvm_dma_t** map, const nvm_ctrl_t* ctrl, size_t si
     memset(p, 0, size);
     host_dma priv;
     priv.owner = of(ctrl);
-    priv.allocated = raw;
+    priv.backing = new (std::nothrow) dma_backing();
+    if (!priv.backing) { cudaFreeHost(raw); return ENOMEM; }
+    priv.backing->allocated = raw;
     const uint64_t dev = device_address_of_host(p);
     int rc = (dev && (dev & (ps - 1)) == 0) ? make_map(map, p, ps, size / ps, dev, nullptr, priv, true) : EFAULT;
-    if (rc) cudaFreeHost(raw);
+    if (rc) { cudaFreeHost(raw); delete priv.backing; }
     return rc;
 }
 
 extern "C" void nvm_dma_unmap(nvm_dma_t* map)
 {
     if (!map) return;
-    nvm_dma_box* box = reinterpret_cast<nvm_dma_box*>(reinterpret_cast<uint8_t*>(map) - offsetof(nvm_dma_box, pub));
-    if (box->priv.owner) {                               /* the memory may no longer be named by commands */
-        pause_guard pause(box->priv.owner);
-        host_ctrl* h = box->priv.owner;
-        for (size_t i = 0; i < map->n_ioaddrs; i++)
-            for (uint32_t k = 0; k < h->n_windows;) {
-                if (h->windows[k].base == map->ioaddrs[i]) { h->windows[k] = h->windows[--h->n_windows]; } else k++;
-            }
-    }
-    if (box->priv.owner && (box->priv.registered || box->priv.allocated)) {
-        pause_guard pause(box->priv.owner);
-        if (box->priv.registered) cudaHostUnregister(box->priv.registered);
-        if (box->priv.allocated) cudaFreeHost(box->priv.allocated);
+    nvm_dma_box* box = box_of(map);
+    host_ctrl* h = box->priv.owner;
+    if (h) {
+        pause_guard pause(h);
+        /* the memory may no longer be named by commands -- unless another descriptor still maps it:
+         * exactly the windows this descriptor added are taken out, one entry each */
+        const size_t n_w = box->priv.page_windows ? map->n_ioaddrs : 1;
+        for (size_t i = 0; i < n_w; i++) {
+            const uint64_t bytes = box->priv.page_windows ? map->page_size : map->n_ioaddrs * map->page_size;
+            for (uint32_t k = 0; k < h->n_windows; k++)
+                if (h->windows[k].base == map->ioaddrs[i] && h->windows[k].bytes == bytes) { h->windows[k] = h->windows[--h->n_windows]; break; }
+        }
+        dma_backing* b = box->priv.backing;
+        if (b && --b->refs == 0) {
+            if (b->registered) cudaHostUnregister(b->registered);
+            if (b->allocated) cudaFreeHost(b->allocated);
+            delete b;
+        }
     }
     free(box);
+}
+
+extern "C" const nvm_ctrl_t* nvm_ctrl_from_dma(const nvm_dma_t* dma)
+{
+    if (!dma) return nullptr;
+    host_ctrl* h = box_of(dma)->priv.owner;
+    return h ? &h->pub : nullptr;
+}
+
+/* ---- status text ------------------------------------------------------------------------------------ */
+
+/* Names of the NVMe completion statuses a program is likely to meet, by status code type (0 generic,
+ * 1 command specific, 2 media and data integrity) and status code (reference: src/error.cpp:139-182
+ * maps the same packing to text). */
+extern "C" const char* nvm_strerror(int status)
+{
+    if (status == 0) return "success";
+    if (status > 0) {
+        switch (status) {
+        case BAM_EIO: case BAM_E2BIG: case BAM_ENOMEM: case BAM_EBUSY: case BAM_EINVAL: case BAM_ENOSPC: case BAM_ERANGE: case BAM_ETIMEDOUT:
+        case BAM_ECUDA: return bam_strerror(status);
+        default: return strerror(status);
+        }
+    }
+    const unsigned sct = ((unsigned)(-status) >> 8) & 0xff, sc = (unsigned)(-status) & 0xff;
+    if (sct == 0) {
+        switch (sc) {
+        case 0x00: return "NVMe: successful completion";
+        case 0x01: return "NVMe: invalid command opcode";
+        case 0x02: return "NVMe: invalid field in command";
+        case 0x03: return "NVMe: command identifier conflict";
+        case 0x04: return "NVMe: data transfer error";
+        case 0x05: return "NVMe: aborted, power loss notification";
+        case 0x06: return "NVMe: internal controller error";
+        case 0x07: return "NVMe: abort requested";
+        case 0x08: return "NVMe: aborted, submission queue deleted";
+        case 0x0b: return "NVMe: invalid namespace or format";
+        case 0x0c: return "NVMe: command sequence error";
+        case 0x13: return "NVMe: PRP offset invalid";
+        case 0x80: return "NVMe: LBA out of range";
+        case 0x81: return "NVMe: capacity exceeded";
+        case 0x82: return "NVMe: namespace not ready";
+        default: return "NVMe: generic command status";
+        }
+    }
+    if (sct == 1) {
+        switch (sc) {
+        case 0x00: return "NVMe: completion queue invalid";
+        case 0x01: return "NVMe: invalid queue identifier";
+        case 0x02: return "NVMe: invalid queue size";
+        case 0x0c: return "NVMe: invalid queue deletion";
+        default: return "NVMe: command specific status";
+        }
+    }
+    if (sct == 2) {
+        switch (sc) {
+        case 0x80: return "NVMe: write fault";
+        case 0x81: return "NVMe: unrecovered read error";
+        case 0x85: return "NVMe: compare failure";
+        case 0x86: return "NVMe: access denied";
+        default: return "NVMe: media or data integrity error";
+        }
+    }
+    return "NVMe: unknown status code type";
 }
 
 /* ---- admin ---------------------------------------------------------------------------------------------- */
@@ -416,6 +589,12 @@ extern "C" int nvm_aq_create(nvm_aq_ref* ref, const nvm_ctrl_t* ctrl, const nvm_
 }
 
 extern "C" void nvm_aq_destroy(nvm_aq_ref ref) { delete ref; }
+
+extern "C" const nvm_ctrl_t* nvm_ctrl_from_aq_ref(nvm_aq_ref ref) { return ref ? &ref->h->pub : nullptr; }
+
+/* References to a remote machine's admin queues do not exist here: every reference is local, and
+ * unbinding a local reference does nothing. */
+extern "C" void nvm_rpc_unbind(nvm_aq_ref) {}
 
 extern "C" int nvm_admin_ctrl_info(nvm_aq_ref ref, struct nvm_ctrl_info* info, void*, uint64_t)
 {

@@ -36,6 +36,7 @@ namespace bam {
 #define BAM_SC_INVALID_OPCODE 0x01u
 #define BAM_SC_INVALID_FIELD 0x02u
 #define BAM_SC_DATA_XFER_ERROR 0x04u
+#define BAM_SC_PRP_OFFSET_INVALID 0x13u
 #define BAM_SC_LBA_OUT_OF_RANGE 0x80u
 
 #define BAM_EMU_STAGE_BYTES 4096
@@ -162,6 +163,35 @@ BAM_DEV void emu_decode(const bam_emu_d_t& c, uint32_t q, uint32_t fetch_i, uint
     else if ((m.prp1 & 15u) || (bytes & 15u)) m.status = BAM_SC_INVALID_FIELD;
 }
 
+/* Whether [mem, mem + len) lies inside one of the memory windows commands of this controller may name. */
+BAM_DEV bool emu_in_window(const bam_emu_d_t& c, uint64_t mem, uint64_t len)
+{
+    for (uint32_t k = 0; k < c.n_windows; k++)
+        if (mem >= c.windows[k].base && mem + len <= c.windows[k].base + c.windows[k].bytes && mem + len >= mem) return true;
+    return false;
+}
+
+/* The next data-page address of a PRP list.  The list lies in memory pages; when entries still follow,
+ * the last 8 bytes of a list page hold the address of the next list page instead of a data page
+ * (`more_follow`: this entry is not the transfer's last). */
+struct emu_list_step { uint64_t mem, next; uint32_t status; };
+BAM_DEV __noinline__ emu_list_step emu_list_entry(const bam_emu_d_t& c, uint64_t mps, uint64_t list_ptr, bool more_follow)
+{
+    emu_list_step r = { 0, 0, BAM_SC_PRP_OFFSET_INVALID };
+    for (int hop = 0; hop < 2; hop++) {
+        if (list_ptr & 7u) return r;
+        if (c.windows && !emu_in_window(c, list_ptr, 8)) { r.status = BAM_SC_DATA_XFER_ERROR; return r; }
+        const uint64_t e = ld_relaxed_sys(reinterpret_cast<const uint64_t*>(list_ptr));
+        const bool last_of_page = ((list_ptr + 8) & (mps - 1)) == 0;
+        if (hop == 0 && last_of_page && more_follow) { list_ptr = e; continue; }     /* follow the link, then read the entry there */
+        r.mem = e;
+        r.next = list_ptr + 8;
+        r.status = BAM_SC_SUCCESS;
+        return r;
+    }
+    return r;
+}
+
 /* Move the data of one command through this lane's stage, segment by segment (a 4 KiB page is
  * one segment).  Returns the NVMe status. */
 BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t stage_smem, uint32_t bar, uint32_t& parity)
@@ -171,23 +201,24 @@ BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t
     uint64_t first = mps - (m.prp1 & (mps - 1));
     if (first > m.bytes) first = m.bytes;
     const bool use_list = (m.bytes - first) > mps;
-    uint32_t done = 0, list_i = 0;
+    uint32_t done = 0;
+    uint64_t list_ptr = m.prp2;                            /* with use_list: where the next list entry lies */
     while (done < m.bytes) {
         uint64_t mem;
         uint32_t len;
         if (done == 0) { mem = m.prp1; len = (uint32_t)first; }
         else {
-            mem = use_list ? ld_relaxed_gpu(reinterpret_cast<const uint64_t*>(m.prp2) + list_i++) : m.prp2;
+            if (use_list) {
+                const emu_list_step e = emu_list_entry(c, mps, list_ptr, m.bytes - done > mps);
+                if (e.status != BAM_SC_SUCCESS) return e.status;
+                mem = e.mem;
+                list_ptr = e.next;
+            } else mem = m.prp2;
             if (mem & (mps - 1)) return BAM_SC_INVALID_FIELD;
             len = m.bytes - done < mps ? m.bytes - done : (uint32_t)mps;
         }
         if (len > BAM_EMU_STAGE_BYTES) len = BAM_EMU_STAGE_BYTES;
-        if (c.windows) {                                   /* an untrusted submitter: is [mem, mem + len) memory it may name? */
-            bool ok = false;
-            for (uint32_t k = 0; k < c.n_windows && !ok; k++)
-                ok = mem >= c.windows[k].base && mem + len <= c.windows[k].base + c.windows[k].bytes && mem + len >= mem;
-            if (!ok) return BAM_SC_DATA_XFER_ERROR;
-        }
+        if (c.windows && !emu_in_window(c, mem, len)) return BAM_SC_DATA_XFER_ERROR;     /* an untrusted submitter */
         uint8_t* media = store + m.media_off + done;
         const void* src = (m.opc == NVM_IO_READ) ? (const void*)media : (const void*)mem;
         void* dst = (m.opc == NVM_IO_READ) ? (void*)mem : (void*)media;

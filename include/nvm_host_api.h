@@ -37,6 +37,15 @@ extern "C" {
 /* ---- controller handle: nvm_ctrl_t is defined in bam/abi_types.h (nvm_types.h:19-28 there) ------ */
 /* The reference opens /dev/libnvm* (a kernel module bound to a raw SSD); not available: ENODEV. */
 int nvm_ctrl_init(nvm_ctrl_t** ctrl, int fd);
+/* A handle from a memory-mapped register window (nvm_ctrl.h:53 there).  The windows that exist here are
+ * those of emulated controllers (mm_ptr of a handle made by nvm_emu_ctrl_init): such a window gives
+ * another handle to the same controller, counted by nvm_ctrl_free; anything else is ENODEV.  The window
+ * holds CAP, VS, CC, CSTS, AQA, ASQ and ACQ at their NVMe offsets, consistent with the handle's fields. */
+#define NVM_CTRL_MEM_MINSIZE 0x2000
+int nvm_raw_ctrl_init(nvm_ctrl_t** ctrl, volatile void* mm_ptr, size_t mm_size);
+/* Reset the controller (nvm_ctrl.h:76 there): all I/O queue pairs are gone afterwards, doorbells read 0
+ * and ASQ / ACQ hold the given page-aligned addresses (EINVAL otherwise). */
+int nvm_raw_ctrl_reset(const nvm_ctrl_t* ctrl, uint64_t acq_ioaddr, uint64_t asq_ioaddr);
 /* A handle over an emulated controller made by bam_ctrl_create (which stays owned by the caller). */
 int nvm_emu_ctrl_init(nvm_ctrl_t** ctrl, bam_ctrl_t emu);
 void nvm_ctrl_free(nvm_ctrl_t* ctrl);
@@ -62,7 +71,12 @@ int nvm_dma_map(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* vaddr, size_t pag
 int nvm_dma_map_host(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* vaddr, size_t size);      /* pins the memory */
 int nvm_dma_map_device(nvm_dma_t** map, const nvm_ctrl_t* ctrl, void* devptr, size_t size);   /* cudaMalloc'd memory */
 int nvm_dma_create(nvm_dma_t** map, const nvm_ctrl_t* ctrl, size_t size);                     /* allocates pinned memory */
+/* Another descriptor of the memory of other_map (nvm_dma.h:48 there); pinned or allocated memory is
+ * released when the last descriptor is unmapped. */
+int nvm_dma_remap(nvm_dma_t** new_map, const nvm_dma_t* other_map);
 void nvm_dma_unmap(nvm_dma_t* map);
+/* The controller a mapping / an admin reference belongs to (nvm_util.h:234-250 there). */
+const nvm_ctrl_t* nvm_ctrl_from_dma(const nvm_dma_t* dma);
 
 /* ---- admin queue reference and identify data (nvm_aq.h, nvm_admin.h, nvm_types.h:198-232) ------- */
 /* struct nvm_ctrl_info and struct nvm_ns_info are defined in bam/abi_types.h */
@@ -70,6 +84,8 @@ void nvm_dma_unmap(nvm_dma_t* map);
 /* dma: memory for the admin queues (unused by the emulator, accepted for source compatibility) */
 int nvm_aq_create(nvm_aq_ref* ref, const nvm_ctrl_t* ctrl, const nvm_dma_t* dma);
 void nvm_aq_destroy(nvm_aq_ref ref);
+const nvm_ctrl_t* nvm_ctrl_from_aq_ref(nvm_aq_ref ref);
+void nvm_rpc_unbind(nvm_aq_ref ref);                     /* references are always local here: does nothing */
 int nvm_admin_ctrl_info(nvm_aq_ref ref, struct nvm_ctrl_info* info, void* buffer, uint64_t ioaddr);
 int nvm_admin_ns_info(nvm_aq_ref ref, struct nvm_ns_info* info, uint32_t ns_id, void* buffer, uint64_t ioaddr);
 int nvm_admin_set_num_queues(nvm_aq_ref ref, uint16_t n_cqs, uint16_t n_sqs);

@@ -77,6 +77,16 @@ def ref_wire():
         L.refw_page_to_block.restype = u64
         L.refw_page_to_block.argtypes = [u64, u64, u64]
         L.refw_sizeof_queue.restype = u32
+        L.refw_cmd_data.restype = u64
+        L.refw_cmd_data.argtypes = [u64, vp, C.POINTER(u64), u64, u64, C.POINTER(u64), C.POINTER(u32)]
+        L.refw_sq_pages.restype = u64
+        L.refw_sq_pages.argtypes = [u64, u32]
+        L.refw_cq_pages.restype = u64
+        L.refw_cq_pages.argtypes = [u64, u32]
+        L.refw_default_cid.restype = u32
+        L.refw_default_cid.argtypes = [u32, C.c_int, u32]
+        L.refw_opcode.restype = u32
+        L.refw_opcode.argtypes = [C.c_int, C.c_int, C.c_int]
         _ref_wire = L
     return _ref_wire
 

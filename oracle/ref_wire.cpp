@@ -2,7 +2,8 @@
  * ref_wire.cpp -- TEST INFRASTRUCTURE: a thin extern "C" face on the REFERENCE's own host-compilable
  * wire-format code, compiled from the reference's sources where they lie (recipe: oracle/Makefile,
  * target _ref/libref_wire.so; nothing of the reference is copied into this repository):
- *   include/nvm_cmd.h    nvm_cmd_header / nvm_cmd_data_ptr / nvm_cmd_rw_blks (command encoding)
+ *   include/nvm_cmd.h    nvm_cmd_header / nvm_cmd_data_ptr / nvm_cmd_rw_blks (command encoding),
+ *                        nvm_cmd_data / nvm_prp_list / nvm_prp_list_chain (PRP lists)
  *   include/nvm_queue.h  nvm_sq_enqueue / nvm_sq_submit / nvm_cq_poll / nvm_cq_dequeue / nvm_sq_update /
  *                        nvm_cq_update (the classic host-side queue protocol)
  *   src/queue.cpp        nvm_queue_clear / nvm_queue_reset / nvm_cq_dequeue_block
@@ -101,9 +102,40 @@ REFW_API int refw_cq_take(void* cq, void* sq, uint64_t timeout_ms, uint16_t* cid
     return 0;
 }
 
+/* The reference's nvm_cmd_data for a transfer of n_pages pages named by ioaddrs, with n_lists list pages of
+ * page_size bytes each at list_mem + l * page_size (bus addresses list_ioaddrs[l]).  dptr4 receives command
+ * dwords 6..9; returns the addresses consumed. */
+REFW_API uint64_t refw_cmd_data(uint64_t n_lists, void* list_mem, const uint64_t* list_ioaddrs, uint64_t page_size, uint64_t n_pages,
+                                const uint64_t* ioaddrs, uint32_t* dptr4)
+{
+    nvm_prp_list_t lists[16];
+    if (n_lists > 16) return 0;
+    for (uint64_t l = 0; l < n_lists; l++) {
+        lists[l].vaddr = static_cast<unsigned char*>(list_mem) + l * page_size;
+        lists[l].local = 1;
+        lists[l].page_size = page_size;
+        lists[l].ioaddr = list_ioaddrs[l];
+    }
+    nvm_cmd_t cmd;
+    memset(&cmd, 0, sizeof cmd);
+    const size_t used = nvm_cmd_data(&cmd, n_lists, n_lists ? lists : NULL, n_pages, ioaddrs);
+    memcpy(dptr4, &cmd.dword[6], 16);
+    return used;
+}
+
 REFW_API const char* refw_strerror(int status) { return nvm_strerror(status); }
 REFW_API int refw_unpack_sct(int status) { return NVM_ERR_UNPACK_SCT(status); }
 REFW_API int refw_unpack_sc(int status) { return NVM_ERR_UNPACK_SC(status); }
 REFW_API uint64_t refw_page_align(uint64_t size, uint64_t page_size) { return NVM_PAGE_ALIGN(size, page_size); }
 REFW_API uint64_t refw_page_to_block(uint64_t page_size, uint64_t block_size, uint64_t pageno) { return NVM_PAGE_TO_BLOCK(page_size, block_size, pageno); }
+REFW_API uint64_t refw_sq_pages(uint64_t page_size, uint32_t qs) { nvm_ctrl_t c; c.page_size = page_size; return NVM_SQ_PAGES(&c, qs); }
+REFW_API uint64_t refw_cq_pages(uint64_t page_size, uint32_t qs) { nvm_ctrl_t c; c.page_size = page_size; return NVM_CQ_PAGES(&c, qs); }
+REFW_API uint32_t refw_default_cid(uint32_t tail, int phase, uint32_t qs)
+{
+    nvm_queue_t q;
+    memset(&q, 0, sizeof q);
+    q.tail = tail; q.phase = (int8_t)phase; q.qs = qs;
+    return NVM_DEFAULT_CID(&q);
+}
+REFW_API uint32_t refw_opcode(int gen, int fun, int data) { return NVM_CMD_OPCODE(gen, fun, data); }
 REFW_API uint32_t refw_sizeof_queue(void) { return (uint32_t)sizeof(nvm_queue_t); }

@@ -5,6 +5,7 @@
  * READ commands that the HOST submits with the classic queue functions -- all served by the
  * emulated controller.  Checks every byte and prints one JSON line.
  */
+#include <cerrno>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -125,14 +126,92 @@ int main()
     const unsigned oob_cid = cpl ? (cpl->dword[3] & 0xffffu) : 0xffffu;
     if (cpl) { nvm_sq_update(&sq); nvm_cq_update(&cq); }
 
+    /* ---- transfers of several pages: PRP2 as second pointer, a PRP list, a list that continues in a second
+     * list page, and list memory the controller was never given ---------------------------------------------- */
+    auto one = [&](uint8_t opcode, uint64_t first_media_page, size_t pages, const nvm_cmd_t& dptr_of) -> int {
+        nvm_cmd_t* c = nvm_sq_enqueue(&sq);
+        if (!c) return -2;
+        memset(c, 0, sizeof *c);
+        nvm_cmd_header(c, NVM_DEFAULT_CID(&sq), opcode, ni.ns_id);
+        c->dword[6] = dptr_of.dword[6]; c->dword[7] = dptr_of.dword[7]; c->dword[8] = dptr_of.dword[8]; c->dword[9] = dptr_of.dword[9];
+        nvm_cmd_rw_blks(c, first_media_page * blocks_per_page, (uint16_t)(pages * blocks_per_page));
+        nvm_sq_submit(&sq);
+        nvm_cpl_t* done = nvm_cq_dequeue_block(&cq, ctrl->timeout);
+        if (!done) return -1;
+        const int st = NVM_ERR_PACK(done, 0);
+        nvm_sq_update(&sq);
+        nvm_cq_update(&cq);
+        return st;
+    };
+    nvm_dma_t* list_mem = nullptr;
+    CHECK(nvm_dma_create(&list_mem, ctrl, 2 * page));
+    int bad_multi = 0, st_two = 0, st_list = 0, st_chain = 0, st_foreign = 0;
+    nvm_cmd_t dp;
+    memset(buf->vaddr, 0, n_pages * page);
+    /* two pages: PRP1 + PRP2 */
+    bad_multi += nvm_cmd_data(&dp, 0, NULL, 2, &buf->ioaddrs[10]) != 2;
+    st_two = one(NVM_IO_READ, 300, 2, dp);
+    bad_multi += memcmp(NVM_DMA_OFFSET(buf, 10), media + 300 * page / 8, 2 * page) != 0;
+    /* 37 pages through one list page; the destination pages are taken in reverse order so that the list matters */
+    std::vector<uint64_t> scattered(37);
+    for (size_t i = 0; i < scattered.size(); i++) scattered[i] = buf->ioaddrs[50 - i];
+    nvm_prp_list_t list0 = NVM_PRP_LIST(list_mem, 0);
+    bad_multi += nvm_cmd_data(&dp, 1, &list0, scattered.size(), scattered.data()) != scattered.size();
+    st_list = one(NVM_IO_READ, 1000, scattered.size(), dp);
+    for (size_t i = 0; i < scattered.size(); i++)
+        bad_multi += memcmp(NVM_DMA_OFFSET(buf, 50 - i), media + (1000 + i) * page / 8, page) != 0;
+    /* 1 + 20 pages with the list starting 11 entries before the end of its page: 11 addresses, the link, 9 more */
+    uint64_t* la = (uint64_t*)NVM_DMA_OFFSET(list_mem, 0);
+    uint64_t* lb = (uint64_t*)NVM_DMA_OFFSET(list_mem, 1);
+    memset(la, 0xff, page); memset(lb, 0xff, page);
+    for (size_t i = 0; i < 11; i++) la[500 + i] = buf->ioaddrs[61 + i];
+    la[511] = list_mem->ioaddrs[1];
+    for (size_t i = 0; i < 9; i++) lb[i] = buf->ioaddrs[72 + i];
+    memset(&dp, 0, sizeof dp);
+    nvm_cmd_data_ptr(&dp, buf->ioaddrs[60], list_mem->ioaddrs[0] + 500 * 8);
+    st_chain = one(NVM_IO_READ, 2000, 21, dp);
+    bad_multi += memcmp(NVM_DMA_OFFSET(buf, 60), media + 2000 * page / 8, 21 * page) != 0;
+    /* a list in memory that was never mapped for the controller: refused, nothing read through it */
+    nvm_cmd_data_ptr(&dp, buf->ioaddrs[0], (uint64_t)(uintptr_t)d_mem + 64 * 1024 * 1024);
+    st_foreign = one(NVM_IO_READ, 0, 5, dp);
+
+    /* ---- handles: a second handle from the register window, the owners of a mapping and of an admin reference,
+     * a second descriptor of a mapping that outlives the first --------------------------------------------------- */
+    int bad_handles = 0;
+    nvm_ctrl_t* again = nullptr;
+    bad_handles += nvm_raw_ctrl_init(&again, ctrl->mm_ptr, NVM_CTRL_MEM_MINSIZE) != 0 || again != ctrl;
+    bad_handles += nvm_raw_ctrl_init(&again, &bad_handles, NVM_CTRL_MEM_MINSIZE) != ENODEV || again != nullptr;
+    bad_handles += nvm_raw_ctrl_init(&again, ctrl->mm_ptr, 0x1000) != EINVAL;
+    nvm_ctrl_free(ctrl);                                                   /* drops the second handle only */
+    const uint64_t cap = *(volatile uint64_t*)ctrl->mm_ptr;
+    bad_handles += (cap & 0xffff) + 1 != ctrl->max_qs || ((cap >> 32) & 0xf) != ctrl->dstrd || (*(volatile uint32_t*)((volatile char*)ctrl->mm_ptr + 0x1c) & 1) != 1;
+    bad_handles += nvm_ctrl_from_dma(buf) != ctrl || nvm_ctrl_from_aq_ref(aq) != ctrl;
+    nvm_rpc_unbind(aq);
+    nvm_dma_t* second = nullptr;
+    CHECK(nvm_dma_remap(&second, buf));
+    bad_handles += second->n_ioaddrs != buf->n_ioaddrs || second->ioaddrs[7] != buf->ioaddrs[7] || second->vaddr != buf->vaddr;
+    nvm_dma_unmap(buf);
+    buf = second;
+    memset(buf->vaddr, 0, 2 * page);                                       /* the memory is still there and still a DMA window */
+    bad_multi += nvm_cmd_data(&dp, 0, NULL, 2, &buf->ioaddrs[0]) != 2;
+    const int st_remap = one(NVM_IO_READ, 4000, 2, dp);
+    bad_handles += st_remap != 0 || memcmp(buf->vaddr, media + 4000 * page / 8, 2 * page) != 0;
+
     printf("{\"page_size\": %zu, \"max_entries\": %u, \"sq_entry\": %zu, \"cq_entry\": %zu, \"ns_blocks\": %zu, \"lba\": %zu, \"queues\": [%u, %u], "
            "\"sq_depth\": %u, \"cq_depth\": %u, \"bad_read\": %d, \"bad_write\": %d, \"bad_neighbours\": %d, \"bad_device_read\": %d, "
-           "\"bad_status\": %d, \"oob_status\": %u, \"oob_cid\": %u}\n",
+           "\"bad_status\": %d, \"oob_status\": %u, \"oob_cid\": %u, \"bad_multi\": %d, \"st_two\": %d, \"st_list\": %d, \"st_chain\": %d, "
+           "\"st_foreign\": %d, \"foreign_text\": \"%s\", \"bad_handles\": %d}\n",
            ci.page_size, (unsigned)ci.max_entries, ci.sq_entry_size, ci.cq_entry_size, ni.size, ni.lba_data_size, n_cqs, n_sqs, sq.qs, cq.qs,
-           bad_read, bad_write, bad_own, bad_dev, bad_status, oob_status, oob_cid);
+           bad_read, bad_write, bad_own, bad_dev, bad_status, oob_status, oob_cid, bad_multi, st_two, st_list, st_chain, st_foreign,
+           nvm_strerror(st_foreign), bad_handles);
 
     CHECK(nvm_admin_sq_delete(aq, &sq, &cq));
     CHECK(nvm_admin_cq_delete(aq, &cq));
+    /* a reset takes the admin queue addresses; misaligned ones are refused */
+    if (nvm_raw_ctrl_reset(ctrl, aq_mem->ioaddrs[0] + 8, aq_mem->ioaddrs[1]) != EINVAL) { fprintf(stderr, "reset accepted a misaligned address\n"); return 1; }
+    CHECK(nvm_raw_ctrl_reset(ctrl, aq_mem->ioaddrs[0], aq_mem->ioaddrs[1]));
+    if (*(volatile uint64_t*)((volatile char*)ctrl->mm_ptr + 0x30) != aq_mem->ioaddrs[0]) { fprintf(stderr, "ACQ register not set\n"); return 1; }
+    nvm_dma_unmap(list_mem);
     nvm_dma_unmap(devbuf); nvm_dma_unmap(own); nvm_dma_unmap(buf); nvm_dma_unmap(q_mem); nvm_dma_unmap(aq_mem);
     cudaFree(d_mem);
     free(own_mem);

@@ -16,6 +16,7 @@
 #include <vector>
 #include <cstdio>
 #include <cstdint>
+#include <cstdlib>
 #include <ctrl.h>
 #include <buffer.h>
 #include <event.h>
@@ -30,6 +31,9 @@ static_assert(sizeof(nvm_cmd_t) == 64 && sizeof(nvm_cpl_t) == 16, "NVMe entry si
 static_assert(NVM_PAGE_ALIGN(4097, 4096) == 8192 && NVM_PAGE_TO_BLOCK(4096, 512, 3) == 24, "page arithmetic");
 static_assert(NVM_ERR_UNPACK_SCT(-0x281) == 2 && NVM_ERR_UNPACK_SC(-0x281) == 0x81 && NVM_ERR_UNPACK_ERRNO(5) == 5, "status packing");
 static_assert(REPLICATE == 0 && STRIPE == 1, "data_dist_t");
+static_assert(NVM_CMD_OPCODE(0, 0, 2) == NVM_IO_READ && NVM_CMD_OPCODE(0, 0, 1) == NVM_IO_WRITE && NVM_CMD_OPCODE(0, 2, 0) == NVM_IO_WRITE_ZEROES &&
+              NVM_CMD_OPCODE(0, 1, 2) == NVM_ADMIN_IDENTIFY && NVM_CMD_OPCODE(0, 2, 1) == NVM_ADMIN_SET_FEATURES, "opcode packing");
+static_assert(NVM_CTRL_MEM_MINSIZE == 0x2000 && sizeof(nvm_prp_list_t) == 32, "register window, list descriptor");
 
 __global__ void touch(array_d_t<uint64_t>* a, QueuePair* qp, Controller* c, unsigned long long* out)
 {
@@ -43,10 +47,34 @@ __global__ void touch(array_d_t<uint64_t>* a, QueuePair* qp, Controller* c, unsi
     t.fini();
 }
 
-int main()
+/* --prp n_lists n_pages: what nvm_cmd_data makes of a transfer of n_pages pages at 0x100000 + i * 4096 with
+ * list pages at bus addresses 0xa000, 0xb000, ... (initialised to all ones), as JSON */
+static int show_prp(size_t n_lists, size_t n_pages)
 {
-    BufferPtr b = createBuffer(64);
-    (void)b;
+    std::vector<std::vector<uint64_t>> pages(n_lists, std::vector<uint64_t>(512, ~0ull));
+    std::vector<nvm_prp_list_t> lists;
+    for (size_t l = 0; l < n_lists; l++) lists.push_back(NVM_PRP_LIST_INIT(pages[l].data(), 1, 4096, 0xa000 + l * 0x1000));
+    std::vector<uint64_t> addrs(n_pages + 1);
+    for (size_t i = 0; i < addrs.size(); i++) addrs[i] = 0x100000ull + i * 4096;
+    nvm_cmd_t cmd = {};
+    const size_t used = nvm_cmd_data(&cmd, n_lists, n_lists ? lists.data() : NULL, n_pages, addrs.data());
+    printf("{\"used\": %zu, \"dptr\": [%u, %u, %u, %u], \"lists\": [", used, cmd.dword[6], cmd.dword[7], cmd.dword[8], cmd.dword[9]);
+    for (size_t l = 0; l < n_lists; l++) {
+        printf("%s[", l ? ", " : "");
+        for (size_t i = 0; i < 512; i++) printf("%s%llu", i ? ", " : "", (unsigned long long)pages[l][i]);
+        printf("]");
+    }
+    printf("]}\n");
+    return 0;
+}
+
+int main(int argc, char** argv)
+{
+    if (argc == 4 && std::string(argv[1]) == "--prp") return show_prp(strtoull(argv[2], nullptr, 0), strtoull(argv[3], nullptr, 0));
+    if (argc > 1) {                        /* needs a GPU; without arguments the program only runs host code */
+        BufferPtr b = createBuffer(64);
+        (void)b;
+    }
     /* the members benchmarks read from a Controller (ctrl.h:39-59 of the reference) */
     Controller* c = nullptr;
     static_assert(sizeof(c->ns.lba_data_size) == sizeof(size_t) && sizeof(c->info.max_entries) == 2, "identify data");
@@ -56,5 +84,41 @@ int main()
     (void)nvm_sq_enqueue;
     (void)nvm_cq_dequeue;
     printf("%s\n", nvm_strerror(0));
-    return 0;
+
+    /* host-side helpers: queue sizing, entry fields, status packing, PRP lists (nvm_util.h:157-227, nvm_error.h:15-48,
+     * nvm_cmd.h:113-236 of the reference) */
+    int bad = 0;
+    nvm_ctrl_t hc = {};
+    hc.page_size = 4096;
+    bad += NVM_SQ_PAGES(&hc, 1024) != 16 || NVM_CQ_PAGES(&hc, 1024) != 4 || NVM_SQ_PAGES(&hc, 64) != 1 || NVM_CQ_PAGES(&hc, 257) != 2;
+    bad += NVM_SQ_SIZE(&hc, 1) != 64 || NVM_CQ_SIZE(&hc, 1) != 256 || NVM_CTRL_PAGES(&hc, 4097) != 2 || NVM_CTRL_ALIGN(&hc, 1) != 4096;
+    nvm_cpl_t cpl = {};
+    cpl.dword[2] = 0x0003002au;                                  /* SQID 3, SQHD 42 */
+    cpl.dword[3] = 0x1234u | (1u << 16) | ((0x80u | (2u << 8)) << 17) | (1u << 31);     /* CID, phase, SC 0x80 / SCT 2, DNR */
+    bad += *NVM_CPL_CID(&cpl) != 0x1234 || *NVM_CPL_SQHD(&cpl) != 42 || *NVM_CPL_SQID(&cpl) != 3;
+    bad += NVM_ERR_SC(&cpl) != 0x80 || NVM_ERR_SCT(&cpl) != 2 || !NVM_ERR_DNR(&cpl) || NVM_ERR_MORE(&cpl) || NVM_ERR_OK(&cpl);
+    bad += NVM_ERR_STATUS(&cpl) != -0x280 || NVM_ERR_PACK(&cpl, 0) != -0x280 || NVM_ERR_PACK(&cpl, 5) != 5 || NVM_ERR_PACK((nvm_cpl_t*)NULL, 0) != 0;
+    nvm_cmd_t cmd = {};
+    nvm_cmd_header(&cmd, 0xbeef, NVM_IO_READ, 9);
+    bad += *NVM_CMD_CID(&cmd) != 0xbeef || *NVM_CMD_NSID(&cmd) != 9;
+    nvm_queue_t sq = {};
+    sq.qs = 64; sq.tail = 5; sq.phase = 1;
+    bad += NVM_DEFAULT_CID(&sq) != 5;
+    sq.phase = 0;
+    bad += NVM_DEFAULT_CID(&sq) != 69;
+
+    std::vector<uint64_t> page_a(512, ~0ull), page_b(512, ~0ull), addrs(700);
+    for (size_t i = 0; i < addrs.size(); i++) addrs[i] = 0x100000ull + i * 4096;
+    nvm_prp_list_t lists[2] = { NVM_PRP_LIST_INIT(page_a.data(), 1, 4096, 0xa000), NVM_PRP_LIST_INIT(page_b.data(), 1, 4096, 0xb000) };
+    bad += nvm_cmd_data(&cmd, 2, lists, 1, addrs.data()) != 1 || cmd.dword[6] != 0x100000u || cmd.dword[8] != 0 || cmd.dword[9] != 0;
+    bad += nvm_cmd_data(&cmd, 2, lists, 2, addrs.data()) != 2 || cmd.dword[8] != 0x101000u;
+    bad += nvm_cmd_data(&cmd, 2, lists, 17, addrs.data()) != 17 || cmd.dword[8] != 0xa000u || page_a[0] != addrs[1] || page_a[15] != addrs[16] || page_a[16] != ~0ull;
+    /* 1 + 600 pages: the first list page takes 511 addresses and the link, the second the other 89 */
+    bad += nvm_cmd_data(&cmd, 2, lists, 601, addrs.data()) != 601 || page_a[510] != addrs[511] || page_a[511] != 0xb000 || page_b[0] != addrs[512] ||
+           page_b[88] != addrs[600];
+    /* exactly one list page: 512 addresses, no link */
+    bad += nvm_cmd_data(&cmd, 1, lists, 513, addrs.data()) != 513 || page_a[511] != addrs[512];
+    bad += nvm_cmd_data(&cmd, 0, NULL, 3, addrs.data()) != 2;                 /* no list memory: two pages at most */
+    printf("{\"bad\": %d}\n", bad);
+    return bad != 0;
 }

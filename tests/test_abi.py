@@ -34,13 +34,22 @@ def test_host_libnvm_symbols_are_exported(bam):
     src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
     src = src[: src.index("static inline")]                 # the classic queue functions are header-only
     names = sorted(set(re.findall(r"\b(nvm_[a-z0-9_]+)\s*\(", src)))
-    names += ["nvm_queue_clear", "nvm_queue_reset", "nvm_cq_dequeue_block"]
-    assert len(names) >= 25
+    names += ["nvm_queue_clear", "nvm_queue_reset", "nvm_cq_dequeue_block", "nvm_strerror"]
+    for n in ("nvm_raw_ctrl_init", "nvm_raw_ctrl_reset", "nvm_dma_remap", "nvm_ctrl_from_dma", "nvm_ctrl_from_aq_ref", "nvm_rpc_unbind"):
+        assert n in names, n
+    assert len(names) >= 32
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/nvm_host_api.h but not exported"
     ctrl = C.c_void_p()
     assert lib.nvm_ctrl_init(C.byref(ctrl), 3) == 19        # ENODEV: there is no kernel module behind a descriptor
     assert lib.nvm_emu_ctrl_init(C.byref(ctrl), None) == 22
+    buf = (C.c_uint8 * 0x2000)()
+    assert lib.nvm_raw_ctrl_init(C.byref(ctrl), buf, 0x2000) == 19 and not ctrl.value     # not the register window of any controller
+    assert lib.nvm_raw_ctrl_init(C.byref(ctrl), buf, 0x1000) == 22                         # smaller than the registers
+    assert lib.nvm_dma_remap(C.byref(ctrl), None) == 22
+    lib.nvm_strerror.restype = C.c_char_p
+    assert lib.nvm_strerror(-0x80) == b"NVMe: LBA out of range" and lib.nvm_strerror(0) == b"success"
+    assert lib.nvm_strerror(-0x281) == b"NVMe: unrecovered read error" and lib.nvm_strerror(22) == b"invalid argument"
 
 
 def test_ctypes_table_covers_header(bam):

@@ -71,4 +71,10 @@ def test_cpp_host_libnvm_io(cuda, bam):
     assert (r["sq_depth"], r["cq_depth"]) == (64, 256)        # the page-sized defaults of sq_create / cq_create
     assert r["bad_read"] == r["bad_write"] == r["bad_neighbours"] == r["bad_device_read"] == r["bad_status"] == 0
     assert r["oob_status"] == 0x80 and r["oob_cid"] == 7      # LBA out of range, generic status code type
+    # transfers of 2, 37 and 21 pages: second pointer, a PRP list, a list continued in a second list page
+    assert r["bad_multi"] == 0 and (r["st_two"], r["st_list"], r["st_chain"]) == (0, 0, 0)
+    # a list in memory the controller was never given: data transfer error, as a packed status and as text
+    assert r["st_foreign"] == -0x04 and "transfer" in r["foreign_text"]
+    # nvm_raw_ctrl_init over the register window, nvm_ctrl_from_dma / _from_aq_ref, nvm_dma_remap outliving its original
+    assert r["bad_handles"] == 0
 

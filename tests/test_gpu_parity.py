@@ -218,9 +218,10 @@ def test_page_scan_cold_and_warm(cuda, bam, orc):
 
 
 def test_large_page_prp2_and_prp_list(cuda, bam, orc):
-    """8 KiB pages use PRP2 as a second pointer, 16 KiB pages a PRP list."""
+    """8 KiB pages use PRP2 as a second pointer, larger pages a PRP list (3 entries for 16 KiB, 15 for
+    64 KiB: the lists of 64 slots span more than one list page without any crossing a page end)."""
     n_elems, seed = 1 << 18, 21
-    for page in (8192, 16384):
+    for page in (8192, 16384, 65536):
         ctrl, cache, arr = make(bam, n_elems, 64, 2, 16, page=page, seed=seed)
         out = cuda.zeros(1, dtype=cuda.int64, device="cuda")
         arr.read(2048, 8, out, access_seed=4)

@@ -12,6 +12,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLDEN = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "golden.json")))
 M64 = (1 << 64) - 1
 
@@ -333,6 +334,53 @@ def test_command_encoding_against_the_reference_builders(orc, bam):
     assert b"LBA out of range" in ref.refw_strerror(-0x80) or b"range" in ref.refw_strerror(-0x80).lower()
     assert ref.refw_page_align(4097, 4096) == 8192 and ref.refw_page_to_block(4096, 512, 3) == 24
     assert ref.refw_sizeof_queue() > 0
+
+
+def test_prp_list_helpers_against_the_reference(orc, bam, tmp_path):
+    """nvm_cmd_data / nvm_prp_list / nvm_prp_list_chain, the queue sizing macros, NVM_DEFAULT_CID, the
+    opcode packing and the status strings of the library's headers against the reference's own (its
+    include/nvm_cmd.h:113-216 and nvm_util.h:186-227 compiled into oracle/_ref/libref_wire.so): same data
+    pointer, same list pages, same number of addresses consumed."""
+    import shutil
+    import subprocess
+    ref = orc.ref_wire()
+    if ref is None:
+        pytest.skip("the reference's wire-format code is not built (needs the reference project)")
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    from bam_b200 import _lib
+    exe = str(tmp_path / "include_compat")
+    res = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-I" + os.path.join(ROOT, "include"),
+                          os.path.join(ROOT, "tests", "cpp", "include_compat.cu"), "-o", exe, "-L" + os.path.dirname(_lib.LIB_PATH),
+                          "-lbam_b200", "-Xlinker", "-rpath=" + os.path.dirname(_lib.LIB_PATH)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    # the program's own host-side checks (macros, entry fields, status packing, list building)
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 0 and json.loads(out.stdout.strip().splitlines()[-1]) == {"bad": 0}, out.stdout + out.stderr
+    for n_lists, n_pages in [(0, 1), (0, 2), (0, 5), (1, 1), (1, 2), (1, 3), (1, 17), (1, 256), (1, 512), (1, 513), (2, 513), (2, 514), (2, 601),
+                             (3, 1100), (4, 1535)]:
+        got = json.loads(subprocess.run([exe, "--prp", str(n_lists), str(n_pages)], capture_output=True, text=True, check=True).stdout)
+        mem = np.full(max(n_lists, 1) * 512, 0xFFFFFFFFFFFFFFFF, dtype=np.uint64)
+        list_io = (C.c_uint64 * max(n_lists, 1))(*[0xa000 + l * 0x1000 for l in range(max(n_lists, 1))])
+        addrs = (C.c_uint64 * (n_pages + 1))(*[0x100000 + i * 4096 for i in range(n_pages + 1)])
+        dptr = (C.c_uint32 * 4)()
+        used = ref.refw_cmd_data(n_lists, mem.ctypes.data, list_io, 4096, n_pages, addrs, dptr)
+        assert got["used"] == used and got["dptr"] == list(dptr), (n_lists, n_pages)
+        for l in range(n_lists):
+            assert got["lists"][l] == mem[l * 512:(l + 1) * 512].tolist(), (n_lists, n_pages, l)
+    lib = bam.load()
+    for qs in (1, 2, 64, 65, 256, 257, 1024):
+        assert ref.refw_sq_pages(4096, qs) == ((qs - 1) & 0xFFFF) * 64 // 4096 + 1
+        assert ref.refw_cq_pages(4096, qs) == ((qs - 1) & 0xFFFF) * 16 // 4096 + 1
+    assert ref.refw_default_cid(5, 1, 64) == 5 and ref.refw_default_cid(5, 0, 64) == 69
+    assert [ref.refw_opcode(0, 0, 2), ref.refw_opcode(0, 0, 1), ref.refw_opcode(0, 2, 0), ref.refw_opcode(0, 1, 2)] == [2, 1, 8, 6]
+    # status text: same subject as the reference's table for the statuses the emulated controller can return
+    lib.nvm_strerror.restype = C.c_char_p
+    lib.nvm_strerror.argtypes = [C.c_int]
+    for status, word in [(-0x80, b"range"), (-0x01, b"opcode"), (-0x02, b"field"), (-0x04, b"transfer"), (-0x13, b"offset"), (-0x101, b"queue")]:
+        assert word in lib.nvm_strerror(status).lower() and word in ref.refw_strerror(status).lower(), status
+    assert lib.nvm_strerror(0) == b"success" and lib.nvm_strerror(2) == ref.refw_strerror(2)       # an errno both pass to strerror()
 
 
 def test_reference_parallel_queue_code_against_the_oracle_controller(orc):
