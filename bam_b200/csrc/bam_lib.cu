@@ -653,6 +653,7 @@ extern "C" int bam_ctrl_create(bam_ctrl_t* out, int device, uint64_t store_bytes
     c->emu.n_ctrl_blocks = BAM_DEFAULT_CTRL_BLOCKS;
     c->emu.lba_log2 = log2_u32(lba_bytes); c->emu.mps_log2 = 12;
     c->emu.batch = 32; c->emu.sys_scope = c->sys_scope;
+    if (const char* e = getenv("BAM_EMU_PROCS_PER_QUEUE")) c->emu.procs_per_queue = (uint32_t)strtoul(e, nullptr, 0);
     c->emu.consumers_remaining = c->d_remaining; c->emu.status = c->d_status;
     int rc = upload_queue_image(c);
     if (rc != BAM_OK) { cudaFree(c->arena); cudaFreeHost(c->store_host); delete c; return rc; }

@@ -14,7 +14,7 @@ from ._lib import CacheStats, StatusOut, check
 
 WHERE = {0: "none", 1: "cid", 2: "sq_turn", 3: "sq_doorbell", 4: "cq_wait", 5: "page_busy",
          6: "find_slot", 7: "bucket_lock", 8: "table_full", 9: "nvme_status", 10: "ctrl_cq_full",
-         11: "range", 12: "tma", 13: "launch"}
+         11: "range", 12: "tma", 13: "launch", 14: "sq_order"}
 
 FAULT_NONE, FAULT_DROP_CPL, FAULT_STATUS = 0, 1, 2
 

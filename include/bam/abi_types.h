@@ -50,6 +50,7 @@
 #define BAM_AT_RANGE 11       /* index outside every range of the array     */
 #define BAM_AT_TMA 12         /* bulk-copy mbarrier wait                    */
 #define BAM_AT_LAUNCH 13      /* the whole launch outlived launch_timeout_ns */
+#define BAM_AT_SQ_ORDER 14    /* controller: an earlier batch of the queue never handed its entries back */
 
 /* Per-controller error/status block in device memory.  code is written once (first error
  * wins); every bounded wait also polls it so that one failure drains the whole launch. */
@@ -199,7 +200,7 @@ typedef struct {
 
 /* ---- emulated NVMe controller (device-resident command processor) ----------------------- */
 typedef struct BAM_ALIGNAS(64) {
-    uint32_t lock;          /* one controller warp fetches from this SQ at a time */
+    uint32_t lock;          /* one controller warp reserves commands of this SQ at a time */
     uint32_t sq_fetch;      /* virtual SQ head: next entry to fetch               */
     uint32_t cq_tail;       /* virtual CQ tail: next completion slot to hand out   */
     uint32_t cq_head;       /* virtual CQ head reconstructed from the doorbell     */
@@ -217,7 +218,10 @@ typedef struct BAM_ALIGNAS(64) {
     struct bam_fault_s* fault;
     uint64_t* served;       /* commands completed, for statistics                            */
     uint32_t cq_qs, cq_qs_log2;   /* depth of the completion queue (may differ from the SQ's)  */
-    uint64_t pad[3];
+    uint32_t sq_decoded;    /* virtual SQ position up to which entries have been read out: batches are reserved
+                             * under `lock`, decoded outside it, and handed back here in order */
+    uint32_t pad32_;
+    uint64_t pad[2];
 } bam_emu_qp_t;
 
 #define BAM_FAULT_NONE 0
@@ -245,7 +249,7 @@ typedef struct {
      * touched.  NULL = no check (the library's own kernels build their PRPs from cache slots). */
     const struct bam_dma_window_s* windows;
     uint32_t n_windows;
-    uint32_t pad_;
+    uint32_t procs_per_queue;   /* command processors (warps) that may serve one queue; 0 = the default of 8 */
 } bam_emu_d_t;
 
 typedef struct bam_dma_window_s { uint64_t base, bytes; } bam_dma_window_t;

@@ -42,7 +42,7 @@ namespace bam {
 #define BAM_EMU_STAGE_BYTES 4096
 #define BAM_EMU_LANES 4             /* lanes of a controller warp that process commands (one stage each) */
 #define BAM_EMU_WARPS 4             /* warps of a controller block that are command processors            */
-#define BAM_EMU_MAX_PROCS_PER_QUEUE 8u
+#define BAM_EMU_MAX_PROCS_PER_QUEUE 32u
 #define BAM_EMU_STAGES (BAM_EMU_LANES * BAM_EMU_WARPS)     /* 4 KiB stages per controller block           */
 /* dynamic shared memory a controller block needs: the stages and one mbarrier per stage */
 #define BAM_EMU_SMEM_BYTES (BAM_EMU_STAGES * BAM_EMU_STAGE_BYTES + 256)
@@ -132,12 +132,37 @@ BAM_DEV uint32_t emu_reserve(const bam_emu_d_t& c, uint32_t q, uint32_t want, ui
     cq_head += (hdb - cq_head) & cmask;
     const uint32_t space = cmask - (cqbase - cq_head);         /* keep one completion slot open */
     uint32_t n = avail < space ? avail : space;
-    if (n > want) n = want;
+    /* a shallow queue is spread over more processors: a sixteenth of its depth per batch (8 at least) keeps
+     * more of its commands in transfer at once than two or three full batches would */
+    uint32_t most = s->qs >> 4;
+    if (most < 8u) most = 8u;
+    if (most > want) most = want;
+    if (n > most) n = most;
     if (n == 0) { st_release_gpu(&s->lock, 0u); return 0; }
     fence_acq_rel_scoped(c.sys_scope != 0);                    /* acquire the command bytes      */
     st_relaxed_gpu(&s->cq_head, cq_head);
     st_relaxed_gpu(&s->cq_tail, cqbase + n);
+    st_relaxed_gpu(&s->sq_fetch, fetch + n);
+    st_release_gpu(&s->lock, 0u);                              /* the next batch can be reserved while this one is read out */
     return n;
+}
+
+/* Lane 0 of a processor, after its warp has read the SQ entries [fetch, fetch + n) of queue q: hand them
+ * back IN ORDER.  A completion tells the submitter that every entry below its SQ head value is free
+ * again, and completions of a later batch may be posted before those of an earlier one; so no batch
+ * passes this point before all earlier batches of the queue have read their entries out. */
+BAM_DEV void emu_hand_back(const bam_emu_d_t& c, uint32_t q, uint32_t fetch, uint32_t n)
+{
+    uint32_t* dec = &c.qps[q].sq_decoded;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t polls = 0;
+    while (ld_acquire_gpu(dec) != fetch) {
+        if (((++polls) & 255u) == 0u && global_timer_ns() - t0 > c.status->spin_timeout_ns) {
+            status_fail(c.status, BAM_ETIMEDOUT, BAM_AT_SQ_ORDER, fetch);
+            return;                                            /* the launch is draining: leave the counter alone */
+        }
+    }
+    st_release_gpu(dec, fetch + n);
 }
 
 /* Read and decode SQ entry `fetch_i` of queue pair q. */
@@ -249,8 +274,8 @@ BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t
 
 /* Body of a controller block.  Warps [0, BAM_EMU_WARPS) are command processors; in each, lanes
  * [0, BAM_EMU_LANES) own one 4 KiB stage and one mbarrier.  A processor reserves a batch of up to 32
- * commands from one queue under that queue's fetch lock, every lane decodes one of them side by
- * side, the lock is released, and the stage-owning lanes transfer and complete the commands
+ * commands from one queue under that queue's lock (held for the reservation only), every lane decodes
+ * one of them side by side, the entries are handed back in order, and the stage-owning lanes transfer and complete the commands
  * BAM_EMU_LANES at a time, so the latencies of a round overlap and the lock is held once per batch.  Runs until
  * every workload block of the launch has finished (consumers_remaining == 0) or an error has been
  * flagged.  `smem` is the block's dynamic shared memory (BAM_EMU_SMEM_BYTES, 128-byte aligned). */
@@ -272,8 +297,8 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
     __syncwarp(full);
 
     const uint64_t t_start = global_timer_ns();
-    /* with few queues, more than a handful of processors per queue only fight for its fetch lock */
-    const bool spare = me >= c.n_qps * BAM_EMU_MAX_PROCS_PER_QUEUE;
+    /* with few queues, more than a few dozen processors per queue only add polling traffic on its lock */
+    const bool spare = me >= c.n_qps * (c.procs_per_queue ? c.procs_per_queue : BAM_EMU_MAX_PROCS_PER_QUEUE);
     const uint32_t rounds = (c.n_qps + n_procs - 1) / n_procs;
     uint32_t want = c.batch < 32u ? c.batch : 32u;
     if (want == 0) want = 1;
@@ -301,14 +326,13 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
             bq = __shfl_sync(full, bq, 0);
             __syncwarp(full);                                  /* lane 0's acquire fence covers the batch */
             const uint32_t qmask = c.qps[bq].qs - 1u;
-            /* every lane decodes one SQ entry of the batch; then the queue is handed back */
+            /* every lane decodes one SQ entry of the batch (the queue's lock is free again already) */
             emu_cmd_t m;
             m.prp1 = m.prp2 = m.media_off = 0; m.bytes = m.cq_virt = m.cid = m.opc = 0; m.status = BAM_SC_SUCCESS;
             if (lane < n) emu_decode(c, bq, fetch + lane, cqbase + lane, (fetch + n) & qmask, m);
             __syncwarp(full);
             if (lane == 0) {
-                st_relaxed_gpu(&c.qps[bq].sq_fetch, fetch + n);
-                st_release_gpu(&c.qps[bq].lock, 0u);
+                emu_hand_back(c, bq, fetch, n);
 #ifdef BAM_PROFILE
                 { long long t = clock64(); BAM_PROF_ADD(c.status, 16, 1); BAM_PROF_ADD(c.status, 17, n); BAM_PROF_ADD(c.status, 18, t - pt); pt = t; }
 #endif
