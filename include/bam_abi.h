@@ -60,7 +60,10 @@ int bam_ctrl_fill_store_striped(bam_ctrl_t c, uint64_t seed, uint64_t first_elem
 /* Copy caller data into the store at a byte offset (host memcpy). */
 int bam_ctrl_write_store(bam_ctrl_t c, uint64_t byte_offset, const void* src, uint64_t bytes);
 /* Controller warps: n_blocks blocks of the fused launches run the command processor;
- * batch = commands a warp fetches per lock hold.  0 keeps the current value. */
+ * batch = the most commands a warp reserves from a queue at a time (at most 32; a queue shallower than
+ * 16 x batch is cut into batches of a sixteenth of its depth, 8 at least).  0 keeps the current value.
+ * At most 32 processor warps serve one queue; the environment variable BAM_EMU_PROCS_PER_QUEUE, read by
+ * bam_ctrl_create, overrides that number (a tuning aid). */
 int bam_ctrl_configure(bam_ctrl_t c, uint32_t n_ctrl_blocks, uint32_t batch, uint64_t spin_timeout_ns);
 /* Upper limit for one fused launch (default 300 s): the controller blocks flag BAM_ETIMEDOUT and
  * every wait in the launch drains. */
