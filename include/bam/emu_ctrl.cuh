@@ -21,9 +21,10 @@
  * completed releases the completion entry.  What limits a software controller is not the copy
  * but the chain of dependent protocol steps per command (doorbell read, lock, SQ entry read,
  * completion release at system scope), so those are overlapped SIMT-style: a processor is one
- * warp, it reserves a BATCH of commands from one queue under that queue's fetch lock, and then
- * BAM_EMU_LANES lanes each decode, transfer and complete their own command side by side.
- * Several processors may serve one queue; the lock covers only the reservation.
+ * warp, it reserves a BATCH of commands from one queue under that queue's lock, all lanes read
+ * one SQ entry each, and then BAM_EMU_LANES lanes transfer and complete the commands side by side.
+ * Several processors may serve one queue; the lock covers only the reservation, and the batches
+ * hand their SQ entries back in order (emu_hand_back) before any of their completions is posted.
  */
 #ifndef BAM_EMU_CTRL_CUH
 #define BAM_EMU_CTRL_CUH
@@ -112,9 +113,9 @@ BAM_DEV void emu_post_completion(const bam_emu_d_t& c, const emu_cmd_t& m, uint3
     red_add_relaxed(s->served, 1ull);
 }
 
-/* Lane 0 of a processor: look at queue pair q and, if commands are waiting, take the fetch lock
- * and reserve up to `want` of them together with their completion slots.  Returns the number
- * reserved (0: nothing taken, lock not held).  The doorbells are polled with relaxed loads; one
+/* Lane 0 of a processor: look at queue pair q and, if commands are waiting, take the queue's lock,
+ * reserve up to `want` of them together with their completion slots, and release the lock.  Returns
+ * the number reserved (0: nothing taken).  The doorbells are polled with relaxed loads; one
  * acquire fence follows only when there is work. */
 BAM_DEV uint32_t emu_reserve(const bam_emu_d_t& c, uint32_t q, uint32_t want, uint32_t& fetch, uint32_t& cqbase)
 {
