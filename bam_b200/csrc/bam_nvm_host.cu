@@ -171,14 +171,14 @@ struct pause_guard {
 
 /* The read-only registers a program may look at, at their NVMe offsets: CAP (0x00: MQES 15:0, CQR 16,
  * TO 31:24 in 500 ms units, DSTRD 35:32, CSS 37 = NVM command set, MPSMIN 51:48, MPSMAX 55:52),
- * VS (0x08) = 1.3, CC (0x14: EN 0, MPS 10:7, IOSQES 19:16 = 6, IOCQES 23:20 = 4), CSTS (0x1c: RDY 0),
+ * VS (0x08) = 1.4, CC (0x14: EN 0, MPS 10:7, IOSQES 19:16 = 6, IOCQES 23:20 = 4), CSTS (0x1c: RDY 0),
  * AQA / ASQ / ACQ (0x24 / 0x28 / 0x30). */
 void write_registers(host_ctrl* h, uint64_t asq, uint64_t acq)
 {
     const uint64_t cap = (uint64_t)(h->pub.max_qs - 1) | (1ull << 16) | ((h->pub.timeout / 500) << 24) | ((uint64_t)h->pub.dstrd << 32) |
                          (1ull << 37);
     *reinterpret_cast<volatile uint64_t*>(h->regs_host + 0x00) = cap;
-    *reinterpret_cast<volatile uint32_t*>(h->regs_host + 0x08) = 0x00010300u;
+    *reinterpret_cast<volatile uint32_t*>(h->regs_host + 0x08) = 0x00010400u;
     *reinterpret_cast<volatile uint32_t*>(h->regs_host + 0x14) = 1u | (6u << 16) | (4u << 20);
     *reinterpret_cast<volatile uint32_t*>(h->regs_host + 0x1c) = 1u;
     *reinterpret_cast<volatile uint32_t*>(h->regs_host + 0x24) = ((uint32_t)(h->pub.page_size / 16 - 1) << 16) | (uint32_t)(h->pub.page_size / 64 - 1);
@@ -596,53 +596,318 @@ extern "C" const nvm_ctrl_t* nvm_ctrl_from_aq_ref(nvm_aq_ref ref) { return ref ?
  * unbinding a local reference does nothing. */
 extern "C" void nvm_rpc_unbind(nvm_aq_ref) {}
 
-extern "C" int nvm_admin_ctrl_info(nvm_aq_ref ref, struct nvm_ctrl_info* info, void*, uint64_t)
+/* ---- the controller's side of the admin commands ------------------------------------------------------
+ * What an NVMe controller does when it executes an admin command, as functions over the handle's state.
+ * They return an NVMe status (status code | status code type << 8; 0 = success).  h->lock is held. */
+
+#define ADM_SC_INVALID_OPCODE 0x001u
+#define ADM_SC_INVALID_FIELD 0x002u
+#define ADM_SC_DATA_XFER 0x004u
+#define ADM_SC_INVALID_NS 0x00bu
+#define ADM_SC_CQ_INVALID 0x100u
+#define ADM_SC_QID_INVALID 0x101u
+#define ADM_SC_QSIZE_INVALID 0x102u
+#define ADM_SC_LOG_PAGE_INVALID 0x109u
+#define ADM_SC_QUEUE_DELETION 0x10cu
+
+static uint32_t log2_of(uint32_t x) { uint32_t l = 0; while ((1u << l) < x) l++; return l; }
+
+/* host pointer behind a bus address that lies, with `bytes` bytes, inside memory mapped for this controller;
+ * *device is set when the memory is GPU memory (then the returned pointer is the device pointer) */
+static void* admin_memory(host_ctrl* h, uint64_t ioaddr, size_t bytes, bool* device)
 {
-    if (!ref || !info) return EINVAL;
-    memset(info, 0, sizeof *info);
-    info->nvme_version = 0x00010400;                       /* 1.4 */
-    info->page_size = ref->h->pub.page_size;
-    info->db_stride = (size_t)4 << ref->h->pub.dstrd;
-    info->timeout = ref->h->pub.timeout;
-    info->contiguous = 1;
-    info->max_entries = (uint16_t)ref->h->pub.max_qs;
-    memcpy(info->serial_no, "BAMB200EMU0000000001", 20);
-    memset(info->model_no, ' ', sizeof info->model_no);
-    memcpy(info->model_no, "emulated NVMe controller (pinned host memory)", 45 < sizeof info->model_no ? 45 : sizeof info->model_no);
-    memcpy(info->firmware, "1.0     ", 8);
-    info->max_data_size = (size_t)1 << 20;                  /* the largest cache page the library accepts */
-    info->max_data_pages = info->max_data_size / info->page_size;
-    info->cq_entry_size = sizeof(nvm_cpl_t);
-    info->sq_entry_size = sizeof(nvm_cmd_t);
-    info->max_out_cmds = BAM_CID_SPACE;
-    info->max_n_ns = 1;
+    bool ok = false;
+    for (uint32_t k = 0; k < h->n_windows && !ok; k++)
+        ok = ioaddr >= h->windows[k].base && ioaddr + bytes <= h->windows[k].base + h->windows[k].bytes;
+    if (!ok) return nullptr;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, reinterpret_cast<void*>((uintptr_t)ioaddr)) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+    *device = attr.type == cudaMemoryTypeDevice;
+    if (*device) return attr.devicePointer;
+    return attr.type == cudaMemoryTypeHost ? attr.hostPointer : nullptr;
+}
+
+static uint32_t ctrl_cq_create(host_ctrl* h, uint32_t id, uint32_t qs, uint64_t dev)
+{
+    if (id == 0 || id > NVM_HOST_MAX_QUEUES || id > h->granted_cqs || h->have_cq[id]) return ADM_SC_QID_INVALID;
+    if (qs < 2 || qs > h->pub.max_qs || (qs & (qs - 1))) return ADM_SC_QSIZE_INVALID;      /* the command processor wants a power of two */
+    h->have_cq[id] = true;
+    h->cq_mem_dev[id] = reinterpret_cast<nvm_cpl_t*>((uintptr_t)dev);
+    h->cq_qs[id] = qs;
     return 0;
 }
 
-extern "C" int nvm_admin_ns_info(nvm_aq_ref ref, struct nvm_ns_info* info, uint32_t ns_id, void*, uint64_t)
+static uint32_t ctrl_sq_create(host_ctrl* h, uint32_t id, uint32_t cqid, uint32_t qs, uint64_t dev, int* host_error)
+{
+    if (id == 0 || id > NVM_HOST_MAX_QUEUES || id > h->granted_sqs || h->have_sq[id]) return ADM_SC_QID_INVALID;
+    if (cqid == 0 || cqid > NVM_HOST_MAX_QUEUES || !h->have_cq[cqid]) return ADM_SC_CQ_INVALID;
+    if (qs < 2 || qs > h->pub.max_qs || (qs & (qs - 1))) return ADM_SC_QSIZE_INVALID;
+    cudaSetDevice(h->emu->device);
+    if ((*host_error = stop_service_locked(h)) != 0) return 0;
+    uint32_t slot = 0;                                     /* position in the table = creation order */
+    for (uint16_t k = 1; k <= NVM_HOST_MAX_QUEUES; k++) if (h->have_sq[k]) slot++;
+    bam_emu_qp_t* e = &h->h_qps[slot];
+    memset(e, 0, sizeof *e);
+    e->sq_mem = reinterpret_cast<nvm_cmd_t*>((uintptr_t)dev);
+    e->cq_mem = h->cq_mem_dev[cqid];
+    e->sq_db = reinterpret_cast<uint32_t*>(h->regs_dev + NVM_SQ_DBL_OFFSET(id, h->pub.dstrd));
+    e->cq_db = reinterpret_cast<uint32_t*>(h->regs_dev + NVM_CQ_DBL_OFFSET(cqid, h->pub.dstrd));
+    e->qs = qs; e->qs_log2 = log2_of(qs);
+    e->cq_qs = h->cq_qs[cqid]; e->cq_qs_log2 = log2_of(e->cq_qs);
+    e->sqid = (uint16_t)id; e->cqid = (uint16_t)cqid;
+    e->store = h->emu->store_dev; e->store_bytes = h->emu->store_bytes;
+    e->fault = h->d_fault; e->served = h->d_served;
+    *reinterpret_cast<volatile uint32_t*>(h->regs_host + NVM_SQ_DBL_OFFSET(id, h->pub.dstrd)) = 0;
+    *reinterpret_cast<volatile uint32_t*>(h->regs_host + NVM_CQ_DBL_OFFSET(cqid, h->pub.dstrd)) = 0;
+    h->have_sq[id] = true;
+    rebuild_table(h);
+    *host_error = start_service_locked(h);
+    return 0;
+}
+
+static uint32_t ctrl_cq_delete(host_ctrl* h, uint32_t id)
+{
+    if (id == 0 || id > NVM_HOST_MAX_QUEUES || !h->have_cq[id]) return ADM_SC_QID_INVALID;
+    for (uint32_t k = 0; k < h->n_qps; k++)
+        if (h->h_qps[k].cqid == id) return ADM_SC_QUEUE_DELETION;           /* a submission queue still completes into it */
+    h->have_cq[id] = false;
+    return 0;
+}
+
+static uint32_t ctrl_sq_delete(host_ctrl* h, uint32_t id, int* host_error)
+{
+    if (id == 0 || id > NVM_HOST_MAX_QUEUES || !h->have_sq[id]) return ADM_SC_QID_INVALID;
+    cudaSetDevice(h->emu->device);
+    *host_error = stop_service_locked(h);
+    /* close the gap in the table */
+    uint32_t slot = 0, n = 0;
+    for (uint16_t k = 1; k <= NVM_HOST_MAX_QUEUES; k++) { if (k == id) slot = n; if (h->have_sq[k]) n++; }
+    for (uint32_t k = slot; k + 1 < n; k++) h->h_qps[k] = h->h_qps[k + 1];
+    h->have_sq[id] = false;
+    rebuild_table(h);
+    if (*host_error == 0) *host_error = start_service_locked(h);
+    return 0;
+}
+
+/* Identify data at the offsets of the NVMe specification (the ones the reference reads: src/admin.cpp:139-152
+ * for the controller, :189-198 for a namespace). */
+static void identify_ctrl_page(const host_ctrl* h, uint8_t* page)
+{
+    memset(page, 0, 4096);
+    page[0] = 0xde; page[1] = 0x10;                            /* PCI vendor id of the GPU's maker; subsystem vendor 0 */
+    memcpy(page + 4, "BAMB200EMU0000000001", 20);               /* serial number */
+    memset(page + 24, ' ', 40);
+    memcpy(page + 24, "emulated NVMe controller (pinned memory)", 40);
+    memcpy(page + 64, "1.0     ", 8);                           /* firmware revision */
+    page[77] = 8;                                               /* MDTS: 2^8 pages of 4 KiB = 1 MiB, the largest cache page the library accepts */
+    page[512] = 0x66;                                           /* SQES: 64-byte entries required and maximum */
+    page[513] = 0x44;                                           /* CQES: 16-byte entries */
+    const uint16_t maxcmd = 0xffff;                             /* command ids in flight per queue (the field's largest value) */
+    memcpy(page + 514, &maxcmd, 2);
+    const uint32_t nn = 1;
+    memcpy(page + 516, &nn, 4);
+}
+
+static void identify_ns_page(const host_ctrl* h, uint8_t* page)
+{
+    memset(page, 0, 4096);
+    const uint64_t blocks = h->emu->store_bytes / h->emu->lba_bytes;
+    memcpy(page + 0, &blocks, 8);                               /* NSZE */
+    memcpy(page + 8, &blocks, 8);                               /* NCAP */
+    memcpy(page + 16, &blocks, 8);                              /* NUSE */
+    page[25] = 0;                                               /* NLBAF: one format */
+    page[26] = 0;                                               /* FLBAS: format 0 */
+    const uint32_t lbaf0 = log2_of(h->emu->lba_bytes) << 16;    /* no metadata, LBADS in bits 23:16 */
+    memcpy(page + 128, &lbaf0, 4);
+}
+
+/* copy `bytes` bytes to the memory behind a command's PRP1; NVMe status */
+static uint32_t admin_write_out(host_ctrl* h, uint64_t prp1, const void* src, size_t bytes)
+{
+    bool device = false;
+    void* dst = admin_memory(h, prp1, bytes, &device);
+    if (!dst) return ADM_SC_DATA_XFER;
+    if (!device) { memcpy(dst, src, bytes); return 0; }
+    /* GPU memory: a synchronous copy can wait for the device to go idle, which a running service kernel never is */
+    cudaSetDevice(h->emu->device);
+    const bool was_running = h->running;
+    if (was_running) stop_service_locked(h);
+    const cudaError_t e = cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice);
+    if (was_running) start_service_locked(h);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return ADM_SC_DATA_XFER; }
+    return 0;
+}
+
+/* Execute one admin command the way the controller would (nvm_rpc.h:53 in the reference submits it to the
+ * admin queue pair and waits): IDENTIFY (controller, namespace), SET / GET FEATURES "number of queues",
+ * CREATE / DELETE of I/O completion and submission queues, GET LOG PAGE (error, health and firmware logs, all
+ * empty).  The completion is filled in; the return value is 0, an errno, or the packed NVMe status. */
+extern "C" int nvm_raw_rpc(nvm_aq_ref ref, nvm_cmd_t* cmd, nvm_cpl_t* cpl)
+{
+    if (!ref || !cmd || !cpl) return EINVAL;
+    host_ctrl* h = ref->h;
+    std::lock_guard<std::mutex> g(h->lock);
+    const uint32_t opcode = cmd->dword[0] & 0xffu, cid = cmd->dword[0] >> 16, nsid = cmd->dword[1];
+    const uint64_t prp1 = ((uint64_t)cmd->dword[7] << 32) | cmd->dword[6];
+    const uint32_t dw10 = cmd->dword[10], dw11 = cmd->dword[11];
+    uint32_t status = 0, result = 0;
+    int host_error = 0;
+    uint8_t page[4096];
+    switch (opcode) {
+    case 0x06:                                                     /* IDENTIFY: CNS 1 = controller, 0 = namespace */
+        if ((dw10 & 0xff) == 1) identify_ctrl_page(h, page);
+        else if ((dw10 & 0xff) == 0) { if (nsid != 1) { status = ADM_SC_INVALID_NS; break; } identify_ns_page(h, page); }
+        else { status = ADM_SC_INVALID_FIELD; break; }
+        status = admin_write_out(h, prp1, page, sizeof page);
+        break;
+    case 0x09:                                                     /* SET FEATURES */
+    case 0x0a:                                                     /* GET FEATURES */
+        if ((dw10 & 0xff) != 0x07) { status = ADM_SC_INVALID_FIELD; break; }
+        if (opcode == 0x09) {                                      /* requested counts are zero-based */
+            const uint32_t want_sq = (dw11 & 0xffff) + 1, want_cq = (dw11 >> 16) + 1;
+            h->granted_sqs = (uint16_t)(want_sq < NVM_HOST_MAX_QUEUES ? want_sq : NVM_HOST_MAX_QUEUES);
+            h->granted_cqs = (uint16_t)(want_cq < NVM_HOST_MAX_QUEUES ? want_cq : NVM_HOST_MAX_QUEUES);
+        }
+        result = ((uint32_t)(h->granted_cqs - 1) << 16) | (uint32_t)(h->granted_sqs - 1);
+        break;
+    case 0x05: {                                                   /* CREATE I/O COMPLETION QUEUE: physically contiguous only */
+        const uint32_t qs = (dw10 >> 16) + 1;
+        bool device = false;
+        void* mem = (dw11 & 1u) ? admin_memory(h, prp1, (size_t)qs * sizeof(nvm_cpl_t), &device) : nullptr;
+        if (!(dw11 & 1u)) { status = ADM_SC_INVALID_FIELD; break; }
+        if (!mem || device) { status = ADM_SC_DATA_XFER; break; }  /* host-driven queues live in host memory */
+        status = ctrl_cq_create(h, dw10 & 0xffff, qs, prp1);
+        if (status == 0) memset(mem, 0, (size_t)qs * sizeof(nvm_cpl_t));
+        break;
+    }
+    case 0x01: {                                                   /* CREATE I/O SUBMISSION QUEUE */
+        const uint32_t qs = (dw10 >> 16) + 1;
+        bool device = false;
+        void* mem = (dw11 & 1u) ? admin_memory(h, prp1, (size_t)qs * sizeof(nvm_cmd_t), &device) : nullptr;
+        if (!(dw11 & 1u)) { status = ADM_SC_INVALID_FIELD; break; }
+        if (!mem || device) { status = ADM_SC_DATA_XFER; break; }
+        memset(mem, 0, (size_t)qs * sizeof(nvm_cmd_t));
+        status = ctrl_sq_create(h, dw10 & 0xffff, dw11 >> 16, qs, prp1, &host_error);
+        break;
+    }
+    case 0x04: status = ctrl_cq_delete(h, dw10 & 0xffff); break;
+    case 0x00: status = ctrl_sq_delete(h, dw10 & 0xffff, &host_error); break;
+    case 0x02: {                                                   /* GET LOG PAGE: NUMD (zero-based dwords) in 27:16, LID in 7:0 */
+        const uint32_t lid = dw10 & 0xff;
+        const size_t bytes = (size_t)(((dw10 >> 16) & 0xfff) + 1) * 4;
+        if (lid < 1 || lid > 3) { status = ADM_SC_LOG_PAGE_INVALID; break; }
+        if (bytes > sizeof page) { status = ADM_SC_INVALID_FIELD; break; }
+        memset(page, 0, sizeof page);                              /* no errors logged, no wear, one firmware slot */
+        status = admin_write_out(h, prp1, page, bytes);
+        break;
+    }
+    default: status = ADM_SC_INVALID_OPCODE; break;
+    }
+    cpl->dword[0] = result;
+    cpl->dword[1] = 0;
+    cpl->dword[2] = 0;                                             /* admin queue: SQ head 0, SQ id 0 */
+    cpl->dword[3] = cid | (1u << 16) | (status << 17);
+    if (host_error) return host_error;
+    return status ? -(int)status : 0;
+}
+
+/* ---- the admin functions programs call: thin clients of nvm_raw_rpc, as in the reference (src/admin.cpp) --- */
+
+static void admin_command(nvm_cmd_t* cmd, uint8_t opcode, uint32_t nsid, uint64_t prp1, uint32_t dw10, uint32_t dw11)
+{
+    memset(cmd, 0, sizeof *cmd);
+    cmd->dword[0] = opcode;
+    cmd->dword[1] = nsid;
+    cmd->dword[6] = (uint32_t)prp1; cmd->dword[7] = (uint32_t)(prp1 >> 32);
+    cmd->dword[10] = dw10; cmd->dword[11] = dw11;
+}
+
+extern "C" int nvm_admin_ctrl_info(nvm_aq_ref ref, struct nvm_ctrl_info* info, void* buffer, uint64_t ioaddr)
 {
     if (!ref || !info) return EINVAL;
-    if (ns_id != 1) return EINVAL;
+    host_ctrl* h = ref->h;
     memset(info, 0, sizeof *info);
-    info->ns_id = 1;
-    info->lba_data_size = ref->h->emu->lba_bytes;
-    info->size = info->capacity = info->utilization = ref->h->emu->store_bytes / ref->h->emu->lba_bytes;
+    const uint8_t* regs = h->regs_host;
+    const uint64_t cap = *reinterpret_cast<const volatile uint64_t*>(regs);
+    info->nvme_version = *reinterpret_cast<const volatile uint32_t*>(regs + 0x08);
+    info->page_size = h->pub.page_size;
+    info->db_stride = (size_t)1 << h->pub.dstrd;               /* in doorbell registers, as the reference reports it */
+    info->timeout = ((cap >> 24) & 0xff) * 500;
+    info->contiguous = (int)((cap >> 16) & 1);
+    info->max_entries = (uint16_t)((cap & 0xffff) + 1);
+    uint8_t local[4096];
+    const uint8_t* page = local;
+    if (buffer && ioaddr) {                                    /* through the command interface, into the caller's page */
+        nvm_cmd_t cmd; nvm_cpl_t cpl;
+        admin_command(&cmd, 0x06, 0, ioaddr, 1, 0);
+        const int rc = nvm_raw_rpc(ref, &cmd, &cpl);
+        if (rc) return rc;
+        page = static_cast<const uint8_t*>(buffer);
+    } else {
+        std::lock_guard<std::mutex> g(h->lock);
+        identify_ctrl_page(h, local);
+    }
+    memcpy(info->pci_vendor, page, 4);
+    memcpy(info->serial_no, page + 4, 20);
+    memcpy(info->model_no, page + 24, 40);
+    memcpy(info->firmware, page + 64, 8);
+    info->max_data_size = ((size_t)1 << page[77]) * ((size_t)1 << (12 + ((cap >> 48) & 0xf)));
+    info->max_data_pages = info->max_data_size / info->page_size;
+    info->sq_entry_size = (size_t)1 << (page[512] & 0xf);
+    info->cq_entry_size = (size_t)1 << (page[513] & 0xf);
+    uint16_t maxcmd; memcpy(&maxcmd, page + 514, 2);
+    uint32_t nn; memcpy(&nn, page + 516, 4);
+    info->max_out_cmds = maxcmd;
+    info->max_n_ns = nn;
+    return 0;
+}
+
+extern "C" int nvm_admin_ns_info(nvm_aq_ref ref, struct nvm_ns_info* info, uint32_t ns_id, void* buffer, uint64_t ioaddr)
+{
+    if (!ref || !info) return EINVAL;
+    host_ctrl* h = ref->h;
+    memset(info, 0, sizeof *info);
+    uint8_t local[4096];
+    const uint8_t* page = local;
+    if (buffer && ioaddr) {
+        nvm_cmd_t cmd; nvm_cpl_t cpl;
+        admin_command(&cmd, 0x06, ns_id, ioaddr, 0, 0);
+        const int rc = nvm_raw_rpc(ref, &cmd, &cpl);
+        if (rc) return rc;
+        page = static_cast<const uint8_t*>(buffer);
+    } else {
+        if (ns_id != 1) return EINVAL;
+        std::lock_guard<std::mutex> g(h->lock);
+        identify_ns_page(h, local);
+    }
+    info->ns_id = ns_id;
+    uint64_t v;
+    memcpy(&v, page + 0, 8); info->size = v;
+    memcpy(&v, page + 8, 8); info->capacity = v;
+    memcpy(&v, page + 16, 8); info->utilization = v;
+    uint32_t lbaf; memcpy(&lbaf, page + 128 + 4 * (page[26] & 0xf), 4);
+    info->lba_data_size = (size_t)1 << ((lbaf >> 16) & 0xff);
+    info->metadata_size = lbaf & 0xffff;
     return 0;
 }
 
 extern "C" int nvm_admin_set_num_queues(nvm_aq_ref ref, uint16_t n_cqs, uint16_t n_sqs)
 {
     if (!ref || n_cqs == 0 || n_sqs == 0) return EINVAL;
-    ref->h->granted_cqs = n_cqs < NVM_HOST_MAX_QUEUES ? n_cqs : NVM_HOST_MAX_QUEUES;
-    ref->h->granted_sqs = n_sqs < NVM_HOST_MAX_QUEUES ? n_sqs : NVM_HOST_MAX_QUEUES;
-    return 0;
+    nvm_cmd_t cmd; nvm_cpl_t cpl;
+    admin_command(&cmd, 0x09, 0, 0, 0x07, ((uint32_t)(n_cqs - 1) << 16) | (uint32_t)(n_sqs - 1));
+    return nvm_raw_rpc(ref, &cmd, &cpl);
 }
 
 extern "C" int nvm_admin_get_num_queues(nvm_aq_ref ref, uint16_t* n_cqs, uint16_t* n_sqs)
 {
     if (!ref || !n_cqs || !n_sqs) return EINVAL;
-    *n_cqs = ref->h->granted_cqs;
-    *n_sqs = ref->h->granted_sqs;
+    nvm_cmd_t cmd; nvm_cpl_t cpl;
+    admin_command(&cmd, 0x0a, 0, 0, 0x07, 0);
+    const int rc = nvm_raw_rpc(ref, &cmd, &cpl);
+    if (rc) return rc;
+    *n_sqs = (uint16_t)((cpl.dword[0] & 0xffff) + 1);
+    *n_cqs = (uint16_t)((cpl.dword[0] >> 16) + 1);
     return 0;
 }
 
@@ -654,11 +919,10 @@ extern "C" int nvm_admin_request_num_queues(nvm_aq_ref ref, uint16_t* n_cqs, uin
     return nvm_admin_get_num_queues(ref, n_cqs, n_sqs);
 }
 
-static int queue_memory(const nvm_ctrl_t* ctrl, const nvm_dma_t* dma, size_t offset, size_t qs, size_t es, void** host, uint64_t* dev)
+static int queue_memory(const nvm_dma_t* dma, size_t offset, size_t qs, size_t es, void** host, uint64_t* dev)
 {
     if (!dma || !dma->vaddr || !dma->local || offset >= dma->n_ioaddrs) return EINVAL;
     if (qs * es > (dma->n_ioaddrs - offset) * dma->page_size) return EINVAL;
-    (void)ctrl;
     *host = static_cast<uint8_t*>(dma->vaddr) + offset * dma->page_size;
     *dev = dma->ioaddrs[offset];
     return 0;
@@ -666,94 +930,77 @@ static int queue_memory(const nvm_ctrl_t* ctrl, const nvm_dma_t* dma, size_t off
 
 extern "C" int nvm_admin_cq_create(nvm_aq_ref ref, nvm_queue_t* cq, uint16_t id, const nvm_dma_t* dma, size_t offset, size_t qs)
 {
-    if (!ref || !cq || id == 0 || id > NVM_HOST_MAX_QUEUES) return EINVAL;
+    if (!ref || !cq || id == 0) return EINVAL;
     host_ctrl* h = ref->h;
     if (qs == 0) qs = h->pub.page_size / sizeof(nvm_cpl_t);
-    if (qs < 2 || qs > h->pub.max_qs || (qs & (qs - 1))) return EINVAL;      /* the command processor wants a power of two */
+    if (qs < 2 || qs > 0x10000 || qs > h->pub.max_qs) return EINVAL;
     void* host; uint64_t dev;
-    int rc = queue_memory(&h->pub, dma, offset, qs, sizeof(nvm_cpl_t), &host, &dev);
+    int rc = queue_memory(dma, offset, qs, sizeof(nvm_cpl_t), &host, &dev);
     if (rc) return rc;
-    std::lock_guard<std::mutex> g(h->lock);
-    if (h->have_cq[id]) return EEXIST;
-    memset(host, 0, qs * sizeof(nvm_cpl_t));
-    rc = nvm_queue_clear(cq, &h->pub, true, id, (uint32_t)qs, true, host, dev);
+    nvm_queue_t queue;
+    rc = nvm_queue_clear(&queue, &h->pub, true, id, (uint32_t)qs, true, host, dev);
     if (rc) return rc;
-    h->have_cq[id] = true;
-    h->cq_mem_dev[id] = reinterpret_cast<nvm_cpl_t*>((uintptr_t)dev);
-    h->cq_qs[id] = (uint32_t)qs;
+    nvm_cmd_t cmd; nvm_cpl_t cpl;
+    admin_command(&cmd, 0x05, 0, dev, ((uint32_t)(qs - 1) << 16) | id, 1u);
+    rc = nvm_raw_rpc(ref, &cmd, &cpl);
+    if (rc) return rc;
+    memcpy((void*)cq, &queue, sizeof queue);
     return 0;
 }
 
 extern "C" int nvm_admin_sq_create(nvm_aq_ref ref, nvm_queue_t* sq, const nvm_queue_t* cq, uint16_t id, const nvm_dma_t* dma, size_t offset,
                                    size_t qs)
 {
-    if (!ref || !sq || !cq || id == 0 || id > NVM_HOST_MAX_QUEUES) return EINVAL;
+    if (!ref || !sq || !cq || id == 0) return EINVAL;
     host_ctrl* h = ref->h;
     if (qs == 0) qs = h->pub.page_size / sizeof(nvm_cmd_t);
-    if (qs < 2 || qs > h->pub.max_qs || (qs & (qs - 1))) return EINVAL;
+    if (qs < 2 || qs > 0x10000 || qs > h->pub.max_qs) return EINVAL;
     void* host; uint64_t dev;
-    int rc = queue_memory(&h->pub, dma, offset, qs, sizeof(nvm_cmd_t), &host, &dev);
+    int rc = queue_memory(dma, offset, qs, sizeof(nvm_cmd_t), &host, &dev);
     if (rc) return rc;
-    std::lock_guard<std::mutex> g(h->lock);
-    if (!h->have_cq[cq->no] || h->have_sq[id]) return h->have_sq[id] ? EEXIST : EINVAL;
-    cudaSetDevice(h->emu->device);
-    rc = stop_service_locked(h);
+    nvm_queue_t queue;
+    rc = nvm_queue_clear(&queue, &h->pub, false, id, (uint32_t)qs, true, host, dev);
     if (rc) return rc;
-    memset(host, 0, qs * sizeof(nvm_cmd_t));
-    rc = nvm_queue_clear(sq, &h->pub, false, id, (uint32_t)qs, true, host, dev);
+    nvm_cmd_t cmd; nvm_cpl_t cpl;
+    admin_command(&cmd, 0x01, 0, dev, ((uint32_t)(qs - 1) << 16) | id, ((uint32_t)cq->no << 16) | 1u);
+    rc = nvm_raw_rpc(ref, &cmd, &cpl);
     if (rc) return rc;
-    uint32_t slot = 0;                                     /* position in the table = creation order */
-    for (uint16_t k = 1; k <= NVM_HOST_MAX_QUEUES; k++) if (h->have_sq[k]) slot++;
-    bam_emu_qp_t* e = &h->h_qps[slot];
-    memset(e, 0, sizeof *e);
-    e->sq_mem = reinterpret_cast<nvm_cmd_t*>((uintptr_t)dev);
-    e->cq_mem = h->cq_mem_dev[cq->no];
-    e->sq_db = reinterpret_cast<uint32_t*>(h->regs_dev + NVM_SQ_DBL_OFFSET(id, h->pub.dstrd));
-    e->cq_db = reinterpret_cast<uint32_t*>(h->regs_dev + NVM_CQ_DBL_OFFSET(cq->no, h->pub.dstrd));
-    e->qs = (uint32_t)qs;
-    e->qs_log2 = 0; while ((1u << e->qs_log2) < qs) e->qs_log2++;
-    e->cq_qs = h->cq_qs[cq->no];
-    e->cq_qs_log2 = 0; while ((1u << e->cq_qs_log2) < e->cq_qs) e->cq_qs_log2++;
-    e->sqid = id; e->cqid = cq->no;
-    e->store = h->emu->store_dev; e->store_bytes = h->emu->store_bytes;
-    e->fault = h->d_fault; e->served = h->d_served;
-    *reinterpret_cast<volatile uint32_t*>(h->regs_host + NVM_SQ_DBL_OFFSET(id, h->pub.dstrd)) = 0;
-    *reinterpret_cast<volatile uint32_t*>(h->regs_host + NVM_CQ_DBL_OFFSET(cq->no, h->pub.dstrd)) = 0;
-    h->have_sq[id] = true;
-    rebuild_table(h);
-    return start_service_locked(h);
+    memcpy((void*)sq, &queue, sizeof queue);
+    return 0;
 }
 
 extern "C" int nvm_admin_cq_delete(nvm_aq_ref ref, nvm_queue_t* cq)
 {
-    if (!ref || !cq || cq->no == 0 || cq->no > NVM_HOST_MAX_QUEUES) return EINVAL;
-    std::lock_guard<std::mutex> g(ref->h->lock);
-    ref->h->have_cq[cq->no] = false;
+    if (!ref || !cq || cq->db == nullptr) return EINVAL;
+    nvm_cmd_t cmd; nvm_cpl_t cpl;
+    admin_command(&cmd, 0x04, 0, 0, cq->no, 0);
+    const int rc = nvm_raw_rpc(ref, &cmd, &cpl);
+    if (rc) return rc;
     cq->db = nullptr;
     return 0;
 }
 
 extern "C" int nvm_admin_sq_delete(nvm_aq_ref ref, nvm_queue_t* sq, const nvm_queue_t*)
 {
-    if (!ref || !sq || sq->no == 0 || sq->no > NVM_HOST_MAX_QUEUES) return EINVAL;
-    host_ctrl* h = ref->h;
-    std::lock_guard<std::mutex> g(h->lock);
-    if (!h->have_sq[sq->no]) return EINVAL;
-    cudaSetDevice(h->emu->device);
-    int rc = stop_service_locked(h);
-    /* close the gap in the table */
-    uint32_t slot = 0, n = 0;
-    for (uint16_t k = 1; k <= NVM_HOST_MAX_QUEUES; k++) { if (k == sq->no) slot = n; if (h->have_sq[k]) n++; }
-    for (uint32_t k = slot; k + 1 < n; k++) h->h_qps[k] = h->h_qps[k + 1];
-    h->have_sq[sq->no] = false;
+    if (!ref || !sq || sq->db == nullptr) return EINVAL;
+    nvm_cmd_t cmd; nvm_cpl_t cpl;
+    admin_command(&cmd, 0x00, 0, 0, sq->no, 0);
+    const int rc = nvm_raw_rpc(ref, &cmd, &cpl);
+    if (rc) return rc;
     sq->db = nullptr;
-    rebuild_table(h);
-    if (rc == 0) rc = start_service_locked(h);
-    return rc;
+    return 0;
 }
 
-extern "C" int nvm_raw_rpc(nvm_aq_ref, nvm_cmd_t*, nvm_cpl_t*) { return ENOTSUP; }
-extern "C" int nvm_admin_get_log_page(nvm_aq_ref, uint32_t, void*, uint64_t, uint8_t, uint64_t) { return ENOTSUP; }
+/* `ptr` is where the caller will read the page, `ioaddr` the bus address of the same memory (nvm_admin.h:111-117
+ * in the reference).  One controller page at most; the logs of the emulated controller are empty. */
+extern "C" int nvm_admin_get_log_page(nvm_aq_ref ref, uint32_t ns_id, void* ptr, uint64_t ioaddr, uint8_t log_id, uint64_t log_offset)
+{
+    if (!ref || !ptr || !ioaddr) return EINVAL;
+    nvm_cmd_t cmd; nvm_cpl_t cpl;
+    admin_command(&cmd, 0x02, ns_id, ioaddr, ((uint32_t)(4096 / 4 - 1) << 16) | log_id, 0);
+    cmd.dword[12] = (uint32_t)log_offset; cmd.dword[13] = (uint32_t)(log_offset >> 32);
+    return nvm_raw_rpc(ref, &cmd, &cpl);
+}
 
 /* ---- host-side queue descriptors -------------------------------------------------------------------------- */
 

@@ -7,8 +7,8 @@
  * (nvm_ctrl_t) is made from an emulated controller (nvm_emu_ctrl_init), its "register window"
  * (mm_ptr) is a page of pinned host memory with the doorbell registers at their NVMe offsets, a DMA
  * mapping pins memory and reports device-visible addresses as bus addresses (ioaddr == the address
- * the GPU uses), and the admin functions answer from the emulator's configuration instead of
- * sending admin commands.  I/O queue pairs created with nvm_admin_cq_create / nvm_admin_sq_create
+ * the GPU uses), and admin commands are executed on the host by nvm_raw_rpc, the way the controller
+ * would execute them from its admin queue (there is no admin queue memory to poll).  I/O queue pairs created with nvm_admin_cq_create / nvm_admin_sq_create
  * live in caller memory (a DMA mapping of host memory) and are driven from the HOST with the
  * classic single-threaded queue functions below; their commands are executed by the controller's
  * command processor running as a service kernel on the GPU (started by nvm_admin_sq_create,
@@ -97,7 +97,12 @@ int nvm_admin_cq_create(nvm_aq_ref ref, nvm_queue_t* cq, uint16_t id, const nvm_
 int nvm_admin_cq_delete(nvm_aq_ref ref, nvm_queue_t* cq);
 int nvm_admin_sq_create(nvm_aq_ref ref, nvm_queue_t* sq, const nvm_queue_t* cq, uint16_t id, const nvm_dma_t* dma, size_t offset, size_t qs);
 int nvm_admin_sq_delete(nvm_aq_ref ref, nvm_queue_t* sq, const nvm_queue_t* cq);
-/* Admin pass-through and log pages need a real admin queue: ENOTSUP. */
+/* Admin pass-through (nvm_rpc.h:53 there): the command is executed the way the controller would execute it
+ * from its admin queue -- IDENTIFY (CNS 1 controller, CNS 0 namespace; the page goes to PRP1, which must lie
+ * in memory mapped with nvm_dma_*), SET / GET FEATURES 0x07 (number of queues), CREATE / DELETE I/O completion
+ * and submission queue (contiguous, power-of-two sizes, host memory), GET LOG PAGE 1..3 (empty logs) -- and
+ * the completion is filled in.  Returns 0, an errno, or the packed NVMe status -(SCT << 8 | SC).  The
+ * nvm_admin_* functions above are clients of this call, as in the reference (src/admin.cpp). */
 int nvm_raw_rpc(nvm_aq_ref ref, nvm_cmd_t* cmd, nvm_cpl_t* cpl);
 int nvm_admin_get_log_page(nvm_aq_ref ref, uint32_t ns_id, void* ptr, uint64_t ioaddr, uint8_t log_id, uint64_t log_offset);
 

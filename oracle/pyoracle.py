@@ -30,6 +30,7 @@ def build(force=False):
 REF_WIRE_PATH = os.path.join(HERE, "_ref", "libref_wire.so")
 REF_PQ_PATH = os.path.join(HERE, "_ref", "libref_pq.so")
 REF_CACHE_PATH = os.path.join(HERE, "_ref", "libref_cache.so")
+REF_ADMIN_PATH = os.path.join(HERE, "_ref", "libref_admin.so")
 REFERENCE_ROOT = "/root/reference"
 
 
@@ -38,9 +39,9 @@ def build_ref_wire(force=False):
     they lie) into oracle/_ref/libref_wire.so.  Needs the reference project; returns None without it and
     without a prebuilt library."""
     if os.path.isdir(os.path.join(REFERENCE_ROOT, "include")):
-        srcs = [os.path.join(HERE, f) for f in ("ref_wire.cpp", "ref_pq.cpp", "ref_cache.cpp", "Makefile")]
+        srcs = [os.path.join(HERE, f) for f in ("ref_wire.cpp", "ref_pq.cpp", "ref_cache.cpp", "ref_admin.cpp", "Makefile")]
         srcs.append(os.path.join(HERE, "ref_shim", "simt", "atomic"))
-        built = [REF_WIRE_PATH, REF_PQ_PATH, REF_CACHE_PATH]
+        built = [REF_WIRE_PATH, REF_PQ_PATH, REF_CACHE_PATH, REF_ADMIN_PATH]
         if force or not all(map(os.path.exists, built)) or min(map(os.path.getmtime, built)) < max(map(os.path.getmtime, srcs)):
             subprocess.run(["make", "-C", HERE, "-B", "ref", "REFERENCE=" + REFERENCE_ROOT], check=True, capture_output=True)
     return REF_WIRE_PATH if os.path.exists(REF_WIRE_PATH) else None
@@ -89,6 +90,39 @@ def ref_wire():
         L.refw_opcode.argtypes = [C.c_int, C.c_int, C.c_int]
         _ref_wire = L
     return _ref_wire
+
+
+_ref_admin = None
+
+
+def ref_admin():
+    """ctypes handle of the reference's admin layer (src/admin.cpp) whose nvm_raw_rpc is bound by the caller
+    (refa_bind) to the library under test, or None."""
+    global _ref_admin
+    if _ref_admin is None:
+        build_ref_wire()
+        if not os.path.exists(REF_ADMIN_PATH):
+            return None
+        L = C.CDLL(REF_ADMIN_PATH)
+        u16, u8 = C.c_uint16, C.c_uint8
+        L.refa_bind.argtypes = [vp, vp]
+        L.refa_ctrl_info.argtypes = [vp, vp, vp, u64]
+        L.refa_ns_info.argtypes = [vp, vp, u32, vp, u64]
+        L.refa_request_num_queues.argtypes = [vp, C.POINTER(u16), C.POINTER(u16)]
+        L.refa_get_num_queues.argtypes = [vp, C.POINTER(u16), C.POINTER(u16)]
+        L.refa_queue_alloc.restype = vp
+        L.refa_queue_free.argtypes = [vp]
+        L.refa_queue_qs.restype = u32
+        L.refa_queue_qs.argtypes = [vp]
+        L.refa_queue_doorbell_offset.restype = u64
+        L.refa_queue_doorbell_offset.argtypes = [vp, vp]
+        L.refa_cq_create.argtypes = [vp, vp, u16, vp, u64, u64]
+        L.refa_sq_create.argtypes = [vp, vp, vp, u16, vp, u64, u64]
+        L.refa_cq_delete.argtypes = [vp, vp]
+        L.refa_sq_delete.argtypes = [vp, vp, vp]
+        L.refa_rw.argtypes = [vp, vp, u8, u32, u64, u64, u16, u64]
+        _ref_admin = L
+    return _ref_admin
 
 
 _ref_pq = None

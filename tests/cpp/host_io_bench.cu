@@ -20,6 +20,7 @@
 #include <nvm_cmd.h>
 #include <nvm_error.h>
 #include <nvm_util.h>
+#include <nvm_rpc.h>
 #include "bam_synth.h"
 
 #define CHECK(x) do { int rc_ = (x); if (rc_) { fprintf(stderr, "%s failed: %s\n", #x, nvm_strerror(rc_)); return 1; } } while (0)
@@ -197,13 +198,67 @@ int main()
     const int st_remap = one(NVM_IO_READ, 4000, 2, dp);
     bad_handles += st_remap != 0 || memcmp(buf->vaddr, media + 4000 * page / 8, 2 * page) != 0;
 
+    /* ---- admin commands through the pass-through: what the controller answers, and what it refuses ------------ */
+    int bad_admin = 0;
+    {
+        nvm_cmd_t ac; nvm_cpl_t ap;
+        uint8_t* apage = (uint8_t*)NVM_DMA_OFFSET(aq_mem, 1);
+        memset(&ac, 0, sizeof ac);
+        nvm_cmd_header(&ac, 77, NVM_ADMIN_IDENTIFY, 0);
+        nvm_cmd_data_ptr(&ac, aq_mem->ioaddrs[1], 0);
+        ac.dword[10] = 1;                                                  /* identify controller */
+        memset(apage, 0xee, page);
+        bad_admin += nvm_raw_rpc(aq, &ac, &ap) != 0 || !NVM_ERR_OK(&ap) || *NVM_CPL_CID(&ap) != 77;
+        bad_admin += memcmp(apage + 4, ci.serial_no, 20) != 0 || memcmp(apage + 24, ci.model_no, 40) != 0 || apage[77] != 8 ||
+                     apage[512] != 0x66 || apage[513] != 0x44 || ci.max_data_size != (1u << 20) || ci.nvme_version != 0x00010400;
+        ac.dword[10] = 0; ac.dword[1] = 1;                                 /* identify namespace 1, into GPU memory */
+        nvm_cmd_data_ptr(&ac, devbuf->ioaddrs[0], 0);
+        bad_admin += nvm_raw_rpc(aq, &ac, &ap) != 0;
+        uint64_t nsze = 0;
+        cudaMemcpy(&nsze, d_mem, 8, cudaMemcpyDeviceToHost);
+        bad_admin += nsze != ni.size;
+        ac.dword[1] = 2;                                                   /* no such namespace */
+        bad_admin += nvm_raw_rpc(aq, &ac, &ap) != -0x00b;
+        memset(&ac, 0, sizeof ac);
+        nvm_cmd_header(&ac, 1, NVM_ADMIN_GET_FEATURES, 0);
+        ac.dword[10] = 0x07;
+        bad_admin += nvm_raw_rpc(aq, &ac, &ap) != 0 || ap.dword[0] != ((3u << 16) | 3u);       /* 4 + 4 queues, zero-based */
+        ac.dword[10] = 0x02;                                               /* a feature the controller does not have */
+        bad_admin += nvm_raw_rpc(aq, &ac, &ap) != -0x002;
+        memset(&ac, 0, sizeof ac);
+        nvm_cmd_header(&ac, 2, 0x7f, 0);
+        bad_admin += nvm_raw_rpc(aq, &ac, &ap) != -0x001 || NVM_ERR_SC(&ap) != 0x01;
+        /* queue 9 was never granted; queue 1 exists; the completion queue cannot go while its submission queue lives */
+        nvm_queue_t extra;
+        memset(&extra, 0, sizeof extra);
+        extra.no = 7;                                                      /* stands for a completion queue that does not exist */
+        bad_admin += nvm_admin_cq_create(aq, &extra, 9, list_mem, 0, 0) != -0x101;
+        bad_admin += nvm_admin_cq_create(aq, &extra, 1, list_mem, 0, 0) != -0x101;
+        nvm_queue_t cq_copy = cq;
+        bad_admin += nvm_admin_cq_delete(aq, &cq_copy) != -0x10c || strstr(nvm_strerror(-0x10c), "deletion") == NULL;
+        bad_admin += nvm_admin_sq_create(aq, &extra, &extra, 2, list_mem, 0, 0) != -0x100;       /* no such completion queue */
+        /* a queue in memory the controller was never given */
+        memset(&ac, 0, sizeof ac);
+        nvm_cmd_header(&ac, 3, NVM_ADMIN_CREATE_CQ, 0);
+        nvm_cmd_data_ptr(&ac, (uint64_t)(uintptr_t)&ac, 0);
+        ac.dword[10] = (255u << 16) | 2; ac.dword[11] = 1;
+        bad_admin += nvm_raw_rpc(aq, &ac, &ap) != -0x004;
+        /* log pages: empty health log; an unknown log id */
+        memset(apage, 0xee, page);
+        bad_admin += nvm_admin_get_log_page(aq, NVM_CMD_NS_ALL, apage, aq_mem->ioaddrs[1], 2, 0) != 0 || apage[0] != 0 || apage[4095] != 0;
+        bad_admin += nvm_admin_get_log_page(aq, NVM_CMD_NS_ALL, apage, aq_mem->ioaddrs[1], 9, 0) != -0x109;
+        /* I/O still works after all of this */
+        bad_multi += nvm_cmd_data(&dp, 0, NULL, 1, &buf->ioaddrs[3]) != 1;
+        bad_admin += one(NVM_IO_READ, 77, 1, dp) != 0 || memcmp(NVM_DMA_OFFSET(buf, 3), media + 77 * page / 8, page) != 0;
+    }
+
     printf("{\"page_size\": %zu, \"max_entries\": %u, \"sq_entry\": %zu, \"cq_entry\": %zu, \"ns_blocks\": %zu, \"lba\": %zu, \"queues\": [%u, %u], "
            "\"sq_depth\": %u, \"cq_depth\": %u, \"bad_read\": %d, \"bad_write\": %d, \"bad_neighbours\": %d, \"bad_device_read\": %d, "
            "\"bad_status\": %d, \"oob_status\": %u, \"oob_cid\": %u, \"bad_multi\": %d, \"st_two\": %d, \"st_list\": %d, \"st_chain\": %d, "
-           "\"st_foreign\": %d, \"foreign_text\": \"%s\", \"bad_handles\": %d}\n",
+           "\"st_foreign\": %d, \"foreign_text\": \"%s\", \"bad_handles\": %d, \"bad_admin\": %d}\n",
            ci.page_size, (unsigned)ci.max_entries, ci.sq_entry_size, ci.cq_entry_size, ni.size, ni.lba_data_size, n_cqs, n_sqs, sq.qs, cq.qs,
            bad_read, bad_write, bad_own, bad_dev, bad_status, oob_status, oob_cid, bad_multi, st_two, st_list, st_chain, st_foreign,
-           nvm_strerror(st_foreign), bad_handles);
+           nvm_strerror(st_foreign), bad_handles, bad_admin);
 
     CHECK(nvm_admin_sq_delete(aq, &sq, &cq));
     CHECK(nvm_admin_cq_delete(aq, &cq));

@@ -77,4 +77,6 @@ def test_cpp_host_libnvm_io(cuda, bam):
     assert r["st_foreign"] == -0x04 and "transfer" in r["foreign_text"]
     # nvm_raw_ctrl_init over the register window, nvm_ctrl_from_dma / _from_aq_ref, nvm_dma_remap outliving its original
     assert r["bad_handles"] == 0
+    # nvm_raw_rpc: identify (into host and into GPU memory), features, refused opcodes / queue ids / memory, log pages
+    assert r["bad_admin"] == 0
 

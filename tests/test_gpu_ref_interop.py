@@ -272,3 +272,98 @@ def test_device_command_encoding_equals_the_reference_builders(cuda, bam, orc):
         ref.refw_encode_rw(cidv, opc, ns, prp1, prp2, lba, nb, want)
         assert lib.bam_encode_rw_command(got, cidv, opc, ns, prp1, prp2, lba, nb, 1) == 0
         assert bytes(got) == bytes(want)
+
+
+class NvmCtrlInfo(C.Structure):                   # struct nvm_ctrl_info (include/nvm_types.h:198-216 of the reference)
+    _fields_ = [("nvme_version", u32), ("page_size", C.c_size_t), ("db_stride", C.c_size_t), ("timeout", u64), ("contiguous", C.c_int),
+                ("max_entries", u16), ("pci_vendor", u8 * 4), ("serial_no", C.c_char * 20), ("model_no", C.c_char * 40),
+                ("firmware", C.c_char * 8), ("max_data_size", C.c_size_t), ("max_data_pages", C.c_size_t), ("cq_entry_size", C.c_size_t),
+                ("sq_entry_size", C.c_size_t), ("max_out_cmds", C.c_size_t), ("max_n_ns", C.c_size_t)]
+
+
+class NvmNsInfo(C.Structure):                     # struct nvm_ns_info (:225-233 there)
+    _fields_ = [("ns_id", u32), ("size", C.c_size_t), ("capacity", C.c_size_t), ("utilization", C.c_size_t),
+                ("lba_data_size", C.c_size_t), ("metadata_size", C.c_size_t)]
+
+
+def test_reference_admin_layer_over_the_pass_through(cuda, bam, orc):
+    """The reference's whole host stack above nvm_raw_rpc -- src/admin.cpp building the admin commands and parsing
+    the identify pages, src/queue.cpp setting the queue descriptors up, include/nvm_queue.h driving them --
+    compiled from the reference's sources (oracle/_ref/libref_admin.so), with nvm_raw_rpc bound to this
+    library: the emulated controller executes the admin commands and then serves the queue pair the
+    reference's code created."""
+    ra = orc.ref_admin()
+    if ra is None:
+        pytest.skip("the reference's admin layer is not built (needs the reference project)")
+    lib = bam.load()
+    for name, args in (("nvm_emu_ctrl_init", [C.POINTER(vp), vp]), ("nvm_aq_create", [C.POINTER(vp), vp, vp]),
+                       ("nvm_dma_create", [C.POINTER(vp), vp, C.c_size_t]), ("nvm_admin_ctrl_info", [vp, vp, vp, u64]),
+                       ("nvm_admin_ns_info", [vp, vp, u32, vp, u64]), ("nvm_admin_get_num_queues", [vp, C.POINTER(u16), C.POINTER(u16)])):
+        getattr(lib, name).argtypes = args
+        getattr(lib, name).restype = C.c_int
+    for name in ("nvm_dma_unmap", "nvm_aq_destroy", "nvm_ctrl_free"):
+        getattr(lib, name).argtypes = [vp]
+        getattr(lib, name).restype = None
+    ra.refa_bind(C.cast(lib.nvm_raw_rpc, vp), C.cast(lib.nvm_ctrl_from_aq_ref, vp))
+
+    n_media_pages, seed = 2048, 91
+    emu = bam.Controller(n_media_pages * PAGE, 0, queue_depth=64, num_queues=1)
+    emu.set_launch_timeout(60 * 1_000_000_000)               # the service kernel leaves after a minute at most
+    media = emu.store_numpy()
+    media[:] = orc.fill_store(seed, 0, n_media_pages * 512)
+    nctrl, aq, qmem, buf = vp(), vp(), vp(), vp()
+    assert lib.nvm_emu_ctrl_init(C.byref(nctrl), emu.h) == 0
+    ctrl = NvmCtrl.from_address(nctrl.value)
+    assert lib.nvm_aq_create(C.byref(aq), nctrl, None) == 0
+    assert lib.nvm_dma_create(C.byref(qmem), nctrl, 2 * PAGE) == 0
+    assert lib.nvm_dma_create(C.byref(buf), nctrl, 4 * PAGE) == 0
+    bd = NvmDma.from_address(buf.value)
+    b_io = ioaddrs(buf, 4)
+
+    # identify: the reference's parse of the pages the controller returns == this library's own answer
+    theirs, mine = NvmCtrlInfo(), NvmCtrlInfo()
+    assert ra.refa_ctrl_info(aq, C.byref(theirs), bd.vaddr, b_io[0]) == 0
+    assert lib.nvm_admin_ctrl_info(aq, C.byref(mine), bd.vaddr + PAGE, b_io[1]) == 0
+    assert bytes(theirs) == bytes(mine)
+    assert (theirs.nvme_version, theirs.page_size, theirs.max_entries, theirs.timeout, theirs.contiguous) == (0x00010400, 4096, 1024, 5000, 1)
+    assert (theirs.max_data_size, theirs.sq_entry_size, theirs.cq_entry_size, theirs.max_n_ns) == (1 << 20, 64, 16, 1)
+    assert theirs.serial_no.startswith(b"BAMB200EMU")
+    ns_theirs, ns_mine = NvmNsInfo(), NvmNsInfo()
+    assert ra.refa_ns_info(aq, C.byref(ns_theirs), 1, bd.vaddr, b_io[0]) == 0
+    assert lib.nvm_admin_ns_info(aq, C.byref(ns_mine), 1, bd.vaddr + PAGE, b_io[1]) == 0
+    assert bytes(ns_theirs) == bytes(ns_mine)
+    assert (ns_theirs.size, ns_theirs.lba_data_size, ns_theirs.metadata_size) == (n_media_pages * 8, 512, 0)
+    assert ra.refa_ns_info(aq, C.byref(ns_theirs), 3, bd.vaddr, b_io[0]) == -0x00b          # invalid namespace, as a packed status
+
+    # number of queues: set by the reference's code (3 completion, 5 submission queues), read back by both.  The
+    # controller answers as the NVMe specification lays the result out (completion queues in the upper half);
+    # the reference reads the halves the other way round (src/admin.cpp:466-467, 503-504), on any controller
+    ncq, nsq = u16(3), u16(5)
+    assert ra.refa_request_num_queues(aq, C.byref(ncq), C.byref(nsq)) == 0 and (ncq.value, nsq.value) == (5, 3)
+    ncq2, nsq2 = u16(), u16()
+    assert lib.nvm_admin_get_num_queues(aq, C.byref(ncq2), C.byref(nsq2)) == 0 and (ncq2.value, nsq2.value) == (3, 5)
+
+    # a queue pair created by the reference's code (its descriptors, its commands), page-sized defaults
+    rcq, rsq, extra = ra.refa_queue_alloc(), ra.refa_queue_alloc(), ra.refa_queue_alloc()
+    assert ra.refa_cq_create(aq, extra, 9, qmem, 0, 0) == -0x101                              # queue 9 was never granted
+    assert ra.refa_cq_create(aq, rcq, 1, qmem, 0, 0) == 0 and ra.refa_queue_qs(rcq) == 256
+    assert ra.refa_sq_create(aq, rsq, rcq, 1, qmem, 1, 0) == 0 and ra.refa_queue_qs(rsq) == 64
+    assert ra.refa_queue_doorbell_offset(rsq, ctrl.mm_ptr) == 0x1008 and ra.refa_queue_doorbell_offset(rcq, ctrl.mm_ptr) == 0x100c
+    assert ra.refa_cq_delete(aq, rcq) == -0x10c                                               # its submission queue still exists
+    data = np.frombuffer((C.c_uint8 * (4 * PAGE)).from_address(bd.vaddr), dtype=np.uint64)
+    for k in range(150):                                                                      # more than two wraps of the 64-entry SQ
+        page = (k * 37) % n_media_pages
+        assert ra.refa_rw(rsq, rcq, 2, 1, b_io[k & 3], page * 8, 8, 5000) == 0, k
+        assert (data[(k & 3) * 512:(k & 3) * 512 + 512] == media[page * 512:(page + 1) * 512]).all(), k
+    data[:512] = orc.fill_store(seed + 1, 0, 512)
+    assert ra.refa_rw(rsq, rcq, 1, 1, b_io[0], 700 * 8, 8, 5000) == 0                         # WRITE
+    assert (media[700 * 512:701 * 512] == orc.fill_store(seed + 1, 0, 512)).all()
+    assert ra.refa_rw(rsq, rcq, 2, 1, b_io[0], n_media_pages * 8, 8, 5000) == -0x80           # LBA out of range
+    assert ra.refa_sq_delete(aq, rsq, rcq) == 0 and ra.refa_cq_delete(aq, rcq) == 0
+    del data
+    for q in (rcq, rsq, extra):
+        ra.refa_queue_free(q)
+    lib.nvm_dma_unmap(buf); lib.nvm_dma_unmap(qmem)
+    lib.nvm_aq_destroy(aq)
+    lib.nvm_ctrl_free(nctrl)
+    emu.close()
