@@ -8,7 +8,7 @@
  * path.  The restatement below is pinned by (a) published known-answer vectors of the generators it
  * shares with the device code (SplitMix64, PCG32, CRC-32), (b) independent numpy / zlib / scipy
  * re-computations, and (c) the reference's OWN code for this path, compiled for the host from its
- * sources where they lie (Makefile target `ref`, glue in ref_wire.cpp / ref_pq.cpp / ref_cache.cpp) and
+ * sources where they lie (Makefile target `ref`, glue in ref_wire.cpp / ref_pq.cpp / ref_cache.cpp / ref_admin.cpp) and
  * run beside it in the test-suite: command encoding byte for byte, its parallel queue code against the
  * controller below, its cache + array read path against ref_array_read on the same access lists (same
  * checksum, hits, misses and page reads).
