@@ -81,6 +81,7 @@ SIGNATURES = {
     "bam_gen_block_pages": (ci, [vp, u64, u64, u64, vp]),
     "bam_direct_page_sums": (ci, [vp, u64, u64, u32, vp, vp]),
     "bam_direct_checksum": (ci, [vp, u64, u64, u64, vp, vp]),
+    "bam_identify_page": (ci, [u32, u64, u32, vp]),
     "bam_encode_rw_command": (ci, [vp, C.c_uint16, C.c_uint8, u32, u64, u64, u64, C.c_uint16, ci]),
     "bam_launch_geometry": (ci, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
 }

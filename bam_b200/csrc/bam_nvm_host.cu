@@ -691,7 +691,7 @@ static uint32_t ctrl_sq_delete(host_ctrl* h, uint32_t id, int* host_error)
 
 /* Identify data at the offsets of the NVMe specification (the ones the reference reads: src/admin.cpp:139-152
  * for the controller, :189-198 for a namespace). */
-static void identify_ctrl_page(const host_ctrl* h, uint8_t* page)
+static void identify_ctrl_page(uint8_t* page)
 {
     memset(page, 0, 4096);
     page[0] = 0xde; page[1] = 0x10;                            /* PCI vendor id of the GPU's maker; subsystem vendor 0 */
@@ -708,17 +708,28 @@ static void identify_ctrl_page(const host_ctrl* h, uint8_t* page)
     memcpy(page + 516, &nn, 4);
 }
 
-static void identify_ns_page(const host_ctrl* h, uint8_t* page)
+static void identify_ns_page(uint64_t store_bytes, uint32_t lba_bytes, uint8_t* page)
 {
     memset(page, 0, 4096);
-    const uint64_t blocks = h->emu->store_bytes / h->emu->lba_bytes;
+    const uint64_t blocks = store_bytes / lba_bytes;
     memcpy(page + 0, &blocks, 8);                               /* NSZE */
     memcpy(page + 8, &blocks, 8);                               /* NCAP */
     memcpy(page + 16, &blocks, 8);                              /* NUSE */
     page[25] = 0;                                               /* NLBAF: one format */
     page[26] = 0;                                               /* FLBAS: format 0 */
-    const uint32_t lbaf0 = log2_of(h->emu->lba_bytes) << 16;    /* no metadata, LBADS in bits 23:16 */
+    const uint32_t lbaf0 = log2_of(lba_bytes) << 16;    /* no metadata, LBADS in bits 23:16 */
     memcpy(page + 128, &lbaf0, 4);
+}
+
+/* The identify page an emulated controller answers with (cns 1: controller; cns 0: namespace 1 of a store of
+ * store_bytes bytes in logical blocks of lba_bytes), without a controller or a GPU. */
+extern "C" int bam_identify_page(uint32_t cns, uint64_t store_bytes, uint32_t lba_bytes, void* out4096)
+{
+    if (!out4096 || cns > 1) return BAM_EINVAL;
+    if (cns == 1) { identify_ctrl_page(static_cast<uint8_t*>(out4096)); return BAM_OK; }
+    if (lba_bytes < 512 || (lba_bytes & (lba_bytes - 1)) || store_bytes < lba_bytes) return BAM_EINVAL;
+    identify_ns_page(store_bytes, lba_bytes, static_cast<uint8_t*>(out4096));
+    return BAM_OK;
 }
 
 /* copy `bytes` bytes to the memory behind a command's PRP1; NVMe status */
@@ -755,8 +766,8 @@ extern "C" int nvm_raw_rpc(nvm_aq_ref ref, nvm_cmd_t* cmd, nvm_cpl_t* cpl)
     uint8_t page[4096];
     switch (opcode) {
     case 0x06:                                                     /* IDENTIFY: CNS 1 = controller, 0 = namespace */
-        if ((dw10 & 0xff) == 1) identify_ctrl_page(h, page);
-        else if ((dw10 & 0xff) == 0) { if (nsid != 1) { status = ADM_SC_INVALID_NS; break; } identify_ns_page(h, page); }
+        if ((dw10 & 0xff) == 1) identify_ctrl_page(page);
+        else if ((dw10 & 0xff) == 0) { if (nsid != 1) { status = ADM_SC_INVALID_NS; break; } identify_ns_page(h->emu->store_bytes, h->emu->lba_bytes, page); }
         else { status = ADM_SC_INVALID_FIELD; break; }
         status = admin_write_out(h, prp1, page, sizeof page);
         break;
@@ -845,7 +856,7 @@ extern "C" int nvm_admin_ctrl_info(nvm_aq_ref ref, struct nvm_ctrl_info* info, v
         page = static_cast<const uint8_t*>(buffer);
     } else {
         std::lock_guard<std::mutex> g(h->lock);
-        identify_ctrl_page(h, local);
+        identify_ctrl_page(local);
     }
     memcpy(info->pci_vendor, page, 4);
     memcpy(info->serial_no, page + 4, 20);
@@ -878,7 +889,7 @@ extern "C" int nvm_admin_ns_info(nvm_aq_ref ref, struct nvm_ns_info* info, uint3
     } else {
         if (ns_id != 1) return EINVAL;
         std::lock_guard<std::mutex> g(h->lock);
-        identify_ns_page(h, local);
+        identify_ns_page(h->emu->store_bytes, h->emu->lba_bytes, local);
     }
     info->ns_id = ns_id;
     uint64_t v;

@@ -307,6 +307,10 @@ int bam_direct_checksum(const uint64_t* idx_dev, uint64_t n, uint64_t store_seed
                         uint64_t* sum_out_dev, void* stream);
 
 /* Grid the launchers use: total blocks, controller blocks among them, threads per block. */
+/* The 4096-byte IDENTIFY page an emulated controller returns (cns 1: controller data; cns 0: namespace 1 of a
+ * store of store_bytes bytes in logical blocks of lba_bytes), at the offsets of the NVMe specification that the
+ * reference parses (src/admin.cpp:139-152, :189-198).  Needs no controller and no GPU. */
+int bam_identify_page(uint32_t cns, uint64_t store_bytes, uint32_t lba_bytes, void* out4096);
 /* The 64-byte NVMe read/write command the library writes into a submission queue for these fields
  * (nvm_cmd_header / nvm_cmd_data_ptr / nvm_cmd_rw_blks, include/nvm_cmd.h:54-88), for checks against
  * other encoders; on_device != 0 runs the register-built form in a kernel. */

@@ -469,3 +469,75 @@ def test_reference_cache_code_with_concurrent_threads(orc):
     assert ref.accesses == len(idx) and ref.hits + ref.misses == len(idx) and ref.read_ios == ref.misses
     assert all(s > 0 for s in served)                       # thread number mod 3 picks the queue pair, as smid does
 
+
+
+def test_reference_admin_layer_parses_the_identify_pages(orc, bam):
+    """The reference's admin layer (src/admin.cpp compiled into oracle/_ref/libref_admin.so) over a controller
+    played by a Python callback: its IDENTIFY commands are answered with the pages the emulated controller
+    returns (bam_identify_page, which needs no GPU), its register reads go to a window laid out as the
+    library lays its own out; what it parses must be the configuration."""
+    ra = orc.ref_admin()
+    if ra is None:
+        pytest.skip("the reference's admin layer is not built (needs the reference project)")
+    lib = bam.load()
+    u8, u16, u32, u64, vp = C.c_uint8, C.c_uint16, C.c_uint32, C.c_uint64, C.c_void_p
+
+    class NvmCtrl(C.Structure):
+        _fields_ = [("page_size", C.c_size_t), ("dstrd", u8), ("timeout", u64), ("max_qs", u32), ("mm_size", C.c_size_t), ("mm_ptr", vp)]
+
+    class CtrlInfo(C.Structure):
+        _fields_ = [("nvme_version", u32), ("page_size", C.c_size_t), ("db_stride", C.c_size_t), ("timeout", u64), ("contiguous", C.c_int),
+                    ("max_entries", u16), ("pci_vendor", u8 * 4), ("serial_no", C.c_char * 20), ("model_no", C.c_char * 40),
+                    ("firmware", C.c_char * 8), ("max_data_size", C.c_size_t), ("max_data_pages", C.c_size_t), ("cq_entry_size", C.c_size_t),
+                    ("sq_entry_size", C.c_size_t), ("max_out_cmds", C.c_size_t), ("max_n_ns", C.c_size_t)]
+
+    class NsInfo(C.Structure):
+        _fields_ = [("ns_id", u32), ("size", C.c_size_t), ("capacity", C.c_size_t), ("utilization", C.c_size_t),
+                    ("lba_data_size", C.c_size_t), ("metadata_size", C.c_size_t)]
+
+    regs = np.zeros(0x2000, dtype=np.uint8)                     # CAP: MQES 1023, CQR, TO 10 x 500 ms, DSTRD 0, NVM command set; VS 1.4
+    regs[:8].view(np.uint64)[0] = 1023 | (1 << 16) | (10 << 24) | (1 << 37)
+    regs[8:12].view(np.uint32)[0] = 0x00010400
+    ctrl = NvmCtrl(4096, 0, 5000, 1024, 0x2000, regs.ctypes.data)
+    granted = {"cq": 64, "sq": 64}
+    seen = []
+
+    for store_bytes, lba in ((1 << 30, 512), (3 << 28, 4096)):
+        def rpc(ref, cmd, cpl, store_bytes=store_bytes, lba=lba):
+            dw = (u32 * 16).from_address(cmd)
+            out = (u32 * 4).from_address(cpl)
+            opcode, prp1 = dw[0] & 0xff, dw[6] | (dw[7] << 32)
+            seen.append(opcode)
+            if opcode == 0x06:
+                if (dw[10] & 0xff) == 0 and dw[1] != 1:
+                    return -0x00b
+                return lib.bam_identify_page(dw[10] & 0xff, store_bytes, lba, prp1)
+            if opcode in (0x09, 0x0a) and (dw[10] & 0xff) == 0x07:
+                if opcode == 0x09:
+                    granted["sq"], granted["cq"] = (dw[11] & 0xffff) + 1, (dw[11] >> 16) + 1
+                out[0] = ((granted["cq"] - 1) << 16) | (granted["sq"] - 1)
+                return 0
+            return -0x001
+
+        rpc_cb = C.CFUNCTYPE(C.c_int, vp, vp, vp)(rpc)
+        from_cb = C.CFUNCTYPE(vp, vp)(lambda ref: C.addressof(ctrl))
+        ra.refa_bind(C.cast(rpc_cb, vp), C.cast(from_cb, vp))
+        page = np.zeros(4096, dtype=np.uint8)
+        info = CtrlInfo()
+        assert ra.refa_ctrl_info(None, C.byref(info), page.ctypes.data, page.ctypes.data) == 0
+        assert (info.nvme_version, info.page_size, info.db_stride, info.timeout, info.contiguous, info.max_entries) == (0x00010400, 4096, 1, 5000, 1, 1024)
+        assert (info.max_data_size, info.max_data_pages, info.sq_entry_size, info.cq_entry_size, info.max_out_cmds, info.max_n_ns) == \
+               (1 << 20, 256, 64, 16, 0xFFFF, 1)
+        assert info.serial_no == b"BAMB200EMU0000000001" and info.model_no.startswith(b"emulated NVMe controller") and info.firmware == b"1.0     "
+        ns = NsInfo()
+        assert ra.refa_ns_info(None, C.byref(ns), 1, page.ctypes.data, page.ctypes.data) == 0
+        assert (ns.ns_id, ns.size, ns.capacity, ns.utilization, ns.lba_data_size, ns.metadata_size) == \
+               (1, store_bytes // lba, store_bytes // lba, store_bytes // lba, lba, 0)
+        assert ra.refa_ns_info(None, C.byref(ns), 2, page.ctypes.data, page.ctypes.data) == -0x00b
+        # the number-of-queues feature: the command carries completion queues in the upper half (as the
+        # specification says), the reference reads the answer's halves the other way round
+        ncq, nsq = u16(3), u16(5)
+        assert ra.refa_request_num_queues(None, C.byref(ncq), C.byref(nsq)) == 0
+        assert (granted["cq"], granted["sq"]) == (3, 5) and (ncq.value, nsq.value) == (5, 3)
+    assert seen.count(0x06) == 6 and seen.count(0x09) == 2
+    assert lib.bam_identify_page(2, 1 << 30, 512, page.ctypes.data) == 22 and lib.bam_identify_page(0, 1 << 30, 500, page.ctypes.data) == 22
