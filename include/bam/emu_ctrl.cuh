@@ -149,9 +149,12 @@ BAM_DEV uint32_t emu_reserve(const bam_emu_d_t& c, uint32_t q, uint32_t want, ui
 }
 
 /* Lane 0 of a processor, after its warp has read the SQ entries [fetch, fetch + n) of queue q: hand them
- * back IN ORDER.  A completion tells the submitter that every entry below its SQ head value is free
- * again, and completions of a later batch may be posted before those of an earlier one; so no batch
- * passes this point before all earlier batches of the queue have read their entries out. */
+ * back IN ORDER.  A completion's SQ-head value says that every entry below it has been consumed, and the
+ * completions of a later batch may be posted before those of an earlier one; with this step the value is
+ * true at the moment it is posted.  (A submitter that consumes completions strictly in queue order -- this
+ * library's reaper, the reference's move_head_cq -- would be safe without it, because completion slots are
+ * reserved in SQ order and an earlier batch posts only after it has read its entries; one that looks ahead
+ * in the completion queue and trusts what it sees there would not.) */
 BAM_DEV void emu_hand_back(const bam_emu_d_t& c, uint32_t q, uint32_t fetch, uint32_t n)
 {
     uint32_t* dec = &c.qps[q].sq_decoded;

@@ -27,6 +27,7 @@
  */
 #define _GNU_SOURCE
 #include <pthread.h>
+#include <unistd.h>
 #include <sched.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -837,6 +838,146 @@ ORC_API uint64_t orc_wire_ctrl_stop(void* h)
     pthread_join(a->thread, 0);
     uint64_t served = a->served;
     free(a);
+    return served;
+}
+
+/* ---- the device controller's way of sharing ONE queue among several processors, for host threads -------
+ * The GPU controller (include/bam/emu_ctrl.cuh) lets several processors serve a queue: a processor takes the
+ * queue's lock only to RESERVE a batch (SQ entries [fetch, fetch + n) and the completion slots
+ * [cqbase, cqbase + n)), reads the entries out after it has let the lock go, hands them back IN ORDER through
+ * the counter sq_decoded, and then executes and completes its commands whenever it gets to them -- so
+ * completions of a later batch may be posted before those of an earlier one.  A completion's SQ-head value
+ * tells the submitter that every entry below it is free again; the ordered hand-back makes that true at the
+ * moment the value is posted.  This model follows the scheme step by step with n_procs threads, stalling at
+ * random between the steps so that later batches overtake earlier ones (counted); the tests run the reference's
+ * parallel queue code against it on shallow queues, where freed entries are overwritten at once.  What the
+ * runs show: the reference's code completes every command exactly once with the right data however the batches
+ * overtake one another.  (They would not show a missing hand-back: the reference frees entries only when its
+ * completion-queue head moves, which it does in queue order, and completion slots are reserved in SQ order.) */
+struct orc_mt_ctrl_s;
+typedef struct { struct orc_mt_ctrl_s* c; uint32_t me; } orc_mt_arg_t;
+typedef struct orc_mt_ctrl_s {
+    orc_wire_ctrl_t base;              /* queue memory, doorbells, media (its thread member is unused)  */
+    uint32_t lock;                     /* held for the reservation only                                  */
+    uint32_t sq_fetch, cq_tail, cq_head;   /* virtual positions, guarded by lock                          */
+    uint32_t sq_decoded;               /* virtual SQ position up to which entries have been read out      */
+    uint32_t batch, n_procs;
+    uint64_t served_mt, batches, overtaken;    /* overtaken: batches that posted while an earlier one had not finished */
+    uint32_t next_seq;                 /* batch sequence numbers, handed out under lock                    */
+    uint32_t oldest_open;              /* lowest sequence number that has not finished posting (model bookkeeping) */
+    uint32_t done_lock;
+    uint8_t done[1024];
+    pthread_t threads[16];
+    uint32_t seeds[16];
+    orc_mt_arg_t args[16];
+} orc_mt_ctrl_t;
+
+
+static void* orc_mt_ctrl_thread(void* p)
+{
+    orc_mt_arg_t* arg = (orc_mt_arg_t*)p;
+    orc_mt_ctrl_t* c = arg->c;
+    orc_wire_ctrl_t* a = &c->base;
+    uint32_t rnd = c->seeds[arg->me];
+    const uint32_t smask = a->sq_qs - 1, cmask = a->cq_qs - 1;
+    ref_cmd_t local[32];
+    unsigned idle = 0;
+    while (!ld_acq(&a->stop)) {
+        /* reserve under the lock */
+        uint32_t n = 0, fetch = 0, cqbase = 0, seq = 0;
+        if (ld_acq(a->sq_db) != (ld_acq(&c->sq_fetch) & smask) && __atomic_exchange_n(&c->lock, 1u, __ATOMIC_ACQUIRE) == 0u) {
+            fetch = c->sq_fetch;
+            const uint32_t tail = ld_acq(a->sq_db), hdb = ld_acq(a->cq_db);
+            c->cq_head += (hdb - c->cq_head) & cmask;
+            cqbase = c->cq_tail;
+            const uint32_t avail = (tail - fetch) & smask, space = cmask - (cqbase - c->cq_head);
+            n = avail < space ? avail : space;
+            if (n > c->batch) n = c->batch;
+            c->cq_tail = cqbase + n;
+            c->sq_fetch = fetch + n;
+            if (n) seq = c->next_seq++;
+            __atomic_store_n(&c->lock, 0u, __ATOMIC_RELEASE);
+        }
+        if (n == 0) { if (++idle > 64) { sched_yield(); idle = 0; } else __builtin_ia32_pause(); continue; }
+        idle = 0;
+        rnd = rnd * 1664525u + 1013904223u;
+        if (((rnd >> 16) & 15u) == 0u) usleep(100);                /* let later batches get well ahead */
+        else if (rnd & 0x10000u) sched_yield();
+        /* read the entries out, outside the lock */
+        for (uint32_t i = 0; i < n; i++) local[i] = a->sq_mem[(fetch + i) & smask];
+        /* hand them back in order */
+        while (ld_acq(&c->sq_decoded) != fetch) { if (ld_acq(&a->stop)) return 0; __builtin_ia32_pause(); }
+        st_rel(&c->sq_decoded, fetch + n);
+        rnd = rnd * 1664525u + 1013904223u;
+        if (rnd & 0x10000u) sched_yield();
+        /* execute and complete, last command first (completion slots are the batch's own) */
+        if (ld_acq(&c->oldest_open) != seq) __atomic_fetch_add(&c->overtaken, 1, __ATOMIC_RELAXED);
+        for (uint32_t k = n; k-- > 0;) {
+            const ref_cmd_t* cmd = &local[k];
+            uint32_t cid = cmd->dword[0] >> 16, opc = cmd->dword[0] & 0x7fu;
+            uint64_t prp1 = ((uint64_t)cmd->dword[7] << 32) | cmd->dword[6];
+            uint64_t slba = ((uint64_t)cmd->dword[11] << 32) | cmd->dword[10];
+            uint64_t bytes = (uint64_t)((cmd->dword[12] & 0xffffu) + 1) * a->lba_bytes;
+            uint32_t status = 0;
+            if (opc != 0x01u && opc != 0x02u) status = 0x01;
+            else if (slba * a->lba_bytes + bytes > a->store_bytes) status = 0x80;
+            else if (opc == 0x02u) memcpy((void*)(uintptr_t)prp1, a->store + slba * a->lba_bytes, bytes);
+            else memcpy(a->store + slba * a->lba_bytes, (const void*)(uintptr_t)prp1, bytes);
+            const uint32_t slot = cqbase + k;
+            ref_cpl_t* e = a->cq_mem + (slot & cmask);
+            const uint32_t phase = (~(slot >> a->cq_qs_log2)) & 1u;
+            e->dword[0] = 0; e->dword[1] = 0;
+            st_rlx(&e->dword[2], ((fetch + n) & smask) | ((uint32_t)a->sqid << 16));
+            st_rel(&e->dword[3], cid | (phase << 16) | (status << 17));
+        }
+        /* bookkeeping of the model only: which batch is the oldest one still being completed */
+        while (__atomic_exchange_n(&c->done_lock, 1u, __ATOMIC_ACQUIRE) != 0u) __builtin_ia32_pause();
+        c->done[seq & 1023u] = 1;
+        while (c->done[c->oldest_open & 1023u]) { c->done[c->oldest_open & 1023u] = 0; st_rel(&c->oldest_open, c->oldest_open + 1); }
+        __atomic_store_n(&c->done_lock, 0u, __ATOMIC_RELEASE);
+        __atomic_fetch_add(&c->served_mt, n, __ATOMIC_RELAXED);
+        __atomic_fetch_add(&c->batches, 1, __ATOMIC_RELAXED);
+    }
+    return 0;
+}
+
+ORC_API void* orc_wire_ctrl_start_mt(const void* sq_mem, void* cq_mem, void* sq_db, void* cq_db, uint32_t sq_qs, uint32_t cq_qs,
+                                     uint16_t sqid, void* store, uint64_t store_bytes, uint32_t lba_bytes, uint32_t n_procs, uint32_t batch)
+{
+    if (n_procs == 0 || n_procs > 16 || batch == 0 || batch > 32) return 0;
+    orc_mt_ctrl_t* c = (orc_mt_ctrl_t*)calloc(1, sizeof *c);
+    if (!c) return 0;
+    orc_wire_ctrl_t* a = &c->base;
+    a->sq_mem = (const ref_cmd_t*)sq_mem; a->cq_mem = (ref_cpl_t*)cq_mem;
+    a->sq_db = (volatile uint32_t*)sq_db; a->cq_db = (volatile uint32_t*)cq_db;
+    a->sq_qs = sq_qs; a->cq_qs = cq_qs; a->sqid = sqid;
+    while ((1u << a->cq_qs_log2) < cq_qs) a->cq_qs_log2++;
+    a->store = (uint8_t*)store; a->store_bytes = store_bytes; a->lba_bytes = lba_bytes;
+    c->batch = batch; c->n_procs = n_procs;
+    for (uint32_t i = 0; i < n_procs; i++) {
+        c->seeds[i] = 12345u + 977u * i;
+        c->args[i].c = c; c->args[i].me = i;
+        if (pthread_create(&c->threads[i], 0, orc_mt_ctrl_thread, &c->args[i]) != 0) {
+            __atomic_store_n(&a->stop, 1, __ATOMIC_RELEASE);
+            for (uint32_t k = 0; k < i; k++) pthread_join(c->threads[k], 0);
+            free(c);
+            return 0;
+        }
+    }
+    return c;
+}
+
+/* Stops the processors; returns the commands served and, through the pointers, the batches taken and how many
+ * of them posted their completions while an earlier batch had not finished posting its own. */
+ORC_API uint64_t orc_wire_ctrl_stop_mt(void* h, uint64_t* batches, uint64_t* overtaken)
+{
+    orc_mt_ctrl_t* c = (orc_mt_ctrl_t*)h;
+    __atomic_store_n(&c->base.stop, 1, __ATOMIC_RELEASE);
+    for (uint32_t i = 0; i < c->n_procs; i++) pthread_join(c->threads[i], 0);
+    const uint64_t served = c->served_mt;
+    if (batches) *batches = c->batches;
+    if (overtaken) *overtaken = c->overtaken;
+    free(c);
     return served;
 }
 

@@ -245,6 +245,10 @@ def lib():
         L.orc_backing_location.argtypes = [u64, u64, u64, u32, C.POINTER(u32)]
         L.orc_wire_ctrl_start.restype = vp
         L.orc_wire_ctrl_start.argtypes = [vp, vp, vp, vp, u32, u32, C.c_uint16, vp, u64, u32]
+        L.orc_wire_ctrl_start_mt.restype = vp
+        L.orc_wire_ctrl_start_mt.argtypes = [vp, vp, vp, vp, u32, u32, C.c_uint16, vp, u64, u32, u32, u32]
+        L.orc_wire_ctrl_stop_mt.restype = u64
+        L.orc_wire_ctrl_stop_mt.argtypes = [vp, C.POINTER(u64), C.POINTER(u64)]
         L.orc_wire_ctrl_stop.restype = u64
         L.orc_wire_ctrl_stop.argtypes = [vp]
         L.orc_encode_rw.argtypes = [C.c_uint16, C.c_uint8, u32, u64, u64, u64, u32, vp]

@@ -541,3 +541,44 @@ def test_reference_admin_layer_parses_the_identify_pages(orc, bam):
         assert (granted["cq"], granted["sq"]) == (3, 5) and (ncq.value, nsq.value) == (5, 3)
     assert seen.count(0x06) == 6 and seen.count(0x09) == 2
     assert lib.bam_identify_page(2, 1 << 30, 512, page.ctypes.data) == 22 and lib.bam_identify_page(0, 1 << 30, 500, page.ctypes.data) == 22
+
+
+@pytest.mark.parametrize("qs,n_procs,batch", [(16, 4, 4), (16, 6, 2), (64, 4, 8), (8, 3, 2)])
+def test_reference_parallel_queue_code_against_several_processors_per_queue(orc, qs, n_procs, batch):
+    """The scheme by which the GPU controller lets several processors serve ONE queue -- reserve a batch under
+    the queue's lock, read the entries out after the lock has gone, hand them back in order, complete whenever
+    ready, so that later batches overtake earlier ones -- restated for host threads (orc_wire_ctrl_start_mt)
+    under the reference's parallel queue code (oracle/_ref/libref_pq.so) on shallow queues: every command
+    completes exactly once with the right data, the reference's counters end at the request count, and a good
+    part of the batches did post out of order."""
+    pq = orc.ref_pq()
+    if pq is None:
+        pytest.skip("the reference's queue code is not built (needs the reference project)")
+    L = orc.lib()
+    n_pages, n_req, seed = 512, 6000, 17
+    regs = np.zeros(0x2000, dtype=np.uint8)
+    qmem = np.zeros(3 * 4096, dtype=np.uint8)
+    base = (qmem.ctypes.data + 4095) // 4096 * 4096            # page 0: CQ, page 1: SQ
+    media = orc.fill_store(seed, 0, n_pages * 512)
+    bufs = np.zeros((n_req, 512), dtype=np.uint64)
+    ctrl = L.orc_wire_ctrl_start_mt(base + 4096, base, regs.ctypes.data + 0x1000 + 8, regs.ctypes.data + 0x1000 + 12, qs, qs, 1,
+                                    media.ctypes.data, media.nbytes, 512, n_procs, batch)
+    assert ctrl
+    pair = pq.refpq_pair_new(regs.ctypes.data, 1, qs, base + 4096, base + 4096, qs, base, base, 1)
+    assert pair
+    pages = np.random.default_rng(qs + n_procs).integers(0, n_pages, n_req, dtype=np.uint64)
+    lbas = np.ascontiguousarray(pages * np.uint64(8))
+    prps = np.ascontiguousarray(bufs.ctypes.data + np.arange(n_req, dtype=np.uint64) * np.uint64(4096))
+    batches, overtaken = C.c_uint64(), C.c_uint64()
+    try:
+        assert pq.refpq_run(pair, 6, 2, lbas.ctypes.data, prps.ctypes.data, 8, n_req, 60000) == 0, "the protocol stalled"
+        assert (bufs == media.reshape(-1, 512)[pages.astype(np.int64)]).all()
+        state = [C.c_uint32() for _ in range(5)]
+        pq.refpq_state(pair, *(C.byref(x) for x in state))
+        sq_head, sq_tail, cq_head, cq_tail, in_ticket = (x.value for x in state)
+        assert in_ticket == n_req and sq_tail == n_req and cq_head == n_req and sq_head == n_req
+    finally:
+        served = L.orc_wire_ctrl_stop_mt(ctrl, C.byref(batches), C.byref(overtaken))
+    assert served == n_req and batches.value >= n_req // batch
+    assert overtaken.value > batches.value // 20                 # the interleavings the model is there for did occur
+    pq.refpq_pair_free(pair)
