@@ -11,6 +11,9 @@
 #include <nvm_admin.h>
 #include <nvm_error.h>
 #include <nvm_cmd.h>
+#include <nvm_dma.h>
+#include <nvm_aq.h>
+#include <nvm_rpc.h>
 #include <string>
 #include <stdexcept>
 #include <vector>
@@ -31,6 +34,41 @@ static_assert(sizeof(nvm_cmd_t) == 64 && sizeof(nvm_cpl_t) == 16, "NVMe entry si
 static_assert(NVM_PAGE_ALIGN(4097, 4096) == 8192 && NVM_PAGE_TO_BLOCK(4096, 512, 3) == 24, "page arithmetic");
 static_assert(NVM_ERR_UNPACK_SCT(-0x281) == 2 && NVM_ERR_UNPACK_SC(-0x281) == 0x81 && NVM_ERR_UNPACK_ERRNO(5) == 5, "status packing");
 static_assert(REPLICATE == 0 && STRIPE == 1, "data_dist_t");
+
+/* the signatures of the reference's host library (include/nvm_ctrl.h:36-76, nvm_dma.h:35-147, nvm_aq.h:23-38,
+ * nvm_admin.h:18-117, nvm_rpc.h:33-53, nvm_queue.h:30-50,220, nvm_util.h:234-250, nvm_error.h:67): a pointer of
+ * the reference's type must accept the function of that name (nvm_admin_cq_create / sq_create: without the
+ * trailing `need_prp` argument, which has a default there and is always physically-contiguous here) */
+static int (*const sig_ctrl_init)(nvm_ctrl_t**, int) = nvm_ctrl_init;
+static int (*const sig_raw_ctrl_init)(nvm_ctrl_t**, volatile void*, size_t) = nvm_raw_ctrl_init;
+static void (*const sig_ctrl_free)(nvm_ctrl_t*) = nvm_ctrl_free;
+static int (*const sig_raw_ctrl_reset)(const nvm_ctrl_t*, uint64_t, uint64_t) = nvm_raw_ctrl_reset;
+static int (*const sig_dma_map)(nvm_dma_t**, const nvm_ctrl_t*, void*, size_t, size_t, const uint64_t*) = nvm_dma_map;
+static int (*const sig_dma_remap)(nvm_dma_t**, const nvm_dma_t*) = nvm_dma_remap;
+static void (*const sig_dma_unmap)(nvm_dma_t*) = nvm_dma_unmap;
+static int (*const sig_dma_map_host)(nvm_dma_t**, const nvm_ctrl_t*, void*, size_t) = nvm_dma_map_host;
+static int (*const sig_dma_map_device)(nvm_dma_t**, const nvm_ctrl_t*, void*, size_t) = nvm_dma_map_device;
+static int (*const sig_dma_create)(nvm_dma_t**, const nvm_ctrl_t*, size_t) = nvm_dma_create;
+static int (*const sig_aq_create)(nvm_aq_ref*, const nvm_ctrl_t*, const nvm_dma_t*) = nvm_aq_create;
+static void (*const sig_aq_destroy)(nvm_aq_ref) = nvm_aq_destroy;
+static int (*const sig_ctrl_info)(nvm_aq_ref, struct nvm_ctrl_info*, void*, uint64_t) = nvm_admin_ctrl_info;
+static int (*const sig_ns_info)(nvm_aq_ref, struct nvm_ns_info*, uint32_t, void*, uint64_t) = nvm_admin_ns_info;
+static int (*const sig_set_nq)(nvm_aq_ref, uint16_t, uint16_t) = nvm_admin_set_num_queues;
+static int (*const sig_get_nq)(nvm_aq_ref, uint16_t*, uint16_t*) = nvm_admin_get_num_queues;
+static int (*const sig_req_nq)(nvm_aq_ref, uint16_t*, uint16_t*) = nvm_admin_request_num_queues;
+static int (*const sig_cq_create)(nvm_aq_ref, nvm_queue_t*, uint16_t, const nvm_dma_t*, size_t, size_t) = nvm_admin_cq_create;
+static int (*const sig_cq_delete)(nvm_aq_ref, nvm_queue_t*) = nvm_admin_cq_delete;
+static int (*const sig_sq_create)(nvm_aq_ref, nvm_queue_t*, const nvm_queue_t*, uint16_t, const nvm_dma_t*, size_t, size_t) = nvm_admin_sq_create;
+static int (*const sig_sq_delete)(nvm_aq_ref, nvm_queue_t*, const nvm_queue_t*) = nvm_admin_sq_delete;
+static int (*const sig_log_page)(nvm_aq_ref, uint32_t, void*, uint64_t, uint8_t, uint64_t) = nvm_admin_get_log_page;
+static int (*const sig_raw_rpc)(nvm_aq_ref, nvm_cmd_t*, nvm_cpl_t*) = nvm_raw_rpc;
+static void (*const sig_rpc_unbind)(nvm_aq_ref) = nvm_rpc_unbind;
+static int (*const sig_queue_clear)(nvm_queue_t*, const nvm_ctrl_t*, bool, uint16_t, uint32_t, bool, volatile void*, uint64_t) = nvm_queue_clear;
+static void (*const sig_queue_reset)(nvm_queue_t*) = nvm_queue_reset;
+static nvm_cpl_t* (*const sig_dequeue_block)(nvm_queue_t*, uint64_t) = nvm_cq_dequeue_block;
+static const nvm_ctrl_t* (*const sig_from_aq)(nvm_aq_ref) = nvm_ctrl_from_aq_ref;
+static const nvm_ctrl_t* (*const sig_from_dma)(const nvm_dma_t*) = nvm_ctrl_from_dma;
+static const char* (*const sig_strerror)(int) = nvm_strerror;
 static_assert(NVM_CMD_OPCODE(0, 0, 2) == NVM_IO_READ && NVM_CMD_OPCODE(0, 0, 1) == NVM_IO_WRITE && NVM_CMD_OPCODE(0, 2, 0) == NVM_IO_WRITE_ZEROES &&
               NVM_CMD_OPCODE(0, 1, 2) == NVM_ADMIN_IDENTIFY && NVM_CMD_OPCODE(0, 2, 1) == NVM_ADMIN_SET_FEATURES, "opcode packing");
 static_assert(NVM_CTRL_MEM_MINSIZE == 0x2000 && sizeof(nvm_prp_list_t) == 32, "register window, list descriptor");
@@ -88,6 +126,11 @@ int main(int argc, char** argv)
     /* host-side helpers: queue sizing, entry fields, status packing, PRP lists (nvm_util.h:157-227, nvm_error.h:15-48,
      * nvm_cmd.h:113-236 of the reference) */
     int bad = 0;
+    bad += !sig_ctrl_init || !sig_raw_ctrl_init || !sig_ctrl_free || !sig_raw_ctrl_reset || !sig_dma_map || !sig_dma_remap || !sig_dma_unmap ||
+           !sig_dma_map_host || !sig_dma_map_device || !sig_dma_create || !sig_aq_create || !sig_aq_destroy || !sig_ctrl_info || !sig_ns_info ||
+           !sig_set_nq || !sig_get_nq || !sig_req_nq || !sig_cq_create || !sig_cq_delete || !sig_sq_create || !sig_sq_delete || !sig_log_page ||
+           !sig_raw_rpc || !sig_rpc_unbind || !sig_queue_clear || !sig_queue_reset || !sig_dequeue_block || !sig_from_aq || !sig_from_dma ||
+           !sig_strerror;
     nvm_ctrl_t hc = {};
     hc.page_size = 4096;
     bad += NVM_SQ_PAGES(&hc, 1024) != 16 || NVM_CQ_PAGES(&hc, 1024) != 4 || NVM_SQ_PAGES(&hc, 64) != 1 || NVM_CQ_PAGES(&hc, 257) != 2;
