@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbam_b200.so")
-SOURCES = ["bam_lib.cu", "bam_noalloc.cu", "bam_graph.cu", "bam_nvm_host.cu"]
+SOURCES = ["bam_lib.cu", "bam_noalloc.cu", "bam_graph.cu", "bam_exchange.cu", "bam_nvm_host.cu"]
 
 
 def _newer_than(target, deps):

@@ -36,7 +36,7 @@ __global__ void k_init_cache(bam_slot_t* slots, uint32_t n_slots, uint32_t* tabl
 {
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint64_t nthr = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = tid; i < n_slots; i += nthr) { slots[i].tag = BAM_TAG_NONE; slots[i].state = 0; slots[i].pad = 0; }
+    for (uint64_t i = tid; i < n_slots; i += nthr) { slots[i].tag = BAM_TAG_NONE; slots[i].state = 0; slots[i].gen = 0; }
     for (uint64_t i = tid; i < n_words; i += nthr) table[i] = (i % BAM_BUCKET_WORDS) ? BAM_ENTRY_EMPTY : 0u;
 }
 
@@ -250,6 +250,7 @@ struct BlockReadWork {
 };
 
 /* ---- array benchmark --------------------------------------------------------------------- */
+#define BAM_ARRAY_READ_BATCH 4
 struct ArrayReadWork {
     range_d_t<uint64_t> r;
     uint64_t n_lanes, reqs_per_lane;
@@ -264,15 +265,30 @@ struct ArrayReadWork {
         const uint32_t queue = (uint32_t)(gid >> 5);
         const uint64_t n_elems = r.count - r.index_start;
         uint64_t sum = 0;
+        uint32_t hits = 0;
+        /* a lane's requests are served BAM_ARRAY_READ_BATCH at a time, so that it has that many
+         * independent look-ups and element loads in flight */
         for (uint64_t lane = gid; lane < n_lanes; lane += nthr) {
             bam_pcg32_t g;
             bam_lane_stream(&g, access_seed, lane);
-            for (uint64_t k = 0; k < reqs_per_lane; k++) {
-                const uint64_t i = idx ? idx[lane * reqs_per_lane + k] : r.index_start + bam_uniform_index(&g, n_elems);
-                sum += range_read<uint64_t>(r, i, queue);
+            for (uint64_t k = 0; k < reqs_per_lane; k += BAM_ARRAY_READ_BATCH) {
+                size_t ii[BAM_ARRAY_READ_BATCH];
+                uint64_t vv[BAM_ARRAY_READ_BATCH];
+                const uint32_t n = reqs_per_lane - k < BAM_ARRAY_READ_BATCH ? (uint32_t)(reqs_per_lane - k) : BAM_ARRAY_READ_BATCH;
+#pragma unroll
+                for (uint32_t b = 0; b < BAM_ARRAY_READ_BATCH; b++) {
+                    ii[b] = r.index_start;
+                    vv[b] = 0;
+                    if (b < n) ii[b] = idx ? idx[lane * reqs_per_lane + k + b] : r.index_start + bam_uniform_index(&g, n_elems);
+                }
+                range_read_n<uint64_t, BAM_ARRAY_READ_BATCH>(r, ii, n, vv, queue, hits);
+#pragma unroll
+                for (uint32_t b = 0; b < BAM_ARRAY_READ_BATCH; b++) if (b < n) sum += vv[b];
             }
         }
         __syncwarp();
+        const uint32_t wh = __reduce_add_sync(0xffffffffu, hits);
+        if (wh && (threadIdx.x & 31u) == 0u) count_hit(r.cache, wh);
         warp_sum_to(sum, sum_out);
     }
 };
@@ -843,7 +859,7 @@ extern "C" int bam_cache_create_multi(bam_cache_t* out, const bam_ctrl_t* ctrls,
 {
     if (!out) return BAM_EINVAL;
     *out = nullptr;
-    if (!ctrls || n_ctrls == 0 || n_ctrls > BAM_MAX_CTRLS || n_pages == 0 || n_pages >= 0xffffffull) return BAM_EINVAL;
+    if (!ctrls || n_ctrls == 0 || n_ctrls > BAM_MAX_CTRLS || n_pages == 0 || n_pages > BAM_MAX_CACHE_SLOTS) return BAM_EINVAL;
     bam_ctrl* ctrl = ctrls[0];
     if (!ctrl) return BAM_EINVAL;
     if (page_size < 512 || (page_size & (page_size - 1)) || page_size < ctrl->lba_bytes || page_size > (1u << 20)) return BAM_EINVAL;

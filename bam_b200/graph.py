@@ -10,7 +10,7 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import check
+from ._lib import BamError, check
 from .host import Array, Controller, PageCache, _ptr
 
 
@@ -188,6 +188,27 @@ class CsrGraph:
                                                 _ptr(curr_visit), _ptr(next_visit), _ptr(changed), _ptr(scanned),
                                                 _ptr(self.scratch), self.scratch_bytes, _ptr(stream)), "bam_launch_cc_sweep")
 
+    # exchange steps of the sharded traversals (bam_exchange.cu); hdr = int64[2], hdrs = int64[2 * world]
+    def frontier_compact(self, label, level_value, out, hdr, stream=None):
+        check(self.ctrl.lib.bam_launch_frontier_compact(self.cache.h, _ptr(label), label.numel(), level_value, _ptr(out),
+                                                        out.numel(), _ptr(hdr), _ptr(stream)), "bam_launch_frontier_compact")
+
+    def frontier_apply(self, label, level_value, recv, stride, hdrs, world, rank, stream=None):
+        check(self.ctrl.lib.bam_launch_frontier_apply(_ptr(label), label.numel(), level_value, _ptr(recv), stride, _ptr(hdrs),
+                                                      world, rank, _ptr(stream)), "bam_launch_frontier_apply")
+
+    def cc_compact(self, comp, next_visit, out, hdr, stream=None):
+        check(self.ctrl.lib.bam_launch_cc_compact(self.cache.h, _ptr(comp), _ptr(next_visit), comp.numel(), _ptr(out),
+                                                  out.numel(), _ptr(hdr), _ptr(stream)), "bam_launch_cc_compact")
+
+    def cc_apply(self, comp, next_visit, own_begin, own_end, recv, stride, hdrs, world, rank, stream=None):
+        check(self.ctrl.lib.bam_launch_cc_apply(_ptr(comp), _ptr(next_visit), comp.numel(), own_begin, own_end, _ptr(recv),
+                                                stride, _ptr(hdrs), world, rank, _ptr(stream)), "bam_launch_cc_apply")
+
+    def cc_dense_flag(self, comp, before_own, next_visit, own_begin, own_end, stream=None):
+        check(self.ctrl.lib.bam_launch_cc_dense_flag(_ptr(comp), _ptr(before_own), _ptr(next_visit), own_begin, own_end,
+                                                     _ptr(stream)), "bam_launch_cc_dense_flag")
+
     def sssp_sweep(self, v_begin, v_end, label, new_cost, scanned=None, v_base=0, stream=None):
         check(self.ctrl.lib.bam_launch_sssp_sweep(self.offsets.h, self.cols.h, self.weights.h, v_begin, v_end, v_base,
                                                   _ptr(label), _ptr(new_cost), _ptr(scanned), _ptr(self.scratch),
@@ -222,50 +243,21 @@ def shard_vertices_by_edges(offsets, world_size, rank):
     return int(cuts[rank].item()), int(cuts[rank + 1].item())
 
 
-def _all_gather_ragged(t, group=None):
-    """All-gather 1-D tensors of different lengths (counts first, then padded payloads).
-    Returns the concatenation over ranks, in rank order."""
-    import torch
+def gather_headers(hdr, hdrs, group=None):
+    """All-gather the 16-byte headers {entries, status} of every rank's send buffer and bring them to the
+    host: the ONE device-to-host read of a level / sweep.  Returns (counts, statuses) as lists."""
     import torch.distributed as dist
-    world = dist.get_world_size(group)
-    cnt = torch.tensor([t.numel()], dtype=torch.int64, device=t.device)
-    cnts = [torch.zeros_like(cnt) for _ in range(world)]
-    dist.all_gather(cnts, cnt, group=group)
-    cnts = [int(c.item()) for c in cnts]
-    mx = max(cnts)
-    if mx == 0:
-        return t[:0]
-    send = torch.zeros(mx, dtype=t.dtype, device=t.device)       # the compaction result goes into the send buffer
-    send[:t.numel()] = t
-    recv = [torch.empty(mx, dtype=t.dtype, device=t.device) for _ in range(world)]
-    dist.all_gather(recv, send, group=group)
-    return torch.cat([r[:c] for r, c in zip(recv, cnts)])
+    dist.all_gather_into_tensor(hdrs, hdr, group=group)
+    h = hdrs.tolist()
+    return h[0::2], h[1::2]
 
 
-def exchange_bfs_frontier(label, level, group=None):
-    """After a BFS level: share the vertices this rank labelled level+1 and apply everybody's.
-    `label` is the replicated int32 view of the u32 labels.  Returns the size of the new frontier
-    over all ranks (0 = the traversal is finished)."""
-    import torch
-    mine = torch.nonzero(label == level + 1).flatten()
-    everyone = _all_gather_ragged(mine, group)
-    if everyone.numel():
-        label[everyone] = level + 1              # first-writer rule is order independent: same value
-    return int(everyone.numel())
-
-
-def exchange_cc_changes(comp, prev, next_visit, group=None):
-    """After a CC sweep: share (vertex, label) of every label this rank lowered, apply everybody's with
-    min, and flag the changed vertices for their owners' next sweep.  Returns the number of changes."""
-    import torch
-    idx = torch.nonzero(comp != prev).flatten()
-    vals = comp[idx]
-    all_idx = _all_gather_ragged(idx, group)
-    all_vals = _all_gather_ragged(vals, group)
-    if all_idx.numel():
-        comp.scatter_reduce_(0, all_idx, all_vals, reduce="amin", include_self=True)
-        next_visit[all_idx] = 1
-    return int(all_idx.numel())
+def raise_on_rank_failure(statuses):
+    """Every rank sees every rank's status code in the gathered headers, so all of them stop together."""
+    bad = [(r, c) for r, c in enumerate(statuses) if c]
+    if bad:
+        r, c = bad[0]
+        raise BamError(int(c), f"rank {r} reported a device-side failure during the traversal")
 
 
 def allreduce_min_u32(t, group=None):
@@ -286,7 +278,8 @@ def u32_less(a, b):
 
 class DistCsrGraph:
     """One rank's shard (a contiguous vertex range and its adjacency lists) of a CSR graph; BFS and
-    CC run level by level with the frontier / the changed labels exchanged by all-gather."""
+    CC run level by level with the frontier / the changed labels exchanged by all-gather (compaction and
+    apply kernels of bam_exchange.cu around the collective; no per-level allocation)."""
 
     def __init__(self, offsets, cols, rank, world_size, cache_pages, cuda_device=0, group=None, weights=None, **kw):
         self.n = offsets.numel() - 1
@@ -372,9 +365,41 @@ class DistCsrGraph:
     def close(self):
         self.local.close()
 
-    def bfs(self, source):
+    def _buffers(self, kind):
+        """Persistent exchange buffers, allocated at the first traversal of a kind: the send buffer the
+        compaction kernel fills (and the collective reads in place), the receive buffer, the headers."""
         import torch
+        buf = getattr(self, "_xbuf", None)
+        if buf is None:
+            buf = self._xbuf = {}
+        if kind not in buf:
+            dev, n, w = self.torch_device, self.n, self.world
+            d = {"hdr": torch.zeros(2, dtype=torch.int64, device=dev), "hdrs": torch.zeros(2 * w, dtype=torch.int64, device=dev)}
+            if kind == "bfs":
+                d["send"] = torch.empty(n, dtype=torch.int32, device=dev)
+                d["recv"] = torch.empty(n * w, dtype=torch.int32, device=dev)
+            else:
+                d["sparse_cap"] = max(1, int(n * self.CC_DENSE_FRACTION))
+                d["send"] = torch.empty(n, dtype=torch.int64, device=dev)
+                d["recv"] = torch.empty(min(n, d["sparse_cap"]) * w, dtype=torch.int64, device=dev)
+                d["before"] = torch.empty(self.v1 - self.v0, dtype=torch.int64, device=dev)
+            buf[kind] = d
+        return buf[kind]
+
+    # a sweep that changed more than CC_DENSE_FRACTION * n labels, summed over the ranks, is exchanged as
+    # one element-wise MIN all-reduce of the replicas instead of (vertex, label) lists
+    CC_DENSE_FRACTION = 0.25
+
+    def bfs(self, source):
+        """Level-synchronous BFS over the sharded graph.  Per level: the rank's fused level launch, the
+        compaction of what it labelled into the send buffer, one all-gather of the headers (the only
+        device-to-host read of the level: sizes, termination, failures), one all-gather of the frontier
+        sized to the largest contribution, and the apply kernel.  Returns (levels, n_levels, edges this
+        rank scanned)."""
+        import torch
+        import torch.distributed as dist
         dev = self.torch_device
+        b = self._buffers("bfs")
         label = torch.full((self.n,), -1, dtype=torch.int32, device=dev)      # 0xFFFFFFFF
         label[source] = 0
         changed = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -382,28 +407,52 @@ class DistCsrGraph:
         level = 0
         while True:
             self.local.bfs_level(0, self.v1 - self.v0, level, label, changed, scanned, v_base=self.v0)
-            self.local.ctrl.check_status()
-            if exchange_bfs_frontier(label, level, self.group) == 0:
+            self.local.frontier_compact(label, level + 1, b["send"], b["hdr"])
+            counts, statuses = gather_headers(b["hdr"], b["hdrs"], self.group)
+            raise_on_rank_failure(statuses)
+            if sum(counts) == 0:
                 break
+            mx = max(counts)
+            dist.all_gather_into_tensor(b["recv"][:mx * self.world], b["send"][:mx], group=self.group)
+            self.local.frontier_apply(label, level + 1, b["recv"], mx, b["hdrs"], self.world, self.rank)
             level += 1
         return label, level + 1, int(scanned.item())
 
     def cc(self):
+        """Label-propagation CC over the sharded graph.  Per sweep: the rank's fused sweep launch, the
+        compaction of (vertex, label) for every label it lowered, one all-gather of the headers, then
+        either the all-gather of the pairs + apply kernel, or -- when most labels changed -- one MIN
+        all-reduce of the replicas + the kernel that flags the owned vertices whose label fell.
+        Returns (labels, sweeps, edges this rank scanned)."""
         import torch
+        import torch.distributed as dist
         dev = self.torch_device
+        b = self._buffers("cc")
         comp = torch.arange(self.n, dtype=torch.int64, device=dev)
         curr = torch.ones(self.n, dtype=torch.uint8, device=dev)
         nxt = torch.zeros(self.n, dtype=torch.uint8, device=dev)
         changed = torch.zeros(1, dtype=torch.int32, device=dev)
         scanned = torch.zeros(1, dtype=torch.int64, device=dev)
         sweeps = 0
+        self.cc_dense_sweeps = 0
         while True:
-            prev = comp.clone()
             self.local.cc_sweep(0, self.v1 - self.v0, comp, curr, nxt, changed, scanned, v_base=self.v0)
-            self.local.ctrl.check_status()
             sweeps += 1
-            if exchange_cc_changes(comp, prev, nxt, self.group) == 0:
+            self.local.cc_compact(comp, nxt, b["send"], b["hdr"])
+            counts, statuses = gather_headers(b["hdr"], b["hdrs"], self.group)
+            raise_on_rank_failure(statuses)
+            total = sum(counts)
+            if total == 0:
                 break
+            if total > b["sparse_cap"]:
+                b["before"].copy_(comp[self.v0:self.v1])
+                dist.all_reduce(comp, op=dist.ReduceOp.MIN, group=self.group)
+                self.local.cc_dense_flag(comp, b["before"], nxt, self.v0, self.v1)
+                self.cc_dense_sweeps += 1
+            else:
+                mx = max(counts)
+                dist.all_gather_into_tensor(b["recv"][:mx * self.world], b["send"][:mx], group=self.group)
+                self.local.cc_apply(comp, nxt, self.v0, self.v1, b["recv"], mx, b["hdrs"], self.world, self.rank)
             curr.zero_()
             curr, nxt = nxt, curr
         return comp, sweeps, int(scanned.item())

@@ -258,7 +258,8 @@ typedef struct bam_dma_window_s { uint64_t base, bytes; } bam_dma_window_t;
  * Slot state word (32 bits, updated with CAS / fetch-ops):
  *   VALID | BUSY | DIRTY | pin count (29 bits) -- encodings of include/page_cache.h:57-62.
  * Unlike the reference the word belongs to the cache SLOT, not to the data page: the page
- * table is hashed (O(cache) memory) instead of direct-mapped (O(backing store)). */
+ * table is hashed (O(cache) memory) instead of direct-mapped (O(backing store)).
+ * The bucket entries address slots with 24 bits: a cache holds at most 2^24 - 2 slots. */
 #define BAM_VALID 0x80000000u
 #define BAM_BUSY 0x40000000u
 #define BAM_DIRTY 0x20000000u
@@ -268,11 +269,14 @@ typedef struct bam_dma_window_s { uint64_t base, bytes; } bam_dma_window_t;
 #define BAM_SLOT_ERR 0xfffffffeu
 #define BAM_SLOT_RETRY 0xfffffffdu   /* no slot could be claimed right now: release what you hold and ask again */
 #define BAM_SLOT_MAX 0xfffffffcu     /* largest value that is a real slot index */
+#define BAM_MAX_CACHE_SLOTS 0xfffffeull   /* 2^24 - 2: bucket entries hold 24-bit slot indices */
 
 typedef struct BAM_ALIGNAS(16) {
     uint64_t tag;        /* (page index in range << range bits) | range id; BAM_TAG_NONE if unassigned */
     uint32_t state;
-    uint32_t pad;
+    uint32_t gen;        /* recycle generation: incremented when an eviction claims the slot, before its tag is
+                          * cleared and long before new data can land in it.  Readers that pin nothing sample
+                          * {state, gen} (one aligned 64-bit load) before and after they read page data. */
 } bam_slot_t;
 
 /* One page-table bucket = 32 bytes = one DRAM sector: a control word and seven entries.

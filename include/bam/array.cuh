@@ -11,6 +11,11 @@
  * broadcast with __shfl_sync, every lane loads its element, and the leader unpins once.
  * Groups are independent: no lane waits for another group between its pin and its unpin, so
  * a warp never holds one page while waiting for another.
+ *
+ * Element READS of resident pages do not even pin: each lane validates the slot's recycle generation
+ * around its load (range_try_read) and only the lanes that could not be served that way -- page
+ * absent, being filled or evicted -- go through the coalesced pinning path.  Writes, cursors
+ * (bam_ptr) and raw page views keep pinning.
  */
 #ifndef BAM_ARRAY_CUH
 #define BAM_ARRAY_CUH
@@ -110,12 +115,17 @@ struct array_d_t {
          * because the range id is part of the page's global address */
         const bool valid = ri >= 0;
         const range_d_t<T>& r = d_ranges[valid ? ri : 0];
+        /* first without a pin; what that cannot serve goes through the pinning path below */
+        const bool fast = valid && range_try_read(r, i, v);
+        const uint32_t fm = __ballot_sync(mask, fast);
+        if (fm && lane_id() == (uint32_t)(__ffs(fm) - 1)) count_hit(r.cache, __popc(fm));
+        if (fm == mask) return v;
         const uint64_t page = valid ? r.get_page(i) : ~0ull;
-        const uint64_t key = valid ? r.get_global_address(page) : ~0ull;
+        const uint64_t key = valid && !fast ? r.get_global_address(page) : ~(uint64_t)lane_id();
         const uint32_t eq = __match_any_sync(mask, key);
         const uint32_t leader = __ffs(eq) - 1;
         const uint32_t cnt = __popc(eq);
-        bool pending = valid;
+        bool pending = valid && !fast;
         spin_t sp;
         for (;;) {
             uint32_t slot = r.acquire_page_warp(mask, pending && lane_id() == leader, valid ? page : 0, cnt, false, default_queue());
@@ -271,18 +281,30 @@ struct array_d_t {
     }
 };
 
-/* Same read as array_d_t<T>::seq_read for the common single-range array whose descriptor sits
- * in kernel parameter space (no pointer chasing through global memory per access). */
+/* One element read that pins nothing (cache.cuh: opt_probe / opt_validate); false = not read, take
+ * the pinning path.  Per thread, no warp cooperation. */
 template <typename T>
-BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
+BAM_DEV bool range_try_read(const range_d_t<T>& r, size_t i, T& v)
 {
-    const uint32_t mask = __activemask();
-    const uint64_t page = r.get_page(i);
-    const uint32_t eq = __match_any_sync(mask, page);
+    const uint64_t tag = r.get_global_address(r.get_page(i));
+    const opt_probe_t pr = opt_probe(r.cache, tag);
+    if (pr.slot == BAM_SLOT_NONE) return false;
+    v = ld_strong(reinterpret_cast<const T*>(r.get_cache_page_addr(pr.slot) + r.get_subindex(i)));
+    fence_acq_rel_gpu();
+    return opt_validate(r.cache, tag, pr);
+}
+
+/* The pinning read, warp-cooperative: every lane of `mask` calls it, lanes with want == true read
+ * element i.  Lanes that touch the same page share one pin. */
+template <typename T>
+BAM_DEV T range_read_pinned(const range_d_t<T>& r, uint32_t mask, bool want, size_t i, uint32_t queue)
+{
+    const uint64_t page = want ? r.get_page(i) : 0;
+    const uint32_t eq = __match_any_sync(mask, want ? page : ~(uint64_t)lane_id());
     const uint32_t leader = __ffs(eq) - 1;
     const uint32_t cnt = __popc(eq);
     T v = T();
-    bool pending = true;
+    bool pending = want;
     spin_t sp;
     for (;;) {
         uint32_t slot = r.acquire_page_warp(mask, pending && lane_id() == leader, page, cnt, false, queue);
@@ -297,6 +319,78 @@ BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
         if (__any_sync(mask, sp.expired(r.cache.status, BAM_AT_FIND_SLOT, page))) break;
     }
     return v;
+}
+
+/* Same read as array_d_t<T>::seq_read for the common single-range array whose descriptor sits
+ * in kernel parameter space (no pointer chasing through global memory per access): first without
+ * a pin; the lanes that could not be served that way then pin their pages together. */
+template <typename T>
+BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
+{
+    const uint32_t mask = __activemask();
+    T v = T();
+    const bool ok = range_try_read(r, i, v);
+    const uint32_t okm = __ballot_sync(mask, ok);
+    if (okm && lane_id() == (uint32_t)(__ffs(okm) - 1)) count_hit(r.cache, __popc(okm));
+    if (okm != mask) {
+        const T x = range_read_pinned(r, mask, !ok, i, queue);
+        if (!ok) v = x;
+    }
+    return v;
+}
+
+/* N element reads of one thread at once.  The N look-ups, slot records and element loads are issued
+ * side by side (straight-line code, two fences for all of them), so a thread has N independent
+ * accesses in flight instead of a chain of dependent ones; what that cannot serve (absent or busy
+ * pages, a second candidate in the bucket) is retried with the full look-up and then pinned.
+ * n <= N elements are valid; `hits` accumulates the accesses served without a page read. */
+template <typename T, int N>
+BAM_DEV void range_read_n(const range_d_t<T>& r, const size_t* i, uint32_t n, T* v, uint32_t queue, uint32_t& hits)
+{
+    const uint32_t mask = __activemask();
+    uint64_t tag[N];
+    uint32_t cand[N];
+    opt_probe_t pr[N];
+#pragma unroll
+    for (int b = 0; b < N; b++) {
+        tag[b] = r.get_global_address(r.get_page(i[b]));
+        const uint64_t h = pt_hash(tag[b]);
+        cand[b] = (uint32_t)b < n ? opt_home_candidate(r.cache, (uint32_t)h & r.cache.bucket_mask, (uint32_t)(h >> 56)) : BAM_SLOT_NONE;
+    }
+#pragma unroll
+    for (int b = 0; b < N; b++) pr[b] = opt_probe_record(r.cache, tag[b], cand[b]);
+    fence_acq_rel_gpu();
+#pragma unroll
+    for (int b = 0; b < N; b++)
+        if (pr[b].slot != BAM_SLOT_NONE) v[b] = ld_strong(reinterpret_cast<const T*>(r.get_cache_page_addr(pr[b].slot) + r.get_subindex(i[b])));
+    fence_acq_rel_gpu();
+    uint32_t need = 0;
+#pragma unroll
+    for (int b = 0; b < N; b++) {
+        const bool ok = pr[b].slot != BAM_SLOT_NONE && opt_validate(r.cache, tag[b], pr[b]);
+        if (ok) hits++;
+        else if ((uint32_t)b < n) need |= 1u << b;
+    }
+    if (!__any_sync(mask, need != 0u)) return;
+    /* leftovers, one per round: full look-up without a pin, then the pinning path for the warp */
+    while (__any_sync(mask, need != 0u)) {
+        const int b = need ? __ffs(need) - 1 : 0;
+        size_t ii = i[0];
+#pragma unroll
+        for (int k = 1; k < N; k++) if (b == k) ii = i[k];
+        T x = T();
+        bool want = need != 0u;
+        if (want && range_try_read(r, ii, x)) { want = false; hits++; }
+        if (__any_sync(mask, want)) {
+            const T y = range_read_pinned(r, mask, want, ii, queue);
+            if (want) x = y;
+        }
+        if (need) {
+#pragma unroll
+            for (int k = 0; k < N; k++) if (b == k) v[k] = x;
+            need &= need - 1;
+        }
+    }
 }
 
 /* Per-thread cursor that keeps the page of its last access pinned, so a run of accesses to one

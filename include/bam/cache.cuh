@@ -17,6 +17,9 @@
  *    an unpinned, non-busy word, so a pinned page can never be recycled and a reader that
  *    raced with a recycle sees a tag mismatch, undoes its pin and looks the page up again.
  *  - Eviction is a clock sweep over the slots (the reference's page_ticket hand, :1802).
+ *  - Read-only element accesses to resident pages take no pin at all: they validate a recycle
+ *    generation around the data load (opt_probe / opt_validate below) and fall back to the pinning
+ *    path on any doubt.
  *
  * Slot life cycle:   0 (free) --CAS--> BUSY (filling) --xor--> VALID (+pins)
  *                    VALID,0 pins --CAS--> VALID|BUSY (evicting: tag cleared, entry removed)
@@ -141,9 +144,12 @@ BAM_DEV uint32_t find_slot(const page_cache_d_t& pc, uint32_t max_tries = 0xffff
         const uint32_t st = ld_relaxed_gpu(&sl->state);
         if (st == 0u) {
             if (atom_cas_acquire(&sl->state, 0u, BAM_BUSY) == 0u) { BAM_PROF_ADD(pc.status, 12, 1); BAM_PROF_ADD(pc.status, 13, tries); return s; }
-        } else if ((st & ~BAM_DIRTY) == BAM_VALID) {
-            if ((st & BAM_DIRTY) && !dirty_tag) continue;     /* this caller cannot write back: leave it */
+        } else if ((st & ~BAM_DIRTY) == BAM_VALID && (!(st & BAM_DIRTY) || dirty_tag)) {
+            /* a dirty victim is left alone by a caller that cannot write it back */
             if (atom_cas_acquire(&sl->state, st, st | BAM_BUSY) == st) {
+                /* the slot is claimed: readers that hold no pin must learn of it before the tag goes
+                 * and long before other data can land here (the releases below order the bump first) */
+                red_add_relaxed(&sl->gen, 1u);
                 if (st & BAM_DIRTY) {
                     /* the victim must reach the backing store first.  Its tag and table entry stay,
                      * so anyone who wants that page meanwhile finds the slot VALID|BUSY and waits
@@ -159,6 +165,7 @@ BAM_DEV uint32_t find_slot(const page_cache_d_t& pc, uint32_t max_tries = 0xffff
                 return s;
             }
         }
+        /* every path that did not claim a slot ends here: the wait is bounded whatever the sweep met */
         if ((tries & 63u) == 0u && sp.expired(pc.status, BAM_AT_FIND_SLOT)) return BAM_SLOT_ERR;
     }
 }
@@ -268,6 +275,68 @@ BAM_DEV int access_data_async(const page_cache_d_t* pc, QueuePair* qp, uint64_t 
 }
 BAM_DEV int poll_async(QueuePair* qp, uint16_t cid, uint16_t /*sq_pos*/) { return access_data_complete(qp, cid); }
 
+/* ---- reads that pin nothing -------------------------------------------------------------------
+ * A read-only access to a resident page needs no pin: look the slot up, sample {state, gen}, read the
+ * element, sample {tag, state, gen} again.  The slot held the page during the whole read if it was
+ * VALID and not BUSY at the first sample and its generation and tag are unchanged at the second:
+ * an eviction bumps the generation right after it claims the slot, before the tag is cleared and long
+ * before the fill of another page can write into the slot.  The order sample -> data -> sample is kept
+ * with two device-scope fences (or, in opt_read below, an acquire load and one fence).  Anything
+ * else -- page absent, being filled or evicted, recycled under the reader -- makes the caller fall back
+ * to the pinning path.  Two L2 atomics per access of the pinning hit path become none. */
+struct opt_probe_t {
+    uint32_t slot;      /* BAM_SLOT_NONE: take the pinning path */
+    uint32_t gen;
+};
+
+/* First half: look-up and first sample, an acquire load: the data load that follows is ordered after it. */
+BAM_DEV opt_probe_t opt_probe(const page_cache_d_t& pc, uint64_t tag)
+{
+    opt_probe_t pr = { BAM_SLOT_NONE, 0u };
+    const uint64_t h = pt_hash(tag);
+    const uint32_t s = pt_lookup(pc, tag, (uint32_t)h & pc.bucket_mask, (uint32_t)(h >> 56));
+    if (s == BAM_SLOT_NONE) return pr;
+    const uint64_t sg = ld_acquire_gpu(reinterpret_cast<const uint64_t*>(&pc.slots[s].state));
+    if (((uint32_t)sg & (BAM_VALID | BAM_BUSY)) != BAM_VALID) return pr;
+    pr.slot = s;
+    pr.gen = (uint32_t)(sg >> 32);
+    return pr;
+}
+
+/* The same for the common case, as straight-line code so that several probes of one thread overlap:
+ * only the home bucket is examined and only its first entry with the right fingerprint; the slot
+ * record {tag, state, gen} is one 128-bit load.  Returns BAM_SLOT_NONE whenever the full look-up
+ * would have to go on (another candidate, an overflowed bucket).  The caller fences before its data loads. */
+BAM_DEV uint32_t opt_home_candidate(const page_cache_d_t& pc, uint32_t home, uint32_t fp)
+{
+    const uint32_t* w = pc.table + (size_t)home * BAM_BUCKET_WORDS;
+    const uint4 lo = ld_cg_v4(w);
+    const uint4 hi = ld_cg_v4(w + 4);
+    const uint32_t e[8] = { lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w };
+    uint32_t cand = BAM_SLOT_NONE;
+#pragma unroll
+    for (int i = 7; i >= 1; i--)
+        if (e[i] != BAM_ENTRY_EMPTY && (e[i] >> 24) == fp) cand = e[i] & 0xffffffu;
+    return cand;
+}
+BAM_DEV opt_probe_t opt_probe_record(const page_cache_d_t& pc, uint64_t tag, uint32_t cand)
+{
+    opt_probe_t pr = { BAM_SLOT_NONE, 0u };
+    if (cand == BAM_SLOT_NONE) return pr;
+    const uint4 rec = ld_relaxed_gpu_v4(&pc.slots[cand]);
+    if (((((uint64_t)rec.y) << 32) | rec.x) != tag || (rec.z & (BAM_VALID | BAM_BUSY)) != BAM_VALID) return pr;
+    pr.slot = cand;
+    pr.gen = rec.w;
+    return pr;
+}
+
+/* Second half, after the data load and a load-load fence: true if the data belonged to `tag`. */
+BAM_DEV bool opt_validate(const page_cache_d_t& pc, uint64_t tag, const opt_probe_t& pr)
+{
+    const uint4 rec = ld_relaxed_gpu_v4(&pc.slots[pr.slot]);
+    return ((((uint64_t)rec.y) << 32) | rec.x) == tag && rec.w == pr.gen;
+}
+
 BAM_DEV void count_hit(const page_cache_d_t& pc, uint32_t count) { red_add_relaxed(&pc.stats[get_smid() & (BAM_STAT_STRIPES - 1)].hits, (uint64_t)count); }
 BAM_DEV void count_miss(const page_cache_d_t& pc, uint32_t count)
 {
@@ -308,9 +377,20 @@ BAM_DEV uint32_t cache_acquire(const page_cache_d_t& pc, uint64_t tag, uint32_t 
             if (sp.expired(st, BAM_AT_PAGE_BUSY, tag)) return BAM_SLOT_ERR;
             continue;
         }
-        /* miss: claim a slot, publish the mapping, fill the slot */
-        const uint32_t v = find_slot(pc);
+        /* miss: claim a slot (a dirty victim is written back first), publish the mapping, fill the slot */
+        uint64_t victim_tag = BAM_TAG_NONE;
+        const uint32_t v = find_slot(pc, 0xffffffffu, &victim_tag);
         if (v == BAM_SLOT_ERR) return BAM_SLOT_ERR;
+        if (victim_tag != BAM_TAG_NONE) {
+            uint32_t wctrl = 0;
+            const uint64_t wlba = backing_location_of_tag(pc, victim_tag, wctrl) * pc.n_blocks_per_page;
+            for (uint32_t k = 0; k < pc.n_ctrls; k++) {
+                if (wctrl != BAM_ALL_CTRLS && wctrl != k) continue;
+                if (access_data_raw(pick_queue(pc, k, queue), wlba, pc.n_blocks_per_page, slot_bus_addr(pc, v), slot_prp2(pc, v),
+                                    NVM_IO_WRITE) != BAM_OK) return BAM_SLOT_ERR;
+            }
+            finish_evict(pc, v, victim_tag);
+        }
         bam_slot_t* sl = &pc.slots[v];
         st_relaxed_gpu(&sl->tag, tag);
         __threadfence();

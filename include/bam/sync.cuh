@@ -39,6 +39,17 @@ BAM_DEV void st_release_gpu(uint64_t* p, uint64_t v) { asm volatile("st.release.
 BAM_DEV void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 BAM_DEV void st_release_sys(uint64_t* p, uint64_t v) { asm volatile("st.release.sys.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory"); }
 
+BAM_DEV uint4 ld_relaxed_gpu_v4(const void* p) { uint4 v; asm volatile("ld.relaxed.gpu.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory"); return v; }
+
+/* A strong (L2-coherent) load of one element: the data loads of readers that hold no pin. */
+template <typename T>
+BAM_DEV T ld_strong(const T* p)
+{
+    if constexpr (sizeof(T) == 8) { uint64_t v = ld_relaxed_gpu(reinterpret_cast<const uint64_t*>(p)); return *reinterpret_cast<T*>(&v); }
+    else if constexpr (sizeof(T) == 4) { uint32_t v = ld_relaxed_gpu(reinterpret_cast<const uint32_t*>(p)); return *reinterpret_cast<T*>(&v); }
+    else return *reinterpret_cast<const volatile T*>(p);
+}
+
 BAM_DEV void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 BAM_DEV void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 

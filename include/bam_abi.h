@@ -96,7 +96,8 @@ int bam_ctrl_emu_descriptor(bam_ctrl_t c, void* out, size_t out_bytes); /* bam_e
 
 /* ---- page cache --------------------------------------------------------------------------
  * Replaces page_cache_t::page_cache_t(page_size, n_pages, gpu, ctrl, max_range, ctrls)
- * (include/page_cache.h:697-875). */
+ * (include/page_cache.h:697-875).  n_pages is at most BAM_MAX_CACHE_SLOTS (2^24 - 2 = 16,777,214: the
+ * page table addresses slots with 24 bits; 64 GiB of 4 KiB pages); more is refused with BAM_EINVAL. */
 int bam_cache_create(bam_cache_t* out, bam_ctrl_t ctrl, uint32_t page_size, uint64_t n_pages);
 /* The same constructor with its `ctrls` vector of several controllers (page_cache.h:714-720: one
  * cache in front of n SSDs).  All controllers must sit on the same GPU with the same block size.
@@ -242,6 +243,38 @@ int bam_bfs_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vertices, uint
                 uint32_t* label_dev, uint32_t* n_levels_out, uint64_t* edges_scanned_out);
 int bam_cc_run(bam_array_t offsets, bam_array_t cols, uint64_t n_vertices, uint64_t* comp_dev,
                uint32_t* n_sweeps_out, uint64_t* edges_scanned_out);
+
+/* ---- exchange steps of the multi-GPU traversals ---------------------------------------------------
+ * No counterpart in the reference, whose BFS and CC run on one GPU (benchmarks/bfs/main.cu:1577-1736,
+ * benchmarks/cc/main.cu:1418-1623).  With the graph sharded by vertex range and the label array
+ * replicated, every rank runs, after each level / sweep:  compact -> all-gather of the 16-byte headers
+ * -> all-gather of the payloads (both by the caller, into this GPU's own memory) -> apply.
+ * A header is two u64: {entries appended, status code of `pc`'s controller (0 = fine)}; the gathered
+ * headers hdrs_dev[2 * world] tell every rank how many entries each rank sent, whether the traversal is
+ * over (no entries at all) and whether a rank failed.  Received payloads sit `stride` entries apart:
+ * rank r's entries are recv[r * stride .. r * stride + hdrs[2 r]).  The entries of my_rank are skipped.
+ * Vertex ids must fit 32 bits (n_vertices <= 2^32).  Plain kernels on `stream`; pc may be NULL. */
+/* BFS: append every vertex v with label[v] == level_value (the vertices this rank labelled in the
+ * level it just ran) to out_dev[capacity] (u32). */
+int bam_launch_frontier_compact(bam_cache_t pc, const uint32_t* label_dev, uint64_t n_vertices, uint32_t level_value,
+                                uint32_t* out_dev, uint64_t capacity, uint64_t* hdr_dev, void* stream);
+/* BFS: label[v] = level_value for every received v that is still unreached (0xFFFFFFFF). */
+int bam_launch_frontier_apply(uint32_t* label_dev, uint64_t n_vertices, uint32_t level_value, const uint32_t* recv_dev,
+                              uint64_t stride, const uint64_t* hdrs_dev, uint32_t world, uint32_t my_rank, void* stream);
+/* CC: append (v << 32 | comp[v]) for every vertex flagged in next_visit_dev (the vertices whose label
+ * this rank lowered in the sweep it just ran) to out_pairs_dev[capacity] (u64). */
+int bam_launch_cc_compact(bam_cache_t pc, const uint64_t* comp_dev, const uint8_t* next_visit_dev, uint64_t n_vertices,
+                          uint64_t* out_pairs_dev, uint64_t capacity, uint64_t* hdr_dev, void* stream);
+/* CC: comp[v] = min(comp[v], label) for every received pair; a vertex of [own_begin, own_end) whose
+ * label fell is flagged in next_visit_dev for this rank's next sweep. */
+int bam_launch_cc_apply(uint64_t* comp_dev, uint8_t* next_visit_dev, uint64_t n_vertices, uint64_t own_begin, uint64_t own_end,
+                        const uint64_t* recv_pairs_dev, uint64_t stride, const uint64_t* hdrs_dev, uint32_t world,
+                        uint32_t my_rank, void* stream);
+/* CC, dense form for sweeps that change most labels: after the caller has combined the replicas with
+ * an element-wise MIN all-reduce, flag the owned vertices whose label is now below before_own_dev
+ * (the caller's copy of comp[own_begin .. own_end) taken before the all-reduce). */
+int bam_launch_cc_dense_flag(const uint64_t* comp_dev, const uint64_t* before_own_dev, uint8_t* next_visit_dev,
+                             uint64_t own_begin, uint64_t own_end, void* stream);
 
 /* Single-source shortest paths over a weighted CSR graph (benchmarks/sssp/main.cu): `weights` is a
  * third array over the same cache, u32 elements, weights[j] belongs to edge cols[j] (the .val file

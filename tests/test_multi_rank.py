@@ -54,8 +54,10 @@ def test_sharded_checksum_reduces_to_global():
 
 
 def _graph_worker(rank, world, port, q):
-    """Distributed BFS and CC with the product's exchange functions; the per-level kernel is played
-    by numpy on the rank's vertex range (the CUDA kernels are covered by the GPU tests)."""
+    """Distributed BFS and CC: the product's host loops (DistCsrGraph.bfs / .cc: persistent buffers,
+    header all-gather, sized payload all-gather, sparse or dense CC exchange, termination) over gloo;
+    the level / sweep kernel and the compaction / apply kernels are played by numpy on the rank's
+    vertex range (the CUDA kernels themselves are covered by the GPU tests)."""
     sys.path.insert(0, ROOT)
     from oracle import pyoracle as orc
     import bam_b200
@@ -64,41 +66,19 @@ def _graph_worker(rank, world, port, q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     off, cols = orc.rmat_csr(2, 10, 16)
     n = len(off) - 1
-    v0, v1 = bam_b200.shard_vertices(n, world, rank)
-    offi, coli = off.astype(np.int64), cols.astype(np.int64)
+    g = bam_b200.DistCsrGraph.__new__(bam_b200.DistCsrGraph)
+    g.n, g.rank, g.world, g.group, g.device = n, rank, world, None, None
+    g.v0, g.v1 = bam_b200.shard_vertices(n, world, rank)
+    g.local = _HostShard(off, cols, None)
     src = int(orc.max_degree_vertex(off))
-    # BFS
-    label = torch.full((n,), -1, dtype=torch.int32)
-    label[src] = 0
-    level = 0
-    while True:
-        lab = label.numpy()
-        for u in np.flatnonzero(lab[v0:v1] == level) + v0:
-            nb = coli[offi[u]:offi[u + 1]]
-            lab[nb[lab[nb] == -1]] = level + 1
-        if bam_b200.exchange_bfs_frontier(label, level) == 0:
-            break
-        level += 1
-    # CC
-    comp = torch.arange(n, dtype=torch.int64)
-    curr = torch.ones(n, dtype=torch.uint8)
-    nxt = torch.zeros(n, dtype=torch.uint8)
-    sweeps = 0
-    while True:
-        prev = comp.clone()
-        c, nv = comp.numpy(), nxt.numpy()
-        for u in np.flatnonzero(curr.numpy()[v0:v1]) + v0:
-            for w in coli[offi[u]:offi[u + 1]]:
-                if c[u] < c[w]:
-                    c[w] = c[u]; nv[w] = 1
-                elif c[w] < c[u]:
-                    c[u] = c[w]; nv[u] = 1
-        sweeps += 1
-        if bam_b200.exchange_cc_changes(comp, prev, nxt) == 0:
-            break
-        curr.zero_()
-        curr, nxt = nxt, curr
-    q.put((rank, label.numpy().view(np.uint32).copy(), comp.numpy().view(np.uint64).copy(), level + 1, sweeps))
+    label, n_levels, _ = g.bfs(src)
+    out = [rank, label.numpy().view(np.uint32).copy(), n_levels]
+    for fraction in (0.25, float(world)):        # the default mix of dense and sparse sweeps, then sparse only
+        g.CC_DENSE_FRACTION = fraction
+        g._xbuf.pop("cc", None)
+        comp, sweeps, _ = g.cc()
+        out += [comp.numpy().view(np.uint64).copy(), sweeps, g.cc_dense_sweeps]
+    q.put(tuple(out))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -119,9 +99,11 @@ def test_distributed_bfs_cc_exchange_matches_oracle():
     off, cols = orc.rmat_csr(2, 10, 16)
     want_lv, _ = orc.bfs(off, cols, orc.max_degree_vertex(off))
     want_lab, _ = orc.cc(off, cols)
-    for _, lv, lab, n_levels, sweeps in res:            # every replica ends bit-identical to the oracle
-        assert (lv == want_lv).all() and (lab == want_lab).all()
-        assert n_levels == int(want_lv[want_lv != 0xFFFFFFFF].max()) + 1 and sweeps >= 1
+    for _, lv, n_levels, lab_a, sweeps_a, dense_a, lab_b, sweeps_b, dense_b in res:    # every replica ends bit-identical to the oracle
+        assert (lv == want_lv).all() and (lab_a == want_lab).all() and (lab_b == want_lab).all()
+        assert n_levels == int(want_lv[want_lv != 0xFFFFFFFF].max()) + 1 and sweeps_a >= 1 and sweeps_b >= 1
+        assert dense_a >= 1 and dense_a < sweeps_a          # the first sweep changes most labels, the last ones few
+        assert dense_b == 0
 
 
 class _HostShard:
@@ -134,6 +116,54 @@ class _HostShard:
 
     def __init__(self, off, cols, wts):
         self.off, self.cols, self.wts, self.ctrl = off.astype(np.int64), cols.astype(np.int64), wts, self._Ctrl()
+
+    def bfs_level(self, v_begin, v_end, level, label, changed, scanned, v_base=0):
+        lab = label.numpy()
+        for u in np.flatnonzero(lab[v_base + v_begin:v_base + v_end] == level) + v_base + v_begin:
+            nb = self.cols[self.off[u]:self.off[u + 1]]
+            lab[nb[lab[nb] == -1]] = level + 1
+
+    def cc_sweep(self, v_begin, v_end, comp, curr_visit, next_visit, changed, scanned, v_base=0):
+        c, nv = comp.numpy(), next_visit.numpy()
+        for u in np.flatnonzero(curr_visit.numpy()[v_base + v_begin:v_base + v_end]) + v_base + v_begin:
+            for w in self.cols[self.off[u]:self.off[u + 1]]:
+                if c[u] < c[w]:
+                    c[w] = c[u]; nv[w] = 1
+                elif c[w] < c[u]:
+                    c[u] = c[w]; nv[u] = 1
+
+    # the exchange kernels of bam_exchange.cu, restated
+    def frontier_compact(self, label, level_value, out, hdr):
+        idx = np.flatnonzero(label.numpy() == level_value)
+        out.numpy()[:len(idx)] = idx
+        hdr[0], hdr[1] = len(idx), 0
+
+    def frontier_apply(self, label, level_value, recv, stride, hdrs, world, rank):
+        lab, h = label.numpy(), hdrs.tolist()
+        for r in range(world):
+            if r != rank:
+                v = recv.numpy()[r * stride:r * stride + h[2 * r]]
+                lab[v[lab[v] == -1]] = level_value
+
+    def cc_compact(self, comp, next_visit, out, hdr):
+        idx = np.flatnonzero(next_visit.numpy())
+        out.numpy()[:len(idx)] = (idx.astype(np.int64) << 32) | comp.numpy()[idx]
+        hdr[0], hdr[1] = len(idx), 0
+
+    def cc_apply(self, comp, next_visit, own_begin, own_end, recv, stride, hdrs, world, rank):
+        c, nv, h = comp.numpy(), next_visit.numpy(), hdrs.tolist()
+        for r in range(world):
+            if r == rank:
+                continue
+            for e in recv.numpy()[r * stride:r * stride + h[2 * r]]:
+                v, lab = int(e) >> 32, int(e) & 0xFFFFFFFF
+                if lab < c[v]:
+                    c[v] = lab
+                    if own_begin <= v < own_end:
+                        nv[v] = 1
+
+    def cc_dense_flag(self, comp, before_own, next_visit, own_begin, own_end):
+        next_visit.numpy()[own_begin:own_end][comp.numpy()[own_begin:own_end] < before_own.numpy()] = 1
 
     def sssp_sweep(self, v_begin, v_end, label, new_cost, scanned, v_base=0):
         lab, nc = label.numpy(), new_cost.numpy().view(np.uint32)
