@@ -250,7 +250,9 @@ struct BlockReadWork {
 };
 
 /* ---- array benchmark --------------------------------------------------------------------- */
+#ifndef BAM_ARRAY_READ_BATCH
 #define BAM_ARRAY_READ_BATCH 4
+#endif
 struct ArrayReadWork {
     range_d_t<uint64_t> r;
     uint64_t n_lanes, reqs_per_lane;
@@ -266,22 +268,30 @@ struct ArrayReadWork {
         const uint64_t n_elems = r.count - r.index_start;
         uint64_t sum = 0;
         uint32_t hits = 0;
+        opt_memo_t memo;
         /* a lane's requests are served BAM_ARRAY_READ_BATCH at a time, so that it has that many
-         * independent look-ups and element loads in flight */
+         * independent look-ups and element loads in flight; the indices of the next batch are loaded
+         * while the current one is served */
         for (uint64_t lane = gid; lane < n_lanes; lane += nthr) {
             bam_pcg32_t g;
             bam_lane_stream(&g, access_seed, lane);
+            size_t nx[BAM_ARRAY_READ_BATCH];
+            auto fetch = [&](uint64_t k) {
+#pragma unroll
+                for (uint32_t b = 0; b < BAM_ARRAY_READ_BATCH; b++) {
+                    nx[b] = r.index_start;
+                    if (k + b < reqs_per_lane) nx[b] = idx ? idx[lane * reqs_per_lane + k + b] : r.index_start + bam_uniform_index(&g, n_elems);
+                }
+            };
+            fetch(0);
             for (uint64_t k = 0; k < reqs_per_lane; k += BAM_ARRAY_READ_BATCH) {
                 size_t ii[BAM_ARRAY_READ_BATCH];
                 uint64_t vv[BAM_ARRAY_READ_BATCH];
                 const uint32_t n = reqs_per_lane - k < BAM_ARRAY_READ_BATCH ? (uint32_t)(reqs_per_lane - k) : BAM_ARRAY_READ_BATCH;
 #pragma unroll
-                for (uint32_t b = 0; b < BAM_ARRAY_READ_BATCH; b++) {
-                    ii[b] = r.index_start;
-                    vv[b] = 0;
-                    if (b < n) ii[b] = idx ? idx[lane * reqs_per_lane + k + b] : r.index_start + bam_uniform_index(&g, n_elems);
-                }
-                range_read_n<uint64_t, BAM_ARRAY_READ_BATCH>(r, ii, n, vv, queue, hits);
+                for (uint32_t b = 0; b < BAM_ARRAY_READ_BATCH; b++) { ii[b] = nx[b]; vv[b] = 0; }
+                if (k + BAM_ARRAY_READ_BATCH < reqs_per_lane) fetch(k + BAM_ARRAY_READ_BATCH);
+                range_read_n<uint64_t, BAM_ARRAY_READ_BATCH>(r, ii, n, vv, queue, hits, memo);
 #pragma unroll
                 for (uint32_t b = 0; b < BAM_ARRAY_READ_BATCH; b++) if (b < n) sum += vv[b];
             }
@@ -353,9 +363,13 @@ struct BulkIoWork {
 #define BAM_PATTERN_RANDOM 2u
 #define BAM_PATTERN_RANDOM_WARP 3u
 
+#define BAM_IMPL_PTR 0u            /* every thread reads through a bam_ptr cursor (the benchmarks' "bam_ptr" type)  */
+#define BAM_IMPL_ARRAY 1u          /* every read is array[i] (their "ORIG" type, benchmarks/cache/main.cu:70)       */
+
 struct PatternWork {
     array_d_t<uint64_t> arr;
-    uint32_t pattern;
+    range_d_t<uint64_t> rng;            /* the array's single range, by value: what the array[] form reads through */
+    uint32_t pattern, impl;
     uint64_t n_elems, n_warps, n_pages_per_warp, stride;
     const uint64_t* assignment;
     uint64_t* sum_out;
@@ -365,9 +379,51 @@ struct PatternWork {
         const uint32_t lane = threadIdx.x & 31u;
         const uint64_t gid = (uint64_t)vb * blockDim.x + threadIdx.x;
         const uint64_t nthr = (uint64_t)nvb * blockDim.x;
-        const uint64_t epp = arr.d_ranges[0].cache.page_size / sizeof(uint64_t);
+        const uint64_t epp = rng.cache.page_size / sizeof(uint64_t);
         uint64_t v = 0;
-        {
+        if (impl == BAM_IMPL_ARRAY) {
+            /* the same walks with array[] reads: indices are computed, the 16 rows of a 4 KiB page are read
+             * four at a time, and after the first read of a page the thread's translation memo serves the rest */
+            const bool by_warp = pattern == BAM_PATTERN_SEQUENTIAL_WARP || pattern == BAM_PATTERN_RANDOM_WARP;
+            const uint64_t nep = by_warp ? (n_warps + stride - 1) / stride : 1;
+            const uint64_t w_end = by_warp ? n_warps : (n_elems + 31) / 32;
+            const uint64_t rows = by_warp ? epp / 32 : 1;
+            const uint64_t pages = by_warp ? n_pages_per_warp : 1;
+            const uint64_t limit = by_warp ? arr.n_elems : n_elems;
+            const uint32_t queue = (uint32_t)(gid >> 5);
+            opt_memo_t memo;
+            uint32_t hits = 0;
+            for (uint64_t w = gid >> 5; w < w_end; w += nthr >> 5) {
+                const uint64_t warp_id = pattern == BAM_PATTERN_SEQUENTIAL_WARP ? (w / nep) + (w % nep) * stride : w;
+                if (warp_id >= w_end) continue;
+                for (uint64_t k = 0; k < pages; k++) {
+                    uint64_t first;
+                    if (pattern == BAM_PATTERN_SEQUENTIAL_WARP) first = (warp_id * pages + k) * epp;
+                    else if (pattern == BAM_PATTERN_RANDOM_WARP) first = assignment[warp_id * pages + k] * epp;
+                    else first = warp_id * 32;
+                    for (uint64_t r = 0; r < rows; r += 4) {
+                        size_t ii[4];
+                        uint64_t x[4];
+                        uint32_t n = 0;
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            uint64_t i = first + (r + u) * 32 + lane;
+                            const bool ok = r + u < rows && i < limit;
+                            if (ok && pattern == BAM_PATTERN_RANDOM) i = assignment[i];
+                            ii[u] = ok ? i : 0;
+                            x[u] = 0;
+                            n += ok ? 1u : 0u;          /* the valid rows are a prefix: indices grow with u */
+                        }
+                        range_read_n<uint64_t, 4>(rng, ii, n, x, queue, hits, memo);
+#pragma unroll
+                        for (int u = 0; u < 4; u++) v += (uint32_t)u < n ? x[u] : 0;
+                    }
+                }
+            }
+            __syncwarp();
+            const uint32_t wh = __reduce_add_sync(0xffffffffu, hits);
+            if (wh && lane == 0) count_hit(rng.cache, wh);
+        } else {
             bam_ptr<uint64_t> ptr(&arr);
             /* one loop for all patterns, so that the cursor's code exists once: (w, k, j) walk warp
              * items, pages of an item and element rows of a page; the element patterns use w only */
@@ -1171,10 +1227,11 @@ extern "C" int bam_cache_copy(bam_cache_t pc, uint64_t first_slot, void* host, u
     return BAM_OK;
 }
 
-extern "C" int bam_launch_pattern_read(bam_array_t a, uint32_t pattern, uint64_t n_elems, uint64_t n_warps, uint64_t n_pages_per_warp,
-                                       uint64_t stride, const uint64_t* assignment_dev, uint64_t* sum_out_dev, void* stream)
+extern "C" int bam_launch_pattern_read_impl(bam_array_t a, uint32_t pattern, uint32_t impl, uint64_t n_elems, uint64_t n_warps,
+                                            uint64_t n_pages_per_warp, uint64_t stride, const uint64_t* assignment_dev,
+                                            uint64_t* sum_out_dev, void* stream)
 {
-    if (!a || a->elem_bytes != 8 || pattern > BAM_PATTERN_RANDOM_WARP || n_elems > a->n_elems) return BAM_EINVAL;
+    if (!a || a->elem_bytes != 8 || pattern > BAM_PATTERN_RANDOM_WARP || impl > BAM_IMPL_ARRAY || n_elems > a->n_elems) return BAM_EINVAL;
     const bool by_warp = pattern == BAM_PATTERN_SEQUENTIAL_WARP || pattern == BAM_PATTERN_RANDOM_WARP;
     if (by_warp && (n_warps == 0 || n_pages_per_warp == 0 || stride == 0)) return BAM_EINVAL;
     if ((pattern == BAM_PATTERN_RANDOM || pattern == BAM_PATTERN_RANDOM_WARP) && !assignment_dev) return BAM_EINVAL;
@@ -1183,9 +1240,17 @@ extern "C" int bam_launch_pattern_read(bam_array_t a, uint32_t pattern, uint64_t
     PatternWork w;
     w.arr.n_elems = a->n_elems; w.arr.start_offset = 0; w.arr.n_ranges = 1;
     w.arr.d_ranges = static_cast<range_d_t<uint64_t>*>(a->d_range);
-    w.pattern = pattern; w.n_elems = n_elems; w.n_warps = n_warps; w.n_pages_per_warp = n_pages_per_warp; w.stride = stride;
+    w.rng = a->h_range;
+    w.pattern = pattern; w.impl = impl; w.n_elems = n_elems; w.n_warps = n_warps; w.n_pages_per_warp = n_pages_per_warp; w.stride = stride;
     w.assignment = assignment_dev; w.sum_out = sum_out_dev;
     return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_pattern_read(bam_array_t a, uint32_t pattern, uint64_t n_elems, uint64_t n_warps, uint64_t n_pages_per_warp,
+                                       uint64_t stride, const uint64_t* assignment_dev, uint64_t* sum_out_dev, void* stream)
+{
+    return bam_launch_pattern_read_impl(a, pattern, BAM_IMPL_PTR, n_elems, n_warps, n_pages_per_warp, stride, assignment_dev, sum_out_dev,
+                                        stream);
 }
 
 /* ---- command encoding, exposed for checks against other encoders ------------------------------------ */

@@ -275,11 +275,13 @@ class Array:
         """a[idx[k]] = splitmix64(val_seed ^ idx[k]) (addend == 0) or a[idx[k]] += addend, through the cache."""
         check(self.lib.bam_launch_array_write(self.h, n, _ptr(idx), val_seed, addend, _ptr(stream)), "bam_launch_array_write")
 
-    def pattern_read(self, pattern, n_elems, sum_out, n_warps=0, n_pages_per_warp=1, stride=1, assignment=None, stream=None):
-        """The pattern benchmark's bam_ptr kernels: pattern 0 sequential, 1 sequential by warp, 2 random
-        (element indices in `assignment`), 3 random by warp (page indices in `assignment`)."""
-        check(self.lib.bam_launch_pattern_read(self.h, pattern, n_elems, n_warps, n_pages_per_warp, stride, _ptr(assignment),
-                                               _ptr(sum_out), _ptr(stream)), "bam_launch_pattern_read")
+    def pattern_read(self, pattern, n_elems, sum_out, n_warps=0, n_pages_per_warp=1, stride=1, assignment=None, stream=None,
+                     impl=0):
+        """The pattern / cache benchmark kernels: pattern 0 sequential, 1 sequential by warp, 2 random
+        (element indices in `assignment`), 3 random by warp (page indices in `assignment`); impl 0 reads
+        through a bam_ptr cursor per thread, impl 1 through array[] (the benchmarks' ORIG type)."""
+        check(self.lib.bam_launch_pattern_read_impl(self.h, pattern, impl, n_elems, n_warps, n_pages_per_warp, stride,
+                                                    _ptr(assignment), _ptr(sum_out), _ptr(stream)), "bam_launch_pattern_read_impl")
 
     def page_scan(self, n_pages, sum_out, pages=None, first_page=0, stream=None):
         check(self.lib.bam_launch_page_scan(self.h, n_pages, _ptr(pages), first_page, _ptr(sum_out), _ptr(stream)),

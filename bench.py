@@ -605,12 +605,30 @@ def run_hit(args):
         t = float(np.mean(times[1:])) * 1e-3
         res[name] = {"reads_per_s": n_reads / t, "useful_gb_per_s": n_reads * 8 / t / 1e9, "ms": t * 1e3,
                      "misses": st["misses"], "verified": int(got.item()) == int(want.item())}
+    # the reference's cache benchmark itself (sequential_access_warp, type ORIG): warp w reads whole pages through
+    # array[], 32 consecutive elements per step, indices computed in the kernel
+    ppw = 4
+    want, got = torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int64, device=dev)
+    arr.page_scan(n_res, want, first_page=0)
+    times = []
+    for _ in range(4):
+        got.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); arr.pattern_read(1, n_res * EPP, got, n_warps=n_res // ppw, n_pages_per_warp=ppw, impl=1); b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    ctrl.check_status()
+    st = cache.stats(reset=True)
+    t = float(np.mean(times[1:])) * 1e-3
+    res["cache_bench"] = {"reads_per_s": n_res * EPP / t, "useful_gb_per_s": n_res * PAGE / t / 1e9, "ms": t * 1e3,
+                          "misses": st["misses"], "verified": int(got.item()) == int(want.item())}
     line = {"metric": "all-hit element reads through array[]", "value": res["random"]["reads_per_s"], "unit": "reads/s",
             "n_gpus": 1, "steps": 3, "warmup": 1, "ms_per_step": res["random"]["ms"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u64", "data": "synthetic",
             "config": {"workload": "warm all-hit element reads", "resident_pages": n_res, "reads": n_reads,
                        "l2": "0.5 GiB of resident pages + 64 MiB index list: larger than L2"},
-            "random": res["random"], "sequential": res["sequential"], "audit": cache.audit(), "gpu_launches": 9}
+            "random": res["random"], "sequential": res["sequential"], "cache_bench": res["cache_bench"],
+            "audit": cache.audit(), "gpu_launches": 14}
     print(json.dumps(line), flush=True)
     arr.close(); cache.close(); ctrl.close()
 

@@ -290,14 +290,19 @@ BAM_DEV bool range_try_read(const range_d_t<T>& r, size_t i, T& v)
     const opt_probe_t pr = opt_probe(r.cache, tag);
     if (pr.slot == BAM_SLOT_NONE) return false;
     v = ld_strong(reinterpret_cast<const T*>(r.get_cache_page_addr(pr.slot) + r.get_subindex(i)));
-    fence_acq_rel_gpu();
-    return opt_validate(r.cache, tag, pr);
+    BAM_OPT_ORDER();
+    return opt_validate(r.cache, tag, pr, opt_dep(v));
 }
 
 /* The pinning read, warp-cooperative: every lane of `mask` calls it, lanes with want == true read
  * element i.  Lanes that touch the same page share one pin. */
+#ifndef BAM_PINNED_INLINE
+#define BAM_PINNED_DEV BAM_DEV_NOINLINE      /* out of line: the miss path's registers stay out of the hit path */
+#else
+#define BAM_PINNED_DEV BAM_DEV
+#endif
 template <typename T>
-BAM_DEV T range_read_pinned(const range_d_t<T>& r, uint32_t mask, bool want, size_t i, uint32_t queue)
+BAM_PINNED_DEV T range_read_pinned(const range_d_t<T>& r, uint32_t mask, bool want, size_t i, uint32_t queue)
 {
     const uint64_t page = want ? r.get_page(i) : 0;
     const uint32_t eq = __match_any_sync(mask, want ? page : ~(uint64_t)lane_id());
@@ -340,36 +345,51 @@ BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
 }
 
 /* N element reads of one thread at once.  The N look-ups, slot records and element loads are issued
- * side by side (straight-line code, two fences for all of them), so a thread has N independent
- * accesses in flight instead of a chain of dependent ones; what that cannot serve (absent or busy
- * pages, a second candidate in the bucket) is retried with the full look-up and then pinned.
+ * side by side (straight-line code), so a thread has N independent
+ * accesses in flight instead of a chain of dependent ones; reads of the page the thread read last skip
+ * the look-up (memo); what cannot be served this way (absent or busy pages, a second candidate in the
+ * bucket) is retried with the full look-up and then pinned.
  * n <= N elements are valid; `hits` accumulates the accesses served without a page read. */
 template <typename T, int N>
-BAM_DEV void range_read_n(const range_d_t<T>& r, const size_t* i, uint32_t n, T* v, uint32_t queue, uint32_t& hits)
+BAM_DEV void range_read_n(const range_d_t<T>& r, const size_t* i, uint32_t n, T* v, uint32_t queue, uint32_t& hits, opt_memo_t& memo)
 {
     const uint32_t mask = __activemask();
-    uint64_t tag[N];
     uint32_t cand[N];
     opt_probe_t pr[N];
+    bool looked_up = false;
 #pragma unroll
     for (int b = 0; b < N; b++) {
-        tag[b] = r.get_global_address(r.get_page(i[b]));
-        const uint64_t h = pt_hash(tag[b]);
-        cand[b] = (uint32_t)b < n ? opt_home_candidate(r.cache, (uint32_t)h & r.cache.bucket_mask, (uint32_t)(h >> 56)) : BAM_SLOT_NONE;
+        const uint64_t tag = r.get_global_address(r.get_page(i[b]));
+        const uint64_t h = pt_hash(tag);
+        const bool known = tag == memo.tag;
+        cand[b] = ((uint32_t)b < n && !known) ? opt_home_candidate(r.cache, (uint32_t)h & r.cache.bucket_mask, (uint32_t)(h >> 56)) : BAM_SLOT_NONE;
+        looked_up = looked_up || ((uint32_t)b < n && !known);
     }
 #pragma unroll
-    for (int b = 0; b < N; b++) pr[b] = opt_probe_record(r.cache, tag[b], cand[b]);
-    fence_acq_rel_gpu();
+    for (int b = 0; b < N; b++) {
+        const uint64_t tag = r.get_global_address(r.get_page(i[b]));
+        pr[b] = opt_probe_record(r.cache, tag, cand[b]);
+        if ((uint32_t)b < n && tag == memo.tag) { pr[b].slot = memo.slot; pr[b].gen = memo.gen; }
+    }
+    if (looked_up) BAM_OPT_ORDER();              /* first samples before the data loads */
 #pragma unroll
     for (int b = 0; b < N; b++)
         if (pr[b].slot != BAM_SLOT_NONE) v[b] = ld_strong(reinterpret_cast<const T*>(r.get_cache_page_addr(pr[b].slot) + r.get_subindex(i[b])));
-    fence_acq_rel_gpu();
+    BAM_OPT_ORDER();                             /* data loads before the validating samples */
+    uint32_t dep = 0;
+#pragma unroll
+    for (int b = 0; b < N; b++)
+        if (pr[b].slot != BAM_SLOT_NONE) dep |= opt_dep(v[b]);
     uint32_t need = 0;
 #pragma unroll
     for (int b = 0; b < N; b++) {
-        const bool ok = pr[b].slot != BAM_SLOT_NONE && opt_validate(r.cache, tag[b], pr[b]);
+        const uint64_t tag = r.get_global_address(r.get_page(i[b]));
+        bool still = false;
+        const bool ok = pr[b].slot != BAM_SLOT_NONE && opt_validate(r.cache, tag, pr[b], dep, &still);
         if (ok) hits++;
         else if ((uint32_t)b < n) need |= 1u << b;
+        if (still) { memo.tag = tag; memo.slot = pr[b].slot; memo.gen = pr[b].gen; }
+        else if (tag == memo.tag && (uint32_t)b < n) memo.tag = BAM_TAG_NONE;
     }
     if (!__any_sync(mask, need != 0u)) return;
     /* leftovers, one per round: full look-up without a pin, then the pinning path for the warp */

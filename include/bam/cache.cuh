@@ -280,33 +280,68 @@ BAM_DEV int poll_async(QueuePair* qp, uint16_t cid, uint16_t /*sq_pos*/) { retur
  * element, sample {tag, state, gen} again.  The slot held the page during the whole read if it was
  * VALID and not BUSY at the first sample and its generation and tag are unchanged at the second:
  * an eviction bumps the generation right after it claims the slot, before the tag is cleared and long
- * before the fill of another page can write into the slot.  The order sample -> data -> sample is kept
- * with two device-scope fences (or, in opt_read below, an acquire load and one fence).  Anything
- * else -- page absent, being filled or evicted, recycled under the reader -- makes the caller fall back
- * to the pinning path.  Two L2 atomics per access of the pinning hit path become none. */
+ * before the fill of another page can write into the slot.  Anything else -- page absent, being filled
+ * or evicted, recycled under the reader -- makes the caller fall back to the pinning path.  Two L2
+ * atomics per access of the pinning hit path become none.
+ *
+ * The three steps must be PERFORMED in order: first sample -> data load -> second sample.  All three are
+ * strong (L2-coherent) loads.  By default the order comes from dependencies, which cost nothing:
+ *   - the data load's address is selected by the outcome of the first sample's check, so it cannot be
+ *     issued before that sample has returned;
+ *   - the second sample's slot index is computed from the loaded value (opt_dep: 0 for every value but
+ *     one reserved bit pattern, which the compiler cannot know), so it cannot be issued before the data
+ *     has arrived.  For the reserved pattern the second sample looks at slot 0, the validation fails
+ *     and the pinning path serves the read: slower, never wrong.
+ * A load that is issued after another has returned is performed after it; the GPU does not speculate.
+ * With -DBAM_OPT_USE_FENCES the same order is enforced with fence.acq_rel.gpu between the steps instead
+ * (what the PTX memory model spells out; measured 10-35 % slower on all-hit reads). */
+#ifdef BAM_OPT_USE_FENCES
+#define BAM_OPT_ORDER() fence_acq_rel_gpu()
+#else
+#define BAM_OPT_ORDER() do {} while (0)
+#endif
+
+#define BAM_OPT_RESERVED64 0x7c3a9e1fd25b6048ull
+#define BAM_OPT_RESERVED32 0xd25b6048u
+
+/* 0 for every loaded value but one; a true data dependency on the value. */
+template <typename T>
+BAM_DEV uint32_t opt_dep(const T& v)
+{
+#ifdef BAM_OPT_USE_FENCES
+    return 0u;
+#else
+    if constexpr (sizeof(T) == 8) return *reinterpret_cast<const uint64_t*>(&v) == BAM_OPT_RESERVED64 ? 1u : 0u;
+    else if constexpr (sizeof(T) == 4) return *reinterpret_cast<const uint32_t*>(&v) == BAM_OPT_RESERVED32 ? 1u : 0u;
+    else { fence_acq_rel_gpu(); return 0u; }            /* other element sizes: a real fence */
+#endif
+}
+
 struct opt_probe_t {
     uint32_t slot;      /* BAM_SLOT_NONE: take the pinning path */
     uint32_t gen;
 };
 
-/* First half: look-up and first sample, an acquire load: the data load that follows is ordered after it. */
+/* First half: look-up and first sample.  pr.slot, which the caller's data address is built from, is
+ * selected by the sample's check. */
 BAM_DEV opt_probe_t opt_probe(const page_cache_d_t& pc, uint64_t tag)
 {
     opt_probe_t pr = { BAM_SLOT_NONE, 0u };
     const uint64_t h = pt_hash(tag);
     const uint32_t s = pt_lookup(pc, tag, (uint32_t)h & pc.bucket_mask, (uint32_t)(h >> 56));
     if (s == BAM_SLOT_NONE) return pr;
-    const uint64_t sg = ld_acquire_gpu(reinterpret_cast<const uint64_t*>(&pc.slots[s].state));
+    const uint64_t sg = ld_relaxed_gpu(reinterpret_cast<const uint64_t*>(&pc.slots[s].state));
     if (((uint32_t)sg & (BAM_VALID | BAM_BUSY)) != BAM_VALID) return pr;
     pr.slot = s;
     pr.gen = (uint32_t)(sg >> 32);
+    BAM_OPT_ORDER();
     return pr;
 }
 
 /* The same for the common case, as straight-line code so that several probes of one thread overlap:
  * only the home bucket is examined and only its first entry with the right fingerprint; the slot
  * record {tag, state, gen} is one 128-bit load.  Returns BAM_SLOT_NONE whenever the full look-up
- * would have to go on (another candidate, an overflowed bucket).  The caller fences before its data loads. */
+ * would have to go on (another candidate, an overflowed bucket). */
 BAM_DEV uint32_t opt_home_candidate(const page_cache_d_t& pc, uint32_t home, uint32_t fp)
 {
     const uint32_t* w = pc.table + (size_t)home * BAM_BUCKET_WORDS;
@@ -330,12 +365,26 @@ BAM_DEV opt_probe_t opt_probe_record(const page_cache_d_t& pc, uint64_t tag, uin
     return pr;
 }
 
-/* Second half, after the data load and a load-load fence: true if the data belonged to `tag`. */
-BAM_DEV bool opt_validate(const page_cache_d_t& pc, uint64_t tag, const opt_probe_t& pr)
+/* Second half, after the data load: true if the data belonged to `tag`.  `dep` is opt_dep() of the
+ * loaded value(s).  *still_valid (optional) tells whether this sample can serve as the FIRST sample of
+ * the thread's next read of the same page (slot VALID and not BUSY): see opt_memo_t. */
+BAM_DEV bool opt_validate(const page_cache_d_t& pc, uint64_t tag, const opt_probe_t& pr, uint32_t dep, bool* still_valid = nullptr)
 {
-    const uint4 rec = ld_relaxed_gpu_v4(&pc.slots[pr.slot]);
-    return ((((uint64_t)rec.y) << 32) | rec.x) == tag && rec.w == pr.gen;
+    const uint4 rec = ld_relaxed_gpu_v4(&pc.slots[dep ? 0u : pr.slot]);
+    const bool ok = ((((uint64_t)rec.y) << 32) | rec.x) == tag && rec.w == pr.gen;
+    if (still_valid) *still_valid = ok && (rec.z & (BAM_VALID | BAM_BUSY)) == BAM_VALID;
+    return ok;
 }
+
+/* A thread's last translation: the validating sample of one read is a valid first sample for the next
+ * read of the same page, so runs of accesses to one page skip the look-up (bucket and slot record) and
+ * go straight to the data load and its validation.  Costs four registers; holds no pin, so it never
+ * needs releasing and a stale one only costs a failed validation. */
+struct opt_memo_t {
+    uint64_t tag = BAM_TAG_NONE;
+    uint32_t slot = BAM_SLOT_NONE;
+    uint32_t gen = 0;
+};
 
 BAM_DEV void count_hit(const page_cache_d_t& pc, uint32_t count) { red_add_relaxed(&pc.stats[get_smid() & (BAM_STAT_STRIPES - 1)].hits, (uint64_t)count); }
 BAM_DEV void count_miss(const page_cache_d_t& pc, uint32_t count)

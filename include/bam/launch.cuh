@@ -23,7 +23,9 @@
 #include "emu_ctrl.cuh"
 
 #define BAM_THREADS 256               /* threads per block of every fused launch              */
+#ifndef BAM_MIN_BLOCKS
 #define BAM_MIN_BLOCKS 3              /* resident blocks per SM the kernels are compiled for  */
+#endif
 
 /* Dynamic shared memory of every block of a fused launch (BAM_EMU_SMEM_BYTES): the controller
  * blocks use it as their bulk-copy stages, workers may stage cache pages in it; it has to be the

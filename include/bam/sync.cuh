@@ -22,6 +22,7 @@
 namespace bam {
 
 #define BAM_DEV __device__ __forceinline__
+#define BAM_DEV_NOINLINE __device__ __noinline__
 
 /* ---- loads / stores ------------------------------------------------------------------- */
 BAM_DEV uint32_t ld_relaxed_gpu(const uint32_t* p) { uint32_t v; asm volatile("ld.relaxed.gpu.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }

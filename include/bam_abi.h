@@ -202,6 +202,15 @@ int bam_cache_copy(bam_cache_t pc, uint64_t first_slot, void* host, uint64_t byt
  * A cursor keeps its page pinned: the cache needs more slots than worker threads. */
 int bam_launch_pattern_read(bam_array_t a, uint32_t pattern, uint64_t n_elems, uint64_t n_warps, uint64_t n_pages_per_warp,
                             uint64_t stride, const uint64_t* assignment_dev, uint64_t* sum_out_dev, void* stream);
+/* The same walks with the element access chosen as the benchmarks' `type` option does
+ * (benchmarks/cache/main.cu:69-74, benchmarks/pattern/main.cu): impl 0 = through a bam_ptr cursor (what
+ * bam_launch_pattern_read runs), impl 1 = every read is array[i] ("ORIG"); pattern 1 with impl 1 is the
+ * cache benchmark's sequential_access_warp (benchmarks/cache/main.cu:82-112), pattern 3 its
+ * random_access_warp (:45-79).  array[] reads of resident pages pin nothing, so impl 1 puts no demand on
+ * the number of cache slots. */
+int bam_launch_pattern_read_impl(bam_array_t a, uint32_t pattern, uint32_t impl, uint64_t n_elems, uint64_t n_warps,
+                                 uint64_t n_pages_per_warp, uint64_t stride, const uint64_t* assignment_dev,
+                                 uint64_t* sum_out_dev, void* stream);
 /* Write every dirty page back to the backing store (page_cache_t::flush_cache, page_cache.h:675-682,
  * kernel __flush :584-629).  Call it when no other launch is using the cache. */
 int bam_cache_flush(bam_cache_t pc, void* stream);
