@@ -371,3 +371,109 @@ def bind_to_gpu_numa(cuda_device):
         return {"numa_node": node, "cpus": len(cpus)}
     except Exception:
         return None
+
+
+def probe_uplink_groups(n_bytes=128 << 20, shared_below=0.8):
+    """Which GPUs of this box share a host uplink, found by measurement: every visible GPU copies from
+    pinned host memory alone, then every pair copies at the same time; two GPUs whose rate falls below
+    `shared_below` of their solo rate when they copy together sit behind one uplink (a PCIe switch).
+    Returns (groups, solo_gb_per_s): groups is a list of lists of device indices.  The PCI tree in
+    sysfs is not used: on virtualised hosts it is flat and says nothing about the switches."""
+    import torch
+    n = torch.cuda.device_count()
+    host, dev, streams = [], [], []
+    for d in range(n):
+        host.append(torch.empty(n_bytes, dtype=torch.uint8).pin_memory())
+        dev.append(torch.empty(n_bytes, dtype=torch.uint8, device=f"cuda:{d}"))
+        streams.append(torch.cuda.Stream(device=d))
+
+    def run(devs):
+        best = {d: 0.0 for d in devs}
+        for _ in range(3):
+            ev = {}
+            for d in devs:
+                with torch.cuda.device(d):
+                    ev[d] = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            for d in devs:
+                with torch.cuda.device(d), torch.cuda.stream(streams[d]):
+                    ev[d][0].record(streams[d])
+                    dev[d].copy_(host[d], non_blocking=True)
+                    ev[d][1].record(streams[d])
+            for d in devs:
+                streams[d].synchronize()
+                best[d] = max(best[d], n_bytes / (ev[d][0].elapsed_time(ev[d][1]) * 1e-3) / 1e9)
+        return best
+
+    solo = {}
+    for d in range(n):
+        solo[d] = run([d])[d]
+    parent = list(range(n))
+
+    def find(x):
+        while parent[x] != x:
+            parent[x] = parent[parent[x]]
+            x = parent[x]
+        return x
+
+    for i in range(n):
+        for j in range(i + 1, n):
+            if find(i) == find(j):
+                continue
+            both = run([i, j])
+            if min(both[i] / solo[i], both[j] / solo[j]) < shared_below:
+                parent[find(j)] = find(i)
+    groups = {}
+    for d in range(n):
+        groups.setdefault(find(d), []).append(d)
+    del host, dev
+    return sorted(groups.values()), [solo[d] for d in range(n)]
+
+
+def spread_over_uplinks(groups):
+    """Device order that deals the GPUs round-robin over the uplink groups: the first len(groups)
+    ranks each get an uplink of their own."""
+    order, k = [], 0
+    while any(k < len(g) for g in groups):
+        order += [g[k] for g in groups if k < len(g)]
+        k += 1
+    return order
+
+
+def place_rank(world, local_rank, tag):
+    """CUDA device for `local_rank` of a `world`-rank job on this box, spreading the ranks over distinct
+    host uplinks first.  Matters only when fewer ranks than GPUs run: which GPUs share an uplink decides
+    how much host-link bandwidth each rank gets.  Rank 0 measures (probe_uplink_groups) and leaves the
+    result in a file in the temporary directory named after `tag` (the job's rendezvous port); the other
+    ranks wait for it (bounded).  Returns (device, info); on any failure the identity placement."""
+    import json
+    import tempfile
+    import time
+    import torch
+    n = torch.cuda.device_count()
+    info = {"visible_gpus": n, "placement": "identity"}
+    if world >= n or n <= 1:
+        return local_rank % max(1, n), info
+    path = os.path.join(tempfile.gettempdir(), f"bam_b200_placement_{tag}.json")
+    try:
+        if local_rank == 0:
+            groups, solo = probe_uplink_groups()
+            order = spread_over_uplinks(groups)
+            rec = {"groups": groups, "order": order, "solo_gb_per_s": [round(x, 1) for x in solo]}
+            tmp = path + f".{os.getpid()}"
+            with open(tmp, "w") as f:
+                json.dump(rec, f)
+            os.replace(tmp, path)
+        else:
+            t0 = time.time()
+            while not os.path.exists(path):
+                if time.time() - t0 > 120:
+                    raise TimeoutError("placement file never appeared")
+                time.sleep(0.05)
+            with open(path) as f:
+                rec = json.load(f)
+        info = {"visible_gpus": n, "placement": "spread over host uplinks (measured)", "uplink_groups": rec["groups"],
+                "device_order": rec["order"], "solo_gb_per_s": rec["solo_gb_per_s"]}
+        return rec["order"][local_rank], info
+    except Exception as e:       # placement is an optimisation: never fail the job over it
+        info["placement"] = f"identity ({type(e).__name__}: {e})"
+        return local_rank % n, info

@@ -55,6 +55,10 @@ def parse():
                          "hit = element reads that all hit a small warm cache (the case profiled for the hit path)")
     ap.add_argument("--reqs-log2", type=int, default=24, help="block: log2 of the requests per sweep point")
     ap.add_argument("--scale", type=int, default=0, help="R-MAT scale for bfs (default 24) / cc (default 26)")
+    ap.add_argument("--graph-cache-gib", type=float, default=0.0, help="page cache per GPU of the graph steps (default: 4 for BFS, 8 for CC)")
+    ap.add_argument("--graph-steps", type=int, default=3, help="timed traversals per graph in the default run")
+    ap.add_argument("--no-graphs", action="store_true", help="default run: skip the BFS and CC parts")
+    ap.add_argument("--graphs-last", action="store_true", help="default run: BFS and CC after the array scan instead of before it")
     ap.add_argument("--cpu-sample-lanes", type=int, default=1 << 12)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ctrls", type=int, default=1, help="zipf: controllers behind each GPU's cache")
@@ -181,36 +185,48 @@ def run_reference(args, rank, world):
     lanes = args.cpu_sample_lanes
     # shrink the in-memory cache of the sample to what the sample can touch
     cache_slots = min(cache_pages, lanes * args.reqs)
-    times, ios, acc = [], 0, 0
+    times, ios, acc, misses = [], 0, 0, 0
     use_ref_code = reference_code_available(orc)
     for s in range(args.warmup + args.steps):
         if use_ref_code:
             st, dt = cpu_reference_code_step(orc, n_local, 0, cache_slots, ctrl_threads, args.depth, lanes, args.reqs,
                                              ACCESS_SEED + 1000 + s, workers, store, cdf)
             if s >= args.warmup:
-                times.append(dt); ios += st.read_ios; acc += st.accesses
+                times.append(dt); ios += st.read_ios; acc += st.accesses; misses += st.misses
         else:
             r = cpu_reference_step(orc, n_local, 0, cache_slots, min(args.queues, 128), args.depth, lanes, args.reqs,
                                    ACCESS_SEED + 1000 + s, workers, ctrl_threads, store, cdf)
             if s >= args.warmup:
-                times.append(r.seconds); ios += r.read_ios; acc += r.accesses
+                times.append(r.seconds); ios += r.read_ios; acc += r.accesses; misses += r.misses
     t = sum(times)
     value = ios / t
+    qps_used = ctrl_threads if use_ref_code else min(args.queues, 128)
+    depth_used = min(args.depth, 64) if use_ref_code else args.depth
     sample = (f"{lanes} lanes x {args.reqs} reads per step of the same Zipf(0.99) stream over one {n_local}-page shard, "
               f"cold cache of {cache_slots} slots each step, {workers} reader threads + {ctrl_threads} controller threads; "
               + ("the reference's own page cache and queue code compiled for host threads (oracle/_ref), "
-                 f"{ctrl_threads} queue pairs of depth {min(args.depth, 64)}" if use_ref_code
+                 f"{qps_used} queue pairs of depth {depth_used}" if use_ref_code
                  else "CPU restatement of the reference's protocol"))
+    # the config says what THIS arm ran: a bounded sample of the workload, on rank 0's host cores only
+    cfg = workload_config(args, world)
+    cfg.update({"sample_of": cfg["workload"] + f": {args.lanes * args.reqs} reads per GPU per step, {args.queues} x {args.depth} "
+                             f"queues and a {args.cache_gib} GiB cache per GPU, {world} shard(s)",
+                "workload": "bounded CPU sample of the multi-GPU skewed array scan (one shard, host threads)",
+                "shards_run": 1, "reads_per_gpu_per_step": lanes * args.reqs, "queues_per_gpu": qps_used,
+                "queue_depth": depth_used, "cache_gib_per_gpu": cache_slots * PAGE / (1 << 30), "cache_slots": cache_slots,
+                "reader_threads": workers, "controller_threads": ctrl_threads})
     line = {
         "impl": "reference", "metric": "4KB-page IOPS via page cache", "value": value, "unit": "IOPS",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / max(1, args.steps),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-        "config": workload_config(args, world),
-        "gb_per_s": value * PAGE / 1e9, "accesses_per_s": acc / t,
+        "config": cfg,
+        "gb_per_s": value * PAGE / 1e9, "accesses_per_s": acc / t, "hit_rate": 1.0 - misses / max(1, acc),
         "cpu_baseline": {"value": value, "unit": "IOPS", "cores": workers + ctrl_threads, "kind": "reference" if use_ref_code else "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "IOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "note": "one host runs one shard's sample whatever --gpus says: compare it with the per-GPU figures of the CUDA arm; "
+                "a cold sample of this length has a lower hit rate than the full step, so compare accesses_per_s as well as IOPS",
     }
     print(json.dumps(line), flush=True)
 
@@ -242,48 +258,93 @@ def verify_bfs(off, cols, lv, src):
     return ok and bool(has_parent[(lv != inf) & (lv != 0)].all())
 
 
-def verify_cc(off, cols, lab):
-    """label[v] <= v, label[label[v]] == label[v], labels equal across every edge."""
+def cc_fixed_point(off, cols):
+    """Min-vertex component labels computed independently of the library: label propagation with plain
+    tensor operations on the copy of the CSR in GPU memory (every vertex takes the minimum over its
+    neighbours, then one pointer jump), iterated to the fixed point.  Edge sources are recovered in
+    chunks so that the working set stays a fraction of the edge list."""
     import torch
-    n = off.numel() - 1
-    srcs = torch.repeat_interleave(torch.arange(n, device=off.device), off[1:] - off[:-1])
-    return bool((lab <= torch.arange(n, device=off.device)).all()) and bool((lab[lab] == lab).all()) and \
-        bool((lab[srcs] == lab[cols]).all())
+    n, dev = off.numel() - 1, off.device
+    lab = torch.arange(n, dtype=torch.int64, device=dev)
+    chunk = 1 << 22                                     # vertices per chunk
+    while True:
+        new = lab.clone()
+        for v0 in range(0, n, chunk):
+            v1 = min(n, v0 + chunk)
+            e0, e1 = int(off[v0].item()), int(off[v1].item())
+            if e1 == e0:
+                continue
+            srcs = torch.repeat_interleave(torch.arange(v0, v1, device=dev), off[v0 + 1:v1 + 1] - off[v0:v1])
+            nb = cols[e0:e1]
+            new.scatter_reduce_(0, srcs, lab[nb], reduce="amin", include_self=True)
+            new.scatter_reduce_(0, nb, lab[srcs], reduce="amin", include_self=True)
+            del srcs
+        new = torch.minimum(new, new[new])
+        if bool((new == lab).all()):
+            return lab
+        lab = new
 
 
-def run_graph(args, rank, world, local_rank):
+def verify_cc(off, cols, lab):
+    """Exact: the labels equal the independently computed min-vertex labels (cc_fixed_point) bit for bit."""
+    return bool((cc_fixed_point(off, cols) == lab).all())
+
+
+def graph_cpu_baselines(args, keep, cc_cache_pages):
+    """The same traversals through the CPU restatement of the reference's cache and queues on all host
+    cores, cold cache of the same size: BFS on the very store image the GPU run used (result compared
+    with the GPU's levels), CC on that same scale-24 graph as a bounded sample.  Returns (bfs, cc)."""
+    from oracle import pyoracle as orc
+    cores = os.cpu_count() or 1
+    ctrl_threads = max(1, cores // 8)
+    workers = max(1, cores - ctrl_threads)
+    out = []
+    for kind in (0, 1):
+        try:
+            vres, sc, it, r = orc.ref_graph_run(keep["store"], keep["n"], keep["off_bytes"], kind, keep["src"] if kind == 0 else 0,
+                                                keep["bfs_cache_pages"] if kind == 0 else cc_cache_pages,
+                                                min(args.queues, 128), args.depth, workers, ctrl_threads)
+            b = {"value": sc / r.seconds / 1e9, "unit": "GTEPS", "cores": workers + ctrl_threads, "kind": "port",
+                 "seconds": r.seconds, "read_ios": r.read_ios}
+            if kind == 0:
+                b["sample"] = "the whole traversal on the same backing store, cold cache of the same size"
+                b["matches_gpu_result"] = bool((vres.view(np.int32) == keep["levels"]).all())
+            else:
+                b["sample"] = (f"CC over the R-MAT scale {keep['scale']} graph of the BFS step (a bounded sample), "
+                               "cold cache of the same size as the GPU's")
+        except Exception as e:
+            b = {"value": None, "unit": "GTEPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+        out.append(b)
+    return out
+
+
+def measure_graph(kind, args, rank, world, dev_index, steps, warmup, link_agg):
     """BFS (R-MAT scale 24, 4 GiB cache) or CC (scale 26, 8 GiB cache) over a CSR graph whose offsets
     and edges are read only through bam::array; one step = one whole traversal from a cold cache.
     With N > 1 ranks the graph is sharded by vertex range (each rank's rows in its own backing
     store, cache and queues), labels are replicated and the frontier / changed labels are exchanged
-    by NCCL all-gather after every level."""
+    by NCCL all-gather after every level (compaction and apply kernels around the collective).
+    Returns the result object on rank 0 (None elsewhere); torch.distributed must be initialised
+    when world > 1.  `link_agg`: pinned-copy GB/s of all ranks at once (the host-link roofline)."""
     import torch
     import torch.distributed as dist
     import bam_b200
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-    bam_b200.bind_to_gpu_numa(local_rank)
-    bfs = args.workload == "bfs"
+    dev = torch.device("cuda", dev_index)
+    bfs = kind == "bfs"
     scale = args.scale or (24 if bfs else 26)
-    cache_gib = args.cache_gib if args.cache_gib != 16.0 else (4.0 if bfs else 8.0)
+    cache_gib = args.graph_cache_gib or (4.0 if bfs else 8.0)
     t0 = time.time()
     off, cols = bam_b200.build_rmat_csr(1, scale, 16, device=dev)
     n, m = off.numel() - 1, cols.numel()
     src = int(torch.argmax(off[1:] - off[:-1]).item())          # highest degree, lowest id on ties
-    kw = dict(cache_pages=int(cache_gib * (1 << 30)) // PAGE, cuda_device=local_rank, queue_depth=args.depth,
+    kw = dict(cache_pages=int(cache_gib * (1 << 30)) // PAGE, cuda_device=dev_index, queue_depth=args.depth,
               num_queues=args.queues, ctrl_blocks=args.ctrl_blocks)
     gr = bam_b200.DistCsrGraph(off, cols, rank, world, **kw) if world > 1 else bam_b200.CsrGraph(off, cols, **kw)
     loc = gr.local if world > 1 else gr
     setup_s = time.time() - t0
     times, scanned, iters, ios = [], 0, 0, []
-    sampler = ClockSampler(local_rank)
     out = None
-    for s in range(args.warmup + args.steps):
-        if s == args.warmup and rank == 0:
-            sampler.start()
+    for s in range(warmup + steps):
         loc.cache.invalidate()
         loc.cache.stats(reset=True)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -295,57 +356,115 @@ def run_graph(args, rank, world, local_rank):
         b.record()
         torch.cuda.synchronize()
         loc.ctrl.check_status()
-        if s >= args.warmup:
+        if s >= warmup:
             times.append(a.elapsed_time(b)); ios.append(loc.cache.stats()["read_ios"])
-    clocks = sampler.stop() if rank == 0 else None
+    t_verify = time.time()
     ok = verify_bfs(off, cols, out, src) if bfs else verify_cc(off, cols, out)
     ok = ok and loc.cache.audit() == 0
-    red = torch.tensor([sum(times), float(scanned), float(np.mean(ios)), float(ok)], dtype=torch.float64, device=dev)
+    same = 1.0
+    if world > 1:                                                # every replica must hold the same bits
+        ref = out.clone()
+        dist.broadcast(ref, 0)
+        same = float(bool((ref == out).all()))
+    verify_s = time.time() - t_verify
+    red = torch.tensor([sum(times), float(scanned), float(np.mean(ios)), float(ok), same], dtype=torch.float64, device=dev)
     if world > 1:
         mx = red.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         dist.all_reduce(red, op=dist.ReduceOp.SUM)
-        t_ms, scanned_all, ios_all, n_ok = float(mx[0]), float(red[1]), float(red[2]), float(red[3])
+        t_ms, scanned_all, ios_all, n_ok, n_same = float(mx[0]), float(red[1]), float(red[2]), float(red[3]), float(red[4])
     else:
-        t_ms, scanned_all, ios_all, n_ok = float(red[0]), float(red[1]), float(red[2]), float(red[3])
+        t_ms, scanned_all, ios_all, n_ok, n_same = (float(x) for x in red.tolist())
+    res = None
     if rank == 0:
-        t = t_ms * 1e-3
-        line = {"metric": "BFS GTEPS through bam::array" if bfs else "CC GTEPS through bam::array",
-                "value": scanned_all * len(times) / t / 1e9, "unit": "GTEPS", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": 1e3 * t / len(times), "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-                "config": {"workload": f"{'BFS' if bfs else 'CC'} over R-MAT scale {scale} edge factor 16 (a,b,c = .57,.19,.19), "
-                                       "undirected, de-duplicated; u64 offsets and edges read through the page cache, "
-                                       "cold cache at the start of every traversal",
-                           "vertices": n, "directed_edges": m, "cache_gib_per_gpu": cache_gib, "queues": args.queues,
-                           "queue_depth": args.depth, "source": src, "sharding": "vertex range" if world > 1 else "none",
-                           "l2": "graph (GiB) far larger than L2; no explicit flush"},
-                ("levels" if bfs else "sweeps"): iters, "edges_scanned_per_step": scanned_all,
-                "read_ios_per_step": ios_all, "link_gb_per_s": ios_all * PAGE / (t / len(times)) / 1e9,
-                "verified": bool(n_ok == world), "gpu_launches": iters * args.steps, "clocks": clocks, "setup_s": setup_s}
-        if world == 1 and not args.no_cpu_baseline:
-            # the same traversal through the CPU restatement of the reference's cache and queues, on the
-            # very store the GPU run used (cold cache, all host cores)
-            try:
-                from oracle import pyoracle as orc
-                cores = os.cpu_count() or 1
-                ctrl_threads = max(1, cores // 8)
-                workers = max(1, cores - ctrl_threads)
-                store = loc.ctrl.store_numpy()
-                res, sc, it, r = orc.ref_graph_run(store, n, loc.off_bytes, 0 if bfs else 1, src, kw["cache_pages"],
-                                                   min(args.queues, 128), args.depth, workers, ctrl_threads)
-                same = bool((torch.from_numpy(res.view(np.int32 if bfs else np.int64)).to(out.device) == out).all().item())
-                line["cpu_baseline"] = {"value": sc / r.seconds / 1e9, "unit": "GTEPS", "cores": workers + ctrl_threads,
-                                        "kind": "port", "seconds": r.seconds, "read_ios": r.read_ios,
-                                        "matches_gpu_result": same,
-                                        "sample": "the whole traversal on the same backing store, cold cache of the same size"}
-            except Exception as e:
-                line["cpu_baseline"] = {"value": None, "unit": "GTEPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
-        print(json.dumps(line), flush=True)
+        t = t_ms * 1e-3 / len(times)
+        link = ios_all * PAGE / t / 1e9
+        res = {"gteps": scanned_all / t / 1e9, "ms": t * 1e3, ("levels" if bfs else "sweeps"): iters,
+               "steps": steps, "warmup": warmup,
+               "graph": f"R-MAT scale {scale}, edge factor 16 (a,b,c = .57,.19,.19), undirected, de-duplicated",
+               "vertices": n, "directed_edges": m, "cache_gib_per_gpu": cache_gib, "source": src if bfs else None,
+               "sharding": "vertex range, edge balanced" if world > 1 else "none",
+               "edges_scanned": scanned_all, "read_ios": ios_all,
+               "roofline": {"bound": "host_link", "achieved": link, "peak": link_agg, "unit": "GB/s",
+                            "frac": link / link_agg if link_agg else None,
+                            "kernel": "bam_fused<BfsLevelWork>" if bfs else "bam_fused<CcSweepWork>",
+                            "note": "cold traversal: read_ios x 4096 B cross the host link; peak = pinned-memory H2D copy "
+                                    "measured in this run on all ranks at once"},
+               "verified": bool(n_ok == world and n_same == world),
+               "verified_how": ("levels pinned by the BFS certificate on the CSR in GPU memory" if bfs else
+                                "labels equal an independent min-label fixed point computed with tensor operations on the CSR in GPU memory")
+                               + ("; every rank's replica equal to rank 0's bit for bit" if world > 1 else ""),
+               "gpu_launches": (iters * (3 if world > 1 else 1)) * (steps + warmup), "setup_s": setup_s, "verify_s": verify_s}
+        if world > 1 and not bfs:
+            res["dense_exchange_sweeps"] = getattr(gr, "cc_dense_sweeps", None)
+    keep = None
+    if bfs and world == 1 and not args.no_cpu_baseline:
+        # what the CPU baselines need later (they run after every GPU measurement): the store image, the
+        # GPU's levels to compare with, and the cache geometry
+        keep = {"store": loc.ctrl.store_numpy().copy(), "n": n, "off_bytes": loc.off_bytes, "scale": scale, "src": src,
+                "levels": out.cpu().numpy().copy(), "bfs_cache_pages": kw["cache_pages"]}
     gr.close()
+    del off, cols, out
+    torch.cuda.empty_cache()
+    return res, keep
+
+
+def run_graph(args, rank, world, local_rank):
+    """--workload bfs | cc: the traversal alone, one JSON line."""
+    import torch
+    import torch.distributed as dist
+    import bam_b200
+    dev_index, placement = bam_b200.place_rank(world, local_rank, f"{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}")
+    torch.cuda.set_device(dev_index)
+    dev = torch.device("cuda", dev_index)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    bam_b200.bind_to_gpu_numa(dev_index)
+    bfs = args.workload == "bfs"
+    _, link_agg = measure_link_rate(torch, dist, dev, world, 3)
+    sampler = ClockSampler(dev_index)
+    if rank == 0:
+        sampler.start()
+    res, keep = measure_graph(args.workload, args, rank, world, dev_index, args.steps, args.warmup, link_agg)
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        if keep is not None:
+            res["cpu_baseline"] = graph_cpu_baselines(args, keep, 0)[0]
+        line = {"metric": "BFS GTEPS through bam::array" if bfs else "CC GTEPS through bam::array",
+                "value": res["gteps"], "unit": "GTEPS", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": res["ms"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+                "config": {"workload": f"{'BFS' if bfs else 'CC'} over {res['graph']}; u64 offsets and edges read through the "
+                                       "page cache, cold cache at the start of every traversal",
+                           "queues": args.queues, "queue_depth": args.depth, "placement": placement,
+                           "l2": "graph (GiB) far larger than L2; no explicit flush"},
+                "clocks": clocks}
+        line.update(res)
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def measure_link_rate(torch, dist, dev, world, reps):
+    """Pinned-memory H2D copy rate of this rank while every rank copies: (per-GPU mean, aggregate) in GB/s."""
+    stream = torch.cuda.current_stream()
+    pin = torch.empty(1 << 30, dtype=torch.uint8).pin_memory()
+    dbuf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    best = 0.0
+    for _ in range(reps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream); dbuf.copy_(pin, non_blocking=True); b.record(stream); stream.synchronize()
+        best = max(best, (1 << 30) / (a.elapsed_time(b) * 1e-3) / 1e9)
+    del pin, dbuf
+    link = torch.tensor([best], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(link, op=dist.ReduceOp.SUM)
+    return float(link.item()) / world, float(link.item())
 
 
 def verify_sssp(off, cols, wts, dist, src):
@@ -659,6 +778,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    # ranks are spread over distinct host uplinks first (matters when fewer ranks than GPUs run)
+    dev_index, placement = bam_b200.place_rank(world, local_rank, f"{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}")
+    local_rank = dev_index                                  # from here on: the CUDA device of this rank
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -668,9 +790,26 @@ def main():
     numa = bam_b200.bind_to_gpu_numa(local_rank)          # the pinned shard is placed next to its GPU
     total_pages = int(args.store_gib * (1 << 30)) // PAGE
     first_page, n_local = bam_b200.shard_pages(total_pages, world, rank)
-    cache_pages = min(int(args.cache_gib * (1 << 30)) // PAGE, (1 << 24) - 2)
+    cache_pages = int(args.cache_gib * (1 << 30)) // PAGE
+    if cache_pages > (1 << 24) - 2:
+        raise SystemExit(f"--cache-gib {args.cache_gib}: {cache_pages} slots exceed the library's limit of 2^24 - 2 slots per cache")
     lanes, reqs = args.lanes, args.reqs
     n_acc = lanes * reqs
+
+    # ---- the metric's second half: BFS and CC GTEPS through bam::array, on the same ranks ---------------
+    graph_res = {}
+
+    def graph_part():
+        if args.no_graphs:
+            return
+        _, agg = measure_link_rate(torch, dist, dev, world, 3)
+        gsteps, gwarm = max(1, min(args.steps, args.graph_steps)), 1
+        bfs_res, keep = measure_graph("bfs", args, rank, world, local_rank, gsteps, gwarm, agg)
+        cc_res, _ = measure_graph("cc", args, rank, world, local_rank, gsteps, gwarm, agg)
+        graph_res["bfs"], graph_res["cc"], graph_res["keep"] = bfs_res, cc_res, keep
+
+    if not args.graphs_last:
+        graph_part()
 
     t0 = time.time()
     k_ctrls = max(1, args.ctrls)
@@ -715,20 +854,7 @@ def main():
         torch.cuda.synchronize()
 
     def measure_link(reps):
-        """Pinned-memory H2D copy rate of this rank while every rank copies: (per-GPU mean, aggregate) in GB/s."""
-        pin = torch.empty(1 << 30, dtype=torch.uint8).pin_memory()
-        dbuf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
-        best = 0.0
-        for _ in range(reps):
-            barrier()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream); dbuf.copy_(pin, non_blocking=True); b.record(stream); stream.synchronize()
-            best = max(best, (1 << 30) / (a.elapsed_time(b) * 1e-3) / 1e9)
-        del pin, dbuf
-        link = torch.tensor([best], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(link, op=dist.ReduceOp.SUM)
-        return float(link.item()) / world, float(link.item())
+        return measure_link_rate(torch, dist, dev, world, reps)
 
     # Pages the controller keeps in flight (16 per controller block) are sized to the bandwidth-delay product of
     # the link this rank really gets: GPUs that share a PCIe uplink see about half the bandwidth and twice the
@@ -849,8 +975,24 @@ def main():
             times.append(a.elapsed_time(b))
         ctrl.check_status()
         cache.stats(reset=True)
-        hit_seq = {"ms": float(np.mean(times[1:])), "reads": n_rand, "ok": int(rsum.item()) == int(rwant.item())}
+        hit_seq_listed = {"ms": float(np.mean(times[1:])), "reads": n_rand, "ok": int(rsum.item()) == int(rwant.item())}
         del d_ridx, seq
+        # the cache benchmark itself (sequential_access_warp with type ORIG, benchmarks/cache/main.cu:82-112): warp w
+        # reads whole pages through array[], 32 consecutive elements per step, indices computed in the kernel
+        cwant, csum = torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int64, device=dev)
+        arr.page_scan(n_scan, cwant, first_page=0, stream=sptr)
+        times = []
+        for _ in range(4):
+            csum.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); arr.pattern_read(1, n_scan * EPP, csum, n_warps=n_scan // 4, n_pages_per_warp=4, stream=sptr, impl=1)
+            b.record(stream)
+            stream.synchronize()
+            times.append(a.elapsed_time(b))
+        ctrl.check_status()
+        cst = cache.stats(reset=True)
+        hit_seq = {"ms": float(np.mean(times[1:])), "reads": (n_scan // 4) * 4 * EPP, "misses": cst["misses"],
+                   "ok": int(csum.item()) == int(cwant.item()) or n_scan % 4 != 0}
         # the reference's pattern benchmark, warm: every warp reads one resident 4 KiB page through a bam_ptr
         # cursor (nvm-pattern-bench --impl_type=3, 10 passes); checked against the page scan's sum of the same pages
         pwant, psum = torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int64, device=dev)
@@ -925,8 +1067,9 @@ def main():
                                  "useful_gb_per_s": hit_rand["reads"] * 8 / (hit_rand["ms"] * 1e-3) / 1e9,
                                  "sector_gb_per_s": hit_rand["reads"] * 32 / (hit_rand["ms"] * 1e-3) / 1e9,
                                  "misses": hit_rand["misses"], "verified": hit_rand["ok"],
-                                 "note": "2^26 uniform 8-byte reads over resident pages through the cache (all hits): one "
-                                         "32-byte sector of page data per read plus bucket, slot word and two atomics"},
+                                 "note": "2^26 uniform 8-byte reads from an index list over resident pages through array[] (all hits): "
+                                         "per read one 32-byte sector of page data, the bucket and the slot record (twice); "
+                                         "no pin, no atomic"},
             "hit_pattern_bam_ptr": {"elems_per_s": hit_ptr["elems"] / (hit_ptr["ms"] * 1e-3),
                                     "gib_per_s": hit_ptr["elems"] * 8 / (hit_ptr["ms"] * 1e-3) / (1 << 30),
                                     "pages": hit_ptr["elems"] // EPP, "misses": hit_ptr["misses"], "verified": hit_ptr["ok"],
@@ -936,14 +1079,32 @@ def main():
                                             "own GPU (asplosaoe/nvm_pattern_bench.log:26-62)"},
             "hit_sequential_reads": {"reads_per_s": hit_seq["reads"] / (hit_seq["ms"] * 1e-3),
                                      "gb_per_s": hit_seq["reads"] * 8 / (hit_seq["ms"] * 1e-3) / 1e9, "verified": hit_seq["ok"],
+                                     "misses": hit_seq["misses"],
+                                     "frac_of_hbm": hit_seq["reads"] * 8 / (hit_seq["ms"] * 1e-3) / 1e9 / hbm_peak,
                                      "vs_published": hit_seq["reads"] / (hit_seq["ms"] * 1e-3) / 2.272e10,
-                                     "note": "warm cache, each warp reads 32 consecutive 8-byte elements per step through "
-                                             "array[] (the reference's cache benchmark, 169 GiB/s in its published log)"},
+                                     "note": "warm cache, the reference's cache benchmark (sequential_access_warp, type ORIG): every "
+                                             "warp reads whole resident pages through array[], 32 consecutive 8-byte elements per "
+                                             "step, indices computed in the kernel; 169 GiB/s in its published log"},
+            "hit_sequential_reads_listed": {"reads_per_s": hit_seq_listed["reads"] / (hit_seq_listed["ms"] * 1e-3),
+                                            "gb_per_s": hit_seq_listed["reads"] * 8 / (hit_seq_listed["ms"] * 1e-3) / 1e9,
+                                            "verified": hit_seq_listed["ok"],
+                                            "note": "the same access shape driven by a 2^26-entry index list in HBM (8 bytes of "
+                                                    "index traffic per 8 bytes read)"},
             "clocks": clocks, "setup_s": setup_s, "numa_rank0": numa,
         }
+        line["config"]["placement"] = placement
         line["config"]["controller_blocks"] = ctrl_blocks
         line["config"]["controller_blocks_rule"] = ("given on the command line" if args.ctrl_blocks else
                                                     "48 x (pinned-copy GB/s measured on all ranks at once) / 55, in steps of 8")
+    arr.close(); cache.close()
+    for c in ctrls:
+        c.close()
+    del d_idx, sums, want, d_cdf, h_idx, d_stage
+    torch.cuda.empty_cache()
+    if args.graphs_last:
+        graph_part()
+    # ---- CPU baselines last: nothing that runs on the host cores precedes a GPU measurement ----------------
+    if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             try:
                 from oracle import pyoracle as orc
@@ -953,31 +1114,35 @@ def main():
                 cl = args.cpu_sample_lanes
                 store = np.empty(n_local * EPP, dtype=np.uint64)
                 slots = min(cache_pages, cl * reqs)
-                t_cpu, ios_cpu = 0.0, 0
+                t_cpu, ios_cpu, acc_cpu, miss_cpu = 0.0, 0, 0, 0
                 use_ref_code = reference_code_available(orc)
                 for s in range(3):
                     if use_ref_code:
                         stc, dt = cpu_reference_code_step(orc, n_local, first_page, slots, ctrl_threads, args.depth, cl, reqs,
                                                           ACCESS_SEED + 5000 + s, workers, store, cdf)
-                        t_cpu += dt; ios_cpu += stc.read_ios
+                        t_cpu += dt; ios_cpu += stc.read_ios; acc_cpu += stc.accesses; miss_cpu += stc.misses
                     else:
                         r = cpu_reference_step(orc, n_local, first_page, slots, min(args.queues, 128), args.depth, cl, reqs,
                                                ACCESS_SEED + 5000 + s, workers, ctrl_threads, store, cdf)
-                        t_cpu += r.seconds; ios_cpu += r.read_ios
+                        t_cpu += r.seconds; ios_cpu += r.read_ios; acc_cpu += r.accesses; miss_cpu += r.misses
                 line["cpu_baseline"] = {
                     "value": ios_cpu / t_cpu, "unit": "IOPS", "cores": workers + ctrl_threads,
                     "kind": "reference" if use_ref_code else "port",
+                    "accesses_per_s": acc_cpu / t_cpu, "hit_rate": 1.0 - miss_cpu / max(1, acc_cpu),
                     "sample": f"3 x ({cl} lanes x {reqs} reads) of the same Zipf stream, cold {slots}-slot cache, "
                               f"{workers} reader + {ctrl_threads} controller threads"
                               + ("; the reference's own page cache and queue code compiled for host threads (oracle/_ref)"
                                  if use_ref_code else "; CPU restatement of the reference's protocol")}
             except Exception as e:  # the baseline is reported, never required
                 line["cpu_baseline"] = {"value": None, "unit": "IOPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+        if graph_res:
+            if graph_res.get("keep") is not None:
+                graph_res["bfs"]["cpu_baseline"], graph_res["cc"]["cpu_baseline"] = graph_cpu_baselines(
+                    args, graph_res["keep"], int((args.graph_cache_gib or 8.0) * (1 << 30)) // PAGE)
+            line["bfs"], line["cc"] = graph_res["bfs"], graph_res["cc"]
+            line["gpu_launches"] += line["bfs"]["gpu_launches"] + line["cc"]["gpu_launches"]
+            line["verified"] = bool(line["verified"] and line["bfs"]["verified"] and line["cc"]["verified"])
         print(json.dumps(line), flush=True)
-
-    arr.close(); cache.close()
-    for c in ctrls:
-        c.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

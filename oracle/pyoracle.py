@@ -31,7 +31,19 @@ REF_WIRE_PATH = os.path.join(HERE, "_ref", "libref_wire.so")
 REF_PQ_PATH = os.path.join(HERE, "_ref", "libref_pq.so")
 REF_CACHE_PATH = os.path.join(HERE, "_ref", "libref_cache.so")
 REF_ADMIN_PATH = os.path.join(HERE, "_ref", "libref_admin.so")
-REFERENCE_ROOT = "/root/reference"
+
+
+def _reference_root():
+    """Where the reference project lies: $BAM_REFERENCE_ROOT, else a directory `reference` next to this
+    repository.  Without either only prebuilt libraries under oracle/_ref are used, and the tests that need
+    the reference's code skip with a message that says so."""
+    env = os.environ.get("BAM_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+REFERENCE_ROOT = _reference_root()
 
 
 def build_ref_wire(force=False):
