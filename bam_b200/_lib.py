@@ -16,6 +16,11 @@ class CacheStats(C.Structure):
     _fields_ = [("hits", u64), ("misses", u64), ("read_ios", u64)]
 
 
+class RangeDesc(C.Structure):
+    _fields_ = [("index_start", u64), ("index_end", u64), ("store_byte_offset", u64), ("page_start_offset", u64),
+                ("dist", u32), ("reserved", u32)]
+
+
 class StatusOut(C.Structure):
     _fields_ = [("code", u32), ("where", u32), ("detail", u64)]
 
@@ -53,6 +58,7 @@ SIGNATURES = {
     "bam_cache_descriptor": (ci, [vp, vp, C.c_size_t]),
     "bam_array_create": (ci, [C.POINTER(vp), vp, u64, u32, u64]),
     "bam_array_create_dist": (ci, [C.POINTER(vp), vp, u64, u32, u64, u32]),
+    "bam_array_create_ranges": (ci, [C.POINTER(vp), vp, u64, u32, C.POINTER(RangeDesc), u32]),
     "bam_array_destroy": (ci, [vp]),
     "bam_array_device_ptr": (vp, [vp]),
     "bam_launch_block_read": (ci, [vp, u64, vp, u64, vp, vp, vp]),

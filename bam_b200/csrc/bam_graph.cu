@@ -579,6 +579,8 @@ static int check_graph_args(bam_array_t offsets, bam_array_t cols)
     if (!offsets || !cols) return BAM_EINVAL;
     if (offsets->elem_bytes != 8 || cols->elem_bytes != 8) return BAM_EINVAL;
     if (offsets->pc != cols->pc) return BAM_EINVAL;
+    /* the traversal kernels take each array's one range by value and walk whole pages of it */
+    if (offsets->n_ranges != 1 || cols->n_ranges != 1 || offsets->h_range.page_start_offset || cols->h_range.page_start_offset) return BAM_EINVAL;
     return BAM_OK;
 }
 

@@ -68,8 +68,9 @@ struct bam_array {
     bam_cache* pc = nullptr;
     uint32_t elem_bytes = 0;
     uint64_t n_elems = 0;
-    bam::range_d_t<uint64_t> h_range;   /* layout does not depend on the element type */
-    void* d_range = nullptr;
+    bam::range_d_t<uint64_t> h_range;   /* the first range; layout does not depend on the element type */
+    uint32_t n_ranges = 1;              /* launchers that take one range by value need n_ranges == 1 */
+    void* d_range = nullptr;            /* device array of n_ranges descriptors */
     void* d_array = nullptr;
 };
 

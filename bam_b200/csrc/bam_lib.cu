@@ -303,6 +303,33 @@ struct ArrayReadWork {
     }
 };
 
+/* The same benchmark over an array of several ranges: every read is array[i] (array_d_t::seq_read looks the
+ * range up, page_cache.h:1318-1329 and :1541-1574 in the reference). */
+struct ArrayReadRangesWork {
+    array_d_t<uint64_t> arr;
+    uint64_t n_lanes, reqs_per_lane;
+    const uint64_t* idx;
+    uint64_t access_seed;
+    uint64_t* sum_out;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint64_t gid = (uint64_t)vb * blockDim.x + threadIdx.x;
+        const uint64_t nthr = (uint64_t)nvb * blockDim.x;
+        uint64_t sum = 0;
+        for (uint64_t lane = gid; lane < n_lanes; lane += nthr) {
+            bam_pcg32_t g;
+            bam_lane_stream(&g, access_seed, lane);
+            for (uint64_t k = 0; k < reqs_per_lane; k++) {
+                const uint64_t i = idx ? idx[lane * reqs_per_lane + k] : bam_uniform_index(&g, arr.n_elems);
+                sum += arr[i];
+            }
+        }
+        __syncwarp();
+        warp_sum_to(sum, sum_out);
+    }
+};
+
 /* ---- write path ----------------------------------------------------------------------------------
  * Element writes and atomic adds through the cache (the vectoradd-style consumers of the
  * reference, benchmarks/vectoradd/main.cu:103-118), and the write-back of every dirty page
@@ -537,27 +564,39 @@ struct PageScanWork {
             const uint32_t n_pieces = n_lanes_ok * ppp;
             const uint64_t my_base = (ok >> lane) & 1u ? r.get_cache_page_addr(slot) : 0;
             /* issue piece q into stage q & 1 */
+            uint32_t inflight = 0;                                 /* bit s: stage s has a bulk load under way */
             auto issue = [&](uint32_t q) {
                 const uint32_t src_lane = __fns(ok, 0, (int)(q / ppp) + 1);
                 const uint64_t base = __shfl_sync(0xffffffffu, my_base, src_lane);
+                const uint32_t st = q & 1u;
                 if (lane == 0) {
-                    const uint32_t st = q & 1u;
                     mbar_expect_tx(bar0 + st * 8, plen);
                     bulk_load(stage0 + st * BAM_EMU_STAGE_BYTES, reinterpret_cast<const void*>(base + (uint64_t)(q % ppp) * BAM_EMU_STAGE_BYTES), plen, bar0 + st * 8);
                 }
+                inflight |= 1u << st;
+            };
+            /* wait for stage st's load, bounded like every other wait of the library; false = gave up */
+            auto wait_stage = [&](uint32_t st, uint64_t detail) {
+                const uint64_t t0 = global_timer_ns();
+                uint32_t polls = 0;
+                while (!mbar_test(bar0 + st * 8, (parity >> st) & 1u)) {
+                    if (((++polls) & 1023u) == 0u) {
+                        if (global_timer_ns() - t0 > r.cache.status->spin_timeout_ns) {
+                            status_fail(r.cache.status, BAM_ETIMEDOUT, BAM_AT_TMA, detail);
+                            return false;
+                        }
+                    }
+                }
+                parity ^= 1u << st;
+                inflight &= ~(1u << st);
+                return true;
             };
             if (n_pieces > 0) issue(0);
             if (n_pieces > 1) issue(1);
             for (uint32_t q = 0; q < n_pieces; q++) {
                 const uint32_t st = q & 1u;
-                uint32_t polls = 0;
-                while (!mbar_test(bar0 + st * 8, (parity >> st) & 1u)) {
-                    if (((++polls) & 0xfffffu) == 0u) {            /* bounded: give up after ~1e8 polls */
-                        if (polls > (1u << 27)) status_fail(r.cache.status, BAM_ETIMEDOUT, BAM_AT_TMA, q);
-                        if (status_bad(r.cache.status)) { failed = true; break; }
-                    }
-                }
-                parity ^= 1u << st;
+                /* a failure anywhere in the launch ends the scan: nothing more is read or issued */
+                if (!wait_stage(st, q) || status_bad(r.cache.status)) { failed = true; break; }
                 const uint8_t* sm = bam_dyn_smem + (size_t)(wib * 2 + st) * BAM_EMU_STAGE_BYTES;
 #pragma unroll
                 for (uint32_t o = lane * 16; o < BAM_EMU_STAGE_BYTES; o += 512) {
@@ -568,6 +607,12 @@ struct PageScanWork {
                 }
                 __syncwarp();                                      /* everyone has read the stage       */
                 if (q + 2 < n_pieces) issue(q + 2);
+            }
+            /* leaving early: let the loads that are still under way land first (bounded), so that no bulk
+             * copy targets this block's shared memory after the block has gone */
+            if (failed) {
+                for (uint32_t st = 0; st < 2; st++)
+                    if ((inflight >> st) & 1u) (void)wait_stage(st, 0xffffffffull);
             }
             if ((ok >> lane) & 1u) r.release_page(slot, 1);
         }
@@ -725,7 +770,6 @@ extern "C" int bam_ctrl_create(bam_ctrl_t* out, int device, uint64_t store_bytes
     c->emu.n_ctrl_blocks = BAM_DEFAULT_CTRL_BLOCKS;
     c->emu.lba_log2 = log2_u32(lba_bytes); c->emu.mps_log2 = 12;
     c->emu.batch = 32; c->emu.sys_scope = c->sys_scope;
-    if (const char* e = getenv("BAM_EMU_PROCS_PER_QUEUE")) c->emu.procs_per_queue = (uint32_t)strtoul(e, nullptr, 0);
     c->emu.consumers_remaining = c->d_remaining; c->emu.status = c->d_status;
     int rc = upload_queue_image(c);
     if (rc != BAM_OK) { cudaFree(c->arena); cudaFreeHost(c->store_host); delete c; return rc; }
@@ -1083,51 +1127,68 @@ extern "C" int bam_cache_descriptor(bam_cache_t pc, void* out, size_t out_bytes)
 
 /* ---- arrays ----------------------------------------------------------------------------------- */
 
-extern "C" int bam_array_create_dist(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
-                                     uint64_t store_byte_offset, uint32_t dist)
+extern "C" int bam_array_create_ranges(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
+                                       const bam_range_desc_t* ranges, uint32_t n_ranges)
 {
     if (!out) return BAM_EINVAL;
     *out = nullptr;
-    if (!pc || n_elems == 0 || (elem_bytes != 4 && elem_bytes != 8)) return BAM_EINVAL;
-    if (dist != BAM_DIST_REPLICATE && dist != BAM_DIST_STRIPE) return BAM_EINVAL;
-    if (store_byte_offset % pc->d.page_size) return BAM_EINVAL;
-    const uint64_t page_count = (n_elems * elem_bytes + pc->d.page_size - 1) / pc->d.page_size;
+    if (!pc || n_elems == 0 || (elem_bytes != 4 && elem_bytes != 8) || !ranges || n_ranges == 0) return BAM_EINVAL;
+    if (pc->n_ranges + n_ranges > BAM_MAX_RANGES) return BAM_ENOSPC;
+    const uint64_t psz = pc->d.page_size;
     const uint32_t n_ctrls = pc->d.n_ctrls;
-    /* bytes of the range that each controller must hold, from store_byte_offset on */
-    const uint64_t per_ctrl = (dist == BAM_DIST_STRIPE && n_ctrls > 1)
-                                  ? (page_count + n_ctrls - 1) / n_ctrls * pc->d.page_size
-                                  : n_elems * elem_bytes;
-    if (pc->members.empty()) {
-        if (store_byte_offset + per_ctrl > pc->ctrl->store_bytes) return BAM_EINVAL;
-    } else {
-        for (bam_ctrl* m : pc->members)
-            if (store_byte_offset + per_ctrl > m->store_bytes) return BAM_EINVAL;
+    std::vector<range_d_t<uint64_t>> h(n_ranges);
+    for (uint32_t k = 0; k < n_ranges; k++) {
+        const bam_range_desc_t& d = ranges[k];
+        if (d.index_end <= d.index_start || d.index_end > n_elems) return BAM_EINVAL;
+        if (d.dist != BAM_DIST_REPLICATE && d.dist != BAM_DIST_STRIPE) return BAM_EINVAL;
+        if (d.store_byte_offset % psz || d.page_start_offset >= psz || d.page_start_offset % elem_bytes) return BAM_EINVAL;
+        for (uint32_t j = 0; j < k; j++)            /* index ranges must not overlap */
+            if (d.index_start < ranges[j].index_end && ranges[j].index_start < d.index_end) return BAM_EINVAL;
+        const uint64_t bytes = d.page_start_offset + (d.index_end - d.index_start) * elem_bytes;
+        const uint64_t page_count = (bytes + psz - 1) / psz;
+        /* bytes of the range that each controller must hold, from store_byte_offset on */
+        const uint64_t per_ctrl = (d.dist == BAM_DIST_STRIPE && n_ctrls > 1) ? (page_count + n_ctrls - 1) / n_ctrls * psz : bytes;
+        if (pc->members.empty()) {
+            if (d.store_byte_offset + per_ctrl > pc->ctrl->store_bytes) return BAM_EINVAL;
+        } else {
+            for (bam_ctrl* m : pc->members)
+                if (d.store_byte_offset + per_ctrl > m->store_bytes) return BAM_EINVAL;
+        }
+        range_d_t<uint64_t>& r = h[k];
+        r.index_start = d.index_start; r.count = d.index_end; r.range_id = pc->n_ranges + k;
+        r.page_start_offset = d.page_start_offset;
+        r.page_start = d.store_byte_offset / psz;
+        r.page_count = page_count;
+        r.n_elems_per_page = psz / elem_bytes;
+        r.dist = d.dist; r.pad_ = 0;
+        r.cache = pc->d;
     }
-    if (pc->n_ranges >= BAM_MAX_RANGES) return BAM_ENOSPC;
     CK(cudaSetDevice(pc->ctrl->device));
     bam_array* a = new (std::nothrow) bam_array();
     if (!a) return BAM_ENOMEM;
-    a->pc = pc; a->elem_bytes = elem_bytes; a->n_elems = n_elems;
-    range_d_t<uint64_t>& r = a->h_range;
-    r.index_start = 0; r.count = n_elems; r.range_id = pc->n_ranges;
-    r.page_start_offset = 0;
-    r.page_start = store_byte_offset / pc->d.page_size;
-    r.page_count = page_count;
-    r.n_elems_per_page = pc->d.page_size / elem_bytes;
-    r.dist = dist; r.pad_ = 0;
-    r.cache = pc->d;
+    a->pc = pc; a->elem_bytes = elem_bytes; a->n_elems = n_elems; a->n_ranges = n_ranges;
+    a->h_range = h[0];
     struct { uint64_t n_elems, start_offset, n_ranges; void* d_ranges; } h_arr;
-    cudaError_t e = cudaMalloc(&a->d_range, sizeof r);
+    cudaError_t e = cudaMalloc(&a->d_range, sizeof(range_d_t<uint64_t>) * n_ranges);
     if (e == cudaSuccess) e = cudaMalloc(&a->d_array, sizeof h_arr);
-    if (e == cudaSuccess) e = cudaMemcpy(a->d_range, &r, sizeof r, cudaMemcpyHostToDevice);
-    h_arr.n_elems = n_elems; h_arr.start_offset = store_byte_offset; h_arr.n_ranges = 1; h_arr.d_ranges = a->d_range;
+    if (e == cudaSuccess) e = cudaMemcpy(a->d_range, h.data(), sizeof(range_d_t<uint64_t>) * n_ranges, cudaMemcpyHostToDevice);
+    h_arr.n_elems = n_elems; h_arr.start_offset = ranges[0].store_byte_offset; h_arr.n_ranges = n_ranges; h_arr.d_ranges = a->d_range;
     if (e == cudaSuccess) e = cudaMemcpy(a->d_array, &h_arr, sizeof h_arr, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMemcpy(pc->d.range_page_starts + r.range_id, &r.page_start, 8, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMemcpy(pc->d.range_dists + r.range_id, &dist, 4, cudaMemcpyHostToDevice);
+    for (uint32_t k = 0; k < n_ranges && e == cudaSuccess; k++) {
+        e = cudaMemcpy(pc->d.range_page_starts + h[k].range_id, &h[k].page_start, 8, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(pc->d.range_dists + h[k].range_id, &h[k].dist, 4, cudaMemcpyHostToDevice);
+    }
     if (e != cudaSuccess) { g_last_cuda = e; cudaFree(a->d_range); cudaFree(a->d_array); delete a; return BAM_ECUDA; }
-    pc->n_ranges++;
+    pc->n_ranges += n_ranges;
     *out = a;
     return BAM_OK;
+}
+
+extern "C" int bam_array_create_dist(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
+                                     uint64_t store_byte_offset, uint32_t dist)
+{
+    const bam_range_desc_t one = { 0, n_elems, store_byte_offset, 0, dist, 0 };
+    return bam_array_create_ranges(out, pc, n_elems, elem_bytes, &one, 1);
 }
 
 extern "C" int bam_array_create(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
@@ -1184,6 +1245,13 @@ extern "C" int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t r
     if (!a || a->elem_bytes != 8) return BAM_EINVAL;
     bam_ctrl* c = a->pc->ctrl;
     CK(cudaSetDevice(c->device));
+    if (a->n_ranges > 1) {
+        ArrayReadRangesWork m;
+        m.arr.n_elems = a->n_elems; m.arr.start_offset = 0; m.arr.n_ranges = a->n_ranges;
+        m.arr.d_ranges = static_cast<range_d_t<uint64_t>*>(a->d_range);
+        m.n_lanes = n_lanes; m.reqs_per_lane = reqs_per_lane; m.idx = idx_dev; m.access_seed = access_seed; m.sum_out = sum_out_dev;
+        return launch_fused(c, m, (cudaStream_t)stream);
+    }
     ArrayReadWork w;
     w.r = a->h_range; w.n_lanes = n_lanes; w.reqs_per_lane = reqs_per_lane; w.idx = idx_dev;
     w.access_seed = access_seed; w.sum_out = sum_out_dev;
@@ -1197,7 +1265,7 @@ extern "C" int bam_launch_array_write(bam_array_t a, uint64_t n, const uint64_t*
     bam_ctrl* c = a->pc->ctrl;
     CK(cudaSetDevice(c->device));
     ArrayWriteWork w;
-    w.arr.n_elems = a->n_elems; w.arr.start_offset = 0; w.arr.n_ranges = 1;
+    w.arr.n_elems = a->n_elems; w.arr.start_offset = 0; w.arr.n_ranges = a->n_ranges;
     w.arr.d_ranges = static_cast<range_d_t<uint64_t>*>(a->d_range);
     w.n = n; w.idx = idx_dev; w.val_seed = val_seed; w.addend = addend;
     return launch_fused(c, w, (cudaStream_t)stream);
@@ -1237,8 +1305,9 @@ extern "C" int bam_launch_pattern_read_impl(bam_array_t a, uint32_t pattern, uin
     if ((pattern == BAM_PATTERN_RANDOM || pattern == BAM_PATTERN_RANDOM_WARP) && !assignment_dev) return BAM_EINVAL;
     bam_ctrl* c = a->pc->ctrl;
     CK(cudaSetDevice(c->device));
+    if (a->n_ranges > 1 && impl == BAM_IMPL_ARRAY) return BAM_EINVAL;       /* that form reads through one range held by value */
     PatternWork w;
-    w.arr.n_elems = a->n_elems; w.arr.start_offset = 0; w.arr.n_ranges = 1;
+    w.arr.n_elems = a->n_elems; w.arr.start_offset = 0; w.arr.n_ranges = a->n_ranges;
     w.arr.d_ranges = static_cast<range_d_t<uint64_t>*>(a->d_range);
     w.rng = a->h_range;
     w.pattern = pattern; w.impl = impl; w.n_elems = n_elems; w.n_warps = n_warps; w.n_pages_per_warp = n_pages_per_warp; w.stride = stride;
@@ -1303,7 +1372,7 @@ extern "C" int bam_cache_flush(bam_cache_t pc, void* stream)
 extern "C" int bam_launch_page_scan(bam_array_t a, uint64_t n_pages, const uint64_t* pages_dev, uint64_t first_page,
                                     uint64_t* sum_out_dev, void* stream)
 {
-    if (!a || a->elem_bytes != 8) return BAM_EINVAL;
+    if (!a || a->elem_bytes != 8 || a->n_ranges != 1 || a->h_range.page_start_offset != 0) return BAM_EINVAL;
     bam_ctrl* c = a->pc->ctrl;
     CK(cudaSetDevice(c->device));
     PageScanWork w;

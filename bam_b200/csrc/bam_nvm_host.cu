@@ -124,7 +124,8 @@ int start_service_locked(host_ctrl* h)
     /* the data pointers of host-submitted commands are checked against the memory mapped for DMA */
     if (cudaMemcpy(h->d_windows, h->windows, sizeof(bam_dma_window_t) * NVM_HOST_MAX_WINDOWS, cudaMemcpyHostToDevice) != cudaSuccess) return EIO;
     emu.windows = h->d_windows; emu.n_windows = h->n_windows;
-    if (getenv("BAM_NVM_DEBUG")) {
+#ifdef BAM_NVM_DEBUG          /* a build-time aid: dumps every pointer the service kernel is handed */
+    {
         auto show = [](const char* what, const void* p) {
             cudaPointerAttributes a;
             cudaError_t e = cudaPointerGetAttributes(&a, p);
@@ -143,6 +144,7 @@ int start_service_locked(host_ctrl* h)
         for (uint32_t k = 0; k < h->n_windows; k++)
             fprintf(stderr, "[nvm] window %u: %p + %llu\n", k, (void*)(uintptr_t)h->windows[k].base, (unsigned long long)h->windows[k].bytes);
     }
+#endif
     if (cudaFuncSetAttribute(k_nvm_host_service, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BAM_EMU_SMEM_BYTES) != cudaSuccess) return EIO;
     k_nvm_host_service<<<NVM_HOST_SERVICE_BLOCKS, BAM_THREADS, BAM_EMU_SMEM_BYTES, h->stream>>>(emu);
     if (cudaGetLastError() != cudaSuccess) return EIO;

@@ -252,6 +252,20 @@ class Array:
               "bam_array_create_dist")
         self.n_elems, self.elem_bytes, self.dist = n_elems, elem_bytes, dist
 
+    @classmethod
+    def from_ranges(cls, cache, n_elems, ranges, elem_bytes=8):
+        """array_t over several range_t: `ranges` is a list of (index_start, index_end, store_byte_offset,
+        page_start_offset, dist) -- element index_start of a range lives page_start_offset bytes into the
+        backing page at store_byte_offset."""
+        a = cls.__new__(cls)
+        a.lib, a.cache, a.h = cache.lib, cache, C.c_void_p()
+        descs = (_lib.RangeDesc * len(ranges))(*[_lib.RangeDesc(r[0], r[1], r[2], r[3] if len(r) > 3 else 0,
+                                                                r[4] if len(r) > 4 else REPLICATE, 0) for r in ranges])
+        check(a.lib.bam_array_create_ranges(C.byref(a.h), cache.h, n_elems, elem_bytes, descs, len(ranges)),
+              "bam_array_create_ranges")
+        a.n_elems, a.elem_bytes, a.dist = n_elems, elem_bytes, None
+        return a
+
     def close(self):
         if self.h:
             self.lib.bam_array_destroy(self.h)

@@ -226,6 +226,9 @@ BAM_DEV __noinline__ emu_list_step emu_list_entry(const bam_emu_d_t& c, uint64_t
 BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t stage_smem, uint32_t bar, uint32_t& parity)
 {
     const uint64_t mps = 1ull << c.mps_log2;
+    /* a PRP segment is moved through one stage in one piece: the controller's memory page size must be the
+     * stage size (both 4 KiB; bam_ctrl_create and the libnvm layer set mps_log2 = 12) */
+    if (mps != BAM_EMU_STAGE_BYTES) return BAM_SC_INVALID_FIELD;
     uint8_t* const store = c.qps[m.q].store;               /* the media of the controller that owns the queue */
     uint64_t first = mps - (m.prp1 & (mps - 1));
     if (first > m.bytes) first = m.bytes;

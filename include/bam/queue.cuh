@@ -31,6 +31,7 @@
 #ifndef BAM_QUEUE_CUH
 #define BAM_QUEUE_CUH
 
+#include <stddef.h>
 #include "sync.cuh"
 
 namespace bam {
@@ -222,9 +223,23 @@ BAM_DEV uint32_t cq_poll(QueuePair* qp, uint32_t cid)
     }
 }
 
-/* Kept for source compatibility with callers of the reference API: the reaper inside cq_poll
- * has already consumed the entry, advanced the head and rung the doorbell. */
-BAM_DEV void cq_dequeue(nvm_queue_t*, uint32_t, nvm_queue_t*) {}
+/* The reference's parameter lists (include/nvm_parallel_queue.h:333, :379, :425), so that its call sequence
+ *     sq_pos = sq_enqueue(&qp->sq, &cmd); cq_pos = cq_poll(&qp->cq, cid); sq_dequeue(&qp->sq, sq_pos);
+ *     cq_dequeue(&qp->cq, cq_pos); put_cid(&qp->sq, cid);        (benchmarks/block/main.cu:86-93)
+ * compiles and works unchanged.  cq_poll finds the queue pair that embeds `cq`; what it returns is the NVMe
+ * status of the command (0 = success), not a queue position: the reaper inside it has already consumed the
+ * entry, re-opened the submission slot, advanced the head and rung the doorbell, so sq_dequeue and
+ * cq_dequeue have nothing left to do and ignore their position argument. */
+BAM_DEV uint32_t cq_poll(nvm_queue_t* cq, uint16_t search_cid, uint32_t* loc_ = nullptr, uint32_t* cq_head = nullptr)
+{
+    QueuePair* qp = reinterpret_cast<QueuePair*>(reinterpret_cast<char*>(cq) - offsetof(QueuePair, cq));
+    const uint32_t status = cq_poll(qp, (uint32_t)search_cid);
+    if (loc_) *loc_ = 0;
+    if (cq_head) *cq_head = ld_relaxed_gpu(&cq->head);
+    return status;
+}
+BAM_DEV void sq_dequeue(nvm_queue_t*, uint16_t) {}
+BAM_DEV void cq_dequeue(nvm_queue_t*, uint16_t, nvm_queue_t* = nullptr, uint32_t = 0, uint32_t = 0) {}
 
 /* ================================================================================================
  * Warp-cooperative I/O.

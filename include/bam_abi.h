@@ -62,8 +62,7 @@ int bam_ctrl_write_store(bam_ctrl_t c, uint64_t byte_offset, const void* src, ui
 /* Controller warps: n_blocks blocks of the fused launches run the command processor;
  * batch = the most commands a warp reserves from a queue at a time (at most 32; a queue shallower than
  * 16 x batch is cut into batches of a sixteenth of its depth, 8 at least).  0 keeps the current value.
- * At most 32 processor warps serve one queue; the environment variable BAM_EMU_PROCS_PER_QUEUE, read by
- * bam_ctrl_create, overrides that number (a tuning aid). */
+ * At most 32 processor warps serve one queue. */
 int bam_ctrl_configure(bam_ctrl_t c, uint32_t n_ctrl_blocks, uint32_t batch, uint64_t spin_timeout_ns);
 /* Upper limit for one fused launch (default 300 s): the controller blocks flag BAM_ETIMEDOUT and
  * every wait in the launch drains. */
@@ -131,7 +130,8 @@ int bam_cache_descriptor(bam_cache_t pc, void* out, size_t out_bytes);  /* page_
  * All calls share that array: calls that can overlap on the GPU (different streams, no ordering
  * between them) race and give wrong counts; calls on one stream are safe.  The first call on each
  * device also looks up the array's device address; make that first call outside any stream
- * capture. */
+ * capture.  Like every entry point that takes a cache, the call makes the cache's GPU the calling
+ * thread's current device (cudaSetDevice) and leaves it so. */
 int bam_cache_audit_noalloc(bam_cache_t pc, uint64_t* violations_out_dev, void* stream);
 
 /* ---- arrays --------------------------------------------------------------------------------
@@ -147,6 +147,25 @@ int bam_array_create(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_
  * lives on controller p % n at backing page store_byte_offset / page_size + p / n). */
 int bam_array_create_dist(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
                           uint64_t store_byte_offset, uint32_t dist);
+/* array_t<T> over a vector of range_t<T> (page_cache.h:1754-1772; the device side looks an index up with
+ * find_range, :1318-1329): range k covers the element indices [index_start, index_end) and its element
+ * index_start lives page_start_offset bytes into the backing page at store_byte_offset (range_t's
+ * page_start * page_size and page_start_offset, :985-1030 -- the shape benchmarks/bfs/main.cu:1481-1484 builds
+ * for an edge list that starts at a file offset).  store_byte_offset must be page aligned,
+ * page_start_offset smaller than a page and a multiple of elem_bytes; index ranges must not overlap;
+ * indices outside every range fail with BAM_ERANGE in the status block.  bam_launch_array_read,
+ * bam_launch_array_write and the cursor patterns accept such arrays; the launchers that walk whole pages
+ * of one range (page scan, graph traversals, the array[] pattern form) need a single range with
+ * page_start_offset 0 and return BAM_EINVAL otherwise. */
+typedef struct {
+    uint64_t index_start, index_end;
+    uint64_t store_byte_offset;
+    uint64_t page_start_offset;
+    uint32_t dist;               /* BAM_DIST_REPLICATE / BAM_DIST_STRIPE */
+    uint32_t reserved;
+} bam_range_desc_t;
+int bam_array_create_ranges(bam_array_t* out, bam_cache_t pc, uint64_t n_elems, uint32_t elem_bytes,
+                            const bam_range_desc_t* ranges, uint32_t n_ranges);
 int bam_array_destroy(bam_array_t a);
 void* bam_array_device_ptr(bam_array_t a);         /* array_d_t<T>* (array_t::d_array_ptr) */
 

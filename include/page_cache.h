@@ -91,7 +91,7 @@ struct range_t {
         : index_start(is), count(cnt), page_start(ps), page_count(pc), page_start_offset(pso), page_size(p_size), cache(c),
           dist(d)
     {
-        if (pso != 0) throw std::runtime_error("range_t: page_start_offset must be 0");
+        if (pso >= p_size) throw std::runtime_error("range_t: page_start_offset must be smaller than a page");
     }
 };
 
@@ -104,12 +104,16 @@ struct array_t {
     array_t(const uint64_t num_elems, const uint64_t disk_start_offset, const std::vector<range_t<T>*>& ranges,
             uint32_t /*cudaDevice*/)
     {
-        if (ranges.size() != 1) throw std::runtime_error("array_t: exactly one range is supported");
-        range_t<T>* r = ranges[0];
-        cache = r->cache;
+        if (ranges.empty()) throw std::runtime_error("array_t: at least one range is needed");
+        cache = ranges[0]->cache;
         (void)disk_start_offset;
-        int rc = bam_array_create_dist(&h, cache->h, num_elems, (uint32_t)sizeof(T), r->page_start * r->page_size,
-                                       (uint32_t)r->dist);
+        std::vector<bam_range_desc_t> descs;
+        for (const range_t<T>* r : ranges) {
+            if (r->cache != cache) throw std::runtime_error("array_t: all ranges must sit on one page cache");
+            descs.push_back(bam_range_desc_t{ r->index_start, r->count, r->page_start * r->page_size, r->page_start_offset,
+                                              (uint32_t)r->dist, 0u });
+        }
+        int rc = bam_array_create_ranges(&h, cache->h, num_elems, (uint32_t)sizeof(T), descs.data(), (uint32_t)descs.size());
         if (rc != 0) throw std::runtime_error(std::string("Failed to create array: ") + bam_strerror(rc));
         d_array_ptr = static_cast<array_d_t<T>*>(bam_array_device_ptr(h));
     }

@@ -3,6 +3,7 @@
  * driven from user kernels and checked on the host against the store's definition:
  *   array_d_t::get_raw / release_raw, acquire_page / release_page, memcpy  (page_cache.h:1256-1537)
  *   bafs_ptr::memcpy_to_array_aligned                                      (bafs_ptr.h:121-123)
+ *   bafs_ptr: *p, p[i], p + i, p - i, ++p, p++, --p, p--, ==, !=, p(i, v)   (bafs_ptr.h:17-132)
  *   read_data / write_data / access_data_async / poll_async                (page_cache.h:1930-2132)
  * Prints one JSON line with the number of mismatches of each part.
  */
@@ -36,6 +37,33 @@ struct RawViewKernel {                /* out[k] = a[idx[k]] via get_raw, out2[k]
                 uint64_t* p = a->acquire_page(idx[k], slot, start, end);
                 out2[k] = (p && idx[k] >= start && idx[k] < end) ? p[idx[k] - start] : 0;
                 a->release_page(idx[k], slot);
+            }
+        }
+    }
+};
+
+struct BafsOpsKernel {                /* thread k works on a pointer to element 5 k; four reads and the comparisons per thread */
+    array_d_t<uint64_t>* a;
+    uint64_t n;
+    uint64_t* out;                    /* out[4 k ..]: *p, p[3], *(p + 7), the element after three steps from p + 7 */
+    unsigned int* bad_cmp;
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint64_t stride = (uint64_t)nvb * blockDim.x;
+        for (uint64_t base = (uint64_t)vb * blockDim.x + (threadIdx.x & ~31u); base < n; base += stride) {
+            const uint64_t k = base + (threadIdx.x & 31u);
+            if (k < n) {
+                bafs_ptr<uint64_t> p(a, 5 * k);
+                out[4 * k] = *p;
+                out[4 * k + 1] = p[3];
+                bafs_ptr<uint64_t> q = p + 7;
+                out[4 * k + 2] = *q;
+                ++q; q++; --q;                                   /* 5 k + 8 */
+                bafs_ptr<uint64_t> r = q--;                      /* r at 5 k + 8, q back at 5 k + 7 */
+                out[4 * k + 3] = *r;
+                const bool ok = (p + 7 == q) && (r - 1 == q) && (p != q) && !(p == r) && ((p + 8) == r);
+                if (!ok) atomicAdd(bad_cmp, 1u);
             }
         }
     }
@@ -128,6 +156,23 @@ int main()
         cuda_err_chk(cudaMemcpy(out2.data(), d_out2, n * 8, cudaMemcpyDeviceToHost));
         for (uint64_t k = 0; k < n; k++) { bad_raw += out[k] != store[idx[k]]; bad_acq += out2[k] != store[idx[k]]; }
 
+        /* 1b. the pointer operators of bafs_ptr, on the device */
+        const uint64_t n_ops = 1 << 15;
+        uint64_t* d_ops;
+        unsigned int* d_badcmp;
+        cuda_err_chk(cudaMalloc(&d_ops, n_ops * 4 * 8)); cuda_err_chk(cudaMalloc(&d_badcmp, 4));
+        cuda_err_chk(cudaMemset(d_badcmp, 0, 4));
+        cuda_err_chk(bam::launch_fused(h_pc.emu(), BafsOpsKernel{ a.d_array_ptr, n_ops, d_ops, d_badcmp }));
+        cuda_err_chk(cudaDeviceSynchronize());
+        std::vector<uint64_t> ops(n_ops * 4);
+        unsigned int badcmp = 0;
+        cuda_err_chk(cudaMemcpy(ops.data(), d_ops, ops.size() * 8, cudaMemcpyDeviceToHost));
+        cuda_err_chk(cudaMemcpy(&badcmp, d_badcmp, 4, cudaMemcpyDeviceToHost));
+        int bad_ops = (int)badcmp;
+        for (uint64_t k = 0; k < n_ops; k++)
+            bad_ops += (ops[4 * k] != store[5 * k]) + (ops[4 * k + 1] != store[5 * k + 3]) + (ops[4 * k + 2] != store[5 * k + 7]) +
+                       (ops[4 * k + 3] != store[5 * k + 8]);
+
         /* 2. memcpy: 300 copies of 1000 elements from odd offsets (every copy crosses pages, half are unaligned) */
         const uint64_t n_copies = 300, len = 1000, first = 3, step = 3001;
         uint64_t* d_dst;
@@ -173,9 +218,9 @@ int main()
         }
         bam_status_out_t st;
         bam_ctrl_status(ctrl.h, &st, 0);
-        printf("{\"bad_get_raw\": %d, \"bad_acquire_page\": %d, \"bad_memcpy\": %d, \"bad_raw_io\": %d, \"bad_async\": %d, "
-               "\"status\": %u, \"where\": %u, \"audit\": %llu}\n", bad_raw, bad_acq, bad_cpy, bad_io, bad_async, st.code, st.where,
-               (unsigned long long)bad_audit);
+        printf("{\"bad_get_raw\": %d, \"bad_acquire_page\": %d, \"bad_bafs_ptr_ops\": %d, \"bad_memcpy\": %d, \"bad_raw_io\": %d, "
+               "\"bad_async\": %d, \"status\": %u, \"where\": %u, \"audit\": %llu}\n", bad_raw, bad_acq, bad_ops, bad_cpy, bad_io, bad_async,
+               st.code, st.where, (unsigned long long)bad_audit);
         ctrl.close();
     } catch (const std::exception& ex) {
         fprintf(stderr, "error: %s\n", ex.what());

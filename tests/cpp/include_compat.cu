@@ -85,6 +85,23 @@ __global__ void touch(array_d_t<uint64_t>* a, QueuePair* qp, Controller* c, unsi
     t.fini();
 }
 
+/* the reference's raw access sequence (benchmarks/block/main.cu:66-93, access_data there), compiled as written */
+__device__ void ref_access_data(QueuePair* qp, uint64_t starting_lba, uint64_t n_blocks, uint64_t prp1, uint64_t prp2)
+{
+    nvm_cmd_t cmd;
+    uint16_t cid = get_cid(&(qp->sq));
+    nvm_cmd_header(&cmd, cid, NVM_IO_READ, qp->nvmNamespace);
+    nvm_cmd_data_ptr(&cmd, prp1, prp2);
+    nvm_cmd_rw_blks(&cmd, starting_lba, n_blocks);
+    uint16_t sq_pos = sq_enqueue(&qp->sq, &cmd);
+    uint32_t cq_pos = cq_poll(&qp->cq, cid);
+    sq_dequeue(&qp->sq, sq_pos);
+    cq_dequeue(&qp->cq, cq_pos);
+    put_cid(&qp->sq, cid);
+}
+
+__global__ void touch_raw(QueuePair* qp, uint64_t prp1) { ref_access_data(qp, 0, 8, prp1, 0); }
+
 /* --prp n_lists n_pages: what nvm_cmd_data makes of a transfer of n_pages pages at 0x100000 + i * 4096 with
  * list pages at bus addresses 0xa000, 0xb000, ... (initialised to all ones), as JSON */
 static int show_prp(size_t n_lists, size_t n_pages)

@@ -55,7 +55,7 @@ def test_cpp_device_api(cuda, bam):
     from bam_b200 import _build
     exe = _build.build_cpp_bench(name="device_api_bench")
     r = run(exe)
-    assert r == {"bad_get_raw": 0, "bad_acquire_page": 0, "bad_memcpy": 0, "bad_raw_io": 0, "bad_async": 0,
+    assert r == {"bad_get_raw": 0, "bad_acquire_page": 0, "bad_bafs_ptr_ops": 0, "bad_memcpy": 0, "bad_raw_io": 0, "bad_async": 0,
                  "status": 0, "where": 0, "audit": 0}
 
 

@@ -57,8 +57,19 @@ def test_noalloc_audit_matches_allocating_audit(cuda, bam, orc):
 def test_noalloc_audit_rejects_bad_arguments(cuda, bam):
     lib = bam.load()
     assert lib.bam_cache_audit_noalloc(None, None, None) == 22
+    # the size check needs a real cache of one slot more than the scratch covers: about 4.5 GB of device
+    # memory.  On a GPU that other jobs have filled, that part is skipped rather than failed.
+    free_bytes, _ = cuda.cuda.mem_get_info()
+    if free_bytes < 6 << 30:
+        pytest.skip("less than 6 GB of device memory free: the oversize cache cannot be built")
     ctrl = bam.Controller(1 << 20, 0, queue_depth=8, num_queues=1)
-    cache = bam.PageCache(ctrl, 512, 8_380_417)            # one slot more than the scratch covers
+    try:
+        cache = bam.PageCache(ctrl, 512, 8_380_417)
+    except bam.BamError as e:
+        ctrl.close()
+        if e.code == 12:
+            pytest.skip("the oversize cache could not be allocated")
+        raise
     out = cuda.zeros(1, dtype=cuda.int64, device="cuda")
     rc = lib.bam_cache_audit_noalloc(cache.h, C.c_void_p(out.data_ptr()), None)
     assert rc == 7 and b"limit" in lib.bam_strerror(rc)
