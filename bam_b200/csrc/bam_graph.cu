@@ -41,106 +41,180 @@ struct graph_scratch_t {
     graph_item_t items[1];
 };
 
-/* Pin the page of `r` holding element index i for the whole warp (lane 0 asks). */
-BAM_DEV const uint64_t* warp_page_of(const range_d_t<uint64_t>& r, uint64_t i, uint32_t queue, uint32_t& slot)
-{
-    const uint64_t page = r.get_page(i);
-    slot = range_pin_page(r, 0xffffffffu, (threadIdx.x & 31u) == 0u, page, 1, queue);
-    slot = __shfl_sync(0xffffffffu, slot, 0);
-    if (slot == BAM_SLOT_ERR) return nullptr;
-    return reinterpret_cast<const uint64_t*>(r.get_cache_page_addr(slot));
-}
+/* ---- edge weights (SSSP): edge j of the column array carries weight wt[j] (u32 array) --------------
+ * A 4 KiB page of column indices holds 512 edges; their weights are 2 KiB, so they sit inside ONE page of
+ * the weight array (weight page = column page >> 1 for equal page sizes).  The walkers below are written
+ * once for both kinds of graph: Wt is wrange_t for a weighted graph and no_weights_t otherwise, and the
+ * edge callback always receives a weight (0 without weights). */
+typedef range_d_t<uint32_t> wrange_t;
+struct no_weights_t {};
 
-/* The whole warp walks cols[begin, end) page by page and calls fn(neighbour) per edge. */
-template <class EdgeFn>
-BAM_DEV bool warp_walk_edges(const range_d_t<uint64_t>& col, uint64_t begin, uint64_t end, uint32_t queue, EdgeFn fn)
+BAM_DEV const range_d_t<uint64_t>& as_u64_range(const wrange_t& w) { return reinterpret_cast<const range_d_t<uint64_t>&>(w); }
+template <class Wt> struct has_weights { static constexpr bool value = false; };
+template <> struct has_weights<wrange_t> { static constexpr bool value = true; };
+
+/* The whole warp walks cols[begin, end) and calls fn(neighbour, weight) per edge.  Up to BAM_WALK_PAGES
+ * column pages are pinned per step in ONE cooperative call (lane k asks for the k-th of them, lanes 16..
+ * for the weight pages that go with them), so their reads are in flight together; then the warp consumes
+ * them one after the other, 256 contiguous bytes of column indices per step. */
+#ifndef BAM_WALK_PAGES
+#define BAM_WALK_PAGES 4u
+#endif
+template <class Wt, class EdgeFn>
+BAM_DEV bool warp_walk_edges(const range_d_t<uint64_t>& col, const Wt& wt, uint64_t begin, uint64_t end, uint32_t queue, EdgeFn fn)
 {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t epp_log = col.cache.page_size_log - 3;
     for (uint64_t i = begin; i < end;) {
-        uint64_t pend = ((i >> epp_log) + 1) << epp_log;               /* first index of the next page */
-        if (pend > end) pend = end;
-        uint32_t slot;
-        const uint64_t* base = warp_page_of(col, i, queue, slot);
-        if (!base) return false;
-        const uint64_t page_first = (i >> epp_log) << epp_log;
-        for (uint64_t j = i + lane; j < pend; j += 32) fn(base[j - page_first]);
+        const uint64_t p0 = i >> epp_log;
+        const uint64_t p_last = (end - 1) >> epp_log;
+        const uint32_t np = p_last - p0 + 1 < BAM_WALK_PAGES ? (uint32_t)(p_last - p0 + 1) : BAM_WALK_PAGES;
+        bool want = lane < np;
+        uint64_t page = p0 + lane;
+        uint64_t wp0 = 0;
+        uint32_t wshift = 0;
+        const range_d_t<uint64_t>* r = &col;
+        if constexpr (has_weights<Wt>::value) {
+            wshift = (wt.cache.page_size_log - 2) - epp_log;              /* column pages per weight page, log2 */
+            wp0 = p0 >> wshift;
+            const uint32_t nw = (uint32_t)(((p0 + np - 1) >> wshift) - wp0 + 1);
+            if (lane >= 16) { r = &as_u64_range(wt); page = wp0 + (lane - 16); want = lane - 16 < nw; }
+        }
+        uint32_t slot = range_pin_page(*r, 0xffffffffu, want, page, 1, queue);
+        const bool bad = __any_sync(0xffffffffu, want && slot == BAM_SLOT_ERR);
+        if (!bad) {
+            for (uint32_t k = 0; k < np; k++) {
+                const uint32_t sl = __shfl_sync(0xffffffffu, slot, k);
+                const uint64_t page_first = (p0 + k) << epp_log;
+                const uint64_t lo = page_first > i ? page_first : i;
+                uint64_t hi = page_first + (1ull << epp_log);
+                if (hi > end) hi = end;
+                const uint64_t* base = reinterpret_cast<const uint64_t*>(col.get_cache_page_addr(sl));
+                if constexpr (has_weights<Wt>::value) {
+                    const uint64_t wp = (p0 + k) >> wshift;
+                    const uint32_t wsl = __shfl_sync(0xffffffffu, slot, 16 + (int)(wp - wp0));
+                    const uint32_t* wbase = reinterpret_cast<const uint32_t*>(wt.get_cache_page_addr(wsl));
+                    const uint64_t wfirst = wp << (wt.cache.page_size_log - 2);
+                    for (uint64_t j = lo + lane; j < hi; j += 32) fn(base[j - page_first], wbase[j - wfirst]);
+                } else {
+                    for (uint64_t j = lo + lane; j < hi; j += 32) fn(base[j - page_first], 0u);
+                }
+            }
+        }
         __syncwarp();
-        if (lane == 0) col.release_page(slot, 1);
-        i = pend;
+        if (want && slot <= BAM_SLOT_MAX) r->release_page(slot, 1);
+        if (bad) return false;
+        i = (p0 + np) << epp_log;
     }
     return true;
 }
 
+/* Row offsets [s, e) of the 32 consecutive vertices of a chunk (lane <-> vertex v; the whole warp calls it):
+ * every lane reads off[v] once -- consecutive elements, mostly one cached page, read without a pin -- and
+ * takes its end from the next lane; only the last lane's end is a second read.  Lanes with act == false
+ * get s == e == 0.  Indices are clamped to the array (it has one entry per vertex plus one). */
+BAM_DEV void chunk_offsets(const range_d_t<uint64_t>& off, uint64_t v, bool act, uint32_t queue, uint64_t& s, uint64_t& e)
+{
+#ifdef BAM_EXP_OLD_OFFSETS
+    s = e = 0;
+    if (act) { s = range_read<uint64_t>(off, v, queue); e = range_read<uint64_t>(off, v + 1, queue); }
+    __syncwarp();
+    return;
+#endif
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t last = off.count - 1;                              /* largest valid index */
+    const uint64_t v31 = __shfl_sync(0xffffffffu, v, 31) + 1;
+    const uint64_t mine = range_read<uint64_t>(off, v < last ? v : last, queue);
+    const uint64_t after = range_read<uint64_t>(off, v31 < last ? v31 : last, queue);
+    const uint64_t next = __shfl_down_sync(0xffffffffu, mine, 1);
+    s = act ? mine : 0;
+    e = act ? (lane == 31 ? after : next) : 0;
+}
+
 /* One chunk of 32 consecutive local vertices (lane <-> vertex v, act = vertex is in the frontier).
- * Offsets come through the cache as one or two coalesced page reads.  The FIRST edge page of every
- * active vertex is pinned in one cooperative call (lanes that share a page share a pin, and all
- * missing pages are in flight together); lists that continue on further pages are walked page by
- * page; heavy lists become work items.  fn(src_lane, neighbour) is called for every edge. */
-template <class EdgeFn>
-BAM_DEV bool chunk_visit(const range_d_t<uint64_t>& off, const range_d_t<uint64_t>& col, uint64_t v, uint64_t u_global,
+ * Offsets come through the cache (chunk_offsets).  Without weights the FIRST edge page of every active
+ * vertex is pinned in one cooperative call (lanes that share a page share a pin, and all missing pages are
+ * in flight together) and lists that continue on further pages are walked from there; with weights every
+ * vertex's list is walked in turn (column and weight pages pinned together); heavy lists become work
+ * items.  fn(src_lane, neighbour, weight) is called for every edge. */
+template <class Wt, class EdgeFn>
+BAM_DEV bool chunk_visit(const range_d_t<uint64_t>& off, const range_d_t<uint64_t>& col, const Wt& wt, uint64_t v, uint64_t u_global,
                          bool act, uint32_t queue, graph_scratch_t* scratch, uint64_t& edges, EdgeFn fn)
 {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t epp_log = col.cache.page_size_log - 3;
     uint64_t s = 0, e = 0;
-    if (act) {
-        s = range_read<uint64_t>(off, v, queue);
-        e = range_read<uint64_t>(off, v + 1, queue);
-    }
-    __syncwarp();
+    chunk_offsets(off, v, act, queue, s, e);
     const uint64_t deg = e - s;
     edges += deg;
     bool heavy = act && scratch && deg > BAM_HEAVY_EDGES;
     if (heavy) {
-        const uint32_t n_it = (uint32_t)((deg + BAM_ITEM_EDGES - 1) / BAM_ITEM_EDGES);
+        /* items are cut at multiples of BAM_ITEM_EDGES of the edge index (whole pages), so no two items share
+         * a page: the warps that draw neighbouring items at the same moment never miss on the same page */
+        const uint64_t a0 = (s + BAM_ITEM_EDGES - 1) / BAM_ITEM_EDGES * BAM_ITEM_EDGES;     /* first cut after s */
+        const uint32_t n_it = (uint32_t)((e - a0 + BAM_ITEM_EDGES - 1) / BAM_ITEM_EDGES) + (a0 > s ? 1u : 0u);
         const uint32_t base = atom_add_relaxed(&scratch->n_items, n_it);
         /* publish what fits (the scratch is sized so that everything does); anything beyond the
          * capacity is walked by this warp below, and tickets past the capacity are never waited on */
         const uint32_t fit = base >= scratch->capacity ? 0u : (scratch->capacity - base < n_it ? scratch->capacity - base : n_it);
+        uint64_t b0 = s;
         for (uint32_t k = 0; k < fit; k++) {
             graph_item_t* it = &scratch->items[base + k];
-            const uint64_t b0 = s + (uint64_t)k * BAM_ITEM_EDGES;
+            uint64_t b1 = (b0 / BAM_ITEM_EDGES + 1) * BAM_ITEM_EDGES;
+            if (b1 > e) b1 = e;
             it->u = u_global;
             it->begin = b0;
             __threadfence();
-            st_release_gpu(&it->end, b0 + BAM_ITEM_EDGES < e ? b0 + BAM_ITEM_EDGES : e);
+            st_release_gpu(&it->end, b1);
+            b0 = b1;
         }
-        if (fit < n_it) { s += (uint64_t)fit * BAM_ITEM_EDGES; heavy = false; }
+        if (fit < n_it) { s = b0; heavy = false; }
     }
     const bool light = act && !heavy && e > s;
     const uint32_t lm = __ballot_sync(0xffffffffu, light);
     if (lm == 0) return true;
-    const uint64_t page0 = s >> epp_log;
-    const uint32_t eq = __match_any_sync(0xffffffffu, light ? page0 : (~0ull - lane));
-    const uint32_t leader = __ffs(eq) - 1;
-    uint32_t slot = range_pin_page(col, 0xffffffffu, light && lane == leader, page0, (uint32_t)__popc(eq), queue);
-    slot = __shfl_sync(0xffffffffu, slot, leader);
-    if (__any_sync(0xffffffffu, light && slot == BAM_SLOT_ERR)) return false;
     bool ok = true;
     uint32_t am = lm;
-    while (am) {
-        const int src = __ffs(am) - 1;
-        am &= am - 1;
-        const uint64_t vs = __shfl_sync(0xffffffffu, s, src);
-        const uint64_t ve = __shfl_sync(0xffffffffu, e, src);
-        const uint32_t sl = __shfl_sync(0xffffffffu, slot, src);
-        const uint64_t page_first = (vs >> epp_log) << epp_log;
-        uint64_t first_end = page_first + (1ull << epp_log);
-        if (first_end > ve) first_end = ve;
-        const uint64_t* base = reinterpret_cast<const uint64_t*>(col.get_cache_page_addr(sl));
-        for (uint64_t j = vs + lane; j < first_end; j += 32) fn(src, base[j - page_first]);
-        if (first_end < ve) ok = warp_walk_edges(col, first_end, ve, queue, [&](uint64_t nb) { fn(src, nb); }) && ok;
-        if (!ok) break;
+    if constexpr (has_weights<Wt>::value) {
+        while (am && ok) {
+            const int src = __ffs(am) - 1;
+            am &= am - 1;
+            const uint64_t vs = __shfl_sync(0xffffffffu, s, src);
+            const uint64_t ve = __shfl_sync(0xffffffffu, e, src);
+            ok = warp_walk_edges(col, wt, vs, ve, queue, [&](uint64_t nb, uint32_t w) { fn(src, nb, w); });
+        }
+        __syncwarp();
+        return ok;
+    } else {
+        const uint64_t page0 = s >> epp_log;
+        const uint32_t eq = __match_any_sync(0xffffffffu, light ? page0 : (~0ull - lane));
+        const uint32_t leader = __ffs(eq) - 1;
+        uint32_t slot = range_pin_page(col, 0xffffffffu, light && lane == leader, page0, (uint32_t)__popc(eq), queue);
+        slot = __shfl_sync(0xffffffffu, slot, leader);
+        if (__any_sync(0xffffffffu, light && slot == BAM_SLOT_ERR)) return false;
+        while (am) {
+            const int src = __ffs(am) - 1;
+            am &= am - 1;
+            const uint64_t vs = __shfl_sync(0xffffffffu, s, src);
+            const uint64_t ve = __shfl_sync(0xffffffffu, e, src);
+            const uint32_t sl = __shfl_sync(0xffffffffu, slot, src);
+            const uint64_t page_first = (vs >> epp_log) << epp_log;
+            uint64_t first_end = page_first + (1ull << epp_log);
+            if (first_end > ve) first_end = ve;
+            const uint64_t* base = reinterpret_cast<const uint64_t*>(col.get_cache_page_addr(sl));
+            for (uint64_t j = vs + lane; j < first_end; j += 32) fn(src, base[j - page_first], 0u);
+            if (first_end < ve) ok = warp_walk_edges(col, wt, first_end, ve, queue, [&](uint64_t nb, uint32_t w) { fn(src, nb, w); }) && ok;
+            if (!ok) break;
+        }
+        __syncwarp();
+        if (light && lane == leader && slot != BAM_SLOT_ERR) col.release_page(slot, (uint32_t)__popc(eq));
+        return ok;
     }
-    __syncwarp();
-    if (light && lane == leader && slot != BAM_SLOT_ERR) col.release_page(slot, (uint32_t)__popc(eq));
-    return ok;
 }
 
-/* After its own chunks a warp helps with the heavy items.  fn(u_global, neighbour) per edge. */
-template <class EdgeFn>
-BAM_DEV void consume_heavy_items(const range_d_t<uint64_t>& col, graph_scratch_t* scratch, uint32_t n_warps_total,
+/* After its own chunks a warp helps with the heavy items.  fn(u_global, neighbour, weight) per edge. */
+template <class Wt, class EdgeFn>
+BAM_DEV void consume_heavy_items(const range_d_t<uint64_t>& col, const Wt& wt, graph_scratch_t* scratch, uint32_t n_warps_total,
                                  uint32_t queue, EdgeFn fn)
 {
     if (!scratch) return;
@@ -170,7 +244,7 @@ BAM_DEV void consume_heavy_items(const range_d_t<uint64_t>& col, graph_scratch_t
             if (__any_sync(0xffffffffu, sp.expired(col.cache.status, BAM_AT_PAGE_BUSY, idx))) return;
         }
         const uint64_t u = it->u, begin = it->begin;
-        if (!warp_walk_edges(col, begin, end, queue, [&](uint64_t nb) { fn(u, nb); })) return;
+        if (!warp_walk_edges(col, wt, begin, end, queue, [&](uint64_t nb, uint32_t w) { fn(u, nb, w); })) return;
     }
 }
 
@@ -202,9 +276,9 @@ struct BfsLevelWork {
             const uint64_t v = c0 + lane;
             const bool act = v < v_end && label[v_base + v] == level;
             if (__ballot_sync(0xffffffffu, act) == 0) continue;
-            if (!chunk_visit(off, col, v, v_base + v, act, queue, scratch, edges, [&](int, uint64_t nb) { relax(nb); })) break;
+            if (!chunk_visit(off, col, no_weights_t{}, v, v_base + v, act, queue, scratch, edges, [&](int, uint64_t nb, uint32_t) { relax(nb); })) break;
         }
-        consume_heavy_items(col, scratch, (uint32_t)nwarps, queue, [&](uint64_t, uint64_t nb) { relax(nb); });
+        consume_heavy_items(col, no_weights_t{}, scratch, (uint32_t)nwarps, queue, [&](uint64_t, uint64_t nb, uint32_t) { relax(nb); });
         __syncwarp();
         if (__any_sync(0xffffffffu, ch) && lane == 0) *changed = 1u;
         warp_sum_to(edges, scanned);
@@ -245,131 +319,14 @@ struct CcSweepWork {
             const bool act = v < v_end && curr_visit[v_base + v] != 0;
             if (__ballot_sync(0xffffffffu, act) == 0) continue;
             const uint64_t ubase = v_base + c0;
-            if (!chunk_visit(off, col, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb) { relax(ubase + src, nb); })) break;
+            if (!chunk_visit(off, col, no_weights_t{}, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t) { relax(ubase + src, nb); })) break;
         }
-        consume_heavy_items(col, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb) { relax(u, nb); });
+        consume_heavy_items(col, no_weights_t{}, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t) { relax(u, nb); });
         __syncwarp();
         if (__any_sync(0xffffffffu, ch) && lane == 0) *changed = 1u;
         warp_sum_to(edges, scanned);
     }
 };
-
-/* ---- weighted walks (SSSP): edge j of the column array carries weight wt[j] (u32 array) ----------
- * A 4 KiB page of column indices holds 512 edges; their weights are 2 KiB, so they sit inside ONE
- * page of the weight array (weight page = column page / 2 for equal page sizes).  The walkers pin
- * the two pages together. */
-typedef range_d_t<uint32_t> wrange_t;
-
-BAM_DEV const range_d_t<uint64_t>& as_u64_range(const wrange_t& w) { return reinterpret_cast<const range_d_t<uint64_t>&>(w); }
-
-/* The whole warp walks cols[begin, end) page by page and calls fn(neighbour, weight) per edge. */
-template <class EdgeFn>
-BAM_DEV bool warp_walk_edges_w(const range_d_t<uint64_t>& col, const wrange_t& wt, uint64_t begin, uint64_t end, uint32_t queue,
-                               EdgeFn fn)
-{
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t epp_log = col.cache.page_size_log - 3;
-    const uint32_t wpp_log = wt.cache.page_size_log - 2;
-    for (uint64_t i = begin; i < end;) {
-        uint64_t pend = ((i >> epp_log) + 1) << epp_log;               /* first index of the next page */
-        if (pend > end) pend = end;
-        /* lane 0 asks for the column page, lane 1 for the weight page: one all-or-nothing round */
-        const range_d_t<uint64_t>& r = lane == 1 ? as_u64_range(wt) : col;
-        const uint64_t pg = lane == 1 ? (i >> wpp_log) : (i >> epp_log);
-        uint32_t slot = range_pin_page(r, 0xffffffffu, lane < 2, pg, 1, queue);
-        const uint32_t cs = __shfl_sync(0xffffffffu, slot, 0), ws = __shfl_sync(0xffffffffu, slot, 1);
-        if (cs == BAM_SLOT_ERR || ws == BAM_SLOT_ERR) {
-            if (lane < 2 && slot <= BAM_SLOT_MAX) r.release_page(slot, 1);
-            return false;
-        }
-        const uint64_t* cbase = reinterpret_cast<const uint64_t*>(col.get_cache_page_addr(cs));
-        const uint32_t* wbase = reinterpret_cast<const uint32_t*>(wt.get_cache_page_addr(ws));
-        const uint64_t cfirst = (i >> epp_log) << epp_log, wfirst = (i >> wpp_log) << wpp_log;
-        for (uint64_t j = i + lane; j < pend; j += 32) fn(cbase[j - cfirst], wbase[j - wfirst]);
-        __syncwarp();
-        if (lane < 2) r.release_page(slot, 1);
-        i = pend;
-    }
-    return true;
-}
-
-/* chunk_visit for a weighted graph: fn(src_lane, neighbour, weight) per edge. */
-template <class EdgeFn>
-BAM_DEV bool chunk_visit_w(const range_d_t<uint64_t>& off, const range_d_t<uint64_t>& col, const wrange_t& wt, uint64_t v,
-                           uint64_t u_global, bool act, uint32_t queue, graph_scratch_t* scratch, uint64_t& edges, EdgeFn fn)
-{
-    uint64_t s = 0, e = 0;
-    if (act) {
-        s = range_read<uint64_t>(off, v, queue);
-        e = range_read<uint64_t>(off, v + 1, queue);
-    }
-    __syncwarp();
-    const uint64_t deg = e - s;
-    edges += deg;
-    bool heavy = act && scratch && deg > BAM_HEAVY_EDGES;
-    if (heavy) {
-        const uint32_t n_it = (uint32_t)((deg + BAM_ITEM_EDGES - 1) / BAM_ITEM_EDGES);
-        const uint32_t base = atom_add_relaxed(&scratch->n_items, n_it);
-        const uint32_t fit = base >= scratch->capacity ? 0u : (scratch->capacity - base < n_it ? scratch->capacity - base : n_it);
-        for (uint32_t k = 0; k < fit; k++) {
-            graph_item_t* it = &scratch->items[base + k];
-            const uint64_t b0 = s + (uint64_t)k * BAM_ITEM_EDGES;
-            it->u = u_global;
-            it->begin = b0;
-            __threadfence();
-            st_release_gpu(&it->end, b0 + BAM_ITEM_EDGES < e ? b0 + BAM_ITEM_EDGES : e);
-        }
-        if (fit < n_it) { s += (uint64_t)fit * BAM_ITEM_EDGES; heavy = false; }
-    }
-    const bool light = act && !heavy && e > s;
-    uint32_t am = __ballot_sync(0xffffffffu, light);
-    bool ok = true;
-    /* one vertex after the other; every page pair is pinned by the whole warp in one round */
-    while (am && ok) {
-        const int src = __ffs(am) - 1;
-        am &= am - 1;
-        const uint64_t vs = __shfl_sync(0xffffffffu, s, src);
-        const uint64_t ve = __shfl_sync(0xffffffffu, e, src);
-        ok = warp_walk_edges_w(col, wt, vs, ve, queue, [&](uint64_t nb, uint32_t w) { fn(src, nb, w); });
-    }
-    __syncwarp();
-    return ok;
-}
-
-template <class EdgeFn>
-BAM_DEV void consume_heavy_items_w(const range_d_t<uint64_t>& col, const wrange_t& wt, graph_scratch_t* scratch,
-                                   uint32_t n_warps_total, uint32_t queue, EdgeFn fn)
-{
-    if (!scratch) return;
-    const uint32_t lane = threadIdx.x & 31u;
-    if (lane == 0) { __threadfence(); red_add_release(&scratch->producers_done, 1u); }
-    __syncwarp();
-    for (;;) {
-        uint32_t idx = 0;
-        if (lane == 0) idx = atom_add_relaxed(&scratch->cursor, 1u);
-        idx = __shfl_sync(0xffffffffu, idx, 0);
-        if (idx >= scratch->capacity) return;
-        graph_item_t* it = &scratch->items[idx];
-        uint64_t end = 0;
-        spin_t sp;
-        for (;;) {
-            uint32_t done = 0;
-            if (lane == 0) {
-                end = ld_acquire_gpu(&it->end);
-                if (end == 0 && ld_acquire_gpu(&scratch->producers_done) == n_warps_total &&
-                    ld_acquire_gpu(&scratch->n_items) <= idx) done = 1;
-                if (end == 0 && !done) end = ld_acquire_gpu(&it->end);
-            }
-            end = __shfl_sync(0xffffffffu, end, 0);
-            done = __shfl_sync(0xffffffffu, done, 0);
-            if (end != 0) break;
-            if (done) return;
-            if (__any_sync(0xffffffffu, sp.expired(col.cache.status, BAM_AT_PAGE_BUSY, idx))) return;
-        }
-        const uint64_t u = it->u, begin = it->begin;
-        if (!warp_walk_edges_w(col, wt, begin, end, queue, [&](uint64_t nb, uint32_t w) { fn(u, nb, w); })) return;
-    }
-}
 
 /* One relaxation sweep of label-correcting single-source shortest paths (benchmarks/sssp/main.cu:
  * 115-146, 174-202: kernel_*_pc): every vertex flagged in `label` offers cost + weight to its
@@ -405,9 +362,9 @@ struct SsspSweepWork {
             if (__ballot_sync(0xffffffffu, act) == 0) continue;
             if (act) label[v_base + v] = 0;
             const uint64_t ubase = v_base + c0;
-            if (!chunk_visit_w(off, col, wt, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t w) { relax(ubase + src, nb, w); })) break;
+            if (!chunk_visit(off, col, wt, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t w) { relax(ubase + src, nb, w); })) break;
         }
-        consume_heavy_items_w(col, wt, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t w) { relax(u, nb, w); });
+        consume_heavy_items(col, wt, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t w) { relax(u, nb, w); });
         warp_sum_to(edges, scanned);
     }
 };
@@ -467,9 +424,9 @@ struct PrSweepWork {
             if (__ballot_sync(0xffffffffu, act) == 0) continue;
             if (act) label[v_base + v] = 0;
             const uint64_t ubase = v_base + c0;
-            if (!chunk_visit(off, col, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb) { push(ubase + src, nb); })) break;
+            if (!chunk_visit(off, col, no_weights_t{}, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t) { push(ubase + src, nb); })) break;
         }
-        consume_heavy_items(col, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb) { push(u, nb); });
+        consume_heavy_items(col, no_weights_t{}, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t) { push(u, nb); });
         warp_sum_to(edges, scanned);
     }
 };
@@ -571,7 +528,8 @@ static int prepare_scratch(void* scratch_dev, uint64_t scratch_bytes, cudaStream
 
 extern "C" uint64_t bam_graph_scratch_bytes(uint64_t n_edges)
 {
-    return offsetof(graph_scratch_t, items) + (n_edges / BAM_ITEM_EDGES + n_edges / BAM_HEAVY_EDGES + 1024) * sizeof(graph_item_t);
+    /* a heavy list of d edges gives at most d / BAM_ITEM_EDGES + 2 items, and there are at most n_edges / BAM_HEAVY_EDGES heavy lists */
+    return offsetof(graph_scratch_t, items) + (n_edges / BAM_ITEM_EDGES + 2 * (n_edges / BAM_HEAVY_EDGES) + 1024) * sizeof(graph_item_t);
 }
 
 static int check_graph_args(bam_array_t offsets, bam_array_t cols)

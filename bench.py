@@ -379,7 +379,8 @@ def measure_graph(kind, args, rank, world, dev_index, steps, warmup, link_agg):
     if rank == 0:
         t = t_ms * 1e-3 / len(times)
         link = ios_all * PAGE / t / 1e9
-        res = {"gteps": scanned_all / t / 1e9, "ms": t * 1e3, ("levels" if bfs else "sweeps"): iters,
+        res = {"gteps": scanned_all / t / 1e9, "ms": t * 1e3, "ms_best_step_rank0": float(min(times)),
+               ("levels" if bfs else "sweeps"): iters,
                "steps": steps, "warmup": warmup,
                "graph": f"R-MAT scale {scale}, edge factor 16 (a,b,c = .57,.19,.19), undirected, de-duplicated",
                "vertices": n, "directed_edges": m, "cache_gib_per_gpu": cache_gib, "source": src if bfs else None,
