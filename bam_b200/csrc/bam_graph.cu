@@ -131,20 +131,18 @@ BAM_DEV void chunk_offsets(const range_d_t<uint64_t>& off, uint64_t v, bool act,
     e = act ? (lane == 31 ? after : next) : 0;
 }
 
-/* One chunk of 32 consecutive local vertices (lane <-> vertex v, act = vertex is in the frontier).
- * Offsets come through the cache (chunk_offsets).  Without weights the FIRST edge page of every active
- * vertex is pinned in one cooperative call (lanes that share a page share a pin, and all missing pages are
- * in flight together) and lists that continue on further pages are walked from there; with weights every
- * vertex's list is walked in turn (column and weight pages pinned together); heavy lists become work
- * items.  fn(src_lane, neighbour, weight) is called for every edge. */
+/* One chunk of 32 consecutive local vertices (lane <-> vertex with row offsets [s, e), act = vertex is in
+ * the frontier; s == e == 0 for the others).  Without weights the FIRST edge page of every active vertex is
+ * pinned in one cooperative call (lanes that share a page share a pin, and all missing pages are in flight
+ * together) and lists that continue on further pages are walked from there; with weights every vertex's
+ * list is walked in turn (column and weight pages pinned together); heavy lists become work items.
+ * fn(src_lane, neighbour, weight) is called for every edge. */
 template <class Wt, class EdgeFn>
-BAM_DEV bool chunk_visit(const range_d_t<uint64_t>& off, const range_d_t<uint64_t>& col, const Wt& wt, uint64_t v, uint64_t u_global,
+BAM_DEV bool chunk_visit(const range_d_t<uint64_t>& col, const Wt& wt, uint64_t s, uint64_t e, uint64_t u_global,
                          bool act, uint32_t queue, graph_scratch_t* scratch, uint64_t& edges, EdgeFn fn)
 {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t epp_log = col.cache.page_size_log - 3;
-    uint64_t s = 0, e = 0;
-    chunk_offsets(off, v, act, queue, s, e);
     const uint64_t deg = e - s;
     edges += deg;
     bool heavy = act && scratch && deg > BAM_HEAVY_EDGES;
@@ -248,6 +246,47 @@ BAM_DEV void consume_heavy_items(const range_d_t<uint64_t>& col, const Wt& wt, g
     }
 }
 
+/* The sweep of one warp over its chunks of 32 consecutive vertices [c0, c0 + 32), c0 = v_begin + 32 (warp +
+ * k n_warps): chunks without an active vertex are skipped, and the row offsets of the warp's next chunk with
+ * active vertices are read before the current chunk is processed (the two offset reads are out of the way
+ * when its turn comes).  Starting the page reads of the next chunk's first edge pages at that point as well
+ * was tried and gave nothing measurable: the traversals are not bound by one warp's chain of waits.
+ * active(v) says whether local vertex v takes part
+ * (it is called once per vertex and may clear the vertex's flag); fn(c0, src_lane, neighbour, weight) is
+ * called for every edge of an active vertex c0 + src_lane.  Ends with the warp's share of the heavy items. */
+template <class Wt, class ActiveFn, class EdgeFn>
+BAM_DEV void sweep_chunks(const range_d_t<uint64_t>& off, const range_d_t<uint64_t>& col, const Wt& wt, uint64_t v_begin, uint64_t v_end,
+                          uint64_t v_base, uint64_t warp, uint64_t nwarps, graph_scratch_t* scratch, uint64_t& edges, ActiveFn active,
+                          EdgeFn fn)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t queue = (uint32_t)warp;
+    struct chunk_t { uint64_t c0, s, e; bool act; };
+    auto advance = [&](uint64_t from, chunk_t& ch) {
+        for (uint64_t c0 = from; c0 < v_end; c0 += nwarps * 32) {
+            const uint64_t v = c0 + lane;
+            const bool act = v < v_end && active(v);
+            if (__ballot_sync(0xffffffffu, act) == 0u) continue;
+            ch.c0 = c0; ch.act = act;
+            chunk_offsets(off, v, act, queue, ch.s, ch.e);
+            return true;
+        }
+        return false;
+    };
+    chunk_t cur, nxt;
+    bool have = advance(v_begin + warp * 32, cur);
+    while (have) {
+        const bool have_next = advance(cur.c0 + nwarps * 32, nxt);
+        const uint64_t c0 = cur.c0;
+        const bool ok = chunk_visit(col, wt, cur.s, cur.e, v_base + c0 + lane, cur.act, queue, scratch, edges,
+                                    [&](int src, uint64_t nb, uint32_t w) { fn(c0, src, nb, w); });
+        if (!ok) break;
+        cur = nxt;
+        have = have_next;
+    }
+    consume_heavy_items(col, wt, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t w) { fn(u - v_base, 0, nb, w); });
+}
+
 struct BfsLevelWork {
     range_d_t<uint64_t> off, col;
     uint64_t v_begin, v_end;
@@ -264,7 +303,6 @@ struct BfsLevelWork {
         const uint32_t wpb = blockDim.x >> 5;
         const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
         const uint64_t nwarps = (uint64_t)nvb * wpb;
-        const uint32_t queue = (uint32_t)warp;
         uint64_t edges = 0;
         bool ch = false;
         uint32_t* lab = label;
@@ -272,13 +310,12 @@ struct BfsLevelWork {
         auto relax = [&](uint64_t nb) {
             if (lab[nb] == BAM_BFS_INF) { lab[nb] = next_level; ch = true; }
         };
-        for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
-            const uint64_t v = c0 + lane;
-            const bool act = v < v_end && label[v_base + v] == level;
-            if (__ballot_sync(0xffffffffu, act) == 0) continue;
-            if (!chunk_visit(off, col, no_weights_t{}, v, v_base + v, act, queue, scratch, edges, [&](int, uint64_t nb, uint32_t) { relax(nb); })) break;
-        }
-        consume_heavy_items(col, no_weights_t{}, scratch, (uint32_t)nwarps, queue, [&](uint64_t, uint64_t nb, uint32_t) { relax(nb); });
+        const uint32_t* labc = label;
+        const uint64_t vb0 = v_base;
+        const uint32_t lv = level;
+        sweep_chunks(off, col, no_weights_t{}, v_begin, v_end, v_base, warp, nwarps, scratch, edges,
+                     [&](uint64_t v) { return labc[vb0 + v] == lv; },
+                     [&](uint64_t, int, uint64_t nb, uint32_t) { relax(nb); });
         __syncwarp();
         if (__any_sync(0xffffffffu, ch) && lane == 0) *changed = 1u;
         warp_sum_to(edges, scanned);
@@ -302,7 +339,6 @@ struct CcSweepWork {
         const uint32_t wpb = blockDim.x >> 5;
         const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
         const uint64_t nwarps = (uint64_t)nvb * wpb;
-        const uint32_t queue = (uint32_t)warp;
         uint64_t edges = 0;
         bool ch = false;
         unsigned long long* cp = comp;
@@ -314,14 +350,11 @@ struct CcSweepWork {
             if (cu < cn) { atomicMin(&cp[nb], cu); nv[nb] = 1; ch = true; }
             else if (cn < cu) { atomicMin(&cp[u], cn); nv[u] = 1; ch = true; }
         };
-        for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
-            const uint64_t v = c0 + lane;
-            const bool act = v < v_end && curr_visit[v_base + v] != 0;
-            if (__ballot_sync(0xffffffffu, act) == 0) continue;
-            const uint64_t ubase = v_base + c0;
-            if (!chunk_visit(off, col, no_weights_t{}, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t) { relax(ubase + src, nb); })) break;
-        }
-        consume_heavy_items(col, no_weights_t{}, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t) { relax(u, nb); });
+        const uint8_t* cv = curr_visit;
+        const uint64_t vb0 = v_base;
+        sweep_chunks(off, col, no_weights_t{}, v_begin, v_end, v_base, warp, nwarps, scratch, edges,
+                     [&](uint64_t v) { return cv[vb0 + v] != 0; },
+                     [&](uint64_t c0, int src, uint64_t nb, uint32_t) { relax(vb0 + c0 + src, nb); });
         __syncwarp();
         if (__any_sync(0xffffffffu, ch) && lane == 0) *changed = 1u;
         warp_sum_to(edges, scanned);
@@ -345,26 +378,20 @@ struct SsspSweepWork {
 
     __device__ void operator()(uint32_t vb, uint32_t nvb) const
     {
-        const uint32_t lane = threadIdx.x & 31u;
         const uint32_t wpb = blockDim.x >> 5;
         const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
         const uint64_t nwarps = (uint64_t)nvb * wpb;
-        const uint32_t queue = (uint32_t)warp;
         uint64_t edges = 0;
         uint32_t* nc = new_cost;
         auto relax = [&](uint64_t u, uint64_t nb, uint32_t w) {
             const uint32_t cand = *reinterpret_cast<volatile uint32_t*>(&nc[u]) + w;
             if (*reinterpret_cast<volatile uint32_t*>(&nc[nb]) > cand) atomicMin(&nc[nb], cand);
         };
-        for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
-            const uint64_t v = c0 + lane;
-            const bool act = v < v_end && label[v_base + v] != 0;
-            if (__ballot_sync(0xffffffffu, act) == 0) continue;
-            if (act) label[v_base + v] = 0;
-            const uint64_t ubase = v_base + c0;
-            if (!chunk_visit(off, col, wt, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t w) { relax(ubase + src, nb, w); })) break;
-        }
-        consume_heavy_items(col, wt, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t w) { relax(u, nb, w); });
+        uint8_t* lb = label;
+        const uint64_t vb0 = v_base;
+        sweep_chunks(off, col, wt, v_begin, v_end, v_base, warp, nwarps, scratch, edges,
+                     [&](uint64_t v) { const bool a = lb[vb0 + v] != 0; if (a) lb[vb0 + v] = 0; return a; },
+                     [&](uint64_t c0, int src, uint64_t nb, uint32_t w) { relax(vb0 + c0 + src, nb, w); });
         warp_sum_to(edges, scanned);
     }
 };
@@ -409,24 +436,18 @@ struct PrSweepWork {
 
     __device__ void operator()(uint32_t vb, uint32_t nvb) const
     {
-        const uint32_t lane = threadIdx.x & 31u;
         const uint32_t wpb = blockDim.x >> 5;
         const uint64_t warp = (uint64_t)vb * wpb + (threadIdx.x >> 5);
         const uint64_t nwarps = (uint64_t)nvb * wpb;
-        const uint32_t queue = (uint32_t)warp;
         uint64_t edges = 0;
         unsigned long long* res = residual;
         const uint64_t* dl = delta;
         auto push = [&](uint64_t u, uint64_t nb) { atomicAdd(&res[nb], (unsigned long long)dl[u]); };
-        for (uint64_t c0 = v_begin + warp * 32; c0 < v_end; c0 += nwarps * 32) {
-            const uint64_t v = c0 + lane;
-            const bool act = v < v_end && label[v_base + v] != 0;
-            if (__ballot_sync(0xffffffffu, act) == 0) continue;
-            if (act) label[v_base + v] = 0;
-            const uint64_t ubase = v_base + c0;
-            if (!chunk_visit(off, col, no_weights_t{}, v, v_base + v, act, queue, scratch, edges, [&](int src, uint64_t nb, uint32_t) { push(ubase + src, nb); })) break;
-        }
-        consume_heavy_items(col, no_weights_t{}, scratch, (uint32_t)nwarps, queue, [&](uint64_t u, uint64_t nb, uint32_t) { push(u, nb); });
+        uint8_t* lb = label;
+        const uint64_t vb0 = v_base;
+        sweep_chunks(off, col, no_weights_t{}, v_begin, v_end, v_base, warp, nwarps, scratch, edges,
+                     [&](uint64_t v) { const bool a = lb[vb0 + v] != 0; if (a) lb[vb0 + v] = 0; return a; },
+                     [&](uint64_t c0, int src, uint64_t nb, uint32_t) { push(vb0 + c0 + src, nb); });
         warp_sum_to(edges, scanned);
     }
 };
