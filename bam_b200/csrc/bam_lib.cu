@@ -390,6 +390,9 @@ struct BulkIoWork {
 #define BAM_PATTERN_RANDOM 2u
 #define BAM_PATTERN_RANDOM_WARP 3u
 
+#ifndef BAM_PATTERN_ROWS
+#define BAM_PATTERN_ROWS 4            /* rows of a page the array[] form reads per batch */
+#endif
 #define BAM_IMPL_PTR 0u            /* every thread reads through a bam_ptr cursor (the benchmarks' "bam_ptr" type)  */
 #define BAM_IMPL_ARRAY 1u          /* every read is array[i] (their "ORIG" type, benchmarks/cache/main.cu:70)       */
 
@@ -410,7 +413,7 @@ struct PatternWork {
         uint64_t v = 0;
         if (impl == BAM_IMPL_ARRAY) {
             /* the same walks with array[] reads: indices are computed, the 16 rows of a 4 KiB page are read
-             * four at a time, and after the first read of a page the thread's translation memo serves the rest */
+             * BAM_PATTERN_ROWS at a time, and after the first read of a page the thread's translation memo serves the rest */
             const bool by_warp = pattern == BAM_PATTERN_SEQUENTIAL_WARP || pattern == BAM_PATTERN_RANDOM_WARP;
             const uint64_t nep = by_warp ? (n_warps + stride - 1) / stride : 1;
             const uint64_t w_end = by_warp ? n_warps : (n_elems + 31) / 32;
@@ -428,12 +431,12 @@ struct PatternWork {
                     if (pattern == BAM_PATTERN_SEQUENTIAL_WARP) first = (warp_id * pages + k) * epp;
                     else if (pattern == BAM_PATTERN_RANDOM_WARP) first = assignment[warp_id * pages + k] * epp;
                     else first = warp_id * 32;
-                    for (uint64_t r = 0; r < rows; r += 4) {
-                        size_t ii[4];
-                        uint64_t x[4];
+                    for (uint64_t r = 0; r < rows; r += BAM_PATTERN_ROWS) {
+                        size_t ii[BAM_PATTERN_ROWS];
+                        uint64_t x[BAM_PATTERN_ROWS];
                         uint32_t n = 0;
 #pragma unroll
-                        for (int u = 0; u < 4; u++) {
+                        for (int u = 0; u < BAM_PATTERN_ROWS; u++) {
                             uint64_t i = first + (r + u) * 32 + lane;
                             const bool ok = r + u < rows && i < limit;
                             if (ok && pattern == BAM_PATTERN_RANDOM) i = assignment[i];
@@ -441,9 +444,9 @@ struct PatternWork {
                             x[u] = 0;
                             n += ok ? 1u : 0u;          /* the valid rows are a prefix: indices grow with u */
                         }
-                        range_read_n<uint64_t, 4>(rng, ii, n, x, queue, hits, memo);
+                        range_read_n<uint64_t, BAM_PATTERN_ROWS>(rng, ii, n, x, queue, hits, memo);
 #pragma unroll
-                        for (int u = 0; u < 4; u++) v += (uint32_t)u < n ? x[u] : 0;
+                        for (int u = 0; u < BAM_PATTERN_ROWS; u++) v += (uint32_t)u < n ? x[u] : 0;
                     }
                 }
             }

@@ -381,11 +381,21 @@ BAM_DEV void range_read_n(const range_d_t<T>& r, const size_t* i, uint32_t n, T*
     for (int b = 0; b < N; b++)
         if (pr[b].slot != BAM_SLOT_NONE) dep |= opt_dep(v[b]);
     uint32_t need = 0;
+    /* one validating sample per slot: neighbours in the batch that read the same slot under the same
+     * generation (a run of accesses to one page) share it */
+    uint32_t v_slot = BAM_SLOT_NONE, v_gen = 0;
+    bool v_ok = false, v_still = false;
 #pragma unroll
     for (int b = 0; b < N; b++) {
         const uint64_t tag = r.get_global_address(r.get_page(i[b]));
-        bool still = false;
-        const bool ok = pr[b].slot != BAM_SLOT_NONE && opt_validate(r.cache, tag, pr[b], dep, &still);
+        bool still = false, ok = false;
+        if (pr[b].slot != BAM_SLOT_NONE) {
+            if (pr[b].slot == v_slot && pr[b].gen == v_gen) { ok = v_ok; still = v_still; }
+            else {
+                ok = opt_validate(r.cache, tag, pr[b], dep, &still);
+                v_slot = pr[b].slot; v_gen = pr[b].gen; v_ok = ok; v_still = still;
+            }
+        }
         if (ok) hits++;
         else if ((uint32_t)b < n) need |= 1u << b;
         if (still) { memo.tag = tag; memo.slot = pr[b].slot; memo.gen = pr[b].gen; }
