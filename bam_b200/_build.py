@@ -29,21 +29,29 @@ def nvcc_path():
     return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
 
 
-def build_library(force=False, verbose=False):
-    """Compile the CUDA library; returns the path of the .so."""
-    if not force and not _newer_than(LIB, _deps()):
-        return LIB
+PROFILE_LIB = os.path.join(HERE, "libbam_b200_prof.so")
+
+
+def build_library(force=False, verbose=False, profile=False):
+    """Compile the CUDA library; returns the path of the .so.  profile=True builds a second library with
+    -DBAM_PROFILE (cycle and event counters of the queue protocol, the cache and the controller, read with
+    bam_ctrl_profile); select it at run time with BAM_B200_LIB=<path>."""
+    lib = PROFILE_LIB if profile else LIB
+    if not force and not _newer_than(lib, _deps()):
+        return lib
     cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "-Xptxas", "-v", "-shared", "-Xcompiler", "-fPIC",
-           "-I" + os.path.join(ROOT, "include"), "-I" + CSRC, "-o", LIB]
+           "-Xptxas", "-v", "-shared", "-Xcompiler", "-fPIC"] + (["-DBAM_PROFILE"] if profile else []) + [
+           "-I" + os.path.join(ROOT, "include"), "-I" + CSRC, "-o", lib + ".tmp"]
     cmd += [os.path.join(CSRC, s) for s in SOURCES]
     res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode == 0:
+        os.replace(lib + ".tmp", lib)          # a reader never sees a half-written library
     if verbose or res.returncode != 0:
         print(res.stdout)
         print(res.stderr)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed building libbam_b200.so")
-    return LIB
+        raise RuntimeError("nvcc failed building " + os.path.basename(lib))
+    return lib
 
 
 def build_cpp_bench(force=False, name="array_bench"):

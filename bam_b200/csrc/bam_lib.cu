@@ -930,7 +930,7 @@ static int cache_reset_device(bam_cache* pc)
 {
     k_init_cache<<<pc->ctrl->num_sms * 4, 256>>>(pc->d.slots, pc->d.n_slots, pc->d.table, pc->n_buckets * BAM_BUCKET_WORDS);
     CK(cudaGetLastError());
-    CK(cudaMemset(pc->d.clock_hand, 0, 8));
+    CK(cudaMemset(pc->d.clock_hand, 0, 8 * BAM_HAND_STRIDE * BAM_MAX_HANDS));
     CK(cudaMemset(pc->d.stats, 0, sizeof(bam_stat_stripe_t) * BAM_STAT_STRIPES));
     CK(cudaDeviceSynchronize());
     return BAM_OK;
@@ -982,6 +982,7 @@ extern "C" int bam_cache_create_multi(bam_cache_t* out, const bam_ctrl_t* ctrls,
     memset(&d, 0, sizeof d);
     d.page_size = page_size; d.page_size_minus_1 = page_size - 1; d.page_size_log = log2_u32(page_size);
     d.n_slots = (uint32_t)n_pages;
+    for (d.n_hands = 1; d.n_hands < BAM_MAX_HANDS && (uint64_t)d.n_hands * 2 * BAM_SLOTS_PER_HAND <= n_pages;) d.n_hands <<= 1;
     d.bucket_mask = (uint32_t)(pc->n_buckets - 1);
     d.n_blocks_per_page = page_size / ctrl->lba_bytes;
     d.d_ctrl = ctrl->d_ctrl; d.status = status_block(ctrl); d.n_ctrls = n_ctrls;
@@ -1000,7 +1001,7 @@ extern "C" int bam_cache_create_multi(bam_cache_t* out, const bam_ctrl_t* ctrls,
     alloc((void**)&d.base_addr, n_pages * (size_t)page_size);
     alloc((void**)&d.slots, n_pages * sizeof(bam_slot_t));
     alloc((void**)&d.table, pc->n_buckets * BAM_BUCKET_WORDS * 4);
-    alloc((void**)&d.clock_hand, 8);
+    alloc((void**)&d.clock_hand, 8 * BAM_HAND_STRIDE * BAM_MAX_HANDS);
     alloc((void**)&d.stats, sizeof(bam_stat_stripe_t) * BAM_STAT_STRIPES);
     alloc((void**)&d.range_page_starts, 8 * BAM_MAX_RANGES);
     alloc((void**)&d.range_dists, 4 * BAM_MAX_RANGES);
@@ -1099,7 +1100,7 @@ extern "C" int bam_cache_invalidate_async(bam_cache_t pc, void* stream)
     cudaStream_t s = (cudaStream_t)stream;
     k_init_cache<<<pc->ctrl->num_sms * 4, 256, 0, s>>>(pc->d.slots, pc->d.n_slots, pc->d.table, pc->n_buckets * BAM_BUCKET_WORDS);
     CK(cudaGetLastError());
-    CK(cudaMemsetAsync(pc->d.clock_hand, 0, 8, s));
+    CK(cudaMemsetAsync(pc->d.clock_hand, 0, 8 * BAM_HAND_STRIDE * BAM_MAX_HANDS, s));
     return BAM_OK;
 }
 

@@ -673,6 +673,7 @@ def run_array(args):
         ctrl.check_status()
         times.append(a.elapsed_time(b)); sums.append(int(out.item()) & ((1 << 64) - 1))
     st = cache.stats()
+    prof = ctrl.profile(reset=False)                                                 # zeros unless the library was built with -DBAM_PROFILE
     want = orc.array_checksum(STORE_SEED, n_elems, ACCESS_SEED, 0, lanes, reqs)       # the oracle needs no store
     t = float(np.mean(times)) * 1e-3
     line = {"metric": "array random-read through the page cache, 1 queue pair", "value": st["read_ios"] / t, "unit": "IOPS",
@@ -684,6 +685,20 @@ def run_array(args):
             "checksum": f"{sums[-1]:#018x}", "verified": all(x == want for x in sums) and cache.audit() == 0,
             "elements_per_s": lanes * reqs / t, "gb_per_s": st["read_ios"] * PAGE / t / 1e9,
             "hit_rate": st["hits"] / max(1, st["accesses"]), "gpu_launches": args.steps}
+    if any(prof):
+        # a -DBAM_PROFILE build (BAM_B200_LIB=...): where a command's life goes, in SM cycles, summed over the steps
+        cmds, batches = max(1, prof[0]), max(1, prof[16])
+        line["protocol_counters"] = {
+            "commands": prof[0], "sq_turn_wait_cycles_per_cmd": prof[1] / cmds, "cid_cycles_per_cmd": prof[2] / cmds,
+            "publish_cycles_per_cmd": prof[3] / cmds, "completion_wait_cycles_per_cmd": prof[4] / cmds,
+            "reaps": prof[5], "cycles_per_reap": prof[6] / max(1, prof[5]), "entries_per_reap": prof[7] / max(1, prof[5]),
+            "doorbell_sweeps": prof[8], "entries_per_sweep": prof[9] / max(1, prof[8]),
+            "ctrl_batches": prof[16], "ctrl_cmds_per_batch": prof[17] / batches, "ctrl_fetch_cycles_per_batch": prof[18] / batches,
+            "ctrl_batch_cycles": prof[19] / batches, "ctrl_load_wait_cycles_per_cmd": prof[20] / max(1, prof[17]),
+            "ctrl_load_and_store_cycles_per_cmd": prof[21] / max(1, prof[17]), "ctrl_post_cycles_per_cmd": prof[22] / max(1, prof[17]),
+            "ctrl_idle_polls": prof[23], "ctrl_cycles_per_idle_poll": prof[24] / max(1, prof[23]),
+            "note": "SM cycles at the clock printed by nvidia-smi; the counters add overhead of their own, the IOPS of this "
+                    "build are lower than the product build's"}
     print(json.dumps(line), flush=True)
     arr.close(); cache.close(); ctrl.close()
 

@@ -287,6 +287,9 @@ typedef struct BAM_ALIGNAS(16) {
 #define BAM_ENTRY_EMPTY 0xffffffffu
 #define BAM_MAX_PROBE 8
 
+#define BAM_MAX_HANDS 16          /* clock hands of a large cache: an SM draws from hand smid % n_hands */
+#define BAM_SLOTS_PER_HAND 4096   /* a cache gets a further hand for every so many slots, up to BAM_MAX_HANDS */
+#define BAM_HAND_STRIDE 4         /* u64 words between two hands: one 32-byte sector each */
 #define BAM_STAT_STRIPES 64
 typedef struct BAM_ALIGNAS(32) { uint64_t hits, misses, read_ios, pad; } bam_stat_stripe_t;
 
@@ -311,11 +314,12 @@ typedef struct {
     uint32_t* table;             /* n_buckets * 8 words                          */
     uint32_t bucket_mask;        /* n_buckets - 1 (power of two)                 */
     uint32_t n_blocks_per_page;  /* logical blocks per cache page                */
-    uint64_t* clock_hand;        /* the sweep position (page_ticket in the reference) */
+    uint64_t* clock_hand;        /* the sweep positions (page_ticket in the reference): n_hands counters, one per
+                                  * 32-byte sector; hand h sweeps the slots s with s % n_hands == h */
     Controller* d_ctrl;          /* backing controller (the first one when there are several) */
     Controller** d_ctrls;        /* [n_ctrls] all backing controllers             */
     uint32_t n_ctrls;
-    uint32_t pad_;
+    uint32_t n_hands;            /* power of two; 1 for caches of fewer than BAM_SLOTS_PER_HAND * 2 slots */
     uint32_t* range_dists;       /* [BAM_MAX_RANGES] BAM_DIST_* of each range      */
     bam_stat_stripe_t* stats;    /* [BAM_STAT_STRIPES]                           */
     bam_status_t* status;

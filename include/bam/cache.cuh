@@ -16,7 +16,9 @@
  *    validate the slot's tag; eviction claims a slot with a 32-bit CAS that only succeeds on
  *    an unpinned, non-busy word, so a pinned page can never be recycled and a reader that
  *    raced with a recycle sees a tag mismatch, undoes its pin and looks the page up again.
- *  - Eviction is a clock sweep over the slots (the reference's page_ticket hand, :1802).
+ *  - Eviction is a clock sweep over the slots (the reference's page_ticket hand, :1802), with up to 16 hands
+ *    for a large cache: the SMs are dealt over the hands and every hand sweeps its own residue class of
+ *    slots, so the misses of the whole GPU do not meet on one counter.
  *  - Read-only element accesses to resident pages take no pin at all: they validate a recycle
  *    generation around the data load (opt_probe / opt_validate below) and fall back to the pinning
  *    path on any doubt.
@@ -138,8 +140,12 @@ BAM_DEV uint32_t find_slot(const page_cache_d_t& pc, uint32_t max_tries = 0xffff
 #pragma unroll 1
     for (uint32_t tries = 1;; tries++) {
         if (tries > max_tries) return BAM_SLOT_NONE;          /* caller asked for a bounded attempt */
-        const uint64_t t = atom_add_relaxed(pc.clock_hand, 1ull);
-        const uint32_t s = (uint32_t)(t % pc.n_slots);
+        /* one hand per group of SMs instead of one counter for the whole GPU (the reference's page_ticket is
+         * a single address every miss of every SM hits): hand h visits the slots s = k * n_hands + h in order */
+        const uint32_t hand = get_smid() & (pc.n_hands - 1u);
+        const uint64_t t = atom_add_relaxed(pc.clock_hand + (size_t)hand * BAM_HAND_STRIDE, 1ull);
+        const uint32_t per_hand = (pc.n_slots - hand + pc.n_hands - 1u) / pc.n_hands;       /* slots of this hand (>= 1) */
+        const uint32_t s = (uint32_t)(t % per_hand) * pc.n_hands + hand;
         bam_slot_t* sl = &pc.slots[s];
         const uint32_t st = ld_relaxed_gpu(&sl->state);
         if (st == 0u) {

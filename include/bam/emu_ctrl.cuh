@@ -110,7 +110,38 @@ BAM_DEV void emu_post_completion(const bam_emu_d_t& c, const emu_cmd_t& m, uint3
         const uint64_t dw3 = m.cid | (phase << 16) | (status << 17);
         st_release_scoped(reinterpret_cast<uint64_t*>(&e->dword[2]), dw2 | (dw3 << 32), c.sys_scope != 0);
     }
-    red_add_relaxed(s->served, 1ull);
+}
+
+/* What a processor needs from the queue descriptor to post the completions of a batch, loaded once per
+ * batch instead of once per command (the descriptor lives in global memory: five dependent loads). */
+struct emu_cq_view_t {
+    nvm_cpl_t* cq_mem;
+    uint32_t cq_mask, cq_log2, sqid;
+    bool plain;                 /* no fault plan armed: completions are posted as they are */
+};
+
+BAM_DEV emu_cq_view_t emu_cq_view(const bam_emu_d_t& c, uint32_t q)
+{
+    const bam_emu_qp_t* s = &c.qps[q];
+    emu_cq_view_t v;
+    v.cq_mem = s->cq_mem;
+    v.cq_mask = s->cq_qs - 1u;
+    v.cq_log2 = s->cq_qs_log2;
+    v.sqid = s->sqid;
+    v.plain = s->fault == nullptr || ld_relaxed_gpu(&s->fault->mode) == BAM_FAULT_NONE;
+    return v;
+}
+
+/* emu_post_completion for the common case (no fault plan), from the per-batch view; the caller counts the
+ * served commands once per batch. */
+BAM_DEV void emu_post_completion_plain(const bam_emu_d_t& c, const emu_cq_view_t& v, const emu_cmd_t& m, uint32_t status)
+{
+    const uint32_t phase = (~(m.cq_virt >> v.cq_log2)) & 1u;
+    nvm_cpl_t* e = &v.cq_mem[m.cq_virt & v.cq_mask];
+    *reinterpret_cast<volatile uint64_t*>(&e->dword[0]) = 0ull;
+    const uint64_t dw2 = m.sqhd | (v.sqid << 16);
+    const uint64_t dw3 = m.cid | (phase << 16) | (status << 17);
+    st_release_scoped(reinterpret_cast<uint64_t*>(&e->dword[2]), dw2 | (dw3 << 32), c.sys_scope != 0);
 }
 
 /* Lane 0 of a processor: look at queue pair q and, if commands are waiting, take the queue's lock,
@@ -338,6 +369,7 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
             m.prp1 = m.prp2 = m.media_off = 0; m.bytes = m.cq_virt = m.cid = m.opc = 0; m.status = BAM_SC_SUCCESS;
             if (lane < n) emu_decode(c, bq, fetch + lane, cqbase + lane, (fetch + n) & qmask, m);
             __syncwarp(full);
+            const emu_cq_view_t cqv = emu_cq_view(c, bq);
             if (lane == 0) {
                 emu_hand_back(c, bq, fetch, n);
 #ifdef BAM_PROFILE
@@ -364,13 +396,17 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
 #ifdef BAM_PROFILE
                     long long t1 = clock64();
 #endif
-                    if (status != 0xffffffffu) emu_post_completion(c, w, status);
+                    if (status != 0xffffffffu) {
+                        if (cqv.plain) emu_post_completion_plain(c, cqv, w, status);
+                        else emu_post_completion(c, w, status);
+                    }
 #ifdef BAM_PROFILE
                     BAM_PROF_ADD(c.status, 22, clock64() - t1);
 #endif
                 }
                 __syncwarp(full);
             }
+            if (lane == 0) red_add_relaxed(c.qps[bq].served, (uint64_t)n);      /* statistics: once per batch */
 #ifdef BAM_PROFILE
             if (lane == 0) BAM_PROF_ADD(c.status, 19, clock64() - pt);
 #endif

@@ -65,3 +65,17 @@ def test_rmat_csr_is_a_simple_symmetric_graph(orc, seed, scale, ef):
     for v in range(n):                                         # adjacency lists sorted
         row = cols[off[v]:off[v + 1]]
         assert (np.diff(row.astype(np.int64)) > 0).all()
+
+
+def test_ranks_are_dealt_over_uplink_groups():
+    """Placement of fewer ranks than GPUs: one GPU of every uplink group first, then the second of each."""
+    import bam_b200
+    assert bam_b200.spread_over_uplinks([[0, 1], [2, 3], [4, 5], [6, 7]]) == [0, 2, 4, 6, 1, 3, 5, 7]
+    assert bam_b200.spread_over_uplinks([[0, 2], [1, 3], [4, 6], [5, 7]])[:4] == [0, 1, 4, 5]
+    assert bam_b200.spread_over_uplinks([[0, 1, 2], [3]]) == [0, 3, 1, 2]
+    assert bam_b200.spread_over_uplinks([[0], [1], [2], [3]]) == [0, 1, 2, 3]
+    order = bam_b200.spread_over_uplinks([[3, 5, 6], [0, 7], [1, 2, 4]])
+    assert sorted(order) == list(range(8)) and {order[0], order[1], order[2]} == {3, 0, 1}
+    # as many ranks as GPUs (or no GPU at all): nothing to choose, nothing is measured
+    dev, info = bam_b200.place_rank(8, 3, "test")
+    assert info["placement"] == "identity"
