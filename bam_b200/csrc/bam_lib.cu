@@ -253,7 +253,11 @@ struct BlockReadWork {
 #ifndef BAM_ARRAY_READ_BATCH
 #define BAM_ARRAY_READ_BATCH 4
 #endif
+#ifndef BAM_ARRAY_MIN_BLOCKS
+#define BAM_ARRAY_MIN_BLOCKS BAM_MIN_BLOCKS
+#endif
 struct ArrayReadWork {
+    static constexpr int min_blocks = BAM_ARRAY_MIN_BLOCKS;
     range_d_t<uint64_t> r;
     uint64_t n_lanes, reqs_per_lane;
     const uint64_t* idx;
@@ -397,6 +401,7 @@ struct BulkIoWork {
 #define BAM_IMPL_ARRAY 1u          /* every read is array[i] (their "ORIG" type, benchmarks/cache/main.cu:70)       */
 
 struct PatternWork {
+    static constexpr int min_blocks = BAM_ARRAY_MIN_BLOCKS;
     array_d_t<uint64_t> arr;
     range_d_t<uint64_t> rng;            /* the array's single range, by value: what the array[] form reads through */
     uint32_t pattern, impl;

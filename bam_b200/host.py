@@ -387,12 +387,15 @@ def bind_to_gpu_numa(cuda_device):
         return None
 
 
-def probe_uplink_groups(n_bytes=128 << 20, shared_below=0.8):
-    """Which GPUs of this box share a host uplink, found by measurement: every visible GPU copies from
-    pinned host memory alone, then every pair copies at the same time; two GPUs whose rate falls below
-    `shared_below` of their solo rate when they copy together sit behind one uplink (a PCIe switch).
-    Returns (groups, solo_gb_per_s): groups is a list of lists of device indices.  The PCI tree in
-    sysfs is not used: on virtualised hosts it is flat and says nothing about the switches."""
+def probe_uplink_groups(n_bytes=128 << 20, shared_below=0.8, max_set=4):
+    """Which GPUs of this box share host-link capacity, found by measurement: every visible GPU copies from
+    pinned host memory alone; then sets of 2, 3 and 4 GPUs copy at the same time, and the members of a set
+    whose rate falls below `shared_below` of their solo rate sit behind one shared link.  Sets larger than
+    pairs matter: four GPUs behind one switch whose uplink carries two GPUs' worth of traffic slow down
+    only when three of them copy at once.  Returns (groups, solo_gb_per_s): groups is a list of lists of
+    device indices.  The PCI tree in sysfs is not used: on virtualised hosts it is flat and says nothing
+    about the switches."""
+    import itertools
     import torch
     n = torch.cuda.device_count()
     host, dev, streams = [], [], []
@@ -401,9 +404,9 @@ def probe_uplink_groups(n_bytes=128 << 20, shared_below=0.8):
         dev.append(torch.empty(n_bytes, dtype=torch.uint8, device=f"cuda:{d}"))
         streams.append(torch.cuda.Stream(device=d))
 
-    def run(devs):
+    def run(devs, reps=2):
         best = {d: 0.0 for d in devs}
-        for _ in range(3):
+        for _ in range(reps):
             ev = {}
             for d in devs:
                 with torch.cuda.device(d):
@@ -420,7 +423,7 @@ def probe_uplink_groups(n_bytes=128 << 20, shared_below=0.8):
 
     solo = {}
     for d in range(n):
-        solo[d] = run([d])[d]
+        solo[d] = run([d], reps=3)[d]
     parent = list(range(n))
 
     def find(x):
@@ -429,13 +432,14 @@ def probe_uplink_groups(n_bytes=128 << 20, shared_below=0.8):
             x = parent[x]
         return x
 
-    for i in range(n):
-        for j in range(i + 1, n):
-            if find(i) == find(j):
-                continue
-            both = run([i, j])
-            if min(both[i] / solo[i], both[j] / solo[j]) < shared_below:
-                parent[find(j)] = find(i)
+    for k in range(2, min(max_set, n) + 1):
+        for combo in itertools.combinations(range(n), k):
+            if len({find(d) for d in combo}) == 1:
+                continue                                  # already known to share
+            together = run(list(combo))
+            slow = [d for d in combo if together[d] / solo[d] < shared_below]
+            for d in slow[1:]:
+                parent[find(d)] = find(slow[0])
     groups = {}
     for d in range(n):
         groups.setdefault(find(d), []).append(d)

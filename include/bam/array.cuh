@@ -344,6 +344,24 @@ BAM_DEV T range_read(const range_d_t<T>& r, size_t i, uint32_t queue)
     return v;
 }
 
+/* What the batched reader could not serve at once, for one element per lane: every lane of `mask` calls it,
+ * lanes with want == true read element i -- first with the full look-up and no pin, then pinned together.
+ * Out of line: its registers stay out of the batched loop. */
+template <typename T>
+struct slow_read_t { T value; uint32_t hit; };          /* hit = 1: served without a page read or a pin */
+
+template <typename T>
+BAM_PINNED_DEV slow_read_t<T> range_read_slow(const range_d_t<T>& r, uint32_t mask, bool want, size_t i, uint32_t queue)
+{
+    slow_read_t<T> out = { T(), 0u };
+    if (want && range_try_read(r, i, out.value)) { want = false; out.hit = 1u; }
+    if (__any_sync(mask, want)) {
+        const T y = range_read_pinned(r, mask, want, i, queue);
+        if (want) out.value = y;
+    }
+    return out;
+}
+
 /* N element reads of one thread at once.  The N look-ups, slot records and element loads are issued
  * side by side (straight-line code), so a thread has N independent
  * accesses in flight instead of a chain of dependent ones; reads of the page the thread read last skip
@@ -402,22 +420,17 @@ BAM_DEV void range_read_n(const range_d_t<T>& r, const size_t* i, uint32_t n, T*
         else if (tag == memo.tag && (uint32_t)b < n) memo.tag = BAM_TAG_NONE;
     }
     if (!__any_sync(mask, need != 0u)) return;
-    /* leftovers, one per round: full look-up without a pin, then the pinning path for the warp */
+    /* leftovers, one per round, out of line: full look-up without a pin, then the pinning path for the warp */
     while (__any_sync(mask, need != 0u)) {
         const int b = need ? __ffs(need) - 1 : 0;
         size_t ii = i[0];
 #pragma unroll
         for (int k = 1; k < N; k++) if (b == k) ii = i[k];
-        T x = T();
-        bool want = need != 0u;
-        if (want && range_try_read(r, ii, x)) { want = false; hits++; }
-        if (__any_sync(mask, want)) {
-            const T y = range_read_pinned(r, mask, want, ii, queue);
-            if (want) x = y;
-        }
+        const slow_read_t<T> x = range_read_slow(r, mask, need != 0u, ii, queue);
         if (need) {
 #pragma unroll
-            for (int k = 0; k < N; k++) if (b == k) v[k] = x;
+            for (int k = 0; k < N; k++) if (b == k) v[k] = x.value;
+            hits += x.hit;
             need &= need - 1;
         }
     }

@@ -33,8 +33,15 @@
 extern __shared__ __align__(128) uint8_t bam_dyn_smem[];
 #define BAM_FUSED_SMEM BAM_EMU_SMEM_BYTES
 
+/* A workload may ask for another register budget than the default: `static constexpr int min_blocks = 2;` in
+ * the functor compiles its kernel for two resident blocks per SM (128 registers per thread instead of 80). */
+template <class Work, class = void>
+struct fused_min_blocks { static constexpr int value = BAM_MIN_BLOCKS; };
 template <class Work>
-__global__ void __launch_bounds__(BAM_THREADS, BAM_MIN_BLOCKS)
+struct fused_min_blocks<Work, decltype((void)Work::min_blocks)> { static constexpr int value = Work::min_blocks; };
+
+template <class Work>
+__global__ void __launch_bounds__(BAM_THREADS, fused_min_blocks<Work>::value)
 bam_fused(const __grid_constant__ bam_emu_d_t emu, const __grid_constant__ Work work)
 {
     if (blockIdx.x < emu.n_ctrl_blocks) {
