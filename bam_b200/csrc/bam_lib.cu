@@ -253,11 +253,11 @@ struct BlockReadWork {
 #ifndef BAM_ARRAY_READ_BATCH
 #define BAM_ARRAY_READ_BATCH 4
 #endif
-#ifndef BAM_ARRAY_MIN_BLOCKS
-#define BAM_ARRAY_MIN_BLOCKS BAM_MIN_BLOCKS
-#endif
 struct ArrayReadWork {
-    static constexpr int min_blocks = BAM_ARRAY_MIN_BLOCKS;
+    /* two resident blocks per SM (128 registers per thread): the batched reader keeps four look-ups, slot
+     * records and element loads per lane in registers; measured against three blocks of 80 registers, all-hit
+     * random reads 12.4 -> 16.4 G/s, the miss-bound scan unchanged */
+    static constexpr int min_blocks = 2;
     range_d_t<uint64_t> r;
     uint64_t n_lanes, reqs_per_lane;
     const uint64_t* idx;
@@ -401,7 +401,6 @@ struct BulkIoWork {
 #define BAM_IMPL_ARRAY 1u          /* every read is array[i] (their "ORIG" type, benchmarks/cache/main.cu:70)       */
 
 struct PatternWork {
-    static constexpr int min_blocks = BAM_ARRAY_MIN_BLOCKS;
     array_d_t<uint64_t> arr;
     range_d_t<uint64_t> rng;            /* the array's single range, by value: what the array[] form reads through */
     uint32_t pattern, impl;
@@ -1440,7 +1439,7 @@ extern "C" int bam_launch_geometry(bam_ctrl_t c, uint32_t* grid, uint32_t* ctrl_
     if (!c) return BAM_EINVAL;
     CK(cudaSetDevice(c->device));
     uint32_t g = 0;
-    int rc = fused_geometry<ArrayReadWork>(c, &g);
+    int rc = fused_geometry<BlockReadWork>(c, &g);        /* the largest grid any launcher uses (three blocks per SM) */
     if (rc) return rc;
     if (grid) *grid = g;
     if (ctrl_blocks) *ctrl_blocks = c->emu.n_ctrl_blocks;

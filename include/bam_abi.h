@@ -367,7 +367,6 @@ int bam_direct_page_sums(const uint64_t* pages_dev, uint64_t n, uint64_t store_s
 int bam_direct_checksum(const uint64_t* idx_dev, uint64_t n, uint64_t store_seed, uint64_t first_elem,
                         uint64_t* sum_out_dev, void* stream);
 
-/* Grid the launchers use: total blocks, controller blocks among them, threads per block. */
 /* The 4096-byte IDENTIFY page an emulated controller returns (cns 1: controller data; cns 0: namespace 1 of a
  * store of store_bytes bytes in logical blocks of lba_bytes), at the offsets of the NVMe specification that the
  * reference parses (src/admin.cpp:139-152, :189-198).  Needs no controller and no GPU. */
@@ -377,6 +376,9 @@ int bam_identify_page(uint32_t cns, uint64_t store_bytes, uint32_t lba_bytes, vo
  * other encoders; on_device != 0 runs the register-built form in a kernel. */
 int bam_encode_rw_command(void* out64, uint16_t cid, uint8_t opcode, uint32_t ns_id, uint64_t prp1, uint64_t prp2,
                           uint64_t start_lba, uint16_t n_blks, int on_device);
+/* The largest grid a launcher uses on this controller's GPU (three blocks per SM; some workloads run two):
+ * total blocks, controller blocks among them, threads per block.  Callers size the per-thread landing slots of
+ * bam_launch_block_read(_depth) with it. */
 int bam_launch_geometry(bam_ctrl_t c, uint32_t* grid, uint32_t* ctrl_blocks, uint32_t* threads);
 
 #ifdef __cplusplus
