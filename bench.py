@@ -58,6 +58,8 @@ def parse():
     ap.add_argument("--graph-cache-gib", type=float, default=0.0, help="page cache per GPU of the graph steps (default: 4 for BFS, 8 for CC)")
     ap.add_argument("--graph-steps", type=int, default=5, help="timed traversals per graph in the default run (BFS: twice as many)")
     ap.add_argument("--no-graphs", action="store_true", help="default run: skip the BFS and CC parts")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="default run: skip the single-queue array read and the block-level sweep (the two other configurations)")
     ap.add_argument("--graphs-last", action="store_true", help="default run: BFS and CC after the array scan instead of before it")
     ap.add_argument("--cpu-sample-lanes", type=int, default=1 << 12)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -599,6 +601,14 @@ def run_rank(args):
 
 
 def run_block(args):
+    print(json.dumps(measure_block(args)), flush=True)
+
+
+def run_array(args):
+    print(json.dumps(measure_array(args)), flush=True)
+
+
+def measure_block(args):
     """Block-level random read throughput (the nvm-block-bench shape): 4 KiB reads at seeded random
     page-aligned offsets of a 16 GiB store, no cache reuse, swept over queue count x depth.  Every
     sweep point is verified: the wrapping sum of all words read must equal the sum recomputed from the
@@ -646,10 +656,10 @@ def run_block(args):
             "config": {"workload": "block-level 4 KiB random reads", "store_gib": store_gib, "requests_per_point": n_reqs,
                        "l2": "every request reads a different 4 KiB page of a store far larger than L2"},
             "sweep": points, "verified": all(p["verified"] for p in points), "gpu_launches": 2 * len(points)}
-    print(json.dumps(line), flush=True)
+    return line
 
 
-def run_array(args):
+def measure_array(args):
     """Array random-read checksum (the nvm-array-bench shape): 2^27 u64 elements (1 GiB), 256 MiB cache,
     ONE queue pair of depth 1024, 2^20 reader lanes x 64 uniform indices; bit-exact wrapping sum."""
     import torch
@@ -699,8 +709,8 @@ def run_array(args):
             "ctrl_idle_polls": prof[23], "ctrl_cycles_per_idle_poll": prof[24] / max(1, prof[23]),
             "note": "SM cycles at the clock printed by nvidia-smi; the counters add overhead of their own, the IOPS of this "
                     "build are lower than the product build's"}
-    print(json.dumps(line), flush=True)
     arr.close(); cache.close(); ctrl.close()
+    return line
 
 
 def run_hit(args):
@@ -827,8 +837,19 @@ def main():
         cc_res, _ = measure_graph("cc", args, rank, world, local_rank, gsteps, gwarm, agg)
         graph_res["bfs"], graph_res["cc"], graph_res["keep"] = bfs_res, cc_res, keep
 
+    def graph_part_guarded():
+        # a failure of the traversal part must not cost the array-scan line; with several ranks it cannot be
+        # contained (the other ranks would wait in a collective), so there it ends the run
+        if world > 1:
+            return graph_part()
+        try:
+            graph_part()
+        except Exception as e:
+            graph_res.clear()
+            graph_res["error"] = f"{type(e).__name__}: {e}"
+
     if not args.graphs_last:
-        graph_part()
+        graph_part_guarded()
 
     t0 = time.time()
     k_ctrls = max(1, args.ctrls)
@@ -1121,7 +1142,19 @@ def main():
     del d_idx, sums, want, d_cdf, h_idx, d_stage
     torch.cuda.empty_cache()
     if args.graphs_last:
-        graph_part()
+        graph_part_guarded()
+    # ---- the other two configurations at full size (one GPU only): array random read through ONE queue pair, and the
+    # block-level queue count x depth sweep; each verified (checksum against the oracle; sums and page CRC-32s)
+    extras = {}
+    if world == 1 and not args.no_extras:
+        try:
+            a = measure_array(argparse.Namespace(**{**vars(args), "steps": 1, "ctrl_blocks": 0}))
+            extras["array_single_queue"] = {k: a[k] for k in ("value", "unit", "ms_per_step", "gb_per_s", "elements_per_s", "hit_rate",
+                                                              "checksum", "verified", "config")}
+            b = measure_block(argparse.Namespace(**{**vars(args), "store_gib": 64.0, "ctrl_blocks": 0}))
+            extras["block_sweep"] = {"best_iops": b["value"], "sweep": b["sweep"], "verified": b["verified"], "config": b["config"]}
+        except Exception as e:
+            extras["error"] = f"{type(e).__name__}: {e}"
     # ---- CPU baselines last: nothing that runs on the host cores precedes a GPU measurement ----------------
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
@@ -1154,7 +1187,15 @@ def main():
                                  if use_ref_code else "; CPU restatement of the reference's protocol")}
             except Exception as e:  # the baseline is reported, never required
                 line["cpu_baseline"] = {"value": None, "unit": "IOPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
-        if graph_res:
+        if extras:
+            line.update(extras)
+            line["gpu_launches"] += 1 + 24
+            line["verified"] = bool(line["verified"] and "error" not in extras and extras["array_single_queue"]["verified"]
+                                    and extras["block_sweep"]["verified"])
+        if "error" in graph_res:
+            line["bfs"] = line["cc"] = {"error": graph_res["error"], "verified": False}
+            line["verified"] = False
+        elif graph_res:
             if graph_res.get("keep") is not None:
                 graph_res["bfs"]["cpu_baseline"], graph_res["cc"]["cpu_baseline"] = graph_cpu_baselines(
                     args, graph_res["keep"], int((args.graph_cache_gib or 8.0) * (1 << 30)) // PAGE)
