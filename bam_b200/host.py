@@ -469,7 +469,7 @@ def place_rank(world, local_rank, tag):
     import torch
     n = torch.cuda.device_count()
     info = {"visible_gpus": n, "placement": "identity"}
-    if world >= n or n <= 1:
+    if world >= n or n <= 1 or world == 1:           # a single rank has every link to itself: nothing to measure
         return local_rank % max(1, n), info
     path = os.path.join(tempfile.gettempdir(), f"bam_b200_placement_{tag}.json")
     try:
