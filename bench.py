@@ -360,6 +360,7 @@ def measure_graph(kind, args, rank, world, dev_index, steps, warmup, link_agg):
         loc.ctrl.check_status()
         if s >= warmup:
             times.append(a.elapsed_time(b)); ios.append(loc.cache.stats()["read_ios"])
+    prof = loc.ctrl.profile(reset=True)                       # zeros unless the library was built with -DBAM_PROFILE
     t_verify = time.time()
     ok = verify_bfs(off, cols, out, src) if bfs else verify_cc(off, cols, out)
     ok = ok and loc.cache.audit() == 0
@@ -403,6 +404,8 @@ def measure_graph(kind, args, rank, world, dev_index, steps, warmup, link_agg):
                "gpu_launches": (iters * (3 if world > 1 else 1)) * (steps + warmup), "setup_s": setup_s, "verify_s": verify_s}
         if world > 1 and not bfs:
             res["dense_exchange_sweeps"] = getattr(gr, "cc_dense_sweeps", None)
+        if any(prof):
+            res["protocol_counters"] = protocol_counters(prof)
     keep = None
     if bfs and world == 1 and not args.no_cpu_baseline:
         # what the CPU baselines need later (they run after every GPU measurement): the store image, the
@@ -608,6 +611,25 @@ def run_array(args):
     print(json.dumps(measure_array(args)), flush=True)
 
 
+def protocol_counters(prof):
+    """The 32 counters of a -DBAM_PROFILE build of the library (BAM_B200_LIB=...), per command / batch: where a
+    command's life goes, in SM cycles, summed over everything the controller has run since they were last reset."""
+    cmds, batches = max(1, prof[0]), max(1, prof[16])
+    return {
+        "commands": prof[0], "sq_turn_wait_cycles_per_cmd": prof[1] / cmds, "cid_cycles_per_cmd": prof[2] / cmds,
+        "publish_cycles_per_cmd": prof[3] / cmds, "completion_wait_cycles_per_cmd": prof[4] / cmds,
+        "reaps": prof[5], "cycles_per_reap": prof[6] / max(1, prof[5]), "entries_per_reap": prof[7] / max(1, prof[5]),
+        "doorbell_sweeps": prof[8], "entries_per_sweep": prof[9] / max(1, prof[8]),
+        "cache_lost_inserts": prof[10], "cache_evictions": prof[11], "cache_free_claims": prof[12],
+        "cache_sweep_probes_per_claim": prof[13] / max(1, prof[11] + prof[12]),
+        "ctrl_batches": prof[16], "ctrl_cmds_per_batch": prof[17] / batches, "ctrl_fetch_cycles_per_batch": prof[18] / batches,
+        "ctrl_batch_cycles": prof[19] / batches, "ctrl_load_wait_cycles_per_cmd": prof[20] / max(1, prof[17]),
+        "ctrl_load_and_store_cycles_per_cmd": prof[21] / max(1, prof[17]), "ctrl_post_cycles_per_cmd": prof[22] / max(1, prof[17]),
+        "ctrl_idle_polls": prof[23], "ctrl_cycles_per_idle_poll": prof[24] / max(1, prof[23]),
+        "note": "SM cycles at the clock printed by nvidia-smi; the counters add overhead of their own, the rates of this "
+                "build are lower than the product build's"}
+
+
 def measure_block(args):
     """Block-level random read throughput (the nvm-block-bench shape): 4 KiB reads at seeded random
     page-aligned offsets of a 16 GiB store, no cache reuse, swept over queue count x depth.  Every
@@ -696,19 +718,7 @@ def measure_array(args):
             "elements_per_s": lanes * reqs / t, "gb_per_s": st["read_ios"] * PAGE / t / 1e9,
             "hit_rate": st["hits"] / max(1, st["accesses"]), "gpu_launches": args.steps}
     if any(prof):
-        # a -DBAM_PROFILE build (BAM_B200_LIB=...): where a command's life goes, in SM cycles, summed over the steps
-        cmds, batches = max(1, prof[0]), max(1, prof[16])
-        line["protocol_counters"] = {
-            "commands": prof[0], "sq_turn_wait_cycles_per_cmd": prof[1] / cmds, "cid_cycles_per_cmd": prof[2] / cmds,
-            "publish_cycles_per_cmd": prof[3] / cmds, "completion_wait_cycles_per_cmd": prof[4] / cmds,
-            "reaps": prof[5], "cycles_per_reap": prof[6] / max(1, prof[5]), "entries_per_reap": prof[7] / max(1, prof[5]),
-            "doorbell_sweeps": prof[8], "entries_per_sweep": prof[9] / max(1, prof[8]),
-            "ctrl_batches": prof[16], "ctrl_cmds_per_batch": prof[17] / batches, "ctrl_fetch_cycles_per_batch": prof[18] / batches,
-            "ctrl_batch_cycles": prof[19] / batches, "ctrl_load_wait_cycles_per_cmd": prof[20] / max(1, prof[17]),
-            "ctrl_load_and_store_cycles_per_cmd": prof[21] / max(1, prof[17]), "ctrl_post_cycles_per_cmd": prof[22] / max(1, prof[17]),
-            "ctrl_idle_polls": prof[23], "ctrl_cycles_per_idle_poll": prof[24] / max(1, prof[23]),
-            "note": "SM cycles at the clock printed by nvidia-smi; the counters add overhead of their own, the IOPS of this "
-                    "build are lower than the product build's"}
+        line["protocol_counters"] = protocol_counters(prof)
     arr.close(); cache.close(); ctrl.close()
     return line
 
