@@ -70,6 +70,8 @@ BAM_DEV void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes)
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+/* the stage can be overwritten once the bulk store has READ it; the data may still be on its way */
+BAM_DEV void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 BAM_DEV void bulk_store_wait_all()
 {
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -310,6 +312,48 @@ BAM_DEV uint32_t emu_transfer(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t
     return BAM_SC_SUCCESS;
 }
 
+/* A transfer of one segment that fits a stage -- every 4 KiB page read or write of the cache -- can be split
+ * in two so that a mover lane overlaps the landing of one page with the load of the next:
+ * emu_load_page_overlapped starts the load into the stage, runs `while_in_flight` (the caller's chance to let
+ * the previous page land and post its completion), then waits for the load (returns false with *status set
+ * when the command must not be transferred, or with *status == 0xffffffff when the load never completed).
+ * The caller then starts the store with bulk_store and may start the next load as soon as
+ * bulk_store_wait_read() says the stage has been read. */
+BAM_DEV bool emu_one_segment(const bam_emu_d_t& c, const emu_cmd_t& m)
+{
+    const uint64_t mps = 1ull << c.mps_log2;
+    return mps == BAM_EMU_STAGE_BYTES && m.bytes <= mps - (m.prp1 & (mps - 1));
+}
+
+template <class WhileInFlight>
+BAM_DEV bool emu_load_page_overlapped(const bam_emu_d_t& c, const emu_cmd_t& m, uint32_t stage_smem, uint32_t bar, uint32_t& parity,
+                                      void*& dst, uint32_t* status, WhileInFlight while_in_flight)
+{
+    if (c.windows && !emu_in_window(c, m.prp1, m.bytes)) { while_in_flight(); *status = BAM_SC_DATA_XFER_ERROR; return false; }
+    uint8_t* media = c.qps[m.q].store + m.media_off;
+    const void* src = (m.opc == NVM_IO_READ) ? (const void*)media : (const void*)m.prp1;
+    dst = (m.opc == NVM_IO_READ) ? (void*)m.prp1 : (void*)media;
+    BAM_PROF_T0();
+    /* a WRITE's source is a cache page other threads wrote with ordinary stores: order them
+     * before the bulk engine's read */
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+    mbar_expect_tx(bar, m.bytes);
+    bulk_load(stage_smem, src, m.bytes, bar);
+    while_in_flight();
+    const uint64_t t0 = global_timer_ns();
+    uint32_t polls = 0;
+    while (!mbar_test(bar, parity)) {
+        if (((++polls) & 1023u) == 0u) {
+            const uint64_t waited = global_timer_ns() - t0;
+            if (waited > c.status->spin_timeout_ns) status_fail(c.status, BAM_ETIMEDOUT, BAM_AT_TMA, (uint64_t)dst);
+            if (waited > 2 * c.status->spin_timeout_ns) { *status = 0xffffffffu; return false; }     /* the copy never landed */
+        }
+    }
+    parity ^= 1u;
+    BAM_PROF_LAP(c.status, 20);
+    return true;
+}
+
 /* Body of a controller block.  Warps [0, BAM_EMU_WARPS) are command processors; in each, lanes
  * [0, BAM_EMU_LANES) own one 4 KiB stage and one mbarrier.  A processor reserves a batch of up to 32
  * commands from one queue under that queue's lock (held for the reservation only), every lane decodes
@@ -376,7 +420,26 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
                 { long long t = clock64(); BAM_PROF_ADD(c.status, 16, 1); BAM_PROF_ADD(c.status, 17, n); BAM_PROF_ADD(c.status, 18, t - pt); pt = t; }
 #endif
             }
-            /* the mover lanes work through the batch, BAM_EMU_LANES commands per round */
+            /* the mover lanes work through the batch, BAM_EMU_LANES commands per round.  A lane keeps the store of
+             * its previous page in flight while it loads the next one: the stage is free again as soon as the bulk
+             * store has read it, and the previous command's completion is posted once its page has landed */
+            emu_cmd_t prev;
+            bool have_prev = false;
+            auto post = [&](const emu_cmd_t& w, uint32_t status) {
+#ifdef BAM_PROFILE
+                long long t1 = clock64();
+#endif
+                if (status != 0xffffffffu) {
+                    if (cqv.plain) emu_post_completion_plain(c, cqv, w, status);
+                    else emu_post_completion(c, w, status);
+                }
+#ifdef BAM_PROFILE
+                BAM_PROF_ADD(c.status, 22, clock64() - t1);
+#endif
+            };
+            auto land_prev = [&]() {                       /* the previous page has landed: complete its command */
+                if (have_prev) { bulk_store_wait_all(); post(prev, BAM_SC_SUCCESS); have_prev = false; }
+            };
             for (uint32_t r0 = 0; r0 < n; r0 += BAM_EMU_LANES) {
                 const uint32_t src = r0 + (lane & (BAM_EMU_LANES - 1));
                 emu_cmd_t w;
@@ -392,20 +455,22 @@ BAM_DEV void emu_controller_main(const bam_emu_d_t& c, uint8_t* smem)
                 w.sqhd = (fetch + n) & qmask;
                 if (mover && src < n) {
                     uint32_t status = w.status;
-                    if (status == BAM_SC_SUCCESS) status = emu_transfer(c, w, stage_smem, bar, parity);
-#ifdef BAM_PROFILE
-                    long long t1 = clock64();
-#endif
-                    if (status != 0xffffffffu) {
-                        if (cqv.plain) emu_post_completion_plain(c, cqv, w, status);
-                        else emu_post_completion(c, w, status);
+                    if (status == BAM_SC_SUCCESS && emu_one_segment(c, w)) {
+                        if (have_prev) bulk_store_wait_read();           /* the stage is free for the next load */
+                        void* dst = nullptr;
+                        /* (the load is started inside; while it is in flight the previous page lands) */
+                        const bool loaded = emu_load_page_overlapped(c, w, stage_smem, bar, parity, dst, &status, land_prev);
+                        if (loaded) { bulk_store(dst, stage_smem, w.bytes); prev = w; have_prev = true; }
+                        else post(w, status);
+                    } else {
+                        land_prev();
+                        if (status == BAM_SC_SUCCESS) status = emu_transfer(c, w, stage_smem, bar, parity);
+                        post(w, status);
                     }
-#ifdef BAM_PROFILE
-                    BAM_PROF_ADD(c.status, 22, clock64() - t1);
-#endif
                 }
                 __syncwarp(full);
             }
+            if (mover) land_prev();
             if (lane == 0) red_add_relaxed(c.qps[bq].served, (uint64_t)n);      /* statistics: once per batch */
 #ifdef BAM_PROFILE
             if (lane == 0) BAM_PROF_ADD(c.status, 19, clock64() - pt);
