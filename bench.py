@@ -344,22 +344,27 @@ def measure_graph(kind, args, rank, world, dev_index, steps, warmup, link_agg):
     gr = bam_b200.DistCsrGraph(off, cols, rank, world, **kw) if world > 1 else bam_b200.CsrGraph(off, cols, **kw)
     loc = gr.local if world > 1 else gr
     setup_s = time.time() - t0
-    times, scanned, iters, ios = [], 0, 0, []
+    times, times_e2e, scanned, iters, ios = [], [], 0, 0, []
     out = None
+    # the end-to-end span of a step ends when the labels are in pinned host memory (the graph itself always comes
+    # from pinned host memory, page by page, through the controller)
+    h_out = torch.empty(n, dtype=torch.int32 if bfs else torch.int64).pin_memory()
     for s in range(warmup + steps):
         loc.cache.invalidate()
         loc.cache.stats(reset=True)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         a.record()
         out, iters, scanned = gr.bfs(src) if bfs else gr.cc()
         b.record()
+        h_out.copy_(out, non_blocking=True)
+        c.record()
         torch.cuda.synchronize()
         loc.ctrl.check_status()
         if s >= warmup:
-            times.append(a.elapsed_time(b)); ios.append(loc.cache.stats()["read_ios"])
+            times.append(a.elapsed_time(b)); times_e2e.append(a.elapsed_time(c)); ios.append(loc.cache.stats()["read_ios"])
     prof = loc.ctrl.profile(reset=True)                       # zeros unless the library was built with -DBAM_PROFILE
     t_verify = time.time()
     ok = verify_bfs(off, cols, out, src) if bfs else verify_cc(off, cols, out)
@@ -372,8 +377,10 @@ def measure_graph(kind, args, rank, world, dev_index, steps, warmup, link_agg):
     verify_s = time.time() - t_verify
     red = torch.tensor([float(scanned), float(np.mean(ios)), float(ok), same], dtype=torch.float64, device=dev)
     step_ms = torch.tensor(times, dtype=torch.float64, device=dev)          # every step starts at a barrier: a step takes as long as its slowest rank
+    e2e_ms = torch.tensor(times_e2e, dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(step_ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
         dist.all_reduce(red, op=dist.ReduceOp.SUM)
     scanned_all, ios_all, n_ok, n_same = (float(x) for x in red.tolist())
     step_ms = step_ms.tolist()
@@ -401,6 +408,11 @@ def measure_graph(kind, args, rank, world, dev_index, steps, warmup, link_agg):
                "verified_how": ("levels pinned by the BFS certificate on the CSR in GPU memory" if bfs else
                                 "labels equal an independent min-label fixed point computed with tensor operations on the CSR in GPU memory")
                                + ("; every rank's replica equal to rank 0's bit for bit" if world > 1 else ""),
+               "e2e": {"value": scanned_all / (float(e2e_ms.mean().item()) * 1e-3) / 1e9, "unit": "GTEPS",
+                       "ms": float(e2e_ms.mean().item()), "ms_median_step": float(e2e_ms.median().item()),
+                       "h2d_bytes_per_step": int(ios_all * PAGE), "d2h_bytes_per_step": int(h_out.numel() * h_out.element_size() * world),
+                       "note": "the traversal call with the graph in pinned host memory (every page it reads crosses the host link "
+                               "inside the timed span) plus the copy of the labels to pinned host memory"},
                "gpu_launches": (iters * (3 if world > 1 else 1)) * (steps + warmup), "setup_s": setup_s, "verify_s": verify_s}
         if world > 1 and not bfs:
             res["dense_exchange_sweeps"] = getattr(gr, "cc_dense_sweeps", None)
