@@ -70,6 +70,7 @@ SIGNATURES = {
     "bam_launch_cc_apply": (ci, [vp, vp, u64, u64, u64, vp, u64, vp, u32, u32, vp]),
     "bam_launch_cc_dense_flag": (ci, [vp, vp, vp, u64, u64, vp]),
     "bam_launch_array_write": (ci, [vp, u64, vp, u64, u64, vp]),
+    "bam_launch_thread_acquire": (ci, [vp, u64, u64, u32, vp, vp]),
     "bam_launch_pattern_read": (ci, [vp, u32, u64, u64, u64, u64, vp, vp, vp]),
     "bam_launch_pattern_read_impl": (ci, [vp, u32, u32, u64, u64, u64, u64, vp, vp, vp]),
     "bam_launch_bulk_io": (ci, [vp, u64, u64, u64, ci, vp]),

@@ -357,6 +357,33 @@ struct ArrayWriteWork {
     }
 };
 
+/* ---- the per-thread protocol ------------------------------------------------------------------------
+ * Every participating lane pins a page, reads its first element and unpins it entirely on its own, the way a
+ * diverged caller uses range_d_t::acquire_page(page, count, write, queue) (page_cache.h:1122-1224 in the
+ * reference: no warp-mates to share look-ups, slot claims or write-backs with).  `lanes` says which lanes of
+ * every warp take part; the others sit the launch out. */
+struct ThreadAcquireWork {
+    range_d_t<uint64_t> r;
+    uint64_t first_page, n_pages;
+    uint32_t lanes;
+    uint64_t* first_words;              /* first_words[k] = element 0 of page first_page + k */
+
+    __device__ void operator()(uint32_t vb, uint32_t nvb) const
+    {
+        const uint32_t lane = threadIdx.x & 31u;
+        const uint64_t warp = ((uint64_t)vb * blockDim.x + threadIdx.x) >> 5, nwarps = ((uint64_t)nvb * blockDim.x) >> 5;
+        if ((lanes >> lane) & 1u) {
+            const uint32_t per_warp = __popc(lanes), rank = __popc(lanes & ((1u << lane) - 1u));
+            for (uint64_t k = warp * per_warp + rank; k < n_pages; k += nwarps * per_warp) {
+                const uint32_t slot = r.acquire_page(first_page + k, 1, false, (uint32_t)warp);
+                if (slot > BAM_SLOT_MAX) break;                       /* the status block says why */
+                first_words[k] = ld_strong(reinterpret_cast<const uint64_t*>(r.get_cache_page_addr(slot)));
+                r.release_page(slot, 1);
+            }
+        }
+    }
+};
+
 /* ---- bulk transfer between cache memory and the store (benchmarks/readwrite/main.cu:283-390) -------
  * The reference's loader copies a chunk of a file into the cache's memory and lets a kernel issue one
  * NVMe WRITE per cache page (sequential_access_kernel with WRITE, :93-130 there); reading back is the
@@ -1276,6 +1303,18 @@ extern "C" int bam_launch_array_write(bam_array_t a, uint64_t n, const uint64_t*
     w.arr.n_elems = a->n_elems; w.arr.start_offset = 0; w.arr.n_ranges = a->n_ranges;
     w.arr.d_ranges = static_cast<range_d_t<uint64_t>*>(a->d_range);
     w.n = n; w.idx = idx_dev; w.val_seed = val_seed; w.addend = addend;
+    return launch_fused(c, w, (cudaStream_t)stream);
+}
+
+extern "C" int bam_launch_thread_acquire(bam_array_t a, uint64_t first_page, uint64_t n_pages, uint32_t lanes,
+                                         uint64_t* first_words_dev, void* stream)
+{
+    if (!a || a->elem_bytes != 8 || a->n_ranges != 1 || !first_words_dev || lanes == 0 || n_pages == 0) return BAM_EINVAL;
+    if (first_page + n_pages > a->h_range.page_count || a->h_range.page_start_offset) return BAM_EINVAL;
+    bam_ctrl* c = a->pc->ctrl;
+    CK(cudaSetDevice(c->device));
+    ThreadAcquireWork w;
+    w.r = a->h_range; w.first_page = first_page; w.n_pages = n_pages; w.lanes = lanes; w.first_words = first_words_dev;
     return launch_fused(c, w, (cudaStream_t)stream);
 }
 

@@ -289,6 +289,12 @@ class Array:
         """a[idx[k]] = splitmix64(val_seed ^ idx[k]) (addend == 0) or a[idx[k]] += addend, through the cache."""
         check(self.lib.bam_launch_array_write(self.h, n, _ptr(idx), val_seed, addend, _ptr(stream)), "bam_launch_array_write")
 
+    def thread_acquire(self, first_page, n_pages, first_words, lanes=0x80081, stream=None):
+        """The per-thread protocol: the lanes of every warp named by the bit mask `lanes` (default: lanes 0, 7
+        and 19) each pin page first_page + k on their own, store its first element in first_words[k] and unpin it."""
+        check(self.lib.bam_launch_thread_acquire(self.h, first_page, n_pages, lanes, _ptr(first_words), _ptr(stream)),
+              "bam_launch_thread_acquire")
+
     def pattern_read(self, pattern, n_elems, sum_out, n_warps=0, n_pages_per_warp=1, stride=1, assignment=None, stream=None,
                      impl=0):
         """The pattern / cache benchmark kernels: pattern 0 sequential, 1 sequential by warp, 2 random

@@ -203,6 +203,14 @@ int bam_launch_array_read(bam_array_t a, uint64_t n_lanes, uint64_t reqs_per_lan
 int bam_launch_array_write(bam_array_t a, uint64_t n, const uint64_t* idx_dev, uint64_t val_seed, uint64_t addend,
                            void* stream);
 
+/* The per-thread protocol: the lanes named by `lanes` (bit l = lane l of every warp) each pin page
+ * first_page + k of the array's single range, read its first element into first_words_dev[k] and unpin it,
+ * every lane on its own with no help from its warp-mates -- range_d_t<T>::acquire_page(page, count, write,
+ * queue) / release_page as a diverged caller uses them (page_cache.h:1122-1224, find_slot :1786-1927).  A
+ * miss whose victim is dirty writes it back itself. */
+int bam_launch_thread_acquire(bam_array_t a, uint64_t first_page, uint64_t n_pages, uint32_t lanes,
+                              uint64_t* first_words_dev, void* stream);
+
 /* Bulk transfer between the cache's memory and the store, one NVMe command per cache page (the loader
  * and the read-back of benchmarks/readwrite/main.cu:283-390): request r moves cache slot first_slot + r
  * to (write != 0) or from store page first_store_page + r.  The cache's page table is not involved: use

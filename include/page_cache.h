@@ -7,8 +7,9 @@
  *   array_t<T>(n_elems, disk_start_offset, ranges, cudaDevice)                  (:1719-1772)
  *   array_d_t<T>, range_d_t<T>, bam_ptr<T>, tlb<T,n>, bam_ptr_tlb<T,n>, page_cache_d_t (device side)
  * The host classes are thin wrappers over the C ABI (bam_abi.h); the device side is
- * include/bam/*.cuh.  Arrays of one range are supported (every benchmark of the reference
- * builds exactly one range per array).  Compile with nvcc.
+ * include/bam/*.cuh.  An array takes one or several ranges, and a range may start inside a page
+ * (page_start_offset < page_size); the page-walking launchers of the C ABI want a single range
+ * that starts on a page boundary.  Compile with nvcc.
  */
 #ifndef BAM_COMPAT_PAGE_CACHE_H
 #define BAM_COMPAT_PAGE_CACHE_H

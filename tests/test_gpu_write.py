@@ -94,3 +94,50 @@ def test_file_round_trip_through_the_store(cuda, bam, orc, tmp_path):
     assert (np.fromfile(back, dtype=np.uint8) == blob).all()
     cache.close(); ctrl.close()
 
+
+
+def test_per_thread_acquire_writes_back_dirty_victims(cuda, bam, orc):
+    """range_d_t::acquire_page as a diverged caller uses it (every lane on its own) on a cache whose every slot
+    holds a dirty page: each miss has to claim a dirty victim and write it back itself.  Waits are short
+    (5 s), so a miss that found no way forward would come back as a time-out at find_slot, not hold the launch."""
+    torch = cuda
+    pages, slots, seed, vseed = 256, 64, 13, 91
+    ctrl = bam.Controller(pages * 4096, 0, queue_depth=16, num_queues=2)
+    ctrl.configure(ctrl_blocks=2, spin_timeout_ns=5 * SEC)
+    ctrl.set_launch_timeout(60 * SEC)
+    ctrl.set_max_grid(4)                                  # two worker blocks: 16 warps x 3 lanes pin one page each at a time
+    ctrl.fill_store(seed)
+    cache = bam.PageCache(ctrl, 4096, slots)
+    arr = bam.Array(cache, pages * 512)
+    torch.cuda.synchronize()
+    before = ctrl.store_numpy().copy()
+    # element 1 of each of the first 128 pages is written: 128 dirty pages go through 64 slots, the last 64 stay
+    idx = np.arange(128, dtype=np.uint64) * np.uint64(512) + np.uint64(1)
+    d_idx = torch.from_numpy(idx.view(np.int64)).cuda()
+    arr.write(len(idx), d_idx, val_seed=vseed)
+    assert ctrl.status() == (0, "none", 0) and cache.audit() == 0
+    with np.errstate(over="ignore"):
+        new = np_splitmix64(np.uint64(vseed) ^ idx)
+    only_cached = int((ctrl.store_numpy()[idx.astype(np.int64)] != new).sum())
+    assert only_cached >= 32                              # these pages live only in the cache, dirty
+    # 128 clean pages, pinned by lanes 0, 7 and 19 of every warp, each for itself
+    first_words = torch.zeros(128, dtype=torch.int64, device="cuda")
+    cache.stats(reset=True)
+    arr.thread_acquire(128, 128, first_words)
+    assert ctrl.status() == (0, "none", 0) and cache.audit() == 0
+    got = first_words.cpu().numpy().view(np.uint64)
+    assert (got == before[(128 + np.arange(128)) * 512]).all()
+    # 128 misses went through 64 slots: every dirty page has reached the store by now, without a flush
+    after = ctrl.store_numpy()
+    assert (after[idx.astype(np.int64)] == new).all()
+    want = before.copy()
+    want[idx.astype(np.int64)] = new
+    assert (after == want).all()
+    st = cache.stats()
+    assert st["misses"] == 128 and st["read_ios"] == 128 and st["hits"] == 0
+    # argument checks
+    with pytest.raises(bam.BamError):
+        arr.thread_acquire(200, 128, first_words)         # runs past the last page of the range
+    with pytest.raises(bam.BamError):
+        arr.thread_acquire(0, 16, first_words, lanes=0)
+    arr.close(); cache.close(); ctrl.close()
