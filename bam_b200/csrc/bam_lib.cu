@@ -890,6 +890,7 @@ extern "C" int bam_ctrl_set_max_grid(bam_ctrl_t c, uint32_t max_grid)
 {
     if (!c) return BAM_EINVAL;
     c->max_grid = max_grid;
+    c->emu.max_grid = max_grid;         /* launches through the device header see it in the descriptor */
     return BAM_OK;
 }
 

@@ -250,6 +250,8 @@ typedef struct {
     const struct bam_dma_window_s* windows;
     uint32_t n_windows;
     uint32_t procs_per_queue;   /* command processors (warps) that may serve one queue; 0 = the default of 8 */
+    uint32_t max_grid;          /* host side only: cap on the blocks of a fused launch (bam_ctrl_set_max_grid), 0 = none */
+    uint32_t reserved_;
 } bam_emu_d_t;
 
 typedef struct bam_dma_window_s { uint64_t base, bytes; } bam_dma_window_t;

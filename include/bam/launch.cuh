@@ -72,7 +72,8 @@ inline uint32_t fused_max_grid(cudaError_t* err = nullptr)
 }
 
 /* Launch `work` fused with the controller described by `emu` (bam_ctrl_emu_descriptor) on stream
- * s.  max_grid caps the total number of blocks (0 = all that are co-resident).  Asynchronous. */
+ * s.  max_grid caps the total number of blocks (0 = the cap the descriptor carries, and without one all
+ * blocks that are co-resident).  Asynchronous. */
 template <class Work>
 inline cudaError_t launch_fused(const bam_emu_d_t& emu, const Work& work, cudaStream_t s = 0, uint32_t max_grid = 0,
                                 uint32_t* grid_out = nullptr)
@@ -80,6 +81,7 @@ inline cudaError_t launch_fused(const bam_emu_d_t& emu, const Work& work, cudaSt
     cudaError_t e = cudaSuccess;
     uint32_t grid = fused_max_grid<Work>(&e);
     if (e != cudaSuccess) return e;
+    if (max_grid == 0) max_grid = emu.max_grid;              /* the controller's own cap (bam_ctrl_set_max_grid) */
     if (max_grid && grid > max_grid) grid = max_grid;
     if (grid <= emu.n_ctrl_blocks) return cudaErrorInvalidConfiguration;
     const uint32_t n_work = grid - emu.n_ctrl_blocks;

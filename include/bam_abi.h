@@ -73,7 +73,9 @@ int bam_ctrl_set_launch_timeout(bam_ctrl_t c, uint64_t launch_timeout_ns);
  * the queue pairs. */
 int bam_ctrl_set_scope(bam_ctrl_t c, int system_scope);
 /* Cap the grid of the fused launches (0 = as many blocks as are co-resident).  Small caches
- * need it: each resident warp may pin up to 32 pages at once. */
+ * need it: each resident warp may pin up to 32 pages at once.  The cap also travels in the descriptor
+ * bam_ctrl_emu_descriptor returns, so bam::launch_fused of the device headers applies it to user
+ * kernels; fetch the descriptor after this call. */
 int bam_ctrl_set_max_grid(bam_ctrl_t c, uint32_t max_grid);
 /* Fault injection on the controller side (host-configured, never faults the GPU):
  * mode BAM_FAULT_DROP_CPL swallows the completion of the nth command from now,

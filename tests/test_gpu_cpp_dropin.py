@@ -80,3 +80,24 @@ def test_cpp_host_libnvm_io(cuda, bam):
     # nvm_raw_rpc: identify (into host and into GPU memory), features, refused opcodes / queue ids / memory, log pages
     assert r["bad_admin"] == 0
 
+
+
+def test_grid_cap_travels_in_the_launch_descriptor(cuda, bam):
+    """bam_ctrl_set_max_grid reaches user kernels launched through the device headers: bam::launch_fused takes
+    the cap from the descriptor bam_ctrl_emu_descriptor hands out (include/bam/launch.cuh)."""
+    import ctypes as C
+    ctrl = bam.Controller(1 << 20, 0, queue_depth=16, num_queues=2)
+    buf = (C.c_uint8 * 256)()
+
+    def max_grid():
+        assert ctrl.lib.bam_ctrl_emu_descriptor(ctrl.h, buf, 256) == 0
+        # qps (8), six 32-bit fields, three pointers, n_windows, procs_per_queue, then max_grid
+        return int.from_bytes(bytes(buf[64:68]), "little")
+
+    assert max_grid() == 0
+    ctrl.set_max_grid(5)
+    assert max_grid() == 5
+    ctrl.set_max_grid(0)
+    assert max_grid() == 0
+    assert ctrl.lib.bam_ctrl_emu_descriptor(ctrl.h, buf, 16) != 0       # a buffer too small for the descriptor
+    ctrl.close()
